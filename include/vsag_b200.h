@@ -1,0 +1,266 @@
+/*
+ * vsag_b200.h -- C ABI of the B200 (sm_100a) engine for VSAG's dense data-parallel hot path:
+ * IVF partition training (k-means), SQ8 / 1-bit RaBitQ encoders, the IVF inverted-list scan with
+ * fused top-k and fp32 rerank, and exact BruteForce kNN.
+ *
+ * This is the boundary a VSAG build binds to replace its CPU implementation of that path.  Each
+ * entry point names the reference interface it stands in for (paths are relative to the
+ * antgroup/vsag source tree).
+ *
+ * Conventions
+ *   - Every function returns 0 on success or a negative VB200_* code (same numbering as
+ *     include/vsag/vsag_c_api.h:20-34, so a caller can forward it as an Error_t code).  The text of
+ *     the last error of the calling thread is read with vb200_last_error().
+ *   - Matrices are row-major and dense.  Data pointers may be host or device pointers; the library
+ *     detects which (cudaPointerGetAttributes), stages host data through the current stream, and
+ *     returns after the results are complete in the caller's memory.  Pointers are borrowed for
+ *     the duration of the call only.
+ *   - Handles own device memory and are bound to the CUDA device current at creation.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     VB200_INTERNAL_ERROR.
+ */
+#ifndef VSAG_B200_H_
+#define VSAG_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define VB200_API __attribute__((visibility("default")))
+#else
+#define VB200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VB200_SUCCESS 0
+#define VB200_UNKNOWN_ERROR -1
+#define VB200_INTERNAL_ERROR -2
+#define VB200_INVALID_ARGUMENT -3
+#define VB200_WRONG_STATUS -4
+#define VB200_BUILD_TWICE -5
+#define VB200_INDEX_NOT_EMPTY -6
+#define VB200_UNSUPPORTED_INDEX -7
+#define VB200_UNSUPPORTED_INDEX_OPERATION -8
+#define VB200_DIMENSION_NOT_EQUAL -9
+#define VB200_INDEX_EMPTY -10
+#define VB200_NO_ENOUGH_MEMORY -11
+
+/* metric_type values of IndexCommonParam (src/index_common_param.cpp:117-174). */
+#define VB200_METRIC_L2 0
+#define VB200_METRIC_IP 1
+#define VB200_METRIC_COSINE 2
+
+/* base_quantization_type values served by the engine (src/algorithm/ivf/ivf.cpp:140-395). */
+#define VB200_QUANT_FP32 0
+#define VB200_QUANT_SQ8 1
+#define VB200_QUANT_RABITQ 2
+#define VB200_QUANT_BF16 3
+
+/* SQTrainMode (src/quantization/scalar_quantization/scalar_quantization_trainer.h:25-29). */
+#define VB200_SQ_TRAIN_CLASSIC 1
+#define VB200_SQ_TRAIN_TRUNC_BOUND 3
+
+typedef struct vb200_ivf* vb200_ivf_t;
+typedef struct vb200_bf* vb200_bf_t;
+
+/* ---------------------------------------------------------------------------------------------
+ * Library state
+ * ------------------------------------------------------------------------------------------- */
+
+/* Copies the calling thread's last error text into buf (NUL terminated) and returns its code. */
+VB200_API int vb200_last_error(char* buf, size_t buf_len);
+
+/* CUDA stream (a cudaStream_t) the calling thread's subsequent calls launch on; NULL = the
+ * default stream. */
+VB200_API int vb200_set_stream(void* cuda_stream);
+
+/* Number of kernels this library has launched in the process so far. */
+VB200_API uint64_t vb200_kernel_launches(void);
+
+/* Number of CUDA devices visible, or a negative VB200_* code. */
+VB200_API int vb200_device_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * SQ8 scalar quantizer
+ * ------------------------------------------------------------------------------------------- */
+
+/* Per-dimension bounds.  Replaces ScalarQuantizer<metric,8>::TrainImpl
+ * (src/quantization/scalar_quantization/scalar_quantizer.cpp:51-74) and
+ * ScalarQuantizationTrainer::Train (scalar_quantization_trainer.cpp:31-146): at most 100000 rows
+ * sampled as row (j * (2147483647 % n)) % n, then CLASSIC min/max or TRUNC_BOUND order
+ * statistics.  Outputs lower[dim] and diff[dim] = upper - lower, bit-equal to the reference for
+ * finite inputs. */
+VB200_API int vb200_sq8_train(const float* data, uint64_t count, uint32_t dim, int mode, float* lower, float* diff);
+
+/* codes[count x dim], one byte per dimension.  Replaces ScalarQuantizer<metric,8>::EncodeOneImpl /
+ * EncodeBatch (scalar_quantizer.cpp:85-110); bit-exact. */
+VB200_API int vb200_sq8_encode(const float* data, uint64_t count, uint32_t dim, const float* lower,
+                     const float* diff, uint8_t* codes);
+
+/* ---------------------------------------------------------------------------------------------
+ * k-means (IVF partition training)
+ * ------------------------------------------------------------------------------------------- */
+
+/* labels[i] = argmin_j |c_j|^2 - 2<c_j, x_i>, lowest j on ties; *mean_err (optional) = mean of
+ * (min + |x_i|^2).  Replaces KMeansCluster::find_nearest_one_with_blas
+ * (src/impl/cluster/kmeans_cluster.cpp:192-305) for every k (the reference switches to an
+ * approximate graph search at k >= 10000, :307-365). */
+VB200_API int vb200_kmeans_assign(const float* data, uint64_t count, uint32_t dim, const float* centroids,
+                        uint32_t k, int32_t* labels, double* mean_err);
+
+/* One centroid update from labels: mean of the members, empty clusters re-seeded from data row
+ * (j * 2654435761 + iter) % count.  Replaces kmeans_cluster.cpp:106-172.  centroids[k x dim] is
+ * overwritten, counts[k] (optional) receives the cluster sizes. */
+VB200_API int vb200_kmeans_update(const float* data, uint64_t count, uint32_t dim, const int32_t* labels,
+                        uint32_t k, uint32_t iter, float* centroids, int32_t* counts);
+
+/* `iters` Lloyd iterations starting from centroids[k x dim] (in/out).  Replaces
+ * KMeansCluster::Run (kmeans_cluster.cpp:46-190) with caller-supplied initial centroids.
+ * labels[count] (optional) receives the labels of the last assignment. */
+VB200_API int vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, int iters,
+                       float* centroids, int32_t* labels, double* mean_err);
+
+/* ---------------------------------------------------------------------------------------------
+ * RaBitQ, 1 bit per dimension, fp32 query ("standard" layout)
+ * ------------------------------------------------------------------------------------------- */
+
+/* Bytes per code record: ceil(dim/8) sign bytes padded to 4, fp32 norm, fp32 error
+ * (src/quantization/rabitq_quantization/rabitq_quantizer.cpp:102-185). */
+VB200_API uint64_t vb200_rabitq_code_size(uint32_t dim);
+
+/* centroid[dim] = rotation * mean(data).  Replaces RaBitQuantizer::TrainImpl
+ * (rabitq_quantizer.cpp:209-254); `rotation` is the dim x dim row-major orthogonal matrix the
+ * reference draws in RandomOrthogonalMatrix::Train
+ * (src/impl/transform/random_orthogonal_transformer.cpp:32-149). */
+VB200_API int vb200_rabitq_train(const float* data, uint64_t count, uint32_t dim, const float* rotation,
+                       float* centroid);
+
+/* codes[count x code_size].  Replaces RaBitQuantizer::EncodeOneInternal, 1-bit branch
+ * (rabitq_quantizer.cpp:723-857). */
+VB200_API int vb200_rabitq_encode(const float* data, uint64_t count, uint32_t dim, const float* rotation,
+                        const float* centroid, uint8_t* codes);
+
+/* out[count x (dim+1)]: rotated, centred, normalised query followed by its norm.  Replaces
+ * RaBitQuantizer::ProcessQueryImpl (rabitq_quantizer.cpp:2130-2217). */
+VB200_API int vb200_rabitq_process_query(const float* queries, uint64_t count, uint32_t dim,
+                               const float* rotation, const float* centroid, float* out);
+
+/* ---------------------------------------------------------------------------------------------
+ * IVF index (vsag::Factory::CreateIndex("ivf", ...))
+ * ------------------------------------------------------------------------------------------- */
+
+/* Replaces IVF::IVF (src/algorithm/ivf/ivf.cpp:412-474): nlist = buckets_count, quant =
+ * base_quantization_type (VB200_QUANT_FP32 is not a bucket codec here; use SQ8 or RABITQ),
+ * use_reorder keeps the fp32 rows for exact rerank (precise_quantization_type fp32). */
+VB200_API int vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_reorder,
+                     vb200_ivf_t* out);
+VB200_API int vb200_ivf_destroy(vb200_ivf_t index);
+
+/* List sharding for multi-GPU search: this handle keeps only lists l with l % world == rank.
+ * Must be called before the first add.  Default: rank 0 of 1. */
+VB200_API int vb200_ivf_set_shard(vb200_ivf_t index, uint32_t rank, uint32_t world);
+
+/* IVF::Train (ivf.cpp:564-588): k-means on the rows given (the caller has already sampled them;
+ * the reference samples with std::random_device, src/utils/util_functions.cpp:273-330), initial
+ * centroids = init[nlist x dim] or the first nlist rows when init is NULL; then trains the
+ * bucket quantizer on the same rows.  For RABITQ, `rotation` must have been set first. */
+VB200_API int vb200_ivf_train(vb200_ivf_t index, const float* data, uint64_t count, int kmeans_iters,
+                    const float* init);
+
+/* Model import/export, the pieces IVF::ExportModel / Serialize carry (ivf.cpp:990-1056,
+ * :1677-1691): centroids[nlist x dim]; SQ8 lower[dim], diff[dim]
+ * (scalar_quantizer.cpp:199-204); RaBitQ rotation[dim x dim], centroid[dim]
+ * (rabitq_quantizer.cpp:2245-2254). */
+VB200_API int vb200_ivf_set_centroids(vb200_ivf_t index, const float* centroids);
+VB200_API int vb200_ivf_get_centroids(vb200_ivf_t index, float* centroids);
+VB200_API int vb200_ivf_set_sq8_model(vb200_ivf_t index, const float* lower, const float* diff);
+VB200_API int vb200_ivf_get_sq8_model(vb200_ivf_t index, float* lower, float* diff);
+VB200_API int vb200_ivf_set_rabitq_rotation(vb200_ivf_t index, const float* rotation);
+VB200_API int vb200_ivf_set_rabitq_centroid(vb200_ivf_t index, const float* centroid);
+VB200_API int vb200_ivf_get_rabitq_centroid(vb200_ivf_t index, float* centroid);
+
+/* IVF::Add (ivf.cpp:590-724): assigns each row to its nearest centroid (exact, where the
+ * reference asks an approximate graph router), encodes it and appends it to that list in row
+ * order.  labels_in (optional) supplies the list of every row instead of computing it.
+ * ids[count] are the user labels; inner ids continue from the current element count. */
+VB200_API int vb200_ivf_add(vb200_ivf_t index, const float* data, uint64_t count, const int64_t* ids,
+                  const int32_t* labels_in);
+
+/* Number of vectors added (all shards count every row) and bytes of device memory held. */
+VB200_API int64_t vb200_ivf_num_elements(vb200_ivf_t index);
+VB200_API int64_t vb200_ivf_memory_usage(vb200_ivf_t index);
+
+/* Inverted-file layout readback for parity checks: list_sizes[nlist]; then, with offsets the
+ * exclusive prefix of the sizes, codes[total x code_size] and inner_ids[total] in list order
+ * (the layout of BucketDataCell, src/datacell/bucket_datacell.h:891-904).  Any pointer may be
+ * NULL.  code_size = dim (SQ8) or vb200_rabitq_code_size(dim). */
+VB200_API int vb200_ivf_get_lists(vb200_ivf_t index, int64_t* list_sizes, uint8_t* codes, int64_t* inner_ids);
+
+/* IVF::KnnSearch / SearchWithRequest batch branch (ivf.cpp:892-907, :2052-2354, :1693-1828):
+ * for each of nq queries, routes to the nprobe = scan_buckets_count nearest lists (exact),
+ * scans them, keeps the k best (factor*k when reorder is on, then reranks with the fp32 rows,
+ * src/impl/reorder/flatten_reorder.cpp:76-118).  ids[nq x k] user labels (-1 pad),
+ * dists[nq x k] ascending (+inf pad).
+ * bucket_ids (optional, [nq x nprobe], -1 = skip) bypasses routing like
+ * SearchRequest::bucket_ids_ (include/vsag/search_request.h:227). */
+VB200_API int vb200_ivf_search(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t k,
+                     uint32_t nprobe, float factor, const int32_t* bucket_ids, int64_t* ids,
+                     float* dists);
+
+/* Routing only, like the disable_bucket_scan search mode (IVF::route_buckets_only,
+ * ivf.cpp:1589-1660): bucket_ids[nq x nprobe] ascending by centroid distance,
+ * bucket_dists optional. */
+VB200_API int vb200_ivf_route(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t nprobe,
+                    int32_t* bucket_ids, float* bucket_dists);
+
+/* Same search, but stops before the label translation and returns this shard's partial result as
+ * device-resident sortable keys for a cross-GPU merge: keys_dev[nq x k] (uint64, distance in the
+ * high word) and labels_dev[nq x k] must be device pointers. */
+VB200_API int vb200_ivf_search_partial(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t k,
+                             uint32_t nprobe, float factor, uint64_t* keys_dev, int64_t* labels_dev);
+
+/* Logical bytes of codes the last search scanned (sum over queries of probed list lengths x
+ * code size), the figure the HBM roofline of the scan is computed from. */
+VB200_API int64_t vb200_ivf_last_scan_bytes(vb200_ivf_t index);
+
+/* Merges `parts` partial results laid out [parts][nq][k] (as gathered from the ranks) into
+ * ids[nq x k], dists[nq x k].  Inputs are device pointers; outputs host or device. */
+VB200_API int vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32_t parts,
+                         uint64_t nq, uint32_t k, int64_t* ids, float* dists);
+
+/* ---------------------------------------------------------------------------------------------
+ * BruteForce index (vsag::Factory::CreateIndex("brute_force", ...))
+ * ------------------------------------------------------------------------------------------- */
+
+/* Replaces BruteForce::BruteForce with base_quantization_type fp32 or bf16
+ * (src/algorithm/bruteforce/bruteforce.cpp:1273-1361). */
+VB200_API int vb200_bf_create(uint32_t dim, int metric, int quant, vb200_bf_t* out);
+VB200_API int vb200_bf_destroy(vb200_bf_t index);
+
+/* BruteForce::Add (bruteforce.cpp:213-293): fp32 rows; a bf16 index rounds them with
+ * generic::FloatToBF16 (src/simd/generic.cpp:198-202). */
+VB200_API int vb200_bf_add(vb200_bf_t index, const float* data, uint64_t count, const int64_t* ids);
+
+/* Rows that are already bf16 (uint16 bit patterns), for bf16 indexes only. */
+VB200_API int vb200_bf_add_bf16(vb200_bf_t index, const uint16_t* data, uint64_t count, const int64_t* ids);
+
+VB200_API int64_t vb200_bf_num_elements(vb200_bf_t index);
+
+/* BruteForce::KnnSearch (bruteforce.cpp:354-635) for a batch of nq queries (the reference takes
+ * one query per call; nq = 1 gives the same result).  ids[nq x k] labels (-1 pad),
+ * dists[nq x k] ascending (+inf pad). */
+VB200_API int vb200_bf_search(vb200_bf_t index, const float* queries, uint64_t nq, uint32_t k, int64_t* ids,
+                    float* dists);
+
+/* Partial result for a row-sharded index, see vb200_ivf_search_partial. */
+VB200_API int vb200_bf_search_partial(vb200_bf_t index, const float* queries, uint64_t nq, uint32_t k,
+                            uint64_t* keys_dev, int64_t* labels_dev);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* VSAG_B200_H_ */

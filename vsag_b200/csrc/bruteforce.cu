@@ -1,0 +1,384 @@
+// Exact BruteForce kNN over fp32 or bf16 rows: dense score slabs select a few candidates more
+// than k per query, which are then re-scored in the reference's arithmetic and ordered.
+#include "dense.cuh"
+
+namespace vb200 {
+
+constexpr uint32_t BF_SLACK = 16;                 // candidates kept beyond k before re-scoring
+constexpr uint64_t BF_COL_CHUNK = uint64_t{1} << 20;
+constexpr uint64_t BF_SLAB_FLOATS = uint64_t{256} << 20;  // 1 GiB of scores
+
+// generic::FloatToBF16 (src/simd/generic.cpp:198-202): add 0x8000, keep the high half.
+__global__ void
+float_to_bf16_kernel(const float* __restrict__ in, uint64_t n, uint16_t* __restrict__ out) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        out[i] = static_cast<uint16_t>((__float_as_uint(in[i]) + 0x8000u) >> 16);
+    }
+}
+
+// One CTA per query, one thread per candidate: distance as the reference computes it for one
+// row -- an FMA chain over the dimensions in ascending order
+// (FP32Quantizer::ComputeDistImpl, src/quantization/fp32_quantizer.cpp:163-190;
+// HalfPrecisionQuantizer, src/quantization/scalar_quantization/half_precision_quantizer.cpp:54-123)
+// -- then a sort by (distance, row).
+template <typename T>
+__global__ void __launch_bounds__(128)
+bf_rescore_kernel(const T* __restrict__ queries, uint32_t dim, const T* __restrict__ base,
+                  const uint64_t* __restrict__ cand, uint32_t ncand, uint32_t n2, uint32_t k,
+                  int metric, uint64_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    const T* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
+    const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
+    for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
+        uint64_t key = KEY_INF;
+        if (i < ncand && cq[i] != KEY_INF) {
+            uint32_t row = static_cast<uint32_t>(cq[i]);
+            const T* x = base + static_cast<uint64_t>(row) * dim;
+            float s = 0.f;
+            if (metric == VB200_METRIC_L2) {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    float t = __fsub_rn(widen(x[d]), widen(q[d]));
+                    s = fmaf(t, t, s);
+                }
+            } else {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    s = fmaf(widen(x[d]), widen(q[d]), s);
+                }
+                s = __fsub_rn(1.0f, s);
+            }
+            key = make_key(s, row);
+        }
+        keys[i] = key;
+    }
+    block_bitonic_sort(keys, n2);
+    uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+        dst[i] = i < n2 ? keys[i] : KEY_INF;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+bf_merge_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_t k, uint32_t cap,
+                uint64_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    uint32_t* state = reinterpret_cast<uint32_t*>(keys + cap);
+    BlockSelect sel;
+    sel.init(keys, state, k, cap);
+    const uint64_t* src = part + static_cast<uint64_t>(blockIdx.x) * per_query;
+    for (uint64_t base = 0; base < per_query; base += blockDim.x) {
+        sel.make_room(blockDim.x);
+        uint64_t thr = sel.threshold();
+        uint64_t i = base + threadIdx.x;
+        if (i < per_query) {
+            uint64_t key = __ldg(src + i);
+            if (key != KEY_INF) {
+                sel.offer(key, thr);
+            }
+        }
+    }
+    uint32_t cnt = sel.finish();
+    uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+        dst[i] = i < cnt ? keys[i] : KEY_INF;
+    }
+}
+
+__global__ void
+bf_results_kernel(const uint64_t* __restrict__ keys, uint64_t total, const int64_t* __restrict__ labels,
+                  int64_t* __restrict__ ids, float* __restrict__ dists, uint64_t* __restrict__ keys_out) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    uint64_t key = keys[e];
+    if (keys_out != nullptr) {
+        keys_out[e] = key;
+    }
+    if (key == KEY_INF) {
+        ids[e] = -1;
+        if (dists != nullptr) {
+            dists[e] = INFINITY;
+        }
+    } else {
+        ids[e] = labels[static_cast<uint32_t>(key)];
+        if (dists != nullptr) {
+            dists[e] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+        }
+    }
+}
+
+}  // namespace vb200
+
+using namespace vb200;
+
+struct vb200_bf {
+    uint32_t dim = 0;
+    int metric = 0, quant = 0;
+    uint64_t n = 0;
+    DevBuf<float> base_f32;
+    DevBuf<uint16_t> base_bf16;
+    DevBuf<float> norms;
+    DevBuf<int64_t> labels;
+    // search workspace
+    DevBuf<float> q_f32, scores;
+    DevBuf<uint16_t> q_bf16;
+    DevBuf<uint64_t> part, cand, keys;
+    DevBuf<int64_t> out_ids;
+    DevBuf<float> out_dists;
+    std::mutex mu;
+};
+
+template <typename T>
+static int
+bf_grow(DevBuf<T>& buf, size_t keep, size_t need) {
+    if (need <= buf.cap) {
+        return 0;
+    }
+    size_t cap = buf.cap * 2 > need ? buf.cap * 2 : need;
+    DevBuf<T> bigger;
+    if (bigger.reserve(cap) != 0) {
+        VB_TRY(bigger.reserve(need));
+    }
+    if (keep > 0) {
+        VB_CUDA(cudaMemcpyAsync(bigger.ptr, buf.ptr, keep * sizeof(T), cudaMemcpyDeviceToDevice,
+                                current_stream()));
+        VB_TRY(sync_stream());
+    }
+    buf = std::move(bigger);
+    return 0;
+}
+
+extern "C" int
+vb200_bf_create(uint32_t dim, int metric, int quant, vb200_bf_t* out) {
+    VB_CHECK_ARG(out != nullptr, "null output handle");
+    VB_CHECK_ARG(dim > 0, "dim must be positive");
+    VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP,
+                 "metric_type must be l2 or ip for this engine (got %d)", metric);
+    VB_CHECK_ARG(quant == VB200_QUANT_FP32 || quant == VB200_QUANT_BF16,
+                 "base_quantization_type must be fp32 or bf16 for this engine (got %d)", quant);
+    if (vb200_device_count() <= 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "no CUDA device available; this engine has no CPU path");
+    }
+    vb200_bf* ix = new (std::nothrow) vb200_bf();
+    if (ix == nullptr) {
+        VB_FAIL(VB200_NO_ENOUGH_MEMORY, "out of host memory");
+    }
+    ix->dim = dim;
+    ix->metric = metric;
+    ix->quant = quant;
+    *out = ix;
+    return 0;
+}
+
+extern "C" int
+vb200_bf_destroy(vb200_bf_t ix) {
+    delete ix;
+    return 0;
+}
+
+static int
+bf_append_labels_and_norms(vb200_bf* ix, const int64_t* ids, uint64_t count) {
+    VB_TRY(bf_grow(ix->labels, ix->n, ix->n + count));
+    VB_CUDA(cudaMemcpyAsync(ix->labels.ptr + ix->n, ids, count * sizeof(int64_t), cudaMemcpyDefault,
+                            current_stream()));
+    VB_TRY(bf_grow(ix->norms, ix->n, ix->n + count));
+    if (ix->quant == VB200_QUANT_FP32) {
+        VB_TRY(row_sqnorm_f32(ix->base_f32.ptr + ix->n * ix->dim, count, ix->dim, ix->norms.ptr + ix->n));
+    } else {
+        VB_TRY(row_sqnorm_bf16(ix->base_bf16.ptr + ix->n * ix->dim, count, ix->dim, ix->norms.ptr + ix->n));
+    }
+    VB_TRY(sync_stream());
+    ix->n += count;
+    return 0;
+}
+
+extern "C" int
+vb200_bf_add(vb200_bf_t ix, const float* data, uint64_t count, const int64_t* ids) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    if (count == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(data != nullptr && ids != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    VB_CHECK_ARG(ix->n + count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
+    const uint64_t elems = count * ix->dim;
+    if (ix->quant == VB200_QUANT_FP32) {
+        VB_TRY(bf_grow(ix->base_f32, ix->n * ix->dim, (ix->n + count) * ix->dim));
+        VB_CUDA(cudaMemcpyAsync(ix->base_f32.ptr + ix->n * ix->dim, data, elems * sizeof(float),
+                                cudaMemcpyDefault, current_stream()));
+    } else {
+        VB_TRY(bf_grow(ix->base_bf16, ix->n * ix->dim, (ix->n + count) * ix->dim));
+        DevInput<float> x;
+        VB_TRY(x.bind(data, elems));
+        uint64_t blocks = (elems + 255) / 256;
+        VB_CHECK_ARG(blocks <= 0x7fffffffu, "add batch too large");
+        VB_LAUNCH(float_to_bf16_kernel, static_cast<uint32_t>(blocks), 256, 0, x.ptr, elems,
+                  ix->base_bf16.ptr + ix->n * ix->dim);
+        VB_TRY(sync_stream());
+    }
+    return bf_append_labels_and_norms(ix, ids, count);
+}
+
+extern "C" int
+vb200_bf_add_bf16(vb200_bf_t ix, const uint16_t* data, uint64_t count, const int64_t* ids) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    if (count == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(data != nullptr && ids != nullptr, "null pointer");
+    VB_CHECK_ARG(ix->quant == VB200_QUANT_BF16, "index does not store bf16 rows");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    VB_CHECK_ARG(ix->n + count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
+    VB_TRY(bf_grow(ix->base_bf16, ix->n * ix->dim, (ix->n + count) * ix->dim));
+    VB_CUDA(cudaMemcpyAsync(ix->base_bf16.ptr + ix->n * ix->dim, data, count * ix->dim * sizeof(uint16_t),
+                            cudaMemcpyDefault, current_stream()));
+    return bf_append_labels_and_norms(ix, ids, count);
+}
+
+extern "C" int64_t
+vb200_bf_num_elements(vb200_bf_t ix) {
+    return ix == nullptr ? 0 : static_cast<int64_t>(ix->n);
+}
+
+// Leaves the k best keys (payload = row) per query in ix->keys.
+static int
+bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
+    const uint32_t dim = ix->dim;
+    const uint64_t n = ix->n;
+    uint32_t kcand = k + BF_SLACK;
+    if (kcand > n) {
+        kcand = static_cast<uint32_t>(n);
+    }
+    VB_CHECK_ARG(kcand <= 1024, "k = %u is too large (limit %u)", k, 1024 - BF_SLACK);
+    const bool l2 = ix->metric == VB200_METRIC_L2;
+    const bool bf16 = ix->quant == VB200_QUANT_BF16;
+
+    const float* q_dev = queries;
+    if (!is_device_pointer(queries)) {
+        VB_TRY(ix->q_f32.reserve(nq * dim));
+        VB_CUDA(cudaMemcpyAsync(ix->q_f32.ptr, queries, nq * dim * sizeof(float), cudaMemcpyHostToDevice,
+                                current_stream()));
+        q_dev = ix->q_f32.ptr;
+    }
+    if (bf16) {
+        VB_TRY(ix->q_bf16.reserve(nq * dim));
+        VB_LAUNCH(float_to_bf16_kernel, static_cast<uint32_t>((nq * dim + 255) / 256), 256, 0, q_dev,
+                  nq * dim, ix->q_bf16.ptr);
+    }
+    const uint64_t col_chunk = n < BF_COL_CHUNK ? n : BF_COL_CHUNK;
+    const uint32_t nchunks = static_cast<uint32_t>((n + col_chunk - 1) / col_chunk);
+    uint64_t q_chunk = BF_SLAB_FLOATS / col_chunk;
+    if (q_chunk < 1) {
+        q_chunk = 1;
+    }
+    if (q_chunk > nq) {
+        q_chunk = nq;
+    }
+    VB_TRY(ix->scores.reserve(q_chunk * col_chunk));
+    const uint32_t keys_ld = nchunks * kcand;
+    VB_TRY(ix->part.reserve(nq * keys_ld));
+    for (uint64_t qb = 0; qb < nq; qb += q_chunk) {
+        const uint64_t qn = nq - qb < q_chunk ? nq - qb : q_chunk;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint64_t c0 = static_cast<uint64_t>(c) * col_chunk;
+            const uint64_t cn = n - c0 < col_chunk ? n - c0 : col_chunk;
+            const float* bias = l2 ? ix->norms.ptr + c0 : nullptr;
+            const float alpha = l2 ? -2.0f : -1.0f;
+            if (bf16) {
+                VB_TRY(dense_scores_bf16(ix->q_bf16.ptr + qb * dim, qn, ix->base_bf16.ptr + c0 * dim, cn,
+                                         dim, alpha, bias, ix->scores.ptr, cn));
+            } else {
+                VB_TRY(dense_scores_f32(q_dev + qb * dim, qn, ix->base_f32.ptr + c0 * dim, cn, dim, alpha,
+                                        bias, ix->scores.ptr, cn));
+            }
+            uint32_t kc = kcand < cn ? kcand : static_cast<uint32_t>(cn);
+            if (kc < kcand) {  // short tail chunk: clear its slots first
+                VB_CUDA(cudaMemset2DAsync(ix->part.ptr + qb * keys_ld + static_cast<uint64_t>(c) * kcand,
+                                          keys_ld * sizeof(uint64_t), 0xFF, kcand * sizeof(uint64_t), qn,
+                                          current_stream()));
+            }
+            VB_TRY(select_rows(ix->scores.ptr, qn, cn, cn, kc, static_cast<uint32_t>(c0),
+                               ix->part.ptr + qb * keys_ld + static_cast<uint64_t>(c) * kcand, keys_ld));
+        }
+    }
+    const uint64_t* cand = ix->part.ptr;
+    if (nchunks > 1) {
+        VB_TRY(ix->cand.reserve(nq * kcand));
+        uint32_t cap = next_pow2(kcand + 256);
+        size_t smem = cap * sizeof(uint64_t) + 16;
+        VB_LAUNCH(bf_merge_kernel, static_cast<uint32_t>(nq), 256, smem, ix->part.ptr,
+                  static_cast<uint64_t>(keys_ld), kcand, cap, ix->cand.ptr);
+        cand = ix->cand.ptr;
+    }
+    VB_TRY(ix->keys.reserve(nq * k));
+    uint32_t n2 = next_pow2(kcand < 2 ? 2 : kcand);
+    if (bf16) {
+        VB_LAUNCH(bf_rescore_kernel<uint16_t>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t),
+                  ix->q_bf16.ptr, dim, ix->base_bf16.ptr, cand, kcand, n2, k, ix->metric, ix->keys.ptr);
+    } else {
+        VB_LAUNCH(bf_rescore_kernel<float>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev,
+                  dim, ix->base_f32.ptr, cand, kcand, n2, k, ix->metric, ix->keys.ptr);
+    }
+    return 0;
+}
+
+static int
+bf_check_search(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    VB_CHECK_ARG(queries != nullptr || nq == 0, "query pointer is null");
+    VB_CHECK_ARG(k >= 1, "k must be positive");
+    return 0;
+}
+
+extern "C" int
+vb200_bf_search(vb200_bf_t ix, const float* queries, uint64_t nq, uint32_t k, int64_t* ids,
+                float* dists) {
+    VB_TRY(bf_check_search(ix, queries, nq, k));
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(ids != nullptr && dists != nullptr, "null output pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    const uint64_t total = nq * k;
+    if (ix->n == 0) {
+        std::vector<int64_t> hi(total, -1);
+        std::vector<float> hd(total, INFINITY);
+        VB_CUDA(cudaMemcpy(ids, hi.data(), total * sizeof(int64_t), cudaMemcpyDefault));
+        VB_CUDA(cudaMemcpy(dists, hd.data(), total * sizeof(float), cudaMemcpyDefault));
+        return 0;
+    }
+    VB_TRY(bf_search_keys(ix, queries, nq, k));
+    VB_TRY(ix->out_ids.reserve(total));
+    VB_TRY(ix->out_dists.reserve(total));
+    VB_LAUNCH(bf_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, ix->keys.ptr, total,
+              ix->labels.ptr, ix->out_ids.ptr, ix->out_dists.ptr, nullptr);
+    VB_TRY(copy_out(ids, ix->out_ids.ptr, total));
+    VB_TRY(copy_out(dists, ix->out_dists.ptr, total));
+    return sync_stream();
+}
+
+extern "C" int
+vb200_bf_search_partial(vb200_bf_t ix, const float* queries, uint64_t nq, uint32_t k,
+                        uint64_t* keys_dev, int64_t* labels_dev) {
+    VB_TRY(bf_check_search(ix, queries, nq, k));
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(keys_dev != nullptr && labels_dev != nullptr, "null output pointer");
+    VB_CHECK_ARG(is_device_pointer(keys_dev) && is_device_pointer(labels_dev),
+                 "partial results are written to device memory");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    const uint64_t total = nq * k;
+    if (ix->n == 0) {
+        VB_CUDA(cudaMemsetAsync(keys_dev, 0xFF, total * sizeof(uint64_t), current_stream()));
+        VB_CUDA(cudaMemsetAsync(labels_dev, 0xFF, total * sizeof(int64_t), current_stream()));
+        return sync_stream();
+    }
+    VB_TRY(bf_search_keys(ix, queries, nq, k));
+    VB_LAUNCH(bf_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, ix->keys.ptr, total,
+              ix->labels.ptr, labels_dev, nullptr, keys_dev);
+    return sync_stream();
+}

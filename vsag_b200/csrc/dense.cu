@@ -1,0 +1,249 @@
+// Host wrappers for the fixed-order dense kernels, the row-wise top-k selector and the library
+// state (error text, stream, launch counter).
+#include "dense.cuh"
+
+namespace vb200 {
+
+// ---------------------------------------------------------------------------------------------
+// library state
+// ---------------------------------------------------------------------------------------------
+static thread_local int tl_err_code = 0;
+static thread_local char tl_err_msg[1024] = {0};
+static thread_local cudaStream_t tl_stream = nullptr;
+std::atomic<uint64_t> g_kernel_launches{0};
+
+void
+set_last_error(int code, const char* fmt, ...) {
+    tl_err_code = code;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_err_msg, sizeof(tl_err_msg), fmt, ap);
+    va_end(ap);
+}
+
+int
+last_error_code() {
+    return tl_err_code;
+}
+
+cudaStream_t
+current_stream() {
+    return tl_stream;
+}
+
+int
+sm_count() {
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0;
+        cudaDeviceProp prop;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaGetDeviceProperties(&prop, dev) == cudaSuccess) {
+            cached = prop.multiProcessorCount;
+        } else {
+            cudaGetLastError();
+            cached = 148;
+        }
+    }
+    return cached;
+}
+
+bool
+is_device_pointer(const void* p) {
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+// ---------------------------------------------------------------------------------------------
+// dense wrappers
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+static bool
+vec_ok(const T* A, const T* B, uint32_t dim) {
+    const uint32_t per = 16 / sizeof(T);
+    return dim % per == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+}
+
+template <typename T>
+static int
+dense_scores_impl(const T* A, uint64_t m, const T* B, uint64_t n, uint32_t dim, float alpha,
+                  const float* bias, float* out, uint64_t ld) {
+    if (m == 0 || n == 0) {
+        return 0;
+    }
+    const uint64_t row_tiles = (m + DENSE_BM - 1) / DENSE_BM;
+    const uint64_t col_tiles = (n + DENSE_BN - 1) / DENSE_BN;
+    // Enough column groups to fill the machine a few times over, never more than 65535.
+    uint64_t want_ctas = static_cast<uint64_t>(sm_count()) * 8;
+    uint64_t groups = (want_ctas + row_tiles - 1) / row_tiles;
+    if (groups > col_tiles) {
+        groups = col_tiles;
+    }
+    if (groups < 1) {
+        groups = 1;
+    }
+    uint32_t tiles_per_cta = static_cast<uint32_t>((col_tiles + groups - 1) / groups);
+    groups = (col_tiles + tiles_per_cta - 1) / tiles_per_cta;
+    VB_CHECK_ARG(groups <= 65535 && row_tiles <= 0x7fffffffu, "dense_scores: shape too large");
+    dim3 grid(static_cast<uint32_t>(row_tiles), static_cast<uint32_t>(groups));
+    auto kernel = vec_ok(A, B, dim) ? dense_kernel<T, T, DENSE_STORE, true>
+                                    : dense_kernel<T, T, DENSE_STORE, false>;
+    VB_LAUNCH(kernel, grid, DENSE_THREADS, 0, A, m, B, n, dim, alpha, bias, out, ld, nullptr, nullptr,
+              tiles_per_cta);
+    return 0;
+}
+
+int
+dense_scores_f32(const float* A, uint64_t m, const float* B, uint64_t n, uint32_t dim, float alpha,
+                 const float* bias, float* out, uint64_t ld) {
+    return dense_scores_impl<float>(A, m, B, n, dim, alpha, bias, out, ld);
+}
+
+int
+dense_scores_bf16(const uint16_t* A, uint64_t m, const uint16_t* B, uint64_t n, uint32_t dim,
+                  float alpha, const float* bias, float* out, uint64_t ld) {
+    return dense_scores_impl<uint16_t>(A, m, B, n, dim, alpha, bias, out, ld);
+}
+
+int
+dense_argmin_f32(const float* A, uint64_t m, const float* B, uint64_t n, uint32_t dim, float alpha,
+                 const float* bias, int32_t* labels, float* best) {
+    if (m == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(n > 0 && n < 0x7fffffffu, "dense_argmin: bad column count");
+    const uint64_t row_tiles = (m + DENSE_BM - 1) / DENSE_BM;
+    const uint64_t col_tiles = (n + DENSE_BN - 1) / DENSE_BN;
+    VB_CHECK_ARG(row_tiles <= 0x7fffffffu, "dense_argmin: too many rows");
+    dim3 grid(static_cast<uint32_t>(row_tiles), 1);
+    auto kernel = vec_ok(A, B, dim) ? dense_kernel<float, float, DENSE_ARGMIN, true>
+                                    : dense_kernel<float, float, DENSE_ARGMIN, false>;
+    VB_LAUNCH(kernel, grid, DENSE_THREADS, 0, A, m, B, n, dim, alpha, bias, nullptr, 0, labels, best,
+              static_cast<uint32_t>(col_tiles));
+    return 0;
+}
+
+template <typename T>
+__global__ void
+row_sqnorm_kernel(const T* __restrict__ M, uint64_t rows, uint32_t dim, float* __restrict__ sq) {
+    uint64_t r = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r >= rows) {
+        return;
+    }
+    const T* p = M + r * dim;
+    float s = 0.f;
+    for (uint32_t d = 0; d < dim; ++d) {
+        float v = widen(p[d]);
+        s = fmaf(v, v, s);
+    }
+    sq[r] = s;
+}
+
+int
+row_sqnorm_f32(const float* M, uint64_t rows, uint32_t dim, float* sq) {
+    if (rows == 0) {
+        return 0;
+    }
+    VB_LAUNCH(row_sqnorm_kernel<float>, static_cast<uint32_t>((rows + 127) / 128), 128, 0, M, rows,
+              dim, sq);
+    return 0;
+}
+
+int
+row_sqnorm_bf16(const uint16_t* M, uint64_t rows, uint32_t dim, float* sq) {
+    if (rows == 0) {
+        return 0;
+    }
+    VB_LAUNCH(row_sqnorm_kernel<uint16_t>, static_cast<uint32_t>((rows + 127) / 128), 128, 0, M,
+              rows, dim, sq);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// row-wise top-k over a materialised score matrix
+// ---------------------------------------------------------------------------------------------
+constexpr int SELECT_THREADS = 256;
+
+__global__ void __launch_bounds__(SELECT_THREADS)
+select_rows_kernel(const float* __restrict__ scores, uint64_t n, uint64_t ld, uint32_t k,
+                   uint32_t cap, uint32_t col_base, uint64_t* __restrict__ keys_out,
+                   uint32_t keys_ld) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    uint32_t* state = reinterpret_cast<uint32_t*>(keys + cap);
+    BlockSelect sel;
+    sel.init(keys, state, k, cap);
+    const float* row = scores + static_cast<uint64_t>(blockIdx.x) * ld;
+    for (uint64_t base = 0; base < n; base += SELECT_THREADS) {
+        sel.make_room(SELECT_THREADS);
+        uint64_t thr = sel.threshold();
+        uint64_t c = base + threadIdx.x;
+        if (c < n) {
+            float s = __ldg(row + c);
+            if (s == s) {  // NaN scores are never candidates
+                sel.offer(make_key(s, static_cast<uint32_t>(c) + col_base), thr);
+            }
+        }
+    }
+    uint32_t cnt = sel.finish();
+    uint64_t* dst = keys_out + static_cast<uint64_t>(blockIdx.x) * keys_ld;
+    for (uint32_t i = threadIdx.x; i < k; i += SELECT_THREADS) {
+        dst[i] = i < cnt ? keys[i] : KEY_INF;
+    }
+}
+
+int
+select_rows(const float* scores, uint64_t m, uint64_t n, uint64_t ld, uint32_t k, uint32_t col_base,
+            uint64_t* keys_out, uint32_t keys_ld) {
+    if (m == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(k >= 1 && k <= 1024, "select_rows: k must be in [1, 1024], got %u", k);
+    VB_CHECK_ARG(m <= 0x7fffffffu, "select_rows: too many rows");
+    uint32_t cap = next_pow2(k + SELECT_THREADS);
+    size_t smem = cap * sizeof(uint64_t) + 4 * sizeof(uint32_t);
+    VB_LAUNCH(select_rows_kernel, static_cast<uint32_t>(m), SELECT_THREADS, smem, scores, n, ld, k,
+              cap, col_base, keys_out, keys_ld);
+    return 0;
+}
+
+}  // namespace vb200
+
+// ---------------------------------------------------------------------------------------------
+// C ABI: library state
+// ---------------------------------------------------------------------------------------------
+extern "C" int
+vb200_last_error(char* buf, size_t buf_len) {
+    if (buf != nullptr && buf_len > 0) {
+        strncpy(buf, vb200::tl_err_msg, buf_len - 1);
+        buf[buf_len - 1] = 0;
+    }
+    return vb200::tl_err_code;
+}
+
+extern "C" int
+vb200_set_stream(void* cuda_stream) {
+    vb200::tl_stream = static_cast<cudaStream_t>(cuda_stream);
+    return 0;
+}
+
+extern "C" uint64_t
+vb200_kernel_launches(void) {
+    return vb200::g_kernel_launches.load();
+}
+
+extern "C" int
+vb200_device_count(void) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        VB_FAIL(VB200_INTERNAL_ERROR, "no CUDA device: %s", cudaGetErrorString(e));
+    }
+    return n;
+}

@@ -1,0 +1,1200 @@
+// IVF index: device-resident inverted lists, exact routing, the batched list-major scan
+// scheduler, the partial-result merge and the fp32 rerank.
+#include <cub/device/device_radix_sort.cuh>
+
+#include "dense.cuh"
+#include "ivf_scan.cuh"
+#include "kmeans.cuh"
+#include "rabitq.cuh"
+#include "sq8.cuh"
+
+namespace vb200 {
+
+constexpr uint32_t NONE32 = 0xFFFFFFFFu;
+constexpr uint32_t ROUTE_SLACK = 8;   // extra routing candidates re-scored exactly
+constexpr int SQ8_QT = 16;
+constexpr int RABITQ_QT = 8;
+
+template <typename T>
+static int
+grow_preserve(DevBuf<T>& buf, size_t keep, size_t need) {
+    if (need <= buf.cap) {
+        return 0;
+    }
+    size_t cap = buf.cap * 2 > need ? buf.cap * 2 : need;
+    DevBuf<T> bigger;
+    if (bigger.reserve(cap) != 0) {
+        VB_TRY(bigger.reserve(need));
+    }
+    if (keep > 0) {
+        VB_CUDA(cudaMemcpyAsync(bigger.ptr, buf.ptr, keep * sizeof(T), cudaMemcpyDeviceToDevice,
+                                current_stream()));
+        VB_TRY(sync_stream());
+    }
+    buf = std::move(bigger);
+    return 0;
+}
+
+struct SearchWorkspace {
+    DevBuf<float> queries;      // staged queries / processed RaBitQ queries
+    DevBuf<float> qproc;
+    DevBuf<float> scores;       // routing score slab
+    DevBuf<uint64_t> cand;      // routing candidates
+    DevBuf<int32_t> probes;     // [nq x nprobe]
+    DevBuf<float> probe_dists;
+    DevBuf<uint32_t> pair_cnt;  // [nlist + 1]
+    DevBuf<uint32_t> cursor;    // [nlist]
+    DevBuf<uint32_t> pair_off;  // [nlist + 1]
+    DevBuf<uint32_t> item_off;  // [nlist + 1]
+    DevBuf<uint32_t> pair_q, pair_slot;
+    DevBuf<uint32_t> thr;       // [nq]
+    DevBuf<uint64_t> part;      // [nq x nprobe x k]
+    DevBuf<uint64_t> keys;      // [nq x kscan]
+    DevBuf<uint64_t> keys2;     // [nq x k] after rerank
+    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1] item counter (as uint32)
+    DevBuf<int64_t> out_ids;
+    DevBuf<float> out_dists;
+};
+
+}  // namespace vb200
+
+using namespace vb200;
+
+struct vb200_ivf {
+    uint32_t dim = 0, nlist = 0;
+    int metric = 0, quant = 0;
+    bool use_reorder = false;
+    uint32_t shard_rank = 0, shard_world = 1;
+    uint32_t code_size = 0, code_stride = 0, dpad = 0;
+    int device = 0;
+
+    bool has_centroids = false, has_model = false, has_rotation = false;
+    DevBuf<float> centroids, c_sq;
+    DevBuf<float> lower, diff;           // SQ8, padded to dpad
+    DevBuf<float> rotation, rq_centroid; // RaBitQ
+
+    uint64_t n_total = 0;   // rows seen (inner ids 0 .. n_total-1)
+    uint64_t n_stored = 0;  // rows held by this shard
+    DevBuf<uint8_t> codes;
+    DevBuf<uint32_t> list_off;
+    std::vector<uint32_t> list_off_host;
+    DevBuf<uint32_t> pos_inner;
+    DevBuf<int64_t> labels;
+    DevBuf<float> flat;
+
+    KMeansWorkspace kws;
+    SearchWorkspace ws;
+    std::mutex mu;
+    int64_t last_scan_bytes = 0;
+};
+
+namespace vb200 {
+
+// ---------------------------------------------------------------------------------------------
+// build kernels
+// ---------------------------------------------------------------------------------------------
+
+// keys[i] = (list << 32) | i for rows this shard stores, (nlist << 32) | i otherwise; add_cnt[list]++.
+__global__ void
+ivf_make_keys_kernel(const int32_t* __restrict__ labels, uint64_t n, uint32_t nlist, uint32_t rank,
+                     uint32_t world, uint64_t* __restrict__ keys, uint32_t* __restrict__ add_cnt) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) {
+        return;
+    }
+    int32_t l = labels[i];
+    uint32_t list = nlist;
+    if (l >= 0 && static_cast<uint32_t>(l) < nlist && static_cast<uint32_t>(l) % world == rank) {
+        list = static_cast<uint32_t>(l);
+        atomicAdd(add_cnt + list, 1u);
+    }
+    keys[i] = (static_cast<uint64_t>(list) << 32) | static_cast<uint32_t>(i);
+}
+
+// Moves the rows already stored to their place in the regrown arrays (16 bytes per thread).
+__global__ void
+ivf_move_old_kernel(const uint8_t* __restrict__ old_codes, const uint32_t* __restrict__ old_inner,
+                    const uint32_t* __restrict__ old_off, const uint32_t* __restrict__ new_off,
+                    uint32_t nlist, uint64_t n_old, uint32_t stride16,
+                    uint8_t* __restrict__ new_codes, uint32_t* __restrict__ new_inner) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= n_old * stride16) {
+        return;
+    }
+    uint32_t p = static_cast<uint32_t>(e / stride16);
+    uint32_t c = static_cast<uint32_t>(e % stride16);
+    uint32_t lo = 0, hi = nlist;  // largest l with old_off[l] <= p
+    while (hi - lo > 1) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (old_off[mid] <= p) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    uint32_t np = new_off[lo] + (p - old_off[lo]);
+    reinterpret_cast<uint4*>(new_codes)[static_cast<uint64_t>(np) * stride16 + c] =
+        reinterpret_cast<const uint4*>(old_codes)[static_cast<uint64_t>(p) * stride16 + c];
+    if (c == 0) {
+        new_inner[np] = old_inner[p];
+    }
+}
+
+// Sorted key s -> destination position of its row: after the rows the list already held, in
+// ascending row order (the append order of IVF::Add with thread_count 1, ivf.cpp:662-676).
+__global__ void
+ivf_place_new_kernel(const uint64_t* __restrict__ sorted_keys, uint64_t n, uint32_t nlist,
+                     const uint32_t* __restrict__ new_off, const uint32_t* __restrict__ old_off,
+                     const uint32_t* __restrict__ add_off, uint32_t inner_base,
+                     uint32_t* __restrict__ dst_of_row, uint32_t* __restrict__ new_inner) {
+    uint64_t s = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (s >= n) {
+        return;
+    }
+    uint64_t key = sorted_keys[s];
+    uint32_t list = static_cast<uint32_t>(key >> 32);
+    uint32_t row = static_cast<uint32_t>(key);
+    if (list >= nlist) {
+        dst_of_row[row] = NONE32;
+        return;
+    }
+    uint32_t old_size = old_off[list + 1] - old_off[list];
+    uint32_t np = new_off[list] + old_size + static_cast<uint32_t>(s - add_off[list]);
+    dst_of_row[row] = np;
+    new_inner[np] = inner_base + row;
+}
+
+// ---------------------------------------------------------------------------------------------
+// search kernels
+// ---------------------------------------------------------------------------------------------
+
+// Re-scores the routing candidates of one query exactly and orders them: distance ascending,
+// lower list id first on ties.  L2: FMA chain of (q-c)^2 over d ascending; IP: 1 - chain of q*c
+// (the loop of IVF::route_buckets_only, src/algorithm/ivf/ivf.cpp:1589-1660).
+__global__ void __launch_bounds__(128)
+route_finalize_kernel(const float* __restrict__ queries, uint32_t dim,
+                      const float* __restrict__ centroids, const uint64_t* __restrict__ cand,
+                      uint32_t ncand, uint32_t n2, uint32_t nprobe, int metric,
+                      int32_t* __restrict__ probes, float* __restrict__ probe_dists) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    const float* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
+    const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
+    for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
+        uint64_t key = KEY_INF;
+        if (i < ncand && cq[i] != KEY_INF) {
+            uint32_t list = static_cast<uint32_t>(cq[i]);
+            const float* c = centroids + static_cast<uint64_t>(list) * dim;
+            float s = 0.f;
+            if (metric == VB200_METRIC_L2) {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    float t = __fsub_rn(__ldg(q + d), __ldg(c + d));
+                    s = fmaf(t, t, s);
+                }
+            } else {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    s = fmaf(__ldg(q + d), __ldg(c + d), s);
+                }
+                s = __fsub_rn(1.0f, s);
+            }
+            key = make_key(s, list);
+        }
+        keys[i] = key;
+    }
+    block_bitonic_sort(keys, n2);
+    for (uint32_t i = threadIdx.x; i < nprobe; i += blockDim.x) {
+        uint64_t key = keys[i];
+        uint64_t o = static_cast<uint64_t>(blockIdx.x) * nprobe + i;
+        probes[o] = key == KEY_INF ? -1 : static_cast<int32_t>(static_cast<uint32_t>(key));
+        if (probe_dists != nullptr) {
+            probe_dists[o] = key == KEY_INF ? INFINITY : ordered_to_float(static_cast<uint32_t>(key >> 32));
+        }
+    }
+}
+
+__device__ __forceinline__ bool
+probe_is_live(int32_t l, uint32_t nlist, uint32_t rank, uint32_t world, const uint32_t* list_off) {
+    if (l < 0 || static_cast<uint32_t>(l) >= nlist || static_cast<uint32_t>(l) % world != rank) {
+        return false;
+    }
+    return list_off[l + 1] > list_off[l];
+}
+
+__global__ void
+pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nlist, uint32_t rank,
+                  uint32_t world, const uint32_t* __restrict__ list_off, uint32_t* __restrict__ pair_cnt) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    int32_t l = probes[e];
+    if (probe_is_live(l, nlist, rank, world, list_off)) {
+        atomicAdd(pair_cnt + l, 1u);
+    }
+}
+
+// Single CTA: exclusive prefixes over the lists of (pairs) and of (tiles of qt queries), plus
+// the logical scan volume sum(pairs[l] * len[l]).
+__global__ void __launch_bounds__(1024)
+pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restrict__ list_off,
+                 uint32_t nlist, uint32_t qt, uint32_t code_size, uint32_t* __restrict__ pair_off,
+                 uint32_t* __restrict__ item_off, uint64_t* __restrict__ scalars) {
+    __shared__ uint32_t s_pairs[1024];
+    __shared__ uint32_t s_items[1024];
+    __shared__ unsigned long long s_bytes;
+    __shared__ uint32_t base_pairs, base_items;
+    if (threadIdx.x == 0) {
+        s_bytes = 0;
+        base_pairs = 0;
+        base_items = 0;
+    }
+    __syncthreads();
+    unsigned long long my_bytes = 0;
+    for (uint32_t b = 0; b < nlist; b += 1024) {
+        uint32_t l = b + threadIdx.x;
+        uint32_t c = l < nlist ? pair_cnt[l] : 0;
+        uint32_t t = (c + qt - 1) / qt;
+        if (l < nlist) {
+            my_bytes += static_cast<unsigned long long>(c) * (list_off[l + 1] - list_off[l]) * code_size;
+        }
+        s_pairs[threadIdx.x] = c;
+        s_items[threadIdx.x] = t;
+        __syncthreads();
+        for (uint32_t off = 1; off < 1024; off <<= 1) {  // Hillis-Steele inclusive scan
+            uint32_t vp = 0, vi = 0;
+            if (threadIdx.x >= off) {
+                vp = s_pairs[threadIdx.x - off];
+                vi = s_items[threadIdx.x - off];
+            }
+            __syncthreads();
+            s_pairs[threadIdx.x] += vp;
+            s_items[threadIdx.x] += vi;
+            __syncthreads();
+        }
+        if (l < nlist) {
+            pair_off[l] = base_pairs + s_pairs[threadIdx.x] - c;
+            item_off[l] = base_items + s_items[threadIdx.x] - t;
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) {
+            base_pairs += s_pairs[1023];
+            base_items += s_items[1023];
+        }
+        __syncthreads();
+    }
+    atomicAdd(&s_bytes, my_bytes);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        pair_off[nlist] = base_pairs;
+        item_off[nlist] = base_items;
+        scalars[0] = s_bytes;
+        scalars[1] = 0;  // work-queue head for the scan kernel
+    }
+}
+
+__global__ void
+pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
+                    uint32_t nlist, uint32_t rank, uint32_t world,
+                    const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ pair_off,
+                    uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_q,
+                    uint32_t* __restrict__ pair_slot) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    int32_t l = probes[e];
+    if (probe_is_live(l, nlist, rank, world, list_off)) {
+        uint32_t s = pair_off[l] + atomicAdd(cursor + l, 1u);
+        pair_q[s] = static_cast<uint32_t>(e / nprobe);
+        pair_slot[s] = static_cast<uint32_t>(e);
+    }
+}
+
+// Per query: the k smallest of its `per_query` partial keys, ascending.
+__global__ void __launch_bounds__(256)
+merge_keys_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_t k, uint32_t cap,
+                  uint64_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    uint32_t* state = reinterpret_cast<uint32_t*>(keys + cap);
+    BlockSelect sel;
+    sel.init(keys, state, k, cap);
+    const uint64_t* src = part + static_cast<uint64_t>(blockIdx.x) * per_query;
+    for (uint64_t base = 0; base < per_query; base += blockDim.x) {
+        sel.make_room(blockDim.x);
+        uint64_t thr = sel.threshold();
+        uint64_t i = base + threadIdx.x;
+        if (i < per_query) {
+            uint64_t key = __ldg(src + i);
+            if (key != KEY_INF) {
+                sel.offer(key, thr);
+            }
+        }
+    }
+    uint32_t cnt = sel.finish();
+    uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+        dst[i] = i < cnt ? keys[i] : KEY_INF;
+    }
+}
+
+// Replaces each key's payload (a code position) by the inner id stored there.
+__global__ void
+keys_pos_to_inner_kernel(uint64_t* __restrict__ keys, uint64_t total,
+                         const uint32_t* __restrict__ pos_inner) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    uint64_t key = keys[e];
+    if (key != KEY_INF) {
+        keys[e] = (key & 0xFFFFFFFF00000000ull) | pos_inner[static_cast<uint32_t>(key)];
+    }
+}
+
+// FlattenReorder::Reorder, simple path (src/impl/reorder/flatten_reorder.cpp:76-118): one CTA per
+// query recomputes every candidate against its fp32 row (one warp per candidate) and keeps k.
+__global__ void __launch_bounds__(256)
+rerank_kernel(const float* __restrict__ queries, uint32_t dim, const float* __restrict__ flat,
+              const uint64_t* __restrict__ cand, uint32_t ncand, uint32_t n2, uint32_t k, int metric,
+              uint64_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    const float* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
+    const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
+        keys[i] = KEY_INF;
+    }
+    __syncthreads();
+    for (uint32_t c = warp; c < ncand; c += nwarps) {
+        uint64_t key = cq[c];
+        if (key == KEY_INF) {
+            continue;
+        }
+        uint32_t inner = static_cast<uint32_t>(key);
+        const float* x = flat + static_cast<uint64_t>(inner) * dim;
+        float s = 0.f;
+        for (uint32_t d = lane; d < dim; d += 32) {
+            float a = __ldg(q + d), b = __ldg(x + d);
+            if (metric == VB200_METRIC_L2) {
+                float t = a - b;
+                s = fmaf(t, t, s);
+            } else {
+                s = fmaf(a, b, s);
+            }
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            s += __shfl_xor_sync(0xffffffffu, s, off);
+        }
+        if (lane == 0) {
+            float dist = metric == VB200_METRIC_L2 ? s : 1.0f - s;
+            keys[c] = make_key(dist, inner);
+        }
+    }
+    block_bitonic_sort(keys, n2);
+    uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+        dst[i] = i < n2 ? keys[i] : KEY_INF;
+    }
+}
+
+// keys (payload = inner id) -> user labels and distances.
+__global__ void
+keys_to_results_kernel(const uint64_t* __restrict__ keys, uint64_t total,
+                       const int64_t* __restrict__ labels, int64_t* __restrict__ ids,
+                       float* __restrict__ dists) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    uint64_t key = keys[e];
+    if (key == KEY_INF) {
+        ids[e] = -1;
+        dists[e] = INFINITY;
+    } else {
+        ids[e] = labels[static_cast<uint32_t>(key)];
+        dists[e] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+    }
+}
+
+// Cross-shard merge input: labels gathered beside the keys; payload = index into the gathered
+// arrays so the label can be fetched after selection.
+__global__ void
+tag_partials_kernel(const uint64_t* __restrict__ keys, uint32_t parts, uint64_t nq, uint32_t k,
+                    uint64_t* __restrict__ tagged) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    uint64_t total = static_cast<uint64_t>(parts) * nq * k;
+    if (e >= total) {
+        return;
+    }
+    // input [part][q][i] -> output [q][part][i]
+    uint64_t part = e / (nq * k);
+    uint64_t rem = e % (nq * k);
+    uint64_t q = rem / k, i = rem % k;
+    uint64_t key = keys[e];
+    uint64_t o = (q * parts + part) * k + i;
+    tagged[o] = key == KEY_INF ? KEY_INF : ((key & 0xFFFFFFFF00000000ull) | static_cast<uint32_t>(e));
+}
+
+static int
+launch_merge(const uint64_t* part, uint64_t nq, uint64_t per_query, uint32_t k, uint64_t* out) {
+    uint32_t cap = next_pow2(k + 256);
+    size_t smem = cap * sizeof(uint64_t) + 16;
+    if (smem > 48 * 1024) {
+        VB_CUDA(cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+    }
+    VB_LAUNCH(merge_keys_kernel, static_cast<uint32_t>(nq), 256, smem, part, per_query, k, cap, out);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// routing
+// ---------------------------------------------------------------------------------------------
+static int
+ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe, int32_t* probes_dev,
+                 float* dists_dev) {
+    SearchWorkspace& ws = ix->ws;
+    const uint32_t nlist = ix->nlist;
+    uint32_t ncand = nprobe + ROUTE_SLACK < nlist ? nprobe + ROUTE_SLACK : nlist;
+    VB_CHECK_ARG(ncand <= 1024, "scan_buckets_count %u is too large (limit %u)", nprobe,
+                 1024 - ROUTE_SLACK);
+    uint64_t slab = (uint64_t{256} << 20) / nlist;  // rows of a 1 GiB score slab
+    if (slab < 1) {
+        slab = 1;
+    }
+    if (slab > nq) {
+        slab = nq;
+    }
+    VB_TRY(ws.scores.reserve(slab * nlist));
+    VB_TRY(ws.cand.reserve(nq * ncand));
+    const bool l2 = ix->metric == VB200_METRIC_L2;
+    for (uint64_t b = 0; b < nq; b += slab) {
+        uint64_t n = nq - b < slab ? nq - b : slab;
+        VB_TRY(dense_scores_f32(q_dev + b * ix->dim, n, ix->centroids.ptr, nlist, ix->dim,
+                                l2 ? -2.0f : -1.0f, l2 ? ix->c_sq.ptr : nullptr, ws.scores.ptr, nlist));
+        VB_TRY(select_rows(ws.scores.ptr, n, nlist, nlist, ncand, 0, ws.cand.ptr + b * ncand, ncand));
+    }
+    uint32_t n2 = next_pow2(ncand < 2 ? 2 : ncand);
+    VB_LAUNCH(route_finalize_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev,
+              ix->dim, ix->centroids.ptr, ws.cand.ptr, ncand, n2, nprobe, ix->metric, probes_dev,
+              dists_dev);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// scan
+// ---------------------------------------------------------------------------------------------
+template <typename Kernel>
+static int
+launch_scan(Kernel kernel, const ScanParams& p, size_t smem) {
+    if (smem > 48 * 1024) {
+        VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+    }
+    int per_sm = 0;
+    VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SCAN_THREADS, smem));
+    if (per_sm < 1) {
+        VB_FAIL(VB200_INVALID_ARGUMENT,
+                "scan tile needs %zu bytes of shared memory, more than one SM has", smem);
+    }
+    uint32_t grid = static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(per_sm);
+    VB_LAUNCH(kernel, grid, SCAN_THREADS, smem, p);
+    return 0;
+}
+
+// Scans the probed lists of every query and leaves, per query, the kscan best as keys
+// (payload = inner id) in ws.keys.
+static int
+ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kscan, uint32_t nprobe,
+                const int32_t* probes_dev) {
+    SearchWorkspace& ws = ix->ws;
+    const uint32_t nlist = ix->nlist;
+    const uint64_t total = nq * nprobe;
+    VB_CHECK_ARG(total < 0xFFFFFFFFull, "query batch too large: %llu probes",
+                 static_cast<unsigned long long>(total));
+    VB_CHECK_ARG(kscan >= 1 && kscan <= 1024 - SCAN_THREADS, "k = %u out of range [1, %d]", kscan,
+                 1024 - SCAN_THREADS);
+    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : RABITQ_QT;
+
+    VB_TRY(ws.pair_cnt.reserve(nlist + 1));
+    VB_TRY(ws.cursor.reserve(nlist));
+    VB_TRY(ws.pair_off.reserve(nlist + 1));
+    VB_TRY(ws.item_off.reserve(nlist + 1));
+    VB_TRY(ws.pair_q.reserve(total));
+    VB_TRY(ws.pair_slot.reserve(total));
+    VB_TRY(ws.thr.reserve(nq));
+    VB_TRY(ws.part.reserve(total * kscan));
+    VB_TRY(ws.keys.reserve(nq * kscan));
+    VB_TRY(ws.scalars.reserve(2));
+    cudaStream_t st = current_stream();
+    VB_CUDA(cudaMemsetAsync(ws.pair_cnt.ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
+    VB_CUDA(cudaMemsetAsync(ws.cursor.ptr, 0, nlist * sizeof(uint32_t), st));
+    VB_CUDA(cudaMemsetAsync(ws.thr.ptr, 0xFF, nq * sizeof(uint32_t), st));
+    VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
+
+    const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
+    VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nlist, ix->shard_rank,
+              ix->shard_world, ix->list_off.ptr, ws.pair_cnt.ptr);
+    VB_LAUNCH(pair_scan_kernel, 1, 1024, 0, ws.pair_cnt.ptr, ix->list_off.ptr, nlist,
+              static_cast<uint32_t>(qt), ix->code_size, ws.pair_off.ptr, ws.item_off.ptr,
+              ws.scalars.ptr);
+    VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, nlist, ix->shard_rank,
+              ix->shard_world, ix->list_off.ptr, ws.pair_off.ptr, ws.cursor.ptr, ws.pair_q.ptr,
+              ws.pair_slot.ptr);
+
+    ScanParams p{};
+    p.codes = ix->codes.ptr;
+    p.code_stride = ix->code_stride;
+    p.dim = ix->dim;
+    p.dpad = ix->dpad;
+    p.list_off = ix->list_off.ptr;
+    p.pair_off = ws.pair_off.ptr;
+    p.pair_q = ws.pair_q.ptr;
+    p.pair_slot = ws.pair_slot.ptr;
+    p.item_off = ws.item_off.ptr;
+    p.nlist = nlist;
+    p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 1);
+    p.k = kscan;
+    p.cap = next_pow2(kscan + SCAN_THREADS);
+    p.thr_g = ws.thr.ptr;
+    p.part = ws.part.ptr;
+    p.queries = q_dev;
+    p.lower = ix->lower.ptr;
+    p.diff = ix->diff.ptr;
+    p.inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(ix->dim));
+    p.metric = ix->metric;
+    if (ix->quant == VB200_QUANT_SQ8) {
+        size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, (2 + SQ8_QT) * ix->dpad);
+        if (ix->metric == VB200_METRIC_L2) {
+            VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT, VB200_METRIC_L2>, p, smem));
+        } else {
+            VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT, VB200_METRIC_IP>, p, smem));
+        }
+    } else {
+        size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
+        VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
+    }
+    VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.keys.ptr));
+    const uint64_t nkeys = nq * kscan;
+    VB_LAUNCH(keys_pos_to_inner_kernel, static_cast<uint32_t>((nkeys + 255) / 256), 256, 0, ws.keys.ptr,
+              nkeys, ix->pos_inner.ptr);
+    return 0;
+}
+
+static int
+check_search_ready(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    VB_CHECK_ARG(queries != nullptr || nq == 0, "query pointer is null");
+    VB_CHECK_ARG(k >= 1, "k must be positive");
+    VB_CHECK_ARG(nprobe >= 1, "scan_buckets_count must be positive");
+    if (!ix->has_centroids || !ix->has_model) {
+        VB_FAIL(VB200_WRONG_STATUS, "index is not trained");
+    }
+    return 0;
+}
+
+// Full pipeline up to per-query keys with inner-id payloads (k of them, ascending) in *keys_out.
+static int
+ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe,
+                float factor, const int32_t* bucket_ids, const uint64_t** keys_out) {
+    SearchWorkspace& ws = ix->ws;
+    if (nprobe > ix->nlist) {
+        nprobe = ix->nlist;  // clamp like IVF::create_search_param (ivf.cpp:1573-1575)
+    }
+    uint32_t kscan = k;
+    const bool rerank = ix->use_reorder;
+    if (rerank) {
+        VB_CHECK_ARG(factor > 0.0f, "factor must be positive when use_reorder is true, got %f", factor);
+        kscan = static_cast<uint32_t>(static_cast<int64_t>(factor * static_cast<float>(k)));
+        if (kscan < 1) {
+            kscan = 1;
+        }
+    }
+    // queries on the device
+    const float* q_dev = queries;
+    if (!is_device_pointer(queries)) {
+        VB_TRY(ws.queries.reserve(nq * ix->dim));
+        VB_CUDA(cudaMemcpyAsync(ws.queries.ptr, queries, nq * ix->dim * sizeof(float),
+                                cudaMemcpyHostToDevice, current_stream()));
+        q_dev = ws.queries.ptr;
+    }
+    // probes
+    VB_TRY(ws.probes.reserve(nq * nprobe));
+    if (bucket_ids != nullptr) {
+        VB_CUDA(cudaMemcpyAsync(ws.probes.ptr, bucket_ids, nq * nprobe * sizeof(int32_t),
+                                cudaMemcpyDefault, current_stream()));
+    } else {
+        VB_TRY(ivf_route_device(ix, q_dev, nq, nprobe, ws.probes.ptr, nullptr));
+    }
+    // codec-specific query transform
+    const float* q_scan = q_dev;
+    if (ix->quant == VB200_QUANT_RABITQ) {
+        VB_TRY(ws.qproc.reserve(nq * (ix->dim + 1)));
+        VB_TRY(rabitq_process_query_device(q_dev, nq, ix->dim, ix->rotation.ptr, ix->rq_centroid.ptr,
+                                           ws.qproc.ptr));
+        q_scan = ws.qproc.ptr;
+    }
+    VB_TRY(ivf_scan_device(ix, q_scan, nq, kscan, nprobe, ws.probes.ptr));
+    const uint64_t* keys = ws.keys.ptr;
+    if (rerank) {
+        VB_TRY(ws.keys2.reserve(nq * k));
+        uint32_t n2 = next_pow2(kscan < 2 ? 2 : kscan);
+        VB_LAUNCH(rerank_kernel, static_cast<uint32_t>(nq), 256, n2 * sizeof(uint64_t), q_dev, ix->dim,
+                  ix->flat.ptr, ws.keys.ptr, kscan, n2, k, ix->metric, ws.keys2.ptr);
+        keys = ws.keys2.ptr;
+    } else if (kscan != k) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "scan depth mismatch");
+    }
+    *keys_out = keys;
+    return 0;
+}
+
+}  // namespace vb200
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+
+extern "C" int
+vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_reorder,
+                 vb200_ivf_t* out) {
+    VB_CHECK_ARG(out != nullptr, "null output handle");
+    VB_CHECK_ARG(dim > 0, "dim must be positive");
+    VB_CHECK_ARG(nlist >= 1, "buckets_count must be at least 1");
+    VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP,
+                 "metric_type must be l2 or ip for this engine (got %d)", metric);
+    VB_CHECK_ARG(quant == VB200_QUANT_SQ8 || quant == VB200_QUANT_RABITQ,
+                 "base_quantization_type must be sq8 or rabitq for this engine (got %d)", quant);
+    VB_CHECK_ARG(!(quant == VB200_QUANT_RABITQ && metric != VB200_METRIC_L2),
+                 "rabitq buckets support metric l2 only");
+    int ndev = vb200_device_count();
+    if (ndev <= 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "no CUDA device available; this engine has no CPU path");
+    }
+    vb200_ivf* ix = new (std::nothrow) vb200_ivf();
+    if (ix == nullptr) {
+        VB_FAIL(VB200_NO_ENOUGH_MEMORY, "out of host memory");
+    }
+    ix->dim = dim;
+    ix->metric = metric;
+    ix->nlist = nlist;
+    ix->quant = quant;
+    ix->use_reorder = use_reorder != 0;
+    cudaGetDevice(&ix->device);
+    if (quant == VB200_QUANT_SQ8) {
+        ix->code_size = dim;
+        ix->dpad = (dim + 15) / 16 * 16;
+        ix->code_stride = ix->dpad;
+    } else {
+        ix->code_size = rabitq_code_size(dim);
+        ix->dpad = rabitq_bits_bytes(dim) * 8;
+        ix->code_stride = (ix->code_size + 15) / 16 * 16;
+    }
+    ix->list_off_host.assign(nlist + 1, 0);
+    int s = ix->list_off.reserve(nlist + 1);
+    if (s == 0) {
+        cudaError_t e = cudaMemset(ix->list_off.ptr, 0, (nlist + 1) * sizeof(uint32_t));
+        if (e != cudaSuccess) {
+            set_last_error(VB200_INTERNAL_ERROR, "cudaMemset failed: %s", cudaGetErrorString(e));
+            s = VB200_INTERNAL_ERROR;
+        }
+    }
+    if (s != 0) {
+        delete ix;
+        return s;
+    }
+    *out = ix;
+    return 0;
+}
+
+extern "C" int
+vb200_ivf_destroy(vb200_ivf_t ix) {
+    delete ix;
+    return 0;
+}
+
+extern "C" int
+vb200_ivf_set_shard(vb200_ivf_t ix, uint32_t rank, uint32_t world) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    VB_CHECK_ARG(world >= 1 && rank < world, "bad shard %u of %u", rank, world);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "set_shard must precede the first add");
+    }
+    ix->shard_rank = rank;
+    ix->shard_world = world;
+    return 0;
+}
+
+static int
+ivf_refresh_centroid_norms(vb200_ivf* ix) {
+    VB_TRY(ix->c_sq.reserve(ix->nlist));
+    VB_TRY(row_sqnorm_f32(ix->centroids.ptr, ix->nlist, ix->dim, ix->c_sq.ptr));
+    ix->has_centroids = true;
+    return 0;
+}
+
+extern "C" int
+vb200_ivf_set_centroids(vb200_ivf_t ix, const float* centroids) {
+    VB_CHECK_ARG(ix != nullptr && centroids != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    const size_t n = static_cast<size_t>(ix->nlist) * ix->dim;
+    VB_TRY(ix->centroids.reserve(n));
+    VB_CUDA(cudaMemcpyAsync(ix->centroids.ptr, centroids, n * sizeof(float), cudaMemcpyDefault,
+                            current_stream()));
+    VB_TRY(ivf_refresh_centroid_norms(ix));
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_get_centroids(vb200_ivf_t ix, float* centroids) {
+    VB_CHECK_ARG(ix != nullptr && centroids != nullptr, "null pointer");
+    if (!ix->has_centroids) {
+        VB_FAIL(VB200_WRONG_STATUS, "index has no centroids yet");
+    }
+    VB_TRY(copy_out(centroids, ix->centroids.ptr, static_cast<size_t>(ix->nlist) * ix->dim));
+    return sync_stream();
+}
+
+static int
+ivf_store_sq8_model(vb200_ivf* ix, const float* lower_any, const float* diff_any) {
+    VB_TRY(ix->lower.reserve(ix->dpad));
+    VB_TRY(ix->diff.reserve(ix->dpad));
+    cudaStream_t st = current_stream();
+    VB_CUDA(cudaMemsetAsync(ix->lower.ptr, 0, ix->dpad * sizeof(float), st));
+    VB_CUDA(cudaMemsetAsync(ix->diff.ptr, 0, ix->dpad * sizeof(float), st));
+    VB_CUDA(cudaMemcpyAsync(ix->lower.ptr, lower_any, ix->dim * sizeof(float), cudaMemcpyDefault, st));
+    VB_CUDA(cudaMemcpyAsync(ix->diff.ptr, diff_any, ix->dim * sizeof(float), cudaMemcpyDefault, st));
+    ix->has_model = true;
+    return 0;
+}
+
+extern "C" int
+vb200_ivf_set_sq8_model(vb200_ivf_t ix, const float* lower, const float* diff) {
+    VB_CHECK_ARG(ix != nullptr && lower != nullptr && diff != nullptr, "null pointer");
+    VB_CHECK_ARG(ix->quant == VB200_QUANT_SQ8, "index is not sq8");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "quantizer model cannot change after vectors were added");
+    }
+    VB_TRY(ivf_store_sq8_model(ix, lower, diff));
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_get_sq8_model(vb200_ivf_t ix, float* lower, float* diff) {
+    VB_CHECK_ARG(ix != nullptr && lower != nullptr && diff != nullptr, "null pointer");
+    if (ix->quant != VB200_QUANT_SQ8 || !ix->has_model) {
+        VB_FAIL(VB200_WRONG_STATUS, "index has no sq8 model");
+    }
+    VB_TRY(copy_out(lower, ix->lower.ptr, ix->dim));
+    VB_TRY(copy_out(diff, ix->diff.ptr, ix->dim));
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_set_rabitq_rotation(vb200_ivf_t ix, const float* rotation) {
+    VB_CHECK_ARG(ix != nullptr && rotation != nullptr, "null pointer");
+    VB_CHECK_ARG(ix->quant == VB200_QUANT_RABITQ, "index is not rabitq");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "quantizer model cannot change after vectors were added");
+    }
+    const size_t n = static_cast<size_t>(ix->dim) * ix->dim;
+    VB_TRY(ix->rotation.reserve(n));
+    VB_CUDA(cudaMemcpyAsync(ix->rotation.ptr, rotation, n * sizeof(float), cudaMemcpyDefault,
+                            current_stream()));
+    ix->has_rotation = true;
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_set_rabitq_centroid(vb200_ivf_t ix, const float* centroid) {
+    VB_CHECK_ARG(ix != nullptr && centroid != nullptr, "null pointer");
+    VB_CHECK_ARG(ix->quant == VB200_QUANT_RABITQ, "index is not rabitq");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "quantizer model cannot change after vectors were added");
+    }
+    if (!ix->has_rotation) {
+        VB_FAIL(VB200_WRONG_STATUS, "set the rotation before the centroid");
+    }
+    VB_TRY(ix->rq_centroid.reserve(ix->dim));
+    VB_CUDA(cudaMemcpyAsync(ix->rq_centroid.ptr, centroid, ix->dim * sizeof(float), cudaMemcpyDefault,
+                            current_stream()));
+    ix->has_model = true;
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_get_rabitq_centroid(vb200_ivf_t ix, float* centroid) {
+    VB_CHECK_ARG(ix != nullptr && centroid != nullptr, "null pointer");
+    if (ix->quant != VB200_QUANT_RABITQ || !ix->has_model) {
+        VB_FAIL(VB200_WRONG_STATUS, "index has no rabitq model");
+    }
+    VB_TRY(copy_out(centroid, ix->rq_centroid.ptr, ix->dim));
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_iters, const float* init) {
+    VB_CHECK_ARG(ix != nullptr && data != nullptr, "null pointer");
+    VB_CHECK_ARG(count >= ix->nlist, "k cannot be larger than count (%u lists, %llu rows)", ix->nlist,
+                 static_cast<unsigned long long>(count));
+    VB_CHECK_ARG(kmeans_iters >= 0, "iteration count must not be negative");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "train must precede add");
+    }
+    if (ix->quant == VB200_QUANT_RABITQ && !ix->has_rotation) {
+        VB_FAIL(VB200_WRONG_STATUS, "rabitq index needs its rotation matrix before training");
+    }
+    DevInput<float> x;
+    VB_TRY(x.bind(data, count * ix->dim));
+    const size_t kd = static_cast<size_t>(ix->nlist) * ix->dim;
+    VB_TRY(ix->centroids.reserve(kd));
+    const float* seed = init != nullptr ? init : x.ptr;
+    VB_CUDA(cudaMemcpyAsync(ix->centroids.ptr, seed, kd * sizeof(float), cudaMemcpyDefault,
+                            current_stream()));
+    DevBuf<int32_t> lab;
+    VB_TRY(lab.reserve(count));
+    for (int it = 0; it < kmeans_iters; ++it) {
+        VB_TRY(kmeans_assign_device(ix->kws, x.ptr, count, ix->dim, ix->centroids.ptr, ix->nlist,
+                                    lab.ptr, nullptr));
+        VB_TRY(kmeans_update_device(ix->kws, x.ptr, count, ix->dim, lab.ptr, ix->nlist,
+                                    static_cast<uint32_t>(it), ix->centroids.ptr));
+    }
+    VB_TRY(ivf_refresh_centroid_norms(ix));
+    if (ix->quant == VB200_QUANT_SQ8) {
+        DevBuf<float> model;
+        VB_TRY(model.reserve(2 * static_cast<size_t>(ix->dim)));
+        VB_TRY(sq8_train_device(x.ptr, count, ix->dim, VB200_SQ_TRAIN_TRUNC_BOUND, model.ptr,
+                                model.ptr + ix->dim));
+        VB_TRY(ivf_store_sq8_model(ix, model.ptr, model.ptr + ix->dim));
+    } else {
+        VB_TRY(ix->rq_centroid.reserve(ix->dim));
+        VB_TRY(rabitq_train_device(x.ptr, count, ix->dim, ix->rotation.ptr, ix->rq_centroid.ptr));
+        ix->has_model = true;
+    }
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* ids,
+              const int32_t* labels_in) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    if (count == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(data != nullptr && ids != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (!ix->has_centroids || !ix->has_model) {
+        VB_FAIL(VB200_WRONG_STATUS, "index is not trained");
+    }
+    VB_CHECK_ARG(ix->n_total + count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
+    const uint32_t nlist = ix->nlist, dim = ix->dim;
+    cudaStream_t st = current_stream();
+
+    DevInput<float> x;
+    VB_TRY(x.bind(data, count * dim));
+    // 1. list of every row
+    DevBuf<int32_t> lab;
+    VB_TRY(lab.reserve(count));
+    if (labels_in != nullptr) {
+        VB_CUDA(cudaMemcpyAsync(lab.ptr, labels_in, count * sizeof(int32_t), cudaMemcpyDefault, st));
+    } else {
+        const bool l2 = ix->metric == VB200_METRIC_L2;
+        VB_TRY(dense_argmin_f32(x.ptr, count, ix->centroids.ptr, nlist, dim, l2 ? -2.0f : -1.0f,
+                                l2 ? ix->c_sq.ptr : nullptr, lab.ptr, nullptr));
+    }
+    // 2. sort rows by (list, row)
+    DevBuf<uint64_t> keys, sorted;
+    DevBuf<uint32_t> add_cnt;
+    VB_TRY(keys.reserve(count));
+    VB_TRY(sorted.reserve(count));
+    VB_TRY(add_cnt.reserve(nlist + 1));
+    VB_CUDA(cudaMemsetAsync(add_cnt.ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
+    VB_LAUNCH(ivf_make_keys_kernel, static_cast<uint32_t>((count + 255) / 256), 256, 0, lab.ptr, count,
+              nlist, ix->shard_rank, ix->shard_world, keys.ptr, add_cnt.ptr);
+    {
+        int end_bit = 33;
+        while ((uint64_t{1} << (end_bit - 32)) <= nlist) {
+            ++end_bit;
+        }
+        size_t tmp_bytes = 0;
+        VB_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, tmp_bytes, keys.ptr, sorted.ptr,
+                                               static_cast<int64_t>(count), 0, end_bit, st));
+        DevBuf<uint8_t> tmp;
+        VB_TRY(tmp.reserve(tmp_bytes > 0 ? tmp_bytes : 1));
+        VB_CUDA(cub::DeviceRadixSort::SortKeys(tmp.ptr, tmp_bytes, keys.ptr, sorted.ptr,
+                                               static_cast<int64_t>(count), 0, end_bit, st));
+        g_kernel_launches.fetch_add(1);
+        VB_TRY(sync_stream());
+    }
+    // 3. new offsets (host side; nlist entries)
+    std::vector<uint32_t> add_host(nlist + 1), add_off(nlist + 1), new_off(nlist + 1);
+    VB_CUDA(cudaMemcpyAsync(add_host.data(), add_cnt.ptr, (nlist + 1) * sizeof(uint32_t),
+                            cudaMemcpyDeviceToHost, st));
+    VB_TRY(sync_stream());
+    uint64_t run_add = 0, run_new = 0;
+    for (uint32_t l = 0; l < nlist; ++l) {
+        add_off[l] = static_cast<uint32_t>(run_add);
+        new_off[l] = static_cast<uint32_t>(run_new);
+        run_add += add_host[l];
+        run_new += (ix->list_off_host[l + 1] - ix->list_off_host[l]) + add_host[l];
+    }
+    add_off[nlist] = static_cast<uint32_t>(run_add);
+    new_off[nlist] = static_cast<uint32_t>(run_new);
+    const uint64_t n_new_stored = run_new;
+    DevBuf<uint32_t> add_off_dev, new_off_dev;
+    VB_TRY(add_off_dev.reserve(nlist + 1));
+    VB_TRY(new_off_dev.reserve(nlist + 1));
+    VB_CUDA(cudaMemcpyAsync(add_off_dev.ptr, add_off.data(), (nlist + 1) * sizeof(uint32_t),
+                            cudaMemcpyHostToDevice, st));
+    VB_CUDA(cudaMemcpyAsync(new_off_dev.ptr, new_off.data(), (nlist + 1) * sizeof(uint32_t),
+                            cudaMemcpyHostToDevice, st));
+    // 4. regrown arrays
+    DevBuf<uint8_t> new_codes;
+    DevBuf<uint32_t> new_inner, dst_of_row;
+    const uint32_t stride = ix->code_stride;
+    VB_TRY(new_codes.reserve((n_new_stored > 0 ? n_new_stored : 1) * stride));
+    VB_TRY(new_inner.reserve(n_new_stored > 0 ? n_new_stored : 1));
+    VB_TRY(dst_of_row.reserve(count));
+    VB_CUDA(cudaMemsetAsync(new_codes.ptr, 0, (n_new_stored > 0 ? n_new_stored : 1) * stride, st));
+    if (ix->n_stored > 0) {
+        uint64_t work = ix->n_stored * (stride / 16);
+        VB_LAUNCH(ivf_move_old_kernel, static_cast<uint32_t>((work + 255) / 256), 256, 0, ix->codes.ptr,
+                  ix->pos_inner.ptr, ix->list_off.ptr, new_off_dev.ptr, nlist, ix->n_stored, stride / 16,
+                  new_codes.ptr, new_inner.ptr);
+    }
+    VB_LAUNCH(ivf_place_new_kernel, static_cast<uint32_t>((count + 255) / 256), 256, 0, sorted.ptr, count,
+              nlist, new_off_dev.ptr, ix->list_off.ptr, add_off_dev.ptr,
+              static_cast<uint32_t>(ix->n_total), dst_of_row.ptr, new_inner.ptr);
+    // 5. encode the new rows in place
+    if (ix->quant == VB200_QUANT_SQ8) {
+        VB_TRY(sq8_encode_device(x.ptr, count, dim, ix->lower.ptr, ix->diff.ptr, dst_of_row.ptr,
+                                 new_codes.ptr, stride));
+    } else {
+        VB_TRY(rabitq_encode_device(x.ptr, count, dim, ix->rotation.ptr, ix->rq_centroid.ptr,
+                                    dst_of_row.ptr, new_codes.ptr, stride));
+    }
+    // 6. labels and (for reorder) the fp32 rows, by inner id
+    VB_TRY(grow_preserve(ix->labels, ix->n_total, ix->n_total + count));
+    VB_CUDA(cudaMemcpyAsync(ix->labels.ptr + ix->n_total, ids, count * sizeof(int64_t),
+                            cudaMemcpyDefault, st));
+    if (ix->use_reorder) {
+        VB_TRY(grow_preserve(ix->flat, ix->n_total * dim, (ix->n_total + count) * dim));
+        VB_CUDA(cudaMemcpyAsync(ix->flat.ptr + ix->n_total * dim, x.ptr, count * dim * sizeof(float),
+                                cudaMemcpyDeviceToDevice, st));
+    }
+    VB_TRY(sync_stream());
+    // 7. commit
+    ix->codes = std::move(new_codes);
+    ix->pos_inner = std::move(new_inner);
+    ix->list_off = std::move(new_off_dev);
+    ix->list_off_host = new_off;
+    ix->n_stored = n_new_stored;
+    ix->n_total += count;
+    return 0;
+}
+
+extern "C" int64_t
+vb200_ivf_num_elements(vb200_ivf_t ix) {
+    return ix == nullptr ? 0 : static_cast<int64_t>(ix->n_total);
+}
+
+extern "C" int64_t
+vb200_ivf_memory_usage(vb200_ivf_t ix) {
+    if (ix == nullptr) {
+        return 0;
+    }
+    return static_cast<int64_t>(ix->codes.bytes() + ix->pos_inner.bytes() + ix->labels.bytes() +
+                                ix->flat.bytes() + ix->centroids.bytes() + ix->rotation.bytes() +
+                                ix->list_off.bytes());
+}
+
+extern "C" int
+vb200_ivf_get_lists(vb200_ivf_t ix, int64_t* list_sizes, uint8_t* codes, int64_t* inner_ids) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (list_sizes != nullptr) {
+        for (uint32_t l = 0; l < ix->nlist; ++l) {
+            list_sizes[l] = static_cast<int64_t>(ix->list_off_host[l + 1] - ix->list_off_host[l]);
+        }
+    }
+    if (ix->n_stored == 0) {
+        return 0;
+    }
+    if (codes != nullptr) {
+        VB_CHECK_ARG(!is_device_pointer(codes), "get_lists writes host memory");
+        VB_CUDA(cudaMemcpy2D(codes, ix->code_size, ix->codes.ptr, ix->code_stride, ix->code_size,
+                             ix->n_stored, cudaMemcpyDeviceToHost));
+    }
+    if (inner_ids != nullptr) {
+        std::vector<uint32_t> tmp(ix->n_stored);
+        VB_CUDA(cudaMemcpy(tmp.data(), ix->pos_inner.ptr, ix->n_stored * sizeof(uint32_t),
+                           cudaMemcpyDeviceToHost));
+        for (uint64_t i = 0; i < ix->n_stored; ++i) {
+            inner_ids[i] = tmp[i];
+        }
+    }
+    return 0;
+}
+
+extern "C" int
+vb200_ivf_route(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t nprobe,
+                int32_t* bucket_ids, float* bucket_dists) {
+    VB_CHECK_ARG(ix != nullptr && bucket_ids != nullptr, "null pointer");
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(queries != nullptr, "query pointer is null");
+    VB_CHECK_ARG(nprobe >= 1 && nprobe <= ix->nlist, "scan_buckets_count out of range");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (!ix->has_centroids) {
+        VB_FAIL(VB200_WRONG_STATUS, "index is not trained");
+    }
+    DevInput<float> q;
+    VB_TRY(q.bind(queries, nq * ix->dim));
+    VB_TRY(ix->ws.probes.reserve(nq * nprobe));
+    VB_TRY(ix->ws.probe_dists.reserve(nq * nprobe));
+    VB_TRY(ivf_route_device(ix, q.ptr, nq, nprobe, ix->ws.probes.ptr, ix->ws.probe_dists.ptr));
+    VB_TRY(copy_out(bucket_ids, ix->ws.probes.ptr, nq * nprobe));
+    if (bucket_dists != nullptr) {
+        VB_TRY(copy_out(bucket_dists, ix->ws.probe_dists.ptr, nq * nprobe));
+    }
+    return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_search(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe,
+                 float factor, const int32_t* bucket_ids, int64_t* ids, float* dists) {
+    VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(ids != nullptr && dists != nullptr, "null output pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    SearchWorkspace& ws = ix->ws;
+    const uint64_t total = nq * k;
+    VB_TRY(ws.out_ids.reserve(total));
+    VB_TRY(ws.out_dists.reserve(total));
+    if (ix->n_total == 0) {
+        // Empty index: every slot padded, like the Dim=0 dataset of IndexImpl (index_impl.h:60-63).
+        std::vector<int64_t> hi(total, -1);
+        std::vector<float> hd(total, INFINITY);
+        VB_CUDA(cudaMemcpy(ids, hi.data(), total * sizeof(int64_t), cudaMemcpyDefault));
+        VB_CUDA(cudaMemcpy(dists, hd.data(), total * sizeof(float), cudaMemcpyDefault));
+        ix->last_scan_bytes = 0;
+        return 0;
+    }
+    const uint64_t* keys = nullptr;
+    VB_TRY(ivf_search_keys(ix, queries, nq, k, nprobe, factor, bucket_ids, &keys));
+    VB_LAUNCH(keys_to_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
+              ix->labels.ptr, ws.out_ids.ptr, ws.out_dists.ptr);
+    VB_TRY(copy_out(ids, ws.out_ids.ptr, total));
+    VB_TRY(copy_out(dists, ws.out_dists.ptr, total));
+    uint64_t scan_bytes = 0;
+    VB_CUDA(cudaMemcpyAsync(&scan_bytes, ws.scalars.ptr, sizeof(uint64_t), cudaMemcpyDeviceToHost,
+                            current_stream()));
+    VB_TRY(sync_stream());
+    ix->last_scan_bytes = static_cast<int64_t>(scan_bytes);
+    return 0;
+}
+
+// keys (payload = inner id) -> keys unchanged plus the label of each entry.
+__global__ void
+keys_labels_kernel(const uint64_t* __restrict__ keys, uint64_t total,
+                   const int64_t* __restrict__ labels, uint64_t* __restrict__ keys_out,
+                   int64_t* __restrict__ labels_out) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    uint64_t key = keys[e];
+    keys_out[e] = key;
+    labels_out[e] = key == KEY_INF ? -1 : labels[static_cast<uint32_t>(key)];
+}
+
+extern "C" int
+vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k,
+                         uint32_t nprobe, float factor, uint64_t* keys_dev, int64_t* labels_dev) {
+    VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(keys_dev != nullptr && labels_dev != nullptr, "null output pointer");
+    VB_CHECK_ARG(is_device_pointer(keys_dev) && is_device_pointer(labels_dev),
+                 "partial results are written to device memory");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    const uint64_t total = nq * k;
+    if (ix->n_total == 0 || ix->n_stored == 0) {
+        VB_CUDA(cudaMemsetAsync(keys_dev, 0xFF, total * sizeof(uint64_t), current_stream()));
+        VB_CUDA(cudaMemsetAsync(labels_dev, 0xFF, total * sizeof(int64_t), current_stream()));
+        ix->last_scan_bytes = 0;
+        return sync_stream();
+    }
+    const uint64_t* keys = nullptr;
+    VB_TRY(ivf_search_keys(ix, queries, nq, k, nprobe, factor, nullptr, &keys));
+    VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
+              ix->labels.ptr, keys_dev, labels_dev);
+    uint64_t scan_bytes = 0;
+    VB_CUDA(cudaMemcpyAsync(&scan_bytes, ix->ws.scalars.ptr, sizeof(uint64_t), cudaMemcpyDeviceToHost,
+                            current_stream()));
+    VB_TRY(sync_stream());
+    ix->last_scan_bytes = static_cast<int64_t>(scan_bytes);
+    return 0;
+}
+
+extern "C" int64_t
+vb200_ivf_last_scan_bytes(vb200_ivf_t ix) {
+    return ix == nullptr ? 0 : ix->last_scan_bytes;
+}
+
+// labels gathered beside tagged keys: payload indexes the gathered label array.
+__global__ void
+tagged_to_results_kernel(const uint64_t* __restrict__ keys, uint64_t total,
+                         const int64_t* __restrict__ gathered_labels, int64_t* __restrict__ ids,
+                         float* __restrict__ dists) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    uint64_t key = keys[e];
+    if (key == KEY_INF) {
+        ids[e] = -1;
+        dists[e] = INFINITY;
+    } else {
+        ids[e] = gathered_labels[static_cast<uint32_t>(key)];
+        dists[e] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+    }
+}
+
+extern "C" int
+vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32_t parts, uint64_t nq,
+                     uint32_t k, int64_t* ids, float* dists) {
+    VB_CHECK_ARG(keys_dev != nullptr && labels_dev != nullptr && ids != nullptr && dists != nullptr,
+                 "null pointer");
+    VB_CHECK_ARG(parts >= 1 && k >= 1 && k <= 1024, "bad merge shape");
+    if (nq == 0) {
+        return 0;
+    }
+    const uint64_t in_total = static_cast<uint64_t>(parts) * nq * k;
+    VB_CHECK_ARG(in_total < 0xFFFFFFFFull, "merge input too large");
+    DevBuf<uint64_t> tagged, merged;
+    DevBuf<int64_t> out_ids;
+    DevBuf<float> out_dists;
+    VB_TRY(tagged.reserve(in_total));
+    VB_TRY(merged.reserve(nq * k));
+    VB_TRY(out_ids.reserve(nq * k));
+    VB_TRY(out_dists.reserve(nq * k));
+    VB_LAUNCH(tag_partials_kernel, static_cast<uint32_t>((in_total + 255) / 256), 256, 0, keys_dev, parts,
+              nq, k, tagged.ptr);
+    VB_TRY(launch_merge(tagged.ptr, nq, static_cast<uint64_t>(parts) * k, k, merged.ptr));
+    VB_LAUNCH(tagged_to_results_kernel, static_cast<uint32_t>((nq * k + 255) / 256), 256, 0, merged.ptr,
+              nq * k, labels_dev, out_ids.ptr, out_dists.ptr);
+    VB_TRY(copy_out(ids, out_ids.ptr, nq * k));
+    VB_TRY(copy_out(dists, out_dists.ptr, nq * k));
+    return sync_stream();
+}

@@ -1,0 +1,287 @@
+"""Thin Python handles over the C ABI (include/vsag_b200.h).
+
+Every function takes numpy arrays (host) or torch tensors (host or CUDA) and forwards plain
+pointers; all arithmetic happens in libvsag_b200.so on the GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi
+from ._capi import VsagB200Error, check, ptr
+
+METRIC_L2, METRIC_IP, METRIC_COSINE = 0, 1, 2
+QUANT_FP32, QUANT_SQ8, QUANT_RABITQ, QUANT_BF16 = 0, 1, 2, 3
+SQ_TRAIN_CLASSIC, SQ_TRAIN_TRUNC_BOUND = 1, 3
+
+METRICS = {"l2": METRIC_L2, "ip": METRIC_IP, "cosine": METRIC_COSINE}
+
+
+def _is_torch(x) -> bool:
+    return hasattr(x, "data_ptr")
+
+
+def _rows(x) -> int:
+    return int(x.shape[0])
+
+
+def _empty_like_side(ref, shape, dtype):
+    """Output buffer on the same side (host numpy / torch device) as `ref`."""
+    if _is_torch(ref) and ref.is_cuda:
+        import torch
+
+        tdt = {np.float32: torch.float32, np.int64: torch.int64, np.int32: torch.int32,
+               np.uint8: torch.uint8}[dtype]
+        return torch.empty(shape, dtype=tdt, device=ref.device)
+    return np.empty(shape, dtype=dtype)
+
+
+def device_count() -> int:
+    n = _capi.load().vb200_device_count()
+    if n < 0:
+        check(n)
+    return n
+
+
+def kernel_launches() -> int:
+    return int(_capi.load().vb200_kernel_launches())
+
+
+def set_stream(stream_handle: int | None) -> None:
+    check(_capi.load().vb200_set_stream(C.c_void_p(stream_handle or 0)))
+
+
+# ------------------------------------------------------------------------------------------------
+# quantizers and k-means
+# ------------------------------------------------------------------------------------------------
+def sq8_train(data, mode: int = SQ_TRAIN_TRUNC_BOUND):
+    n, d = data.shape
+    lower = np.empty(d, np.float32)
+    diff = np.empty(d, np.float32)
+    check(_capi.load().vb200_sq8_train(ptr(data, np.float32), n, d, mode, ptr(lower), ptr(diff)))
+    return lower, diff
+
+
+def sq8_encode(data, lower, diff):
+    n, d = data.shape
+    codes = _empty_like_side(data, (n, d), np.uint8)
+    check(_capi.load().vb200_sq8_encode(ptr(data, np.float32), n, d, ptr(lower, np.float32),
+                                        ptr(diff, np.float32), ptr(codes)))
+    return codes
+
+
+def kmeans_assign(data, centroids, want_err: bool = False):
+    n, d = data.shape
+    k = _rows(centroids)
+    labels = _empty_like_side(data, (n,), np.int32)
+    err = C.c_double(0.0)
+    check(_capi.load().vb200_kmeans_assign(ptr(data, np.float32), n, d, ptr(centroids, np.float32), k,
+                                           ptr(labels), C.byref(err) if want_err else None))
+    return (labels, err.value) if want_err else labels
+
+
+def kmeans_update(data, labels, k: int, it: int = 0):
+    n, d = data.shape
+    centroids = np.empty((k, d), np.float32)
+    counts = np.empty(k, np.int32)
+    check(_capi.load().vb200_kmeans_update(ptr(data, np.float32), n, d, ptr(labels, np.int32), k, it,
+                                           ptr(centroids), ptr(counts)))
+    return centroids, counts
+
+
+def kmeans_train(data, init_centroids: np.ndarray, iters: int):
+    n, d = data.shape
+    centroids = np.ascontiguousarray(init_centroids, dtype=np.float32).copy()
+    k = centroids.shape[0]
+    labels = np.empty(n, np.int32)
+    err = C.c_double(0.0)
+    check(_capi.load().vb200_kmeans_train(ptr(data, np.float32), n, d, k, iters, ptr(centroids),
+                                          ptr(labels), C.byref(err)))
+    return centroids, labels, err.value
+
+
+def rabitq_code_size(dim: int) -> int:
+    return int(_capi.load().vb200_rabitq_code_size(dim))
+
+
+def rabitq_train(data, rotation):
+    n, d = data.shape
+    centroid = np.empty(d, np.float32)
+    check(_capi.load().vb200_rabitq_train(ptr(data, np.float32), n, d, ptr(rotation, np.float32),
+                                          ptr(centroid)))
+    return centroid
+
+
+def rabitq_encode(data, rotation, centroid):
+    n, d = data.shape
+    codes = np.empty((n, rabitq_code_size(d)), np.uint8)
+    check(_capi.load().vb200_rabitq_encode(ptr(data, np.float32), n, d, ptr(rotation, np.float32),
+                                           ptr(centroid, np.float32), ptr(codes)))
+    return codes
+
+
+def rabitq_process_query(queries, rotation, centroid):
+    n, d = queries.shape
+    out = np.empty((n, d + 1), np.float32)
+    check(_capi.load().vb200_rabitq_process_query(ptr(queries, np.float32), n, d,
+                                                  ptr(rotation, np.float32), ptr(centroid, np.float32),
+                                                  ptr(out)))
+    return out
+
+
+def merge_partials(keys_dev, labels_dev, parts: int, nq: int, k: int):
+    ids = np.empty((nq, k), np.int64)
+    dists = np.empty((nq, k), np.float32)
+    check(_capi.load().vb200_merge_partials(ptr(keys_dev), ptr(labels_dev), parts, nq, k, ptr(ids),
+                                            ptr(dists)))
+    return ids, dists
+
+
+# ------------------------------------------------------------------------------------------------
+# index handles
+# ------------------------------------------------------------------------------------------------
+class IvfHandle:
+    """Owns a vb200_ivf_t."""
+
+    def __init__(self, dim: int, metric: int, nlist: int, quant: int, use_reorder: bool = False):
+        self._lib = _capi.load()
+        h = C.c_void_p()
+        check(self._lib.vb200_ivf_create(dim, metric, nlist, quant, int(use_reorder), C.byref(h)))
+        self._h = h
+        self.dim, self.metric, self.nlist, self.quant, self.use_reorder = dim, metric, nlist, quant, use_reorder
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.vb200_ivf_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    @property
+    def code_size(self) -> int:
+        return self.dim if self.quant == QUANT_SQ8 else rabitq_code_size(self.dim)
+
+    def set_shard(self, rank: int, world: int) -> None:
+        check(self._lib.vb200_ivf_set_shard(self._h, rank, world))
+
+    def train(self, data, iters: int = 25, init=None) -> None:
+        check(self._lib.vb200_ivf_train(self._h, ptr(data, np.float32), _rows(data), iters,
+                                        ptr(init, np.float32)))
+
+    def set_centroids(self, centroids) -> None:
+        check(self._lib.vb200_ivf_set_centroids(self._h, ptr(centroids, np.float32)))
+
+    def get_centroids(self) -> np.ndarray:
+        out = np.empty((self.nlist, self.dim), np.float32)
+        check(self._lib.vb200_ivf_get_centroids(self._h, ptr(out)))
+        return out
+
+    def set_sq8_model(self, lower, diff) -> None:
+        check(self._lib.vb200_ivf_set_sq8_model(self._h, ptr(lower, np.float32), ptr(diff, np.float32)))
+
+    def get_sq8_model(self):
+        lower = np.empty(self.dim, np.float32)
+        diff = np.empty(self.dim, np.float32)
+        check(self._lib.vb200_ivf_get_sq8_model(self._h, ptr(lower), ptr(diff)))
+        return lower, diff
+
+    def set_rabitq_rotation(self, rotation) -> None:
+        check(self._lib.vb200_ivf_set_rabitq_rotation(self._h, ptr(rotation, np.float32)))
+
+    def set_rabitq_centroid(self, centroid) -> None:
+        check(self._lib.vb200_ivf_set_rabitq_centroid(self._h, ptr(centroid, np.float32)))
+
+    def get_rabitq_centroid(self) -> np.ndarray:
+        out = np.empty(self.dim, np.float32)
+        check(self._lib.vb200_ivf_get_rabitq_centroid(self._h, ptr(out)))
+        return out
+
+    def add(self, data, ids, labels=None) -> None:
+        check(self._lib.vb200_ivf_add(self._h, ptr(data, np.float32), _rows(data), ptr(ids, np.int64),
+                                      ptr(labels, np.int32)))
+
+    def num_elements(self) -> int:
+        return int(self._lib.vb200_ivf_num_elements(self._h))
+
+    def memory_usage(self) -> int:
+        return int(self._lib.vb200_ivf_memory_usage(self._h))
+
+    def get_lists(self):
+        sizes = np.empty(self.nlist, np.int64)
+        check(self._lib.vb200_ivf_get_lists(self._h, ptr(sizes), None, None))
+        total = int(sizes.sum())
+        codes = np.empty((total, self.code_size), np.uint8)
+        inner = np.empty(total, np.int64)
+        check(self._lib.vb200_ivf_get_lists(self._h, None, ptr(codes), ptr(inner)))
+        return sizes, codes, inner
+
+    def route(self, queries, nprobe: int):
+        nq = _rows(queries)
+        ids = np.empty((nq, nprobe), np.int32)
+        dists = np.empty((nq, nprobe), np.float32)
+        check(self._lib.vb200_ivf_route(self._h, ptr(queries, np.float32), nq, nprobe, ptr(ids), ptr(dists)))
+        return ids, dists
+
+    def search(self, queries, k: int, nprobe: int, factor: float = 2.0, bucket_ids=None, out=None):
+        nq = _rows(queries)
+        if out is None:
+            ids = _empty_like_side(queries, (nq, k), np.int64)
+            dists = _empty_like_side(queries, (nq, k), np.float32)
+        else:
+            ids, dists = out
+        check(self._lib.vb200_ivf_search(self._h, ptr(queries, np.float32), nq, k, nprobe, factor,
+                                         ptr(bucket_ids, np.int32), ptr(ids), ptr(dists)))
+        return ids, dists
+
+    def search_partial(self, queries, k: int, nprobe: int, factor: float, keys_dev, labels_dev) -> None:
+        check(self._lib.vb200_ivf_search_partial(self._h, ptr(queries, np.float32), _rows(queries), k,
+                                                 nprobe, factor, ptr(keys_dev), ptr(labels_dev)))
+
+    def last_scan_bytes(self) -> int:
+        return int(self._lib.vb200_ivf_last_scan_bytes(self._h))
+
+
+class BfHandle:
+    """Owns a vb200_bf_t."""
+
+    def __init__(self, dim: int, metric: int, quant: int = QUANT_FP32):
+        self._lib = _capi.load()
+        h = C.c_void_p()
+        check(self._lib.vb200_bf_create(dim, metric, quant, C.byref(h)))
+        self._h = h
+        self.dim, self.metric, self.quant = dim, metric, quant
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.vb200_bf_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def add(self, data, ids) -> None:
+        check(self._lib.vb200_bf_add(self._h, ptr(data, np.float32), _rows(data), ptr(ids, np.int64)))
+
+    def add_bf16(self, data, ids) -> None:
+        check(self._lib.vb200_bf_add_bf16(self._h, ptr(data, np.uint16), _rows(data), ptr(ids, np.int64)))
+
+    def num_elements(self) -> int:
+        return int(self._lib.vb200_bf_num_elements(self._h))
+
+    def search(self, queries, k: int, out=None):
+        nq = _rows(queries)
+        if out is None:
+            ids = _empty_like_side(queries, (nq, k), np.int64)
+            dists = _empty_like_side(queries, (nq, k), np.float32)
+        else:
+            ids, dists = out
+        check(self._lib.vb200_bf_search(self._h, ptr(queries, np.float32), nq, k, ptr(ids), ptr(dists)))
+        return ids, dists
+
+    def search_partial(self, queries, k: int, keys_dev, labels_dev) -> None:
+        check(self._lib.vb200_bf_search_partial(self._h, ptr(queries, np.float32), _rows(queries), k,
+                                                ptr(keys_dev), ptr(labels_dev)))
+
+
+__all__ = [name for name in globals() if not name.startswith("_")]
