@@ -1,0 +1,448 @@
+"""Headline benchmark: IVF-SQ8 search QPS on a synthetic stand-in for Deep-10M.
+
+Workload (the third config of BASELINE.json): base 10,000,000 x 96 fp32 drawn from a Gaussian
+mixture of 16,384 centres (uniform[-1,1], sigma 0.15, seed 2), SQ8 codes, nlist 16,384, nprobe 64,
+10,000 queries from the same mixture (seed 3), k = 10, L2.  The dataset named by the reference's
+documentation is not available offline; this seeded synthetic set has its shape.
+
+A step is one search of the whole 10,000-query batch through the C ABI (vb200_ivf_search):
+routing, pair grouping, list scan with fused top-k, merge.  `value` times it with queries and
+results resident in HBM; `e2e` times the same call with pinned host buffers, so the host<->device
+copies are inside the timed region.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+N_BASE = 10_000_000
+DIM = 96
+NLIST = 16_384
+NPROBE = 64
+N_QUERY = 10_000
+K = 10
+N_CENTRES = 16_384
+SIGMA = 0.15
+TRAIN_ROWS = 64 * NLIST          # the reference's default train_sample_count: max(65536, 64 * nlist)
+KMEANS_ITERS = 25                # hard-coded in IVFNearestPartition::Train
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scan kernel, from the ncu
+# capture summarised under profiles/; None until a capture of this kernel has been taken.
+SCAN_TRAFFIC_BYTES = None
+
+
+def env_int(name: str, default: int) -> int:
+    return int(os.environ.get(name, default))
+
+
+def scaled(n: int) -> int:
+    """VB200_BENCH_SCALE shrinks the workload for dry runs; the default 1.0 is the real config."""
+    s = float(os.environ.get("VB200_BENCH_SCALE", "1.0"))
+    return max(1, int(n * s))
+
+
+def measured_hbm_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workload
+# ------------------------------------------------------------------------------------------------
+def make_data(device, n_base: int, n_query: int):
+    """Seeded Gaussian-mixture base rows and queries, generated on the device in slices."""
+    import torch
+
+    g = torch.Generator(device=device)
+    g.manual_seed(2)
+    centres = torch.rand((N_CENTRES, DIM), generator=g, device=device) * 2.0 - 1.0
+    base = torch.empty((n_base, DIM), dtype=torch.float32, device=device)
+    step = 1_000_000
+    for b in range(0, n_base, step):
+        e = min(n_base, b + step)
+        which = torch.randint(0, N_CENTRES, (e - b,), generator=g, device=device)
+        base[b:e] = centres[which] + SIGMA * torch.randn((e - b, DIM), generator=g, device=device)
+    gq = torch.Generator(device=device)
+    gq.manual_seed(3)
+    which = torch.randint(0, N_CENTRES, (n_query,), generator=gq, device=device)
+    queries = centres[which] + SIGMA * torch.randn((n_query, DIM), generator=gq, device=device)
+    return base, queries.contiguous()
+
+
+def build_index(engine, base, nlist: int, rank: int, world: int, dist):
+    """Trains on rank 0 (centroid sums use float atomics, so ranks would otherwise disagree in the
+    last bit), shares the model, and lets every rank add the rows of the lists it owns."""
+    import torch
+
+    ix = engine.IvfHandle(DIM, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+    if world > 1:
+        ix.set_shard(rank, world)
+    train_rows = min(base.shape[0], scaled(TRAIN_ROWS))
+    centroids = torch.empty((nlist, DIM), dtype=torch.float32, device=base.device)
+    model = torch.empty((2, DIM), dtype=torch.float32, device=base.device)
+    if rank == 0:
+        trainer = engine.IvfHandle(DIM, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+        # a strided sample stands in for the reference's reservoir sample of the same size
+        stride = max(1, base.shape[0] // train_rows)
+        sample = base[::stride][:train_rows].contiguous()
+        trainer.train(sample, iters=env_int("VB200_BENCH_KMEANS_ITERS", KMEANS_ITERS))
+        centroids.copy_(torch.from_numpy(trainer.get_centroids()))
+        lower, diff = trainer.get_sq8_model()
+        model[0].copy_(torch.from_numpy(lower))
+        model[1].copy_(torch.from_numpy(diff))
+        trainer.close()
+        del sample
+    if world > 1:
+        dist.broadcast(centroids, src=0)
+        dist.broadcast(model, src=0)
+    ix.set_centroids(centroids)
+    ix.set_sq8_model(model[0].contiguous(), model[1].contiguous())
+    ids = torch.arange(base.shape[0], dtype=torch.int64, device=base.device)
+    ix.add(base, ids)
+    return ix
+
+
+def recall_at_k(engine, base, queries, got_ids, sample: int) -> float:
+    """recall@k of the first `sample` queries against exact fp32 search on the same base."""
+    bf = engine.BfHandle(DIM, engine.METRIC_L2, engine.QUANT_FP32)
+    import torch
+
+    ids = torch.arange(base.shape[0], dtype=torch.int64, device=base.device)
+    bf.add(base, ids)
+    exact, _ = bf.search(queries[:sample].contiguous(), K)
+    bf.close()
+    exact = exact.cpu().numpy()
+    got = got_ids[:sample].cpu().numpy() if hasattr(got_ids, "cpu") else got_ids[:sample]
+    hits = sum(len(set(a.tolist()) & set(b.tolist())) for a, b in zip(got, exact))
+    return hits / float(sample * K)
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the reference's scan loop on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_scan_setup(ix, queries_host: np.ndarray, nprobe: int):
+    """Host copies of the inverted file plus the probe lists, for the CPU scan."""
+    sizes, codes, inner = ix.get_lists()
+    off = np.zeros(sizes.size + 1, np.int64)
+    np.cumsum(sizes, out=off[1:])
+    lower, diff = ix.get_sq8_model()
+    probes, _ = ix.route(queries_host, nprobe)
+    return dict(codes=codes, off=off, inner=inner, lower=lower, diff=diff, probes=probes)
+
+
+def cpu_scan_run(host: dict, queries_host: np.ndarray, count: int):
+    """Times the reference's per-query bucket scan (32-code blocks + bounded heap) over `count`
+    queries, one query per worker thread on every core.  The distance kernel is the reference's own
+    compiled SQ8ComputeL2Sqr when oracle/_ref is present ("reference"), else the oracle's scalar
+    restatement ("port").  Routing is not timed: the probe lists come from the engine, which
+    favours the CPU arm (the reference routes through a graph search)."""
+    import ctypes as C
+
+    from oracle import pyoracle as O
+
+    R = O.ref()
+    fn = C.cast(R.ref_SQ8ComputeL2Sqr, C.c_void_p) if R is not None else None
+    kind = "reference" if R is not None else "port"
+    q = np.ascontiguousarray(queries_host[:count])
+    probes = np.ascontiguousarray(host["probes"][:count])
+    t0 = time.perf_counter()
+    ids, dists = O.ivf_sq8_search(host["codes"], host["off"], host["inner"], host["lower"], host["diff"], q,
+                                  probes, K, metric=0, fn=fn, nthreads=0)
+    dt = time.perf_counter() - t0
+    return count / dt, kind, O.num_threads(), dt, ids, dists
+
+
+def run_reference_arm(args) -> None:
+    """`--impl reference`: the reference's CPU implementation of the scan on this box's cores."""
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from vsag_b200 import engine
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    n_base, n_query, nlist = scaled(N_BASE), scaled(N_QUERY), max(16, scaled(NLIST))
+    base, queries = make_data(device, n_base, n_query)
+    # The index (codes, lists) is an input of the measurement; it is built with the engine because
+    # the reference library cannot be built offline.  Only the CPU scan below is timed.
+    ix = build_index(engine, base, nlist, 0, 1, None)
+    qh = queries.cpu().numpy()
+    host = cpu_scan_setup(ix, qh, min(NPROBE, nlist))
+    sample = min(n_query, env_int("VB200_CPU_SAMPLE", 2000))
+    for _ in range(max(1, args.warmup)):
+        cpu_scan_run(host, qh, min(sample, 200))
+    times, qps, kind, cores = [], 0.0, "port", 1
+    for _ in range(args.steps):
+        qps, kind, cores, dt, _, _ = cpu_scan_run(host, qh, sample)
+        times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    value = sample / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": "QPS at nprobe=64, IVF-SQ8 10Mx96, k=10", "value": value,
+        "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "IVF-SQ8 search, 10M x 96, nlist 16384, nprobe 64, 10000 queries, k 10",
+                   "n_base": n_base, "nlist": nlist, "nprobe": min(NPROBE, nlist), "k": K},
+        "cpu_baseline": {"value": value, "unit": "queries/s", "cores": cores, "kind": kind,
+                         "sample": f"{sample} of {n_query} queries per step, scan + top-k only "
+                                   "(probe lists precomputed), one query per thread"},
+        "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# engine arm
+# ------------------------------------------------------------------------------------------------
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "engine":
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+
+    from vsag_b200 import engine
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    n_base, n_query, nlist = scaled(N_BASE), scaled(N_QUERY), max(16, scaled(NLIST))
+    nprobe = min(NPROBE, nlist)
+    base, queries = make_data(device, n_base, n_query)
+    ix = build_index(engine, base, nlist, rank, world, dist)
+
+    out_ids = torch.empty((n_query, K), dtype=torch.int64, device=device)
+    out_d = torch.empty((n_query, K), dtype=torch.float32, device=device)
+    if world > 1:
+        keys_local = torch.empty((n_query, K), dtype=torch.int64, device=device)
+        labels_local = torch.empty((n_query, K), dtype=torch.int64, device=device)
+        keys_all = torch.empty((world, n_query, K), dtype=torch.int64, device=device)
+        labels_all = torch.empty((world, n_query, K), dtype=torch.int64, device=device)
+
+    def step_device():
+        if world == 1:
+            ix.search(queries, K, nprobe, out=(out_ids, out_d))
+        else:
+            # every rank scans the probed lists it owns; the per-shard top-k are exchanged with
+            # one all-gather over NVLink and merged locally on every rank
+            ix.search_partial(queries, K, nprobe, 2.0, keys_local, labels_local)
+            dist.all_gather_into_tensor(keys_all, keys_local)
+            dist.all_gather_into_tensor(labels_all, labels_local)
+            engine._capi.check(engine._capi.load().vb200_merge_partials(
+                engine.ptr(keys_all), engine.ptr(labels_all), world, n_query, K, engine.ptr(out_ids),
+                engine.ptr(out_d)))
+
+    def timed(fn, steps: int):
+        """K steps between a barrier + synchronize on both sides; device time from CUDA events on
+        the launching (default) stream; max over ranks."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step_device()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = engine.kernel_launches()
+    scan_ms, scan_bytes = [], []
+
+    def step_and_probe():
+        step_device()
+
+    total_ms = timed(step_and_probe, args.steps)
+    launches = engine.kernel_launches() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    # Kernel-only timing of the scan: events recorded by the library around its launch, read after
+    # a few more (untimed-for-value) steps so the read-back does not sit in the region above.
+    for _ in range(min(5, args.steps)):
+        step_device()
+        scan_ms.append(ix.last_scan_ms())
+        scan_bytes.append(ix.last_scan_bytes())
+    ms_per_step = total_ms / args.steps
+    value = n_query / (ms_per_step / 1e3)
+
+    # end to end: pinned host queries in, host results out, through the same C-ABI call
+    q_host = torch.empty((n_query, DIM), dtype=torch.float32, pin_memory=True)
+    q_host.copy_(queries)
+    ids_host = torch.empty((n_query, K), dtype=torch.int64, pin_memory=True)
+    d_host = torch.empty((n_query, K), dtype=torch.float32, pin_memory=True)
+
+    def step_e2e():
+        if world == 1:
+            ix.search(q_host, K, nprobe, out=(ids_host, d_host))
+        else:
+            queries.copy_(q_host, non_blocking=True)
+            step_device()
+            ids_host.copy_(out_ids, non_blocking=True)
+            d_host.copy_(out_d, non_blocking=True)
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps) / args.steps
+    e2e_value = n_query / (e2e_ms / 1e3)
+
+    if world > 1:
+        sb = torch.tensor([float(np.mean(scan_bytes))], dtype=torch.float64, device=device)
+        dist.all_reduce(sb, op=dist.ReduceOp.SUM)
+        total_scan_bytes = float(sb.item())
+    else:
+        total_scan_bytes = float(np.mean(scan_bytes))
+
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        kernel_ms = float(np.mean(scan_ms))
+        achieved = float(np.mean(scan_bytes)) / (kernel_ms / 1e3) / 1e9
+        line = {
+            "metric": "QPS at nprobe=64, IVF-SQ8 10Mx96, k=10", "value": value, "unit": "queries/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "IVF-SQ8 search, 10M x 96, nlist 16384, nprobe 64, 10000 queries, k 10",
+                       "n_base": n_base, "dim": DIM, "nlist": nlist, "nprobe": nprobe, "n_query": n_query,
+                       "k": K, "parallelism": f"lists sharded over {world} GPU(s)",
+                       "l2_policy": "codes (960 MB) exceed the 126 MB L2; no flush between steps"},
+            "e2e": {"value": e2e_value, "unit": "queries/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": n_query * DIM * 4, "d2h_bytes_per_step": n_query * K * 12},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "ivf_sq8_scan_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                         "traffic": SCAN_TRAFFIC_BYTES, "kernel_ms": kernel_ms,
+                         "algorithmic_bytes_per_launch": float(np.mean(scan_bytes)),
+                         "all_ranks_algorithmic_bytes": total_scan_bytes},
+        }
+        if world == 1:
+            # recall of the measured configuration and the CPU baseline, outside the timed regions
+            line["config"]["recall_at_10"] = recall_at_k(engine, base, queries, out_ids,
+                                                         min(n_query, env_int("VB200_RECALL_SAMPLE", 1000)))
+            qh = q_host.numpy()
+            host = cpu_scan_setup(ix, qh, nprobe)
+            sample = min(n_query, env_int("VB200_CPU_SAMPLE", 2000))
+            cpu_scan_run(host, qh, min(sample, 100))
+            qps, kind, cores, dt, cpu_ids, cpu_d = cpu_scan_run(host, qh, sample)
+            got = ids_host.numpy()[:sample]
+            line["cpu_baseline"] = {"value": qps, "unit": "queries/s", "cores": cores, "kind": kind,
+                                    "sample": f"{sample} of {n_query} queries, scan + top-k only (probe lists "
+                                              f"precomputed), one query per thread, {dt:.2f} s",
+                                    "ids_agree_with_gpu": float(np.mean(cpu_ids == got))}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -226,6 +226,10 @@ VB200_API int vb200_ivf_search_partial(vb200_ivf_t index, const float* queries, 
  * code size), the figure the HBM roofline of the scan is computed from. */
 VB200_API int64_t vb200_ivf_last_scan_bytes(vb200_ivf_t index);
 
+/* Device time of the last search's list-scan kernel in milliseconds, from CUDA events recorded
+ * around its launch on the stream it ran on. */
+VB200_API int vb200_ivf_last_scan_ms(vb200_ivf_t index, float* ms);
+
 /* Merges `parts` partial results laid out [parts][nq][k] (as gathered from the ranks) into
  * ids[nq x k], dists[nq x k].  Inputs are device pointers; outputs host or device. */
 VB200_API int vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32_t parts,

@@ -1,0 +1,201 @@
+"""GPU parity: IVF-SQ8 build layout, routing, list scan with fused top-k, sharding and merge,
+against the CPU oracle, through the C ABI."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from conftest import assert_topk_equal, mixture
+
+pytestmark = pytest.mark.gpu
+
+
+def build_pair(engine, oracle, n, dim, nlist, metric=0, seed=0, iters=3):
+    """Oracle model (centroids, bounds, lists) and an engine index fed with the same model."""
+    x = mixture(seed, n, dim, max(nlist, 2), 0.15)
+    centroids, _, _, _ = oracle.kmeans_run(x, x[:nlist].copy(), iters)
+    labels, _ = oracle.kmeans_assign(x, centroids)
+    lower, diff = oracle.sq8_train(x)
+    off, order = oracle.build_lists(labels, nlist)
+    codes = oracle.sq8_encode(x, lower, diff)[order]
+    ix = engine.IvfHandle(dim, metric, nlist, engine.QUANT_SQ8)
+    ix.set_centroids(centroids)
+    ix.set_sq8_model(lower, diff)
+    ids = np.arange(n, dtype=np.int64) * 3 + 7  # labels differ from inner ids
+    return dict(x=x, centroids=centroids, labels=labels, lower=lower, diff=diff, off=off, order=order,
+                codes=codes, ids=ids, ix=ix)
+
+
+@pytest.mark.parametrize("dim", [1, 7, 96, 100])
+def test_build_layout_matches_oracle(engine, oracle, dim):
+    m = build_pair(engine, oracle, 8000, dim, 24, seed=dim)
+    m["ix"].add(m["x"], m["ids"])  # the engine assigns rows itself
+    sizes, codes, inner = m["ix"].get_lists()
+    assert np.array_equal(sizes, np.diff(m["off"]))
+    assert np.array_equal(inner, m["order"])
+    assert np.array_equal(codes, m["codes"])
+    assert m["ix"].num_elements() == 8000
+
+
+def test_trained_model_matches_oracle(engine, oracle):
+    n, dim, nlist = 20_000, 32, 40
+    x = mixture(4, n, dim, nlist, 0.15)
+    ix = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+    ix.train(x, iters=4)
+    want_c, _, _, _ = oracle.kmeans_run(x, x[:nlist].copy(), 4)
+    np.testing.assert_allclose(ix.get_centroids(), want_c, rtol=1e-3, atol=1e-4)
+    lower, diff = ix.get_sq8_model()
+    want_lower, want_diff = oracle.sq8_train(x)
+    assert np.array_equal(lower, want_lower) and np.array_equal(diff, want_diff)
+
+
+def test_incremental_add_equals_single_add(engine, oracle):
+    m = build_pair(engine, oracle, 9000, 16, 20, seed=3)
+    ix = m["ix"]
+    ix.add(m["x"][:4000], m["ids"][:4000])
+    ix.add(m["x"][4000:4001], m["ids"][4000:4001])
+    ix.add(m["x"][4001:], m["ids"][4001:])
+    sizes, codes, inner = ix.get_lists()
+    assert np.array_equal(sizes, np.diff(m["off"]))
+    assert np.array_equal(inner, m["order"])
+    assert np.array_equal(codes, m["codes"])
+
+
+@pytest.mark.parametrize("metric", [0, 1])
+def test_routing_matches_exact_oracle(engine, oracle, metric):
+    m = build_pair(engine, oracle, 6000, 48, 200, metric=metric, seed=8)
+    q = mixture(80, 300, 48, 200, 0.15)
+    for nprobe in (1, 16, 200):
+        want_ids, want_d = oracle.route(q, m["centroids"], nprobe, metric)
+        got_ids, got_d = m["ix"].route(q, nprobe)
+        np.testing.assert_allclose(got_d, want_d, rtol=1e-6, atol=1e-6)
+        assert_topk_equal(got_ids, got_d, want_ids, want_d, rtol=1e-6)
+
+
+@pytest.mark.parametrize("metric", [0, 1])
+@pytest.mark.parametrize("dim,k", [(96, 10), (7, 1), (100, 100), (1, 5)])
+def test_scan_matches_oracle_with_same_buckets(engine, oracle, metric, dim, k):
+    nlist = 30
+    m = build_pair(engine, oracle, 12_000, dim, nlist, metric=metric, seed=dim + k)
+    m["ix"].add(m["x"], m["ids"], labels=m["labels"])
+    q = mixture(99, 257, dim, nlist, 0.15)
+    probes, _ = oracle.route(q, m["centroids"], 9, metric)
+    probes[5, 3:] = -1          # a query with fewer buckets
+    probes[6, :] = -1           # and one with none
+    want = oracle.ivf_sq8_search(m["codes"], m["off"], m["ids"][m["order"]], m["lower"], m["diff"], q,
+                                 probes, k, metric)
+    got = m["ix"].search(q, k, 9, bucket_ids=probes)
+    assert_topk_equal(got[0], got[1], want[0], want[1], rtol=1e-5, atol=1e-5)
+    assert np.all(got[0][6] == -1) and np.all(np.isinf(got[1][6]))
+    fin = np.isfinite(got[1])
+    assert np.all(np.diff(np.where(fin, got[1], np.inf), axis=1) >= 0)  # ascending, padding last
+
+
+def test_ragged_lists(engine, oracle):
+    """List lengths 0, 1, 31, 32, 33, 127, 128, 129, 300 (the reference scans 32 codes at a time,
+    the engine 128 rows per pass)."""
+    dim = 24
+    lens = [0, 1, 31, 32, 33, 127, 128, 129, 300, 0]
+    nlist = len(lens)
+    labels = np.concatenate([np.full(c, l, np.int32) for l, c in enumerate(lens)])
+    rng = np.random.default_rng(0)
+    rng.shuffle(labels)
+    n = labels.size
+    x = mixture(5, n, dim, 8, 0.2)
+    lower, diff = oracle.sq8_train(x)
+    off, order = oracle.build_lists(labels, nlist)
+    codes = oracle.sq8_encode(x, lower, diff)[order]
+    ix = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+    ix.set_centroids(mixture(6, nlist, dim, 8, 0.2))
+    ix.set_sq8_model(lower, diff)
+    ids = np.arange(n, dtype=np.int64)
+    ix.add(x, ids, labels=labels)
+    sizes, got_codes, inner = ix.get_lists()
+    assert sizes.tolist() == lens and np.array_equal(got_codes, codes) and np.array_equal(inner, order)
+    q = mixture(7, 40, dim, 8, 0.2)
+    probes = np.tile(np.arange(nlist, dtype=np.int32), (40, 1))
+    for k in (1, 10, 400):
+        want = oracle.ivf_sq8_search(codes, off, order, lower, diff, q, probes, k)
+        got = ix.search(q, k, nlist, bucket_ids=probes)
+        assert_topk_equal(got[0], got[1], want[0], want[1], rtol=1e-5, atol=1e-5)
+
+
+def test_end_to_end_search_matches_oracle_pipeline(engine, oracle):
+    dim, nlist, k, nprobe = 96, 64, 10, 8
+    m = build_pair(engine, oracle, 30_000, dim, nlist, seed=21)
+    m["ix"].add(m["x"], m["ids"])
+    q = mixture(22, 500, dim, nlist, 0.15)
+    probes, _ = oracle.route(q, m["centroids"], nprobe)
+    want = oracle.ivf_sq8_search(m["codes"], m["off"], m["ids"][m["order"]], m["lower"], m["diff"], q,
+                                 probes, k)
+    got = m["ix"].search(q, k, nprobe)
+    assert_topk_equal(got[0], got[1], want[0], want[1], rtol=1e-5, atol=1e-5)
+    # single-query calls give the rows of the batched call (the reference's batch branch loops
+    # over queries, ivf.cpp:2137-2210)
+    for i in (0, 17, 499):
+        one = m["ix"].search(q[i:i + 1], k, nprobe)
+        assert np.array_equal(one[0][0], got[0][i]) and np.array_equal(one[1][0], got[1][i])
+    assert m["ix"].last_scan_bytes() == int(dim) * int(np.sum(np.diff(m["off"])[probes[499]]))
+
+
+def test_device_resident_queries_and_outputs(engine, oracle):
+    import torch
+
+    m = build_pair(engine, oracle, 10_000, 32, 16, seed=31)
+    m["ix"].add(torch.from_numpy(m["x"]).cuda(), torch.from_numpy(m["ids"]).cuda())
+    q = mixture(32, 64, 32, 16, 0.15)
+    host = m["ix"].search(q, 5, 4)
+    dev = m["ix"].search(torch.from_numpy(q).cuda(), 5, 4)
+    assert dev[0].is_cuda and np.array_equal(dev[0].cpu().numpy(), host[0])
+    assert np.array_equal(dev[1].cpu().numpy(), host[1])
+
+
+def test_search_edge_cases(engine, oracle):
+    dim, nlist = 8, 4
+    ix = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+    q = np.zeros((3, dim), np.float32)
+    with pytest.raises(engine.VsagB200Error, match="not trained"):
+        ix.search(q, 5, 2)
+    x = mixture(1, 50, dim, 4, 0.2)
+    ix.train(x, iters=2)
+    ids, dists = ix.search(q, 5, 2)           # trained but empty
+    assert np.all(ids == -1) and np.all(np.isinf(dists))
+    ix.add(x[:3], np.array([100, 200, 300], np.int64))
+    ids, dists = ix.search(q, 5, 99)          # nprobe clamps to nlist, k exceeds the population
+    assert sorted(ids[0][:3].tolist()) == [100, 200, 300] and np.all(ids[:, 3:] == -1)
+    with pytest.raises(engine.VsagB200Error):
+        ix.search(q, 0, 2)
+    with pytest.raises(engine.VsagB200Error):
+        ix.search(q, 5, 0)
+    empty = ix.search(np.zeros((0, dim), np.float32), 5, 2)
+    assert empty[0].shape == (0, 5)
+    with pytest.raises(engine.VsagB200Error, match="precede"):
+        ix.set_shard(0, 2)
+
+
+def test_list_sharded_search_equals_unsharded(engine, oracle):
+    """Two shards on one GPU (lists dealt round-robin), partial results merged the way the ranks
+    merge them after the all-gather."""
+    import torch
+
+    dim, nlist, k, nprobe, nq = 32, 48, 10, 12, 200
+    m = build_pair(engine, oracle, 20_000, dim, nlist, seed=41)
+    m["ix"].add(m["x"], m["ids"])
+    q = mixture(42, nq, dim, nlist, 0.15)
+    want = m["ix"].search(q, k, nprobe)
+    world = 3
+    keys = torch.empty((world, nq, k), dtype=torch.int64, device="cuda")
+    labels = torch.empty((world, nq, k), dtype=torch.int64, device="cuda")
+    shards = []
+    for r in range(world):
+        s = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+        s.set_shard(r, world)
+        s.set_centroids(m["centroids"])
+        s.set_sq8_model(m["lower"], m["diff"])
+        s.add(m["x"], m["ids"])
+        sizes, _, _ = s.get_lists()
+        assert np.all(sizes[np.arange(nlist) % world != r] == 0)
+        s.search_partial(q, k, nprobe, 2.0, keys[r], labels[r])
+        shards.append(s)
+    got = engine.merge_partials(keys, labels, world, nq, k)
+    assert_topk_equal(got[0], got[1], want[0], want[1], rtol=0, atol=0)

@@ -86,6 +86,17 @@ struct vb200_ivf {
     SearchWorkspace ws;
     std::mutex mu;
     int64_t last_scan_bytes = 0;
+    cudaEvent_t ev_scan_begin = nullptr, ev_scan_end = nullptr;  // bracket the list-scan kernel
+    bool scan_timed = false;
+
+    ~vb200_ivf() {
+        if (ev_scan_begin != nullptr) {
+            cudaEventDestroy(ev_scan_begin);
+        }
+        if (ev_scan_end != nullptr) {
+            cudaEventDestroy(ev_scan_end);
+        }
+    }
 };
 
 namespace vb200 {
@@ -565,6 +576,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kscan, 
     p.diff = ix->diff.ptr;
     p.inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(ix->dim));
     p.metric = ix->metric;
+    VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
     if (ix->quant == VB200_QUANT_SQ8) {
         size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, (2 + SQ8_QT) * ix->dpad);
         if (ix->metric == VB200_METRIC_L2) {
@@ -576,6 +588,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kscan, 
         size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
         VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
     }
+    VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
+    ix->scan_timed = true;
     VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.keys.ptr));
     const uint64_t nkeys = nq * kscan;
     VB_LAUNCH(keys_pos_to_inner_kernel, static_cast<uint32_t>((nkeys + 255) / 256), 256, 0, ws.keys.ptr,
@@ -694,6 +708,11 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
     }
     ix->list_off_host.assign(nlist + 1, 0);
     int s = ix->list_off.reserve(nlist + 1);
+    if (s == 0 && (cudaEventCreate(&ix->ev_scan_begin) != cudaSuccess ||
+                   cudaEventCreate(&ix->ev_scan_end) != cudaSuccess)) {
+        set_last_error(VB200_INTERNAL_ERROR, "cudaEventCreate failed");
+        s = VB200_INTERNAL_ERROR;
+    }
     if (s == 0) {
         cudaError_t e = cudaMemset(ix->list_off.ptr, 0, (nlist + 1) * sizeof(uint32_t));
         if (e != cudaSuccess) {
@@ -1150,6 +1169,18 @@ vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint
 extern "C" int64_t
 vb200_ivf_last_scan_bytes(vb200_ivf_t ix) {
     return ix == nullptr ? 0 : ix->last_scan_bytes;
+}
+
+extern "C" int
+vb200_ivf_last_scan_ms(vb200_ivf_t ix, float* ms) {
+    VB_CHECK_ARG(ix != nullptr && ms != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (!ix->scan_timed) {
+        VB_FAIL(VB200_WRONG_STATUS, "no search has run on this index yet");
+    }
+    VB_CUDA(cudaEventSynchronize(ix->ev_scan_end));
+    VB_CUDA(cudaEventElapsedTime(ms, ix->ev_scan_begin, ix->ev_scan_end));
+    return 0;
 }
 
 // labels gathered beside tagged keys: payload indexes the gathered label array.

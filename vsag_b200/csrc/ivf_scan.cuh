@@ -389,7 +389,7 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
             if (valid) {
                 float bn = __ldg(reinterpret_cast<const float*>(code + bits_bytes));
                 float err = __ldg(reinterpret_cast<const float*>(code + bits_bytes + 4));
-                if (fabsf(err) < 1e-5f) {
+                if (static_cast<double>(fabsf(err)) < 1e-5) {  // float compared with a double literal, as in the reference
                     err = err >= 0.f ? 1.0f : -1.0f;
                 }
 #pragma unroll

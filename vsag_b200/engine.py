@@ -242,6 +242,11 @@ class IvfHandle:
     def last_scan_bytes(self) -> int:
         return int(self._lib.vb200_ivf_last_scan_bytes(self._h))
 
+    def last_scan_ms(self) -> float:
+        ms = C.c_float(0.0)
+        check(self._lib.vb200_ivf_last_scan_ms(self._h, C.byref(ms)))
+        return float(ms.value)
+
 
 class BfHandle:
     """Owns a vb200_bf_t."""
