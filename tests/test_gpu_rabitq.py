@@ -75,7 +75,10 @@ def test_rerank_matches_oracle(engine, oracle):
     want = oracle.rerank_fp32(m["x"], q, cand, k)
     got = m["ix"].search(q, k, nprobe, factor=factor, bucket_ids=probes)
     assert_topk_equal(got[0], got[1], want[0], want[1], rtol=1e-5, atol=1e-6)
-    # recall against exact search is what the rerank is for
+    # the rerank exists to raise recall against exact search over the 1-bit estimate alone
     exact, _ = oracle.bf_search_fp32(m["x"], q, k)
-    recall = np.mean([len(set(a) & set(b)) / k for a, b in zip(got[0].tolist(), exact.tolist())])
-    assert recall > 0.6
+
+    def recall(ids):
+        return np.mean([len(set(a) & set(b)) / k for a, b in zip(ids.tolist(), exact.tolist())])
+
+    assert recall(got[0]) > recall(cand[:, :k])
