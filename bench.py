@@ -425,7 +425,7 @@ def main() -> None:
                          "algorithmic_bytes_per_launch": float(np.mean(scan_bytes)),
                          "all_ranks_algorithmic_bytes": total_scan_bytes},
         }
-        if world == 1:
+        if world == 1 and not env_int("VB200_BENCH_SKIP_EXTRAS", 0):
             # recall of the measured configuration and the CPU baseline, outside the timed regions
             line["config"]["recall_at_10"] = recall_at_k(engine, base, queries, out_ids,
                                                          min(n_query, env_int("VB200_RECALL_SAMPLE", 1000)))

@@ -86,6 +86,8 @@ def test_scan_matches_oracle_with_same_buckets(engine, oracle, metric, dim, k):
                                  probes, k, metric)
     got = m["ix"].search(q, k, 9, bucket_ids=probes)
     assert_topk_equal(got[0], got[1], want[0], want[1], rtol=1e-5, atol=1e-5)
+    # survivors are re-scored in the reference's operation order: distances are bit-equal
+    assert np.array_equal(got[1], want[1])
     assert np.all(got[0][6] == -1) and np.all(np.isinf(got[1][6]))
     assert np.all(got[1][:, 1:] >= got[1][:, :-1])  # ascending, +inf padding last
 

@@ -13,6 +13,7 @@ namespace vb200 {
 constexpr uint32_t NONE32 = 0xFFFFFFFFu;
 constexpr uint32_t ROUTE_SLACK = 8;   // extra routing candidates re-scored exactly
 constexpr int SQ8_QT = 16;
+constexpr uint32_t SQ8_SLACK = 16;    // survivors kept beyond k for exact re-scoring
 constexpr int RABITQ_QT = 8;
 
 template <typename T>
@@ -38,6 +39,8 @@ grow_preserve(DevBuf<T>& buf, size_t keep, size_t need) {
 struct SearchWorkspace {
     DevBuf<float> queries;      // staged queries / processed RaBitQ queries
     DevBuf<float> qproc;
+    DevBuf<float> qw, qa;       // SQ8 per-query weights and constants
+    DevBuf<uint64_t> merged;    // SQ8 survivors before exact re-scoring
     DevBuf<float> scores;       // routing score slab
     DevBuf<uint64_t> cand;      // routing candidates
     DevBuf<int32_t> probes;     // [nq x nprobe]
@@ -71,6 +74,8 @@ struct vb200_ivf {
     bool has_centroids = false, has_model = false, has_rotation = false;
     DevBuf<float> centroids, c_sq;
     DevBuf<float> lower, diff;           // SQ8, padded to dpad
+    DevBuf<float> sq_scale, sq_mid;      // SQ8: diff/255 and lower + 128*diff/255, padded to dpad
+    DevBuf<float> code_norm;             // SQ8: |decoded code|^2 per position
     DevBuf<float> rotation, rq_centroid; // RaBitQ
 
     uint64_t n_total = 0;   // rows seen (inner ids 0 .. n_total-1)
@@ -173,6 +178,80 @@ ivf_place_new_kernel(const uint64_t* __restrict__ sorted_keys, uint64_t n, uint3
     uint32_t np = new_off[list] + old_size + static_cast<uint32_t>(s - add_off[list]);
     dst_of_row[row] = np;
     new_inner[np] = inner_base + row;
+}
+
+// scale_d = diff_d / 255, mid_d = lower_d + 128 * scale_d (zero beyond dim).
+__global__ void
+sq8_derive_model_kernel(const float* __restrict__ lower, const float* __restrict__ diff, uint32_t dim,
+                        uint32_t dpad, float* __restrict__ scale, float* __restrict__ mid) {
+    uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= dpad) {
+        return;
+    }
+    float s = 0.f, m = 0.f;
+    if (d < dim) {
+        s = __fdiv_rn(diff[d], 255.0f);
+        m = fmaf(128.0f, s, lower[d]);
+    }
+    scale[d] = s;
+    mid[d] = m;
+}
+
+// code_norm[p] = sum_d x_d^2 with x_d the reference's decode fma(code * (1/255), diff, lower).
+__global__ void
+sq8_code_norm_kernel(const uint8_t* __restrict__ codes, uint64_t n, uint32_t dim, uint32_t code_stride,
+                     const float* __restrict__ lower, const float* __restrict__ diff,
+                     float* __restrict__ code_norm) {
+    uint64_t p = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (p >= n) {
+        return;
+    }
+    const uint8_t* c = codes + p * code_stride;
+    const float inv255 = 1.0f / 255.0f;
+    float s = 0.f;
+    for (uint32_t d0 = 0; d0 < dim; d0 += 16) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(c + d0));
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            uint32_t d = d0 + j;
+            if (d < dim) {
+                float code = static_cast<float>((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+                float x = fmaf(__fmul_rn(code, inv255), __ldg(diff + d), __ldg(lower + d));
+                s = fmaf(x, x, s);
+            }
+        }
+    }
+    code_norm[p] = s;
+}
+
+// One warp per query: qw[q][d] = q_d * scale_d (zero padded) and
+//   L2: qa = |q|^2 - 2 sum q_d mid_d      IP: qa = 1 - sum q_d mid_d
+__global__ void __launch_bounds__(128)
+sq8_query_prep_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t dim, uint32_t dpad,
+                      const float* __restrict__ scale, const float* __restrict__ mid, int metric,
+                      float* __restrict__ qw, float* __restrict__ qa) {
+    uint64_t q = static_cast<uint64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    uint32_t lane = threadIdx.x & 31;
+    if (q >= nq) {
+        return;
+    }
+    const float* src = queries + q * dim;
+    float* dst = qw + q * dpad;
+    float qq = 0.f, qm = 0.f;
+    for (uint32_t d = lane; d < dpad; d += 32) {
+        float v = d < dim ? __ldg(src + d) : 0.f;
+        dst[d] = v * scale[d];
+        qq = fmaf(v, v, qq);
+        qm = fmaf(v, mid[d], qm);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        qq += __shfl_xor_sync(0xffffffffu, qq, off);
+        qm += __shfl_xor_sync(0xffffffffu, qm, off);
+    }
+    if (lane == 0) {
+        qa[q] = metric == VB200_METRIC_L2 ? fmaf(-2.0f, qm, qq) : 1.0f - qm;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -518,15 +597,18 @@ launch_scan(Kernel kernel, const ScanParams& p, size_t smem) {
 // Scans the probed lists of every query and leaves, per query, the kscan best as keys
 // (payload = inner id) in ws.keys.
 static int
-ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kscan, uint32_t nprobe,
+ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal, uint32_t nprobe,
                 const int32_t* probes_dev) {
     SearchWorkspace& ws = ix->ws;
+    const bool sq8 = ix->quant == VB200_QUANT_SQ8;
+    // SQ8 ranks with a re-associated distance and re-scores a few more survivors exactly.
+    const uint32_t kscan = sq8 ? kfinal + SQ8_SLACK : kfinal;
     const uint32_t nlist = ix->nlist;
     const uint64_t total = nq * nprobe;
     VB_CHECK_ARG(total < 0xFFFFFFFFull, "query batch too large: %llu probes",
                  static_cast<unsigned long long>(total));
-    VB_CHECK_ARG(kscan >= 1 && kscan <= 1024 - SCAN_THREADS, "k = %u out of range [1, %d]", kscan,
-                 1024 - SCAN_THREADS);
+    VB_CHECK_ARG(kfinal >= 1 && kscan <= 1024 - SCAN_THREADS, "k = %u out of range [1, %u]", kfinal,
+                 1024 - SCAN_THREADS - (sq8 ? SQ8_SLACK : 0));
     const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : RABITQ_QT;
 
     VB_TRY(ws.pair_cnt.reserve(nlist + 1));
@@ -537,8 +619,13 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kscan, 
     VB_TRY(ws.pair_slot.reserve(total));
     VB_TRY(ws.thr.reserve(nq));
     VB_TRY(ws.part.reserve(total * kscan));
-    VB_TRY(ws.keys.reserve(nq * kscan));
+    VB_TRY(ws.keys.reserve(nq * kfinal));
     VB_TRY(ws.scalars.reserve(2));
+    if (sq8) {
+        VB_TRY(ws.qw.reserve(nq * ix->dpad));
+        VB_TRY(ws.qa.reserve(nq));
+        VB_TRY(ws.merged.reserve(nq * kscan));
+    }
     cudaStream_t st = current_stream();
     VB_CUDA(cudaMemsetAsync(ws.pair_cnt.ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
     VB_CUDA(cudaMemsetAsync(ws.cursor.ptr, 0, nlist * sizeof(uint32_t), st));
@@ -572,26 +659,37 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kscan, 
     p.thr_g = ws.thr.ptr;
     p.part = ws.part.ptr;
     p.queries = q_dev;
-    p.lower = ix->lower.ptr;
-    p.diff = ix->diff.ptr;
+    p.qw = ws.qw.ptr;
+    p.qa = ws.qa.ptr;
+    p.code_norm = ix->code_norm.ptr;
+    p.coef_b = ix->metric == VB200_METRIC_L2 ? 1.0f : 0.0f;
+    p.coef_c = ix->metric == VB200_METRIC_L2 ? -2.0f : -1.0f;
     p.inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(ix->dim));
     p.metric = ix->metric;
+    if (sq8) {
+        VB_LAUNCH(sq8_query_prep_kernel, static_cast<uint32_t>((nq + 3) / 4), 128, 0, q_dev, nq, ix->dim,
+                  ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
+    }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
-    if (ix->quant == VB200_QUANT_SQ8) {
-        size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, (2 + SQ8_QT) * ix->dpad);
-        if (ix->metric == VB200_METRIC_L2) {
-            VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT, VB200_METRIC_L2>, p, smem));
-        } else {
-            VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT, VB200_METRIC_IP>, p, smem));
-        }
+    if (sq8) {
+        size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
+        VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem));
     } else {
         size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
         VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
     ix->scan_timed = true;
-    VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.keys.ptr));
-    const uint64_t nkeys = nq * kscan;
+    if (sq8) {
+        VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.merged.ptr));
+        uint32_t n2 = next_pow2(kscan < 2 ? 2 : kscan);
+        VB_LAUNCH(sq8_rescore_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev, ix->dim,
+                  ix->codes.ptr, ix->code_stride, ix->lower.ptr, ix->diff.ptr, ws.merged.ptr, kscan, n2,
+                  kfinal, ix->metric, ws.keys.ptr);
+    } else {
+        VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.keys.ptr));
+    }
+    const uint64_t nkeys = nq * kfinal;
     VB_LAUNCH(keys_pos_to_inner_kernel, static_cast<uint32_t>((nkeys + 255) / 256), 256, 0, ws.keys.ptr,
               nkeys, ix->pos_inner.ptr);
     return 0;
@@ -785,6 +883,10 @@ ivf_store_sq8_model(vb200_ivf* ix, const float* lower_any, const float* diff_any
     VB_CUDA(cudaMemsetAsync(ix->diff.ptr, 0, ix->dpad * sizeof(float), st));
     VB_CUDA(cudaMemcpyAsync(ix->lower.ptr, lower_any, ix->dim * sizeof(float), cudaMemcpyDefault, st));
     VB_CUDA(cudaMemcpyAsync(ix->diff.ptr, diff_any, ix->dim * sizeof(float), cudaMemcpyDefault, st));
+    VB_TRY(ix->sq_scale.reserve(ix->dpad));
+    VB_TRY(ix->sq_mid.reserve(ix->dpad));
+    VB_LAUNCH(sq8_derive_model_kernel, (ix->dpad + 127) / 128, 128, 0, ix->lower.ptr, ix->diff.ptr, ix->dim,
+              ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr);
     ix->has_model = true;
     return 0;
 }
@@ -1007,8 +1109,15 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
         VB_CUDA(cudaMemcpyAsync(ix->flat.ptr + ix->n_total * dim, x.ptr, count * dim * sizeof(float),
                                 cudaMemcpyDeviceToDevice, st));
     }
+    DevBuf<float> new_norm;
+    if (ix->quant == VB200_QUANT_SQ8 && n_new_stored > 0) {
+        VB_TRY(new_norm.reserve(n_new_stored));
+        VB_LAUNCH(sq8_code_norm_kernel, static_cast<uint32_t>((n_new_stored + 127) / 128), 128, 0,
+                  new_codes.ptr, n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_norm.ptr);
+    }
     VB_TRY(sync_stream());
     // 7. commit
+    ix->code_norm = std::move(new_norm);
     ix->codes = std::move(new_codes);
     ix->pos_inner = std::move(new_inner);
     ix->list_off = std::move(new_off_dev);

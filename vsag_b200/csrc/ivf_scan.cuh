@@ -2,8 +2,8 @@
 //
 // Schedule: list-major.  The (query, probed list) pairs of a search batch are grouped by list; a
 // work item is one list and up to QT of the queries that probe it.  A persistent CTA takes items
-// from an atomic counter; each thread owns one code row of the list at a time, decodes it once and
-// scores it against every query of the tile, whose vectors sit in shared memory.  So the codes of
+// from an atomic counter; each thread owns a few code rows of the list at a time, converts them
+// once and scores them against every query of the tile, whose vectors sit in shared memory.  So the codes of
 // a list cross HBM once per tile (and are L2 hits for the other tiles of the same list) instead
 // of once per query as in the reference's query-major loop (src/algorithm/ivf/ivf.cpp:1741-1767,
 // src/datacell/bucket_datacell.h:526-572).
@@ -40,9 +40,12 @@ struct ScanParams {
     uint32_t cap;                // per-query candidate buffer, power of two >= k + SCAN_THREADS
     uint32_t* thr_g;             // [nq] global bound, ordered distance
     uint64_t* part;              // [slots x k] partial results
-    const float* queries;        // SQ8: [nq x dim]; RaBitQ: [nq x (dim + 1)] processed queries
-    const float* lower;          // SQ8 model, padded to dpad with zeros
-    const float* diff;
+    const float* queries;        // RaBitQ: [nq x (dim + 1)] processed queries
+    const float* qw;             // SQ8: [nq x dpad] weights q_d * diff_d / 255, zero padded
+    const float* qa;             // SQ8: [nq] per-query constant of the distance
+    const float* code_norm;      // SQ8: [positions] |x|^2 of each decoded code
+    float coef_b;                // SQ8: distance = qa + coef_b * |x|^2 + coef_c * dot
+    float coef_c;
     float inv_sqrt_d;            // RaBitQ
     int metric;
 };
@@ -169,34 +172,100 @@ tile_smem_bytes(uint32_t cap, uint32_t float_count) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// SQ8: distance of SQ8ComputeL2Sqr / SQ8ComputeIP (src/simd/kernels/sq8_compute.h:44-137):
-// x = fma(code * (1/255), diff, lower); L2: sum (q - x)^2; IP: 1 - sum q * x.
+// SQ8 scan.
+//
+// Reference arithmetic (SQ8ComputeL2Sqr / SQ8ComputeIP, src/simd/kernels/sq8_compute.h:44-137):
+//   x_d = fma(code_d * (1/255), diff_d, lower_d);  L2: sum (q_d - x_d)^2;  IP: 1 - sum q_d * x_d.
+//
+// The scan ranks candidates with an algebraically equal form that costs one FMA per
+// (query, code, dimension) instead of a subtract and an FMA:
+//   with c'_d = code_d - 128 (an int8), s_d = diff_d / 255, mid_d = lower_d + 128 s_d:
+//     x_d = c'_d s_d + mid_d,   sum q_d x_d = sum (q_d s_d) c'_d + sum q_d mid_d
+//   L2: |q|^2 - 2 sum q_d mid_d  +  |x|^2  - 2 sum w_d c'_d,     w_d = q_d s_d
+//   IP: 1 - sum q_d mid_d                  -   sum w_d c'_d
+// w (per query) and |x|^2 (per code) are prepared outside the loop, so the inner loop is a pure
+// FMA of a converted code byte with a weight from shared memory.  Its rounding differs from the
+// reference's order by a few 1e-6 relative; the k + slack survivors of every query are therefore
+// re-scored with the reference's exact operation order afterwards (sq8_rescore_kernel), and only
+// those exact distances are returned.
+//
+// Register tile: a thread owns R code rows (rows t, t+128, ...) and QT accumulators per row, so
+// one 128-bit shared-memory load of weights feeds 4*R FMAs.
 // ---------------------------------------------------------------------------------------------
-template <int QT, int METRIC>
+constexpr int SQ8_ROWS = 4;   // code rows per thread
+
+template <int QT, int NR, int NG>
+__device__ __forceinline__ void
+sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_s, uint32_t dpad,
+              float (&acc)[SQ8_ROWS][QT]) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+#pragma unroll
+        for (int qi = 0; qi < NG * 4; ++qi) {
+            acc[r][qi] = 0.f;
+        }
+    }
+    // Four dimensions per trip, not unrolled: the fully unrolled body (4*NR*NG*4 FMAs) is what has to
+    // stay resident in the instruction cache.
+#pragma unroll 1
+    for (uint32_t c = 0; c < dpad; c += 4) {
+        float cf[NR][4];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            // code - 128 as int8, byte-wise
+            uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(cp[r] + c)) ^ 0x80808080u;
+            cf[r][0] = static_cast<float>(static_cast<int8_t>(raw & 0xffu));
+            cf[r][1] = static_cast<float>(static_cast<int8_t>((raw >> 8) & 0xffu));
+            cf[r][2] = static_cast<float>(static_cast<int8_t>((raw >> 16) & 0xffu));
+            cf[r][3] = static_cast<float>(static_cast<int8_t>(raw >> 24));
+        }
+#pragma unroll
+        for (int qi = 0; qi < NG * 4; ++qi) {
+            float4 wv = *reinterpret_cast<const float4*>(w_s + qi * dpad + c);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                acc[r][qi] = fmaf(cf[r][0], wv.x, acc[r][qi]);
+                acc[r][qi] = fmaf(cf[r][1], wv.y, acc[r][qi]);
+                acc[r][qi] = fmaf(cf[r][2], wv.z, acc[r][qi]);
+                acc[r][qi] = fmaf(cf[r][3], wv.w, acc[r][qi]);
+            }
+        }
+    }
+}
+
+template <int QT, int NR>
+__device__ __forceinline__ void
+sq8_tile_dots_ng(int ng, const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_s,
+                 uint32_t dpad, float (&acc)[SQ8_ROWS][QT]) {
+    static_assert(QT == 16, "query-group dispatch is written for 16-query tiles");
+    switch (ng) {
+        case 1: sq8_tile_dots<QT, NR, 1>(cp, w_s, dpad, acc); break;
+        case 2: sq8_tile_dots<QT, NR, 2>(cp, w_s, dpad, acc); break;
+        case 3: sq8_tile_dots<QT, NR, 3>(cp, w_s, dpad, acc); break;
+        default: sq8_tile_dots<QT, NR, 4>(cp, w_s, dpad, acc); break;
+    }
+}
+
+template <int QT>
 __global__ void __launch_bounds__(SCAN_THREADS)
 ivf_sq8_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ uint32_t s_item[1];
+    __shared__ float s_qa[QT];
     TileSelect<QT> ts;
     float* fbuf;
     tile_carve<QT>(smem, p.cap, 0, fbuf, ts);
     ts.k = p.k;
     ts.cap = p.cap;
     const uint32_t dpad = p.dpad;
-    float* lb_s = fbuf;                 // [dpad]
-    float* df_s = fbuf + dpad;          // [dpad]
-    float* qs = fbuf + 2 * dpad;        // [QT][dpad]
-    for (uint32_t i = threadIdx.x; i < dpad; i += SCAN_THREADS) {
-        lb_s[i] = p.lower[i];
-        df_s[i] = p.diff[i];
-    }
-    const float inv255 = 1.0f / 255.0f;
+    float* w_s = fbuf;  // [QT][dpad]
 
     uint32_t list, tile;
     while (scan_next_item(p, s_item, list, tile)) {
         const uint32_t pbeg = p.pair_off[list] + tile * QT;
         const uint32_t pend = p.pair_off[list + 1];
         const int nqt = static_cast<int>(min(static_cast<uint32_t>(QT), pend - pbeg));
+        const int ng = (nqt + 3) >> 2;
         if (threadIdx.x < QT) {
             int qi = threadIdx.x;
             if (qi < nqt) {
@@ -204,90 +273,113 @@ ivf_sq8_scan_kernel(const ScanParams p) {
                 ts.qidx[qi] = q;
                 ts.slot[qi] = p.pair_slot[pbeg + qi];
                 ts.thr[qi] = p.thr_g[q];
+                s_qa[qi] = __ldg(p.qa + q);
             } else {
                 ts.qidx[qi] = 0;
                 ts.slot[qi] = 0;
                 ts.thr[qi] = 0;
+                s_qa[qi] = 0.f;
             }
             ts.cnt[qi] = 0;
         }
         __syncthreads();
-        for (uint32_t i = threadIdx.x; i < static_cast<uint32_t>(QT) * dpad; i += SCAN_THREADS) {
+        // weights of the tile's queries (rows of zeros for the unused slots of the last group)
+        for (uint32_t i = threadIdx.x * 4; i < static_cast<uint32_t>(ng) * 4 * dpad; i += SCAN_THREADS * 4) {
             uint32_t qi = i / dpad, d = i % dpad;
-            float v = 0.f;
-            if (static_cast<int>(qi) < nqt && d < p.dim) {
-                v = __ldg(p.queries + static_cast<uint64_t>(ts.qidx[qi]) * p.dim + d);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (static_cast<int>(qi) < nqt) {
+                v = __ldg(reinterpret_cast<const float4*>(p.qw + static_cast<uint64_t>(ts.qidx[qi]) * dpad + d));
             }
-            qs[i] = v;
+            *reinterpret_cast<float4*>(w_s + i) = v;
         }
         __syncthreads();
 
         const uint32_t lbeg = p.list_off[list];
         const uint32_t len = p.list_off[list + 1] - lbeg;
-        for (uint32_t r0 = 0; r0 < len; r0 += SCAN_THREADS) {
-            const uint32_t row = r0 + threadIdx.x;
-            const bool valid = row < len;
-            const uint8_t* code = p.codes + static_cast<uint64_t>(lbeg + (valid ? row : 0)) * p.code_stride;
-            float acc[QT];
+        for (uint32_t r0 = 0; r0 < len; r0 += SCAN_THREADS * SQ8_ROWS) {
+            const uint32_t left = len - r0;
+            const int nr = left >= SCAN_THREADS * SQ8_ROWS ? SQ8_ROWS
+                                                           : static_cast<int>((left + SCAN_THREADS - 1) / SCAN_THREADS);
+            const uint8_t* cp[SQ8_ROWS];
+            bool valid[SQ8_ROWS];
 #pragma unroll
-            for (int qi = 0; qi < QT; ++qi) {
-                acc[qi] = 0.f;
+            for (int r = 0; r < SQ8_ROWS; ++r) {
+                uint32_t row = r0 + r * SCAN_THREADS + threadIdx.x;
+                valid[r] = row < len;
+                cp[r] = p.codes + static_cast<uint64_t>(lbeg + (valid[r] ? row : 0)) * p.code_stride;
             }
-            for (uint32_t c = 0; c < dpad; c += 16) {
-                uint4 w = __ldg(reinterpret_cast<const uint4*>(code + c));
-                uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-                float x[16];
+            float acc[SQ8_ROWS][QT];
+            switch (nr) {
+                case 1: sq8_tile_dots_ng<QT, 1>(ng, cp, w_s, dpad, acc); break;
+                case 2: sq8_tile_dots_ng<QT, 2>(ng, cp, w_s, dpad, acc); break;
+                case 3: sq8_tile_dots_ng<QT, 3>(ng, cp, w_s, dpad, acc); break;
+                default: sq8_tile_dots_ng<QT, 4>(ng, cp, w_s, dpad, acc); break;
+            }
+            // one sub-row (at most SCAN_THREADS candidates per query) at a time, so the
+            // per-query buffers never overflow
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float4 lb4 = *reinterpret_cast<const float4*>(lb_s + c + 4 * j);
-                    float4 df4 = *reinterpret_cast<const float4*>(df_s + c + 4 * j);
-                    x[4 * j + 0] = fmaf(__fmul_rn(static_cast<float>(ww[j] & 0xffu), inv255), df4.x, lb4.x);
-                    x[4 * j + 1] = fmaf(__fmul_rn(static_cast<float>((ww[j] >> 8) & 0xffu), inv255), df4.y, lb4.y);
-                    x[4 * j + 2] = fmaf(__fmul_rn(static_cast<float>((ww[j] >> 16) & 0xffu), inv255), df4.z, lb4.z);
-                    x[4 * j + 3] = fmaf(__fmul_rn(static_cast<float>(ww[j] >> 24), inv255), df4.w, lb4.w);
-                }
+            for (int r = 0; r < SQ8_ROWS; ++r) {
+                if (r < nr) {
+                    if (valid[r]) {
+                        const uint32_t pos = lbeg + r0 + r * SCAN_THREADS + threadIdx.x;
+                        const float xb = p.coef_b * __ldg(p.code_norm + pos);
 #pragma unroll
-                for (int g = 0; g < QT; g += 4) {
-                    if (g < nqt) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                float4 qv = *reinterpret_cast<const float4*>(qs + (g + u) * dpad + c + 4 * j);
-                                if (METRIC == VB200_METRIC_L2) {
-                                    float t0 = qv.x - x[4 * j + 0];
-                                    float t1 = qv.y - x[4 * j + 1];
-                                    float t2 = qv.z - x[4 * j + 2];
-                                    float t3 = qv.w - x[4 * j + 3];
-                                    acc[g + u] = fmaf(t0, t0, acc[g + u]);
-                                    acc[g + u] = fmaf(t1, t1, acc[g + u]);
-                                    acc[g + u] = fmaf(t2, t2, acc[g + u]);
-                                    acc[g + u] = fmaf(t3, t3, acc[g + u]);
-                                } else {
-                                    acc[g + u] = fmaf(qv.x, x[4 * j + 0], acc[g + u]);
-                                    acc[g + u] = fmaf(qv.y, x[4 * j + 1], acc[g + u]);
-                                    acc[g + u] = fmaf(qv.z, x[4 * j + 2], acc[g + u]);
-                                    acc[g + u] = fmaf(qv.w, x[4 * j + 3], acc[g + u]);
-                                }
+                        for (int qi = 0; qi < QT; ++qi) {
+                            if (qi < nqt) {
+                                float dist = fmaf(p.coef_c, acc[r][qi], s_qa[qi] + xb);
+                                ts.push(qi, dist, pos);
                             }
                         }
                     }
+                    __syncthreads();
+                    ts.make_room(nqt);
+                    __syncthreads();
                 }
             }
-            if (valid) {
-#pragma unroll
-                for (int qi = 0; qi < QT; ++qi) {
-                    if (qi < nqt) {
-                        float dist = METRIC == VB200_METRIC_L2 ? acc[qi] : 1.0f - acc[qi];
-                        ts.push(qi, dist, lbeg + row);
-                    }
-                }
-            }
-            __syncthreads();
-            ts.make_room(nqt);
-            __syncthreads();
         }
         ts.finish(nqt, p.part, p.thr_g);
+    }
+}
+
+// Exact SQ8 distances of the survivors, in the reference's operation order (one thread per
+// candidate walks the dimensions upward: SQ8ComputeL2Sqr / SQ8ComputeIP with Width 1), then a
+// sort by (distance, position).  cand/out payloads are code positions.
+__global__ void __launch_bounds__(128)
+sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_t* __restrict__ codes,
+                   uint32_t code_stride, const float* __restrict__ lower, const float* __restrict__ diff,
+                   const uint64_t* __restrict__ cand, uint32_t ncand, uint32_t n2, uint32_t k, int metric,
+                   uint64_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    const float* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
+    const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
+    const float inv255 = 1.0f / 255.0f;
+    for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
+        uint64_t key = KEY_INF;
+        if (i < ncand && cq[i] != KEY_INF) {
+            uint32_t pos = static_cast<uint32_t>(cq[i]);
+            const uint8_t* c = codes + static_cast<uint64_t>(pos) * code_stride;
+            float s = 0.f;
+            for (uint32_t d = 0; d < dim; ++d) {
+                float x = fmaf(__fmul_rn(static_cast<float>(c[d]), inv255), __ldg(diff + d), __ldg(lower + d));
+                if (metric == VB200_METRIC_L2) {
+                    float t = __fsub_rn(__ldg(q + d), x);
+                    s = fmaf(t, t, s);
+                } else {
+                    s = fmaf(__ldg(q + d), x, s);
+                }
+            }
+            if (metric != VB200_METRIC_L2) {
+                s = __fsub_rn(1.0f, s);
+            }
+            key = make_key(s, pos);
+        }
+        keys[i] = key;
+    }
+    block_bitonic_sort(keys, n2);
+    uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+        dst[i] = i < n2 ? keys[i] : KEY_INF;
     }
 }
 
