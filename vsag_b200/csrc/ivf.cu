@@ -45,16 +45,17 @@ struct SearchWorkspace {
     DevBuf<uint64_t> cand;      // routing candidates
     DevBuf<int32_t> probes;     // [nq x nprobe]
     DevBuf<float> probe_dists;
-    DevBuf<uint32_t> pair_cnt;  // [nlist + 1]
-    DevBuf<uint32_t> cursor;    // [nlist]
-    DevBuf<uint32_t> pair_off;  // [nlist + 1]
-    DevBuf<uint32_t> item_off;  // [nlist + 1]
-    DevBuf<uint32_t> pair_q, pair_slot;
+    // pair grouping, one set per scan phase (nearest list first, then the rest)
+    DevBuf<uint32_t> pair_cnt[2];  // [nlist + 1]
+    DevBuf<uint32_t> cursor[2];    // [nlist]
+    DevBuf<uint32_t> pair_off[2];  // [nlist + 1]
+    DevBuf<uint32_t> item_off[2];  // [nlist + 1]
+    DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> thr;       // [nq]
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
     DevBuf<uint64_t> keys2;     // [nq x k] after rerank
-    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1] item counter (as uint32)
+    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases
     DevBuf<int64_t> out_ids;
     DevBuf<float> out_dists;
 };
@@ -310,11 +311,17 @@ probe_is_live(int32_t l, uint32_t nlist, uint32_t rank, uint32_t world, const ui
     return list_off[l + 1] > list_off[l];
 }
 
+// Probe ranks [rank_lo, rank_hi) of every query take part in the phase.
 __global__ void
-pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nlist, uint32_t rank,
-                  uint32_t world, const uint32_t* __restrict__ list_off, uint32_t* __restrict__ pair_cnt) {
+pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, uint32_t rank_lo,
+                  uint32_t rank_hi, uint32_t nlist, uint32_t rank, uint32_t world,
+                  const uint32_t* __restrict__ list_off, uint32_t* __restrict__ pair_cnt) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
+        return;
+    }
+    uint32_t pr = static_cast<uint32_t>(e % nprobe);
+    if (pr < rank_lo || pr >= rank_hi) {
         return;
     }
     int32_t l = probes[e];
@@ -328,7 +335,7 @@ pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t n
 __global__ void __launch_bounds__(1024)
 pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restrict__ list_off,
                  uint32_t nlist, uint32_t qt, uint32_t code_size, uint32_t* __restrict__ pair_off,
-                 uint32_t* __restrict__ item_off, uint64_t* __restrict__ scalars) {
+                 uint32_t* __restrict__ item_off, uint64_t* __restrict__ scalars, uint32_t queue_slot) {
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
@@ -377,19 +384,23 @@ pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restri
     if (threadIdx.x == 0) {
         pair_off[nlist] = base_pairs;
         item_off[nlist] = base_items;
-        scalars[0] = s_bytes;
-        scalars[1] = 0;  // work-queue head for the scan kernel
+        scalars[0] += s_bytes;       // logical scan volume, summed over the phases
+        scalars[queue_slot] = 0;     // work-queue head of this phase's scan kernel
     }
 }
 
 __global__ void
 pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
-                    uint32_t nlist, uint32_t rank, uint32_t world,
+                    uint32_t rank_lo, uint32_t rank_hi, uint32_t nlist, uint32_t rank, uint32_t world,
                     const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ pair_off,
                     uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_q,
                     uint32_t* __restrict__ pair_slot) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
+        return;
+    }
+    uint32_t pr = static_cast<uint32_t>(e % nprobe);
+    if (pr < rank_lo || pr >= rank_hi) {
         return;
     }
     int32_t l = probes[e];
@@ -611,36 +622,45 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                  1024 - SCAN_THREADS - (sq8 ? SQ8_SLACK : 0));
     const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : RABITQ_QT;
 
-    VB_TRY(ws.pair_cnt.reserve(nlist + 1));
-    VB_TRY(ws.cursor.reserve(nlist));
-    VB_TRY(ws.pair_off.reserve(nlist + 1));
-    VB_TRY(ws.item_off.reserve(nlist + 1));
-    VB_TRY(ws.pair_q.reserve(total));
-    VB_TRY(ws.pair_slot.reserve(total));
+    // Phase 0 scans every query's nearest list, phase 1 the other probes: after phase 0 the
+    // per-query bound is already close to final, so almost nothing enters the buffers later.
+    const uint32_t n_phases = nprobe > 1 ? 2 : 1;
+    const uint32_t rank_lo[2] = {0, 1}, rank_hi[2] = {1, nprobe};
+    for (uint32_t ph = 0; ph < n_phases; ++ph) {
+        const uint64_t cap_pairs = ph == 0 ? nq : total;
+        VB_TRY(ws.pair_cnt[ph].reserve(nlist + 1));
+        VB_TRY(ws.cursor[ph].reserve(nlist));
+        VB_TRY(ws.pair_off[ph].reserve(nlist + 1));
+        VB_TRY(ws.item_off[ph].reserve(nlist + 1));
+        VB_TRY(ws.pair_q[ph].reserve(cap_pairs));
+        VB_TRY(ws.pair_slot[ph].reserve(cap_pairs));
+    }
     VB_TRY(ws.thr.reserve(nq));
     VB_TRY(ws.part.reserve(total * kscan));
     VB_TRY(ws.keys.reserve(nq * kfinal));
-    VB_TRY(ws.scalars.reserve(2));
+    VB_TRY(ws.scalars.reserve(4));
     if (sq8) {
         VB_TRY(ws.qw.reserve(nq * ix->dpad));
         VB_TRY(ws.qa.reserve(nq));
         VB_TRY(ws.merged.reserve(nq * kscan));
     }
     cudaStream_t st = current_stream();
-    VB_CUDA(cudaMemsetAsync(ws.pair_cnt.ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
-    VB_CUDA(cudaMemsetAsync(ws.cursor.ptr, 0, nlist * sizeof(uint32_t), st));
+    VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, 4 * sizeof(uint64_t), st));
     VB_CUDA(cudaMemsetAsync(ws.thr.ptr, 0xFF, nq * sizeof(uint32_t), st));
     VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
-
     const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
-    VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nlist, ix->shard_rank,
-              ix->shard_world, ix->list_off.ptr, ws.pair_cnt.ptr);
-    VB_LAUNCH(pair_scan_kernel, 1, 1024, 0, ws.pair_cnt.ptr, ix->list_off.ptr, nlist,
-              static_cast<uint32_t>(qt), ix->code_size, ws.pair_off.ptr, ws.item_off.ptr,
-              ws.scalars.ptr);
-    VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, nlist, ix->shard_rank,
-              ix->shard_world, ix->list_off.ptr, ws.pair_off.ptr, ws.cursor.ptr, ws.pair_q.ptr,
-              ws.pair_slot.ptr);
+    for (uint32_t ph = 0; ph < n_phases; ++ph) {
+        VB_CUDA(cudaMemsetAsync(ws.pair_cnt[ph].ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
+        VB_CUDA(cudaMemsetAsync(ws.cursor[ph].ptr, 0, nlist * sizeof(uint32_t), st));
+        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, rank_lo[ph], rank_hi[ph],
+                  nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.pair_cnt[ph].ptr);
+        VB_LAUNCH(pair_scan_kernel, 1, 1024, 0, ws.pair_cnt[ph].ptr, ix->list_off.ptr, nlist,
+                  static_cast<uint32_t>(qt), ix->code_size, ws.pair_off[ph].ptr, ws.item_off[ph].ptr,
+                  ws.scalars.ptr, 1 + ph);
+        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, rank_lo[ph], rank_hi[ph],
+                  nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.pair_off[ph].ptr,
+                  ws.cursor[ph].ptr, ws.pair_q[ph].ptr, ws.pair_slot[ph].ptr);
+    }
 
     ScanParams p{};
     p.codes = ix->codes.ptr;
@@ -648,12 +668,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.dim = ix->dim;
     p.dpad = ix->dpad;
     p.list_off = ix->list_off.ptr;
-    p.pair_off = ws.pair_off.ptr;
-    p.pair_q = ws.pair_q.ptr;
-    p.pair_slot = ws.pair_slot.ptr;
-    p.item_off = ws.item_off.ptr;
     p.nlist = nlist;
-    p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 1);
     p.k = kscan;
     p.cap = next_pow2(kscan + SCAN_THREADS);
     p.thr_g = ws.thr.ptr;
@@ -671,12 +686,19 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                   ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
-    if (sq8) {
-        size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
-        VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem));
-    } else {
-        size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
-        VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
+    for (uint32_t ph = 0; ph < n_phases; ++ph) {
+        p.pair_off = ws.pair_off[ph].ptr;
+        p.pair_q = ws.pair_q[ph].ptr;
+        p.pair_slot = ws.pair_slot[ph].ptr;
+        p.item_off = ws.item_off[ph].ptr;
+        p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 1 + ph);
+        if (sq8) {
+            size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
+            VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem));
+        } else {
+            size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
+            VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
+        }
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
     ix->scan_timed = true;

@@ -51,6 +51,10 @@ struct ScanParams {
 };
 
 // Per-tile selection state in shared memory.
+//
+// A candidate's distance is offered as `partial + qa[qi]`: the scan kernels test
+// partial <= bound - qa (one shared load, one compare) and only build the sortable key for the
+// few candidates that pass.
 template <int QT>
 struct TileSelect {
     uint64_t* keys;   // [QT][cap]
@@ -58,14 +62,24 @@ struct TileSelect {
     uint32_t* thr;    // [QT] ordered distance bound
     uint32_t* slot;   // [QT]
     uint32_t* qidx;   // [QT]
+    float* thrq;      // [QT] bound as a float, minus qa
+    float* qa;        // [QT] per-query additive constant
     uint32_t k, cap;
 
     __device__ __forceinline__ void
-    push(int qi, float dist, uint32_t pos) {
-        uint32_t u = float_to_ordered(dist);
-        if (u <= thr[qi] && dist == dist) {
+    set_bound(int qi, uint32_t u) {
+        thr[qi] = u;
+        // ordered values above +inf are NaN patterns: "no bound yet"
+        float f = u >= 0xFF800000u ? INFINITY : ordered_to_float(u);
+        thrq[qi] = f - qa[qi];
+    }
+
+    __device__ __forceinline__ void
+    push(int qi, float partial, uint32_t pos) {
+        if (partial <= thrq[qi]) {
+            float dist = partial + qa[qi];
             uint32_t s = atomicAdd(&cnt[qi], 1u);
-            keys[static_cast<uint32_t>(qi) * cap + s] = (static_cast<uint64_t>(u) << 32) | pos;
+            keys[static_cast<uint32_t>(qi) * cap + s] = make_key(dist, pos);
         }
     }
 
@@ -86,7 +100,7 @@ struct TileSelect {
             if (c >= k) {
                 uint32_t t = static_cast<uint32_t>(kq[k - 1] >> 32);
                 if (t < thr[qi]) {
-                    thr[qi] = t;
+                    set_bound(qi, t);
                 }
             }
         }
@@ -105,12 +119,15 @@ struct TileSelect {
         }
     }
 
-    // End of the item: write each query's k best to its slot and publish the bound.
+    // End of the item: write each query's (at most k) best to its slot and publish the bound.
+    // Fewer than k survivors are written unsorted: the merge does not need order.
     __device__ __forceinline__ void
     finish(int nqt, uint64_t* part, uint32_t* thr_g) {
         const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int qi = warp; qi < nqt; qi += SCAN_WARPS) {
-            compact(qi, lane);
+            if (cnt[qi] >= k) {
+                compact(qi, lane);
+            }
             uint32_t c = cnt[qi];
             const uint64_t* kq = keys + static_cast<uint32_t>(qi) * cap;
             uint64_t* dst = part + static_cast<uint64_t>(slot[qi]) * k;
@@ -161,14 +178,16 @@ tile_carve(unsigned char* smem, uint32_t cap, uint32_t float_count, float*& fbuf
     ts.thr = w + QT;
     ts.slot = w + 2 * QT;
     ts.qidx = w + 3 * QT;
-    fbuf = reinterpret_cast<float*>(w + 4 * QT);
+    ts.thrq = reinterpret_cast<float*>(w + 4 * QT);
+    ts.qa = reinterpret_cast<float*>(w + 5 * QT);
+    fbuf = reinterpret_cast<float*>(w + 6 * QT);
     (void)float_count;
 }
 
 template <int QT>
 __host__ __device__ inline size_t
 tile_smem_bytes(uint32_t cap, uint32_t float_count) {
-    return static_cast<size_t>(QT) * cap * 8 + 4 * QT * 4 + static_cast<size_t>(float_count) * 4;
+    return static_cast<size_t>(QT) * cap * 8 + 6 * QT * 4 + static_cast<size_t>(float_count) * 4;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -179,7 +198,7 @@ tile_smem_bytes(uint32_t cap, uint32_t float_count) {
 //
 // The scan ranks candidates with an algebraically equal form that costs one FMA per
 // (query, code, dimension) instead of a subtract and an FMA:
-//   with c'_d = code_d - 128 (an int8), s_d = diff_d / 255, mid_d = lower_d + 128 s_d:
+//   with c'_d = code_d - 128, s_d = diff_d / 255, mid_d = lower_d + 128 s_d:
 //     x_d = c'_d s_d + mid_d,   sum q_d x_d = sum (q_d s_d) c'_d + sum q_d mid_d
 //   L2: |q|^2 - 2 sum q_d mid_d  +  |x|^2  - 2 sum w_d c'_d,     w_d = q_d s_d
 //   IP: 1 - sum q_d mid_d                  -   sum w_d c'_d
@@ -206,18 +225,30 @@ sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_
         }
     }
     // Four dimensions per trip, not unrolled: the fully unrolled body (4*NR*NG*4 FMAs) is what has to
-    // stay resident in the instruction cache.
+    // stay resident in the instruction cache.  The code words of the next trip are fetched before
+    // the FMAs of this one.
+    uint32_t nxt[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        nxt[r] = __ldg(reinterpret_cast<const uint32_t*>(cp[r]));
+    }
 #pragma unroll 1
     for (uint32_t c = 0; c < dpad; c += 4) {
         float cf[NR][4];
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-            // code - 128 as int8, byte-wise
-            uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(cp[r] + c)) ^ 0x80808080u;
-            cf[r][0] = static_cast<float>(static_cast<int8_t>(raw & 0xffu));
-            cf[r][1] = static_cast<float>(static_cast<int8_t>((raw >> 8) & 0xffu));
-            cf[r][2] = static_cast<float>(static_cast<int8_t>((raw >> 16) & 0xffu));
-            cf[r][3] = static_cast<float>(static_cast<int8_t>(raw >> 24));
+            // byte b -> float(b) - 128 exactly: 0x4B0000bb is the float 2^23 + b
+            const uint32_t raw = nxt[r];
+            cf[r][0] = __uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7540)) - 8388736.0f;
+            cf[r][1] = __uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7541)) - 8388736.0f;
+            cf[r][2] = __uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7542)) - 8388736.0f;
+            cf[r][3] = __uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7543)) - 8388736.0f;
+        }
+        if (c + 4 < dpad) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                nxt[r] = __ldg(reinterpret_cast<const uint32_t*>(cp[r] + c + 4));
+            }
         }
 #pragma unroll
         for (int qi = 0; qi < NG * 4; ++qi) {
@@ -251,7 +282,6 @@ __global__ void __launch_bounds__(SCAN_THREADS)
 ivf_sq8_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ uint32_t s_item[1];
-    __shared__ float s_qa[QT];
     TileSelect<QT> ts;
     float* fbuf;
     tile_carve<QT>(smem, p.cap, 0, fbuf, ts);
@@ -272,13 +302,13 @@ ivf_sq8_scan_kernel(const ScanParams p) {
                 uint32_t q = p.pair_q[pbeg + qi];
                 ts.qidx[qi] = q;
                 ts.slot[qi] = p.pair_slot[pbeg + qi];
-                ts.thr[qi] = p.thr_g[q];
-                s_qa[qi] = __ldg(p.qa + q);
+                ts.qa[qi] = __ldg(p.qa + q);
+                ts.set_bound(qi, p.thr_g[q]);
             } else {
                 ts.qidx[qi] = 0;
                 ts.slot[qi] = 0;
-                ts.thr[qi] = 0;
-                s_qa[qi] = 0.f;
+                ts.qa[qi] = 0.f;
+                ts.set_bound(qi, 0u);
             }
             ts.cnt[qi] = 0;
         }
@@ -326,8 +356,7 @@ ivf_sq8_scan_kernel(const ScanParams p) {
 #pragma unroll
                         for (int qi = 0; qi < QT; ++qi) {
                             if (qi < nqt) {
-                                float dist = fmaf(p.coef_c, acc[r][qi], s_qa[qi] + xb);
-                                ts.push(qi, dist, pos);
+                                ts.push(qi, fmaf(p.coef_c, acc[r][qi], xb), pos);
                             }
                         }
                     }
@@ -417,12 +446,14 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
                 uint32_t q = p.pair_q[pbeg + qi];
                 ts.qidx[qi] = q;
                 ts.slot[qi] = p.pair_slot[pbeg + qi];
-                ts.thr[qi] = p.thr_g[q];
+                ts.qa[qi] = 0.f;
+                ts.set_bound(qi, p.thr_g[q]);
                 s_qnorm[qi] = __ldg(p.queries + static_cast<uint64_t>(q) * (p.dim + 1) + p.dim);
             } else {
                 ts.qidx[qi] = 0;
                 ts.slot[qi] = 0;
-                ts.thr[qi] = 0;
+                ts.qa[qi] = 0.f;
+                ts.set_bound(qi, 0u);
                 s_qnorm[qi] = 0.f;
             }
             ts.cnt[qi] = 0;
