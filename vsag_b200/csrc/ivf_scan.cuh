@@ -225,15 +225,17 @@ sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_
         }
     }
     // Four dimensions per trip, not unrolled: the fully unrolled body (4*NR*NG*4 FMAs) is what has to
-    // stay resident in the instruction cache.  The code words of the next trip are fetched before
-    // the FMAs of this one.
+    // stay resident in the instruction cache (longer bodies measured slower).  The code bytes of
+    // the next trip are fetched before the FMAs of this one.  w_s holds the weights as
+    // [dpad/4][QT] float4, so every shared load of a trip is the trip's base plus a constant.
     uint32_t nxt[NR];
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
         nxt[r] = __ldg(reinterpret_cast<const uint32_t*>(cp[r]));
     }
+    const float4* wrow = reinterpret_cast<const float4*>(w_s);
 #pragma unroll 1
-    for (uint32_t c = 0; c < dpad; c += 4) {
+    for (uint32_t c = 0; c < dpad; c += 4, wrow += QT) {
         float cf[NR][4];
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
@@ -252,7 +254,7 @@ sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_
         }
 #pragma unroll
         for (int qi = 0; qi < NG * 4; ++qi) {
-            float4 wv = *reinterpret_cast<const float4*>(w_s + qi * dpad + c);
+            float4 wv = wrow[qi];
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 acc[r][qi] = fmaf(cf[r][0], wv.x, acc[r][qi]);
@@ -313,14 +315,19 @@ ivf_sq8_scan_kernel(const ScanParams p) {
             ts.cnt[qi] = 0;
         }
         __syncthreads();
-        // weights of the tile's queries (rows of zeros for the unused slots of the last group)
-        for (uint32_t i = threadIdx.x * 4; i < static_cast<uint32_t>(ng) * 4 * dpad; i += SCAN_THREADS * 4) {
-            uint32_t qi = i / dpad, d = i % dpad;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (static_cast<int>(qi) < nqt) {
-                v = __ldg(reinterpret_cast<const float4*>(p.qw + static_cast<uint64_t>(ts.qidx[qi]) * dpad + d));
+        // weights of the tile's queries as [dpad/4][QT] float4 (zeros for the unused slots of the
+        // last group of four)
+        {
+            const uint32_t d4n = dpad >> 2;
+            float4* w4s = reinterpret_cast<float4*>(w_s);
+            for (uint32_t i = threadIdx.x; i < static_cast<uint32_t>(ng) * 4 * d4n; i += SCAN_THREADS) {
+                uint32_t qi = i / d4n, d4 = i % d4n;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (static_cast<int>(qi) < nqt) {
+                    v = __ldg(reinterpret_cast<const float4*>(p.qw + static_cast<uint64_t>(ts.qidx[qi]) * dpad) + d4);
+                }
+                w4s[d4 * QT + qi] = v;
             }
-            *reinterpret_cast<float4*>(w_s + i) = v;
         }
         __syncthreads();
 
