@@ -123,6 +123,20 @@ VB200_API int vb200_kmeans_update(const float* data, uint64_t count, uint32_t di
 VB200_API int vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, int iters,
                        float* centroids, int32_t* labels, double* mean_err);
 
+/* Same labels as vb200_kmeans_assign, for callers that must not allocate.  No counterpart in the
+ * reference: it exists for hosts where reaching the CUDA allocator is not an option (a serving
+ * thread with a fixed device-memory budget, or one that cannot take the device-wide
+ * synchronisation an allocation or free implies).  It calls no cudaMalloc/cudaFree and no
+ * allocating library routine; the one piece of scratch it needs, the centroid norms, sits in a
+ * fixed 256 KiB array inside the library, so k is limited to 65536 (larger k fails with
+ * VB200_INVALID_ARGUMENT).  data, centroids and labels must be device pointers.
+ * The first call on each device looks up the array's device address; make that first call before
+ * any stream capture.  All calls share the array (it keeps the previous call's contents, which the
+ * next call overwrites before use), so two calls that overlap on the same GPU race: serialise
+ * them. */
+VB200_API int vb200_kmeans_assign_noalloc(const float* data_dev, uint64_t count, uint32_t dim,
+                                const float* centroids_dev, uint32_t k, int32_t* labels_dev);
+
 /* ---------------------------------------------------------------------------------------------
  * RaBitQ, 1 bit per dimension, fp32 query ("standard" layout)
  * ------------------------------------------------------------------------------------------- */

@@ -203,3 +203,51 @@ vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, 
     }
     return sync_stream();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Assignment without any allocation
+// ---------------------------------------------------------------------------------------------
+// Some callers must not reach the CUDA allocator at all: a serving thread that holds a fixed
+// memory budget and cannot tolerate the device-wide synchronisation cudaMalloc/cudaFree imply, or
+// a host that has handed all remaining device memory to another pool.  For them the centroid
+// norms -- the only scratch the assignment needs -- live in this fixed array, which every GPU that
+// loads the library holds (256 KiB) until the process exits.
+constexpr uint32_t NOALLOC_MAX_K = 65536;
+static __device__ __align__(256) float g_noalloc_centroid_sq[NOALLOC_MAX_K];
+
+// Device address of the array above, looked up once per device with that device current.  In host
+// code the symbol itself is only a stand-in; kernels must be given the address this returns.
+static int
+noalloc_scratch(float** out) {
+    static std::mutex mu;
+    static float* cached[64] = {nullptr};
+    int dev = 0;
+    VB_CUDA(cudaGetDevice(&dev));
+    VB_CHECK_ARG(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        VB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_centroid_sq));
+        cached[dev] = static_cast<float*>(p);
+    }
+    *out = cached[dev];
+    return 0;
+}
+
+extern "C" int
+vb200_kmeans_assign_noalloc(const float* data_dev, uint64_t count, uint32_t dim,
+                            const float* centroids_dev, uint32_t k, int32_t* labels_dev) {
+    VB_TRY(check_kmeans_args(data_dev, count, dim, centroids_dev, k));
+    VB_CHECK_ARG(labels_dev != nullptr, "labels cannot be null");
+    VB_CHECK_ARG(k <= NOALLOC_MAX_K, "k = %u exceeds the %u centroids the fixed scratch array holds", k,
+                 NOALLOC_MAX_K);
+    VB_CHECK_ARG(is_device_pointer(data_dev) && is_device_pointer(centroids_dev) &&
+                     is_device_pointer(labels_dev),
+                 "this entry point stages nothing: data, centroids and labels must be device pointers");
+    float* c_sq = nullptr;
+    VB_TRY(noalloc_scratch(&c_sq));
+    // Every call rewrites entries [0, k) before reading them, so nothing has to be cleared.
+    VB_TRY(row_sqnorm_f32(centroids_dev, k, dim, c_sq));
+    VB_TRY(dense_argmin_f32(data_dev, count, centroids_dev, k, dim, -2.0f, c_sq, labels_dev, nullptr));
+    return sync_stream();
+}
