@@ -41,9 +41,11 @@ SIGMA = 0.15
 TRAIN_ROWS = 64 * NLIST          # the reference's default train_sample_count: max(65536, 64 * nlist)
 KMEANS_ITERS = 25                # hard-coded in IVFNearestPartition::Train
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scan kernel, from the ncu
-# capture summarised under profiles/; None until a capture of this kernel has been taken.
-SCAN_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel's two launches per step, from the
+# ncu capture of the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 126.9 MB +
+# 203.5 MB), scaled by 5 to the 10,000,000-row workload: the traffic is one pass over the probed
+# codes plus the partial-result slots, both proportional to the row count.
+SCAN_TRAFFIC_BYTES = 5 * (126.9e6 + 203.5e6)
 
 
 def env_int(name: str, default: int) -> int:
@@ -312,11 +314,11 @@ def main() -> None:
 
     out_ids = torch.empty((n_query, K), dtype=torch.int64, device=device)
     out_d = torch.empty((n_query, K), dtype=torch.float32, device=device)
+    sharded = None
     if world > 1:
-        keys_local = torch.empty((n_query, K), dtype=torch.int64, device=device)
-        labels_local = torch.empty((n_query, K), dtype=torch.int64, device=device)
-        keys_all = torch.empty((world, n_query, K), dtype=torch.int64, device=device)
-        labels_all = torch.empty((world, n_query, K), dtype=torch.int64, device=device)
+        from vsag_b200 import parallel
+
+        sharded = parallel.ShardedIvfSearch(ix, n_query, K, world, device, dist)
 
     def step_device():
         if world == 1:
@@ -324,12 +326,7 @@ def main() -> None:
         else:
             # every rank scans the probed lists it owns; the per-shard top-k are exchanged with
             # one all-gather over NVLink and merged locally on every rank
-            ix.search_partial(queries, K, nprobe, 2.0, keys_local, labels_local)
-            dist.all_gather_into_tensor(keys_all, keys_local)
-            dist.all_gather_into_tensor(labels_all, labels_local)
-            engine._capi.check(engine._capi.load().vb200_merge_partials(
-                engine.ptr(keys_all), engine.ptr(labels_all), world, n_query, K, engine.ptr(out_ids),
-                engine.ptr(out_d)))
+            sharded.search(queries, nprobe, 2.0, out_ids, out_d)
 
     def timed(fn, steps: int):
         """K steps between a barrier + synchronize on both sides; device time from CUDA events on
