@@ -32,12 +32,16 @@ def _nvcc() -> str:
     return nvcc
 
 
+HOST = PKG_DIR / "host"
+
+
 def _sources() -> list[Path]:
-    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")))
+    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")) + list(HOST.glob("*.cpp")))
 
 
 def _headers_mtime() -> float:
-    hdrs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((PKG_DIR.parent / "include").glob("*.h"))
+    hdrs = (list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(HOST.glob("*.h"))
+            + list((PKG_DIR.parent / "include").glob("*.h")))
     return max((h.stat().st_mtime for h in hdrs), default=0.0)
 
 

@@ -1,0 +1,185 @@
+// C functions with the names and signatures of the reference's C API for this path
+// (include/vsag/vsag_c_api.h:36-160, src/vsag_c_api.cpp): factory, destroy, build, add, train,
+// knn_search.  They sit on the vsag::Factory / Index mirror, so a program written against the
+// reference's C API links against libvsag_b200.so unchanged for "ivf" and "brute_force".
+// vsag_index_knn_search_batch is an addition: the reference's C API takes one query per call.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+#include "vsag_host.h"
+
+#define VSAG_C_EXPORT extern "C" __attribute__((visibility("default")))
+
+extern "C" {
+typedef struct Error {
+    int code;
+    char message[1024];
+} Error_t;
+
+typedef void* vsag_index_t;
+
+typedef struct SearchResult {
+    float* dists;
+    int64_t* ids;
+    int64_t count;
+    void* other_result;
+} SearchResult_t;
+}
+
+namespace {
+
+struct IndexBox {
+    std::shared_ptr<vsag::Index> index;
+};
+
+Error_t
+success() {
+    Error_t e;
+    e.code = 0;
+    snprintf(e.message, sizeof(e.message), "%s", "success");
+    return e;
+}
+
+Error_t
+make_error(int code, const std::string& message) {
+    Error_t e;
+    e.code = code;
+    snprintf(e.message, sizeof(e.message), "%s", message.c_str());
+    return e;
+}
+
+Error_t
+make_error(const vsag::Error& err) {
+    return make_error(-static_cast<int>(err.type), err.message);  // VSAG_* codes are the negated enum
+}
+
+thread_local std::string tl_factory_error;
+
+vsag::DatasetPtr
+borrow(const float* data, const int64_t* ids, uint64_t dim, uint64_t count) {
+    return vsag::Dataset::Make()
+        ->Owner(false)
+        ->Dim(static_cast<int64_t>(dim))
+        ->NumElements(static_cast<int64_t>(count))
+        ->Ids(ids)
+        ->Float32Vectors(data);
+}
+
+}  // namespace
+
+VSAG_C_EXPORT vsag_index_t
+vsag_index_factory(const char* index_name, const char* index_param) {
+    if (index_name == nullptr || index_param == nullptr) {
+        tl_factory_error = "index name or parameter is NULL";
+        return nullptr;
+    }
+    auto created = vsag::Factory::CreateIndex(index_name, index_param);
+    if (!created.has_value()) {
+        tl_factory_error = created.error().message;
+        return nullptr;
+    }
+    return new IndexBox{created.value()};
+}
+
+// Text of the last vsag_index_factory failure on this thread (the reference logs it instead).
+VSAG_C_EXPORT const char*
+vsag_index_factory_error(void) {
+    return tl_factory_error.c_str();
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_destroy(vsag_index_t index) {
+    delete static_cast<IndexBox*>(index);
+    return success();
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_build(vsag_index_t index, const float* data, const int64_t* ids, uint64_t dim, uint64_t count) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    auto r = box->index->Build(borrow(data, ids, dim, count));
+    return r.has_value() ? success() : make_error(r.error());
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_add(vsag_index_t index, const float* data, const int64_t* ids, const uint64_t dim,
+               const uint64_t count) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    auto r = box->index->Add(borrow(data, ids, dim, count));
+    return r.has_value() ? success() : make_error(r.error());
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_train(vsag_index_t index, const float* data, const int64_t* ids, const uint64_t dim,
+                 const uint64_t count) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    auto r = box->index->Train(borrow(data, ids, dim, count));
+    return r.has_value() ? success() : make_error(r.error());
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_knn_search(vsag_index_t index, const float* query, uint64_t dim, int64_t k, const char* parameters,
+                      SearchResult_t* search_result) {
+    if (search_result == nullptr) {
+        return make_error(-1, "search result is NULL");
+    }
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (k <= 0) {
+        return make_error(-3, "knn_search requires k >= 1");
+    }
+    auto r = box->index->KnnSearch(borrow(query, nullptr, dim, 1), k, parameters == nullptr ? "{}" : parameters);
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    int64_t to_write = std::min<int64_t>(r.value()->GetDim(), k);
+    for (int64_t i = 0; i < to_write; ++i) {
+        search_result->ids[i] = r.value()->GetIds()[i];
+        search_result->dists[i] = r.value()->GetDistances()[i];
+    }
+    search_result->count = to_write;
+    return success();
+}
+
+// nq queries in one call: ids[nq x k], dists[nq x k], padded with -1 / +inf.
+VSAG_C_EXPORT Error_t
+vsag_index_knn_search_batch(vsag_index_t index, const float* queries, uint64_t dim, uint64_t nq, int64_t k,
+                            const char* parameters, int64_t* ids, float* dists) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (ids == nullptr || dists == nullptr) {
+        return make_error(-3, "output buffers are NULL");
+    }
+    auto r = box->index->KnnSearch(borrow(queries, nullptr, dim, nq), k, parameters == nullptr ? "{}" : parameters);
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    const auto& res = r.value();
+    for (uint64_t q = 0; q < nq; ++q) {
+        for (int64_t i = 0; i < k; ++i) {
+            bool have = static_cast<int64_t>(q) < res->GetNumElements() && i < res->GetDim() && res->GetIds() != nullptr;
+            ids[q * k + i] = have ? res->GetIds()[q * res->GetDim() + i] : -1;
+            dists[q * k + i] = have ? res->GetDistances()[q * res->GetDim() + i] : __builtin_inff();
+        }
+    }
+    return success();
+}
+
+VSAG_C_EXPORT int64_t
+vsag_index_get_num_elements(vsag_index_t index) {
+    auto* box = static_cast<IndexBox*>(index);
+    return box == nullptr ? 0 : box->index->GetNumElements();
+}

@@ -1,0 +1,637 @@
+// Implementation of the vsag::Factory / Index / Dataset mirror over the C ABI (include/vsag_b200.h).
+#include "vsag_host.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <mutex>
+#include <random>
+#include <set>
+
+#include "../../include/vsag_b200.h"
+#include "json_lite.h"
+
+namespace vsag {
+
+using vsag_b200_host::Json;
+
+namespace {
+
+struct HostException {
+    ErrorType type;
+    std::string message;
+};
+
+[[noreturn]] void
+fail(ErrorType type, const std::string& message) {
+    throw HostException{type, message};
+}
+
+void
+check_argument(bool cond, const std::string& message) {
+    if (!cond) {
+        fail(ErrorType::INVALID_ARGUMENT, message);
+    }
+}
+
+// Status of a C-ABI call -> the ErrorType with the same number (codes are the negated enum values,
+// as in include/vsag/vsag_c_api.h:20-34).
+void
+check_status(int status) {
+    if (status == 0) {
+        return;
+    }
+    char msg[1024];
+    vb200_last_error(msg, sizeof(msg));
+    int code = -status;
+    if (code < 1 || code > static_cast<int>(ErrorType::INVALID_BINARY)) {
+        code = static_cast<int>(ErrorType::UNKNOWN_ERROR);
+    }
+    fail(static_cast<ErrorType>(code), msg);
+}
+
+// Runs `fn`, mapping every failure to an Error the way SAFE_CALL does (src/common.h:23-35).
+template <typename T, typename Fn>
+Expected<T>
+safe_call(Fn&& fn) {
+    try {
+        return Expected<T>(fn());
+    } catch (const HostException& e) {
+        return Expected<T>(Error{e.type, e.message});
+    } catch (const std::bad_alloc&) {
+        return Expected<T>(Error{ErrorType::NO_ENOUGH_MEMORY, "bad alloc"});
+    } catch (const std::invalid_argument& e) {
+        return Expected<T>(Error{ErrorType::INVALID_ARGUMENT, e.what()});
+    } catch (const std::exception& e) {
+        return Expected<T>(Error{ErrorType::UNKNOWN_ERROR, e.what()});
+    }
+}
+
+std::string
+lower(std::string s) {
+    std::transform(s.begin(), s.end(), s.begin(), [](unsigned char c) { return std::tolower(c); });
+    return s;
+}
+
+// Keys of `obj` must all be in `allowed` (the reference rejects unknown index_param keys,
+// tests/test_ivf.cpp:1148-1165).
+void
+check_known_keys(const Json& obj, const std::set<std::string>& allowed, const std::string& where) {
+    for (const auto& m : obj.members) {
+        check_argument(allowed.count(m.first) != 0, "unknown parameter \"" + m.first + "\" in " + where);
+    }
+}
+
+int64_t
+get_int(const Json& obj, const std::string& key, int64_t fallback) {
+    const Json* v = obj.Find(key);
+    if (v == nullptr) {
+        return fallback;
+    }
+    check_argument(v->IsInteger(), "parameter \"" + key + "\" must be an integer");
+    return static_cast<int64_t>(v->number);
+}
+
+bool
+get_bool(const Json& obj, const std::string& key, bool fallback) {
+    const Json* v = obj.Find(key);
+    if (v == nullptr) {
+        return fallback;
+    }
+    check_argument(v->IsBool(), "parameter \"" + key + "\" must be a boolean");
+    return v->boolean;
+}
+
+std::string
+get_string(const Json& obj, const std::string& key, const std::string& fallback) {
+    const Json* v = obj.Find(key);
+    if (v == nullptr) {
+        return fallback;
+    }
+    check_argument(v->IsString(), "parameter \"" + key + "\" must be a string");
+    return v->text;
+}
+
+double
+get_number(const Json& obj, const std::string& key, double fallback) {
+    const Json* v = obj.Find(key);
+    if (v == nullptr) {
+        return fallback;
+    }
+    check_argument(v->IsNumber(), "parameter \"" + key + "\" must be a number");
+    return v->number;
+}
+
+struct CommonParam {
+    uint32_t dim = 0;
+    int metric = VB200_METRIC_L2;
+    Json index_param;
+};
+
+// IndexCommonParam::CheckAndCreate (src/index_common_param.cpp:117-174): dtype, metric_type and dim
+// are required.
+CommonParam
+parse_common(const std::string& parameters) {
+    Json root = Json::Parse(parameters);
+    check_argument(root.IsObject(), "parameters must be a JSON object");
+    CommonParam out;
+    check_argument(root.Contains("dtype"), "parameters must contains dtype");
+    std::string dtype = get_string(root, "dtype", "");
+    check_argument(dtype == "float32",
+                   "parameters[dtype] must be float32 for the ivf / brute_force GPU engine, got " + dtype);
+    check_argument(root.Contains("metric_type"), "parameters must contains metric_type");
+    std::string metric = get_string(root, "metric_type", "");
+    if (metric == "l2") {
+        out.metric = VB200_METRIC_L2;
+    } else if (metric == "ip") {
+        out.metric = VB200_METRIC_IP;
+    } else if (metric == "cosine") {
+        fail(ErrorType::INVALID_ARGUMENT, "parameters[metric_type]=cosine is not served by the GPU engine yet");
+    } else {
+        fail(ErrorType::INVALID_ARGUMENT, "parameters[metric_type] must in [l2, ip, cosine], now is " + metric);
+    }
+    check_argument(root.Contains("dim"), "parameters must contain dim");
+    const Json& dim = root.At("dim");
+    check_argument(dim.IsInteger(), "parameters[dim] must be integer type");
+    check_argument(dim.number > 0, "parameters[dim] must be greater than 0");
+    out.dim = static_cast<uint32_t>(dim.number);
+    if (root.Contains("index_param")) {
+        out.index_param = root.At("index_param");
+        check_argument(out.index_param.IsObject(), "parameters[index_param] must be an object");
+    } else {
+        out.index_param.kind = Json::Kind::Object;
+    }
+    return out;
+}
+
+DatasetPtr
+make_empty_result() {
+    // Empty index / empty query: a Dim = 0 dataset (src/index/index_impl.h:60-63, :317-320).
+    return Dataset::Make()->NumElements(1)->Dim(0);
+}
+
+// Packs nq x k padded rows into a result dataset; a single query is trimmed to the entries found
+// (src/utils/util_functions.cpp:68-80), a batch keeps the padding (src/algorithm/ivf/ivf.cpp:2202-2209).
+DatasetPtr
+pack_result(int64_t* ids, float* dists, int64_t nq, int64_t k, const std::string& stats) {
+    int64_t dim = k;
+    if (nq == 1) {
+        dim = 0;
+        while (dim < k && ids[dim] >= 0) {
+            ++dim;
+        }
+    }
+    auto result = Dataset::Make()->NumElements(nq)->Dim(dim)->Ids(ids)->Distances(dists)->Owner(true);
+    result->Statistics(stats);
+    return result;
+}
+
+// A random orthogonal matrix with determinant +1, standing in for
+// RandomOrthogonalMatrix::GenerateRandomOrthogonalMatrix (src/impl/transform/
+// random_orthogonal_transformer.cpp:98-149): Gaussian entries from a seeded mt19937, then
+// Gram-Schmidt (twice, in double) instead of LAPACK QR.
+std::vector<float>
+random_rotation(uint32_t dim, uint32_t seed) {
+    std::mt19937 gen(seed);
+    std::normal_distribution<float> dist(0.0f, 1.0f);
+    std::vector<double> m(static_cast<size_t>(dim) * dim);
+    for (auto& v : m) {
+        v = dist(gen);
+    }
+    for (uint32_t i = 0; i < dim; ++i) {
+        double* row = m.data() + static_cast<size_t>(i) * dim;
+        for (int pass = 0; pass < 2; ++pass) {
+            for (uint32_t j = 0; j < i; ++j) {
+                const double* prev = m.data() + static_cast<size_t>(j) * dim;
+                double dot = 0.0;
+                for (uint32_t d = 0; d < dim; ++d) {
+                    dot += row[d] * prev[d];
+                }
+                for (uint32_t d = 0; d < dim; ++d) {
+                    row[d] -= dot * prev[d];
+                }
+            }
+        }
+        double norm = 0.0;
+        for (uint32_t d = 0; d < dim; ++d) {
+            norm += row[d] * row[d];
+        }
+        norm = std::sqrt(norm);
+        if (norm < 1e-12) {
+            fail(ErrorType::INTERNAL_ERROR, "degenerate random matrix");
+        }
+        for (uint32_t d = 0; d < dim; ++d) {
+            row[d] /= norm;
+        }
+    }
+    std::vector<float> out(m.size());
+    for (size_t i = 0; i < m.size(); ++i) {
+        out[i] = static_cast<float>(m[i]);
+    }
+    return out;
+}
+
+}  // namespace
+
+// -------------------------------------------------------------------------------------------------
+// Dataset
+// -------------------------------------------------------------------------------------------------
+DatasetPtr
+Dataset::Make() {
+    return DatasetPtr(new Dataset());
+}
+
+Dataset::~Dataset() {
+    if (owner_) {
+        delete[] ids_;
+        delete[] distances_;
+        delete[] vectors_;
+        delete[] half_vectors_;
+    }
+}
+
+DatasetPtr Dataset::Owner(bool is_owner) { owner_ = is_owner; return shared_from_this(); }
+DatasetPtr Dataset::NumElements(int64_t n) { num_elements_ = n; return shared_from_this(); }
+DatasetPtr Dataset::Dim(int64_t dim) { dim_ = dim; return shared_from_this(); }
+DatasetPtr Dataset::Ids(const int64_t* ids) { ids_ = ids; return shared_from_this(); }
+DatasetPtr Dataset::Distances(const float* dists) { distances_ = dists; return shared_from_this(); }
+DatasetPtr Dataset::Float32Vectors(const float* v) { vectors_ = v; return shared_from_this(); }
+DatasetPtr Dataset::Float16Vectors(const uint16_t* v) { half_vectors_ = v; return shared_from_this(); }
+DatasetPtr Dataset::Statistics(const std::string& s) { statistics_ = s; return shared_from_this(); }
+
+// -------------------------------------------------------------------------------------------------
+// IVF
+// -------------------------------------------------------------------------------------------------
+namespace {
+
+void
+check_base(const DatasetPtr& base, uint32_t dim, bool need_ids) {
+    check_argument(base != nullptr, "dataset is null");
+    check_argument(base->GetNumElements() >= 0, "dataset has a negative element count");
+    if (base->GetNumElements() == 0) {
+        return;
+    }
+    if (base->GetDim() != static_cast<int64_t>(dim)) {
+        fail(ErrorType::DIMENSION_NOT_EQUAL,
+             "dimension of the dataset (" + std::to_string(base->GetDim()) + ") is not equal to the index (" +
+                 std::to_string(dim) + ")");
+    }
+    check_argument(base->GetFloat32Vectors() != nullptr, "dataset has no float32 vectors");
+    check_argument(!need_ids || base->GetIds() != nullptr, "dataset has no ids");
+}
+
+class GpuIVF : public Index {
+public:
+    GpuIVF(const CommonParam& common) : dim_(common.dim), metric_(common.metric) {
+        const Json& p = common.index_param;
+        // External keys of IVF::CheckAndMappingExternalParam (src/algorithm/ivf/ivf.cpp:140-395)
+        // with the defaults of its template (:78-135).
+        static const std::set<std::string> known = {
+            "buckets_count", "base_quantization_type", "base_io_type", "base_file_path", "precise_io_type",
+            "precise_file_path", "precise_quantization_type", "ivf_train_type", "partition_strategy_type",
+            "use_reorder", "buckets_per_data", "thread_count", "train_sample_count", "use_residual",
+            "rabitq_bits_per_dim_query", "rabitq_bits_per_dim_base", "rabitq_version", "rabitq_use_fht",
+            "rabitq_pca_dim", "use_attribute_filter", "first_order_buckets_count",
+            "second_order_buckets_count"};
+        check_known_keys(p, known, "index_param of ivf");
+        int64_t buckets = get_int(p, "buckets_count", 10);
+        check_argument(buckets >= 1, "buckets_count must be at least 1");
+        nlist_ = static_cast<uint32_t>(buckets);
+        std::string quant = get_string(p, "base_quantization_type", "fp32");
+        if (quant == "sq8") {
+            quant_ = VB200_QUANT_SQ8;
+        } else if (quant == "rabitq") {
+            quant_ = VB200_QUANT_RABITQ;
+        } else {
+            fail(ErrorType::INVALID_ARGUMENT, "base_quantization_type \"" + quant +
+                                                  "\" is not served by the GPU engine (sq8 and rabitq are)");
+        }
+        use_reorder_ = get_bool(p, "use_reorder", false);
+        std::string precise = get_string(p, "precise_quantization_type", "fp32");
+        check_argument(precise == "fp32", "precise_quantization_type must be fp32 for the GPU engine");
+        std::string train_type = get_string(p, "ivf_train_type", "kmeans");
+        check_argument(train_type == "kmeans" || train_type == "random",
+                       "ivf_train_type must be kmeans or random, got " + train_type);
+        kmeans_iters_ = train_type == "kmeans" ? 25 : 0;  // IVFNearestPartition::Train hard-codes 25
+        check_argument(get_string(p, "partition_strategy_type", "ivf") == "ivf",
+                       "partition_strategy_type must be ivf for the GPU engine (gno_imi is out of scope)");
+        check_argument(get_int(p, "buckets_per_data", 1) == 1, "buckets_per_data must be 1 for the GPU engine");
+        check_argument(get_int(p, "thread_count", 1) >= 1, "thread_count must be positive");
+        check_argument(!get_bool(p, "use_residual", false), "use_residual is not served by the GPU engine");
+        check_argument(!get_bool(p, "use_attribute_filter", false),
+                       "use_attribute_filter is not served by the GPU engine");
+        check_argument(get_int(p, "rabitq_bits_per_dim_query", 32) == 32 &&
+                           get_int(p, "rabitq_bits_per_dim_base", 1) == 1,
+                       "the GPU engine serves rabitq with a 32-bit query and 1-bit base codes");
+        check_argument(get_string(p, "rabitq_version", "standard") == "standard" &&
+                           !get_bool(p, "rabitq_use_fht", false) && get_int(p, "rabitq_pca_dim", 0) == 0,
+                       "the GPU engine serves the standard rabitq layout without FHT or PCA");
+        // default of IVFParameter (src/algorithm/ivf/ivf_parameter.cpp:88-98)
+        int64_t def_sample = std::max<int64_t>(65536, 64 * static_cast<int64_t>(nlist_));
+        train_sample_count_ = get_int(p, "train_sample_count", def_sample);
+        check_argument(train_sample_count_ >= 512, "train_sample_count must be at least 512");
+        check_status(vb200_ivf_create(dim_, metric_, nlist_, quant_, use_reorder_ ? 1 : 0, &handle_));
+        if (quant_ == VB200_QUANT_RABITQ) {
+            auto rot = random_rotation(dim_, 47);
+            check_status(vb200_ivf_set_rabitq_rotation(handle_, rot.data()));
+        }
+    }
+
+    ~GpuIVF() override {
+        vb200_ivf_destroy(handle_);
+    }
+
+    Expected<std::vector<int64_t>>
+    Build(const DatasetPtr& base) override {
+        return safe_call<std::vector<int64_t>>([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            check_base(base, dim_, true);
+            if (vb200_ivf_num_elements(handle_) > 0 || built_) {
+                fail(ErrorType::BUILD_TWICE, "index has been build, cannot build again");
+            }
+            if (base->GetNumElements() == 0) {
+                return std::vector<int64_t>{};
+            }
+            train_locked(base);
+            add_locked(base);
+            built_ = true;
+            return std::vector<int64_t>{};
+        });
+    }
+
+    Expected<void*>
+    Train(const DatasetPtr& data) override {
+        return safe_call<void*>([&]() -> void* {
+            std::lock_guard<std::mutex> lock(mu_);
+            check_base(data, dim_, false);
+            check_argument(data->GetNumElements() > 0, "training data is empty");
+            train_locked(data);
+            return nullptr;
+        });
+    }
+
+    Expected<std::vector<int64_t>>
+    Add(const DatasetPtr& base) override {
+        return safe_call<std::vector<int64_t>>([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            check_base(base, dim_, true);
+            if (base->GetNumElements() == 0) {
+                return std::vector<int64_t>{};
+            }
+            if (!trained_) {  // the reference trains on the first batch too (IVF::Add -> Train)
+                train_locked(base);
+            }
+            add_locked(base);
+            return std::vector<int64_t>{};
+        });
+    }
+
+    Expected<DatasetPtr>
+    KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters) const override {
+        return safe_call<DatasetPtr>([&]() {
+            check_argument(query != nullptr, "query is null");
+            check_argument(k > 0, "k must be greater than 0");
+            // IVFSearchParameters::FromJson (src/algorithm/ivf/ivf_parameter.cpp:150-187)
+            Json root = Json::Parse(parameters);
+            check_argument(root.IsObject() && root.Contains("ivf"), "parameters must contains ivf");
+            const Json& ivf = root.At("ivf");
+            check_argument(ivf.IsObject() && ivf.Contains("scan_buckets_count"),
+                           "parameters[ivf] must contains scan_buckets_count");
+            int64_t nprobe = get_int(ivf, "scan_buckets_count", 1);
+            check_argument(nprobe >= 1, "scan_buckets_count must be positive");
+            double factor = get_number(ivf, "factor", 2.0);
+            bool disable_scan = get_bool(ivf, "disable_bucket_scan", false);
+            if (query->GetNumElements() == 0 || vb200_ivf_num_elements(handle_) == 0) {
+                return make_empty_result();
+            }
+            check_base(query, dim_, false);
+            const int64_t nq = query->GetNumElements();
+            if (disable_scan) {
+                // routing only: bucket ids with their centroid distances (IVF::route_buckets_only,
+                // src/algorithm/ivf/ivf.cpp:1589-1660)
+                int64_t np = std::min<int64_t>(nprobe, nlist_);
+                std::vector<int32_t> buckets(static_cast<size_t>(nq * np));
+                auto* dists = new float[static_cast<size_t>(nq * np)];
+                auto* ids = new int64_t[static_cast<size_t>(nq * np)];
+                int status = vb200_ivf_route(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(np),
+                                             buckets.data(), dists);
+                if (status != 0) {
+                    delete[] dists;
+                    delete[] ids;
+                    check_status(status);
+                }
+                for (size_t i = 0; i < buckets.size(); ++i) {
+                    ids[i] = buckets[i];
+                }
+                return Dataset::Make()->NumElements(nq)->Dim(np)->Ids(ids)->Distances(dists)->Owner(true);
+            }
+            auto* ids = new int64_t[static_cast<size_t>(nq * k)];
+            auto* dists = new float[static_cast<size_t>(nq * k)];
+            int status = vb200_ivf_search(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
+                                          static_cast<uint32_t>(std::min<int64_t>(nprobe, 0x7fffffff)),
+                                          static_cast<float>(factor), nullptr, ids, dists);
+            if (status != 0) {
+                delete[] ids;
+                delete[] dists;
+                check_status(status);
+            }
+            int64_t scanned = vb200_ivf_last_scan_bytes(handle_);
+            std::string stats = "{\"dist_cmp\":" + std::to_string(code_size() > 0 ? scanned / code_size() : 0) + "}";
+            return pack_result(ids, dists, nq, k, stats);
+        });
+    }
+
+    int64_t GetNumElements() const override { return vb200_ivf_num_elements(handle_); }
+    int64_t GetMemoryUsage() const override { return vb200_ivf_memory_usage(handle_); }
+    std::string GetIndexType() const override { return "ivf"; }
+
+private:
+    int64_t
+    code_size() const {
+        return quant_ == VB200_QUANT_SQ8 ? dim_ : static_cast<int64_t>(vb200_rabitq_code_size(dim_));
+    }
+
+    void
+    train_locked(const DatasetPtr& data) {
+        if (trained_) {
+            return;
+        }
+        const int64_t n = data->GetNumElements();
+        const float* x = data->GetFloat32Vectors();
+        if (n < static_cast<int64_t>(nlist_)) {
+            fail(ErrorType::INVALID_ARGUMENT, "k cannot be larger than count");
+        }
+        // sample_train_data (src/utils/util_functions.cpp:273-330) draws a reservoir sample from
+        // std::random_device; here a strided sample of the same size (all rows when they fit).
+        std::vector<float> sample;
+        int64_t count = n;
+        if (n > train_sample_count_) {
+            count = std::max<int64_t>(train_sample_count_, nlist_);
+            sample.resize(static_cast<size_t>(count) * dim_);
+            const int64_t stride = n / count;
+            for (int64_t j = 0; j < count; ++j) {
+                std::memcpy(sample.data() + static_cast<size_t>(j) * dim_, x + static_cast<size_t>(j * stride) * dim_,
+                            dim_ * sizeof(float));
+            }
+            x = sample.data();
+        }
+        check_status(vb200_ivf_train(handle_, x, static_cast<uint64_t>(count), kmeans_iters_, nullptr));
+        trained_ = true;
+    }
+
+    void
+    add_locked(const DatasetPtr& base) {
+        check_status(vb200_ivf_add(handle_, base->GetFloat32Vectors(), static_cast<uint64_t>(base->GetNumElements()),
+                                   base->GetIds(), nullptr));
+    }
+
+    uint32_t dim_;
+    int metric_;
+    uint32_t nlist_ = 10;
+    int quant_ = VB200_QUANT_SQ8;
+    bool use_reorder_ = false;
+    int kmeans_iters_ = 25;
+    int64_t train_sample_count_ = 65536;
+    bool trained_ = false;
+    bool built_ = false;
+    vb200_ivf_t handle_ = nullptr;
+    mutable std::mutex mu_;
+};
+
+// -------------------------------------------------------------------------------------------------
+// BruteForce
+// -------------------------------------------------------------------------------------------------
+class GpuBruteForce : public Index {
+public:
+    GpuBruteForce(const CommonParam& common) : dim_(common.dim), metric_(common.metric) {
+        const Json& p = common.index_param;
+        // External keys of BruteForce::CheckAndMappingExternalParam
+        // (src/algorithm/bruteforce/bruteforce.cpp:1273-1361).
+        static const std::set<std::string> known = {"base_quantization_type", "base_io_type", "base_file_path",
+                                                    "thread_count", "resize_increase_count_bit",
+                                                    "use_attribute_filter", "store_raw_vector"};
+        check_known_keys(p, known, "index_param of brute_force");
+        std::string quant = get_string(p, "base_quantization_type", "fp32");
+        if (quant == "fp32") {
+            quant_ = VB200_QUANT_FP32;
+        } else if (quant == "bf16") {
+            quant_ = VB200_QUANT_BF16;
+        } else {
+            fail(ErrorType::INVALID_ARGUMENT, "base_quantization_type \"" + quant +
+                                                  "\" is not served by the GPU engine (fp32 and bf16 are)");
+        }
+        check_argument(!get_bool(p, "use_attribute_filter", false),
+                       "use_attribute_filter is not served by the GPU engine");
+        check_status(vb200_bf_create(dim_, metric_, quant_, &handle_));
+    }
+
+    ~GpuBruteForce() override {
+        vb200_bf_destroy(handle_);
+    }
+
+    Expected<std::vector<int64_t>>
+    Build(const DatasetPtr& base) override {
+        return safe_call<std::vector<int64_t>>([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (vb200_bf_num_elements(handle_) > 0) {
+                fail(ErrorType::BUILD_TWICE, "index has been build, cannot build again");
+            }
+            add_locked(base);
+            return std::vector<int64_t>{};
+        });
+    }
+
+    Expected<void*>
+    Train(const DatasetPtr&) override {
+        return Expected<void*>(nullptr);  // fp32 / bf16 codecs have nothing to train (bruteforce.cpp:91-95)
+    }
+
+    Expected<std::vector<int64_t>>
+    Add(const DatasetPtr& base) override {
+        return safe_call<std::vector<int64_t>>([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            add_locked(base);
+            return std::vector<int64_t>{};
+        });
+    }
+
+    Expected<DatasetPtr>
+    KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters) const override {
+        return safe_call<DatasetPtr>([&]() {
+            check_argument(query != nullptr, "query is null");
+            check_argument(k > 0, "k must be greater than 0");
+            if (!parameters.empty()) {
+                Json root = Json::Parse(parameters);  // "{}", {"parallelism": n} or nested (bruteforce_parameter.h:44-78)
+                check_argument(root.IsObject(), "search parameters must be a JSON object");
+            }
+            if (query->GetNumElements() == 0 || vb200_bf_num_elements(handle_) == 0) {
+                return make_empty_result();
+            }
+            check_base(query, dim_, false);
+            const int64_t nq = query->GetNumElements();
+            auto* ids = new int64_t[static_cast<size_t>(nq * k)];
+            auto* dists = new float[static_cast<size_t>(nq * k)];
+            int status = vb200_bf_search(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k), ids, dists);
+            if (status != 0) {
+                delete[] ids;
+                delete[] dists;
+                check_status(status);
+            }
+            std::string stats = "{\"dist_cmp\":" + std::to_string(vb200_bf_num_elements(handle_) * nq) + "}";
+            return pack_result(ids, dists, nq, k, stats);
+        });
+    }
+
+    int64_t GetNumElements() const override { return vb200_bf_num_elements(handle_); }
+    int64_t GetMemoryUsage() const override {
+        return vb200_bf_num_elements(handle_) * dim_ * (quant_ == VB200_QUANT_FP32 ? 4 : 2);
+    }
+    std::string GetIndexType() const override { return "brute_force"; }
+
+private:
+    void
+    add_locked(const DatasetPtr& base) {
+        check_argument(base != nullptr, "dataset is null");
+        if (base->GetNumElements() == 0) {
+            return;
+        }
+        if (base->GetFloat32Vectors() == nullptr && base->GetFloat16Vectors() != nullptr &&
+            quant_ == VB200_QUANT_BF16) {
+            // rows that are already bf16 bit patterns (Dataset::Float16Vectors, dataset.h:277-284)
+            check_argument(base->GetDim() == static_cast<int64_t>(dim_) && base->GetIds() != nullptr,
+                           "dataset does not match the index");
+            check_status(vb200_bf_add_bf16(handle_, base->GetFloat16Vectors(),
+                                           static_cast<uint64_t>(base->GetNumElements()), base->GetIds()));
+            return;
+        }
+        check_base(base, dim_, true);
+        check_status(vb200_bf_add(handle_, base->GetFloat32Vectors(), static_cast<uint64_t>(base->GetNumElements()),
+                                  base->GetIds()));
+    }
+
+    uint32_t dim_;
+    int metric_;
+    int quant_ = VB200_QUANT_FP32;
+    vb200_bf_t handle_ = nullptr;
+    mutable std::mutex mu_;
+};
+
+}  // namespace
+
+Expected<std::shared_ptr<Index>>
+Factory::CreateIndex(const std::string& name, const std::string& parameters) {
+    return safe_call<std::shared_ptr<Index>>([&]() -> std::shared_ptr<Index> {
+        std::string lowered = lower(name);  // names are case-insensitive (src/factory/index_registry.cpp:41-47)
+        if (lowered != "ivf" && lowered != "brute_force") {
+            fail(ErrorType::UNSUPPORTED_INDEX, "failed to create index(unsupported): " + name);
+        }
+        CommonParam common = parse_common(parameters);
+        if (lowered == "ivf") {
+            return std::make_shared<GpuIVF>(common);
+        }
+        return std::make_shared<GpuBruteForce>(common);
+    });
+}
+
+}  // namespace vsag

@@ -1,0 +1,124 @@
+// Host-side mirror of the part of VSAG's public API that the accelerated path sits behind:
+// vsag::Factory::CreateIndex("ivf" | "brute_force", json), Index::{Build, Train, Add, KnnSearch,
+// GetNumElements, GetMemoryUsage} and the Dataset builder (reference: include/vsag/factory.h:47-50,
+// include/vsag/index.h:126-303, include/vsag/dataset.h:135-511, include/vsag/errors.h:26-48).
+// Same names, argument meaning and error behaviour, written from scratch over the C ABI of
+// include/vsag_b200.h; no exception crosses these calls.
+#pragma once
+
+#include <cstdint>
+#include <functional>
+#include <memory>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace vsag {
+
+enum class ErrorType {
+    UNKNOWN_ERROR = 1,
+    INTERNAL_ERROR,
+    INVALID_ARGUMENT,
+    WRONG_STATUS,
+    BUILD_TWICE,
+    INDEX_NOT_EMPTY,
+    UNSUPPORTED_INDEX,
+    UNSUPPORTED_INDEX_OPERATION,
+    DIMENSION_NOT_EQUAL,
+    INDEX_EMPTY,
+    NO_ENOUGH_MEMORY,
+    READ_ERROR,
+    MISSING_FILE,
+    INVALID_BINARY,
+};
+
+struct Error {
+    ErrorType type;
+    std::string message;
+};
+
+// Stand-in for tl::expected<T, Error> with the members the API's callers use.
+template <typename T>
+class Expected {
+public:
+    Expected(T value) : has_(true), value_(std::move(value)) {}  // NOLINT(google-explicit-constructor)
+    Expected(Error error) : has_(false), error_(std::move(error)) {}  // NOLINT(google-explicit-constructor)
+    bool has_value() const { return has_; }
+    explicit operator bool() const { return has_; }
+    T& value() { return value_; }
+    const T& value() const { return value_; }
+    T& operator*() { return value_; }
+    T* operator->() { return &value_; }
+    const Error& error() const { return error_; }
+
+private:
+    bool has_;
+    T value_{};
+    Error error_{ErrorType::UNKNOWN_ERROR, ""};
+};
+
+class Dataset;
+using DatasetPtr = std::shared_ptr<Dataset>;
+
+// Builder-style container of vectors / ids / distances (include/vsag/dataset.h).  With
+// Owner(true) (the default) the dataset frees ids, distances and vectors with delete[].
+class Dataset : public std::enable_shared_from_this<Dataset> {
+public:
+    static DatasetPtr Make();
+    ~Dataset();
+
+    DatasetPtr Owner(bool is_owner);
+    DatasetPtr NumElements(int64_t num_elements);
+    DatasetPtr Dim(int64_t dim);
+    DatasetPtr Ids(const int64_t* ids);
+    DatasetPtr Distances(const float* dists);
+    DatasetPtr Float32Vectors(const float* vectors);
+    DatasetPtr Float16Vectors(const uint16_t* vectors);  // bf16 bit patterns for a bf16 BruteForce index
+    DatasetPtr Statistics(const std::string& stats);
+
+    int64_t GetNumElements() const { return num_elements_; }
+    int64_t GetDim() const { return dim_; }
+    const int64_t* GetIds() const { return ids_; }
+    const float* GetDistances() const { return distances_; }
+    const float* GetFloat32Vectors() const { return vectors_; }
+    const uint16_t* GetFloat16Vectors() const { return half_vectors_; }
+    const std::string& GetStatistics() const { return statistics_; }
+
+private:
+    Dataset() = default;
+    bool owner_ = true;
+    int64_t num_elements_ = 0;
+    int64_t dim_ = 0;
+    const int64_t* ids_ = nullptr;
+    const float* distances_ = nullptr;
+    const float* vectors_ = nullptr;
+    const uint16_t* half_vectors_ = nullptr;
+    std::string statistics_;
+};
+
+class Index {
+public:
+    virtual ~Index() = default;
+
+    // Train + Add; returns the ids that failed to insert (always empty here).
+    virtual Expected<std::vector<int64_t>> Build(const DatasetPtr& base) = 0;
+    virtual Expected<void*> Train(const DatasetPtr& data) = 0;
+    virtual Expected<std::vector<int64_t>> Add(const DatasetPtr& base) = 0;
+    // query: NumElements >= 1 rows.  One query returns NumElements = 1, Dim = results found
+    // (<= k); a batch returns NumElements = Q, Dim = k padded with id -1 / distance +inf.
+    virtual Expected<DatasetPtr> KnnSearch(const DatasetPtr& query, int64_t k,
+                                           const std::string& parameters) const = 0;
+    virtual int64_t GetNumElements() const = 0;
+    virtual int64_t GetMemoryUsage() const = 0;
+    virtual std::string GetIndexType() const = 0;
+};
+
+class Factory {
+public:
+    // name: "ivf" or "brute_force" (case-insensitive).  parameters: the reference's creation JSON
+    // (dtype, metric_type, dim, index_param{...}).  Unknown names -> UNSUPPORTED_INDEX, bad or
+    // unknown keys / values -> INVALID_ARGUMENT.
+    static Expected<std::shared_ptr<Index>> CreateIndex(const std::string& name, const std::string& parameters);
+};
+
+}  // namespace vsag

@@ -1,0 +1,117 @@
+"""Python face of the Factory / Index mirror, shaped like the reference's pyvsag.Index
+(python_bindings/index_binding.cpp:629-900): Index(name, parameters_json), build, add, knn_search.
+It calls the vsag_index_* C functions exported by libvsag_b200.so (the names of the reference's
+include/vsag/vsag_c_api.h)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi
+
+
+class _Error(C.Structure):
+    _fields_ = [("code", C.c_int), ("message", C.c_char * 1024)]
+
+
+class _SearchResult(C.Structure):
+    _fields_ = [("dists", C.POINTER(C.c_float)), ("ids", C.POINTER(C.c_int64)), ("count", C.c_int64),
+                ("other_result", C.c_void_p)]
+
+
+class VsagError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+_bound = False
+
+
+def _lib():
+    global _bound
+    lib = _capi.load()
+    if not _bound:
+        lib.vsag_index_factory.restype = C.c_void_p
+        lib.vsag_index_factory.argtypes = [C.c_char_p, C.c_char_p]
+        lib.vsag_index_factory_error.restype = C.c_char_p
+        lib.vsag_index_destroy.restype = _Error
+        lib.vsag_index_destroy.argtypes = [C.c_void_p]
+        for name in ("vsag_index_build", "vsag_index_add", "vsag_index_train"):
+            fn = getattr(lib, name)
+            fn.restype = _Error
+            fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64]
+        lib.vsag_index_knn_search.restype = _Error
+        lib.vsag_index_knn_search.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int64, C.c_char_p,
+                                              C.POINTER(_SearchResult)]
+        lib.vsag_index_knn_search_batch.restype = _Error
+        lib.vsag_index_knn_search_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int64,
+                                                    C.c_char_p, C.c_void_p, C.c_void_p]
+        lib.vsag_index_get_num_elements.restype = C.c_int64
+        lib.vsag_index_get_num_elements.argtypes = [C.c_void_p]
+        _bound = True
+    return lib
+
+
+def _check(err: _Error) -> None:
+    if err.code != 0:
+        raise VsagError(err.code, err.message.decode("utf-8", "replace"))
+
+
+class Index:
+    """vsag.Index(name, parameters): "ivf" or "brute_force" with the reference's JSON parameters."""
+
+    def __init__(self, name: str, parameters: str):
+        lib = _lib()
+        self._h = lib.vsag_index_factory(name.encode(), parameters.encode())
+        if not self._h:
+            msg = lib.vsag_index_factory_error().decode("utf-8", "replace")
+            raise VsagError(-3 if "unsupported" not in msg else -7, msg)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _lib().vsag_index_destroy(self._h)
+            self._h = None
+
+    @staticmethod
+    def _rows(vectors, ids, num_elements, dim):
+        vectors = np.ascontiguousarray(vectors, np.float32).reshape(num_elements, dim)
+        ids = np.ascontiguousarray(ids, np.int64)
+        return vectors, ids
+
+    def build(self, vectors, ids, num_elements: int, dim: int) -> None:
+        vectors, ids = self._rows(vectors, ids, num_elements, dim)
+        _check(_lib().vsag_index_build(self._h, vectors.ctypes.data, ids.ctypes.data, dim, num_elements))
+
+    def add(self, vectors, ids, num_elements: int, dim: int) -> None:
+        vectors, ids = self._rows(vectors, ids, num_elements, dim)
+        _check(_lib().vsag_index_add(self._h, vectors.ctypes.data, ids.ctypes.data, dim, num_elements))
+
+    def train(self, vectors, num_elements: int, dim: int) -> None:
+        vectors = np.ascontiguousarray(vectors, np.float32).reshape(num_elements, dim)
+        _check(_lib().vsag_index_train(self._h, vectors.ctypes.data, None, dim, num_elements))
+
+    def knn_search(self, vector, k: int, parameters: str = "{}"):
+        """One query -> (ids, dists) of the entries found (at most k), ascending by distance."""
+        vector = np.ascontiguousarray(vector, np.float32).reshape(-1)
+        ids = np.empty(max(k, 1), np.int64)
+        dists = np.empty(max(k, 1), np.float32)
+        res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
+        _check(_lib().vsag_index_knn_search(self._h, vector.ctypes.data, vector.size, k, parameters.encode(),
+                                            C.byref(res)))
+        return ids[: res.count].copy(), dists[: res.count].copy()
+
+    def knn_search_batch(self, vectors, k: int, parameters: str = "{}"):
+        """nq queries -> ids[nq, k], dists[nq, k] padded with -1 / +inf."""
+        vectors = np.ascontiguousarray(vectors, np.float32)
+        nq, dim = vectors.shape
+        ids = np.empty((nq, k), np.int64)
+        dists = np.empty((nq, k), np.float32)
+        _check(_lib().vsag_index_knn_search_batch(self._h, vectors.ctypes.data, dim, nq, k, parameters.encode(),
+                                                  ids.ctypes.data, dists.ctypes.data))
+        return ids, dists
+
+    def get_num_elements(self) -> int:
+        return int(_lib().vsag_index_get_num_elements(self._h))
