@@ -80,6 +80,13 @@ VB200_API int vb200_set_stream(void* cuda_stream);
 /* Number of kernels this library has launched in the process so far. */
 VB200_API uint64_t vb200_kernel_launches(void);
 
+/* Chooses how the dense contractions (k-means assignment, routing, BruteForce) nominate
+ * candidates: 1 (default) = tcgen05 tensor-core kernels, 0 = the fixed-order fp32 SIMT kernels.
+ * Either way the survivors are re-scored in the reference's exact operation order, so results are
+ * the same; the switch exists for cross-checking and timing.  The environment variable
+ * VB200_DISABLE_TC=1 sets the initial value to 0. */
+VB200_API int vb200_set_tensor_cores(int enable);
+
 /* Number of CUDA devices visible, or a negative VB200_* code. */
 VB200_API int vb200_device_count(void);
 

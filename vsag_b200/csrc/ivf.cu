@@ -995,6 +995,7 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
     }
     DevInput<float> x;
     VB_TRY(x.bind(data, count * ix->dim));
+    ix->kws.forget_points();
     const size_t kd = static_cast<size_t>(ix->nlist) * ix->dim;
     VB_TRY(ix->centroids.reserve(kd));
     const float* seed = init != nullptr ? init : x.ptr;
@@ -1004,7 +1005,7 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
     VB_TRY(lab.reserve(count));
     for (int it = 0; it < kmeans_iters; ++it) {
         VB_TRY(kmeans_assign_device(ix->kws, x.ptr, count, ix->dim, ix->centroids.ptr, ix->nlist,
-                                    lab.ptr, nullptr));
+                                    lab.ptr, nullptr, it > 0 ? lab.ptr : nullptr));
         VB_TRY(kmeans_update_device(ix->kws, x.ptr, count, ix->dim, lab.ptr, ix->nlist,
                                     static_cast<uint32_t>(it), ix->centroids.ptr));
     }

@@ -2,6 +2,8 @@
 // dense kernel with a fused argmin epilogue, and the centroid update.
 #include "kmeans.cuh"
 
+#include <cstdlib>
+
 #include "dense.cuh"
 
 namespace vb200 {
@@ -39,15 +41,198 @@ kmeans_error_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim,
     }
 }
 
+static std::atomic<int> g_tc_enabled{-1};
+
+bool
+tensor_cores_enabled() {
+    int v = g_tc_enabled.load();
+    if (v < 0) {
+        const char* e = getenv("VB200_DISABLE_TC");
+        v = (e != nullptr && e[0] != 0 && e[0] != '0') ? 0 : 1;
+        g_tc_enabled.store(v);
+    }
+    return v == 1;
+}
+
+// Picks, among each row's candidate centroids, the one the reference's arithmetic prefers:
+// score = fma(-2, <c, x>, |c|^2) with the inner product as one ascending FMA chain, lowest index
+// on ties (src/impl/cluster/kmeans_cluster.cpp:262-284).  `lanes` (a power of two <= 32) threads
+// share a row, one candidate each per round; the chain of a candidate stays in one thread.
+__global__ void __launch_bounds__(128)
+kmeans_pick_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, const float* __restrict__ centroids,
+                   const float* __restrict__ c_sq, const uint64_t* __restrict__ cand, uint32_t per_row,
+                   uint32_t lanes, int32_t* __restrict__ labels, float* __restrict__ best_out) {
+    const uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t i = t / lanes;
+    const uint32_t sub = static_cast<uint32_t>(t % lanes);
+    const bool live = i < n;
+    float best = INFINITY;
+    uint32_t best_col = 0x7fffffffu;
+    if (live) {
+        const float* xi = x + i * dim;
+        const uint64_t* ci = cand + i * per_row;
+        const bool vec = (dim & 3u) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(centroids)) & 15u) == 0;
+        for (uint32_t j = sub; j < per_row; j += lanes) {
+            uint64_t key = ci[j];
+            if (key == KEY_INF) {
+                continue;
+            }
+            uint32_t col = static_cast<uint32_t>(key);
+            const float* c = centroids + static_cast<uint64_t>(col) * dim;
+            float ip = 0.f;
+            if (vec) {
+                for (uint32_t d = 0; d < dim; d += 4) {
+                    float4 cv = __ldg(reinterpret_cast<const float4*>(c + d));
+                    float4 xv = __ldg(reinterpret_cast<const float4*>(xi + d));
+                    ip = fmaf(cv.x, xv.x, ip);
+                    ip = fmaf(cv.y, xv.y, ip);
+                    ip = fmaf(cv.z, xv.z, ip);
+                    ip = fmaf(cv.w, xv.w, ip);
+                }
+            } else {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    ip = fmaf(__ldg(c + d), __ldg(xi + d), ip);
+                }
+            }
+            float score = fmaf(-2.0f, ip, __ldg(c_sq + col));
+            if (score < best || (score == best && col < best_col)) {
+                best = score;
+                best_col = col;
+            }
+        }
+    }
+    for (uint32_t off = lanes >> 1; off > 0; off >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        uint32_t oc = __shfl_xor_sync(0xffffffffu, best_col, off);
+        if (ob < best || (ob == best && oc < best_col)) {
+            best = ob;
+            best_col = oc;
+        }
+    }
+    if (live && sub == 0) {
+        labels[i] = best_col == 0x7fffffffu ? 0 : static_cast<int32_t>(best_col);
+        if (best_out != nullptr) {
+            best_out[i] = best;
+        }
+    }
+}
+
+// out[0] = scale * sqrt(max_j sq[j]); one CTA.
+__global__ void __launch_bounds__(256)
+max_norm_kernel(const float* __restrict__ sq, uint32_t k, float scale, float* __restrict__ out) {
+    __shared__ float part[8];
+    float m = 0.f;
+    for (uint32_t j = threadIdx.x; j < k; j += blockDim.x) {
+        m = fmaxf(m, sq[j]);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        part[threadIdx.x >> 5] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) {
+            m = fmaxf(m, part[w]);
+        }
+        out[0] = scale * sqrtf(m);
+    }
+}
+
+// bound[i] = fma(-2, <c_l, x_i>, |c_l|^2) for l = the row's previous label (+inf when it has none).
+__global__ void __launch_bounds__(128)
+kmeans_prev_score_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, const float* __restrict__ centroids,
+                         const float* __restrict__ c_sq, uint32_t k, const int32_t* __restrict__ prev,
+                         float* __restrict__ bound) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) {
+        return;
+    }
+    int32_t l = prev[i];
+    if (l < 0 || static_cast<uint32_t>(l) >= k) {
+        bound[i] = INFINITY;
+        return;
+    }
+    const float* xi = x + i * dim;
+    const float* c = centroids + static_cast<uint64_t>(l) * dim;
+    float ip = 0.f;
+    for (uint32_t d = 0; d < dim; ++d) {
+        ip = fmaf(__ldg(c + d), __ldg(xi + d), ip);
+    }
+    bound[i] = fmaf(-2.0f, ip, __ldg(c_sq + l));
+}
+
+constexpr uint32_t KMEANS_TC_CANDIDATES = 4;
+constexpr uint64_t KMEANS_TC_SLICE = uint64_t{1} << 22;  // rows tiled at once
+
+// Assignment through the tensor cores: candidates from the split-bf16 GEMM, winner by the exact
+// rule above.  Equal to the fixed-order SIMT result whenever the true winner is among the four
+// nominated centroids, i.e. unless more than three others sit within ~1e-5 relative of it.
+static int
+kmeans_assign_tc(KMeansWorkspace& ws, const float* x_dev, uint64_t n, uint32_t dim,
+                 const float* centroids_dev, uint32_t k, int32_t* labels_dev, float* best_dev,
+                 const int32_t* prev_labels_dev) {
+    const uint32_t chunks = (dim + TC_KC - 1) / TC_KC;
+    const size_t c_elems = tc_tiled_elems(k, dim);
+    VB_TRY(ws.c_hi.reserve(c_elems));
+    VB_TRY(ws.c_lo.reserve(c_elems));
+    VB_TRY(tc_pretile_f32(centroids_dev, k, dim, ws.c_hi.ptr, ws.c_lo.ptr));
+    TcOperand b{ws.c_hi.ptr, ws.c_lo.ptr, k, chunks};
+    const uint32_t m = k < KMEANS_TC_CANDIDATES ? k : KMEANS_TC_CANDIDATES;
+    // The split-bf16 scores are within ~3e-5 * |x| * |c| of the exact ones; columns more than
+    // 1e-3 * |x| * max|c| behind a row's best cannot be its exact winner and are skipped.
+    VB_TRY(ws.margin.reserve(1));
+    VB_LAUNCH(max_norm_kernel, 1, 256, 0, ws.c_sq.ptr, k, 1e-3f, ws.margin.ptr);
+    for (uint64_t r0 = 0; r0 < n; r0 += KMEANS_TC_SLICE) {
+        const uint64_t rows = n - r0 < KMEANS_TC_SLICE ? n - r0 : KMEANS_TC_SLICE;
+        const bool whole = rows == n;
+        const bool cached = whole && ws.tiled_rows == x_dev && ws.tiled_n == n && ws.tiled_dim == dim;
+        if (!cached) {
+            const size_t x_elems = tc_tiled_elems(rows, dim);
+            VB_TRY(ws.x_hi.reserve(x_elems));
+            VB_TRY(ws.x_lo.reserve(x_elems));
+            VB_TRY(tc_pretile_f32(x_dev + r0 * dim, rows, dim, ws.x_hi.ptr, ws.x_lo.ptr));
+            VB_TRY(ws.x_sq.reserve(rows));
+            VB_TRY(row_sqnorm_f32(x_dev + r0 * dim, rows, dim, ws.x_sq.ptr));
+            ws.tiled_rows = whole ? x_dev : nullptr;
+            ws.tiled_n = whole ? n : 0;
+            ws.tiled_dim = dim;
+        }
+        TcOperand a{ws.x_hi.ptr, ws.x_lo.ptr, rows, chunks};
+        const float* row_bound = nullptr;
+        if (prev_labels_dev != nullptr) {
+            VB_TRY(ws.row_bound.reserve(rows));
+            VB_LAUNCH(kmeans_prev_score_kernel, static_cast<uint32_t>((rows + 127) / 128), 128, 0, x_dev + r0 * dim,
+                      rows, dim, centroids_dev, ws.c_sq.ptr, k, prev_labels_dev + r0, ws.row_bound.ptr);
+            row_bound = ws.row_bound.ptr;
+        }
+        uint32_t n_split = 1;
+        VB_TRY(tc_candidates(ws.tc, a, b, 3, -2.0f, ws.c_sq.ptr, m, 0, ws.cand, &n_split, ws.x_sq.ptr,
+                             ws.margin.ptr, row_bound));
+        const uint32_t per_row = n_split * m;
+        const uint32_t lanes = per_row >= 32 ? 32u : next_pow2(per_row);
+        const uint64_t threads = rows * lanes;
+        VB_LAUNCH(kmeans_pick_kernel, static_cast<uint32_t>((threads + 127) / 128), 128, 0, x_dev + r0 * dim, rows,
+                  dim, centroids_dev, ws.c_sq.ptr, ws.cand.ptr, per_row, lanes, labels_dev + r0,
+                  best_dev != nullptr ? best_dev + r0 : nullptr);
+    }
+    return 0;
+}
+
 int
 kmeans_assign_device(KMeansWorkspace& ws, const float* x_dev, uint64_t n, uint32_t dim,
                      const float* centroids_dev, uint32_t k, int32_t* labels_dev,
-                     double* mean_err_host) {
+                     double* mean_err_host, const int32_t* prev_labels_dev) {
     VB_TRY(ws.c_sq.reserve(k));
     VB_TRY(ws.best.reserve(n));
     VB_TRY(row_sqnorm_f32(centroids_dev, k, dim, ws.c_sq.ptr));
-    VB_TRY(dense_argmin_f32(x_dev, n, centroids_dev, k, dim, -2.0f, ws.c_sq.ptr, labels_dev,
-                            ws.best.ptr));
+    if (tensor_cores_enabled() && k >= 64 && n >= 128) {
+        VB_TRY(kmeans_assign_tc(ws, x_dev, n, dim, centroids_dev, k, labels_dev, ws.best.ptr, prev_labels_dev));
+    } else {
+        VB_TRY(dense_argmin_f32(x_dev, n, centroids_dev, k, dim, -2.0f, ws.c_sq.ptr, labels_dev,
+                                ws.best.ptr));
+    }
     if (mean_err_host != nullptr) {
         VB_TRY(ws.err.reserve(1));
         VB_CUDA(cudaMemsetAsync(ws.err.ptr, 0, sizeof(double), current_stream()));
@@ -194,7 +379,7 @@ vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, 
     KMeansWorkspace ws;
     for (int it = 0; it < iters; ++it) {
         double* err = (it == iters - 1) ? mean_err : nullptr;
-        VB_TRY(kmeans_assign_device(ws, x.ptr, count, dim, c.ptr, k, lab.ptr, err));
+        VB_TRY(kmeans_assign_device(ws, x.ptr, count, dim, c.ptr, k, lab.ptr, err, it > 0 ? lab.ptr : nullptr));
         VB_TRY(kmeans_update_device(ws, x.ptr, count, dim, lab.ptr, k, static_cast<uint32_t>(it), c.ptr));
     }
     VB_TRY(copy_out(centroids, c.ptr, kd));
@@ -250,4 +435,10 @@ vb200_kmeans_assign_noalloc(const float* data_dev, uint64_t count, uint32_t dim,
     VB_TRY(row_sqnorm_f32(centroids_dev, k, dim, c_sq));
     VB_TRY(dense_argmin_f32(data_dev, count, centroids_dev, k, dim, -2.0f, c_sq, labels_dev, nullptr));
     return sync_stream();
+}
+
+extern "C" int
+vb200_set_tensor_cores(int enable) {
+    g_tc_enabled.store(enable != 0 ? 1 : 0);
+    return 0;
 }

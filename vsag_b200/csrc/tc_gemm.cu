@@ -1,0 +1,571 @@
+// tcgen05 / TMEM candidate-generation GEMM: operand pre-tiling, the kernel and its launcher.
+#include "tc_gemm.cuh"
+
+#include <cuda_bf16.h>
+
+namespace vb200 {
+
+constexpr uint32_t TC_STAGES = 3;
+
+__device__ __forceinline__ float
+widen_in(float v) {
+    return v;
+}
+__device__ __forceinline__ float
+widen_in(uint16_t v) {  // bf16 bit pattern
+    return __uint_as_float(static_cast<uint32_t>(v) << 16);
+}
+
+// ---------------------------------------------------------------------------------------------
+// pre-tiling: element (r, e) of a [rows x dim] matrix goes to
+//   tile r/128, chunk e/64, core matrix ((r%128)/8, (e%64)/8), row r%8, element e%8
+// so a [128 x 64] chunk is 16 KiB contiguous: 8x8-element cores of 128 B, the 8 cores of an 8-row
+// group back to back (1 KiB per group).  Out-of-range rows / dimensions are zero.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool SPLIT>
+__global__ void
+tc_pretile_kernel(const T* __restrict__ src, uint64_t rows, uint32_t dim, uint32_t chunks,
+                  uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, uint64_t total_units) {
+    uint64_t u = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // one 8-element core row
+    if (u >= total_units) {
+        return;
+    }
+    uint32_t rr8 = static_cast<uint32_t>(u & 7);
+    uint32_t core_k = static_cast<uint32_t>((u >> 3) & 7);
+    uint32_t core_r = static_cast<uint32_t>((u >> 6) & 15);
+    uint64_t chunk_id = u >> 10;  // tile * chunks + chunk
+    uint32_t kc = static_cast<uint32_t>(chunk_id % chunks);
+    uint64_t tile = chunk_id / chunks;
+    uint64_t r = tile * 128 + core_r * 8 + rr8;
+    uint32_t e0 = kc * TC_KC + core_k * 8;
+    uint16_t h[8], l[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float x = 0.f;
+        if (r < rows && e0 + i < dim) {
+            x = widen_in(src[r * dim + e0 + i]);
+        }
+        __nv_bfloat16 bh = __float2bfloat16_rn(x);
+        h[i] = __bfloat16_as_ushort(bh);
+        if (SPLIT) {
+            float rest = x - __bfloat162float(bh);
+            l[i] = __bfloat16_as_ushort(__float2bfloat16_rn(rest));
+        }
+    }
+    uint4 vh = make_uint4(h[0] | (uint32_t(h[1]) << 16), h[2] | (uint32_t(h[3]) << 16),
+                          h[4] | (uint32_t(h[5]) << 16), h[6] | (uint32_t(h[7]) << 16));
+    reinterpret_cast<uint4*>(hi)[u] = vh;
+    if (SPLIT) {
+        uint4 vl = make_uint4(l[0] | (uint32_t(l[1]) << 16), l[2] | (uint32_t(l[3]) << 16),
+                              l[4] | (uint32_t(l[5]) << 16), l[6] | (uint32_t(l[7]) << 16));
+        reinterpret_cast<uint4*>(lo)[u] = vl;
+    }
+}
+
+size_t
+tc_tiled_elems(uint64_t rows, uint32_t dim) {
+    uint64_t tiles = (rows + 127) / 128;
+    uint64_t chunks = (dim + TC_KC - 1) / TC_KC;
+    return static_cast<size_t>(tiles * chunks * TC_CHUNK_ELEMS);
+}
+
+template <typename T>
+static int
+pretile_launch(const T* src, uint64_t rows, uint32_t dim, uint16_t* hi, uint16_t* lo) {
+    if (rows == 0) {
+        return 0;
+    }
+    uint32_t chunks = (dim + TC_KC - 1) / TC_KC;
+    uint64_t units = tc_tiled_elems(rows, dim) / 8;
+    uint64_t blocks = (units + 255) / 256;
+    VB_CHECK_ARG(blocks <= 0x7fffffffu, "pretile: matrix too large");
+    if (lo != nullptr) {
+        auto kernel = tc_pretile_kernel<T, true>;
+        VB_LAUNCH(kernel, static_cast<uint32_t>(blocks), 256, 0, src, rows, dim, chunks, hi, lo, units);
+    } else {
+        auto kernel = tc_pretile_kernel<T, false>;
+        VB_LAUNCH(kernel, static_cast<uint32_t>(blocks), 256, 0, src, rows, dim, chunks, hi, lo, units);
+    }
+    return 0;
+}
+
+int
+tc_pretile_f32(const float* src_dev, uint64_t rows, uint32_t dim, uint16_t* hi_dev, uint16_t* lo_dev) {
+    return pretile_launch<float>(src_dev, rows, dim, hi_dev, lo_dev);
+}
+
+int
+tc_pretile_bf16(const uint16_t* src_dev, uint64_t rows, uint32_t dim, uint16_t* hi_dev) {
+    return pretile_launch<uint16_t>(src_dev, rows, dim, hi_dev, nullptr);
+}
+
+// ---------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------
+struct TcShared {
+    uint64_t full[TC_STAGES];    // chunk copies landed
+    uint64_t freed[TC_STAGES];   // MMAs that read the stage retired
+    uint64_t acc_full[2];        // accumulator holds a finished tile
+    uint64_t acc_free[2];        // accumulator drained by the 128 epilogue threads
+    uint32_t tmem_base;
+    uint32_t failed;
+    alignas(16) float bias[2][TC_BN];   // bias of the tile in each accumulator (read as float4)
+};
+
+// Warp-cooperative: sort row `owner`'s buffer, keep its m best, tighten its threshold.  The row's
+// keys are staged through this warp's shared-memory sort area (sorting in global memory is
+// latency-bound: one round trip per compare-exchange stage).
+__device__ __forceinline__ void
+tc_compact_row(uint64_t* my_buf, uint32_t& my_cnt, float& my_thr, uint32_t owner, uint32_t lane, uint32_t m,
+               uint64_t* sort_area) {
+    uint64_t addr = reinterpret_cast<uint64_t>(my_buf);
+    uint32_t lo = __shfl_sync(0xffffffffu, static_cast<uint32_t>(addr), owner);
+    uint32_t hi = __shfl_sync(0xffffffffu, static_cast<uint32_t>(addr >> 32), owner);
+    uint64_t* p = reinterpret_cast<uint64_t*>((static_cast<uint64_t>(hi) << 32) | lo);
+    uint32_t c = __shfl_sync(0xffffffffu, my_cnt, owner);
+    uint32_t n2 = next_pow2(c < 2 ? 2 : c);
+    __syncwarp();
+    for (uint32_t i = lane; i < n2; i += 32) {
+        sort_area[i] = i < c ? p[i] : KEY_INF;
+    }
+    warp_bitonic_sort(sort_area, n2, lane);
+    uint32_t keep = c < m ? c : m;
+    for (uint32_t i = lane; i < keep; i += 32) {
+        p[i] = sort_area[i];
+    }
+    if (lane == owner) {
+        my_cnt = keep;
+        if (c >= m) {
+            my_thr = ordered_to_float(static_cast<uint32_t>(sort_area[m - 1] >> 32));
+        }
+    }
+    __syncwarp();
+}
+
+// SMALL_M: at most four candidates per row, kept sorted in registers by the row's thread (the
+// k-means case); otherwise candidates go to per-row buffers compacted as above.
+template <bool SMALL_M>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_candidates_kernel(const TcParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ TcShared sh;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n_ops = p.n_terms == 3 ? 4u : 2u;
+    const uint32_t stage_bytes = n_ops * TC_CHUNK_BYTES;
+    const uint32_t chunks = p.a.chunks;
+    const uint64_t m_tiles = (p.a.rows + TC_BM - 1) / TC_BM;
+    const uint64_t n_tiles = (p.b.rows + TC_BN - 1) / TC_BN;
+    const uint64_t n_items = m_tiles * p.n_split;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&sh.full[s], 1);
+            mbar_init(&sh.freed[s], 1);
+        }
+        for (uint32_t a = 0; a < 2; ++a) {
+            mbar_init(&sh.acc_full[a], 1);
+            mbar_init(&sh.acc_free[a], TC_EPI_THREADS);
+        }
+        sh.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_EPI_WARPS) {
+        tmem_alloc(&sh.tmem_base, 256);  // two 128-column fp32 accumulators
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = sh.tmem_base;
+
+    if (warp == TC_EPI_WARPS) {
+        // ---------------- controller: bulk copies and MMA issue (one thread) ----------------
+        // Everything here runs on one thread, so it is written for latency: 32-bit counters that
+        // wrap by compare instead of divide, descriptors prepared once per stage.
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
+            const uint32_t n_items32 = static_cast<uint32_t>(n_items);
+            const uint32_t n_tiles32 = static_cast<uint32_t>(n_tiles);
+            // Descriptor of stage 0 / operand 0; the others differ only in the start-address field,
+            // which counts 16-byte units, so they are this value plus small constants kept in registers.
+            const uint64_t desc0 = umma_desc(smem_u32(smem), 128, 1024);
+            const uint64_t stage_units = stage_bytes >> 4;
+            const uint64_t op_units = TC_CHUNK_BYTES >> 4;
+            uint64_t stage_desc = desc0;   // descriptor of the MMA side's current stage
+            bool ok = true;
+
+            // load side: (item, tile, chunk) cursor, stage ring position and its phase
+            uint32_t l_item = blockIdx.x, l_tile = 0, l_chunk = 0, l_tiles = 0, l_mtile = 0, l_ntile0 = 0;
+            uint32_t l_stage = 0, l_phase = 0, l_count = 0;
+            auto open_item = [&](uint32_t item, uint32_t& mtile, uint32_t& ntile0, uint32_t& tiles) {
+                mtile = item / p.n_split;
+                uint32_t split = item - mtile * p.n_split;
+                ntile0 = split * p.tiles_per_split;
+                uint32_t t1 = ntile0 + p.tiles_per_split;
+                if (t1 > n_tiles32) {
+                    t1 = n_tiles32;
+                }
+                tiles = t1 > ntile0 ? t1 - ntile0 : 0;
+            };
+            if (l_item < n_items32) {
+                open_item(l_item, l_mtile, l_ntile0, l_tiles);
+            }
+            auto issue_load = [&]() -> bool {
+                while (l_item < n_items32 && l_tile >= l_tiles) {
+                    l_item += gridDim.x;
+                    l_tile = 0;
+                    l_chunk = 0;
+                    if (l_item < n_items32) {
+                        open_item(l_item, l_mtile, l_ntile0, l_tiles);
+                    }
+                }
+                if (l_item >= n_items32) {
+                    return true;
+                }
+                if (l_count >= TC_STAGES) {
+                    // the stage's previous use must have been consumed by the tensor core
+                    if (!mbar_wait(&sh.freed[l_stage], l_phase ^ 1u)) {
+                        return false;
+                    }
+                }
+                unsigned char* dst = smem + l_stage * stage_bytes;
+                const size_t a_off = (static_cast<size_t>(l_mtile) * chunks + l_chunk) * TC_CHUNK_ELEMS;
+                const size_t b_off = (static_cast<size_t>(l_ntile0 + l_tile) * chunks + l_chunk) * TC_CHUNK_ELEMS;
+                mbar_expect_tx(&sh.full[l_stage], stage_bytes);
+                if (p.n_terms == 3) {
+                    bulk_copy_g2s(dst, p.a.hi + a_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
+                    bulk_copy_g2s(dst + TC_CHUNK_BYTES, p.a.lo + a_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
+                    bulk_copy_g2s(dst + 2 * TC_CHUNK_BYTES, p.b.hi + b_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
+                    bulk_copy_g2s(dst + 3 * TC_CHUNK_BYTES, p.b.lo + b_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
+                } else {
+                    bulk_copy_g2s(dst, p.a.hi + a_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
+                    bulk_copy_g2s(dst + TC_CHUNK_BYTES, p.b.hi + b_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
+                }
+                ++l_count;
+                if (++l_stage == TC_STAGES) {
+                    l_stage = 0;
+                    l_phase ^= 1u;
+                }
+                if (++l_chunk == chunks) {
+                    l_chunk = 0;
+                    ++l_tile;
+                }
+                return true;
+            };
+
+            for (uint32_t i = 0; i + 1 < TC_STAGES && ok; ++i) {
+                ok = issue_load();
+            }
+            // MMA side: stage ring position / phase, accumulator ring position / phase
+            uint32_t m_stage = 0, m_phase = 0, acc = 0, acc_phase = 0, tiles_started = 0;
+            for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
+                uint32_t mtile, ntile0, tiles;
+                open_item(item, mtile, ntile0, tiles);
+                for (uint32_t t = 0; t < tiles && ok; ++t) {
+                    if (tiles_started >= 2) {
+                        // the epilogue must have drained this accumulator's previous tile
+                        ok = mbar_wait(&sh.acc_free[acc], acc_phase ^ 1u);
+                        if (!ok) {
+                            break;
+                        }
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + acc * TC_BN;
+                    for (uint32_t c = 0; c < chunks && ok; ++c) {
+                        ok = mbar_wait(&sh.full[m_stage], m_phase);
+                        if (!ok) {
+                            break;
+                        }
+                        tc_fence_after_sync();
+#pragma unroll
+                        for (uint32_t kk = 0; kk < TC_KC / 16; ++kk) {
+                            // a k-step of 16 elements = two 8-element cores: 256 B = 16 descriptor units
+                            const uint64_t koff = kk * 16;
+                            const uint32_t accumulate = (c == 0 && kk == 0) ? 0u : 1u;
+                            if (p.n_terms == 3) {
+                                const uint64_t a_hi = stage_desc + koff, a_lo = a_hi + op_units;
+                                const uint64_t b_hi = a_hi + 2 * op_units, b_lo = a_hi + 3 * op_units;
+                                umma_bf16(d_tmem, a_hi, b_hi, idesc, accumulate);
+                                umma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
+                                umma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
+                            } else {
+                                const uint64_t a = stage_desc + koff;
+                                umma_bf16(d_tmem, a, a + op_units, idesc, accumulate);
+                            }
+                        }
+                        umma_commit(&sh.freed[m_stage]);
+                        if (c + 1 == chunks) {
+                            umma_commit(&sh.acc_full[acc]);
+                        }
+                        stage_desc += stage_units;
+                        if (++m_stage == TC_STAGES) {
+                            m_stage = 0;
+                            m_phase ^= 1u;
+                            stage_desc = desc0;
+                        }
+                        ok = issue_load();
+                    }
+                    ++tiles_started;
+                    if (++acc == 2) {
+                        acc = 0;
+                        acc_phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                sh.failed = 1;
+                atomicExch(p.error_flag, 1);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: drain the accumulator, keep the m best per row ----------------
+        const uint32_t quarter = warp & 3u;          // TMEM lanes 32 * quarter .. + 31
+        const uint32_t cgroup = warp >> 2;           // columns 32 * cgroup .. + 31 of every tile
+        const uint32_t row = quarter * 32 + lane;
+        uint64_t* buf = p.scratch + ((static_cast<uint64_t>(blockIdx.x) * TC_BM + row) * TC_COL_GROUPS + cgroup) * p.cap;
+        uint64_t* sort_area = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(TC_STAGES) * stage_bytes) +
+                              static_cast<size_t>(warp) * p.cap;
+        uint64_t gtile = 0;
+        bool ok = true;
+        for (uint64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const uint64_t m_tile = item / p.n_split;
+            const uint64_t split = item % p.n_split;
+            const uint64_t t0 = split * p.tiles_per_split;
+            uint64_t t1 = t0 + p.tiles_per_split;
+            if (t1 > n_tiles) {
+                t1 = n_tiles;
+            }
+            const uint64_t grow = m_tile * TC_BM + row;
+            const bool valid_row = grow < p.a.rows;
+            uint32_t cnt = 0;
+            float thr = INFINITY;
+            float next_bias = (cgroup == 0 && p.bias != nullptr && t0 * TC_BN + row < p.b.rows) ? __ldg(p.bias + t0 * TC_BN + row) : 0.f;
+            // SMALL_M: the four best scores of the row, ascending, with their columns
+            float bs0 = INFINITY, bs1 = INFINITY, bs2 = INFINITY, bs3 = INFINITY;
+            const float margin = (SMALL_M && p.a_sq != nullptr && p.margin_scale != nullptr && valid_row)
+                                     ? __ldg(p.margin_scale) * sqrtf(__ldg(p.a_sq + grow))
+                                     : -1.f;
+            float bound = (margin >= 0.f && p.row_bound != nullptr) ? __ldg(p.row_bound + grow) + margin : INFINITY;
+            uint32_t bc0 = 0xFFFFFFFFu, bc1 = 0xFFFFFFFFu, bc2 = 0xFFFFFFFFu, bc3 = 0xFFFFFFFFu;
+            for (uint64_t t = t0; t < t1 && ok; ++t, ++gtile) {
+                const uint32_t acc = static_cast<uint32_t>(gtile & 1);
+                ok = mbar_wait(&sh.acc_full[acc], static_cast<uint32_t>((gtile >> 1) & 1));
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * TC_BN + cgroup * 32;
+                const uint64_t n0 = t * TC_BN;
+                const bool whole_tile = valid_row && n0 + TC_BN <= p.b.rows;
+                // bias of this tile: fetched one tile ahead into a register, shared through smem
+                if (cgroup == 0) {
+                    sh.bias[acc][row] = next_bias;
+                    const uint64_t nn = (t + 1 < t1) ? (t + 1) * TC_BN + row : p.b.rows;
+                    next_bias = (p.bias != nullptr && nn < p.b.rows) ? __ldg(p.bias + nn) : 0.f;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");   // the epilogue threads only
+                uint32_t r[32];
+                tmem_load_32(taddr, r);
+                // the accumulator is in registers now: hand it back before doing the selection
+                tc_fence_before_sync();
+                mbar_arrive(&sh.acc_free[acc]);
+
+                {
+                    const uint32_t cb = cgroup;
+                    if (!SMALL_M) {
+                        uint32_t full = __ballot_sync(0xffffffffu, cnt + 32 > p.cap);
+                        while (full != 0) {
+                            uint32_t owner = __ffs(full) - 1;
+                            tc_compact_row(buf, cnt, thr, owner, lane, p.m, sort_area);
+                            full &= full - 1;
+                        }
+                    }
+                    const uint32_t c0 = static_cast<uint32_t>(n0) + cb * 32;
+                    // Scores of the block and their minimum first (two instructions per element);
+                    // the selection code below runs only when the minimum beats the row's bound.
+                    float sc[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(&sh.bias[acc][cb * 32 + i]);
+                        const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const bool in_range = whole_tile || (valid_row && c0 + i + j < p.b.rows);
+                            sc[i + j] = in_range ? fmaf(p.alpha, __uint_as_float(r[i + j]), bb[j]) : INFINITY;
+                        }
+                    }
+                    // minimum as a tree: a serial chain of 32 dependent fminf would stall the warp
+                    float m16[16], m4[4];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        m16[i] = fminf(sc[i], sc[i + 16]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        m4[i] = fminf(fminf(m16[i], m16[i + 4]), fminf(m16[i + 8], m16[i + 12]));
+                    }
+                    const float mn = fminf(fminf(m4[0], m4[1]), fminf(m4[2], m4[3]));
+                    if (SMALL_M) {
+                        if (mn < bound) {
+                            // rare path: visit only the elements that beat the bound
+                            float tmp[32];
+                            uint32_t hits = 0;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                tmp[i] = sc[i];
+                                hits |= (sc[i] < bound ? 1u : 0u) << i;
+                            }
+                            while (hits != 0) {
+                                const uint32_t i = __ffs(hits) - 1;
+                                hits &= hits - 1;
+                                const float s = tmp[i];
+                                if (s < bs3) {
+                                    // insert into the ascending quadruple (bs0 <= bs1 <= bs2 <= bs3)
+                                    const uint32_t col = c0 + i;
+                                    if (s < bs2) {
+                                        bs3 = bs2;
+                                        bc3 = bc2;
+                                        if (s < bs1) {
+                                            bs2 = bs1;
+                                            bc2 = bc1;
+                                            if (s < bs0) {
+                                                bs1 = bs0;
+                                                bc1 = bc0;
+                                                bs0 = s;
+                                                bc0 = col;
+                                            } else {
+                                                bs1 = s;
+                                                bc1 = col;
+                                            }
+                                        } else {
+                                            bs2 = s;
+                                            bc2 = col;
+                                        }
+                                    } else {
+                                        bs3 = s;
+                                        bc3 = col;
+                                    }
+                                }
+                            }
+                            // with a margin: only columns within it of the best can still win;
+                            // without: anything better than the fourth best is kept
+                            bound = fminf(bound, margin >= 0.f ? fminf(bs3, bs0 + margin) : bs3);
+                        }
+                    } else if (mn < thr) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (sc[i] < thr) {
+                                buf[cnt++] = make_key(sc[i], c0 + i + p.col_base);
+                            }
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                break;
+            }
+            if (SMALL_M) {
+                if (valid_row) {
+                    uint64_t* dst = p.out + ((grow * p.n_split + split) * TC_COL_GROUPS + cgroup) * p.m;
+                    const float fs[4] = {bs0, bs1, bs2, bs3};
+                    const uint32_t fc[4] = {bc0, bc1, bc2, bc3};
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        if (i < p.m) {
+                            dst[i] = fc[i] == 0xFFFFFFFFu ? KEY_INF : make_key(fs[i], fc[i] + p.col_base);
+                        }
+                    }
+                }
+            } else {
+                // final order of every row of this warp, then the m best go out
+                for (uint32_t owner = 0; owner < 32; ++owner) {
+                    tc_compact_row(buf, cnt, thr, owner, lane, p.m, sort_area);
+                    const uint64_t orow = m_tile * TC_BM + quarter * 32 + owner;
+                    if (orow < p.a.rows) {
+                        uint32_t c = __shfl_sync(0xffffffffu, cnt, owner);
+                        uint64_t* dst = p.out + ((orow * p.n_split + split) * TC_COL_GROUPS + cgroup) * p.m;
+                        for (uint32_t i = lane; i < p.m; i += 32) {
+                            dst[i] = i < c ? sort_area[i] : KEY_INF;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicExch(p.error_flag, 1);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == TC_EPI_WARPS) {
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
+int
+tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
+              const float* bias_dev, uint32_t m, uint32_t col_base, DevBuf<uint64_t>& out,
+              uint32_t* n_split_out, const float* a_sq_dev, const float* margin_scale_dev,
+              const float* row_bound_dev) {
+    VB_CHECK_ARG(a.rows > 0 && b.rows > 0, "tc_candidates: empty operand");
+    VB_CHECK_ARG(a.chunks == b.chunks && a.chunks > 0, "tc_candidates: operand depths differ");
+    VB_CHECK_ARG(n_terms == 1 || n_terms == 3, "tc_candidates: 1 or 3 terms");
+    VB_CHECK_ARG(m >= 1 && m <= 480, "tc_candidates: m out of range");
+    const uint64_t m_tiles = (a.rows + TC_BM - 1) / TC_BM;
+    const uint64_t n_tiles = (b.rows + TC_BN - 1) / TC_BN;
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    uint64_t n_split = (2ull * sms + m_tiles - 1) / m_tiles;
+    if (n_split > n_tiles) {
+        n_split = n_tiles;
+    }
+    if (n_split < 1) {
+        n_split = 1;
+    }
+    uint64_t tiles_per_split = (n_tiles + n_split - 1) / n_split;
+    n_split = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+    const uint64_t items = m_tiles * n_split;
+    const uint32_t grid = static_cast<uint32_t>(items < sms ? items : sms);
+
+    TcParams p{};
+    p.a = a;
+    p.b = b;
+    p.n_terms = n_terms;
+    p.alpha = alpha;
+    p.bias = bias_dev;
+    p.a_sq = a_sq_dev;
+    p.margin_scale = margin_scale_dev;
+    p.row_bound = row_bound_dev;
+    p.m = m;
+    p.cap = next_pow2(m + 32 < 64 ? 64 : m + 32);
+    p.n_split = static_cast<uint32_t>(n_split);
+    p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
+    p.col_base = col_base;
+    VB_TRY(ws.scratch.reserve(static_cast<size_t>(grid) * TC_BM * TC_COL_GROUPS * p.cap));
+    VB_TRY(ws.error_flag.reserve(1));
+    VB_TRY(out.reserve(static_cast<size_t>(a.rows) * n_split * TC_COL_GROUPS * m));
+    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
+    p.scratch = ws.scratch.ptr;
+    p.out = out.ptr;
+    p.error_flag = ws.error_flag.ptr;
+
+    const bool small_m = m <= 4;
+    const size_t smem = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES +
+                        (small_m ? 0 : TC_EPI_WARPS * static_cast<size_t>(p.cap) * sizeof(uint64_t)) + 1024;
+    auto kernel = small_m ? tc_candidates_kernel<true> : tc_candidates_kernel<false>;
+    VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
+    int flag = 0;
+    VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
+    VB_TRY(sync_stream());
+    if (flag != 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
+    }
+    *n_split_out = static_cast<uint32_t>(n_split) * TC_COL_GROUPS;
+    return 0;
+}
+
+}  // namespace vb200

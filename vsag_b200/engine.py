@@ -49,6 +49,11 @@ def kernel_launches() -> int:
     return int(_capi.load().vb200_kernel_launches())
 
 
+def set_tensor_cores(enable: bool) -> None:
+    """Tensor-core candidate kernels (default) or the fixed-order SIMT kernels."""
+    check(_capi.load().vb200_set_tensor_cores(int(bool(enable))))
+
+
 def set_stream(stream_handle: int | None) -> None:
     check(_capi.load().vb200_set_stream(C.c_void_p(stream_handle or 0)))
 
