@@ -87,3 +87,42 @@ def test_row_sharded_search_equals_unsharded(engine, oracle):
         parts.append(s)
     got = engine.merge_partials(keys, labels, world, nq, k)
     assert_topk_equal(got[0], got[1], want[0], want[1], rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("metric,quant,n,dim,nq,k", [
+    (0, "fp32", 100_000, 128, 1000, 10),
+    (1, "fp32", 120_077, 100, 1000, 40),
+    (1, "bf16", 150_001, 96, 1000, 100),
+    (0, "bf16", 100_000, 128, 900, 10),
+])
+def test_tensor_core_candidates_equal_simt_path(engine, oracle, metric, quant, n, dim, nq, k):
+    """Large searches nominate candidates with the tcgen05 kernel; after the exact re-scoring the
+    results must be the ones the fixed-order SIMT path gives, and match the oracle."""
+    base = mixture(11, n, dim, 64, 0.25)
+    q = mixture(12, nq, dim, 64, 0.25)
+    ids = np.arange(n, dtype=np.int64) * 3 + 1
+    ix = engine.BfHandle(dim, metric, engine.QUANT_FP32 if quant == "fp32" else engine.QUANT_BF16)
+    ix.add(base[:70_000], ids[:70_000])
+    ix.add(base[70_000:], ids[70_000:])
+    try:
+        engine.set_tensor_cores(True)
+        before = engine.kernel_launches()
+        got_i, got_d = ix.search(q, k)
+        tc_launches = engine.kernel_launches() - before
+        engine.set_tensor_cores(False)
+        before = engine.kernel_launches()
+        want_i, want_d = ix.search(q, k)
+        simt_launches = engine.kernel_launches() - before
+    finally:
+        engine.set_tensor_cores(True)
+    assert tc_launches > 0 and tc_launches != simt_launches  # two different kernel sequences ran
+    assert np.array_equal(got_d, want_d)
+    assert_topk_equal(got_i, got_d, want_i, want_d, rtol=0, atol=0)
+    sub = slice(0, 32)
+    if quant == "fp32":
+        o_i, o_d = oracle.bf_search_fp32(base, q[sub], k, metric)
+    else:
+        o_i, o_d = oracle.bf_search_bf16(oracle.float_to_bf16(base), q[sub], k, metric=metric)
+    o_i = np.where(o_i >= 0, o_i * 3 + 1, -1)
+    assert np.array_equal(got_d[sub], o_d)
+    assert_topk_equal(got_i[sub], got_d[sub], o_i, o_d, rtol=0, atol=0)

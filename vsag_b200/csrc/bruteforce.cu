@@ -1,6 +1,8 @@
 // Exact BruteForce kNN over fp32 or bf16 rows: dense score slabs select a few candidates more
 // than k per query, which are then re-scored in the reference's arithmetic and ordered.
 #include "dense.cuh"
+#include "kmeans.cuh"
+#include "tc_gemm.cuh"
 
 namespace vb200 {
 
@@ -126,6 +128,11 @@ struct vb200_bf {
     DevBuf<float> q_f32, scores;
     DevBuf<uint16_t> q_bf16;
     DevBuf<uint64_t> part, cand, keys;
+    // tensor-core path: the base (and per search the queries) as tiled bf16 terms
+    DevBuf<uint16_t> base_hi, base_lo, q_hi, q_lo;
+    bool tiled_valid = false;
+    DevBuf<uint64_t> tc_out;
+    TcWorkspace tc;
     DevBuf<int64_t> out_ids;
     DevBuf<float> out_dists;
     std::mutex mu;
@@ -192,6 +199,7 @@ bf_append_labels_and_norms(vb200_bf* ix, const int64_t* ids, uint64_t count) {
     }
     VB_TRY(sync_stream());
     ix->n += count;
+    ix->tiled_valid = false;
     return 0;
 }
 
@@ -267,6 +275,52 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
         VB_TRY(ix->q_bf16.reserve(nq * dim));
         VB_LAUNCH(float_to_bf16_kernel, static_cast<uint32_t>((nq * dim + 255) / 256), 256, 0, q_dev,
                   nq * dim, ix->q_bf16.ptr);
+    }
+    // Large problems nominate candidates on the tensor cores; the exact re-scoring below is the
+    // same either way.
+    if (tensor_cores_enabled() && kcand <= tc_max_candidates(bf16 ? 1 : 3) && static_cast<double>(nq) * n * dim >= 1e10) {
+        const uint32_t chunks = (dim + TC_KC - 1) / TC_KC;
+        if (!ix->tiled_valid) {
+            const size_t elems = tc_tiled_elems(n, dim);
+            VB_TRY(ix->base_hi.reserve(elems));
+            if (bf16) {
+                VB_TRY(tc_pretile_bf16(ix->base_bf16.ptr, n, dim, ix->base_hi.ptr));
+            } else {
+                VB_TRY(ix->base_lo.reserve(elems));
+                VB_TRY(tc_pretile_f32(ix->base_f32.ptr, n, dim, ix->base_hi.ptr, ix->base_lo.ptr));
+            }
+            ix->tiled_valid = true;
+        }
+        const size_t q_elems = tc_tiled_elems(nq, dim);
+        VB_TRY(ix->q_hi.reserve(q_elems));
+        if (bf16) {
+            VB_TRY(tc_pretile_bf16(ix->q_bf16.ptr, nq, dim, ix->q_hi.ptr));
+        } else {
+            VB_TRY(ix->q_lo.reserve(q_elems));
+            VB_TRY(tc_pretile_f32(q_dev, nq, dim, ix->q_hi.ptr, ix->q_lo.ptr));
+        }
+        TcOperand a{ix->q_hi.ptr, bf16 ? nullptr : ix->q_lo.ptr, nq, chunks};
+        TcOperand b{ix->base_hi.ptr, bf16 ? nullptr : ix->base_lo.ptr, n, chunks};
+        uint32_t lists = 1;
+        VB_TRY(tc_candidates(ix->tc, a, b, bf16 ? 1 : 3, l2 ? -2.0f : -1.0f, l2 ? ix->norms.ptr : nullptr, kcand, 0,
+                             ix->tc_out, &lists));
+        VB_TRY(ix->cand.reserve(nq * kcand));
+        {
+            uint32_t cap = next_pow2(kcand + 256);
+            size_t smem = cap * sizeof(uint64_t) + 16;
+            VB_LAUNCH(bf_merge_kernel, static_cast<uint32_t>(nq), 256, smem, ix->tc_out.ptr,
+                      static_cast<uint64_t>(lists) * kcand, kcand, cap, ix->cand.ptr);
+        }
+        VB_TRY(ix->keys.reserve(nq * k));
+        uint32_t n2 = next_pow2(kcand < 2 ? 2 : kcand);
+        if (bf16) {
+            VB_LAUNCH(bf_rescore_kernel<uint16_t>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t),
+                      ix->q_bf16.ptr, dim, ix->base_bf16.ptr, ix->cand.ptr, kcand, n2, k, ix->metric, ix->keys.ptr);
+        } else {
+            VB_LAUNCH(bf_rescore_kernel<float>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev, dim,
+                      ix->base_f32.ptr, ix->cand.ptr, kcand, n2, k, ix->metric, ix->keys.ptr);
+        }
+        return 0;
     }
     const uint64_t col_chunk = n < BF_COL_CHUNK ? n : BF_COL_CHUNK;
     const uint32_t nchunks = static_cast<uint32_t>((n + col_chunk - 1) / col_chunk);

@@ -109,7 +109,7 @@ struct TcShared {
     uint64_t acc_free[2];        // accumulator drained by the 128 epilogue threads
     uint32_t tmem_base;
     uint32_t failed;
-    alignas(16) float bias[2][TC_BN];   // bias of the tile in each accumulator (read as float4)
+    alignas(16) float bias[TC_EPI_WARPS][32];   // each epilogue warp's 32 bias values of its current tile
 };
 
 // Warp-cooperative: sort row `owner`'s buffer, keep its m best, tighten its threshold.  The row's
@@ -340,7 +340,14 @@ tc_candidates_kernel(const TcParams p) {
             const bool valid_row = grow < p.a.rows;
             uint32_t cnt = 0;
             float thr = INFINITY;
-            float next_bias = (cgroup == 0 && p.bias != nullptr && t0 * TC_BN + row < p.b.rows) ? __ldg(p.bias + t0 * TC_BN + row) : 0.f;
+            // bias of the warp's 32 columns: fetched one tile ahead into a register (lane = column),
+            // handed to the other lanes through the warp's own shared-memory slot
+            const bool has_bias = p.bias != nullptr;
+            float next_bias = 0.f;
+            if (has_bias) {
+                const uint64_t nn = t0 * TC_BN + cgroup * 32 + lane;
+                next_bias = (t0 < t1 && nn < p.b.rows) ? __ldg(p.bias + nn) : 0.f;
+            }
             // SMALL_M: the four best scores of the row, ascending, with their columns
             float bs0 = INFINITY, bs1 = INFINITY, bs2 = INFINITY, bs3 = INFINITY;
             const float margin = (SMALL_M && p.a_sq != nullptr && p.margin_scale != nullptr && valid_row)
@@ -359,13 +366,13 @@ tc_candidates_kernel(const TcParams p) {
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * TC_BN + cgroup * 32;
                 const uint64_t n0 = t * TC_BN;
                 const bool whole_tile = valid_row && n0 + TC_BN <= p.b.rows;
-                // bias of this tile: fetched one tile ahead into a register, shared through smem
-                if (cgroup == 0) {
-                    sh.bias[acc][row] = next_bias;
-                    const uint64_t nn = (t + 1 < t1) ? (t + 1) * TC_BN + row : p.b.rows;
-                    next_bias = (p.bias != nullptr && nn < p.b.rows) ? __ldg(p.bias + nn) : 0.f;
+                if (has_bias) {
+                    __syncwarp();
+                    sh.bias[warp][lane] = next_bias;
+                    const uint64_t nn = (t + 1 < t1) ? (t + 1) * TC_BN + cgroup * 32 + lane : p.b.rows;
+                    next_bias = nn < p.b.rows ? __ldg(p.bias + nn) : 0.f;
+                    __syncwarp();
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");   // the epilogue threads only
                 uint32_t r[32];
                 tmem_load_32(taddr, r);
                 // the accumulator is in registers now: hand it back before doing the selection
@@ -388,7 +395,8 @@ tc_candidates_kernel(const TcParams p) {
                     float sc[32];
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        const float4 b4 = *reinterpret_cast<const float4*>(&sh.bias[acc][cb * 32 + i]);
+                        const float4 b4 = has_bias ? *reinterpret_cast<const float4*>(&sh.bias[warp][i])
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
                         const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -454,10 +462,16 @@ tc_candidates_kernel(const TcParams p) {
                             bound = fminf(bound, margin >= 0.f ? fminf(bs3, bs0 + margin) : bs3);
                         }
                     } else if (mn < thr) {
+                        // few elements pass: test them in pairs through the first level of the tree
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (sc[i] < thr) {
-                                buf[cnt++] = make_key(sc[i], c0 + i + p.col_base);
+                        for (int i = 0; i < 16; ++i) {
+                            if (m16[i] < thr) {
+                                if (sc[i] < thr) {
+                                    buf[cnt++] = make_key(sc[i], c0 + i + p.col_base);
+                                }
+                                if (sc[i + 16] < thr) {
+                                    buf[cnt++] = make_key(sc[i + 16], c0 + i + 16 + p.col_base);
+                                }
                             }
                         }
                     }
@@ -506,6 +520,23 @@ tc_candidates_kernel(const TcParams p) {
     }
 }
 
+// Largest per-row candidate buffer whose per-warp sort areas fit in shared memory beside the stages.
+static uint32_t
+tc_cap_max(uint32_t n_terms) {
+    const size_t stage_total = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES;
+    const size_t room = 232448 - 4096 - stage_total;
+    uint32_t cap_max = 64;
+    while (static_cast<size_t>(cap_max) * 2 * TC_EPI_WARPS * sizeof(uint64_t) <= room && cap_max < 1024) {
+        cap_max *= 2;
+    }
+    return cap_max;
+}
+
+uint32_t
+tc_max_candidates(uint32_t n_terms) {
+    return tc_cap_max(n_terms) - 32;
+}
+
 int
 tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
               const float* bias_dev, uint32_t m, uint32_t col_base, DevBuf<uint64_t>& out,
@@ -540,7 +571,17 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     p.margin_scale = margin_scale_dev;
     p.row_bound = row_bound_dev;
     p.m = m;
-    p.cap = next_pow2(m + 32 < 64 ? 64 : m + 32);
+    // Per-row candidate buffers: a few times m so compactions are rare, within what the per-warp
+    // shared-memory sort areas can hold next to the operand stages.
+    {
+        const uint32_t cap_max = tc_cap_max(n_terms);
+        uint32_t cap = next_pow2(4 * m < 64 ? 64 : 4 * m);
+        if (cap > cap_max) {
+            cap = cap_max;
+        }
+        VB_CHECK_ARG(m <= 4 || m + 32 <= cap, "tc_candidates: m = %u too large for the shared-memory sort area", m);
+        p.cap = cap;
+    }
     p.n_split = static_cast<uint32_t>(n_split);
     p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
     p.col_base = col_base;

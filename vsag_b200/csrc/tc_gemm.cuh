@@ -218,4 +218,7 @@ int tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint3
                   uint32_t* n_split_out, const float* a_sq_dev = nullptr,
                   const float* margin_scale_dev = nullptr, const float* row_bound_dev = nullptr);
 
+// Largest m tc_candidates accepts for the given number of terms.
+uint32_t tc_max_candidates(uint32_t n_terms);
+
 }  // namespace vb200
