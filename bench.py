@@ -165,7 +165,10 @@ def build_index(engine, base, nlist: int, rank: int, world: int, dist):
         # a strided sample stands in for the reference's reservoir sample of the same size
         stride = max(1, base.shape[0] // train_rows)
         sample = base[::stride][:train_rows].contiguous()
-        trainer.train(sample, iters=env_int("VB200_BENCH_KMEANS_ITERS", KMEANS_ITERS))
+        # k-means++ seeding as KMeansCluster::Run does by default, then the Lloyd iterations
+        seeds = engine.kmeans_init(sample, nlist, seed=47)
+        trainer.train(sample, iters=env_int("VB200_BENCH_KMEANS_ITERS", KMEANS_ITERS), init=seeds)
+        del seeds
         centroids.copy_(torch.from_numpy(trainer.get_centroids()))
         lower, diff = trainer.get_sq8_model()
         model[0].copy_(torch.from_numpy(lower))

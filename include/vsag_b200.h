@@ -130,6 +130,15 @@ VB200_API int vb200_kmeans_update(const float* data, uint64_t count, uint32_t di
 VB200_API int vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, int iters,
                        float* centroids, int32_t* labels, double* mean_err);
 
+/* k-means++ seeding: centroids[k x dim] = k rows of data drawn as
+ * KMeansCluster::select_initial_centroids_kmeans_plus_plus does (kmeans_cluster.cpp:383-435): the
+ * first uniformly, each later one with probability proportional to its squared distance from the
+ * nearest centre chosen so far.  The draws come from std::mt19937(seed) through the same standard
+ * distributions; the reference seeds that generator from std::random_device (kmeans_cluster.cpp:75),
+ * here the caller does.  picked[k] (optional) receives the chosen row numbers. */
+VB200_API int vb200_kmeans_init(const float* data, uint64_t count, uint32_t dim, uint32_t k, uint32_t seed,
+                      float* centroids, int64_t* picked);
+
 /* Same labels as vb200_kmeans_assign, for callers that must not allocate.  No counterpart in the
  * reference: it exists for hosts where reaching the CUDA allocator is not an option (a serving
  * thread with a fixed device-memory budget, or one that cannot take the device-wide

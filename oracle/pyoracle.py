@@ -210,6 +210,33 @@ def kmeans_update(x, labels, k: int, it: int = 0):
     return centroids, counts
 
 
+def kmeans_pp_init(x, k: int, seed: int):
+    """k-means++ seeding with a seeded generator: (centroids [k, d], picked rows [k])."""
+    x, px = _a(x, np.float32)
+    n, d = x.shape
+    centroids = np.empty((k, d), np.float32)
+    picked = np.empty(k, np.int64)
+    lib().orc_kmeans_pp_init(px, _u64(n), _u64(d), _u64(k), _u32(seed), _p(centroids.ctypes.data),
+                             _p(picked.ctypes.data))
+    return centroids, picked
+
+
+def std_draws(seed: int, n: int, count: int, restated: bool):
+    """count (index, real) pairs from the restated draws or from the C++ library itself."""
+    ints = np.empty(count, np.uint64)
+    reals = np.empty(count, np.float64)
+    if restated:
+        fn = lib().orc_std_draws
+    else:
+        so = HERE / "libstd_draws.so"
+        if not so.exists():
+            build()
+        fn = C.CDLL(os.fspath(so)).std_draws
+    fn.restype = None
+    fn(_u32(seed), _u64(n), _u64(count), _p(ints.ctypes.data), _p(reals.ctypes.data))
+    return ints, reals
+
+
 def kmeans_run(x, init, iters: int, per_iter: bool = False):
     x, px = _a(x, np.float32)
     n, d = x.shape

@@ -418,6 +418,105 @@ orc_kmeans_run(const float* x,
     return err;
 }
 
+/* libstdc++ std::uniform_int_distribution<uint64_t>(0, n - 1) over mt19937 for n <= 2^32: the
+ * generator's range covers the request, so one 32-bit draw is scaled by the multiply-and-reject
+ * method of Lemire ("Fast random integer generation in an interval", 2019). */
+static uint64_t
+mt_uniform_index(orc_mt19937* s, uint64_t n) {
+    uint32_t range = (uint32_t)n; /* n == 2^32 wraps to 0: every draw is accepted as it is */
+    if (n >= 4294967296ull) {
+        return mt_next(s);
+    }
+    uint64_t product = (uint64_t)mt_next(s) * range;
+    uint32_t low = (uint32_t)product;
+    if (low < range) {
+        uint32_t threshold = (uint32_t)(0u - range) % range;
+        while (low < threshold) {
+            product = (uint64_t)mt_next(s) * range;
+            low = (uint32_t)product;
+        }
+    }
+    return product >> 32;
+}
+
+/* libstdc++ std::uniform_real_distribution<double>(0, hi) over mt19937:
+ * generate_canonical<double,53> takes two 32-bit draws, low word first, sums them in double
+ * (rounding the 64-bit value to 53 bits), divides by 2^64 and replaces 1.0 by the double below. */
+static double
+mt_uniform_double(orc_mt19937* s, double hi) {
+    double sum = (double)mt_next(s);
+    sum += (double)mt_next(s) * 4294967296.0;
+    double r = sum / 18446744073709551616.0;
+    if (r >= 1.0) {
+        r = nextafter(1.0, 0.0);
+    }
+    return hi * r + 0.0;
+}
+
+/* Draws exported so a test can hold them against the C++ library itself. */
+ORC_API void
+orc_std_draws(uint32_t seed, uint64_t n, uint64_t count, uint64_t* ints, double* reals) {
+    orc_mt19937 s;
+    mt_seed(&s, seed);
+    for (uint64_t i = 0; i < count; ++i) {
+        ints[i] = mt_uniform_index(&s, n);
+        reals[i] = mt_uniform_double(&s, (double)(i + 1) * 1.5);
+    }
+}
+
+/* KMeansCluster::select_initial_centroids_kmeans_plus_plus (kmeans_cluster.cpp:383-435) with the
+ * generator seeded by the caller instead of std::random_device (:75-76): the first centre is a
+ * uniform draw; every later one is the first row whose running sum of min squared distances
+ * reaches a uniform draw from [0, total).  picked, when not NULL, receives the k row numbers. */
+ORC_API void
+orc_kmeans_pp_init(const float* x, uint64_t n, uint64_t dim, uint64_t k, uint32_t seed, float* centroids,
+                   int64_t* picked) {
+    orc_mt19937 s;
+    mt_seed(&s, seed);
+    float* min_d = (float*)malloc(n * sizeof(float));
+    for (uint64_t i = 0; i < n; ++i) {
+        min_d[i] = FLT_MAX;
+    }
+    uint64_t idx = mt_uniform_index(&s, n);
+    memcpy(centroids, x + idx * dim, dim * sizeof(float));
+    if (picked != NULL) {
+        picked[0] = (int64_t)idx;
+    }
+    for (uint64_t c = 1; c < k; ++c) {
+        const float* last = centroids + (c - 1) * dim;
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < (int64_t)n; ++i) {
+            float d = orc_fp32_l2sqr(x + (uint64_t)i * dim, last, dim);
+            if (d < min_d[i]) {
+                min_d[i] = d;
+            }
+        }
+        double total = 0.0;
+        for (uint64_t i = 0; i < n; ++i) {
+            total += min_d[i];
+        }
+        if (total <= 0.0) {
+            idx = mt_uniform_index(&s, n);
+        } else {
+            double threshold = mt_uniform_double(&s, total);
+            double cumulative = 0.0;
+            idx = n - 1;
+            for (uint64_t i = 0; i < n; ++i) {
+                cumulative += min_d[i];
+                if (cumulative >= threshold) {
+                    idx = i;
+                    break;
+                }
+            }
+        }
+        memcpy(centroids + c * dim, x + idx * dim, dim * sizeof(float));
+        if (picked != NULL) {
+            picked[c] = (int64_t)idx;
+        }
+    }
+    free(min_d);
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* Bounded top-k with the reference's heap semantics                                           */
 /* ------------------------------------------------------------------------------------------ */

@@ -118,3 +118,27 @@ def test_kmeans_argument_errors(engine):
     x = np.zeros((4, 3), np.float32)
     with pytest.raises(engine.VsagB200Error, match="k cannot be larger than count"):
         engine.kmeans_train(x, np.zeros((5, 3), np.float32), 1)
+
+
+@pytest.mark.parametrize("n,dim,k,seed", [(20_000, 32, 64, 47), (5_000, 100, 200, 1), (1025, 7, 33, 9)])
+def test_kmeans_pp_seeding_matches_oracle(engine, oracle, n, dim, k, seed):
+    x = mixture(seed, n, dim, 16, 0.2)
+    want_c, want_rows = oracle.kmeans_pp_init(x, k, seed)
+    got_c, got_rows = engine.kmeans_init(x, k, seed, want_rows=True)
+    # the running sums are added in another order on the device: a pick can differ only where
+    # the draw falls within rounding of a boundary, which these seeds do not hit
+    assert np.array_equal(got_rows, want_rows)
+    assert np.array_equal(got_c, want_c)
+    import torch
+
+    dev_c = engine.kmeans_init(torch.from_numpy(x).cuda(), k, seed)
+    assert np.array_equal(dev_c.cpu().numpy(), want_c)
+
+
+def test_kmeans_pp_seeding_with_coinciding_rows(engine, oracle):
+    x = np.repeat(np.arange(3, dtype=np.float32)[:, None], 4, axis=1)[np.arange(300) % 3]
+    want_c, want_rows = oracle.kmeans_pp_init(x, 10, 5)
+    got_c, got_rows = engine.kmeans_init(x, 10, 5, want_rows=True)
+    assert np.array_equal(got_rows, want_rows) and np.array_equal(got_c, want_c)
+    with pytest.raises(engine.VsagB200Error):
+        engine.kmeans_init(x[:5], 6)

@@ -7,6 +7,8 @@ from pathlib import Path
 import numpy as np
 import pytest
 
+from conftest import mixture
+
 GOLDEN = Path(__file__).resolve().parent / "golden" / "ref_simd_golden.npz"
 
 
@@ -178,3 +180,28 @@ def test_empty_and_ragged_lists(oracle):
     n1 = int((off[1] - off[0]) + (off[2] - off[1]))
     assert np.sum(ids[1] >= 0) == n1
     assert np.all(np.diff(dists[1][: n1]) >= 0)
+
+
+@pytest.mark.parametrize("n", [1, 7, 1000, 100_000, 2**31 + 5, 2**32])
+def test_restated_draws_match_cxx_library(oracle, n):
+    """k-means++ draws through std::uniform_int_distribution<uint64_t> and
+    std::uniform_real_distribution<double> over std::mt19937 (kmeans_cluster.cpp:388-417); the C
+    restatement of those two must give the library's own values."""
+    want = oracle.std_draws(47, n, 3000, restated=False)
+    got = oracle.std_draws(47, n, 3000, restated=True)
+    assert np.array_equal(got[0], want[0])
+    assert np.array_equal(got[1], want[1])
+
+
+def test_kmeans_pp_seeding_properties(oracle):
+    x = mixture(5, 4000, 16, 8, 0.05)
+    centroids, picked = oracle.kmeans_pp_init(x, 8, seed=47)
+    assert np.array_equal(centroids, x[picked])
+    assert picked[0] == oracle.std_draws(47, 4000, 1, restated=False)[0][0]
+    # eight well-separated clusters: the squared-distance weighting reaches all of them
+    truth = np.argmin(((x[picked][:, None, :] - x[None, :, :]) ** 2).sum(-1), axis=0)
+    assert len(np.unique(truth)) == 8
+    # every row identical: total weight 0 after the first pick, later picks are uniform draws
+    flat = np.ones((50, 4), np.float32)
+    c2, p2 = oracle.kmeans_pp_init(flat, 5, seed=3)
+    assert np.all(c2 == 1.0) and np.all((p2 >= 0) & (p2 < 50))

@@ -27,6 +27,7 @@ SIGNATURES = {
     "vb200_sq8_encode": (c_int, [c_void_p, c_u64, c_u32, c_void_p, c_void_p, c_void_p]),
     "vb200_kmeans_assign": (c_int, [c_void_p, c_u64, c_u32, c_void_p, c_u32, c_void_p, c_void_p]),
     "vb200_kmeans_update": (c_int, [c_void_p, c_u64, c_u32, c_void_p, c_u32, c_u32, c_void_p, c_void_p]),
+    "vb200_kmeans_init": (c_int, [c_void_p, c_u64, c_u32, c_u32, c_u32, c_void_p, c_void_p]),
     "vb200_kmeans_train": (c_int, [c_void_p, c_u64, c_u32, c_u32, c_int, c_void_p, c_void_p, c_void_p]),
     "vb200_kmeans_assign_noalloc": (c_int, [c_void_p, c_u64, c_u32, c_void_p, c_u32, c_void_p]),
     "vb200_rabitq_code_size": (c_u64, [c_u32]),

@@ -2,6 +2,8 @@
 // dense kernel with a fused argmin epilogue, and the centroid update.
 #include "kmeans.cuh"
 
+#include <random>
+
 #include <cstdlib>
 
 #include "dense.cuh"
@@ -385,6 +387,260 @@ vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, 
     VB_TRY(copy_out(centroids, c.ptr, kd));
     if (labels != nullptr && iters > 0) {
         VB_TRY(copy_out(labels, lab.ptr, count));
+    }
+    return sync_stream();
+}
+
+// ---------------------------------------------------------------------------------------------
+// k-means++ seeding (KMeansCluster::select_initial_centroids_kmeans_plus_plus,
+// src/impl/cluster/kmeans_cluster.cpp:383-435)
+// ---------------------------------------------------------------------------------------------
+namespace vb200 {
+
+constexpr uint32_t KPP_BLOCK_ROWS = 1024;   // rows per CTA of the update kernel = one partial sum
+
+// min_d[i] = min(min_d[i], |x_i - c|^2) with the reference's per-row chain (difference, then one
+// FMA per dimension in ascending order); part[b] = sum of the CTA's rows in double.  A warp
+// stages 32 rows x 32 dimensions through shared memory so the global reads stay coalesced while
+// every lane still walks its own row in order.
+__global__ void __launch_bounds__(256)
+kpp_update_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, const float* __restrict__ centroid,
+                  float* __restrict__ min_d, double* __restrict__ part) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* c = reinterpret_cast<float*>(smem_raw);                       // dim
+    float* tiles = c + ((dim + 31) / 32) * 32;                            // 8 warps x 32 x 33
+    __shared__ double warp_sum[8];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        c[d] = centroid[d];
+    }
+    __syncthreads();
+    float* tile = tiles + warp * (32 * 33);
+    double acc = 0.0;
+    const uint64_t block_row0 = static_cast<uint64_t>(blockIdx.x) * KPP_BLOCK_ROWS;
+    for (uint32_t pass = 0; pass < KPP_BLOCK_ROWS / 256; ++pass) {
+        const uint64_t row0 = block_row0 + (pass * 8 + warp) * 32;
+        if (row0 >= n) {
+            break;
+        }
+        float s = 0.f;
+        for (uint32_t d0 = 0; d0 < dim; d0 += 32) {
+            __syncwarp();
+            for (uint32_t r = 0; r < 32; ++r) {
+                const uint64_t row = row0 + r;
+                const uint32_t d = d0 + lane;
+                tile[r * 33 + lane] = (row < n && d < dim) ? __ldg(x + row * dim + d) : 0.f;
+            }
+            __syncwarp();
+            const uint32_t lim = dim - d0 < 32 ? dim - d0 : 32;
+            for (uint32_t j = 0; j < lim; ++j) {
+                const float t = __fsub_rn(tile[lane * 33 + j], c[d0 + j]);
+                s = fmaf(t, t, s);
+            }
+        }
+        const uint64_t row = row0 + lane;
+        if (row < n) {
+            const float old = min_d[row];
+            const float m = s < old ? s : old;
+            min_d[row] = m;
+            acc += static_cast<double>(m);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    }
+    if (lane == 0) {
+        warp_sum[warp] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 8; ++w) {
+            t += warp_sum[w];
+        }
+        part[blockIdx.x] = t;
+    }
+}
+
+// One CTA: total of the partial sums; threshold = total * u (the uniform draw from [0, total));
+// the first row whose running sum reaches it becomes centroid `slot`.  With total <= 0 (every row
+// coincides with a chosen centre) nothing is picked and the round is recorded in state[0]; the
+// host then finishes the seeding with uniform draws as the reference does.
+__global__ void __launch_bounds__(1024)
+kpp_pick_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, const float* __restrict__ min_d,
+                const double* __restrict__ part, uint32_t n_part, double u, uint32_t slot,
+                float* __restrict__ centroids, int64_t* __restrict__ picked, uint32_t* __restrict__ state) {
+    __shared__ double sh_scan[1024];
+    __shared__ double sh_base;
+    __shared__ uint32_t sh_block;
+    __shared__ unsigned long long sh_row;
+    const uint32_t t = threadIdx.x;
+    // inclusive scan of the partial sums, each thread owning a contiguous run
+    const uint32_t per = (n_part + 1023) / 1024;
+    const uint32_t p0 = t * per;
+    double local = 0.0;
+    for (uint32_t i = p0; i < p0 + per && i < n_part; ++i) {
+        local += part[i];
+    }
+    sh_scan[t] = local;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024; off <<= 1) {
+        double v = t >= off ? sh_scan[t - off] : 0.0;
+        __syncthreads();
+        sh_scan[t] += v;
+        __syncthreads();
+    }
+    const double total = sh_scan[1023];
+    if (!(total > 0.0)) {
+        if (t == 0) {
+            atomicMin(state, slot);
+        }
+        return;
+    }
+    const double thr = total * u + 0.0;
+    if (t == 0) {
+        sh_block = 0xFFFFFFFFu;
+        sh_row = ~0ull;
+    }
+    __syncthreads();
+    // first run, then first partial sum inside it, whose inclusive sum reaches the threshold
+    const double before = t > 0 ? sh_scan[t - 1] : 0.0;
+    if (sh_scan[t] >= thr && !(before >= thr) && p0 < n_part) {
+        const uint32_t last = p0 + per - 1 < n_part ? p0 + per - 1 : n_part - 1;
+        double run = before;
+        for (uint32_t i = p0; i <= last; ++i) {
+            const double next = run + part[i];
+            if (next >= thr || i == last) {
+                sh_block = i;
+                sh_base = run;
+                break;
+            }
+            run = next;
+        }
+    }
+    __syncthreads();
+    uint64_t row_pick = n - 1;   // the reference's default when the running sum never gets there
+    if (sh_block != 0xFFFFFFFFu) {
+        const uint64_t row0 = static_cast<uint64_t>(sh_block) * KPP_BLOCK_ROWS;
+        const uint64_t row = row0 + t;
+        const double base = sh_base;
+        __syncthreads();
+        sh_scan[t] = row < n ? static_cast<double>(min_d[row]) : 0.0;
+        __syncthreads();
+        for (uint32_t off = 1; off < 1024; off <<= 1) {
+            double v = t >= off ? sh_scan[t - off] : 0.0;
+            __syncthreads();
+            sh_scan[t] += v;
+            __syncthreads();
+        }
+        if (row < n && base + sh_scan[t] >= thr) {
+            atomicMin(&sh_row, static_cast<unsigned long long>(row));
+        }
+        __syncthreads();
+        if (sh_row != ~0ull) {
+            row_pick = sh_row;
+        } else {
+            // rounding kept the CTA's own running sum just below the threshold: its last row
+            const uint64_t last = row0 + KPP_BLOCK_ROWS - 1;
+            row_pick = last < n ? last : n - 1;
+        }
+    }
+    for (uint32_t d = t; d < dim; d += blockDim.x) {
+        centroids[static_cast<uint64_t>(slot) * dim + d] = x[row_pick * dim + d];
+    }
+    if (t == 0 && picked != nullptr) {
+        picked[slot] = static_cast<int64_t>(row_pick);
+    }
+}
+
+__global__ void
+kpp_fill_kernel(float* __restrict__ min_d, uint64_t n, uint32_t* __restrict__ state) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        min_d[i] = 3.402823466e+38f;
+    }
+    if (i == 0) {
+        state[0] = 0xFFFFFFFFu;
+    }
+}
+
+__global__ void
+kpp_copy_row_kernel(const float* __restrict__ x, uint64_t row, uint32_t dim, uint32_t slot,
+                    float* __restrict__ centroids, int64_t* __restrict__ picked) {
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        centroids[static_cast<uint64_t>(slot) * dim + d] = x[row * dim + d];
+    }
+    if (threadIdx.x == 0 && picked != nullptr) {
+        picked[slot] = static_cast<int64_t>(row);
+    }
+}
+
+// centroids_dev[k x dim] and (optionally) picked_dev[k] on the device.  The generator and its
+// distributions are the C++ library's, exactly the objects the reference draws from; only the
+// seed is the caller's (the reference takes it from std::random_device).
+int
+kmeans_pp_init_device(const float* x_dev, uint64_t n, uint32_t dim, uint32_t k, uint32_t seed,
+                      float* centroids_dev, int64_t* picked_dev) {
+    VB_CHECK_ARG(n > 0 && k > 0 && k <= n, "k cannot be larger than count");
+    const uint32_t n_part = static_cast<uint32_t>((n + KPP_BLOCK_ROWS - 1) / KPP_BLOCK_ROWS);
+    DevBuf<float> min_d;
+    DevBuf<double> part;
+    DevBuf<uint32_t> state;
+    VB_TRY(min_d.reserve(n));
+    VB_TRY(part.reserve(n_part));
+    VB_TRY(state.reserve(1));
+    VB_LAUNCH(kpp_fill_kernel, static_cast<uint32_t>((n + 255) / 256), 256, 0, min_d.ptr, n, state.ptr);
+    std::mt19937 gen(seed);
+    std::uniform_int_distribution<uint64_t> any_row(0, n - 1);
+    VB_LAUNCH(kpp_copy_row_kernel, 1, 128, 0, x_dev, any_row(gen), dim, 0u, centroids_dev, picked_dev);
+    const size_t smem = (static_cast<size_t>((dim + 31) / 32) * 32 + 8 * 32 * 33) * sizeof(float);
+    VB_CHECK_ARG(smem <= 200 * 1024, "dim too large for the seeding kernel");
+    VB_CUDA(cudaFuncSetAttribute(kpp_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)));
+    std::uniform_real_distribution<double> unit(0.0, 1.0);
+    for (uint32_t c = 1; c < k; ++c) {
+        VB_LAUNCH(kpp_update_kernel, n_part, 256, smem, x_dev, n, dim,
+                  centroids_dev + static_cast<size_t>(c - 1) * dim, min_d.ptr, part.ptr);
+        VB_LAUNCH(kpp_pick_kernel, 1, 1024, 0, x_dev, n, dim, min_d.ptr, part.ptr, n_part, unit(gen), c,
+                  centroids_dev, picked_dev, state.ptr);
+    }
+    uint32_t first_flat = 0xFFFFFFFFu;
+    VB_CUDA(cudaMemcpyAsync(&first_flat, state.ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost, current_stream()));
+    VB_TRY(sync_stream());
+    if (first_flat < k) {
+        // From that round on every row coincides with a chosen centre, so the total stays zero and
+        // the reference draws a uniform row each round.  Replay the generator up to there (each
+        // earlier round consumed one real draw) and finish the same way.
+        std::mt19937 replay(seed);
+        (void)any_row(replay);
+        for (uint32_t c = 1; c < first_flat; ++c) {
+            (void)unit(replay);
+        }
+        for (uint32_t c = first_flat; c < k; ++c) {
+            VB_LAUNCH(kpp_copy_row_kernel, 1, 128, 0, x_dev, any_row(replay), dim, c, centroids_dev, picked_dev);
+        }
+        VB_TRY(sync_stream());
+    }
+    return 0;
+}
+
+}  // namespace vb200
+
+extern "C" int
+vb200_kmeans_init(const float* data, uint64_t count, uint32_t dim, uint32_t k, uint32_t seed, float* centroids,
+                  int64_t* picked) {
+    VB_TRY(check_kmeans_args(data, count, dim, centroids, k));
+    VB_CHECK_ARG(k <= count, "k cannot be larger than count");
+    DevInput<float> x;
+    VB_TRY(x.bind(data, count * dim));
+    DevBuf<float> c;
+    DevBuf<int64_t> rows;
+    VB_TRY(c.reserve(static_cast<size_t>(k) * dim));
+    VB_TRY(rows.reserve(k));
+    VB_TRY(kmeans_pp_init_device(x.ptr, count, dim, k, seed, c.ptr, rows.ptr));
+    VB_TRY(copy_out(centroids, c.ptr, static_cast<size_t>(k) * dim));
+    if (picked != nullptr) {
+        VB_TRY(copy_out(picked, rows.ptr, k));
     }
     return sync_stream();
 }

@@ -34,6 +34,10 @@ struct KMeansWorkspace {
 // tensor-core candidate kernels are the default, the fixed-order SIMT kernels the cross-check.
 bool tensor_cores_enabled();
 
+// k-means++ seeding on the device; see vb200_kmeans_init.  picked_dev may be null.
+int kmeans_pp_init_device(const float* x_dev, uint64_t n, uint32_t dim, uint32_t k, uint32_t seed,
+                          float* centroids_dev, int64_t* picked_dev);
+
 // labels_dev[i] = argmin_j |c_j|^2 - 2 <c_j, x_i> (lowest j on ties).  mean_err_host optional.
 // prev_labels_dev (optional, may alias labels_dev): the labels of the previous Lloyd iteration; the
 // tensor-core path uses them to skip centroids that cannot beat a row's previous one.

@@ -96,6 +96,15 @@ def kmeans_update(data, labels, k: int, it: int = 0):
     return centroids, counts
 
 
+def kmeans_init(data, k: int, seed: int = 47, want_rows: bool = False):
+    """k-means++ seeding: k rows of `data` as initial centroids (and their row numbers)."""
+    n, d = data.shape
+    centroids = _empty_like_side(data, (k, d), np.float32)
+    rows = _empty_like_side(data, (k,), np.int64)
+    check(_capi.load().vb200_kmeans_init(ptr(data, np.float32), n, d, k, seed, ptr(centroids), ptr(rows)))
+    return (centroids, rows) if want_rows else centroids
+
+
 def kmeans_train(data, init_centroids: np.ndarray, iters: int):
     n, d = data.shape
     centroids = np.ascontiguousarray(init_centroids, dtype=np.float32).copy()

@@ -476,7 +476,16 @@ private:
             }
             x = sample.data();
         }
-        check_status(vb200_ivf_train(handle_, x, static_cast<uint64_t>(count), kmeans_iters_, nullptr));
+        // KMeansCluster::Run seeds with k-means++ (src/impl/cluster/kmeans_cluster.h:47); the
+        // generator's seed is fixed here so that a build is reproducible.
+        std::vector<float> seeds;
+        if (kmeans_iters_ > 0) {
+            seeds.resize(static_cast<size_t>(nlist_) * dim_);
+            check_status(vb200_kmeans_init(x, static_cast<uint64_t>(count), static_cast<uint32_t>(dim_), nlist_,
+                                           KMEANS_SEED, seeds.data(), nullptr));
+        }
+        check_status(vb200_ivf_train(handle_, x, static_cast<uint64_t>(count), kmeans_iters_,
+                                     seeds.empty() ? nullptr : seeds.data()));
         trained_ = true;
     }
 
@@ -488,6 +497,7 @@ private:
 
     uint32_t dim_;
     int metric_;
+    static constexpr uint32_t KMEANS_SEED = 47;
     uint32_t nlist_ = 10;
     int quant_ = VB200_QUANT_SQ8;
     bool use_reorder_ = false;
