@@ -321,14 +321,15 @@ def main() -> None:
     if world > 1:
         from vsag_b200 import parallel
 
-        sharded = parallel.ShardedIvfSearch(ix, n_query, K, world, device, dist)
+        sharded = parallel.ShardedIvfSearch(ix, n_query, K, world, device, dist, rank)
 
     def step_device():
         if world == 1:
             ix.search(queries, K, nprobe, out=(out_ids, out_d))
         else:
-            # every rank scans the probed lists it owns; the per-shard top-k are exchanged with
-            # one all-gather over NVLink and merged locally on every rank
+            # every rank routes its slice of the batch, the probe lists are all-gathered, every
+            # rank scans the probed lists it owns, and the per-shard top-k are all-gathered over
+            # NVLink and merged locally
             sharded.search(queries, nprobe, 2.0, out_ids, out_d)
 
     def timed(fn, steps: int):

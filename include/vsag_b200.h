@@ -248,9 +248,11 @@ VB200_API int vb200_ivf_route(vb200_ivf_t index, const float* queries, uint64_t 
 
 /* Same search, but stops before the label translation and returns this shard's partial result as
  * device-resident sortable keys for a cross-GPU merge: keys_dev[nq x k] (uint64, distance in the
- * high word) and labels_dev[nq x k] must be device pointers. */
+ * high word) and labels_dev[nq x k] must be device pointers.  bucket_ids (optional, as in
+ * vb200_ivf_search) lets the ranks route disjoint slices of the batch and share the lists. */
 VB200_API int vb200_ivf_search_partial(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t k,
-                             uint32_t nprobe, float factor, uint64_t* keys_dev, int64_t* labels_dev);
+                             uint32_t nprobe, float factor, const int32_t* bucket_ids, uint64_t* keys_dev,
+                             int64_t* labels_dev);
 
 /* Logical bytes of codes the last search scanned (sum over queries of probed list lengths x
  * code size), the figure the HBM roofline of the scan is computed from. */

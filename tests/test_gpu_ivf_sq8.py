@@ -200,3 +200,15 @@ def test_list_sharded_search_equals_unsharded(engine, oracle):
         shards.append(s)
     got = engine.merge_partials(keys, labels, world, nq, k)
     assert_topk_equal(got[0], got[1], want[0], want[1], rtol=0, atol=0)
+    # the same with the probe lists handed in (the ranks route disjoint slices of the batch and
+    # share them), on either side of the bus, and merged twice through the kept workspace
+    probes, _ = m["ix"].route(q, nprobe)
+    probes_dev = torch.empty((nq, nprobe), dtype=torch.int32, device="cuda")
+    m["ix"].route(torch.from_numpy(q).cuda(), nprobe, out=probes_dev)
+    assert np.array_equal(probes_dev.cpu().numpy(), probes)
+    for r in range(world):
+        shards[r].search_partial(q, k, nprobe, 2.0, keys[r], labels[r],
+                                 bucket_ids=probes if r == 0 else probes_dev)
+    for _ in range(2):
+        again = engine.merge_partials(keys, labels, world, nq, k)
+        assert np.array_equal(again[0], got[0]) and np.array_equal(again[1], got[1])

@@ -63,6 +63,28 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     ok = bool(np.array_equal(got_labels, want))
     # every rank sees the same gathered buffer, rank r's block at index r
     same_block = bool(np.array_equal(keys_all[rank].numpy(), keys_local.numpy()))
+    # query-sharded routing: every rank ranks the centroids for its slice only (here 37 queries
+    # over 2 ranks: 19 + 18, the gathered buffer padded to 2 x 19), all ranks end with all rows
+    cents = rng.random((16, 8)).astype(np.float32)
+    q = rng.random((nq, 8)).astype(np.float32)
+
+    class FakeIndex:
+        calls = []
+
+        def route(self, queries, nprobe, out=None):
+            qq = queries.numpy()
+            self.calls.append(qq.shape[0])
+            dd = ((qq[:, None, :] - cents[None, :, :]) ** 2).sum(-1)
+            out.copy_(torch.from_numpy(np.argsort(dd, axis=1, kind="stable")[:, :nprobe].astype(np.int32)))
+            return out
+
+    fake = FakeIndex()
+    sharded = parallel.ShardedIvfSearch(fake, nq, k, world, torch.device("cpu"), dist, rank)
+    probes = sharded._route(torch.from_numpy(q), 4).numpy()
+    full = np.argsort(((q[:, None, :] - cents[None, :, :]) ** 2).sum(-1), axis=1, kind="stable")[:, :4]
+    lo, hi, per = parallel.query_slice(nq, rank, world)
+    routed = bool(np.array_equal(probes, full)) and fake.calls == [hi - lo] and probes.shape == (nq, 4)
+    ok = ok and routed
     Path(out_dir, f"rank{rank}.txt").write_text(f"{ok} {same_block}")
     dist.barrier()
     dist.destroy_process_group()
@@ -81,3 +103,6 @@ def test_shard_rules():
     assert [parallel.owner_of_list(l, 4) for l in range(6)] == [0, 1, 2, 3, 0, 1]
     ranges = [parallel.row_range(10, r, 3) for r in range(3)]
     assert ranges == [(0, 3), (3, 6), (6, 10)]
+    assert [parallel.query_slice(37, r, 2) for r in range(2)] == [(0, 19, 19), (19, 37, 19)]
+    assert [parallel.query_slice(2, r, 4) for r in range(4)] == [(0, 1, 1), (1, 2, 1), (2, 2, 1), (2, 2, 1)]
+    assert parallel.query_slice(10, 0, 1) == (0, 10, 10)

@@ -1,5 +1,6 @@
 // IVF index: device-resident inverted lists, exact routing, the batched list-major scan
 // scheduler, the partial-result merge and the fp32 rerank.
+#include <algorithm>
 #include <cub/device/device_radix_sort.cuh>
 
 #include "dense.cuh"
@@ -51,6 +52,7 @@ struct SearchWorkspace {
     DevBuf<uint32_t> pair_off[2];  // [nlist + 1]
     DevBuf<uint32_t> item_off[2];  // [nlist + 1]
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
+    DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
     DevBuf<uint32_t> thr;       // [nq]
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
@@ -84,6 +86,7 @@ struct vb200_ivf {
     DevBuf<uint8_t> codes;
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
+    DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
     DevBuf<uint32_t> pos_inner;
     DevBuf<int64_t> labels;
     DevBuf<float> flat;
@@ -311,17 +314,34 @@ probe_is_live(int32_t l, uint32_t nlist, uint32_t rank, uint32_t world, const ui
     return list_off[l + 1] > list_off[l];
 }
 
-// Probe ranks [rank_lo, rank_hi) of every query take part in the phase.
+// first_live[q] = probe rank of the nearest list of query q that this shard holds and that is not
+// empty (nprobe when there is none): the list whose scan gives the query its first bound.
 __global__ void
-pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, uint32_t rank_lo,
-                  uint32_t rank_hi, uint32_t nlist, uint32_t rank, uint32_t world,
+first_live_kernel(const int32_t* __restrict__ probes, uint64_t nq, uint32_t nprobe, uint32_t nlist,
+                  uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off,
+                  uint32_t* __restrict__ first_live) {
+    uint64_t q = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (q >= nq) {
+        return;
+    }
+    uint32_t pr = 0;
+    while (pr < nprobe && !probe_is_live(probes[q * nprobe + pr], nlist, rank, world, list_off)) {
+        ++pr;
+    }
+    first_live[q] = pr;
+}
+
+// Phase 0 takes every query's first live probe, phase 1 the others.
+__global__ void
+pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, uint32_t phase,
+                  const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
                   const uint32_t* __restrict__ list_off, uint32_t* __restrict__ pair_cnt) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
         return;
     }
     uint32_t pr = static_cast<uint32_t>(e % nprobe);
-    if (pr < rank_lo || pr >= rank_hi) {
+    if ((pr == first_live[e / nprobe]) != (phase == 0)) {
         return;
     }
     int32_t l = probes[e];
@@ -330,12 +350,14 @@ pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t n
     }
 }
 
-// Single CTA: exclusive prefixes over the lists of (pairs) and of (tiles of qt queries), plus
-// the logical scan volume sum(pairs[l] * len[l]).
+// Single CTA: exclusive prefixes of (pairs) and of (tiles of qt queries) over the lists taken in
+// `order` (pair_off is stored by list, item_off by position in the order), plus the logical scan
+// volume sum(pairs[l] * len[l]).
 __global__ void __launch_bounds__(1024)
 pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restrict__ list_off,
-                 uint32_t nlist, uint32_t qt, uint32_t code_size, uint32_t* __restrict__ pair_off,
-                 uint32_t* __restrict__ item_off, uint64_t* __restrict__ scalars, uint32_t queue_slot) {
+                 const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt, uint32_t code_size,
+                 uint32_t* __restrict__ pair_off, uint32_t* __restrict__ item_off,
+                 uint64_t* __restrict__ scalars) {
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
@@ -348,10 +370,11 @@ pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restri
     __syncthreads();
     unsigned long long my_bytes = 0;
     for (uint32_t b = 0; b < nlist; b += 1024) {
-        uint32_t l = b + threadIdx.x;
-        uint32_t c = l < nlist ? pair_cnt[l] : 0;
+        const uint32_t pos = b + threadIdx.x;
+        const uint32_t l = pos < nlist ? order[pos] : 0;
+        uint32_t c = pos < nlist ? pair_cnt[l] : 0;
         uint32_t t = (c + qt - 1) / qt;
-        if (l < nlist) {
+        if (pos < nlist) {
             my_bytes += static_cast<unsigned long long>(c) * (list_off[l + 1] - list_off[l]) * code_size;
         }
         s_pairs[threadIdx.x] = c;
@@ -368,9 +391,9 @@ pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restri
             s_items[threadIdx.x] += vi;
             __syncthreads();
         }
-        if (l < nlist) {
+        if (pos < nlist) {
             pair_off[l] = base_pairs + s_pairs[threadIdx.x] - c;
-            item_off[l] = base_items + s_items[threadIdx.x] - t;
+            item_off[pos] = base_items + s_items[threadIdx.x] - t;
         }
         __syncthreads();
         if (threadIdx.x == 1023) {
@@ -385,13 +408,13 @@ pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restri
         pair_off[nlist] = base_pairs;
         item_off[nlist] = base_items;
         scalars[0] += s_bytes;       // logical scan volume, summed over the phases
-        scalars[queue_slot] = 0;     // work-queue head of this phase's scan kernel
     }
 }
 
 __global__ void
 pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
-                    uint32_t rank_lo, uint32_t rank_hi, uint32_t nlist, uint32_t rank, uint32_t world,
+                    uint32_t phase, const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank,
+                    uint32_t world,
                     const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ pair_off,
                     uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_q,
                     uint32_t* __restrict__ pair_slot) {
@@ -400,7 +423,7 @@ pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t
         return;
     }
     uint32_t pr = static_cast<uint32_t>(e % nprobe);
-    if (pr < rank_lo || pr >= rank_hi) {
+    if ((pr == first_live[e / nprobe]) != (phase == 0)) {
         return;
     }
     int32_t l = probes[e];
@@ -622,10 +645,10 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                  1024 - SCAN_THREADS - (sq8 ? SQ8_SLACK : 0));
     const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : RABITQ_QT;
 
-    // Phase 0 scans every query's nearest list, phase 1 the other probes: after phase 0 the
-    // per-query bound is already close to final, so almost nothing enters the buffers later.
+    // Phase 0 scans every query's nearest list (of those this shard holds), phase 1 the other
+    // probes: after phase 0 the per-query bound is already close to final, so almost nothing
+    // enters the buffers later.
     const uint32_t n_phases = nprobe > 1 ? 2 : 1;
-    const uint32_t rank_lo[2] = {0, 1}, rank_hi[2] = {1, nprobe};
     for (uint32_t ph = 0; ph < n_phases; ++ph) {
         const uint64_t cap_pairs = ph == 0 ? nq : total;
         VB_TRY(ws.pair_cnt[ph].reserve(nlist + 1));
@@ -649,15 +672,18 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     VB_CUDA(cudaMemsetAsync(ws.thr.ptr, 0xFF, nq * sizeof(uint32_t), st));
     VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
     const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
+    VB_TRY(ws.first_live.reserve(nq));
+    VB_LAUNCH(first_live_kernel, static_cast<uint32_t>((nq + 255) / 256), 256, 0, probes_dev, nq, nprobe, nlist,
+              ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.first_live.ptr);
     for (uint32_t ph = 0; ph < n_phases; ++ph) {
         VB_CUDA(cudaMemsetAsync(ws.pair_cnt[ph].ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
         VB_CUDA(cudaMemsetAsync(ws.cursor[ph].ptr, 0, nlist * sizeof(uint32_t), st));
-        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, rank_lo[ph], rank_hi[ph],
+        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ph, ws.first_live.ptr,
                   nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.pair_cnt[ph].ptr);
-        VB_LAUNCH(pair_scan_kernel, 1, 1024, 0, ws.pair_cnt[ph].ptr, ix->list_off.ptr, nlist,
-                  static_cast<uint32_t>(qt), ix->code_size, ws.pair_off[ph].ptr, ws.item_off[ph].ptr,
-                  ws.scalars.ptr, 1 + ph);
-        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, rank_lo[ph], rank_hi[ph],
+        VB_LAUNCH(pair_scan_kernel, 1, 1024, 0, ws.pair_cnt[ph].ptr, ix->list_off.ptr, ix->scan_order.ptr,
+                  nlist, static_cast<uint32_t>(qt), ix->code_size, ws.pair_off[ph].ptr, ws.item_off[ph].ptr,
+                  ws.scalars.ptr);
+        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ph, ws.first_live.ptr,
                   nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.pair_off[ph].ptr,
                   ws.cursor[ph].ptr, ws.pair_q[ph].ptr, ws.pair_slot[ph].ptr);
     }
@@ -686,19 +712,23 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                   ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
-    for (uint32_t ph = 0; ph < n_phases; ++ph) {
-        p.pair_off = ws.pair_off[ph].ptr;
-        p.pair_q = ws.pair_q[ph].ptr;
-        p.pair_slot = ws.pair_slot[ph].ptr;
-        p.item_off = ws.item_off[ph].ptr;
-        p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 1 + ph);
-        if (sq8) {
-            size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
-            VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem));
-        } else {
-            size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
-            VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
-        }
+    for (uint32_t ph = 0; ph < 2; ++ph) {
+        const uint32_t src = ph < n_phases ? ph : 0;
+        p.pair_off[ph] = ws.pair_off[src].ptr;
+        p.pair_cnt[ph] = ws.pair_cnt[src].ptr;
+        p.pair_q[ph] = ws.pair_q[src].ptr;
+        p.pair_slot[ph] = ws.pair_slot[src].ptr;
+        p.item_off[ph] = ws.item_off[src].ptr;
+    }
+    p.n_phases = n_phases;
+    p.order = ix->scan_order.ptr;
+    p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 1);
+    if (sq8) {
+        size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
+        VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem));
+    } else {
+        size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
+        VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
     ix->scan_timed = true;
@@ -790,6 +820,25 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
 // =============================================================================================
 // C ABI
 // =============================================================================================
+
+// The scan's work queue hands out the longest lists first so that the last items to finish are
+// short ones.  Recomputed from the host copy of the offsets whenever the lists change.
+static int
+ivf_refresh_scan_order(vb200_ivf* ix) {
+    const uint32_t nlist = ix->nlist;
+    std::vector<uint32_t> order(nlist);
+    for (uint32_t l = 0; l < nlist; ++l) {
+        order[l] = l;
+    }
+    const std::vector<uint32_t>& off = ix->list_off_host;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+        return off[a + 1] - off[a] > off[b + 1] - off[b];
+    });
+    VB_TRY(ix->scan_order.reserve(nlist));
+    VB_CUDA(cudaMemcpyAsync(ix->scan_order.ptr, order.data(), nlist * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                            current_stream()));
+    return sync_stream();
+}
 
 extern "C" int
 vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_reorder,
@@ -1147,7 +1196,7 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     ix->list_off_host = new_off;
     ix->n_stored = n_new_stored;
     ix->n_total += count;
-    return 0;
+    return ivf_refresh_scan_order(ix);
 }
 
 extern "C" int64_t
@@ -1270,7 +1319,8 @@ keys_labels_kernel(const uint64_t* __restrict__ keys, uint64_t total,
 
 extern "C" int
 vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k,
-                         uint32_t nprobe, float factor, uint64_t* keys_dev, int64_t* labels_dev) {
+                         uint32_t nprobe, float factor, const int32_t* bucket_ids, uint64_t* keys_dev,
+                         int64_t* labels_dev) {
     VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
     if (nq == 0) {
         return 0;
@@ -1287,7 +1337,7 @@ vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint
         return sync_stream();
     }
     const uint64_t* keys = nullptr;
-    VB_TRY(ivf_search_keys(ix, queries, nq, k, nprobe, factor, nullptr, &keys));
+    VB_TRY(ivf_search_keys(ix, queries, nq, k, nprobe, factor, bucket_ids, &keys));
     VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
               ix->labels.ptr, keys_dev, labels_dev);
     uint64_t scan_bytes = 0;
@@ -1345,9 +1395,13 @@ vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32
     }
     const uint64_t in_total = static_cast<uint64_t>(parts) * nq * k;
     VB_CHECK_ARG(in_total < 0xFFFFFFFFull, "merge input too large");
-    DevBuf<uint64_t> tagged, merged;
-    DevBuf<int64_t> out_ids;
-    DevBuf<float> out_dists;
+    // Workspace kept between calls (a serving loop merges the same shape every step); one merge
+    // at a time per process.
+    static std::mutex merge_mu;
+    static DevBuf<uint64_t> tagged, merged;
+    static DevBuf<int64_t> out_ids;
+    static DevBuf<float> out_dists;
+    std::lock_guard<std::mutex> lock(merge_mu);
     VB_TRY(tagged.reserve(in_total));
     VB_TRY(merged.reserve(nq * k));
     VB_TRY(out_ids.reserve(nq * k));

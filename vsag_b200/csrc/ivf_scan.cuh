@@ -30,10 +30,16 @@ struct ScanParams {
     uint32_t dim;
     uint32_t dpad;               // dim rounded up (16 for SQ8, 128 for RaBitQ)
     const uint32_t* list_off;    // [nlist + 1] positions
-    const uint32_t* pair_off;    // [nlist + 1] pair ranges per list
-    const uint32_t* pair_q;      // [pairs] query index
-    const uint32_t* pair_slot;   // [pairs] output slot (query * nprobe + probe rank)
-    const uint32_t* item_off;    // [nlist + 1] exclusive prefix of tiles per list
+    // Work items of the two phases (phase 0: every query's nearest list, phase 1: its other
+    // probes), queued one after the other in a single launch.  Within a phase the lists are walked
+    // in `order` (longest first), so the items that finish last are the short ones.
+    const uint32_t* order;         // [nlist] list ids, longest list first
+    const uint32_t* pair_off[2];   // [nlist] first pair of each list
+    const uint32_t* pair_cnt[2];   // [nlist] pairs of each list
+    const uint32_t* pair_q[2];     // [pairs] query index
+    const uint32_t* pair_slot[2];  // [pairs] output slot (query * nprobe + probe rank)
+    const uint32_t* item_off[2];   // [nlist + 1] exclusive prefix of tiles, by position in `order`
+    uint32_t n_phases;
     uint32_t nlist;
     uint32_t* item_counter;      // work queue head
     uint32_t k;
@@ -141,31 +147,54 @@ struct TileSelect {
     }
 };
 
+// A work item: `nqt` queries (pairs pbeg .. pbeg + nqt of phase `ph`) against one list.
+struct ScanItem {
+    uint32_t list;
+    uint32_t pbeg;
+    uint32_t nqt;
+    const uint32_t* pair_q;
+    const uint32_t* pair_slot;
+};
+
 // Fetches the next work item; returns false when the queue is empty.  All threads call it.
+template <int QT>
 __device__ __forceinline__ bool
-scan_next_item(const ScanParams& p, uint32_t* s_item, uint32_t& list, uint32_t& tile) {
+scan_next_item(const ScanParams& p, uint32_t* s_item, ScanItem& it) {
     __syncthreads();
-    const uint32_t n_items = p.item_off[p.nlist];
+    const uint32_t n0 = p.item_off[0][p.nlist];
+    const uint32_t n1 = p.n_phases > 1 ? p.item_off[1][p.nlist] : 0u;
     if (threadIdx.x == 0) {
         s_item[0] = atomicAdd(p.item_counter, 1u);
     }
     __syncthreads();
-    const uint32_t item = s_item[0];
-    if (item >= n_items) {
+    uint32_t item = s_item[0];
+    if (item >= n0 + n1) {
         return false;
     }
-    // Largest l with item_off[l] <= item.
+    const bool second = item >= n0;
+    if (second) {
+        item -= n0;
+    }
+    const uint32_t* item_off = second ? p.item_off[1] : p.item_off[0];
+    // Largest position with item_off[pos] <= item.
     uint32_t lo = 0, hi = p.nlist;
     while (hi - lo > 1) {
         uint32_t mid = (lo + hi) >> 1;
-        if (p.item_off[mid] <= item) {
+        if (item_off[mid] <= item) {
             lo = mid;
         } else {
             hi = mid;
         }
     }
-    list = lo;
-    tile = item - p.item_off[lo];
+    const uint32_t list = p.order[lo];
+    const uint32_t tile = item - item_off[lo];
+    const uint32_t first = (second ? p.pair_off[1] : p.pair_off[0])[list];
+    const uint32_t count = (second ? p.pair_cnt[1] : p.pair_cnt[0])[list];
+    it.list = list;
+    it.pbeg = first + tile * QT;
+    it.nqt = min(static_cast<uint32_t>(QT), count - tile * QT);
+    it.pair_q = second ? p.pair_q[1] : p.pair_q[0];
+    it.pair_slot = second ? p.pair_slot[1] : p.pair_slot[0];
     return true;
 }
 
@@ -292,18 +321,18 @@ ivf_sq8_scan_kernel(const ScanParams p) {
     const uint32_t dpad = p.dpad;
     float* w_s = fbuf;  // [QT][dpad]
 
-    uint32_t list, tile;
-    while (scan_next_item(p, s_item, list, tile)) {
-        const uint32_t pbeg = p.pair_off[list] + tile * QT;
-        const uint32_t pend = p.pair_off[list + 1];
-        const int nqt = static_cast<int>(min(static_cast<uint32_t>(QT), pend - pbeg));
+    ScanItem it;
+    while (scan_next_item<QT>(p, s_item, it)) {
+        const uint32_t list = it.list;
+        const uint32_t pbeg = it.pbeg;
+        const int nqt = static_cast<int>(it.nqt);
         const int ng = (nqt + 3) >> 2;
         if (threadIdx.x < QT) {
             int qi = threadIdx.x;
             if (qi < nqt) {
-                uint32_t q = p.pair_q[pbeg + qi];
+                uint32_t q = it.pair_q[pbeg + qi];
                 ts.qidx[qi] = q;
-                ts.slot[qi] = p.pair_slot[pbeg + qi];
+                ts.slot[qi] = it.pair_slot[pbeg + qi];
                 ts.qa[qi] = __ldg(p.qa + q);
                 ts.set_bound(qi, p.thr_g[q]);
             } else {
@@ -442,17 +471,17 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
     float* sv = fbuf;              // [QT][dpad]
     const uint32_t bits_bytes = ((p.dim + 7) / 8 + 3) / 4 * 4;
 
-    uint32_t list, tile;
-    while (scan_next_item(p, s_item, list, tile)) {
-        const uint32_t pbeg = p.pair_off[list] + tile * QT;
-        const uint32_t pend = p.pair_off[list + 1];
-        const int nqt = static_cast<int>(min(static_cast<uint32_t>(QT), pend - pbeg));
+    ScanItem it;
+    while (scan_next_item<QT>(p, s_item, it)) {
+        const uint32_t list = it.list;
+        const uint32_t pbeg = it.pbeg;
+        const int nqt = static_cast<int>(it.nqt);
         if (threadIdx.x < QT) {
             int qi = threadIdx.x;
             if (qi < nqt) {
-                uint32_t q = p.pair_q[pbeg + qi];
+                uint32_t q = it.pair_q[pbeg + qi];
                 ts.qidx[qi] = q;
-                ts.slot[qi] = p.pair_slot[pbeg + qi];
+                ts.slot[qi] = it.pair_slot[pbeg + qi];
                 ts.qa[qi] = 0.f;
                 ts.set_bound(qi, p.thr_g[q]);
                 s_qnorm[qi] = __ldg(p.queries + static_cast<uint64_t>(q) * (p.dim + 1) + p.dim);

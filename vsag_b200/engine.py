@@ -231,8 +231,13 @@ class IvfHandle:
         check(self._lib.vb200_ivf_get_lists(self._h, None, ptr(codes), ptr(inner)))
         return sizes, codes, inner
 
-    def route(self, queries, nprobe: int):
+    def route(self, queries, nprobe: int, out=None):
+        """(bucket ids, centroid distances) as numpy arrays, or with `out` (an int32 [nq, nprobe]
+        buffer on either side) only the ids, written there."""
         nq = _rows(queries)
+        if out is not None:
+            check(self._lib.vb200_ivf_route(self._h, ptr(queries, np.float32), nq, nprobe, ptr(out), None))
+            return out
         ids = np.empty((nq, nprobe), np.int32)
         dists = np.empty((nq, nprobe), np.float32)
         check(self._lib.vb200_ivf_route(self._h, ptr(queries, np.float32), nq, nprobe, ptr(ids), ptr(dists)))
@@ -249,9 +254,11 @@ class IvfHandle:
                                          ptr(bucket_ids, np.int32), ptr(ids), ptr(dists)))
         return ids, dists
 
-    def search_partial(self, queries, k: int, nprobe: int, factor: float, keys_dev, labels_dev) -> None:
+    def search_partial(self, queries, k: int, nprobe: int, factor: float, keys_dev, labels_dev,
+                       bucket_ids=None) -> None:
         check(self._lib.vb200_ivf_search_partial(self._h, ptr(queries, np.float32), _rows(queries), k,
-                                                 nprobe, factor, ptr(keys_dev), ptr(labels_dev)))
+                                                 nprobe, factor, ptr(bucket_ids, np.int32), ptr(keys_dev),
+                                                 ptr(labels_dev)))
 
     def last_scan_bytes(self) -> int:
         return int(self._lib.vb200_ivf_last_scan_bytes(self._h))

@@ -33,22 +33,51 @@ def exchange_partials(keys_local, labels_local, keys_all, labels_all, dist, grou
     return keys_all, labels_all
 
 
-class ShardedIvfSearch:
-    """Search step of a list-sharded IVF index on this rank's GPU."""
+def query_slice(nq: int, rank: int, world: int) -> tuple[int, int, int]:
+    """(first, last, per): the rows of a batch of nq queries that `rank` routes, and the common
+    slice length `per` = ceil(nq / world) the gathered buffers are padded to."""
+    per = (nq + world - 1) // world
+    lo = min(nq, rank * per)
+    return lo, min(nq, lo + per), per
 
-    def __init__(self, index, nq: int, k: int, world: int, device, dist):
+
+class ShardedIvfSearch:
+    """Search step of a list-sharded IVF index on this rank's GPU.
+
+    Routing is query-sharded (every rank holds all centroids and ranks a 1/world slice of the
+    batch), the probe lists are all-gathered, every rank scans the lists it owns for the whole
+    batch, and the partial top-k are all-gathered and merged."""
+
+    def __init__(self, index, nq: int, k: int, world: int, device, dist, rank: int = 0):
         import torch
 
-        self.index, self.nq, self.k, self.world, self.dist = index, nq, k, world, dist
+        self.index, self.nq, self.k, self.world, self.dist, self.rank = index, nq, k, world, dist, rank
         self.keys_local = torch.empty((nq, k), dtype=torch.int64, device=device)
         self.labels_local = torch.empty((nq, k), dtype=torch.int64, device=device)
         self.keys_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
         self.labels_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
+        self.device = device
+        self._probes_local = None
+        self._probes_all = None
+
+    def _route(self, queries, nprobe: int):
+        import torch
+
+        lo, hi, per = query_slice(self.nq, self.rank, self.world)
+        if self._probes_local is None or self._probes_local.shape != (per, nprobe):
+            self._probes_local = torch.zeros((per, nprobe), dtype=torch.int32, device=self.device)
+            self._probes_all = torch.empty((self.world * per, nprobe), dtype=torch.int32, device=self.device)
+        if hi > lo:
+            self.index.route(queries[lo:hi], nprobe, out=self._probes_local[: hi - lo])
+        self.dist.all_gather_into_tensor(self._probes_all.view(-1), self._probes_local.view(-1))
+        return self._probes_all[: self.nq]
 
     def search(self, queries, nprobe: int, factor: float, out_ids, out_dists):
         from . import _capi
 
-        self.index.search_partial(queries, self.k, nprobe, factor, self.keys_local, self.labels_local)
+        probes = self._route(queries, nprobe) if self.world > 1 else None
+        self.index.search_partial(queries, self.k, nprobe, factor, self.keys_local, self.labels_local,
+                                  bucket_ids=probes)
         exchange_partials(self.keys_local, self.labels_local, self.keys_all, self.labels_all, self.dist)
         _capi.check(_capi.load().vb200_merge_partials(
             _capi.ptr(self.keys_all), _capi.ptr(self.labels_all), self.world, self.nq, self.k,
