@@ -246,12 +246,21 @@ VB200_API int vb200_ivf_search(vb200_ivf_t index, const float* queries, uint64_t
 VB200_API int vb200_ivf_route(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t nprobe,
                     int32_t* bucket_ids, float* bucket_dists);
 
+/* Called by vb200_ivf_search_partial between its two scan phases: bounds_dev[nq] holds, per query,
+ * the distance bound this shard has found so far (+inf = none).  The callee replaces every entry
+ * by the minimum over all shards (an all-reduce with MIN on the communicator it owns), enqueued
+ * on, or ordered with, cuda_stream; it returns 0 on success. */
+typedef int (*vb200_exchange_fn)(float* bounds_dev, uint64_t nq, void* cuda_stream, void* arg);
+
 /* Same search, but stops before the label translation and returns this shard's partial result as
  * device-resident sortable keys for a cross-GPU merge: keys_dev[nq x k] (uint64, distance in the
  * high word) and labels_dev[nq x k] must be device pointers.  bucket_ids (optional, as in
- * vb200_ivf_search) lets the ranks route disjoint slices of the batch and share the lists. */
+ * vb200_ivf_search) lets the ranks route disjoint slices of the batch and share the lists.
+ * exchange (optional) shares the per-query bounds between the shards after each has scanned the
+ * nearest list it holds; without it every shard prunes with its own bounds only. */
 VB200_API int vb200_ivf_search_partial(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t k,
-                             uint32_t nprobe, float factor, const int32_t* bucket_ids, uint64_t* keys_dev,
+                             uint32_t nprobe, float factor, const int32_t* bucket_ids,
+                             vb200_exchange_fn exchange, void* exchange_arg, uint64_t* keys_dev,
                              int64_t* labels_dev);
 
 /* Logical bytes of codes the last search scanned (sum over queries of probed list lengths x

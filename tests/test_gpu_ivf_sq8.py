@@ -212,3 +212,67 @@ def test_list_sharded_search_equals_unsharded(engine, oracle):
     for _ in range(2):
         again = engine.merge_partials(keys, labels, world, nq, k)
         assert np.array_equal(again[0], got[0]) and np.array_equal(again[1], got[1])
+
+
+def test_bound_exchange_between_shards(engine, oracle):
+    """Three shards on one GPU take turns: a first pass collects the bounds each shard finds after
+    its nearest lists, a second pass hands every shard the minimum over all of them through the
+    exchange callback.  Results equal the unsharded search either way."""
+    import torch
+
+    from vsag_b200 import _capi, parallel
+
+    dim, nlist, k, nprobe, nq, world = 32, 48, 10, 12, 200, 3
+    m = build_pair(engine, oracle, 20_000, dim, nlist, seed=43)
+    m["ix"].add(m["x"], m["ids"])
+    q = mixture(44, nq, dim, nlist, 0.15)
+    want = m["ix"].search(q, k, nprobe)
+    shards = []
+    for r in range(world):
+        s = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+        s.set_shard(r, world)
+        s.set_centroids(m["centroids"])
+        s.set_sq8_model(m["lower"], m["diff"])
+        s.add(m["x"], m["ids"])
+        shards.append(s)
+    keys = torch.empty((world, nq, k), dtype=torch.int64, device="cuda")
+    labels = torch.empty((world, nq, k), dtype=torch.int64, device="cuda")
+    local_bounds = []
+
+    def record(ptr, n, _stream, _arg):
+        b = torch.as_tensor(parallel._DevicePointer(ptr, n), device="cuda")
+        local_bounds.append(b.clone())
+        return 0
+
+    cb = _capi.EXCHANGE_FN(record)
+    for r in range(world):
+        shards[r].search_partial(q, k, nprobe, 2.0, keys[r], labels[r], exchange=cb)
+    plain = engine.merge_partials(keys, labels, world, nq, k)
+    assert_topk_equal(plain[0], plain[1], want[0], want[1], rtol=0, atol=0)
+    assert len(local_bounds) == world and all(b.shape == (nq,) for b in local_bounds)
+    tightest = torch.stack(local_bounds).min(dim=0).values
+    assert torch.isfinite(tightest).all()
+
+    def reduce_min(ptr, n, _stream, _arg):
+        b = torch.as_tensor(parallel._DevicePointer(ptr, n), device="cuda")
+        torch.minimum(b, tightest, out=b)
+        return 0
+
+    cb2 = _capi.EXCHANGE_FN(reduce_min)
+    for r in range(world):
+        shards[r].search_partial(q, k, nprobe, 2.0, keys[r], labels[r], exchange=cb2)
+    got = engine.merge_partials(keys, labels, world, nq, k)
+    assert_topk_equal(got[0], got[1], want[0], want[1], rtol=0, atol=0)
+    # the bounds that come back are the ones the second phase prunes with: with a bound of zero
+    # only what each shard found in its nearest list is left, which is worse somewhere
+    zero = _capi.EXCHANGE_FN(lambda ptr, n, _s, _a: int(
+        torch.as_tensor(parallel._DevicePointer(ptr, n), device="cuda").zero_().numel() != n))
+    for r in range(world):
+        shards[r].search_partial(q, k, nprobe, 2.0, keys[r], labels[r], exchange=zero)
+    pruned = engine.merge_partials(keys, labels, world, nq, k)
+    assert np.all(pruned[1] >= want[1]) and np.any(pruned[1] > want[1])
+    # a failing callback is reported, not swallowed
+    bad = _capi.EXCHANGE_FN(lambda *_: 7)
+    with pytest.raises(engine.VsagB200Error, match="exchange"):
+        shards[0].search_partial(q, k, nprobe, 2.0, keys[0], labels[0], exchange=bad)
+    shards[0].search_partial(q, k, nprobe, 2.0, keys[0], labels[0])   # the handle is still usable

@@ -15,6 +15,8 @@ import numpy as np
 _LIB_PATH = Path(__file__).resolve().parent / "libvsag_b200.so"
 
 c_void_p, c_int, c_u32, c_u64, c_i64, c_float = C.c_void_p, C.c_int, C.c_uint32, C.c_uint64, C.c_int64, C.c_float
+# vb200_exchange_fn: int (*)(float* bounds_dev, uint64_t nq, void* cuda_stream, void* arg)
+EXCHANGE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p)
 
 # name -> (restype, argtypes); the single source for the "every declared symbol is exported" test.
 SIGNATURES = {
@@ -52,7 +54,7 @@ SIGNATURES = {
     "vb200_ivf_search": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p, c_void_p]),
     "vb200_ivf_route": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p]),
     "vb200_ivf_search_partial": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p,
-                                         c_void_p]),
+                                         c_void_p, c_void_p, c_void_p]),
     "vb200_ivf_last_scan_bytes": (c_i64, [c_void_p]),
     "vb200_ivf_last_scan_ms": (c_int, [c_void_p, C.POINTER(c_float)]),
     "vb200_merge_partials": (c_int, [c_void_p, c_void_p, c_u32, c_u64, c_u32, c_void_p, c_void_p]),

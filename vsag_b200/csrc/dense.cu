@@ -179,14 +179,30 @@ select_rows_kernel(const float* __restrict__ scores, uint64_t n, uint64_t ld, ui
     BlockSelect sel;
     sel.init(keys, state, k, cap);
     const float* row = scores + static_cast<uint64_t>(blockIdx.x) * ld;
-    for (uint64_t base = 0; base < n; base += SELECT_THREADS) {
-        sel.make_room(SELECT_THREADS);
-        uint64_t thr = sel.threshold();
-        uint64_t c = base + threadIdx.x;
-        if (c < n) {
-            float s = __ldg(row + c);
-            if (s == s) {  // NaN scores are never candidates
-                sel.offer(make_key(s, static_cast<uint32_t>(c) + col_base), thr);
+    // Four rounds' worth of scores are loaded together so that their latency overlaps, and a
+    // round costs one barrier unless some thread actually has a candidate (after the first few
+    // hundred columns almost none does).
+    constexpr int ROUNDS = 4;
+    uint64_t thr = sel.threshold();
+    for (uint64_t base = 0; base < n; base += SELECT_THREADS * ROUNDS) {
+        uint64_t key[ROUNDS];
+#pragma unroll
+        for (int u = 0; u < ROUNDS; ++u) {
+            const uint64_t c = base + static_cast<uint64_t>(u) * SELECT_THREADS + threadIdx.x;
+            key[u] = KEY_INF;
+            if (c < n) {
+                const float s = __ldg(row + c);
+                if (s == s) {  // NaN scores are never candidates
+                    key[u] = make_key(s, static_cast<uint32_t>(c) + col_base);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < ROUNDS; ++u) {
+            if (__syncthreads_or(key[u] < thr)) {
+                sel.make_room(SELECT_THREADS);
+                thr = sel.threshold();
+                sel.offer(key[u], thr);
             }
         }
     }

@@ -47,12 +47,14 @@ struct SearchWorkspace {
     DevBuf<int32_t> probes;     // [nq x nprobe]
     DevBuf<float> probe_dists;
     // pair grouping, one set per scan phase (nearest list first, then the rest)
-    DevBuf<uint32_t> pair_cnt[2];  // [nlist + 1]
-    DevBuf<uint32_t> cursor[2];    // [nlist]
+    DevBuf<uint32_t> pair_ctr;     // pair counts and scatter cursors of both phases: 4 x [nlist]
     DevBuf<uint32_t> pair_off[2];  // [nlist + 1]
     DevBuf<uint32_t> item_off[2];  // [nlist + 1]
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
+    DevBuf<float> bounds;         // [nq] per-query bounds as floats, the buffer the shards exchange
+    vb200_exchange_fn exchange = nullptr;   // set for the duration of one partial search
+    void* exchange_arg = nullptr;
     DevBuf<uint32_t> thr;       // [nq]
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
@@ -331,33 +333,43 @@ first_live_kernel(const int32_t* __restrict__ probes, uint64_t nq, uint32_t npro
     first_live[q] = pr;
 }
 
-// Phase 0 takes every query's first live probe, phase 1 the others.
+// Grouping tables of the two phases: phase 0 takes every query's first live probe, phase 1 the
+// others.
+struct PairTables {
+    uint32_t* cnt[2];       // [nlist] pairs per list
+    uint32_t* cursor[2];    // [nlist] scatter cursors
+    uint32_t* off[2];       // [nlist + 1] first pair of each list
+    uint32_t* item_off[2];  // [nlist + 1] tile prefix by position in the scan order
+    uint32_t* q[2];         // [pairs] query
+    uint32_t* slot[2];      // [pairs] output slot
+};
+
 __global__ void
-pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, uint32_t phase,
+pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
                   const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
-                  const uint32_t* __restrict__ list_off, uint32_t* __restrict__ pair_cnt) {
+                  const uint32_t* __restrict__ list_off, PairTables t) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
         return;
     }
-    uint32_t pr = static_cast<uint32_t>(e % nprobe);
-    if ((pr == first_live[e / nprobe]) != (phase == 0)) {
-        return;
-    }
+    const uint32_t pr = static_cast<uint32_t>(e % nprobe);
+    const uint32_t ph = pr == first_live[e / nprobe] ? 0u : 1u;
     int32_t l = probes[e];
     if (probe_is_live(l, nlist, rank, world, list_off)) {
-        atomicAdd(pair_cnt + l, 1u);
+        atomicAdd((ph == 0 ? t.cnt[0] : t.cnt[1]) + l, 1u);
     }
 }
 
-// Single CTA: exclusive prefixes of (pairs) and of (tiles of qt queries) over the lists taken in
-// `order` (pair_off is stored by list, item_off by position in the order), plus the logical scan
-// volume sum(pairs[l] * len[l]).
+// One CTA per phase: exclusive prefixes of (pairs) and of (tiles of qt queries) over the lists
+// taken in `order` (pair_off is stored by list, item_off by position in the order), plus the
+// logical scan volume sum(pairs[l] * len[l]).
 __global__ void __launch_bounds__(1024)
-pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restrict__ list_off,
+pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
                  const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt, uint32_t code_size,
-                 uint32_t* __restrict__ pair_off, uint32_t* __restrict__ item_off,
                  uint64_t* __restrict__ scalars) {
+    const uint32_t* __restrict__ pair_cnt = blockIdx.x == 0 ? tables.cnt[0] : tables.cnt[1];
+    uint32_t* __restrict__ pair_off = blockIdx.x == 0 ? tables.off[0] : tables.off[1];
+    uint32_t* __restrict__ item_off = blockIdx.x == 0 ? tables.item_off[0] : tables.item_off[1];
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
@@ -407,30 +419,25 @@ pair_scan_kernel(const uint32_t* __restrict__ pair_cnt, const uint32_t* __restri
     if (threadIdx.x == 0) {
         pair_off[nlist] = base_pairs;
         item_off[nlist] = base_items;
-        scalars[0] += s_bytes;       // logical scan volume, summed over the phases
+        atomicAdd(reinterpret_cast<unsigned long long*>(scalars), s_bytes);  // logical scan volume, both phases
     }
 }
 
 __global__ void
 pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
-                    uint32_t phase, const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank,
-                    uint32_t world,
-                    const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ pair_off,
-                    uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_q,
-                    uint32_t* __restrict__ pair_slot) {
+                    const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
+                    const uint32_t* __restrict__ list_off, PairTables t) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
         return;
     }
-    uint32_t pr = static_cast<uint32_t>(e % nprobe);
-    if ((pr == first_live[e / nprobe]) != (phase == 0)) {
-        return;
-    }
+    const uint32_t pr = static_cast<uint32_t>(e % nprobe);
+    const bool first = pr == first_live[e / nprobe];
     int32_t l = probes[e];
     if (probe_is_live(l, nlist, rank, world, list_off)) {
-        uint32_t s = pair_off[l] + atomicAdd(cursor + l, 1u);
-        pair_q[s] = static_cast<uint32_t>(e / nprobe);
-        pair_slot[s] = static_cast<uint32_t>(e);
+        uint32_t s = (first ? t.off[0] : t.off[1])[l] + atomicAdd((first ? t.cursor[0] : t.cursor[1]) + l, 1u);
+        (first ? t.q[0] : t.q[1])[s] = static_cast<uint32_t>(e / nprobe);
+        (first ? t.slot[0] : t.slot[1])[s] = static_cast<uint32_t>(e);
     }
 }
 
@@ -610,6 +617,31 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
 // ---------------------------------------------------------------------------------------------
 // scan
 // ---------------------------------------------------------------------------------------------
+// Per-query bounds leave as plain distances (+inf = none yet) so that ranks can take their
+// minimum with an ordinary float all-reduce, and come back the same way.
+__global__ void
+bounds_to_float_kernel(const uint32_t* __restrict__ thr, uint64_t nq, float* __restrict__ bounds) {
+    uint64_t q = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (q < nq) {
+        const uint32_t u = thr[q];
+        bounds[q] = u > float_to_ordered(INFINITY) ? INFINITY : ordered_to_float(u);
+    }
+}
+
+__global__ void
+bounds_from_float_kernel(const float* __restrict__ bounds, uint64_t nq, uint32_t* __restrict__ thr) {
+    uint64_t q = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (q < nq) {
+        const float b = bounds[q];
+        if (b < INFINITY) {   // NaN and +inf carry no information
+            const uint32_t u = float_to_ordered(b);
+            if (u < thr[q]) {
+                thr[q] = u;
+            }
+        }
+    }
+}
+
 template <typename Kernel>
 static int
 launch_scan(Kernel kernel, const ScanParams& p, size_t smem) {
@@ -649,10 +681,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     // probes: after phase 0 the per-query bound is already close to final, so almost nothing
     // enters the buffers later.
     const uint32_t n_phases = nprobe > 1 ? 2 : 1;
-    for (uint32_t ph = 0; ph < n_phases; ++ph) {
+    for (uint32_t ph = 0; ph < 2; ++ph) {
         const uint64_t cap_pairs = ph == 0 ? nq : total;
-        VB_TRY(ws.pair_cnt[ph].reserve(nlist + 1));
-        VB_TRY(ws.cursor[ph].reserve(nlist));
         VB_TRY(ws.pair_off[ph].reserve(nlist + 1));
         VB_TRY(ws.item_off[ph].reserve(nlist + 1));
         VB_TRY(ws.pair_q[ph].reserve(cap_pairs));
@@ -675,18 +705,23 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     VB_TRY(ws.first_live.reserve(nq));
     VB_LAUNCH(first_live_kernel, static_cast<uint32_t>((nq + 255) / 256), 256, 0, probes_dev, nq, nprobe, nlist,
               ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.first_live.ptr);
-    for (uint32_t ph = 0; ph < n_phases; ++ph) {
-        VB_CUDA(cudaMemsetAsync(ws.pair_cnt[ph].ptr, 0, (nlist + 1) * sizeof(uint32_t), st));
-        VB_CUDA(cudaMemsetAsync(ws.cursor[ph].ptr, 0, nlist * sizeof(uint32_t), st));
-        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ph, ws.first_live.ptr,
-                  nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.pair_cnt[ph].ptr);
-        VB_LAUNCH(pair_scan_kernel, 1, 1024, 0, ws.pair_cnt[ph].ptr, ix->list_off.ptr, ix->scan_order.ptr,
-                  nlist, static_cast<uint32_t>(qt), ix->code_size, ws.pair_off[ph].ptr, ws.item_off[ph].ptr,
-                  ws.scalars.ptr);
-        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ph, ws.first_live.ptr,
-                  nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.pair_off[ph].ptr,
-                  ws.cursor[ph].ptr, ws.pair_q[ph].ptr, ws.pair_slot[ph].ptr);
+    VB_TRY(ws.pair_ctr.reserve(4 * static_cast<size_t>(nlist)));
+    VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
+    PairTables tables{};
+    for (uint32_t ph = 0; ph < 2; ++ph) {
+        tables.cnt[ph] = ws.pair_ctr.ptr + static_cast<size_t>(ph) * nlist;
+        tables.cursor[ph] = ws.pair_ctr.ptr + static_cast<size_t>(2 + ph) * nlist;
+        tables.off[ph] = ws.pair_off[ph].ptr;
+        tables.item_off[ph] = ws.item_off[ph].ptr;
+        tables.q[ph] = ws.pair_q[ph].ptr;
+        tables.slot[ph] = ws.pair_slot[ph].ptr;
     }
+    VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
+              ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables);
+    VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->scan_order.ptr, nlist,
+              static_cast<uint32_t>(qt), ix->code_size, ws.scalars.ptr);
+    VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
+              ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables);
 
     ScanParams p{};
     p.codes = ix->codes.ptr;
@@ -712,23 +747,43 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                   ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
-    for (uint32_t ph = 0; ph < 2; ++ph) {
-        const uint32_t src = ph < n_phases ? ph : 0;
-        p.pair_off[ph] = ws.pair_off[src].ptr;
-        p.pair_cnt[ph] = ws.pair_cnt[src].ptr;
-        p.pair_q[ph] = ws.pair_q[src].ptr;
-        p.pair_slot[ph] = ws.pair_slot[src].ptr;
-        p.item_off[ph] = ws.item_off[src].ptr;
-    }
-    p.n_phases = n_phases;
-    p.order = ix->scan_order.ptr;
-    p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 1);
-    if (sq8) {
-        size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
-        VB_TRY(launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem));
-    } else {
+    auto launch_phases = [&](uint32_t first, uint32_t count, uint32_t queue_slot) -> int {
+        for (uint32_t i = 0; i < 2; ++i) {
+            const uint32_t src = i < count ? first + i : first;
+            p.pair_off[i] = ws.pair_off[src].ptr;
+            p.pair_cnt[i] = tables.cnt[src];
+            p.pair_q[i] = ws.pair_q[src].ptr;
+            p.pair_slot[i] = ws.pair_slot[src].ptr;
+            p.item_off[i] = ws.item_off[src].ptr;
+        }
+        p.n_phases = count;
+        p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + queue_slot);
+        if (sq8) {
+            size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
+            return launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem);
+        }
         size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
-        VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
+        return launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem);
+    };
+    p.order = ix->scan_order.ptr;
+    if (ws.exchange != nullptr && n_phases == 2) {
+        // Sharded search: after every shard has scanned each query's nearest list it holds, the
+        // shards agree on the tightest bound any of them found, so the remaining lists are
+        // pruned as sharply as on one GPU.  The exchange itself (an all-reduce with MIN over
+        // bounds[nq]) belongs to the caller, who owns the communicator; it must be ordered with
+        // the stream it is handed.
+        VB_TRY(launch_phases(0, 1, 1));
+        VB_TRY(ws.bounds.reserve(nq));
+        const uint32_t qblocks = static_cast<uint32_t>((nq + 255) / 256);
+        VB_LAUNCH(bounds_to_float_kernel, qblocks, 256, 0, ws.thr.ptr, nq, ws.bounds.ptr);
+        const int rc = ws.exchange(ws.bounds.ptr, nq, static_cast<void*>(st), ws.exchange_arg);
+        if (rc != 0) {
+            VB_FAIL(VB200_INTERNAL_ERROR, "the bound exchange callback failed with status %d", rc);
+        }
+        VB_LAUNCH(bounds_from_float_kernel, qblocks, 256, 0, ws.bounds.ptr, nq, ws.thr.ptr);
+        VB_TRY(launch_phases(1, 1, 2));
+    } else {
+        VB_TRY(launch_phases(0, n_phases, 1));
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
     ix->scan_timed = true;
@@ -1319,8 +1374,8 @@ keys_labels_kernel(const uint64_t* __restrict__ keys, uint64_t total,
 
 extern "C" int
 vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k,
-                         uint32_t nprobe, float factor, const int32_t* bucket_ids, uint64_t* keys_dev,
-                         int64_t* labels_dev) {
+                         uint32_t nprobe, float factor, const int32_t* bucket_ids, vb200_exchange_fn exchange,
+                         void* exchange_arg, uint64_t* keys_dev, int64_t* labels_dev) {
     VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
     if (nq == 0) {
         return 0;
@@ -1337,7 +1392,12 @@ vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint
         return sync_stream();
     }
     const uint64_t* keys = nullptr;
-    VB_TRY(ivf_search_keys(ix, queries, nq, k, nprobe, factor, bucket_ids, &keys));
+    ix->ws.exchange = exchange;
+    ix->ws.exchange_arg = exchange_arg;
+    const int search_status = ivf_search_keys(ix, queries, nq, k, nprobe, factor, bucket_ids, &keys);
+    ix->ws.exchange = nullptr;
+    ix->ws.exchange_arg = nullptr;
+    VB_TRY(search_status);
     VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
               ix->labels.ptr, keys_dev, labels_dev);
     uint64_t scan_bytes = 0;

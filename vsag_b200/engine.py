@@ -255,10 +255,13 @@ class IvfHandle:
         return ids, dists
 
     def search_partial(self, queries, k: int, nprobe: int, factor: float, keys_dev, labels_dev,
-                       bucket_ids=None) -> None:
+                       bucket_ids=None, exchange=None) -> None:
+        """exchange: an _capi.EXCHANGE_FN instance (kept alive by the caller) that reduces the
+        per-query bounds over the shards, or None."""
+        cb = C.cast(exchange, C.c_void_p) if exchange is not None else None
         check(self._lib.vb200_ivf_search_partial(self._h, ptr(queries, np.float32), _rows(queries), k,
-                                                 nprobe, factor, ptr(bucket_ids, np.int32), ptr(keys_dev),
-                                                 ptr(labels_dev)))
+                                                 nprobe, factor, ptr(bucket_ids, np.int32), cb, None,
+                                                 ptr(keys_dev), ptr(labels_dev)))
 
     def last_scan_bytes(self) -> int:
         return int(self._lib.vb200_ivf_last_scan_bytes(self._h))

@@ -41,12 +41,48 @@ def query_slice(nq: int, rank: int, world: int) -> tuple[int, int, int]:
     return lo, min(nq, lo + per), per
 
 
+class _DevicePointer:
+    """Presents a raw device pointer to torch through the CUDA array interface (no copy)."""
+
+    def __init__(self, ptr: int, count: int):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False),
+                                         "version": 2}
+
+
+def make_bounds_exchange(dist, device, group=None, seen=None):
+    """The callback vb200_ivf_search_partial runs between its two scan phases: an all-reduce with
+    MIN over the per-query bounds, so every shard prunes with the tightest bound any shard found.
+
+    torch orders the collective with its current stream, which must be the stream the library
+    launches on (both are the default stream unless vb200_set_stream changed it).  `seen`, when
+    given, collects the batch sizes the callback was called with (tests)."""
+    import torch
+
+    from . import _capi
+
+    def exchange(ptr, nq, _stream, _arg):
+        try:
+            bounds = torch.as_tensor(_DevicePointer(ptr, nq), device=device)
+            dist.all_reduce(bounds, op=dist.ReduceOp.MIN, group=group)
+            if seen is not None:
+                seen.append(int(nq))
+            return 0
+        except Exception:  # an exception must not unwind through the C frames
+            import traceback
+
+            traceback.print_exc()
+            return 1
+
+    return _capi.EXCHANGE_FN(exchange)
+
+
 class ShardedIvfSearch:
     """Search step of a list-sharded IVF index on this rank's GPU.
 
     Routing is query-sharded (every rank holds all centroids and ranks a 1/world slice of the
     batch), the probe lists are all-gathered, every rank scans the lists it owns for the whole
-    batch, and the partial top-k are all-gathered and merged."""
+    batch -- first each query's nearest list on the rank, then, after an all-reduce (MIN) of the
+    per-query bounds, the others -- and the partial top-k are all-gathered and merged."""
 
     def __init__(self, index, nq: int, k: int, world: int, device, dist, rank: int = 0):
         import torch
@@ -59,6 +95,8 @@ class ShardedIvfSearch:
         self.device = device
         self._probes_local = None
         self._probes_all = None
+        on_gpu = getattr(device, "type", str(device)) == "cuda"
+        self._exchange = make_bounds_exchange(dist, device) if world > 1 and on_gpu else None
 
     def _route(self, queries, nprobe: int):
         import torch
@@ -77,7 +115,7 @@ class ShardedIvfSearch:
 
         probes = self._route(queries, nprobe) if self.world > 1 else None
         self.index.search_partial(queries, self.k, nprobe, factor, self.keys_local, self.labels_local,
-                                  bucket_ids=probes)
+                                  bucket_ids=probes, exchange=self._exchange)
         exchange_partials(self.keys_local, self.labels_local, self.keys_all, self.labels_all, self.dist)
         _capi.check(_capi.load().vb200_merge_partials(
             _capi.ptr(self.keys_all), _capi.ptr(self.labels_all), self.world, self.nq, self.k,
