@@ -276,3 +276,31 @@ def test_bound_exchange_between_shards(engine, oracle):
     with pytest.raises(engine.VsagB200Error, match="exchange"):
         shards[0].search_partial(q, k, nprobe, 2.0, keys[0], labels[0], exchange=bad)
     shards[0].search_partial(q, k, nprobe, 2.0, keys[0], labels[0])   # the handle is still usable
+
+
+@pytest.mark.parametrize("metric", [0, 1])
+def test_tensor_core_routing_equals_simt_and_oracle(engine, oracle, metric):
+    """Batches of 256+ queries over 1024+ lists nominate their probe lists with the tcgen05 kernel;
+    after the exact re-scoring the lists and distances are those of the SIMT path and the oracle."""
+    dim, nlist, nq, nprobe = 96, 2048, 700, 40
+    cents = mixture(51, nlist, dim, 64, 0.3)
+    q = mixture(52, nq, dim, 64, 0.3)
+    ix = engine.IvfHandle(dim, metric, nlist, engine.QUANT_SQ8)
+    ix.set_centroids(cents)
+    try:
+        engine.set_tensor_cores(True)
+        before = engine.kernel_launches()
+        got_ids, got_d = ix.route(q, nprobe)
+        tc_launches = engine.kernel_launches() - before
+        engine.set_tensor_cores(False)
+        before = engine.kernel_launches()
+        simt_ids, simt_d = ix.route(q, nprobe)
+        simt_launches = engine.kernel_launches() - before
+    finally:
+        engine.set_tensor_cores(True)
+    assert tc_launches != simt_launches
+    assert np.array_equal(got_d, simt_d)
+    assert_topk_equal(got_ids, got_d, simt_ids, simt_d, rtol=0, atol=0)
+    want_ids, want_d = oracle.route(q, cents, nprobe, metric)
+    assert np.array_equal(got_d, want_d)
+    assert_topk_equal(got_ids, got_d, want_ids, want_d, rtol=0, atol=0)

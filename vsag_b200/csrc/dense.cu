@@ -213,6 +213,159 @@ select_rows_kernel(const float* __restrict__ scores, uint64_t n, uint64_t ld, ui
     }
 }
 
+// Long rows, modest k: instead of streaming the row through a selector that re-sorts its buffer
+// every few hundred candidates, find the value range of the row, histogram it, read off the bin
+// that holds the k-th smallest score, collect everything up to that bin (a little more than k
+// keys) and sort once.  A row whose scores do not spread (or are not finite) takes the streaming
+// path instead.
+constexpr int HIST_BINS = 2048;
+constexpr uint32_t HIST_CAP = 1024;   // keys collected at most; also the streaming path's buffer
+
+__device__ __forceinline__ uint32_t
+hist_bin(float s, float mn, float scale) {
+    if (!(s > mn)) {
+        return 0;
+    }
+    const float t = (s - mn) * scale;
+    return t >= static_cast<float>(HIST_BINS - 1) ? HIST_BINS - 1 : static_cast<uint32_t>(t);
+}
+
+__global__ void __launch_bounds__(SELECT_THREADS)
+select_rows_hist_kernel(const float* __restrict__ scores, uint64_t n, uint64_t ld, uint32_t k,
+                        uint32_t col_base, uint64_t* __restrict__ keys_out, uint32_t keys_ld) {
+    __shared__ uint32_t hist[HIST_BINS];
+    __shared__ __align__(16) uint64_t keys[HIST_CAP];
+    __shared__ uint32_t state[4];
+    __shared__ uint32_t scan[SELECT_THREADS];
+    __shared__ float red_mn[SELECT_THREADS / 32], red_mx[SELECT_THREADS / 32];
+    __shared__ uint32_t pick_bin, pick_count;
+    const uint32_t tid = threadIdx.x;
+    const float* row = scores + static_cast<uint64_t>(blockIdx.x) * ld;
+    uint64_t* dst = keys_out + static_cast<uint64_t>(blockIdx.x) * keys_ld;
+
+    // range of the finite scores
+    float mn = INFINITY, mx = -INFINITY;
+    for (uint64_t c = tid; c < n; c += SELECT_THREADS) {
+        const float s = __ldg(row + c);
+        if (fabsf(s) < INFINITY) {
+            mn = fminf(mn, s);
+            mx = fmaxf(mx, s);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((tid & 31) == 0) {
+        red_mn[tid >> 5] = mn;
+        red_mx[tid >> 5] = mx;
+    }
+    for (uint32_t b = tid; b < HIST_BINS; b += SELECT_THREADS) {
+        hist[b] = 0;
+    }
+    if (tid == 0) {
+        pick_bin = 0xFFFFFFFFu;
+        pick_count = 0;
+        state[3] = 0;
+    }
+    __syncthreads();
+    mn = red_mn[0];
+    mx = red_mx[0];
+    for (int w = 1; w < SELECT_THREADS / 32; ++w) {
+        mn = fminf(mn, red_mn[w]);
+        mx = fmaxf(mx, red_mx[w]);
+    }
+    const float scale = static_cast<float>(HIST_BINS - 1) / (mx - mn);
+    const bool spread = mx > mn && scale > 0.f && scale < INFINITY;
+    if (spread) {
+        for (uint64_t c = tid; c < n; c += SELECT_THREADS) {
+            const float s = __ldg(row + c);
+            if (s == s) {
+                atomicAdd(&hist[hist_bin(s, mn, scale)], 1u);
+            }
+        }
+        __syncthreads();
+        // inclusive scan of the bins, eight per thread
+        constexpr int PER = HIST_BINS / SELECT_THREADS;
+        uint32_t local[PER];
+        uint32_t sum = 0;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            sum += hist[tid * PER + i];
+            local[i] = sum;
+        }
+        scan[tid] = sum;
+        __syncthreads();
+        for (uint32_t off = 1; off < SELECT_THREADS; off <<= 1) {
+            const uint32_t v = tid >= off ? scan[tid - off] : 0;
+            __syncthreads();
+            scan[tid] += v;
+            __syncthreads();
+        }
+        const uint32_t before = scan[tid] - sum;
+        const uint32_t total = scan[SELECT_THREADS - 1];
+        if (total <= k) {
+            if (tid == 0) {
+                pick_bin = HIST_BINS - 1;
+                pick_count = total;
+            }
+        } else if (before < k && before + sum >= k) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                if (before + local[i] >= k) {
+                    pick_bin = tid * PER + i;
+                    pick_count = before + local[i];
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        const uint32_t last_bin = pick_bin, count = pick_count;
+        if (count <= HIST_CAP) {
+            for (uint64_t c = tid; c < n; c += SELECT_THREADS) {
+                const float s = __ldg(row + c);
+                if (s == s && hist_bin(s, mn, scale) <= last_bin) {
+                    keys[atomicAdd(&state[3], 1u)] = make_key(s, static_cast<uint32_t>(c) + col_base);
+                }
+            }
+            const uint32_t n2 = next_pow2(count < 2 ? 2 : count);
+            __syncthreads();
+            for (uint32_t i = count + tid; i < n2; i += SELECT_THREADS) {
+                keys[i] = KEY_INF;
+            }
+            block_bitonic_sort(keys, n2);
+            for (uint32_t i = tid; i < k; i += SELECT_THREADS) {
+                dst[i] = i < count ? keys[i] : KEY_INF;
+            }
+            return;
+        }
+    }
+    // streaming path
+    __syncthreads();
+    BlockSelect sel;
+    sel.init(keys, state, k, HIST_CAP);
+    uint64_t thr = sel.threshold();
+    for (uint64_t base = 0; base < n; base += SELECT_THREADS) {
+        const uint64_t c = base + tid;
+        uint64_t key = KEY_INF;
+        if (c < n) {
+            const float s = __ldg(row + c);
+            if (s == s) {
+                key = make_key(s, static_cast<uint32_t>(c) + col_base);
+            }
+        }
+        if (__syncthreads_or(key < thr)) {
+            sel.make_room(SELECT_THREADS);
+            thr = sel.threshold();
+            sel.offer(key, thr);
+        }
+    }
+    const uint32_t cnt = sel.finish();
+    for (uint32_t i = tid; i < k; i += SELECT_THREADS) {
+        dst[i] = i < cnt ? keys[i] : KEY_INF;
+    }
+}
+
 int
 select_rows(const float* scores, uint64_t m, uint64_t n, uint64_t ld, uint32_t k, uint32_t col_base,
             uint64_t* keys_out, uint32_t keys_ld) {
@@ -221,6 +374,11 @@ select_rows(const float* scores, uint64_t m, uint64_t n, uint64_t ld, uint32_t k
     }
     VB_CHECK_ARG(k >= 1 && k <= 1024, "select_rows: k must be in [1, 1024], got %u", k);
     VB_CHECK_ARG(m <= 0x7fffffffu, "select_rows: too many rows");
+    if (n >= 4096 && k + SELECT_THREADS <= HIST_CAP) {
+        VB_LAUNCH(select_rows_hist_kernel, static_cast<uint32_t>(m), SELECT_THREADS, 0, scores, n, ld, k, col_base,
+                  keys_out, keys_ld);
+        return 0;
+    }
     uint32_t cap = next_pow2(k + SELECT_THREADS);
     size_t smem = cap * sizeof(uint64_t) + 4 * sizeof(uint32_t);
     VB_LAUNCH(select_rows_kernel, static_cast<uint32_t>(m), SELECT_THREADS, smem, scores, n, ld, k,

@@ -8,6 +8,7 @@
 #include "kmeans.cuh"
 #include "rabitq.cuh"
 #include "sq8.cuh"
+#include "tc_gemm.cuh"
 
 namespace vb200 {
 
@@ -53,6 +54,7 @@ struct SearchWorkspace {
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
     DevBuf<float> bounds;         // [nq] per-query bounds as floats, the buffer the shards exchange
+    DevBuf<uint16_t> q_hi, q_lo;  // tensor-core routing: tiled bf16 terms of the queries
     vb200_exchange_fn exchange = nullptr;   // set for the duration of one partial search
     void* exchange_arg = nullptr;
     DevBuf<uint32_t> thr;       // [nq]
@@ -89,6 +91,10 @@ struct vb200_ivf {
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
+    // tensor-core routing: the centroids as tiled bf16 hi/lo terms (rebuilt when they change)
+    DevBuf<uint16_t> c_hi, c_lo;
+    bool c_tiled = false;
+    TcWorkspace tc;
     DevBuf<uint32_t> pos_inner;
     DevBuf<int64_t> labels;
     DevBuf<float> flat;
@@ -591,21 +597,45 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
     uint32_t ncand = nprobe + ROUTE_SLACK < nlist ? nprobe + ROUTE_SLACK : nlist;
     VB_CHECK_ARG(ncand <= 1024, "scan_buckets_count %u is too large (limit %u)", nprobe,
                  1024 - ROUTE_SLACK);
-    uint64_t slab = (uint64_t{256} << 20) / nlist;  // rows of a 1 GiB score slab
-    if (slab < 1) {
-        slab = 1;
-    }
-    if (slab > nq) {
-        slab = nq;
-    }
-    VB_TRY(ws.scores.reserve(slab * nlist));
     VB_TRY(ws.cand.reserve(nq * ncand));
     const bool l2 = ix->metric == VB200_METRIC_L2;
-    for (uint64_t b = 0; b < nq; b += slab) {
-        uint64_t n = nq - b < slab ? nq - b : slab;
-        VB_TRY(dense_scores_f32(q_dev + b * ix->dim, n, ix->centroids.ptr, nlist, ix->dim,
-                                l2 ? -2.0f : -1.0f, l2 ? ix->c_sq.ptr : nullptr, ws.scores.ptr, nlist));
-        VB_TRY(select_rows(ws.scores.ptr, n, nlist, nlist, ncand, 0, ws.cand.ptr + b * ncand, ncand));
+    const uint64_t ld = (static_cast<uint64_t>(nlist) + 3) / 4 * 4;
+    if (tensor_cores_enabled() && nq >= 256 && nlist >= 1024 && nq * ld <= (uint64_t{1} << 30)) {
+        // Scores from the tcgen05 kernel (split-bf16, good to ~1e-5 relative) nominate the
+        // candidates; the exact re-scoring below orders them and drops the slack, as on the
+        // SIMT path.
+        const uint32_t chunks = (ix->dim + TC_KC - 1) / TC_KC;
+        if (!ix->c_tiled) {
+            const size_t elems = tc_tiled_elems(nlist, ix->dim);
+            VB_TRY(ix->c_hi.reserve(elems));
+            VB_TRY(ix->c_lo.reserve(elems));
+            VB_TRY(tc_pretile_f32(ix->centroids.ptr, nlist, ix->dim, ix->c_hi.ptr, ix->c_lo.ptr));
+            ix->c_tiled = true;
+        }
+        const size_t q_elems = tc_tiled_elems(nq, ix->dim);
+        VB_TRY(ws.q_hi.reserve(q_elems));
+        VB_TRY(ws.q_lo.reserve(q_elems));
+        VB_TRY(tc_pretile_f32(q_dev, nq, ix->dim, ws.q_hi.ptr, ws.q_lo.ptr));
+        TcOperand a{ws.q_hi.ptr, ws.q_lo.ptr, nq, chunks};
+        TcOperand b{ix->c_hi.ptr, ix->c_lo.ptr, nlist, chunks};
+        VB_TRY(ws.scores.reserve(nq * ld));
+        VB_TRY(tc_scores(ix->tc, a, b, 3, l2 ? -2.0f : -1.0f, l2 ? ix->c_sq.ptr : nullptr, ws.scores.ptr, ld));
+        VB_TRY(select_rows(ws.scores.ptr, nq, nlist, ld, ncand, 0, ws.cand.ptr, ncand));
+    } else {
+        uint64_t slab = (uint64_t{256} << 20) / nlist;  // rows of a 1 GiB score slab
+        if (slab < 1) {
+            slab = 1;
+        }
+        if (slab > nq) {
+            slab = nq;
+        }
+        VB_TRY(ws.scores.reserve(slab * nlist));
+        for (uint64_t b = 0; b < nq; b += slab) {
+            uint64_t n = nq - b < slab ? nq - b : slab;
+            VB_TRY(dense_scores_f32(q_dev + b * ix->dim, n, ix->centroids.ptr, nlist, ix->dim,
+                                    l2 ? -2.0f : -1.0f, l2 ? ix->c_sq.ptr : nullptr, ws.scores.ptr, nlist));
+            VB_TRY(select_rows(ws.scores.ptr, n, nlist, nlist, ncand, 0, ws.cand.ptr + b * ncand, ncand));
+        }
     }
     uint32_t n2 = next_pow2(ncand < 2 ? 2 : ncand);
     VB_LAUNCH(route_finalize_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev,
@@ -974,6 +1004,7 @@ static int
 ivf_refresh_centroid_norms(vb200_ivf* ix) {
     VB_TRY(ix->c_sq.reserve(ix->nlist));
     VB_TRY(row_sqnorm_f32(ix->centroids.ptr, ix->nlist, ix->dim, ix->c_sq.ptr));
+    ix->c_tiled = false;
     ix->has_centroids = true;
     return 0;
 }
@@ -1152,9 +1183,14 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     if (labels_in != nullptr) {
         VB_CUDA(cudaMemcpyAsync(lab.ptr, labels_in, count * sizeof(int32_t), cudaMemcpyDefault, st));
     } else {
-        const bool l2 = ix->metric == VB200_METRIC_L2;
-        VB_TRY(dense_argmin_f32(x.ptr, count, ix->centroids.ptr, nlist, dim, l2 ? -2.0f : -1.0f,
-                                l2 ? ix->c_sq.ptr : nullptr, lab.ptr, nullptr));
+        if (ix->metric == VB200_METRIC_L2) {
+            // the k-means assignment (tensor-core candidates + exact pick when large enough)
+            ix->kws.forget_points();
+            VB_TRY(kmeans_assign_device(ix->kws, x.ptr, count, dim, ix->centroids.ptr, nlist, lab.ptr, nullptr));
+            ix->kws.forget_points();
+        } else {
+            VB_TRY(dense_argmin_f32(x.ptr, count, ix->centroids.ptr, nlist, dim, -1.0f, nullptr, lab.ptr, nullptr));
+        }
     }
     // 2. sort rows by (list, row)
     DevBuf<uint64_t> keys, sorted;

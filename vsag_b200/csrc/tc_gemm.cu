@@ -142,11 +142,14 @@ tc_compact_row(uint64_t* my_buf, uint32_t& my_cnt, float& my_thr, uint32_t owner
     __syncwarp();
 }
 
-// SMALL_M: at most four candidates per row, kept sorted in registers by the row's thread (the
-// k-means case); otherwise candidates go to per-row buffers compacted as above.
-template <bool SMALL_M>
+// MODE 0: at most four candidates per row, kept sorted in registers by the row's thread (the
+// k-means case); MODE 1: candidates go to per-row buffers compacted as above; MODE 2: no
+// selection, the scores themselves are stored.
+template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_candidates_kernel(const TcParams p) {
+    constexpr bool SMALL_M = MODE == 0;
+    constexpr bool STORE = MODE == 2;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ TcShared sh;
 
@@ -381,7 +384,7 @@ tc_candidates_kernel(const TcParams p) {
 
                 {
                     const uint32_t cb = cgroup;
-                    if (!SMALL_M) {
+                    if (MODE == 1) {
                         uint32_t full = __ballot_sync(0xffffffffu, cnt + 32 > p.cap);
                         while (full != 0) {
                             uint32_t owner = __ffs(full) - 1;
@@ -403,6 +406,26 @@ tc_candidates_kernel(const TcParams p) {
                             const bool in_range = whole_tile || (valid_row && c0 + i + j < p.b.rows);
                             sc[i + j] = in_range ? fmaf(p.alpha, __uint_as_float(r[i + j]), bb[j]) : INFINITY;
                         }
+                    }
+                    if (STORE) {
+                        // 32 consecutive floats of this thread's row: eight 16-byte stores
+                        if (valid_row) {
+                            float* dst = p.store + grow * p.store_ld + c0;
+                            if (whole_tile) {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4) {
+                                    *reinterpret_cast<float4*>(dst + i) = make_float4(sc[i], sc[i + 1], sc[i + 2], sc[i + 3]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) {
+                                    if (c0 + i < p.b.rows) {
+                                        dst[i] = sc[i];
+                                    }
+                                }
+                            }
+                        }
+                        continue;
                     }
                     // minimum as a tree: a serial chain of 32 dependent fminf would stall the warp
                     float m16[16], m4[4];
@@ -479,6 +502,9 @@ tc_candidates_kernel(const TcParams p) {
             }
             if (!ok) {
                 break;
+            }
+            if (STORE) {
+                continue;
             }
             if (SMALL_M) {
                 if (valid_row) {
@@ -596,7 +622,7 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     const bool small_m = m <= 4;
     const size_t smem = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES +
                         (small_m ? 0 : TC_EPI_WARPS * static_cast<size_t>(p.cap) * sizeof(uint64_t)) + 1024;
-    auto kernel = small_m ? tc_candidates_kernel<true> : tc_candidates_kernel<false>;
+    auto kernel = small_m ? tc_candidates_kernel<0> : tc_candidates_kernel<1>;
     VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
     int flag = 0;
@@ -606,6 +632,56 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
         VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
     }
     *n_split_out = static_cast<uint32_t>(n_split) * TC_COL_GROUPS;
+    return 0;
+}
+
+int
+tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
+          const float* bias_dev, float* scores_dev, uint64_t ld) {
+    VB_CHECK_ARG(a.rows > 0 && b.rows > 0, "tc_scores: empty operand");
+    VB_CHECK_ARG(a.chunks == b.chunks && a.chunks > 0, "tc_scores: operand depths differ");
+    VB_CHECK_ARG(n_terms == 1 || n_terms == 3, "tc_scores: 1 or 3 terms");
+    VB_CHECK_ARG(ld >= b.rows && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(scores_dev) & 15) == 0,
+                 "tc_scores: the score matrix must be 16-byte aligned with a row stride that is a multiple of 4");
+    const uint64_t m_tiles = (a.rows + TC_BM - 1) / TC_BM;
+    const uint64_t n_tiles = (b.rows + TC_BN - 1) / TC_BN;
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    uint64_t n_split = (2ull * sms + m_tiles - 1) / m_tiles;
+    if (n_split > n_tiles) {
+        n_split = n_tiles;
+    }
+    if (n_split < 1) {
+        n_split = 1;
+    }
+    const uint64_t tiles_per_split = (n_tiles + n_split - 1) / n_split;
+    n_split = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+    const uint64_t items = m_tiles * n_split;
+    const uint32_t grid = static_cast<uint32_t>(items < sms ? items : sms);
+    TcParams p{};
+    p.a = a;
+    p.b = b;
+    p.n_terms = n_terms;
+    p.alpha = alpha;
+    p.bias = bias_dev;
+    p.m = 0;
+    p.cap = 0;
+    p.n_split = static_cast<uint32_t>(n_split);
+    p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
+    p.store = scores_dev;
+    p.store_ld = ld;
+    VB_TRY(ws.error_flag.reserve(1));
+    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
+    p.error_flag = ws.error_flag.ptr;
+    const size_t smem = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES + 1024;
+    auto kernel = tc_candidates_kernel<2>;
+    VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
+    int flag = 0;
+    VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
+    VB_TRY(sync_stream());
+    if (flag != 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
+    }
     return 0;
 }
 

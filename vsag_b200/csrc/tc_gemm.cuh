@@ -52,6 +52,8 @@ struct TcParams {
     uint64_t* scratch;        // [grid][128][TC_COL_GROUPS][cap] candidate buffers
     uint64_t* out;            // [a.rows][n_split][TC_COL_GROUPS][m] keys (ordered score << 32 | column), KEY_INF padded
     uint32_t col_base;        // added to column indices in the keys
+    float* store;             // score-matrix mode: [a.rows][store_ld] fp32 scores instead of candidates
+    uint64_t store_ld;        // row stride of `store` in floats (multiple of 4, store 16-byte aligned)
     int* error_flag;          // set non-zero if a bounded wait gave up
 };
 
@@ -217,6 +219,11 @@ int tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint3
                   const float* bias_dev, uint32_t m, uint32_t col_base, DevBuf<uint64_t>& out,
                   uint32_t* n_split_out, const float* a_sq_dev = nullptr,
                   const float* margin_scale_dev = nullptr, const float* row_bound_dev = nullptr);
+
+// The whole score matrix alpha * <a, b> + bias as fp32 in scores_dev[a.rows][ld] (ld >= b.rows, a
+// multiple of 4, scores_dev 16-byte aligned), from the same tensor-core pipeline.
+int tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
+              const float* bias_dev, float* scores_dev, uint64_t ld);
 
 // Largest m tc_candidates accepts for the given number of terms.
 uint32_t tc_max_candidates(uint32_t n_terms);
