@@ -267,6 +267,14 @@ VB200_API int vb200_ivf_search_partial(vb200_ivf_t index, const float* queries, 
  * code size), the figure the HBM roofline of the scan is computed from. */
 VB200_API int64_t vb200_ivf_last_scan_bytes(vb200_ivf_t index);
 
+/* Bytes of codes the last search actually read after list pruning: an SQ8 scan drops a (query,
+ * list) pair unscanned when the triangle inequality on the list's radius shows that nothing in the
+ * list can beat the query's current k-th candidate.  The result is the same as without pruning. */
+VB200_API int64_t vb200_ivf_last_scanned_bytes(vb200_ivf_t index);
+
+/* Turns that list pruning off (0) or on (non-zero, the default); for cross-checks. */
+VB200_API int vb200_ivf_set_list_pruning(vb200_ivf_t index, int enable);
+
 /* Device time of the last search's list-scan kernel in milliseconds, from CUDA events recorded
  * around its launch on the stream it ran on. */
 VB200_API int vb200_ivf_last_scan_ms(vb200_ivf_t index, float* ms);

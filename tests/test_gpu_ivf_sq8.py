@@ -304,3 +304,32 @@ def test_tensor_core_routing_equals_simt_and_oracle(engine, oracle, metric):
     want_ids, want_d = oracle.route(q, cents, nprobe, metric)
     assert np.array_equal(got_d, want_d)
     assert_topk_equal(got_ids, got_d, want_ids, want_d, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("metric", [0, 1])
+def test_list_pruning_changes_nothing_but_the_bytes_read(engine, oracle, metric):
+    """A (query, list) pair is dropped when the list's ball around its centroid lies beyond the
+    query's current bound; the answer must be the one of the full scan (and of the oracle), with
+    fewer code bytes read on clustered data."""
+    # enough (list, query tile) items that most start after the first bounds exist
+    dim, nlist, k, nprobe, nq = 32, 256, 10, 24, 4000
+    m = build_pair(engine, oracle, 60_000, dim, nlist, metric=metric, seed=61)
+    m["ix"].add(m["x"][:22_000], m["ids"][:22_000], labels=m["labels"][:22_000])
+    m["ix"].add(m["x"][22_000:], m["ids"][22_000:], labels=m["labels"][22_000:])   # radii follow incremental adds
+    q = mixture(62, nq, dim, nlist, 0.15)
+    pruned = m["ix"].search(q, k, nprobe)
+    logical, touched = m["ix"].last_scan_bytes(), m["ix"].last_scanned_bytes()
+    m["ix"].set_list_pruning(False)
+    full = m["ix"].search(q, k, nprobe)
+    assert m["ix"].last_scanned_bytes() == m["ix"].last_scan_bytes() == logical
+    m["ix"].set_list_pruning(True)
+    assert np.array_equal(pruned[0], full[0]) and np.array_equal(pruned[1], full[1])
+    assert 0 < touched < logical
+    sub = slice(0, 400)
+    probes, _ = oracle.route(q[sub], m["centroids"], nprobe, metric)
+    want = oracle.ivf_sq8_search(m["codes"], m["off"], m["ids"][m["order"]], m["lower"], m["diff"], q[sub], probes,
+                                 k, metric)
+    assert np.array_equal(pruned[1][sub], want[1])
+    assert_topk_equal(pruned[0][sub], pruned[1][sub], want[0], want[1], rtol=1e-5, atol=1e-5)
+    with pytest.raises(engine.VsagB200Error):
+        m["ix"].set_centroids(m["centroids"])   # would invalidate lists and radii

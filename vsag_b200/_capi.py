@@ -56,6 +56,8 @@ SIGNATURES = {
     "vb200_ivf_search_partial": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p]),
     "vb200_ivf_last_scan_bytes": (c_i64, [c_void_p]),
+    "vb200_ivf_last_scanned_bytes": (c_i64, [c_void_p]),
+    "vb200_ivf_set_list_pruning": (c_int, [c_void_p, c_int]),
     "vb200_ivf_last_scan_ms": (c_int, [c_void_p, C.POINTER(c_float)]),
     "vb200_merge_partials": (c_int, [c_void_p, c_void_p, c_u32, c_u64, c_u32, c_void_p, c_void_p]),
     "vb200_bf_create": (c_int, [c_u32, c_int, c_int, C.POINTER(c_void_p)]),

@@ -53,6 +53,7 @@ struct SearchWorkspace {
     DevBuf<uint32_t> item_off[2];  // [nlist + 1]
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
+    bool pruning = false;         // the last scan dropped (query, list) pairs by the list radius
     DevBuf<float> bounds;         // [nq] per-query bounds as floats, the buffer the shards exchange
     DevBuf<uint16_t> q_hi, q_lo;  // tensor-core routing: tiled bf16 terms of the queries
     vb200_exchange_fn exchange = nullptr;   // set for the duration of one partial search
@@ -91,6 +92,9 @@ struct vb200_ivf {
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
+    DevBuf<float> list_radius;    // SQ8: max |decoded row - centroid| per list (list pruning)
+    bool prune_lists = true;
+    int64_t last_scanned_bytes = 0;
     // tensor-core routing: the centroids as tiled bf16 hi/lo terms (rebuilt when they change)
     DevBuf<uint16_t> c_hi, c_lo;
     bool c_tiled = false;
@@ -235,6 +239,47 @@ sq8_code_norm_kernel(const uint8_t* __restrict__ codes, uint64_t n, uint32_t dim
         }
     }
     code_norm[p] = s;
+}
+
+// One warp per list: radius[l] = max over the list's rows of |decoded row - centroid_l|, rounded
+// up a little, the ball the scan's list pruning relies on.  Empty lists get 0.
+__global__ void __launch_bounds__(128)
+sq8_list_radius_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, uint32_t dim,
+                       const uint32_t* __restrict__ list_off, uint32_t nlist, const float* __restrict__ lower,
+                       const float* __restrict__ diff, const float* __restrict__ centroids,
+                       float* __restrict__ radius) {
+    const uint32_t l = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (l >= nlist) {
+        return;
+    }
+    const float* c = centroids + static_cast<uint64_t>(l) * dim;
+    const float inv255 = 1.0f / 255.0f;
+    float worst = 0.f;
+    for (uint32_t p = list_off[l] + lane; p < list_off[l + 1]; p += 32) {
+        const uint8_t* row = codes + static_cast<uint64_t>(p) * code_stride;
+        float s = 0.f;
+        for (uint32_t d0 = 0; d0 < dim; d0 += 16) {
+            uint4 v = __ldg(reinterpret_cast<const uint4*>(row + d0));
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                uint32_t d = d0 + j;
+                if (d < dim) {
+                    float code = static_cast<float>((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+                    float x = fmaf(__fmul_rn(code, inv255), __ldg(diff + d), __ldg(lower + d));
+                    float t = x - __ldg(c + d);
+                    s = fmaf(t, t, s);
+                }
+            }
+        }
+        worst = fmaxf(worst, s);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+    }
+    if (lane == 0) {
+        radius[l] = sqrtf(worst) * 1.00001f;
+    }
 }
 
 // One warp per query: qw[q][d] = q_d * scale_d (zero padded) and
@@ -772,6 +817,12 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.coef_c = ix->metric == VB200_METRIC_L2 ? -2.0f : -1.0f;
     p.inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(ix->dim));
     p.metric = ix->metric;
+    ws.pruning = sq8 && ix->prune_lists && ix->list_radius.ptr != nullptr;
+    if (ws.pruning) {
+        p.centroids = ix->centroids.ptr;
+        p.list_radius = ix->list_radius.ptr;
+    }
+    p.scanned = reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 3);
     if (sq8) {
         VB_LAUNCH(sq8_query_prep_kernel, static_cast<uint32_t>((nq + 3) / 4), 128, 0, q_dev, nq, ix->dim,
                   ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
@@ -1013,6 +1064,9 @@ extern "C" int
 vb200_ivf_set_centroids(vb200_ivf_t ix, const float* centroids) {
     VB_CHECK_ARG(ix != nullptr && centroids != nullptr, "null pointer");
     std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "centroids cannot change after vectors were added");
+    }
     const size_t n = static_cast<size_t>(ix->nlist) * ix->dim;
     VB_TRY(ix->centroids.reserve(n));
     VB_CUDA(cudaMemcpyAsync(ix->centroids.ptr, centroids, n * sizeof(float), cudaMemcpyDefault,
@@ -1278,6 +1332,11 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
         VB_LAUNCH(sq8_code_norm_kernel, static_cast<uint32_t>((n_new_stored + 127) / 128), 128, 0,
                   new_codes.ptr, n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_norm.ptr);
     }
+    if (ix->quant == VB200_QUANT_SQ8) {
+        VB_TRY(ix->list_radius.reserve(nlist));
+        VB_LAUNCH(sq8_list_radius_kernel, (nlist * 32 + 127) / 128, 128, 0, new_codes.ptr, stride, dim,
+                  new_off_dev.ptr, nlist, ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->list_radius.ptr);
+    }
     VB_TRY(sync_stream());
     // 7. commit
     ix->code_norm = std::move(new_norm);
@@ -1386,11 +1445,11 @@ vb200_ivf_search(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, 
               ix->labels.ptr, ws.out_ids.ptr, ws.out_dists.ptr);
     VB_TRY(copy_out(ids, ws.out_ids.ptr, total));
     VB_TRY(copy_out(dists, ws.out_dists.ptr, total));
-    uint64_t scan_bytes = 0;
-    VB_CUDA(cudaMemcpyAsync(&scan_bytes, ws.scalars.ptr, sizeof(uint64_t), cudaMemcpyDeviceToHost,
-                            current_stream()));
+    uint64_t scalars[4] = {0, 0, 0, 0};
+    VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
-    ix->last_scan_bytes = static_cast<int64_t>(scan_bytes);
+    ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
+    ix->last_scanned_bytes = static_cast<int64_t>(ws.pruning ? scalars[3] : scalars[0]);
     return 0;
 }
 
@@ -1436,17 +1495,30 @@ vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint
     VB_TRY(search_status);
     VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
               ix->labels.ptr, keys_dev, labels_dev);
-    uint64_t scan_bytes = 0;
-    VB_CUDA(cudaMemcpyAsync(&scan_bytes, ix->ws.scalars.ptr, sizeof(uint64_t), cudaMemcpyDeviceToHost,
-                            current_stream()));
+    uint64_t scalars[4] = {0, 0, 0, 0};
+    VB_CUDA(cudaMemcpyAsync(scalars, ix->ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
-    ix->last_scan_bytes = static_cast<int64_t>(scan_bytes);
+    ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
+    ix->last_scanned_bytes = static_cast<int64_t>(ix->ws.pruning ? scalars[3] : scalars[0]);
     return 0;
 }
 
 extern "C" int64_t
 vb200_ivf_last_scan_bytes(vb200_ivf_t ix) {
     return ix == nullptr ? 0 : ix->last_scan_bytes;
+}
+
+extern "C" int64_t
+vb200_ivf_last_scanned_bytes(vb200_ivf_t ix) {
+    return ix == nullptr ? 0 : ix->last_scanned_bytes;
+}
+
+extern "C" int
+vb200_ivf_set_list_pruning(vb200_ivf_t ix, int enable) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    ix->prune_lists = enable != 0;
+    return 0;
 }
 
 extern "C" int

@@ -54,6 +54,12 @@ struct ScanParams {
     float coef_c;
     float inv_sqrt_d;            // RaBitQ
     int metric;
+    // SQ8 list pruning (both null = off): a list whose decoded rows all lie within list_radius[l]
+    // of centroids[l] cannot hold anything closer to q than the triangle inequality allows; when
+    // that is already worse than the query's bound the (query, list) pair is dropped unscanned.
+    const float* centroids;      // [nlist x dim]
+    const float* list_radius;    // [nlist] max |decoded row - centroid|, rounded up
+    unsigned long long* scanned; // bytes of codes actually scanned (pairs kept x list length x code size)
 };
 
 // Per-tile selection state in shared memory.
@@ -325,9 +331,92 @@ ivf_sq8_scan_kernel(const ScanParams p) {
     while (scan_next_item<QT>(p, s_item, it)) {
         const uint32_t list = it.list;
         const uint32_t pbeg = it.pbeg;
-        const int nqt = static_cast<int>(it.nqt);
-        const int ng = (nqt + 3) >> 2;
-        if (threadIdx.x < QT) {
+        int nqt = static_cast<int>(it.nqt);
+        if (p.list_radius != nullptr) {
+            // Eight threads per query measure the query against the list's centroid; the pair
+            // survives unless even the nearest point of the list's ball is beyond the bound.
+            static_assert(SCAN_THREADS == QT * 8, "eight threads per query of the tile");
+            const int qi = threadIdx.x >> 3, part = threadIdx.x & 7;
+            float dot = 0.f, qq = 0.f;
+            uint32_t q = 0;
+            if (qi < nqt) {
+                q = it.pair_q[pbeg + qi];
+                const float* qv = p.queries + static_cast<uint64_t>(q) * p.dim;
+                const float* cv = p.centroids + static_cast<uint64_t>(list) * p.dim;
+                for (uint32_t d = part; d < p.dim; d += 8) {
+                    const float x = __ldg(qv + d), c = __ldg(cv + d);
+                    if (p.metric == 0) {
+                        const float t = x - c;
+                        dot = fmaf(t, t, dot);
+                    } else {
+                        dot = fmaf(x, c, dot);
+                        qq = fmaf(x, x, qq);
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                qq += __shfl_xor_sync(0xffffffffu, qq, o);
+            }
+            if (part == 0 && qi < QT) {
+                bool keep = qi < nqt;
+                if (keep) {
+                    const uint32_t u = p.thr_g[q];
+                    if (u <= float_to_ordered(INFINITY)) {   // the query has a bound already
+                        const float bound = ordered_to_float(u);
+                        const float r = __ldg(p.list_radius + list);
+                        // slack: the distances compared here and in the scan differ in rounding only
+                        float lower;
+                        if (p.metric == 0) {
+                            const float gap = sqrtf(dot) - r;
+                            lower = gap > 0.f ? gap * gap : 0.f;
+                            keep = !(lower > bound * 1.001f + 1e-4f * dot);
+                        } else {
+                            lower = 1.0f - dot - sqrtf(qq) * r;
+                            keep = !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
+                        }
+                    }
+                }
+                ts.cnt[qi] = keep ? 1u : 0u;   // borrowed as the keep flag until the tile is set up
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                // compact the kept queries to the front of the tile
+                int kept = 0;
+                for (int i = 0; i < nqt; ++i) {
+                    if (ts.cnt[i] != 0) {
+                        ts.qidx[kept] = it.pair_q[pbeg + i];
+                        ts.slot[kept] = it.pair_slot[pbeg + i];
+                        ++kept;
+                    }
+                }
+                s_item[0] = static_cast<uint32_t>(kept);
+                if (kept > 0 && p.scanned != nullptr) {
+                    atomicAdd(p.scanned, static_cast<unsigned long long>(kept) *
+                                             (p.list_off[list + 1] - p.list_off[list]) * p.dim);
+                }
+            }
+            __syncthreads();
+            nqt = static_cast<int>(s_item[0]);
+            if (nqt == 0) {
+                continue;
+            }
+            if (threadIdx.x < QT) {
+                const int i = threadIdx.x;
+                if (i < nqt) {
+                    const uint32_t qk = ts.qidx[i];
+                    ts.qa[i] = __ldg(p.qa + qk);
+                    ts.set_bound(i, p.thr_g[qk]);
+                } else {
+                    ts.qidx[i] = 0;
+                    ts.slot[i] = 0;
+                    ts.qa[i] = 0.f;
+                    ts.set_bound(i, 0u);
+                }
+                ts.cnt[i] = 0;
+            }
+        } else if (threadIdx.x < QT) {
             int qi = threadIdx.x;
             if (qi < nqt) {
                 uint32_t q = it.pair_q[pbeg + qi];
@@ -343,6 +432,7 @@ ivf_sq8_scan_kernel(const ScanParams p) {
             }
             ts.cnt[qi] = 0;
         }
+        const int ng = (nqt + 3) >> 2;
         __syncthreads();
         // weights of the tile's queries as [dpad/4][QT] float4 (zeros for the unused slots of the
         // last group of four)

@@ -263,6 +263,13 @@ class IvfHandle:
                                                  nprobe, factor, ptr(bucket_ids, np.int32), cb, None,
                                                  ptr(keys_dev), ptr(labels_dev)))
 
+    def last_scanned_bytes(self) -> int:
+        """Bytes of codes the last search read after list pruning (<= last_scan_bytes)."""
+        return int(self._lib.vb200_ivf_last_scanned_bytes(self._h))
+
+    def set_list_pruning(self, enable: bool) -> None:
+        check(self._lib.vb200_ivf_set_list_pruning(self._h, int(bool(enable))))
+
     def last_scan_bytes(self) -> int:
         return int(self._lib.vb200_ivf_last_scan_bytes(self._h))
 
