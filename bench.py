@@ -11,6 +11,12 @@ results resident in HBM; `e2e` times the same call with pinned host buffers, so 
 copies are inside the timed region.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Two more workloads time the dense contractions of the path on the tensor cores and print the same
+kind of line with a `roofline` bound of "tensor" (they are not the headline):
+
+    python bench.py --workload kmeans       # k-means training, 1,000,000 x 128 against 4,096 centroids
+    python bench.py --workload bruteforce   # exact bf16 inner-product kNN, one GPU's 6,250,000 x 768 shard
 """
 from __future__ import annotations
 
@@ -280,15 +286,215 @@ def run_reference_arm(args) -> None:
 # ------------------------------------------------------------------------------------------------
 # engine arm
 # ------------------------------------------------------------------------------------------------
+# ------------------------------------------------------------------------------------------------
+# dense workloads (tensor-core kernels)
+# ------------------------------------------------------------------------------------------------
+def measured_tensor_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured (burst)"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def run_dense_workload(args) -> None:
+    """k-means training (second config of BASELINE.json) or bf16 BruteForce search (one GPU's shard
+    of the fifth).  Under torchrun every rank works on its own rows: k-means ranks are replicas of
+    the same job on different data, BruteForce ranks hold consecutive row ranges of one base and
+    merge their partial top-k after an all-gather."""
+    import torch
+
+    from vsag_b200 import engine, parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    def timed(fn) -> float:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    g = torch.Generator(device=device)
+    peak, peak_kind = measured_tensor_peak()
+    sampler = ClockSampler(device.index or 0)
+    if args.workload == "kmeans":
+        n, dim, k = scaled(1_000_000), 128, max(64, scaled(4096))
+        g.manual_seed(1 + rank)
+        centres = torch.rand((k, dim), generator=g, device=device) * 2.0 - 1.0
+        x = centres[torch.randint(0, k, (n,), generator=g, device=device)]
+        x = (x + 0.1 * torch.randn((n, dim), generator=g, device=device)).contiguous()
+        seeds = x[:k].clone()
+        engine.kmeans_train(x, seeds, args.warmup)                      # warm-up iterations
+        launches0 = engine.kernel_launches()
+        if rank == 0:
+            sampler.start()
+        torch.cuda.nvtx.range_push("timed_steps")
+        ms = timed(lambda: engine.kmeans_train(x, seeds, args.steps)) / args.steps
+        torch.cuda.nvtx.range_pop()
+        clocks = sampler.stop() if rank == 0 else None
+        launches = engine.kernel_launches() - launches0
+        x_host = torch.empty((n, dim), dtype=torch.float32, pin_memory=True)
+        x_host.copy_(x)
+        seeds_host = seeds.cpu().numpy()
+        e2e_ms = timed(lambda: engine.kmeans_train(x_host, seeds_host, args.steps)) / args.steps
+        flops = 2.0 * n * k * dim
+        line = {
+            "metric": "k-means Lloyd iterations, 1M x 128 rows against 4,096 centroids", "value": world * n / (ms / 1e3),
+            "unit": "rows assigned/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16x3 (split fp32), fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "k-means training: one step = one Lloyd iteration (assignment + centroid update)",
+                       "rows": n, "dim": dim, "centroids": k, "init": "first rows",
+                       "l2_policy": "points (512 MB) exceed the 126 MB L2; no flush between iterations",
+                       "parallelism": f"{world} independent replica(s)"},
+            "e2e": {"value": world * n / (e2e_ms / 1e3), "unit": "rows assigned/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": n * dim * 4 // args.steps, "d2h_bytes_per_step": (k * dim * 4 + n * 4) // args.steps},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "tc_candidates_kernel<0> (assignment)", "achieved": flops / (ms / 1e3) / 1e12,
+                         "peak": peak, "unit": "TFLOP/s", "frac": flops / (ms / 1e3) / 1e12 / peak, "peak_source": peak_kind,
+                         "traffic": None,
+                         "note": "achieved = 2*rows*centroids*dim per iteration over the whole iteration's time; the kernel "
+                                 "issues three bf16 MMAs per product (hi*hi, hi*lo, lo*hi)"},
+        }
+        if rank == 0 and not env_int("VB200_BENCH_SKIP_EXTRAS", 0):
+            from oracle import pyoracle as oracle
+
+            sample = min(n, env_int("VB200_CPU_SAMPLE", 20000))
+            xs, cs = x[:sample].cpu().numpy(), seeds_host
+            t0 = time.perf_counter()
+            oracle.kmeans_assign(xs, cs)
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": sample / dt, "unit": "rows assigned/s", "cores": oracle.num_threads(),
+                                    "kind": "port", "sample": f"assignment of {sample} of {n} rows, {dt:.2f} s"}
+    else:
+        n, dim, nq, k = scaled(6_250_000), 768, max(128, scaled(10_000)), 100
+        ix = engine.BfHandle(dim, engine.METRIC_IP, engine.QUANT_BF16)
+        g.manual_seed(6 + rank)
+        for b in range(0, n, 500_000):
+            c = min(500_000, n - b)
+            rows = torch.randn((c, dim), generator=g, device=device)
+            rows = (rows / rows.norm(dim=1, keepdim=True)).contiguous()
+            ix.add(rows, torch.arange(rank * n + b, rank * n + b + c, dtype=torch.int64, device=device))
+        del rows
+        gq = torch.Generator(device=device)
+        gq.manual_seed(7)
+        q = torch.randn((nq, dim), generator=gq, device=device)
+        q = (q / q.norm(dim=1, keepdim=True)).contiguous()
+        out_ids = torch.empty((nq, k), dtype=torch.int64, device=device)
+        out_d = torch.empty((nq, k), dtype=torch.float32, device=device)
+        if world > 1:
+            keys_local = torch.empty((nq, k), dtype=torch.int64, device=device)
+            labels_local = torch.empty((nq, k), dtype=torch.int64, device=device)
+            keys_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
+            labels_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
+
+        def step(queries=q, ids=out_ids, dists=out_d):
+            if world == 1:
+                ix.search(queries, k, out=(ids, dists))
+            else:
+                ix.search_partial(queries, k, keys_local, labels_local)
+                parallel.exchange_partials(keys_local, labels_local, keys_all, labels_all, dist)
+                engine.merge_partials(keys_all, labels_all, world, nq, k, out=(ids, dists))
+
+        for _ in range(args.warmup):
+            step()
+        launches0 = engine.kernel_launches()
+        if rank == 0:
+            sampler.start()
+        torch.cuda.nvtx.range_push("timed_steps")
+        ms = timed(lambda: [step() for _ in range(args.steps)]) / args.steps
+        torch.cuda.nvtx.range_pop()
+        clocks = sampler.stop() if rank == 0 else None
+        launches = engine.kernel_launches() - launches0
+        q_host = torch.empty((nq, dim), dtype=torch.float32, pin_memory=True)
+        q_host.copy_(q)
+        ids_host = torch.empty((nq, k), dtype=torch.int64, pin_memory=True)
+        d_host = torch.empty((nq, k), dtype=torch.float32, pin_memory=True)
+
+        def step_e2e():
+            if world == 1:
+                step(q_host, ids_host, d_host)
+            else:
+                q.copy_(q_host, non_blocking=True)
+                step()
+                ids_host.copy_(out_ids, non_blocking=True)
+                d_host.copy_(out_d, non_blocking=True)
+
+        step_e2e()
+        e2e_ms = timed(lambda: [step_e2e() for _ in range(args.steps)]) / args.steps
+        flops = 2.0 * n * dim * nq
+        line = {
+            "metric": "BruteForce bf16 inner-product kNN, k=100, 10,000 queries", "value": nq / (ms / 1e3),
+            "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16, fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "exact kNN over bf16 rows: one step = one search of the whole query batch",
+                       "rows_per_gpu": n, "rows": n * world, "dim": dim, "n_query": nq, "k": k,
+                       "l2_policy": "the base (9.6 GB per GPU) exceeds the 126 MB L2; no flush between steps",
+                       "parallelism": f"rows sharded over {world} GPU(s), per-shard top-k merged after an all-gather"},
+            "e2e": {"value": nq / (e2e_ms / 1e3), "unit": "queries/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": nq * dim * 4, "d2h_bytes_per_step": nq * k * 12},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "tc_candidates_kernel<1>", "achieved": flops / (ms / 1e3) / 1e12,
+                         "peak": peak, "unit": "TFLOP/s", "frac": flops / (ms / 1e3) / 1e12 / peak, "peak_source": peak_kind,
+                         "traffic": None, "note": "achieved = 2*rows*dim*queries per GPU over the whole step's time"},
+        }
+        if rank == 0 and world == 1 and not env_int("VB200_BENCH_SKIP_EXTRAS", 0):
+            from oracle import pyoracle as oracle
+
+            sub_rows, sub_q = min(n, 200_000), min(nq, env_int("VB200_CPU_SAMPLE", 64))
+            g2 = torch.Generator(device=device)
+            g2.manual_seed(6)
+            rows = torch.randn((sub_rows, dim), generator=g2, device=device)
+            rows = (rows / rows.norm(dim=1, keepdim=True)).cpu().numpy()
+            base16 = oracle.float_to_bf16(rows)
+            qs = q[:sub_q].cpu().numpy()
+            t0 = time.perf_counter()
+            oracle.bf_search_bf16(base16, qs, k, metric=1)
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": sub_q / dt * sub_rows / n, "unit": "queries/s", "cores": oracle.num_threads(),
+                                    "kind": "port",
+                                    "sample": f"{sub_q} queries against {sub_rows} of {n} rows in {dt:.2f} s, scaled by rows"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--workload", default="ivf_sq8", choices=["ivf_sq8", "kmeans", "bruteforce"])
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "engine":
         args.warmup = 3
+    if args.workload != "ivf_sq8" and args.impl == "engine":
+        run_dense_workload(args)
+        return
 
     if args.impl == "reference":
         run_reference_arm(args)

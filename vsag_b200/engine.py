@@ -107,9 +107,12 @@ def kmeans_init(data, k: int, seed: int = 47, want_rows: bool = False):
 
 def kmeans_train(data, init_centroids: np.ndarray, iters: int):
     n, d = data.shape
-    centroids = np.ascontiguousarray(init_centroids, dtype=np.float32).copy()
+    if _is_torch(init_centroids):
+        centroids = init_centroids.detach().clone().contiguous()
+    else:
+        centroids = np.ascontiguousarray(init_centroids, dtype=np.float32).copy()
     k = centroids.shape[0]
-    labels = np.empty(n, np.int32)
+    labels = _empty_like_side(data, (n,), np.int32)
     err = C.c_double(0.0)
     check(_capi.load().vb200_kmeans_train(ptr(data, np.float32), n, d, k, iters, ptr(centroids),
                                           ptr(labels), C.byref(err)))
@@ -145,9 +148,12 @@ def rabitq_process_query(queries, rotation, centroid):
     return out
 
 
-def merge_partials(keys_dev, labels_dev, parts: int, nq: int, k: int):
-    ids = np.empty((nq, k), np.int64)
-    dists = np.empty((nq, k), np.float32)
+def merge_partials(keys_dev, labels_dev, parts: int, nq: int, k: int, out=None):
+    if out is None:
+        ids = np.empty((nq, k), np.int64)
+        dists = np.empty((nq, k), np.float32)
+    else:
+        ids, dists = out
     check(_capi.load().vb200_merge_partials(ptr(keys_dev), ptr(labels_dev), parts, nq, k, ptr(ids),
                                             ptr(dists)))
     return ids, dists
