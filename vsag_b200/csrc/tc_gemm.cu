@@ -1,11 +1,13 @@
 // tcgen05 / TMEM candidate-generation GEMM: operand pre-tiling, the kernel and its launcher.
 #include "tc_gemm.cuh"
 
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 
 namespace vb200 {
 
-constexpr uint32_t TC_STAGES = 3;
+constexpr uint32_t TC_MAX_STAGES = 6;   // operand stages in flight; the launch picks how many fit
 
 __device__ __forceinline__ float
 widen_in(float v) {
@@ -103,8 +105,10 @@ tc_pretile_bf16(const uint16_t* src_dev, uint64_t rows, uint32_t dim, uint16_t* 
 // the kernel
 // ---------------------------------------------------------------------------------------------
 struct TcShared {
-    uint64_t full[TC_STAGES];    // chunk copies landed
-    uint64_t freed[TC_STAGES];   // MMAs that read the stage retired
+    uint64_t full[TC_MAX_STAGES];    // chunk copies landed
+    uint64_t freed[TC_MAX_STAGES];   // MMAs that read the stage retired
+    uint64_t a_full;             // resident-A mode: the item's A tile has landed
+    uint64_t a_free;             // resident-A mode: the last MMA that reads it has retired
     uint64_t acc_full[2];        // accumulator holds a finished tile
     uint64_t acc_free[2];        // accumulator drained by the 128 epilogue threads
     uint32_t tmem_base;
@@ -155,17 +159,22 @@ tc_candidates_kernel(const TcParams p) {
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_ops = p.n_terms == 3 ? 4u : 2u;
-    const uint32_t stage_bytes = n_ops * TC_CHUNK_BYTES;
+    const uint32_t n_terms_op = p.n_terms == 3 ? 2u : 1u;                       // bf16 terms per operand
+    // resident-A mode: [A tile: chunks x terms][ring of B stages]; otherwise a ring of [A terms][B terms]
+    const uint32_t a_region_bytes = p.a_resident ? p.a.chunks * n_terms_op * TC_CHUNK_BYTES : 0u;
+    const uint32_t stage_bytes = (p.a_resident ? n_terms_op : n_ops) * TC_CHUNK_BYTES;
     const uint32_t chunks = p.a.chunks;
     const uint64_t m_tiles = (p.a.rows + TC_BM - 1) / TC_BM;
     const uint64_t n_tiles = (p.b.rows + TC_BN - 1) / TC_BN;
     const uint64_t n_items = m_tiles * p.n_split;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < TC_STAGES; ++s) {
-            mbar_init(&sh.full[s], 1);
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(&sh.full[s], p.a_resident ? 1 : 2);   // one arrival (with its byte count) per copy thread filling it
             mbar_init(&sh.freed[s], 1);
         }
+        mbar_init(&sh.a_full, 1);
+        mbar_init(&sh.a_free, 1);
         for (uint32_t a = 0; a < 2; ++a) {
             mbar_init(&sh.acc_full[a], 1);
             mbar_init(&sh.acc_free[a], TC_EPI_THREADS);
@@ -181,89 +190,44 @@ tc_candidates_kernel(const TcParams p) {
     tc_fence_after_sync();
     const uint32_t tmem_base = sh.tmem_base;
 
+    const uint32_t n_items32 = static_cast<uint32_t>(n_items);
+    const uint32_t n_tiles32 = static_cast<uint32_t>(n_tiles);
+    auto open_item = [&](uint32_t item, uint32_t& mtile, uint32_t& ntile0, uint32_t& tiles) {
+        mtile = item / p.n_split;
+        uint32_t split = item - mtile * p.n_split;
+        ntile0 = split * p.tiles_per_split;
+        uint32_t t1 = ntile0 + p.tiles_per_split;
+        if (t1 > n_tiles32) {
+            t1 = n_tiles32;
+        }
+        tiles = t1 > ntile0 ? t1 - ntile0 : 0;
+    };
     if (warp == TC_EPI_WARPS) {
-        // ---------------- controller: bulk copies and MMA issue (one thread) ----------------
-        // Everything here runs on one thread, so it is written for latency: 32-bit counters that
-        // wrap by compare instead of divide, descriptors prepared once per stage.
+        // ---------------- MMA issue (one thread) ----------------
+        // Written for latency: 32-bit counters that wrap by compare instead of divide, descriptors
+        // prepared once per stage.
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
-            const uint32_t n_items32 = static_cast<uint32_t>(n_items);
-            const uint32_t n_tiles32 = static_cast<uint32_t>(n_tiles);
             // Descriptor of stage 0 / operand 0; the others differ only in the start-address field,
             // which counts 16-byte units, so they are this value plus small constants kept in registers.
             const uint64_t desc0 = umma_desc(smem_u32(smem), 128, 1024);
             const uint64_t stage_units = stage_bytes >> 4;
             const uint64_t op_units = TC_CHUNK_BYTES >> 4;
-            uint64_t stage_desc = desc0;   // descriptor of the MMA side's current stage
+            const uint64_t ring0 = desc0 + (a_region_bytes >> 4);
+            const bool a_res = p.a_resident != 0;
+            uint64_t stage_desc = ring0;
             bool ok = true;
-
-            // load side: (item, tile, chunk) cursor, stage ring position and its phase
-            uint32_t l_item = blockIdx.x, l_tile = 0, l_chunk = 0, l_tiles = 0, l_mtile = 0, l_ntile0 = 0;
-            uint32_t l_stage = 0, l_phase = 0, l_count = 0;
-            auto open_item = [&](uint32_t item, uint32_t& mtile, uint32_t& ntile0, uint32_t& tiles) {
-                mtile = item / p.n_split;
-                uint32_t split = item - mtile * p.n_split;
-                ntile0 = split * p.tiles_per_split;
-                uint32_t t1 = ntile0 + p.tiles_per_split;
-                if (t1 > n_tiles32) {
-                    t1 = n_tiles32;
-                }
-                tiles = t1 > ntile0 ? t1 - ntile0 : 0;
-            };
-            if (l_item < n_items32) {
-                open_item(l_item, l_mtile, l_ntile0, l_tiles);
-            }
-            auto issue_load = [&]() -> bool {
-                while (l_item < n_items32 && l_tile >= l_tiles) {
-                    l_item += gridDim.x;
-                    l_tile = 0;
-                    l_chunk = 0;
-                    if (l_item < n_items32) {
-                        open_item(l_item, l_mtile, l_ntile0, l_tiles);
-                    }
-                }
-                if (l_item >= n_items32) {
-                    return true;
-                }
-                if (l_count >= TC_STAGES) {
-                    // the stage's previous use must have been consumed by the tensor core
-                    if (!mbar_wait(&sh.freed[l_stage], l_phase ^ 1u)) {
-                        return false;
-                    }
-                }
-                unsigned char* dst = smem + l_stage * stage_bytes;
-                const size_t a_off = (static_cast<size_t>(l_mtile) * chunks + l_chunk) * TC_CHUNK_ELEMS;
-                const size_t b_off = (static_cast<size_t>(l_ntile0 + l_tile) * chunks + l_chunk) * TC_CHUNK_ELEMS;
-                mbar_expect_tx(&sh.full[l_stage], stage_bytes);
-                if (p.n_terms == 3) {
-                    bulk_copy_g2s(dst, p.a.hi + a_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
-                    bulk_copy_g2s(dst + TC_CHUNK_BYTES, p.a.lo + a_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
-                    bulk_copy_g2s(dst + 2 * TC_CHUNK_BYTES, p.b.hi + b_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
-                    bulk_copy_g2s(dst + 3 * TC_CHUNK_BYTES, p.b.lo + b_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
-                } else {
-                    bulk_copy_g2s(dst, p.a.hi + a_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
-                    bulk_copy_g2s(dst + TC_CHUNK_BYTES, p.b.hi + b_off, TC_CHUNK_BYTES, &sh.full[l_stage]);
-                }
-                ++l_count;
-                if (++l_stage == TC_STAGES) {
-                    l_stage = 0;
-                    l_phase ^= 1u;
-                }
-                if (++l_chunk == chunks) {
-                    l_chunk = 0;
-                    ++l_tile;
-                }
-                return true;
-            };
-
-            for (uint32_t i = 0; i + 1 < TC_STAGES && ok; ++i) {
-                ok = issue_load();
-            }
-            // MMA side: stage ring position / phase, accumulator ring position / phase
-            uint32_t m_stage = 0, m_phase = 0, acc = 0, acc_phase = 0, tiles_started = 0;
+            uint32_t m_stage = 0, m_phase = 0, acc = 0, acc_phase = 0, tiles_started = 0, a_phase = 0;
             for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
                 uint32_t mtile, ntile0, tiles;
                 open_item(item, mtile, ntile0, tiles);
+                if (a_res && tiles > 0) {
+                    ok = mbar_wait(&sh.a_full, a_phase);
+                    a_phase ^= 1u;
+                    if (!ok) {
+                        break;
+                    }
+                }
                 for (uint32_t t = 0; t < tiles && ok; ++t) {
                     if (tiles_started >= 2) {
                         // the epilogue must have drained this accumulator's previous tile
@@ -286,27 +250,31 @@ tc_candidates_kernel(const TcParams p) {
                             const uint64_t koff = kk * 16;
                             const uint32_t accumulate = (c == 0 && kk == 0) ? 0u : 1u;
                             if (p.n_terms == 3) {
-                                const uint64_t a_hi = stage_desc + koff, a_lo = a_hi + op_units;
-                                const uint64_t b_hi = a_hi + 2 * op_units, b_lo = a_hi + 3 * op_units;
+                                const uint64_t a_hi = (a_res ? desc0 + c * 2 * op_units : stage_desc) + koff;
+                                const uint64_t b_hi = (a_res ? stage_desc : stage_desc + 2 * op_units) + koff;
+                                const uint64_t a_lo = a_hi + op_units, b_lo = b_hi + op_units;
                                 umma_bf16(d_tmem, a_hi, b_hi, idesc, accumulate);
                                 umma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
                                 umma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
                             } else {
-                                const uint64_t a = stage_desc + koff;
-                                umma_bf16(d_tmem, a, a + op_units, idesc, accumulate);
+                                const uint64_t a = (a_res ? desc0 + c * op_units : stage_desc) + koff;
+                                const uint64_t b = (a_res ? stage_desc : stage_desc + op_units) + koff;
+                                umma_bf16(d_tmem, a, b, idesc, accumulate);
                             }
                         }
                         umma_commit(&sh.freed[m_stage]);
                         if (c + 1 == chunks) {
                             umma_commit(&sh.acc_full[acc]);
+                            if (a_res && t + 1 == tiles) {
+                                umma_commit(&sh.a_free);   // the item's A tile may be overwritten
+                            }
                         }
                         stage_desc += stage_units;
-                        if (++m_stage == TC_STAGES) {
+                        if (++m_stage == p.stages) {
                             m_stage = 0;
                             m_phase ^= 1u;
-                            stage_desc = desc0;
+                            stage_desc = ring0;
                         }
-                        ok = issue_load();
                     }
                     ++tiles_started;
                     if (++acc == 2) {
@@ -321,13 +289,88 @@ tc_candidates_kernel(const TcParams p) {
             }
         }
         __syncwarp();
+    } else if (warp > TC_EPI_WARPS) {
+        // ---------------- operand copies: one thread for A, one for B ----------------
+        // The copy engine of an SM moves a 16 KiB bulk copy at well under the rate the MMAs eat
+        // operands when a single thread issues them one after the other; two issuers overlap.
+        if (lane == 0) {
+            const bool is_a = warp == TC_EPI_WARPS + 1;
+            const TcOperand& op = is_a ? p.a : p.b;
+            const uint32_t terms = n_terms_op;
+            const bool a_res = p.a_resident != 0;
+            bool ok = true;
+            if (is_a && a_res) {
+                // the whole A tile of an item at once, into the resident region
+                uint32_t a_phase = 0, n_loaded = 0;
+                for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
+                    uint32_t mtile, ntile0, tiles;
+                    open_item(item, mtile, ntile0, tiles);
+                    if (tiles == 0) {
+                        continue;
+                    }
+                    if (n_loaded > 0) {
+                        ok = mbar_wait(&sh.a_free, a_phase);   // previous item's MMAs are done with it
+                        a_phase ^= 1u;
+                        if (!ok) {
+                            break;
+                        }
+                    }
+                    mbar_expect_tx(&sh.a_full, a_region_bytes);
+                    for (uint32_t c = 0; c < chunks; ++c) {
+                        const size_t off = (static_cast<size_t>(mtile) * chunks + c) * TC_CHUNK_ELEMS;
+                        unsigned char* dst = smem + c * terms * TC_CHUNK_BYTES;
+                        bulk_copy_g2s(dst, op.hi + off, TC_CHUNK_BYTES, &sh.a_full);
+                        if (terms == 2) {
+                            bulk_copy_g2s(dst + TC_CHUNK_BYTES, op.lo + off, TC_CHUNK_BYTES, &sh.a_full);
+                        }
+                    }
+                    ++n_loaded;
+                }
+            } else {
+                // ring of stages; in resident-A mode the B thread fills whole stages
+                const uint32_t op_off = (is_a || a_res) ? 0u : terms * TC_CHUNK_BYTES;   // A terms first, then B terms
+                uint32_t stage = 0, phase = 0, count = 0;
+                for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
+                    uint32_t mtile, ntile0, tiles;
+                    open_item(item, mtile, ntile0, tiles);
+                    for (uint32_t t = 0; t < tiles && ok; ++t) {
+                        const size_t row_tile = is_a ? mtile : ntile0 + t;
+                        for (uint32_t c = 0; c < chunks; ++c) {
+                            if (count >= p.stages) {
+                                // the stage's previous use must have been consumed by the tensor core
+                                ok = mbar_wait(&sh.freed[stage], phase ^ 1u);
+                                if (!ok) {
+                                    break;
+                                }
+                            }
+                            unsigned char* dst = smem + a_region_bytes + stage * stage_bytes + op_off;
+                            const size_t off = (row_tile * chunks + c) * TC_CHUNK_ELEMS;
+                            mbar_expect_tx(&sh.full[stage], terms * TC_CHUNK_BYTES);
+                            bulk_copy_g2s(dst, op.hi + off, TC_CHUNK_BYTES, &sh.full[stage]);
+                            if (terms == 2) {
+                                bulk_copy_g2s(dst + TC_CHUNK_BYTES, op.lo + off, TC_CHUNK_BYTES, &sh.full[stage]);
+                            }
+                            ++count;
+                            if (++stage == p.stages) {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                atomicExch(p.error_flag, 1);
+            }
+        }
+        __syncwarp();
     } else {
         // ---------------- epilogue: drain the accumulator, keep the m best per row ----------------
         const uint32_t quarter = warp & 3u;          // TMEM lanes 32 * quarter .. + 31
         const uint32_t cgroup = warp >> 2;           // columns 32 * cgroup .. + 31 of every tile
         const uint32_t row = quarter * 32 + lane;
         uint64_t* buf = p.scratch + ((static_cast<uint64_t>(blockIdx.x) * TC_BM + row) * TC_COL_GROUPS + cgroup) * p.cap;
-        uint64_t* sort_area = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(TC_STAGES) * stage_bytes) +
+        uint64_t* sort_area = reinterpret_cast<uint64_t*>(smem + a_region_bytes + static_cast<size_t>(p.stages) * stage_bytes) +
                               static_cast<size_t>(warp) * p.cap;
         uint64_t gtile = 0;
         bool ok = true;
@@ -360,7 +403,7 @@ tc_candidates_kernel(const TcParams p) {
             uint32_t bc0 = 0xFFFFFFFFu, bc1 = 0xFFFFFFFFu, bc2 = 0xFFFFFFFFu, bc3 = 0xFFFFFFFFu;
             for (uint64_t t = t0; t < t1 && ok; ++t, ++gtile) {
                 const uint32_t acc = static_cast<uint32_t>(gtile & 1);
-                ok = mbar_wait(&sh.acc_full[acc], static_cast<uint32_t>((gtile >> 1) & 1));
+                ok = mbar_wait_relaxed(&sh.acc_full[acc], static_cast<uint32_t>((gtile >> 1) & 1));
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     break;
@@ -396,15 +439,35 @@ tc_candidates_kernel(const TcParams p) {
                     // Scores of the block and their minimum first (two instructions per element);
                     // the selection code below runs only when the minimum beats the row's bound.
                     float sc[32];
+                    if (__all_sync(0xffffffffu, whole_tile)) {
+                        // the common case: every row and column of the block exists
+                        if (has_bias) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float4 b4 = has_bias ? *reinterpret_cast<const float4*>(&sh.bias[warp][i])
-                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
-                        const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+                            for (int i = 0; i < 32; i += 4) {
+                                const float4 b4 = *reinterpret_cast<const float4*>(&sh.bias[warp][i]);
+                                sc[i] = fmaf(p.alpha, __uint_as_float(r[i]), b4.x);
+                                sc[i + 1] = fmaf(p.alpha, __uint_as_float(r[i + 1]), b4.y);
+                                sc[i + 2] = fmaf(p.alpha, __uint_as_float(r[i + 2]), b4.z);
+                                sc[i + 3] = fmaf(p.alpha, __uint_as_float(r[i + 3]), b4.w);
+                            }
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const bool in_range = whole_tile || (valid_row && c0 + i + j < p.b.rows);
-                            sc[i + j] = in_range ? fmaf(p.alpha, __uint_as_float(r[i + j]), bb[j]) : INFINITY;
+                            for (int i = 0; i < 32; ++i) {
+                                sc[i] = p.alpha * __uint_as_float(r[i]);
+                            }
+                        }
+                    } else {
+                        const uint32_t cols_left = c0 < p.b.rows ? static_cast<uint32_t>(min(static_cast<uint64_t>(32), p.b.rows - c0)) : 0u;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 b4 = has_bias ? *reinterpret_cast<const float4*>(&sh.bias[warp][i])
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                            const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const bool in_range = valid_row && static_cast<uint32_t>(i + j) < cols_left;
+                                sc[i + j] = in_range ? fmaf(p.alpha, __uint_as_float(r[i + j]), bb[j]) : INFINITY;
+                            }
                         }
                     }
                     if (STORE) {
@@ -546,16 +609,58 @@ tc_candidates_kernel(const TcParams p) {
     }
 }
 
-// Largest per-row candidate buffer whose per-warp sort areas fit in shared memory beside the stages.
+// Shared memory a launch may use for operand stages and sort areas (the rest of the 227 KiB holds
+// the barriers, the bias slots and alignment slack).
+constexpr size_t TC_SMEM_BUDGET = 232448 - 4096;
+constexpr uint32_t TC_MIN_STAGES = 3;
+
+static size_t
+tc_stage_bytes(uint32_t n_terms) {
+    return static_cast<size_t>(n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES;
+}
+
+// Largest per-row candidate buffer whose per-warp sort areas fit beside the fewest stages.
 static uint32_t
 tc_cap_max(uint32_t n_terms) {
-    const size_t stage_total = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES;
-    const size_t room = 232448 - 4096 - stage_total;
+    const size_t room = TC_SMEM_BUDGET - TC_MIN_STAGES * tc_stage_bytes(n_terms);
     uint32_t cap_max = 64;
     while (static_cast<size_t>(cap_max) * 2 * TC_EPI_WARPS * sizeof(uint64_t) <= room && cap_max < 1024) {
         cap_max *= 2;
     }
     return cap_max;
+}
+
+// Shared-memory plan of a launch: whether the A tile of an item stays resident (it does when it
+// is at most 64 KiB, i.e. up to 128 dimensions of split fp32 or 256 of bf16: every B tile of the
+// item then costs only its own bytes), and as many ring stages as fit beside it and the sort
+// areas.  VB200_TC_STAGES / VB200_TC_A_RESIDENT=0 override the choices (for experiments).
+static void
+tc_plan(TcParams& p, size_t sort_bytes, size_t* smem_bytes) {
+    const uint32_t terms = p.n_terms == 3 ? 2u : 1u;
+    const size_t a_region = static_cast<size_t>(p.a.chunks) * terms * TC_CHUNK_BYTES;
+    const char* env_res = std::getenv("VB200_TC_A_RESIDENT");
+    bool resident = a_region <= 65536 && !(env_res != nullptr && env_res[0] == '0');
+    size_t per_stage = (resident ? terms : 2 * terms) * static_cast<size_t>(TC_CHUNK_BYTES);
+    size_t fixed = sort_bytes + (resident ? a_region : 0);
+    if (resident && (TC_SMEM_BUDGET - fixed) / per_stage < TC_MIN_STAGES) {
+        resident = false;
+        per_stage = 2 * terms * static_cast<size_t>(TC_CHUNK_BYTES);
+        fixed = sort_bytes;
+    }
+    uint32_t stages = static_cast<uint32_t>((TC_SMEM_BUDGET - fixed) / per_stage);
+    if (stages > TC_MAX_STAGES) {
+        stages = TC_MAX_STAGES;
+    }
+    const char* env = std::getenv("VB200_TC_STAGES");
+    if (env != nullptr && env[0] != 0) {
+        const uint32_t want = static_cast<uint32_t>(std::atoi(env));
+        if (want >= 2 && want <= stages) {
+            stages = want;
+        }
+    }
+    p.stages = stages;
+    p.a_resident = resident ? 1u : 0u;
+    *smem_bytes = fixed + stages * per_stage + 1024;
 }
 
 uint32_t
@@ -620,8 +725,9 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     p.error_flag = ws.error_flag.ptr;
 
     const bool small_m = m <= 4;
-    const size_t smem = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES +
-                        (small_m ? 0 : TC_EPI_WARPS * static_cast<size_t>(p.cap) * sizeof(uint64_t)) + 1024;
+    const size_t sort_bytes = small_m ? 0 : TC_EPI_WARPS * static_cast<size_t>(p.cap) * sizeof(uint64_t);
+    size_t smem = 0;
+    tc_plan(p, sort_bytes, &smem);
     auto kernel = small_m ? tc_candidates_kernel<0> : tc_candidates_kernel<1>;
     VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
@@ -672,7 +778,8 @@ tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_te
     VB_TRY(ws.error_flag.reserve(1));
     VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
     p.error_flag = ws.error_flag.ptr;
-    const size_t smem = static_cast<size_t>(TC_STAGES) * (n_terms == 3 ? 4 : 2) * TC_CHUNK_BYTES + 1024;
+    size_t smem = 0;
+    tc_plan(p, 0, &smem);
     auto kernel = tc_candidates_kernel<2>;
     VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);

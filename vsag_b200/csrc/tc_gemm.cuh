@@ -27,7 +27,7 @@ constexpr uint32_t TC_CHUNK_BYTES = TC_CHUNK_ELEMS * 2;   // 16 KiB
 constexpr uint32_t TC_COL_GROUPS = 4;      // epilogue warps per TMEM lane quarter; each takes 32 of a tile's columns
 constexpr uint32_t TC_EPI_WARPS = 4 * TC_COL_GROUPS;
 constexpr uint32_t TC_EPI_THREADS = 32 * TC_EPI_WARPS;
-constexpr uint32_t TC_THREADS = TC_EPI_THREADS + 32;   // + the warp that issues copies and MMAs
+constexpr uint32_t TC_THREADS = TC_EPI_THREADS + 96;   // + one warp each to issue the MMAs, the A copies and the B copies
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
 
 struct TcOperand {
@@ -47,6 +47,8 @@ struct TcParams {
     const float* row_bound;   // [a.rows] a score some column is known to reach (warm start), or nullptr
     uint32_t m;               // candidates kept per row
     uint32_t cap;             // per-row buffer, power of two >= m + 32
+    uint32_t stages;          // operand stages in shared memory (2 .. 6)
+    uint32_t a_resident;      // 1: the A tile of a work item stays in shared memory for all its B tiles
     uint32_t n_split;         // column ranges per row tile
     uint32_t tiles_per_split; // B tiles per range
     uint64_t* scratch;        // [grid][128][TC_COL_GROUPS][cap] candidate buffers
@@ -94,6 +96,27 @@ mbar_wait(uint64_t* bar, uint32_t parity) {
         if (done) {
             return true;
         }
+    }
+    return false;
+}
+
+// The same wait for the many epilogue threads: between polls they sleep, so that their polling
+// does not take issue slots from the three single threads that feed the tensor core.
+__device__ __forceinline__ bool
+mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (done) {
+            return true;
+        }
+        __nanosleep(128);
     }
     return false;
 }
