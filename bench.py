@@ -47,11 +47,11 @@ SIGMA = 0.15
 TRAIN_ROWS = 64 * NLIST          # the reference's default train_sample_count: max(65536, 64 * nlist)
 KMEANS_ITERS = 25                # hard-coded in IVFNearestPartition::Train
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel's two launches per step, from the
-# ncu capture of the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 126.9 MB +
-# 203.5 MB), scaled by 5 to the 10,000,000-row workload: the traffic is one pass over the probed
-# codes plus the partial-result slots, both proportional to the row count.
-SCAN_TRAFFIC_BYTES = 5 * (126.9e6 + 203.5e6)
+# dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel's launch, from the ncu capture of
+# the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 284.5 MB + 26.1 MB), scaled
+# by 5 to the 10,000,000-row workload: the traffic is one pass over the codes of the lists that
+# survive pruning plus the partial-result slots, both proportional to the row count.
+SCAN_TRAFFIC_BYTES = 5 * (284.5e6 + 26.1e6)
 
 
 def env_int(name: str, default: int) -> int:
