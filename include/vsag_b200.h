@@ -183,7 +183,7 @@ VB200_API int vb200_rabitq_process_query(const float* queries, uint64_t count, u
  * ------------------------------------------------------------------------------------------- */
 
 /* Replaces IVF::IVF (src/algorithm/ivf/ivf.cpp:412-474): nlist = buckets_count, quant =
- * base_quantization_type (VB200_QUANT_FP32 is not a bucket codec here; use SQ8 or RABITQ),
+ * base_quantization_type (VB200_QUANT_FP32, the reference's default, VB200_QUANT_SQ8 or VB200_QUANT_RABITQ),
  * use_reorder keeps the fp32 rows for exact rerank (precise_quantization_type fp32). */
 VB200_API int vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_reorder,
                      vb200_ivf_t* out);

@@ -110,6 +110,14 @@ def gen_uniform(seed: int, count: int, lo: float = 0.0, hi: float = 1.0) -> np.n
     return out
 
 
+def normalize_rows(x):
+    """Rows divided by their norms the way the reference's Normalize does."""
+    x, px = _a(x, np.float32)
+    out = np.empty_like(x)
+    lib().orc_normalize_rows(px, _u64(x.shape[0]), _u64(x.shape[1]), _p(out.ctypes.data))
+    return out
+
+
 # ---- scalar kernels ----------------------------------------------------------------------------
 def fp32_l2sqr(a, b) -> float:
     a, pa = _a(a, np.float32)
@@ -269,6 +277,21 @@ def build_lists(labels: np.ndarray, nlist: int):
     off = np.zeros(nlist + 1, np.int64)
     np.cumsum(sizes, out=off[1:])
     return off, order
+
+
+def ivf_fp32_search(rows, list_off, inner_ids, q, probes, k: int, metric: int = 0):
+    """IVF scan over fp32 buckets: rows in list order, offsets and ids as for ivf_sq8_search."""
+    rows, pr = _a(rows, np.float32)
+    list_off, po = _a(list_off, np.int64)
+    inner_ids, pi = _a(inner_ids, np.int64)
+    q, pq = _a(q, np.float32)
+    probes, pp = _a(probes, np.int32)
+    nq, d = q.shape
+    ids = np.empty((nq, k), np.int64)
+    dists = np.empty((nq, k), np.float32)
+    lib().orc_ivf_fp32_search(pr, po, pi, _u64(d), pq, _u64(nq), pp, _u64(probes.shape[1]), _i64(k), _i32(metric),
+                              _p(ids.ctypes.data), _p(dists.ctypes.data))
+    return ids, dists
 
 
 def ivf_sq8_search(codes, list_off, inner_ids, lower, diff, q, probes, k: int, metric: int = 0,

@@ -106,6 +106,26 @@ orc_fp32_l2sqr(const float* a, const float* b, uint64_t dim) {
     return sum;
 }
 
+/* Normalize (src/simd/generic.cpp:875-879) row by row: norm = sqrt(FP32ComputeIP(x, x)), every
+ * element divided by it; a zero norm divides by 1 (src/simd/kernels/scalar_op.h:40-42). */
+ORC_API void
+orc_normalize_rows(const float* x, uint64_t n, uint64_t dim, float* out) {
+    for (uint64_t r = 0; r < n; ++r) {
+        const float* a = x + r * dim;
+        float s = 0.0f;
+        for (uint64_t i = 0; i < dim; ++i) {
+            s = fmaf(a[i], a[i], s);
+        }
+        float norm = sqrtf(s);
+        if (norm == 0.0f) {
+            norm = 1.0f;
+        }
+        for (uint64_t i = 0; i < dim; ++i) {
+            out[r * dim + i] = a[i] / norm;
+        }
+    }
+}
+
 /* FP32ComputeIP, scalar order (src/simd/kernels/compute_ip.h:38-92 with Width 1). */
 ORC_API float
 orc_fp32_ip(const float* a, const float* b, uint64_t dim) {
@@ -727,6 +747,48 @@ orc_ivf_sq8_search(const uint8_t* codes,
                     for (int64_t t = 0; t < m; ++t) {
                         heap_offer_strict(&h, k, dist[t], inner_ids[r + t]);
                     }
+                }
+            }
+            heap_drain(&h, k, out_ids + (uint64_t)i * k, out_dists + (uint64_t)i * k);
+        }
+        free(h.a);
+    }
+}
+
+/* The same probe loop over fp32 buckets (FP32Quantizer::ComputeDistImpl,
+ * src/quantization/fp32_quantizer.cpp:163-190): rows[list_off[l] .. list_off[l+1]) are the rows of
+ * list l as they were added. */
+ORC_API void
+orc_ivf_fp32_search(const float* rows,
+                    const int64_t* list_off,
+                    const int64_t* inner_ids,
+                    uint64_t dim,
+                    const float* q,
+                    uint64_t nq,
+                    const int32_t* probes,
+                    uint64_t nprobe,
+                    int64_t k,
+                    int metric,
+                    int64_t* out_ids,
+                    float* out_dists) {
+#pragma omp parallel
+    {
+        orc_heap h;
+        h.a = (orc_rec*)malloc((size_t)(k + 2) * sizeof(orc_rec));
+        h.cap = k + 2;
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t i = 0; i < (int64_t)nq; ++i) {
+            const float* qi = q + (uint64_t)i * dim;
+            h.size = 0;
+            for (uint64_t p = 0; p < nprobe; ++p) {
+                int32_t l = probes[(uint64_t)i * nprobe + p];
+                if (l < 0) {
+                    continue;
+                }
+                for (int64_t r = list_off[l]; r < list_off[l + 1]; ++r) {
+                    const float* x = rows + (uint64_t)r * dim;
+                    float d = metric == 0 ? orc_fp32_l2sqr(x, qi, dim) : 1.0f - orc_fp32_ip(x, qi, dim);
+                    heap_offer_strict(&h, k, d, inner_ids[r]);
                 }
             }
             heap_drain(&h, k, out_ids + (uint64_t)i * k, out_dists + (uint64_t)i * k);

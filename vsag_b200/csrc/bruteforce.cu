@@ -119,6 +119,10 @@ using namespace vb200;
 struct vb200_bf {
     uint32_t dim = 0;
     int metric = 0, quant = 0;
+    // cosine: rows and queries are normalised, then it is the inner-product index
+    // (FP32Quantizer / HalfPrecisionQuantizer with METRIC_TYPE_COSINE)
+    bool cosine = false;
+    DevBuf<float> q_unit;
     uint64_t n = 0;
     DevBuf<float> base_f32;
     DevBuf<uint16_t> base_bf16;
@@ -162,8 +166,8 @@ extern "C" int
 vb200_bf_create(uint32_t dim, int metric, int quant, vb200_bf_t* out) {
     VB_CHECK_ARG(out != nullptr, "null output handle");
     VB_CHECK_ARG(dim > 0, "dim must be positive");
-    VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP,
-                 "metric_type must be l2 or ip for this engine (got %d)", metric);
+    VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP || metric == VB200_METRIC_COSINE,
+                 "metric_type must be l2, ip or cosine (got %d)", metric);
     VB_CHECK_ARG(quant == VB200_QUANT_FP32 || quant == VB200_QUANT_BF16,
                  "base_quantization_type must be fp32 or bf16 for this engine (got %d)", quant);
     if (vb200_device_count() <= 0) {
@@ -174,7 +178,8 @@ vb200_bf_create(uint32_t dim, int metric, int quant, vb200_bf_t* out) {
         VB_FAIL(VB200_NO_ENOUGH_MEMORY, "out of host memory");
     }
     ix->dim = dim;
-    ix->metric = metric;
+    ix->metric = metric == VB200_METRIC_COSINE ? VB200_METRIC_IP : metric;
+    ix->cosine = metric == VB200_METRIC_COSINE;
     ix->quant = quant;
     *out = ix;
     return 0;
@@ -213,18 +218,30 @@ vb200_bf_add(vb200_bf_t ix, const float* data, uint64_t count, const int64_t* id
     std::lock_guard<std::mutex> lock(ix->mu);
     VB_CHECK_ARG(ix->n + count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
     const uint64_t elems = count * ix->dim;
-    if (ix->quant == VB200_QUANT_FP32) {
+    if (ix->quant == VB200_QUANT_FP32 && !ix->cosine) {
         VB_TRY(bf_grow(ix->base_f32, ix->n * ix->dim, (ix->n + count) * ix->dim));
         VB_CUDA(cudaMemcpyAsync(ix->base_f32.ptr + ix->n * ix->dim, data, elems * sizeof(float),
                                 cudaMemcpyDefault, current_stream()));
     } else {
-        VB_TRY(bf_grow(ix->base_bf16, ix->n * ix->dim, (ix->n + count) * ix->dim));
         DevInput<float> x;
         VB_TRY(x.bind(data, elems));
-        uint64_t blocks = (elems + 255) / 256;
-        VB_CHECK_ARG(blocks <= 0x7fffffffu, "add batch too large");
-        VB_LAUNCH(float_to_bf16_kernel, static_cast<uint32_t>(blocks), 256, 0, x.ptr, elems,
-                  ix->base_bf16.ptr + ix->n * ix->dim);
+        DevBuf<float> unit_rows;
+        const float* xr = x.ptr;
+        if (ix->quant == VB200_QUANT_FP32) {
+            VB_TRY(bf_grow(ix->base_f32, ix->n * ix->dim, (ix->n + count) * ix->dim));
+            VB_TRY(normalize_rows_f32(x.ptr, count, ix->dim, ix->base_f32.ptr + ix->n * ix->dim));
+        } else {
+            if (ix->cosine) {
+                VB_TRY(unit_rows.reserve(elems));
+                VB_TRY(normalize_rows_f32(x.ptr, count, ix->dim, unit_rows.ptr));
+                xr = unit_rows.ptr;
+            }
+            VB_TRY(bf_grow(ix->base_bf16, ix->n * ix->dim, (ix->n + count) * ix->dim));
+            uint64_t blocks = (elems + 255) / 256;
+            VB_CHECK_ARG(blocks <= 0x7fffffffu, "add batch too large");
+            VB_LAUNCH(float_to_bf16_kernel, static_cast<uint32_t>(blocks), 256, 0, xr, elems,
+                      ix->base_bf16.ptr + ix->n * ix->dim);
+        }
         VB_TRY(sync_stream());
     }
     return bf_append_labels_and_norms(ix, ids, count);
@@ -238,6 +255,7 @@ vb200_bf_add_bf16(vb200_bf_t ix, const uint16_t* data, uint64_t count, const int
     }
     VB_CHECK_ARG(data != nullptr && ids != nullptr, "null pointer");
     VB_CHECK_ARG(ix->quant == VB200_QUANT_BF16, "index does not store bf16 rows");
+    VB_CHECK_ARG(!ix->cosine, "a cosine index normalises fp32 rows before rounding them: add them with vb200_bf_add");
     std::lock_guard<std::mutex> lock(ix->mu);
     VB_CHECK_ARG(ix->n + count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
     VB_TRY(bf_grow(ix->base_bf16, ix->n * ix->dim, (ix->n + count) * ix->dim));
@@ -270,6 +288,11 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
         VB_CUDA(cudaMemcpyAsync(ix->q_f32.ptr, queries, nq * dim * sizeof(float), cudaMemcpyHostToDevice,
                                 current_stream()));
         q_dev = ix->q_f32.ptr;
+    }
+    if (ix->cosine) {
+        VB_TRY(ix->q_unit.reserve(nq * dim));
+        VB_TRY(normalize_rows_f32(q_dev, nq, dim, ix->q_unit.ptr));
+        q_dev = ix->q_unit.ptr;
     }
     if (bf16) {
         VB_TRY(ix->q_bf16.reserve(nq * dim));

@@ -165,6 +165,59 @@ row_sqnorm_bf16(const uint16_t* M, uint64_t rows, uint32_t dim, float* sq) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Normalize (src/simd/generic.cpp:875-879): norm = sqrt(sum of fma(x_d, x_d, acc)) in ascending d,
+// every element divided by it (by 1 when the norm is 0, src/simd/kernels/scalar_op.h:40-42).
+// One warp per row: the row is staged in shared memory, lane 0 walks the chain, all lanes divide.
+// in == out is allowed.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+normalize_rows_kernel(const float* __restrict__ in, uint64_t rows, uint32_t dim, float* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* stage = reinterpret_cast<float*>(smem_raw) + static_cast<size_t>(threadIdx.x >> 5) * dim;
+    const uint64_t row = static_cast<uint64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const uint32_t lane = threadIdx.x & 31;
+    if (row >= rows) {
+        return;
+    }
+    const float* src = in + row * dim;
+    for (uint32_t d = lane; d < dim; d += 32) {
+        stage[d] = src[d];
+    }
+    __syncwarp();
+    float norm = 0.f;
+    if (lane == 0) {
+        float s = 0.f;
+        for (uint32_t d = 0; d < dim; ++d) {
+            s = fmaf(stage[d], stage[d], s);
+        }
+        norm = __fsqrt_rn(s);
+        if (norm == 0.f) {
+            norm = 1.0f;
+        }
+    }
+    norm = __shfl_sync(0xffffffffu, norm, 0);
+    float* dst = out + row * dim;
+    for (uint32_t d = lane; d < dim; d += 32) {
+        dst[d] = __fdiv_rn(stage[d], norm);
+    }
+}
+
+int
+normalize_rows_f32(const float* in, uint64_t rows, uint32_t dim, float* out) {
+    if (rows == 0) {
+        return 0;
+    }
+    const size_t smem = 4 * static_cast<size_t>(dim) * sizeof(float);
+    VB_CHECK_ARG(smem <= 200 * 1024, "dim too large to normalise on the device");
+    if (smem > 48 * 1024) {
+        VB_CUDA(cudaFuncSetAttribute(normalize_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+    }
+    VB_LAUNCH(normalize_rows_kernel, static_cast<uint32_t>((rows + 3) / 4), 128, smem, in, rows, dim, out);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // row-wise top-k over a materialised score matrix
 // ---------------------------------------------------------------------------------------------
 constexpr int SELECT_THREADS = 256;

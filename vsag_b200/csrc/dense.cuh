@@ -204,6 +204,9 @@ int dense_argmin_f32(const float* A, uint64_t m, const float* B, uint64_t n, uin
                      float alpha, const float* bias, int32_t* labels, float* best);
 // sq[i] = FMA chain of M_i[d]^2 over d ascending.
 int row_sqnorm_f32(const float* M, uint64_t rows, uint32_t dim, float* sq);
+// out[r] = in[r] / |in[r]| (rows of norm 0 stay as they are); in == out is allowed.  The cosine metric is
+// the inner product of rows and queries normalised this way.
+int normalize_rows_f32(const float* in, uint64_t rows, uint32_t dim, float* out);
 int row_sqnorm_bf16(const uint16_t* M, uint64_t rows, uint32_t dim, float* sq);
 
 // For each row of scores[m x n] (leading dimension ld): the `k` smallest as keys

@@ -53,6 +53,7 @@ struct SearchWorkspace {
     DevBuf<uint32_t> item_off[2];  // [nlist + 1]
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
+    DevBuf<float> q_unit;         // cosine: the queries divided by their norms
     bool pruning = false;         // the last scan dropped (query, list) pairs by the list radius
     DevBuf<float> bounds;         // [nq] per-query bounds as floats, the buffer the shards exchange
     DevBuf<uint16_t> q_hi, q_lo;  // tensor-core routing: tiled bf16 terms of the queries
@@ -80,6 +81,9 @@ struct vb200_ivf {
     int device = 0;
 
     bool has_centroids = false, has_model = false, has_rotation = false;
+    // cosine: rows, queries and centroids are normalised and the inner-product path does the rest
+    // (ScalarQuantizer / FP32Quantizer with METRIC_TYPE_COSINE, IVFNearestPartition::Train)
+    bool cosine = false;
     DevBuf<float> centroids, c_sq;
     DevBuf<float> lower, diff;           // SQ8, padded to dpad
     DevBuf<float> sq_scale, sq_mid;      // SQ8: diff/255 and lower + 128*diff/255, padded to dpad
@@ -211,6 +215,23 @@ sq8_derive_model_kernel(const float* __restrict__ lower, const float* __restrict
     }
     scale[d] = s;
     mid[d] = m;
+}
+
+// fp32 buckets: row i of the batch goes, unchanged, to position dst_pos[i] (rows of foreign
+// shards have no position).
+__global__ void
+fp32_place_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim, const uint32_t* __restrict__ dst_pos,
+                       uint8_t* __restrict__ codes, uint32_t code_stride) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= count * dim) {
+        return;
+    }
+    const uint64_t row = e / dim;
+    const uint32_t d = static_cast<uint32_t>(e % dim);
+    const uint32_t pos = dst_pos[row];
+    if (pos != 0xFFFFFFFFu) {
+        reinterpret_cast<float*>(codes + static_cast<uint64_t>(pos) * code_stride)[d] = x[e];
+    }
 }
 
 // code_norm[p] = sum_d x_d^2 with x_d the reference's decode fma(code * (1/255), diff, lower).
@@ -750,7 +771,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                  static_cast<unsigned long long>(total));
     VB_CHECK_ARG(kfinal >= 1 && kscan <= 1024 - SCAN_THREADS, "k = %u out of range [1, %u]", kfinal,
                  1024 - SCAN_THREADS - (sq8 ? SQ8_SLACK : 0));
-    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : RABITQ_QT;
+    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : (ix->quant == VB200_QUANT_FP32 ? FP32_QT : RABITQ_QT);
 
     // Phase 0 scans every query's nearest list (of those this shard holds), phase 1 the other
     // probes: after phase 0 the per-query bound is already close to final, so almost nothing
@@ -843,6 +864,10 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
             return launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem);
         }
+        if (ix->quant == VB200_QUANT_FP32) {
+            size_t smem = tile_smem_bytes<FP32_QT>(p.cap, FP32_QT * ix->dpad);
+            return launch_scan(ivf_fp32_scan_kernel<FP32_QT>, p, smem);
+        }
         size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
         return launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem);
     };
@@ -920,6 +945,11 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
                                 cudaMemcpyHostToDevice, current_stream()));
         q_dev = ws.queries.ptr;
     }
+    if (ix->cosine) {
+        VB_TRY(ws.q_unit.reserve(nq * ix->dim));
+        VB_TRY(normalize_rows_f32(q_dev, nq, ix->dim, ws.q_unit.ptr));
+        q_dev = ws.q_unit.ptr;
+    }
     // probes
     VB_TRY(ws.probes.reserve(nq * nprobe));
     if (bucket_ids != nullptr) {
@@ -982,10 +1012,10 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
     VB_CHECK_ARG(out != nullptr, "null output handle");
     VB_CHECK_ARG(dim > 0, "dim must be positive");
     VB_CHECK_ARG(nlist >= 1, "buckets_count must be at least 1");
-    VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP,
-                 "metric_type must be l2 or ip for this engine (got %d)", metric);
-    VB_CHECK_ARG(quant == VB200_QUANT_SQ8 || quant == VB200_QUANT_RABITQ,
-                 "base_quantization_type must be sq8 or rabitq for this engine (got %d)", quant);
+    VB_CHECK_ARG(quant == VB200_QUANT_SQ8 || quant == VB200_QUANT_RABITQ || quant == VB200_QUANT_FP32,
+                 "base_quantization_type must be fp32, sq8 or rabitq for this engine (got %d)", quant);
+    VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP || metric == VB200_METRIC_COSINE,
+                 "metric_type must be l2, ip or cosine (got %d)", metric);
     VB_CHECK_ARG(!(quant == VB200_QUANT_RABITQ && metric != VB200_METRIC_L2),
                  "rabitq buckets support metric l2 only");
     int ndev = vb200_device_count();
@@ -1000,12 +1030,21 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
     ix->metric = metric;
     ix->nlist = nlist;
     ix->quant = quant;
+    if (metric == VB200_METRIC_COSINE) {
+        ix->metric = VB200_METRIC_IP;
+        ix->cosine = true;
+    }
     ix->use_reorder = use_reorder != 0;
     cudaGetDevice(&ix->device);
     if (quant == VB200_QUANT_SQ8) {
         ix->code_size = dim;
         ix->dpad = (dim + 15) / 16 * 16;
         ix->code_stride = ix->dpad;
+    } else if (quant == VB200_QUANT_FP32) {
+        ix->code_size = dim * 4;
+        ix->dpad = (dim + 3) / 4 * 4;
+        ix->code_stride = ix->dpad * 4;
+        ix->has_model = true;   // nothing to train beyond the centroids
     } else {
         ix->code_size = rabitq_code_size(dim);
         ix->dpad = rabitq_bits_bytes(dim) * 8;
@@ -1198,14 +1237,27 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
         VB_TRY(kmeans_update_device(ix->kws, x.ptr, count, ix->dim, lab.ptr, ix->nlist,
                                     static_cast<uint32_t>(it), ix->centroids.ptr));
     }
+    DevBuf<float> unit_rows;
+    const float* x_model = x.ptr;   // what the bucket quantizer trains on
+    if (ix->cosine) {
+        // k-means runs on the rows as given, its centroids are normalised afterwards
+        // (ivf_nearest_partition.cpp:81-85); the quantizer sees normalised rows
+        // (scalar_quantization_trainer.cpp:139-141).
+        VB_TRY(normalize_rows_f32(ix->centroids.ptr, ix->nlist, ix->dim, ix->centroids.ptr));
+        if (ix->quant == VB200_QUANT_SQ8) {
+            VB_TRY(unit_rows.reserve(count * ix->dim));
+            VB_TRY(normalize_rows_f32(x.ptr, count, ix->dim, unit_rows.ptr));
+            x_model = unit_rows.ptr;
+        }
+    }
     VB_TRY(ivf_refresh_centroid_norms(ix));
     if (ix->quant == VB200_QUANT_SQ8) {
         DevBuf<float> model;
         VB_TRY(model.reserve(2 * static_cast<size_t>(ix->dim)));
-        VB_TRY(sq8_train_device(x.ptr, count, ix->dim, VB200_SQ_TRAIN_TRUNC_BOUND, model.ptr,
+        VB_TRY(sq8_train_device(x_model, count, ix->dim, VB200_SQ_TRAIN_TRUNC_BOUND, model.ptr,
                                 model.ptr + ix->dim));
         VB_TRY(ivf_store_sq8_model(ix, model.ptr, model.ptr + ix->dim));
-    } else {
+    } else if (ix->quant == VB200_QUANT_RABITQ) {
         VB_TRY(ix->rq_centroid.reserve(ix->dim));
         VB_TRY(rabitq_train_device(x.ptr, count, ix->dim, ix->rotation.ptr, ix->rq_centroid.ptr));
         ix->has_model = true;
@@ -1231,6 +1283,13 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
 
     DevInput<float> x;
     VB_TRY(x.bind(data, count * dim));
+    DevBuf<float> unit_rows;
+    const float* xr = x.ptr;   // the rows as the index stores and scores them
+    if (ix->cosine) {
+        VB_TRY(unit_rows.reserve(count * dim));
+        VB_TRY(normalize_rows_f32(x.ptr, count, dim, unit_rows.ptr));
+        xr = unit_rows.ptr;
+    }
     // 1. list of every row
     DevBuf<int32_t> lab;
     VB_TRY(lab.reserve(count));
@@ -1240,10 +1299,10 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
         if (ix->metric == VB200_METRIC_L2) {
             // the k-means assignment (tensor-core candidates + exact pick when large enough)
             ix->kws.forget_points();
-            VB_TRY(kmeans_assign_device(ix->kws, x.ptr, count, dim, ix->centroids.ptr, nlist, lab.ptr, nullptr));
+            VB_TRY(kmeans_assign_device(ix->kws, xr, count, dim, ix->centroids.ptr, nlist, lab.ptr, nullptr));
             ix->kws.forget_points();
         } else {
-            VB_TRY(dense_argmin_f32(x.ptr, count, ix->centroids.ptr, nlist, dim, -1.0f, nullptr, lab.ptr, nullptr));
+            VB_TRY(dense_argmin_f32(xr, count, ix->centroids.ptr, nlist, dim, -1.0f, nullptr, lab.ptr, nullptr));
         }
     }
     // 2. sort rows by (list, row)
@@ -1311,10 +1370,13 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
               static_cast<uint32_t>(ix->n_total), dst_of_row.ptr, new_inner.ptr);
     // 5. encode the new rows in place
     if (ix->quant == VB200_QUANT_SQ8) {
-        VB_TRY(sq8_encode_device(x.ptr, count, dim, ix->lower.ptr, ix->diff.ptr, dst_of_row.ptr,
+        VB_TRY(sq8_encode_device(xr, count, dim, ix->lower.ptr, ix->diff.ptr, dst_of_row.ptr,
                                  new_codes.ptr, stride));
+    } else if (ix->quant == VB200_QUANT_FP32) {
+        VB_LAUNCH(fp32_place_rows_kernel, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count, dim,
+                  dst_of_row.ptr, new_codes.ptr, stride);
     } else {
-        VB_TRY(rabitq_encode_device(x.ptr, count, dim, ix->rotation.ptr, ix->rq_centroid.ptr,
+        VB_TRY(rabitq_encode_device(xr, count, dim, ix->rotation.ptr, ix->rq_centroid.ptr,
                                     dst_of_row.ptr, new_codes.ptr, stride));
     }
     // 6. labels and (for reorder) the fp32 rows, by inner id
@@ -1323,7 +1385,7 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
                             cudaMemcpyDefault, st));
     if (ix->use_reorder) {
         VB_TRY(grow_preserve(ix->flat, ix->n_total * dim, (ix->n_total + count) * dim));
-        VB_CUDA(cudaMemcpyAsync(ix->flat.ptr + ix->n_total * dim, x.ptr, count * dim * sizeof(float),
+        VB_CUDA(cudaMemcpyAsync(ix->flat.ptr + ix->n_total * dim, xr, count * dim * sizeof(float),
                                 cudaMemcpyDeviceToDevice, st));
     }
     DevBuf<float> new_norm;
@@ -1409,7 +1471,13 @@ vb200_ivf_route(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t npro
     VB_TRY(q.bind(queries, nq * ix->dim));
     VB_TRY(ix->ws.probes.reserve(nq * nprobe));
     VB_TRY(ix->ws.probe_dists.reserve(nq * nprobe));
-    VB_TRY(ivf_route_device(ix, q.ptr, nq, nprobe, ix->ws.probes.ptr, ix->ws.probe_dists.ptr));
+    const float* q_dev = q.ptr;
+    if (ix->cosine) {
+        VB_TRY(ix->ws.q_unit.reserve(nq * ix->dim));
+        VB_TRY(normalize_rows_f32(q_dev, nq, ix->dim, ix->ws.q_unit.ptr));
+        q_dev = ix->ws.q_unit.ptr;
+    }
+    VB_TRY(ivf_route_device(ix, q_dev, nq, nprobe, ix->ws.probes.ptr, ix->ws.probe_dists.ptr));
     VB_TRY(copy_out(bucket_ids, ix->ws.probes.ptr, nq * nprobe));
     if (bucket_dists != nullptr) {
         VB_TRY(copy_out(bucket_dists, ix->ws.probe_dists.ptr, nq * nprobe));

@@ -662,4 +662,112 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// fp32 buckets (base_quantization_type "fp32", the reference's default): rows are stored as they
+// came, distances are the reference's own chains (FP32Quantizer::ComputeDistImpl,
+// src/quantization/fp32_quantizer.cpp:163-190): L2 = sum of fma(t, t, acc) with t = x_d - q_d in
+// ascending d, IP = 1 - sum of fma(x_d, q_d, acc).  Values are final: no re-scoring follows.
+// One thread per row, 8-query tiles staged in shared memory, the shared scheduler and selection.
+// ---------------------------------------------------------------------------------------------
+constexpr int FP32_QT = 8;
+
+template <int QT>
+__global__ void __launch_bounds__(SCAN_THREADS)
+ivf_fp32_scan_kernel(const ScanParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ uint32_t s_item[1];
+    TileSelect<QT> ts;
+    float* fbuf;
+    tile_carve<QT>(smem, p.cap, 0, fbuf, ts);
+    ts.k = p.k;
+    ts.cap = p.cap;
+    const uint32_t dpad = p.dpad;  // dim rounded up to 4
+    float* sv = fbuf;              // [QT][dpad]
+
+    ScanItem it;
+    while (scan_next_item<QT>(p, s_item, it)) {
+        const uint32_t list = it.list;
+        const uint32_t pbeg = it.pbeg;
+        const int nqt = static_cast<int>(it.nqt);
+        if (threadIdx.x < QT) {
+            int qi = threadIdx.x;
+            ts.qa[qi] = 0.f;
+            if (qi < nqt) {
+                uint32_t q = it.pair_q[pbeg + qi];
+                ts.qidx[qi] = q;
+                ts.slot[qi] = it.pair_slot[pbeg + qi];
+                ts.set_bound(qi, p.thr_g[q]);
+            } else {
+                ts.qidx[qi] = 0;
+                ts.slot[qi] = 0;
+                ts.set_bound(qi, 0u);
+            }
+            ts.cnt[qi] = 0;
+        }
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < static_cast<uint32_t>(QT) * dpad; i += SCAN_THREADS) {
+            uint32_t qi = i / dpad, d = i % dpad;
+            float v = 0.f;
+            if (static_cast<int>(qi) < nqt && d < p.dim) {
+                v = __ldg(p.queries + static_cast<uint64_t>(ts.qidx[qi]) * p.dim + d);
+            }
+            sv[i] = v;
+        }
+        __syncthreads();
+
+        const uint32_t lbeg = p.list_off[list];
+        const uint32_t len = p.list_off[list + 1] - lbeg;
+        for (uint32_t r0 = 0; r0 < len; r0 += SCAN_THREADS) {
+            const uint32_t row = r0 + threadIdx.x;
+            const bool valid = row < len;
+            const float4* x4 = reinterpret_cast<const float4*>(
+                p.codes + static_cast<uint64_t>(lbeg + (valid ? row : 0)) * p.code_stride);
+            float acc[QT];
+#pragma unroll
+            for (int qi = 0; qi < QT; ++qi) {
+                acc[qi] = 0.f;
+            }
+            for (uint32_t d4 = 0; d4 < (dpad >> 2); ++d4) {
+                const float4 x = __ldg(x4 + d4);   // padding columns hold zeros on both sides
+#pragma unroll
+                for (int qi = 0; qi < QT; ++qi) {
+                    if (qi < nqt) {
+                        const float4 q = *reinterpret_cast<const float4*>(sv + qi * dpad + 4 * d4);
+                        float a = acc[qi];
+                        if (p.metric == 0) {
+                            float t = __fsub_rn(x.x, q.x);
+                            a = fmaf(t, t, a);
+                            t = __fsub_rn(x.y, q.y);
+                            a = fmaf(t, t, a);
+                            t = __fsub_rn(x.z, q.z);
+                            a = fmaf(t, t, a);
+                            t = __fsub_rn(x.w, q.w);
+                            a = fmaf(t, t, a);
+                        } else {
+                            a = fmaf(x.x, q.x, a);
+                            a = fmaf(x.y, q.y, a);
+                            a = fmaf(x.z, q.z, a);
+                            a = fmaf(x.w, q.w, a);
+                        }
+                        acc[qi] = a;
+                    }
+                }
+            }
+            if (valid) {
+#pragma unroll
+                for (int qi = 0; qi < QT; ++qi) {
+                    if (qi < nqt) {
+                        const float dist = p.metric == 0 ? acc[qi] : __fsub_rn(1.0f, acc[qi]);
+                        ts.push(qi, dist, lbeg + row);
+                    }
+                }
+            }
+            __syncthreads();
+            ts.make_room(nqt);
+            __syncthreads();
+        }
+        ts.finish(nqt, p.part, p.thr_g);
+    }
+}
+
 }  // namespace vb200

@@ -181,7 +181,9 @@ class IvfHandle:
 
     @property
     def code_size(self) -> int:
-        return self.dim if self.quant == QUANT_SQ8 else rabitq_code_size(self.dim)
+        if self.quant == QUANT_SQ8:
+            return self.dim
+        return self.dim * 4 if self.quant == QUANT_FP32 else rabitq_code_size(self.dim)
 
     def set_shard(self, rank: int, world: int) -> None:
         check(self._lib.vb200_ivf_set_shard(self._h, rank, world))

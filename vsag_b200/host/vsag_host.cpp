@@ -147,7 +147,7 @@ parse_common(const std::string& parameters) {
     } else if (metric == "ip") {
         out.metric = VB200_METRIC_IP;
     } else if (metric == "cosine") {
-        fail(ErrorType::INVALID_ARGUMENT, "parameters[metric_type]=cosine is not served by the GPU engine yet");
+        out.metric = VB200_METRIC_COSINE;
     } else {
         fail(ErrorType::INVALID_ARGUMENT, "parameters[metric_type] must in [l2, ip, cosine], now is " + metric);
     }
@@ -303,9 +303,11 @@ public:
             quant_ = VB200_QUANT_SQ8;
         } else if (quant == "rabitq") {
             quant_ = VB200_QUANT_RABITQ;
+        } else if (quant == "fp32") {
+            quant_ = VB200_QUANT_FP32;
         } else {
             fail(ErrorType::INVALID_ARGUMENT, "base_quantization_type \"" + quant +
-                                                  "\" is not served by the GPU engine (sq8 and rabitq are)");
+                                                  "\" is not served by the GPU engine (fp32, sq8 and rabitq are)");
         }
         use_reorder_ = get_bool(p, "use_reorder", false);
         std::string precise = get_string(p, "precise_quantization_type", "fp32");
