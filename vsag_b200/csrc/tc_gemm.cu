@@ -162,7 +162,12 @@ tc_candidates_kernel(const TcParams p) {
     const uint32_t n_terms_op = p.n_terms == 3 ? 2u : 1u;                       // bf16 terms per operand
     // resident-A mode: [A tile: chunks x terms][ring of B stages]; otherwise a ring of [A terms][B terms]
     const uint32_t a_region_bytes = p.a_resident ? p.a.chunks * n_terms_op * TC_CHUNK_BYTES : 0u;
-    const uint32_t stage_bytes = (p.a_resident ? n_terms_op : n_ops) * TC_CHUNK_BYTES;
+    // wide mode: a stage holds two consecutive B tiles, term by term ([hi t][hi t+1][lo t][lo t+1]), so
+    // that one 128 x 256 x 16 MMA reads both; the accumulators are 256 columns each.
+    const uint32_t step = p.wide ? 2u : 1u;
+    const uint32_t acc_cols = step * TC_BN;
+    const uint32_t stage_bytes = ((p.a_resident ? 0u : n_terms_op) + n_terms_op * step) * TC_CHUNK_BYTES;
+    (void)n_ops;
     const uint32_t chunks = p.a.chunks;
     const uint64_t m_tiles = (p.a.rows + TC_BM - 1) / TC_BM;
     const uint64_t n_tiles = (p.b.rows + TC_BN - 1) / TC_BN;
@@ -183,7 +188,7 @@ tc_candidates_kernel(const TcParams p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_EPI_WARPS) {
-        tmem_alloc(&sh.tmem_base, 256);  // two 128-column fp32 accumulators
+        tmem_alloc(&sh.tmem_base, 2 * acc_cols);  // two fp32 accumulators of 128 (256 when wide) columns
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -207,7 +212,7 @@ tc_candidates_kernel(const TcParams p) {
         // Written for latency: 32-bit counters that wrap by compare instead of divide, descriptors
         // prepared once per stage.
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
+            const uint32_t idesc_one = umma_idesc_bf16(TC_BM, TC_BN), idesc_two = umma_idesc_bf16(TC_BM, 2 * TC_BN);
             // Descriptor of stage 0 / operand 0; the others differ only in the start-address field,
             // which counts 16-byte units, so they are this value plus small constants kept in registers.
             const uint64_t desc0 = umma_desc(smem_u32(smem), 128, 1024);
@@ -228,7 +233,8 @@ tc_candidates_kernel(const TcParams p) {
                         break;
                     }
                 }
-                for (uint32_t t = 0; t < tiles && ok; ++t) {
+                for (uint32_t t = 0; t < tiles && ok; t += step) {
+                    const uint32_t idesc = (tiles - t >= 2 && step == 2) ? idesc_two : idesc_one;
                     if (tiles_started >= 2) {
                         // the epilogue must have drained this accumulator's previous tile
                         ok = mbar_wait(&sh.acc_free[acc], acc_phase ^ 1u);
@@ -237,7 +243,7 @@ tc_candidates_kernel(const TcParams p) {
                         }
                     }
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + acc * TC_BN;
+                    const uint32_t d_tmem = tmem_base + acc * acc_cols;
                     for (uint32_t c = 0; c < chunks && ok; ++c) {
                         ok = mbar_wait(&sh.full[m_stage], m_phase);
                         if (!ok) {
@@ -252,7 +258,7 @@ tc_candidates_kernel(const TcParams p) {
                             if (p.n_terms == 3) {
                                 const uint64_t a_hi = (a_res ? desc0 + c * 2 * op_units : stage_desc) + koff;
                                 const uint64_t b_hi = (a_res ? stage_desc : stage_desc + 2 * op_units) + koff;
-                                const uint64_t a_lo = a_hi + op_units, b_lo = b_hi + op_units;
+                                const uint64_t a_lo = a_hi + op_units, b_lo = b_hi + step * op_units;
                                 umma_bf16(d_tmem, a_hi, b_hi, idesc, accumulate);
                                 umma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
                                 umma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
@@ -265,7 +271,7 @@ tc_candidates_kernel(const TcParams p) {
                         umma_commit(&sh.freed[m_stage]);
                         if (c + 1 == chunks) {
                             umma_commit(&sh.acc_full[acc]);
-                            if (a_res && t + 1 == tiles) {
+                            if (a_res && t + step >= tiles) {
                                 umma_commit(&sh.a_free);   // the item's A tile may be overwritten
                             }
                         }
@@ -333,8 +339,8 @@ tc_candidates_kernel(const TcParams p) {
                 for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
                     uint32_t mtile, ntile0, tiles;
                     open_item(item, mtile, ntile0, tiles);
-                    for (uint32_t t = 0; t < tiles && ok; ++t) {
-                        const size_t row_tile = is_a ? mtile : ntile0 + t;
+                    for (uint32_t t = 0; t < tiles && ok; t += step) {
+                        const uint32_t here = is_a ? 1u : (tiles - t >= step ? step : 1u);   // B tiles of this step
                         for (uint32_t c = 0; c < chunks; ++c) {
                             if (count >= p.stages) {
                                 // the stage's previous use must have been consumed by the tensor core
@@ -344,11 +350,16 @@ tc_candidates_kernel(const TcParams p) {
                                 }
                             }
                             unsigned char* dst = smem + a_region_bytes + stage * stage_bytes + op_off;
-                            const size_t off = (row_tile * chunks + c) * TC_CHUNK_ELEMS;
-                            mbar_expect_tx(&sh.full[stage], terms * TC_CHUNK_BYTES);
-                            bulk_copy_g2s(dst, op.hi + off, TC_CHUNK_BYTES, &sh.full[stage]);
-                            if (terms == 2) {
-                                bulk_copy_g2s(dst + TC_CHUNK_BYTES, op.lo + off, TC_CHUNK_BYTES, &sh.full[stage]);
+                            mbar_expect_tx(&sh.full[stage], terms * here * TC_CHUNK_BYTES);
+                            for (uint32_t slot = 0; slot < here; ++slot) {
+                                const size_t row_tile = is_a ? mtile : ntile0 + t + slot;
+                                const size_t off = (row_tile * chunks + c) * TC_CHUNK_ELEMS;
+                                const uint32_t slots = is_a ? 1u : step;   // slots per term in the stage
+                                bulk_copy_g2s(dst + slot * TC_CHUNK_BYTES, op.hi + off, TC_CHUNK_BYTES, &sh.full[stage]);
+                                if (terms == 2) {
+                                    bulk_copy_g2s(dst + (slots + slot) * TC_CHUNK_BYTES, op.lo + off, TC_CHUNK_BYTES,
+                                                  &sh.full[stage]);
+                                }
                             }
                             ++count;
                             if (++stage == p.stages) {
@@ -389,9 +400,13 @@ tc_candidates_kernel(const TcParams p) {
             // bias of the warp's 32 columns: fetched one tile ahead into a register (lane = column),
             // handed to the other lanes through the warp's own shared-memory slot
             const bool has_bias = p.bias != nullptr;
+            // first global column of this warp's block `half` in the tile step that starts at B tile t
+            auto block_col = [&](uint64_t t, uint32_t half) -> uint64_t {
+                return p.wide ? (t + (cgroup >> 1)) * TC_BN + (cgroup & 1u) * 64 + half * 32 : t * TC_BN + cgroup * 32;
+            };
             float next_bias = 0.f;
             if (has_bias) {
-                const uint64_t nn = t0 * TC_BN + cgroup * 32 + lane;
+                const uint64_t nn = block_col(t0, 0) + lane;
                 next_bias = (t0 < t1 && nn < p.b.rows) ? __ldg(p.bias + nn) : 0.f;
             }
             // SMALL_M: the four best scores of the row, ascending, with their columns
@@ -401,7 +416,7 @@ tc_candidates_kernel(const TcParams p) {
                                      : -1.f;
             float bound = (margin >= 0.f && p.row_bound != nullptr) ? __ldg(p.row_bound + grow) + margin : INFINITY;
             uint32_t bc0 = 0xFFFFFFFFu, bc1 = 0xFFFFFFFFu, bc2 = 0xFFFFFFFFu, bc3 = 0xFFFFFFFFu;
-            for (uint64_t t = t0; t < t1 && ok; ++t, ++gtile) {
+            for (uint64_t t = t0; t < t1 && ok; t += step, ++gtile) {
                 const uint32_t acc = static_cast<uint32_t>(gtile & 1);
                 ok = mbar_wait_relaxed(&sh.acc_full[acc], static_cast<uint32_t>((gtile >> 1) & 1));
                 ok = __all_sync(0xffffffffu, ok);
@@ -409,24 +424,30 @@ tc_candidates_kernel(const TcParams p) {
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * TC_BN + cgroup * 32;
-                const uint64_t n0 = t * TC_BN;
-                const bool whole_tile = valid_row && n0 + TC_BN <= p.b.rows;
+                const uint32_t here = (t1 - t >= step) ? step : 1u;              // B tiles in this step
+                const bool tile_present = p.wide ? (cgroup >> 1) < here : true;  // this warp's B tile exists
+                for (uint32_t half = 0; half < step; ++half) {
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * acc_cols +
+                                       (p.wide ? cgroup * 64 + half * 32 : cgroup * 32);
+                const uint64_t n0 = block_col(t, half);
+                const bool whole_tile = valid_row && tile_present && n0 + 32 <= p.b.rows;
                 if (has_bias) {
                     __syncwarp();
                     sh.bias[warp][lane] = next_bias;
-                    const uint64_t nn = (t + 1 < t1) ? (t + 1) * TC_BN + cgroup * 32 + lane : p.b.rows;
-                    next_bias = nn < p.b.rows ? __ldg(p.bias + nn) : 0.f;
+                    const bool more = half + 1 < step || t + step < t1;
+                    const uint64_t nn = (half + 1 < step ? n0 + 32 : block_col(t + step, 0)) + lane;
+                    next_bias = (more && nn < p.b.rows) ? __ldg(p.bias + nn) : 0.f;
                     __syncwarp();
                 }
                 uint32_t r[32];
                 tmem_load_32(taddr, r);
-                // the accumulator is in registers now: hand it back before doing the selection
-                tc_fence_before_sync();
-                mbar_arrive(&sh.acc_free[acc]);
+                if (half + 1 == step) {
+                    // the accumulator is in registers now: hand it back before doing the selection
+                    tc_fence_before_sync();
+                    mbar_arrive(&sh.acc_free[acc]);
+                }
 
                 {
-                    const uint32_t cb = cgroup;
                     if (MODE == 1) {
                         uint32_t full = __ballot_sync(0xffffffffu, cnt + 32 > p.cap);
                         while (full != 0) {
@@ -435,7 +456,7 @@ tc_candidates_kernel(const TcParams p) {
                             full &= full - 1;
                         }
                     }
-                    const uint32_t c0 = static_cast<uint32_t>(n0) + cb * 32;
+                    const uint32_t c0 = static_cast<uint32_t>(n0);
                     // Scores of the block and their minimum first (two instructions per element);
                     // the selection code below runs only when the minimum beats the row's bound.
                     float sc[32];
@@ -457,7 +478,9 @@ tc_candidates_kernel(const TcParams p) {
                             }
                         }
                     } else {
-                        const uint32_t cols_left = c0 < p.b.rows ? static_cast<uint32_t>(min(static_cast<uint64_t>(32), p.b.rows - c0)) : 0u;
+                        const uint32_t cols_left = (tile_present && c0 < p.b.rows)
+                                                       ? static_cast<uint32_t>(min(static_cast<uint64_t>(32), p.b.rows - c0))
+                                                       : 0u;
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             const float4 b4 = has_bias ? *reinterpret_cast<const float4*>(&sh.bias[warp][i])
@@ -472,7 +495,7 @@ tc_candidates_kernel(const TcParams p) {
                     }
                     if (STORE) {
                         // 32 consecutive floats of this thread's row: eight 16-byte stores
-                        if (valid_row) {
+                        if (valid_row && tile_present) {
                             float* dst = p.store + grow * p.store_ld + c0;
                             if (whole_tile) {
 #pragma unroll
@@ -562,6 +585,7 @@ tc_candidates_kernel(const TcParams p) {
                         }
                     }
                 }
+                }   // half
             }
             if (!ok) {
                 break;
@@ -605,14 +629,14 @@ tc_candidates_kernel(const TcParams p) {
     tc_fence_before_sync();
     __syncthreads();
     if (warp == TC_EPI_WARPS) {
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, 2 * acc_cols);
     }
 }
 
 // Shared memory a launch may use for operand stages and sort areas (the rest of the 227 KiB holds
 // the barriers, the bias slots and alignment slack).
 constexpr size_t TC_SMEM_BUDGET = 232448 - 4096;
-constexpr uint32_t TC_MIN_STAGES = 3;
+constexpr uint32_t TC_MIN_STAGES = 2;
 
 static size_t
 tc_stage_bytes(uint32_t n_terms) {
@@ -637,17 +661,25 @@ tc_cap_max(uint32_t n_terms) {
 static void
 tc_plan(TcParams& p, size_t sort_bytes, size_t* smem_bytes) {
     const uint32_t terms = p.n_terms == 3 ? 2u : 1u;
-    const size_t a_region = static_cast<size_t>(p.a.chunks) * terms * TC_CHUNK_BYTES;
+    const size_t chunk = TC_CHUNK_BYTES;
+    const size_t a_region = static_cast<size_t>(p.a.chunks) * terms * chunk;
     const char* env_res = std::getenv("VB200_TC_A_RESIDENT");
+    const char* env_wide = std::getenv("VB200_TC_WIDE");
     bool resident = a_region <= 65536 && !(env_res != nullptr && env_res[0] == '0');
-    size_t per_stage = (resident ? terms : 2 * terms) * static_cast<size_t>(TC_CHUNK_BYTES);
-    size_t fixed = sort_bytes + (resident ? a_region : 0);
-    if (resident && (TC_SMEM_BUDGET - fixed) / per_stage < TC_MIN_STAGES) {
+    auto stage_bytes = [&](bool res, bool wide) { return ((res ? 0 : terms) + terms * (wide ? 2 : 1)) * chunk; };
+    auto fits = [&](bool res, bool wide, uint32_t stages) {
+        return sort_bytes + (res ? a_region : 0) + stages * stage_bytes(res, wide) <= TC_SMEM_BUDGET;
+    };
+    if (resident && !fits(true, false, TC_MIN_STAGES)) {
         resident = false;
-        per_stage = 2 * terms * static_cast<size_t>(TC_CHUNK_BYTES);
-        fixed = sort_bytes;
     }
-    uint32_t stages = static_cast<uint32_t>((TC_SMEM_BUDGET - fixed) / per_stage);
+    // Two B tiles per MMA whenever a stage stays affordable: bf16 inputs, or a resident A tile.
+    bool wide = (terms == 1 || resident) && !(env_wide != nullptr && env_wide[0] == '0');
+    if (wide && !fits(resident, true, TC_MIN_STAGES)) {
+        wide = false;
+    }
+    const size_t fixed = sort_bytes + (resident ? a_region : 0);
+    uint32_t stages = static_cast<uint32_t>((TC_SMEM_BUDGET - fixed) / stage_bytes(resident, wide));
     if (stages > TC_MAX_STAGES) {
         stages = TC_MAX_STAGES;
     }
@@ -660,7 +692,8 @@ tc_plan(TcParams& p, size_t sort_bytes, size_t* smem_bytes) {
     }
     p.stages = stages;
     p.a_resident = resident ? 1u : 0u;
-    *smem_bytes = fixed + stages * per_stage + 1024;
+    p.wide = wide ? 1u : 0u;
+    *smem_bytes = fixed + stages * stage_bytes(resident, wide) + 1024;
 }
 
 uint32_t

@@ -49,6 +49,7 @@ struct TcParams {
     uint32_t cap;             // per-row buffer, power of two >= m + 32
     uint32_t stages;          // operand stages in shared memory (2 .. 6)
     uint32_t a_resident;      // 1: the A tile of a work item stays in shared memory for all its B tiles
+    uint32_t wide;            // 1: two B tiles per MMA (128 x 256 x 16), 512 TMEM columns
     uint32_t n_split;         // column ranges per row tile
     uint32_t tiles_per_split; // B tiles per range
     uint64_t* scratch;        // [grid][128][TC_COL_GROUPS][cap] candidate buffers
