@@ -1,6 +1,6 @@
 """Headline benchmark: IVF-SQ8 search QPS on a synthetic stand-in for Deep-10M.
 
-Workload (the third config of BASELINE.json): base 10,000,000 x 96 fp32 drawn from a Gaussian
+Workload (the configuration the headline metric is quoted on): base 10,000,000 x 96 fp32 drawn from a Gaussian
 mixture of 16,384 centres (uniform[-1,1], sigma 0.15, seed 2), SQ8 codes, nlist 16,384, nprobe 64,
 10,000 queries from the same mixture (seed 3), k = 10, L2.  The dataset named by the reference's
 documentation is not available offline; this seeded synthetic set has its shape.
@@ -300,8 +300,8 @@ def measured_tensor_peak() -> tuple[float, str]:
 
 
 def run_dense_workload(args) -> None:
-    """k-means training (second config of BASELINE.json) or bf16 BruteForce search (one GPU's shard
-    of the fifth).  Under torchrun every rank works on its own rows: k-means ranks are replicas of
+    """k-means training (1,000,000 x 128 rows, 4,096 centroids) or bf16 BruteForce search (one GPU's
+    6,250,000-row shard of a 50,000,000 x 768 base).  Under torchrun every rank works on its own rows: k-means ranks are replicas of
     the same job on different data, BruteForce ranks hold consecutive row ranges of one base and
     merge their partial top-k after an all-gather."""
     import torch

@@ -617,18 +617,21 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
                     if (g < nqt) {
 #pragma unroll
                         for (int b4 = 0; b4 < 8; ++b4) {
-                            // bit set -> +sv, clear -> -sv (flip the sign bit)
+                            // bit set -> +sv, clear -> -sv.  fma(sv, +-1, acc) rounds exactly like
+                            // acc + (+-sv), and the four multipliers are shared by the tile's queries.
                             const uint32_t nb = ~w >> (4 * b4);
-                            const uint32_t f0 = (nb & 1u) << 31, f1 = (nb & 2u) << 30;
-                            const uint32_t f2 = (nb & 4u) << 29, f3 = (nb & 8u) << 28;
+                            const float m0 = __uint_as_float(0x3F800000u | ((nb & 1u) << 31));
+                            const float m1 = __uint_as_float(0x3F800000u | ((nb & 2u) << 30));
+                            const float m2 = __uint_as_float(0x3F800000u | ((nb & 4u) << 29));
+                            const float m3 = __uint_as_float(0x3F800000u | ((nb & 8u) << 28));
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
                                 float4 s = *reinterpret_cast<const float4*>(sv + (g + u) * dpad + d0 + 4 * b4);
                                 float a = acc[g + u];
-                                a = __fadd_rn(a, __uint_as_float(__float_as_uint(s.x) ^ f0));
-                                a = __fadd_rn(a, __uint_as_float(__float_as_uint(s.y) ^ f1));
-                                a = __fadd_rn(a, __uint_as_float(__float_as_uint(s.z) ^ f2));
-                                a = __fadd_rn(a, __uint_as_float(__float_as_uint(s.w) ^ f3));
+                                a = fmaf(s.x, m0, a);
+                                a = fmaf(s.y, m1, a);
+                                a = fmaf(s.z, m2, a);
+                                a = fmaf(s.w, m3, a);
                                 acc[g + u] = a;
                             }
                         }
