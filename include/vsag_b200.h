@@ -240,6 +240,30 @@ VB200_API int vb200_ivf_search(vb200_ivf_t index, const float* queries, uint64_t
                      uint32_t nprobe, float factor, const int32_t* bucket_ids, int64_t* ids,
                      float* dists);
 
+/* Id filter of a search (SearchRequest filters, include/vsag/search_request.h; BlackListFilter,
+ * src/impl/filter/black_list_filter.cpp:25-31).  Both parts are optional; pointers may be host or
+ * device memory.
+ *   invalid_label_bits: the reference's bitset filter, bit (label & 0xFFFFFFFF) set = filtered out;
+ *                       labels beyond n_label_bits pass.
+ *   deny_inner_bits:    bit i set = the i-th vector ever added (inner id i) is filtered out; this
+ *                       is what a host callback filter is materialised into. */
+typedef struct vb200_filter {
+    const uint64_t* invalid_label_bits;
+    uint64_t n_label_bits;
+    const uint32_t* deny_inner_bits;
+    uint64_t n_inner_bits;
+} vb200_filter;
+
+/* vb200_ivf_search with an id filter (and always without the vectors removed so far). */
+VB200_API int vb200_ivf_search_filtered(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t k,
+                              uint32_t nprobe, float factor, const int32_t* bucket_ids,
+                              const vb200_filter* filter, int64_t* ids, float* dists);
+
+/* Index::Remove with RemoveMode::MARK_REMOVE (include/vsag/index.h:186-200): the vectors with these
+ * labels stay in their lists but no search returns them any more.  removed (optional) receives how
+ * many labels were found and newly marked. */
+VB200_API int vb200_ivf_remove(vb200_ivf_t index, const int64_t* labels, uint64_t count, uint64_t* removed);
+
 /* Routing only, like the disable_bucket_scan search mode (IVF::route_buckets_only,
  * ivf.cpp:1589-1660): bucket_ids[nq x nprobe] ascending by centroid distance,
  * bucket_dists optional. */
@@ -307,6 +331,12 @@ VB200_API int64_t vb200_bf_num_elements(vb200_bf_t index);
  * dists[nq x k] ascending (+inf pad). */
 VB200_API int vb200_bf_search(vb200_bf_t index, const float* queries, uint64_t nq, uint32_t k, int64_t* ids,
                     float* dists);
+
+/* vb200_bf_search with an id filter, and Index::Remove(MARK_REMOVE); see vb200_ivf_search_filtered and
+ * vb200_ivf_remove. */
+VB200_API int vb200_bf_search_filtered(vb200_bf_t index, const float* queries, uint64_t nq, uint32_t k,
+                             const vb200_filter* filter, int64_t* ids, float* dists);
+VB200_API int vb200_bf_remove(vb200_bf_t index, const int64_t* labels, uint64_t count, uint64_t* removed);
 
 /* Partial result for a row-sharded index, see vb200_ivf_search_partial. */
 VB200_API int vb200_bf_search_partial(vb200_bf_t index, const float* queries, uint64_t nq, uint32_t k,

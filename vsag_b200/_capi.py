@@ -15,6 +15,13 @@ import numpy as np
 _LIB_PATH = Path(__file__).resolve().parent / "libvsag_b200.so"
 
 c_void_p, c_int, c_u32, c_u64, c_i64, c_float = C.c_void_p, C.c_int, C.c_uint32, C.c_uint64, C.c_int64, C.c_float
+class Filter(C.Structure):
+    """vb200_filter: label bitset and / or inner-id bitmap, host or device pointers."""
+
+    _fields_ = [("invalid_label_bits", C.c_void_p), ("n_label_bits", C.c_uint64),
+                ("deny_inner_bits", C.c_void_p), ("n_inner_bits", C.c_uint64)]
+
+
 # vb200_exchange_fn: int (*)(float* bounds_dev, uint64_t nq, void* cuda_stream, void* arg)
 EXCHANGE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p)
 
@@ -52,6 +59,9 @@ SIGNATURES = {
     "vb200_ivf_memory_usage": (c_i64, [c_void_p]),
     "vb200_ivf_get_lists": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "vb200_ivf_search": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p, c_void_p]),
+    "vb200_ivf_search_filtered": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p,
+                                          c_void_p, c_void_p]),
+    "vb200_ivf_remove": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "vb200_ivf_route": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p]),
     "vb200_ivf_search_partial": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p]),
@@ -66,6 +76,8 @@ SIGNATURES = {
     "vb200_bf_add_bf16": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "vb200_bf_num_elements": (c_i64, [c_void_p]),
     "vb200_bf_search": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p]),
+    "vb200_bf_search_filtered": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p, c_void_p]),
+    "vb200_bf_remove": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "vb200_bf_search_partial": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p]),
 }
 

@@ -1,5 +1,8 @@
 // Exact BruteForce kNN over fp32 or bf16 rows: dense score slabs select a few candidates more
 // than k per query, which are then re-scored in the reference's arithmetic and ordered.
+#include <algorithm>
+#include <vector>
+
 #include "dense.cuh"
 #include "kmeans.cuh"
 #include "tc_gemm.cuh"
@@ -35,7 +38,9 @@ bf_rescore_kernel(const T* __restrict__ queries, uint32_t dim, const T* __restri
     const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
     for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
         uint64_t key = KEY_INF;
-        if (i < ncand && cq[i] != KEY_INF) {
+        // candidates with an infinite nominating score are filtered-out rows that only filled up a
+        // short list: they are not results
+        if (i < ncand && cq[i] != KEY_INF && static_cast<uint32_t>(cq[i] >> 32) < 0xFF800000u) {
             uint32_t row = static_cast<uint32_t>(cq[i]);
             const T* x = base + static_cast<uint64_t>(row) * dim;
             float s = 0.f;
@@ -112,6 +117,52 @@ bf_results_kernel(const uint64_t* __restrict__ keys, uint64_t total, const int64
     }
 }
 
+// bias[i] = the row's score bias (its squared norm for L2, 0 for IP), or +inf when row i is
+// removed or filtered out: an infinite score is never nominated.
+__global__ void
+bf_masked_bias_kernel(const float* __restrict__ norms, uint64_t n, const uint32_t* __restrict__ tomb,
+                      const uint32_t* __restrict__ deny, uint64_t deny_bits, const int64_t* __restrict__ labels,
+                      const uint64_t* __restrict__ label_bits, uint64_t n_label_bits, float* __restrict__ bias) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) {
+        return;
+    }
+    bool out = tomb != nullptr && ((tomb[i >> 5] >> (i & 31u)) & 1u);
+    if (!out && deny != nullptr && i < deny_bits) {
+        out = (deny[i >> 5] >> (i & 31u)) & 1u;
+    }
+    if (!out && label_bits != nullptr) {
+        const uint64_t bit = static_cast<uint64_t>(labels[i]) & 0xFFFFFFFFull;
+        out = bit < n_label_bits && ((label_bits[bit >> 6] >> (bit & 63u)) & 1ull);
+    }
+    bias[i] = out ? INFINITY : (norms != nullptr ? norms[i] : 0.f);
+}
+
+__global__ void
+bf_tombstone_kernel(const int64_t* __restrict__ labels, uint64_t n, const int64_t* __restrict__ sorted, uint64_t count,
+                    uint32_t* __restrict__ tomb, unsigned long long* __restrict__ newly) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) {
+        return;
+    }
+    const int64_t label = labels[i];
+    uint64_t lo = 0, hi = count;
+    while (lo < hi) {
+        const uint64_t mid = (lo + hi) >> 1;
+        if (sorted[mid] < label) {
+            lo = mid + 1;
+        } else {
+            hi = mid;
+        }
+    }
+    if (lo < count && sorted[lo] == label) {
+        const uint32_t bit = 1u << (i & 31u);
+        if ((atomicOr(tomb + (i >> 5), bit) & bit) == 0u) {
+            atomicAdd(newly, 1ull);
+        }
+    }
+}
+
 }  // namespace vb200
 
 using namespace vb200;
@@ -123,6 +174,11 @@ struct vb200_bf {
     // (FP32Quantizer / HalfPrecisionQuantizer with METRIC_TYPE_COSINE)
     bool cosine = false;
     DevBuf<float> q_unit;
+    // removed rows (MARK_REMOVE) and the id filter of the running search
+    DevBuf<uint32_t> tombstones;
+    uint64_t tomb_words = 0, n_removed = 0;
+    const vb200_filter* filter = nullptr;
+    DevBuf<float> masked_bias;
     uint64_t n = 0;
     DevBuf<float> base_f32;
     DevBuf<uint16_t> base_bf16;
@@ -202,6 +258,23 @@ bf_append_labels_and_norms(vb200_bf* ix, const int64_t* ids, uint64_t count) {
     } else {
         VB_TRY(row_sqnorm_bf16(ix->base_bf16.ptr + ix->n * ix->dim, count, ix->dim, ix->norms.ptr + ix->n));
     }
+    {
+        // tombstone words for the new rows
+        const uint64_t words = (ix->n + count + 31) / 32;
+        if (words > ix->tomb_words) {
+            DevBuf<uint32_t> bigger;
+            const uint64_t cap = words * 2;
+            VB_TRY(bigger.reserve(cap));
+            VB_CUDA(cudaMemsetAsync(bigger.ptr, 0, cap * sizeof(uint32_t), current_stream()));
+            if (ix->tomb_words > 0) {
+                VB_CUDA(cudaMemcpyAsync(bigger.ptr, ix->tombstones.ptr, ix->tomb_words * sizeof(uint32_t),
+                                        cudaMemcpyDeviceToDevice, current_stream()));
+            }
+            VB_TRY(sync_stream());
+            ix->tombstones = std::move(bigger);
+            ix->tomb_words = cap;
+        }
+    }
     VB_TRY(sync_stream());
     ix->n += count;
     ix->tiled_valid = false;
@@ -266,7 +339,43 @@ vb200_bf_add_bf16(vb200_bf_t ix, const uint16_t* data, uint64_t count, const int
 
 extern "C" int64_t
 vb200_bf_num_elements(vb200_bf_t ix) {
-    return ix == nullptr ? 0 : static_cast<int64_t>(ix->n);
+    return ix == nullptr ? 0 : static_cast<int64_t>(ix->n - ix->n_removed);
+}
+
+extern "C" int
+vb200_bf_remove(vb200_bf_t ix, const int64_t* labels, uint64_t count, uint64_t* removed) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    if (removed != nullptr) {
+        *removed = 0;
+    }
+    if (count == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(labels != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n == 0) {
+        return 0;
+    }
+    std::vector<int64_t> sorted(count);
+    VB_CUDA(cudaMemcpy(sorted.data(), labels, count * sizeof(int64_t), cudaMemcpyDefault));
+    std::sort(sorted.begin(), sorted.end());
+    DevBuf<int64_t> sorted_dev;
+    DevBuf<unsigned long long> newly;
+    VB_TRY(sorted_dev.reserve(count));
+    VB_TRY(newly.reserve(1));
+    cudaStream_t st = current_stream();
+    VB_CUDA(cudaMemcpyAsync(sorted_dev.ptr, sorted.data(), count * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+    VB_CUDA(cudaMemsetAsync(newly.ptr, 0, sizeof(unsigned long long), st));
+    VB_LAUNCH(bf_tombstone_kernel, static_cast<uint32_t>((ix->n + 255) / 256), 256, 0, ix->labels.ptr, ix->n,
+              sorted_dev.ptr, count, ix->tombstones.ptr, newly.ptr);
+    unsigned long long n_new = 0;
+    VB_CUDA(cudaMemcpyAsync(&n_new, newly.ptr, sizeof(n_new), cudaMemcpyDeviceToHost, st));
+    VB_TRY(sync_stream());
+    ix->n_removed += n_new;
+    if (removed != nullptr) {
+        *removed = n_new;
+    }
+    return 0;
 }
 
 // Leaves the k best keys (payload = row) per query in ix->keys.
@@ -299,6 +408,30 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
         VB_LAUNCH(float_to_bf16_kernel, static_cast<uint32_t>((nq * dim + 255) / 256), 256, 0, q_dev,
                   nq * dim, ix->q_bf16.ptr);
     }
+    // score bias per row: |x|^2 for L2, none for IP; +inf for rows that are removed or filtered out
+    const float* bias_all = l2 ? ix->norms.ptr : nullptr;
+    {
+        const vb200_filter* f = ix->filter;
+        const bool user_deny = f != nullptr && f->deny_inner_bits != nullptr && f->n_inner_bits > 0;
+        const bool user_labels = f != nullptr && f->invalid_label_bits != nullptr && f->n_label_bits > 0;
+        if (ix->n_removed > 0 || user_deny || user_labels) {
+            DevInput<uint32_t> deny;
+            DevInput<uint64_t> lbits;
+            if (user_deny) {
+                VB_TRY(deny.bind(f->deny_inner_bits, (f->n_inner_bits + 31) / 32));
+            }
+            if (user_labels) {
+                VB_TRY(lbits.bind(f->invalid_label_bits, (f->n_label_bits + 63) / 64));
+            }
+            VB_TRY(ix->masked_bias.reserve(n));
+            VB_LAUNCH(bf_masked_bias_kernel, static_cast<uint32_t>((n + 255) / 256), 256, 0, bias_all, n,
+                      ix->n_removed > 0 ? ix->tombstones.ptr : nullptr, user_deny ? deny.ptr : nullptr,
+                      user_deny ? f->n_inner_bits : 0, ix->labels.ptr, user_labels ? lbits.ptr : nullptr,
+                      user_labels ? f->n_label_bits : 0, ix->masked_bias.ptr);
+            VB_TRY(sync_stream());   // the staged bitmaps end with this scope
+            bias_all = ix->masked_bias.ptr;
+        }
+    }
     // Large problems nominate candidates on the tensor cores; the exact re-scoring below is the
     // same either way.
     if (tensor_cores_enabled() && kcand <= tc_max_candidates(bf16 ? 1 : 3) && static_cast<double>(nq) * n * dim >= 1e10) {
@@ -325,7 +458,7 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
         TcOperand a{ix->q_hi.ptr, bf16 ? nullptr : ix->q_lo.ptr, nq, chunks};
         TcOperand b{ix->base_hi.ptr, bf16 ? nullptr : ix->base_lo.ptr, n, chunks};
         uint32_t lists = 1;
-        VB_TRY(tc_candidates(ix->tc, a, b, bf16 ? 1 : 3, l2 ? -2.0f : -1.0f, l2 ? ix->norms.ptr : nullptr, kcand, 0,
+        VB_TRY(tc_candidates(ix->tc, a, b, bf16 ? 1 : 3, l2 ? -2.0f : -1.0f, bias_all, kcand, 0,
                              ix->tc_out, &lists));
         VB_TRY(ix->cand.reserve(nq * kcand));
         {
@@ -362,7 +495,7 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
         for (uint32_t c = 0; c < nchunks; ++c) {
             const uint64_t c0 = static_cast<uint64_t>(c) * col_chunk;
             const uint64_t cn = n - c0 < col_chunk ? n - c0 : col_chunk;
-            const float* bias = l2 ? ix->norms.ptr + c0 : nullptr;
+            const float* bias = bias_all != nullptr ? bias_all + c0 : nullptr;
             const float alpha = l2 ? -2.0f : -1.0f;
             if (bf16) {
                 VB_TRY(dense_scores_bf16(ix->q_bf16.ptr + qb * dim, qn, ix->base_bf16.ptr + c0 * dim, cn,
@@ -413,6 +546,12 @@ bf_check_search(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
 extern "C" int
 vb200_bf_search(vb200_bf_t ix, const float* queries, uint64_t nq, uint32_t k, int64_t* ids,
                 float* dists) {
+    return vb200_bf_search_filtered(ix, queries, nq, k, nullptr, ids, dists);
+}
+
+extern "C" int
+vb200_bf_search_filtered(vb200_bf_t ix, const float* queries, uint64_t nq, uint32_t k, const vb200_filter* filter,
+                         int64_t* ids, float* dists) {
     VB_TRY(bf_check_search(ix, queries, nq, k));
     if (nq == 0) {
         return 0;
@@ -427,7 +566,10 @@ vb200_bf_search(vb200_bf_t ix, const float* queries, uint64_t nq, uint32_t k, in
         VB_CUDA(cudaMemcpy(dists, hd.data(), total * sizeof(float), cudaMemcpyDefault));
         return 0;
     }
-    VB_TRY(bf_search_keys(ix, queries, nq, k));
+    ix->filter = filter;
+    const int search_status = bf_search_keys(ix, queries, nq, k);
+    ix->filter = nullptr;
+    VB_TRY(search_status);
     VB_TRY(ix->out_ids.reserve(total));
     VB_TRY(ix->out_dists.reserve(total));
     VB_LAUNCH(bf_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, ix->keys.ptr, total,

@@ -54,6 +54,9 @@ struct SearchWorkspace {
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
     DevBuf<float> q_unit;         // cosine: the queries divided by their norms
+    const vb200_filter* filter = nullptr;   // set for the duration of one filtered search
+    DevBuf<uint32_t> deny_bits;   // tombstones | the caller's deny_inner_bits
+    DevBuf<uint64_t> label_bits;  // device copy of the caller's label bitset
     bool pruning = false;         // the last scan dropped (query, list) pairs by the list radius
     DevBuf<float> bounds;         // [nq] per-query bounds as floats, the buffer the shards exchange
     DevBuf<uint16_t> q_hi, q_lo;  // tensor-core routing: tiled bf16 terms of the queries
@@ -96,6 +99,9 @@ struct vb200_ivf {
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
+    DevBuf<uint32_t> tombstones;  // bitmap over inner ids: vectors removed with MARK_REMOVE
+    uint64_t tomb_words = 0;
+    uint64_t n_removed = 0;
     DevBuf<float> list_radius;    // SQ8: max |decoded row - centroid| per list (list pruning)
     bool prune_lists = true;
     int64_t last_scanned_bytes = 0;
@@ -386,6 +392,42 @@ probe_is_live(int32_t l, uint32_t nlist, uint32_t rank, uint32_t world, const ui
         return false;
     }
     return list_off[l + 1] > list_off[l];
+}
+
+// out = tombstones | extra (either may be shorter than `words`; missing words count as zero).
+__global__ void
+deny_merge_kernel(const uint32_t* __restrict__ tomb, uint64_t tomb_words, const uint32_t* __restrict__ extra,
+                  uint64_t extra_words, uint64_t words, uint32_t* __restrict__ out) {
+    uint64_t w = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (w < words) {
+        out[w] = (w < tomb_words ? tomb[w] : 0u) | (w < extra_words ? extra[w] : 0u);
+    }
+}
+
+// Marks the inner ids whose label is in sorted[0..count): one thread per inner id, binary search.
+__global__ void
+tombstone_kernel(const int64_t* __restrict__ labels, uint64_t n_total, const int64_t* __restrict__ sorted,
+                 uint64_t count, uint32_t* __restrict__ tomb, unsigned long long* __restrict__ newly) {
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_total) {
+        return;
+    }
+    const int64_t label = labels[i];
+    uint64_t lo = 0, hi = count;
+    while (lo < hi) {
+        const uint64_t mid = (lo + hi) >> 1;
+        if (sorted[mid] < label) {
+            lo = mid + 1;
+        } else {
+            hi = mid;
+        }
+    }
+    if (lo < count && sorted[lo] == label) {
+        const uint32_t bit = 1u << (i & 31u);
+        if ((atomicOr(tomb + (i >> 5), bit) & bit) == 0u) {
+            atomicAdd(newly, 1ull);
+        }
+    }
 }
 
 // first_live[q] = probe rank of the nearest list of query q that this shard holds and that is not
@@ -844,6 +886,37 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         p.list_radius = ix->list_radius.ptr;
     }
     p.scanned = reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 3);
+    {
+        // id filter: tombstones and / or the caller's filter of this search
+        const vb200_filter* f = ws.filter;
+        const bool user_deny = f != nullptr && f->deny_inner_bits != nullptr && f->n_inner_bits > 0;
+        const bool user_labels = f != nullptr && f->invalid_label_bits != nullptr && f->n_label_bits > 0;
+        if (ix->n_removed > 0 || user_deny || user_labels) {
+            p.filter_pos_inner = ix->pos_inner.ptr;
+            p.labels = ix->labels.ptr;
+            if (user_deny) {
+                const uint64_t words = (ix->n_total + 31) / 32;
+                const uint64_t extra_words = (f->n_inner_bits + 31) / 32;
+                DevInput<uint32_t> extra;
+                VB_TRY(extra.bind(f->deny_inner_bits, extra_words));
+                VB_TRY(ws.deny_bits.reserve(words));
+                VB_LAUNCH(deny_merge_kernel, static_cast<uint32_t>((words + 255) / 256), 256, 0, ix->tombstones.ptr,
+                          ix->tomb_words, extra.ptr, extra_words, words, ws.deny_bits.ptr);
+                VB_TRY(sync_stream());   // `extra` may be a staging copy that ends with this scope
+                p.deny_inner_bits = ws.deny_bits.ptr;
+            } else if (ix->n_removed > 0) {
+                p.deny_inner_bits = ix->tombstones.ptr;
+            }
+            if (user_labels) {
+                const uint64_t words = (f->n_label_bits + 63) / 64;
+                VB_TRY(ws.label_bits.reserve(words));
+                VB_CUDA(cudaMemcpyAsync(ws.label_bits.ptr, f->invalid_label_bits, words * sizeof(uint64_t),
+                                        cudaMemcpyDefault, st));
+                p.invalid_label_bits = ws.label_bits.ptr;
+                p.n_label_bits = f->n_label_bits;
+            }
+        }
+    }
     if (sq8) {
         VB_LAUNCH(sq8_query_prep_kernel, static_cast<uint32_t>((nq + 3) / 4), 128, 0, q_dev, nq, ix->dim,
                   ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
@@ -1379,7 +1452,23 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
         VB_TRY(rabitq_encode_device(xr, count, dim, ix->rotation.ptr, ix->rq_centroid.ptr,
                                     dst_of_row.ptr, new_codes.ptr, stride));
     }
-    // 6. labels and (for reorder) the fp32 rows, by inner id
+    // 6. labels and (for reorder) the fp32 rows, by inner id; tombstone words for the new ids
+    {
+        const uint64_t words = (ix->n_total + count + 31) / 32;
+        if (words > ix->tomb_words) {
+            DevBuf<uint32_t> bigger;
+            const uint64_t cap = words * 2;
+            VB_TRY(bigger.reserve(cap));
+            VB_CUDA(cudaMemsetAsync(bigger.ptr, 0, cap * sizeof(uint32_t), st));
+            if (ix->tomb_words > 0) {
+                VB_CUDA(cudaMemcpyAsync(bigger.ptr, ix->tombstones.ptr, ix->tomb_words * sizeof(uint32_t),
+                                        cudaMemcpyDeviceToDevice, st));
+            }
+            VB_TRY(sync_stream());
+            ix->tombstones = std::move(bigger);
+            ix->tomb_words = cap;
+        }
+    }
     VB_TRY(grow_preserve(ix->labels, ix->n_total, ix->n_total + count));
     VB_CUDA(cudaMemcpyAsync(ix->labels.ptr + ix->n_total, ids, count * sizeof(int64_t),
                             cudaMemcpyDefault, st));
@@ -1411,9 +1500,45 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     return ivf_refresh_scan_order(ix);
 }
 
+extern "C" int
+vb200_ivf_remove(vb200_ivf_t ix, const int64_t* labels, uint64_t count, uint64_t* removed) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    if (removed != nullptr) {
+        *removed = 0;
+    }
+    if (count == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(labels != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total == 0) {
+        return 0;
+    }
+    std::vector<int64_t> sorted(count);
+    VB_CUDA(cudaMemcpy(sorted.data(), labels, count * sizeof(int64_t), cudaMemcpyDefault));
+    std::sort(sorted.begin(), sorted.end());
+    DevBuf<int64_t> sorted_dev;
+    DevBuf<unsigned long long> newly;
+    VB_TRY(sorted_dev.reserve(count));
+    VB_TRY(newly.reserve(1));
+    cudaStream_t st = current_stream();
+    VB_CUDA(cudaMemcpyAsync(sorted_dev.ptr, sorted.data(), count * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+    VB_CUDA(cudaMemsetAsync(newly.ptr, 0, sizeof(unsigned long long), st));
+    VB_LAUNCH(tombstone_kernel, static_cast<uint32_t>((ix->n_total + 255) / 256), 256, 0, ix->labels.ptr, ix->n_total,
+              sorted_dev.ptr, count, ix->tombstones.ptr, newly.ptr);
+    unsigned long long n_new = 0;
+    VB_CUDA(cudaMemcpyAsync(&n_new, newly.ptr, sizeof(n_new), cudaMemcpyDeviceToHost, st));
+    VB_TRY(sync_stream());
+    ix->n_removed += n_new;
+    if (removed != nullptr) {
+        *removed = n_new;
+    }
+    return 0;
+}
+
 extern "C" int64_t
 vb200_ivf_num_elements(vb200_ivf_t ix) {
-    return ix == nullptr ? 0 : static_cast<int64_t>(ix->n_total);
+    return ix == nullptr ? 0 : static_cast<int64_t>(ix->n_total - ix->n_removed);
 }
 
 extern "C" int64_t
@@ -1488,6 +1613,13 @@ vb200_ivf_route(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t npro
 extern "C" int
 vb200_ivf_search(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe,
                  float factor, const int32_t* bucket_ids, int64_t* ids, float* dists) {
+    return vb200_ivf_search_filtered(ix, queries, nq, k, nprobe, factor, bucket_ids, nullptr, ids, dists);
+}
+
+extern "C" int
+vb200_ivf_search_filtered(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe,
+                          float factor, const int32_t* bucket_ids, const vb200_filter* filter, int64_t* ids,
+                          float* dists) {
     VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
     if (nq == 0) {
         return 0;
@@ -1508,7 +1640,10 @@ vb200_ivf_search(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, 
         return 0;
     }
     const uint64_t* keys = nullptr;
-    VB_TRY(ivf_search_keys(ix, queries, nq, k, nprobe, factor, bucket_ids, &keys));
+    ws.filter = filter;
+    const int search_status = ivf_search_keys(ix, queries, nq, k, nprobe, factor, bucket_ids, &keys);
+    ws.filter = nullptr;
+    VB_TRY(search_status);
     VB_LAUNCH(keys_to_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
               ix->labels.ptr, ws.out_ids.ptr, ws.out_dists.ptr);
     VB_TRY(copy_out(ids, ws.out_ids.ptr, total));

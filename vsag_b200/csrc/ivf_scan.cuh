@@ -60,7 +60,32 @@ struct ScanParams {
     const float* centroids;      // [nlist x dim]
     const float* list_radius;    // [nlist] max |decoded row - centroid|, rounded up
     unsigned long long* scanned; // bytes of codes actually scanned (pairs kept x list length x code size)
+    // Id filter (filter_pos_inner null = none): a row is skipped when its inner id is tombstoned or
+    // when bit (label & 0xFFFFFFFF) of the caller's bitset is set (BlackListFilter::CheckValid,
+    // src/impl/filter/black_list_filter.cpp:25-31; deleted ids: InnerIndexInterface::create_search_filter,
+    // src/algorithm/inner_index_interface.cpp:1100-1131).
+    const uint32_t* filter_pos_inner;    // [positions] inner id of each stored row
+    const uint32_t* deny_inner_bits;     // bitmap over inner ids, or null
+    const int64_t* labels;               // [n_total] label per inner id (for the label bitset)
+    const uint64_t* invalid_label_bits;  // caller's bitset over labels, or null
+    uint64_t n_label_bits;
 };
+
+// True when the row at `pos` must not become a candidate.
+__device__ __forceinline__ bool
+scan_row_filtered(const ScanParams& p, uint32_t pos) {
+    const uint32_t inner = __ldg(p.filter_pos_inner + pos);
+    if (p.deny_inner_bits != nullptr && ((__ldg(p.deny_inner_bits + (inner >> 5)) >> (inner & 31u)) & 1u)) {
+        return true;
+    }
+    if (p.invalid_label_bits != nullptr) {
+        const uint64_t bit = static_cast<uint64_t>(__ldg(p.labels + inner)) & 0xFFFFFFFFull;
+        if (bit < p.n_label_bits && ((__ldg(p.invalid_label_bits + (bit >> 6)) >> (bit & 63u)) & 1ull)) {
+            return true;
+        }
+    }
+    return false;
+}
 
 // Per-tile selection state in shared memory.
 //
@@ -89,6 +114,20 @@ struct TileSelect {
     __device__ __forceinline__ void
     push(int qi, float partial, uint32_t pos) {
         if (partial <= thrq[qi]) {
+            float dist = partial + qa[qi];
+            uint32_t s = atomicAdd(&cnt[qi], 1u);
+            keys[static_cast<uint32_t>(qi) * cap + s] = make_key(dist, pos);
+        }
+    }
+
+    // The same with an id filter: only rows that beat the bound are looked up (few), so the filter
+    // costs nothing on the rows the bound rejects anyway.
+    __device__ __forceinline__ void
+    push(const ScanParams& p, int qi, float partial, uint32_t pos) {
+        if (partial <= thrq[qi]) {
+            if (p.filter_pos_inner != nullptr && scan_row_filtered(p, pos)) {
+                return;
+            }
             float dist = partial + qa[qi];
             uint32_t s = atomicAdd(&cnt[qi], 1u);
             keys[static_cast<uint32_t>(qi) * cap + s] = make_key(dist, pos);
@@ -482,7 +521,7 @@ ivf_sq8_scan_kernel(const ScanParams p) {
 #pragma unroll
                         for (int qi = 0; qi < QT; ++qi) {
                             if (qi < nqt) {
-                                ts.push(qi, fmaf(p.coef_c, acc[r][qi], xb), pos);
+                                ts.push(p, qi, fmaf(p.coef_c, acc[r][qi], xb), pos);
                             }
                         }
                     }
@@ -653,7 +692,7 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
                         float p2 = __fmul_rn(qn, qn);
                         float p3 = __fmul_rn(__fmul_rn(__fmul_rn(-2.0f, bn), qn), est);
                         float dist = __fadd_rn(__fadd_rn(p1, p2), p3);
-                        ts.push(qi, dist, lbeg + row);
+                        ts.push(p, qi, dist, lbeg + row);
                     }
                 }
             }
@@ -761,7 +800,7 @@ ivf_fp32_scan_kernel(const ScanParams p) {
                 for (int qi = 0; qi < QT; ++qi) {
                     if (qi < nqt) {
                         const float dist = p.metric == 0 ? acc[qi] : __fsub_rn(1.0f, acc[qi]);
-                        ts.push(qi, dist, lbeg + row);
+                        ts.push(p, qi, dist, lbeg + row);
                     }
                 }
             }

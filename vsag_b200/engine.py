@@ -262,6 +262,31 @@ class IvfHandle:
                                          ptr(bucket_ids, np.int32), ptr(ids), ptr(dists)))
         return ids, dists
 
+    def remove(self, labels) -> int:
+        """Marks the vectors with these labels as removed; returns how many were newly marked."""
+        labels = np.ascontiguousarray(labels, np.int64)
+        n = C.c_uint64(0)
+        check(self._lib.vb200_ivf_remove(self._h, ptr(labels, np.int64), labels.size, C.byref(n)))
+        return int(n.value)
+
+    def search_filtered(self, queries, k: int, nprobe: int, factor: float = 2.0, bucket_ids=None,
+                        invalid_label_bits=None, deny_inner_bits=None):
+        """invalid_label_bits: uint64 words, bit (label & 0xFFFFFFFF) set = filtered out;
+        deny_inner_bits: uint32 words over insertion order."""
+        nq = _rows(queries)
+        ids = _empty_like_side(queries, (nq, k), np.int64)
+        dists = _empty_like_side(queries, (nq, k), np.float32)
+        f = _capi.Filter()
+        if invalid_label_bits is not None:
+            invalid_label_bits = np.ascontiguousarray(invalid_label_bits, np.uint64)
+            f.invalid_label_bits, f.n_label_bits = invalid_label_bits.ctypes.data, invalid_label_bits.size * 64
+        if deny_inner_bits is not None:
+            deny_inner_bits = np.ascontiguousarray(deny_inner_bits, np.uint32)
+            f.deny_inner_bits, f.n_inner_bits = deny_inner_bits.ctypes.data, deny_inner_bits.size * 32
+        check(self._lib.vb200_ivf_search_filtered(self._h, ptr(queries, np.float32), nq, k, nprobe, factor,
+                                                  ptr(bucket_ids, np.int32), C.byref(f), ptr(ids), ptr(dists)))
+        return ids, dists
+
     def search_partial(self, queries, k: int, nprobe: int, factor: float, keys_dev, labels_dev,
                        bucket_ids=None, exchange=None) -> None:
         """exchange: an _capi.EXCHANGE_FN instance (kept alive by the caller) that reduces the
@@ -321,6 +346,27 @@ class BfHandle:
         else:
             ids, dists = out
         check(self._lib.vb200_bf_search(self._h, ptr(queries, np.float32), nq, k, ptr(ids), ptr(dists)))
+        return ids, dists
+
+    def remove(self, labels) -> int:
+        labels = np.ascontiguousarray(labels, np.int64)
+        n = C.c_uint64(0)
+        check(self._lib.vb200_bf_remove(self._h, ptr(labels, np.int64), labels.size, C.byref(n)))
+        return int(n.value)
+
+    def search_filtered(self, queries, k: int, invalid_label_bits=None, deny_inner_bits=None):
+        nq = _rows(queries)
+        ids = _empty_like_side(queries, (nq, k), np.int64)
+        dists = _empty_like_side(queries, (nq, k), np.float32)
+        f = _capi.Filter()
+        if invalid_label_bits is not None:
+            invalid_label_bits = np.ascontiguousarray(invalid_label_bits, np.uint64)
+            f.invalid_label_bits, f.n_label_bits = invalid_label_bits.ctypes.data, invalid_label_bits.size * 64
+        if deny_inner_bits is not None:
+            deny_inner_bits = np.ascontiguousarray(deny_inner_bits, np.uint32)
+            f.deny_inner_bits, f.n_inner_bits = deny_inner_bits.ctypes.data, deny_inner_bits.size * 32
+        check(self._lib.vb200_bf_search_filtered(self._h, ptr(queries, np.float32), nq, k, C.byref(f), ptr(ids),
+                                                 ptr(dists)))
         return ids, dists
 
     def search_partial(self, queries, k: int, keys_dev, labels_dev) -> None:

@@ -178,6 +178,69 @@ vsag_index_knn_search_batch(vsag_index_t index, const float* queries, uint64_t d
     return success();
 }
 
+// Two additions to the reference's C interface (include/vsag/vsag_c_api.h has no filter or remove
+// entry point; the C++ interface does, include/vsag/index.h:186-200, 276-303).
+// invalid_bits: n_words 64-bit words, bit (id & 0xFFFFFFFF) set = filtered out; may be NULL.
+// deny_modulus > 0 additionally filters, through the callback overload, every id with
+// id % deny_modulus == 0 (a stand-in for a host callback, for bindings that cannot pass one).
+VSAG_C_EXPORT Error_t
+vsag_index_knn_search_filtered(vsag_index_t index, const float* query, uint64_t dim, int64_t k, const char* parameters,
+                               const uint64_t* invalid_bits, uint64_t n_words, int64_t deny_modulus,
+                               SearchResult_t* search_result) {
+    if (search_result == nullptr) {
+        return make_error(-1, "search result is NULL");
+    }
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (k <= 0) {
+        return make_error(-3, "knn_search requires k >= 1");
+    }
+    const std::string params = parameters == nullptr ? "{}" : parameters;
+    auto q = borrow(query, nullptr, dim, 1);
+    auto r = [&]() {
+        if (deny_modulus > 0) {
+            return box->index->KnnSearch(q, k, params, [=](int64_t id) { return id % deny_modulus == 0; });
+        }
+        auto bits = vsag::Bitset::Make();
+        for (uint64_t w = 0; invalid_bits != nullptr && w < n_words; ++w) {
+            for (int b = 0; b < 64; ++b) {
+                if ((invalid_bits[w] >> b) & 1u) {
+                    bits->Set(static_cast<int64_t>(w * 64 + b));
+                }
+            }
+        }
+        return box->index->KnnSearch(q, k, params, bits);
+    }();
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    int64_t to_write = std::min<int64_t>(r.value()->GetDim(), k);
+    for (int64_t i = 0; i < to_write; ++i) {
+        search_result->ids[i] = r.value()->GetIds()[i];
+        search_result->dists[i] = r.value()->GetDistances()[i];
+    }
+    search_result->count = to_write;
+    return success();
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_remove(vsag_index_t index, const int64_t* ids, uint64_t count, uint32_t* removed) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    auto r = box->index->Remove(std::vector<int64_t>(ids, ids + count));
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    if (removed != nullptr) {
+        *removed = r.value();
+    }
+    return success();
+}
+
 VSAG_C_EXPORT int64_t
 vsag_index_get_num_elements(vsag_index_t index) {
     auto* box = static_cast<IndexBox*>(index);

@@ -391,6 +391,46 @@ public:
 
     Expected<DatasetPtr>
     KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters) const override {
+        return knn_impl(query, k, parameters, nullptr);
+    }
+
+    Expected<DatasetPtr>
+    KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters, BitsetPtr invalid) const override {
+        if (invalid == nullptr || invalid->Words().empty()) {
+            return knn_impl(query, k, parameters, nullptr);
+        }
+        vb200_filter f{invalid->Words().data(), invalid->Words().size() * 64, nullptr, 0};
+        return knn_impl(query, k, parameters, &f);
+    }
+
+    Expected<DatasetPtr>
+    KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters,
+              const std::function<bool(int64_t)>& filter) const override {
+        if (!filter) {
+            return knn_impl(query, k, parameters, nullptr);
+        }
+        // the callback is evaluated once per stored vector and becomes a bitmap over insertion order
+        std::vector<uint32_t> deny((labels_host_.size() + 31) / 32, 0);
+        for (size_t i = 0; i < labels_host_.size(); ++i) {
+            if (filter(labels_host_[i])) {
+                deny[i >> 5] |= 1u << (i & 31);
+            }
+        }
+        vb200_filter f{nullptr, 0, deny.data(), labels_host_.size()};
+        return knn_impl(query, k, parameters, &f);
+    }
+
+    Expected<uint32_t>
+    Remove(const std::vector<int64_t>& ids) override {
+        return safe_call<uint32_t>([&]() {
+            uint64_t removed = 0;
+            check_status(remove_labels(ids.data(), ids.size(), &removed));
+            return static_cast<uint32_t>(removed);
+        });
+    }
+
+    Expected<DatasetPtr>
+    knn_impl(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter) const {
         return safe_call<DatasetPtr>([&]() {
             check_argument(query != nullptr, "query is null");
             check_argument(k > 0, "k must be greater than 0");
@@ -430,9 +470,9 @@ public:
             }
             auto* ids = new int64_t[static_cast<size_t>(nq * k)];
             auto* dists = new float[static_cast<size_t>(nq * k)];
-            int status = vb200_ivf_search(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
-                                          static_cast<uint32_t>(std::min<int64_t>(nprobe, 0x7fffffff)),
-                                          static_cast<float>(factor), nullptr, ids, dists);
+            int status = vb200_ivf_search_filtered(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
+                                                   static_cast<uint32_t>(std::min<int64_t>(nprobe, 0x7fffffff)),
+                                                   static_cast<float>(factor), nullptr, filter, ids, dists);
             if (status != 0) {
                 delete[] ids;
                 delete[] dists;
@@ -495,7 +535,15 @@ private:
     add_locked(const DatasetPtr& base) {
         check_status(vb200_ivf_add(handle_, base->GetFloat32Vectors(), static_cast<uint64_t>(base->GetNumElements()),
                                    base->GetIds(), nullptr));
+        labels_host_.insert(labels_host_.end(), base->GetIds(), base->GetIds() + base->GetNumElements());
     }
+
+    int
+    remove_labels(const int64_t* ids, uint64_t count, uint64_t* removed) {
+        return vb200_ivf_remove(handle_, ids, count, removed);
+    }
+
+    std::vector<int64_t> labels_host_;   // ids in insertion order, for callback filters
 
     uint32_t dim_;
     int metric_;
@@ -570,6 +618,46 @@ public:
 
     Expected<DatasetPtr>
     KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters) const override {
+        return knn_impl(query, k, parameters, nullptr);
+    }
+
+    Expected<DatasetPtr>
+    KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters, BitsetPtr invalid) const override {
+        if (invalid == nullptr || invalid->Words().empty()) {
+            return knn_impl(query, k, parameters, nullptr);
+        }
+        vb200_filter f{invalid->Words().data(), invalid->Words().size() * 64, nullptr, 0};
+        return knn_impl(query, k, parameters, &f);
+    }
+
+    Expected<DatasetPtr>
+    KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters,
+              const std::function<bool(int64_t)>& filter) const override {
+        if (!filter) {
+            return knn_impl(query, k, parameters, nullptr);
+        }
+        // the callback is evaluated once per stored vector and becomes a bitmap over insertion order
+        std::vector<uint32_t> deny((labels_host_.size() + 31) / 32, 0);
+        for (size_t i = 0; i < labels_host_.size(); ++i) {
+            if (filter(labels_host_[i])) {
+                deny[i >> 5] |= 1u << (i & 31);
+            }
+        }
+        vb200_filter f{nullptr, 0, deny.data(), labels_host_.size()};
+        return knn_impl(query, k, parameters, &f);
+    }
+
+    Expected<uint32_t>
+    Remove(const std::vector<int64_t>& ids) override {
+        return safe_call<uint32_t>([&]() {
+            uint64_t removed = 0;
+            check_status(remove_labels(ids.data(), ids.size(), &removed));
+            return static_cast<uint32_t>(removed);
+        });
+    }
+
+    Expected<DatasetPtr>
+    knn_impl(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter) const {
         return safe_call<DatasetPtr>([&]() {
             check_argument(query != nullptr, "query is null");
             check_argument(k > 0, "k must be greater than 0");
@@ -584,7 +672,8 @@ public:
             const int64_t nq = query->GetNumElements();
             auto* ids = new int64_t[static_cast<size_t>(nq * k)];
             auto* dists = new float[static_cast<size_t>(nq * k)];
-            int status = vb200_bf_search(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k), ids, dists);
+            int status = vb200_bf_search_filtered(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
+                                                  filter, ids, dists);
             if (status != 0) {
                 delete[] ids;
                 delete[] dists;
@@ -615,12 +704,21 @@ private:
                            "dataset does not match the index");
             check_status(vb200_bf_add_bf16(handle_, base->GetFloat16Vectors(),
                                            static_cast<uint64_t>(base->GetNumElements()), base->GetIds()));
+            labels_host_.insert(labels_host_.end(), base->GetIds(), base->GetIds() + base->GetNumElements());
             return;
         }
         check_base(base, dim_, true);
         check_status(vb200_bf_add(handle_, base->GetFloat32Vectors(), static_cast<uint64_t>(base->GetNumElements()),
                                   base->GetIds()));
+        labels_host_.insert(labels_host_.end(), base->GetIds(), base->GetIds() + base->GetNumElements());
     }
+
+    int
+    remove_labels(const int64_t* ids, uint64_t count, uint64_t* removed) {
+        return vb200_bf_remove(handle_, ids, count, removed);
+    }
+
+    std::vector<int64_t> labels_host_;   // ids in insertion order, for callback filters
 
     uint32_t dim_;
     int metric_;

@@ -96,6 +96,33 @@ private:
     std::string statistics_;
 };
 
+// Growable bit set for the pre-filter of a search (include/vsag/bitset.h): bit i set means that the
+// vector whose id is i (id & 0xFFFFFFFF) is filtered out.
+class Bitset {
+public:
+    static std::shared_ptr<Bitset> Make() { return std::make_shared<Bitset>(); }
+    void Set(int64_t pos, bool value = true) {
+        const size_t word = static_cast<size_t>(pos) >> 6;
+        if (word >= words_.size()) {
+            if (!value) {
+                return;
+            }
+            words_.resize(word + 1, 0);
+        }
+        const uint64_t bit = uint64_t{1} << (pos & 63);
+        words_[word] = value ? (words_[word] | bit) : (words_[word] & ~bit);
+    }
+    bool Test(int64_t pos) const {
+        const size_t word = static_cast<size_t>(pos) >> 6;
+        return word < words_.size() && ((words_[word] >> (pos & 63)) & 1u) != 0;
+    }
+    const std::vector<uint64_t>& Words() const { return words_; }
+
+private:
+    std::vector<uint64_t> words_;
+};
+using BitsetPtr = std::shared_ptr<Bitset>;
+
 class Index {
 public:
     virtual ~Index() = default;
@@ -108,6 +135,15 @@ public:
     // (<= k); a batch returns NumElements = Q, Dim = k padded with id -1 / distance +inf.
     virtual Expected<DatasetPtr> KnnSearch(const DatasetPtr& query, int64_t k,
                                            const std::string& parameters) const = 0;
+    // The same search with a pre-filter (include/vsag/index.h:276-303): `invalid` marks ids that are
+    // filtered out; `filter` returns true for an id that is filtered out.
+    virtual Expected<DatasetPtr> KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters,
+                                           BitsetPtr invalid) const = 0;
+    virtual Expected<DatasetPtr> KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters,
+                                           const std::function<bool(int64_t)>& filter) const = 0;
+    // RemoveMode::MARK_REMOVE (include/vsag/index.h:186-200): the vectors stay stored but are never
+    // returned again; the result is the number of ids found and newly marked.
+    virtual Expected<uint32_t> Remove(const std::vector<int64_t>& ids) = 0;
     virtual int64_t GetNumElements() const = 0;
     virtual int64_t GetMemoryUsage() const = 0;
     virtual std::string GetIndexType() const = 0;

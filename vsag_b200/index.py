@@ -49,6 +49,11 @@ def _lib():
         lib.vsag_index_knn_search_batch.restype = _Error
         lib.vsag_index_knn_search_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int64,
                                                     C.c_char_p, C.c_void_p, C.c_void_p]
+        lib.vsag_index_knn_search_filtered.restype = _Error
+        lib.vsag_index_knn_search_filtered.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int64, C.c_char_p,
+                                                       C.c_void_p, C.c_uint64, C.c_int64, C.POINTER(_SearchResult)]
+        lib.vsag_index_remove.restype = _Error
+        lib.vsag_index_remove.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32)]
         lib.vsag_index_get_num_elements.restype = C.c_int64
         lib.vsag_index_get_num_elements.argtypes = [C.c_void_p]
         _bound = True
@@ -102,6 +107,31 @@ class Index:
         _check(_lib().vsag_index_knn_search(self._h, vector.ctypes.data, vector.size, k, parameters.encode(),
                                             C.byref(res)))
         return ids[: res.count].copy(), dists[: res.count].copy()
+
+    def knn_search_filtered(self, vector, k: int, parameters: str = "{}", invalid_ids=None, deny_modulus: int = 0):
+        """knn_search with a pre-filter: `invalid_ids` become the bitset of filtered-out ids;
+        `deny_modulus` > 0 filters every id divisible by it through the callback overload."""
+        vector = np.ascontiguousarray(vector, np.float32).reshape(-1)
+        ids = np.empty(max(k, 1), np.int64)
+        dists = np.empty(max(k, 1), np.float32)
+        res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
+        words = None
+        if invalid_ids is not None and len(invalid_ids) > 0:
+            invalid_ids = np.asarray(invalid_ids, np.int64) & 0xFFFFFFFF
+            words = np.zeros(int(invalid_ids.max()) // 64 + 1, np.uint64)
+            np.bitwise_or.at(words, invalid_ids // 64, np.uint64(1) << (invalid_ids % 64).astype(np.uint64))
+        _check(_lib().vsag_index_knn_search_filtered(
+            self._h, vector.ctypes.data, vector.size, k, parameters.encode(),
+            None if words is None else words.ctypes.data, 0 if words is None else words.size, deny_modulus,
+            C.byref(res)))
+        return ids[: res.count].copy(), dists[: res.count].copy()
+
+    def remove(self, ids) -> int:
+        """Index::Remove with MARK_REMOVE: how many of the ids were found and newly marked."""
+        ids = np.ascontiguousarray(ids, np.int64)
+        removed = C.c_uint32(0)
+        _check(_lib().vsag_index_remove(self._h, ids.ctypes.data, ids.size, C.byref(removed)))
+        return int(removed.value)
 
     def knn_search_batch(self, vectors, k: int, parameters: str = "{}"):
         """nq queries -> ids[nq, k], dists[nq, k] padded with -1 / +inf."""
