@@ -102,7 +102,8 @@ struct vb200_ivf {
     DevBuf<uint32_t> tombstones;  // bitmap over inner ids: vectors removed with MARK_REMOVE
     uint64_t tomb_words = 0;
     uint64_t n_removed = 0;
-    DevBuf<float> list_radius;    // SQ8: max |decoded row - centroid| per list (list pruning)
+    DevBuf<float> ball_centre;    // SQ8 list pruning: [nlist][SQ8_BALLS][dim] centres of the covering balls
+    DevBuf<float> ball_radius;    // [nlist][SQ8_BALLS] their radii (-1: empty)
     bool prune_lists = true;
     int64_t last_scanned_bytes = 0;
     // tensor-core routing: the centroids as tiled bf16 hi/lo terms (rebuilt when they change)
@@ -268,44 +269,143 @@ sq8_code_norm_kernel(const uint8_t* __restrict__ codes, uint64_t n, uint32_t dim
     code_norm[p] = s;
 }
 
-// One warp per list: radius[l] = max over the list's rows of |decoded row - centroid_l|, rounded
-// up a little, the ball the scan's list pruning relies on.  Empty lists get 0.
+// Covering balls of a list for the scan's pruning: SQ8_BALLS centres per list (farthest-point
+// seeds refined by two Lloyd steps over the list's decoded rows) and, per centre, the largest
+// distance of a row assigned to it, rounded up.  Every row lies in the ball it is assigned to, so
+// a query farther than that from every ball cannot have a neighbour in the list -- whatever the
+// quality of the little clustering.  A list that holds two clusters of the data gets two small
+// balls instead of one large one.  One CTA per list; empty balls have radius -1.
+__device__ __forceinline__ float
+sq8_row_dist(const uint8_t* __restrict__ row, uint32_t dim, const float* __restrict__ lower,
+             const float* __restrict__ diff, const float* __restrict__ centre) {
+    const float inv255 = 1.0f / 255.0f;
+    float s = 0.f;
+    for (uint32_t d0 = 0; d0 < dim; d0 += 16) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(row + d0));
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            uint32_t d = d0 + j;
+            if (d < dim) {
+                float code = static_cast<float>((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+                float x = fmaf(__fmul_rn(code, inv255), __ldg(diff + d), __ldg(lower + d));
+                float t = x - centre[d];
+                s = fmaf(t, t, s);
+            }
+        }
+    }
+    return s;
+}
+
 __global__ void __launch_bounds__(128)
-sq8_list_radius_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, uint32_t dim,
-                       const uint32_t* __restrict__ list_off, uint32_t nlist, const float* __restrict__ lower,
-                       const float* __restrict__ diff, const float* __restrict__ centroids,
-                       float* __restrict__ radius) {
-    const uint32_t l = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (l >= nlist) {
+sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, uint32_t dim,
+                      const uint32_t* __restrict__ list_off, const float* __restrict__ lower,
+                      const float* __restrict__ diff, const float* __restrict__ centroids,
+                      float* __restrict__ ball_centre, float* __restrict__ ball_radius) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* seeds = reinterpret_cast<float*>(smem_raw);              // [SQ8_BALLS][dim]
+    float* sums = seeds + SQ8_BALLS * dim;                          // [SQ8_BALLS][dim]
+    __shared__ unsigned long long best;                             // (ordered distance << 32) | row
+    __shared__ uint32_t cnt[SQ8_BALLS];
+    __shared__ uint32_t rmax[SQ8_BALLS];
+    const uint32_t l = blockIdx.x, tid = threadIdx.x;
+    const uint32_t beg = list_off[l], len = list_off[l + 1] - beg;
+    float* out_c = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
+    float* out_r = ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS;
+    if (len == 0) {
+        for (uint32_t i = tid; i < SQ8_BALLS * dim; i += blockDim.x) {
+            out_c[i] = 0.f;
+        }
+        if (tid < SQ8_BALLS) {
+            out_r[tid] = -1.0f;
+        }
         return;
     }
-    const float* c = centroids + static_cast<uint64_t>(l) * dim;
     const float inv255 = 1.0f / 255.0f;
-    float worst = 0.f;
-    for (uint32_t p = list_off[l] + lane; p < list_off[l + 1]; p += 32) {
-        const uint8_t* row = codes + static_cast<uint64_t>(p) * code_stride;
-        float s = 0.f;
-        for (uint32_t d0 = 0; d0 < dim; d0 += 16) {
-            uint4 v = __ldg(reinterpret_cast<const uint4*>(row + d0));
-            uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                uint32_t d = d0 + j;
-                if (d < dim) {
-                    float code = static_cast<float>((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
-                    float x = fmaf(__fmul_rn(code, inv255), __ldg(diff + d), __ldg(lower + d));
-                    float t = x - __ldg(c + d);
-                    s = fmaf(t, t, s);
+    auto row_ptr = [&](uint32_t r) { return codes + static_cast<uint64_t>(beg + r) * code_stride; };
+    auto decode_to = [&](uint32_t r, float* dst) {   // all threads: dst[d] = decoded row r
+        const uint8_t* row = row_ptr(r);
+        for (uint32_t d = tid; d < dim; d += blockDim.x) {
+            dst[d] = fmaf(__fmul_rn(static_cast<float>(row[d]), inv255), __ldg(diff + d), __ldg(lower + d));
+        }
+    };
+    // farthest-point seeding, starting from the row farthest from the list's centroid
+    for (uint32_t d = tid; d < dim; d += blockDim.x) {
+        sums[d] = centroids[static_cast<uint64_t>(l) * dim + d];
+    }
+    for (int j = 0; j < SQ8_BALLS; ++j) {
+        if (tid == 0) {
+            best = 0ull;
+        }
+        __syncthreads();
+        unsigned long long mine = 0ull;
+        for (uint32_t r = tid; r < len; r += blockDim.x) {
+            float dmin;
+            if (j == 0) {
+                dmin = sq8_row_dist(row_ptr(r), dim, lower, diff, sums);
+            } else {
+                dmin = INFINITY;
+                for (int t = 0; t < j; ++t) {
+                    dmin = fminf(dmin, sq8_row_dist(row_ptr(r), dim, lower, diff, seeds + t * dim));
+                }
+            }
+            const unsigned long long key = (static_cast<unsigned long long>(__float_as_uint(dmin)) << 32) | (len - 1 - r);
+            mine = key > mine ? key : mine;   // distances are non-negative: their bit patterns order like the values
+        }
+        atomicMax(&best, mine);
+        __syncthreads();
+        const uint32_t pick = len - 1 - static_cast<uint32_t>(best & 0xFFFFFFFFull);
+        decode_to(pick < len ? pick : 0, seeds + j * dim);
+        __syncthreads();
+    }
+    // two Lloyd steps, then the radii
+    for (int it = 0; it < 3; ++it) {
+        const bool last = it == 2;
+        for (uint32_t i = tid; i < SQ8_BALLS * dim; i += blockDim.x) {
+            sums[i] = 0.f;
+        }
+        if (tid < SQ8_BALLS) {
+            cnt[tid] = 0;
+            rmax[tid] = 0;
+        }
+        __syncthreads();
+        for (uint32_t r = tid; r < len; r += blockDim.x) {
+            int arg = 0;
+            float dbest = INFINITY;
+            for (int t = 0; t < SQ8_BALLS; ++t) {
+                const float dd = sq8_row_dist(row_ptr(r), dim, lower, diff, seeds + t * dim);
+                if (dd < dbest) {
+                    dbest = dd;
+                    arg = t;
+                }
+            }
+            atomicAdd(&cnt[arg], 1u);
+            if (last) {
+                atomicMax(&rmax[arg], __float_as_uint(dbest));
+            } else {
+                const uint8_t* row = row_ptr(r);
+                for (uint32_t d = 0; d < dim; ++d) {
+                    const float x = fmaf(__fmul_rn(static_cast<float>(row[d]), inv255), __ldg(diff + d), __ldg(lower + d));
+                    atomicAdd(&sums[arg * dim + d], x);
                 }
             }
         }
-        worst = fmaxf(worst, s);
+        __syncthreads();
+        if (!last) {
+            for (uint32_t i = tid; i < SQ8_BALLS * dim; i += blockDim.x) {
+                const uint32_t c = cnt[i / dim];
+                if (c > 0) {
+                    seeds[i] = sums[i] / static_cast<float>(c);
+                }
+            }
+            __syncthreads();
+        }
     }
-    for (int o = 16; o > 0; o >>= 1) {
-        worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+    for (uint32_t i = tid; i < SQ8_BALLS * dim; i += blockDim.x) {
+        out_c[i] = seeds[i];
     }
-    if (lane == 0) {
-        radius[l] = sqrtf(worst) * 1.00001f;
+    if (tid < SQ8_BALLS) {
+        out_r[tid] = cnt[tid] > 0 ? sqrtf(__uint_as_float(rmax[tid])) * 1.00001f + 1e-12f : -1.0f;
     }
 }
 
@@ -880,10 +980,10 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.coef_c = ix->metric == VB200_METRIC_L2 ? -2.0f : -1.0f;
     p.inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(ix->dim));
     p.metric = ix->metric;
-    ws.pruning = sq8 && ix->prune_lists && ix->list_radius.ptr != nullptr;
+    ws.pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
     if (ws.pruning) {
-        p.centroids = ix->centroids.ptr;
-        p.list_radius = ix->list_radius.ptr;
+        p.ball_centre = ix->ball_centre.ptr;
+        p.ball_radius = ix->ball_radius.ptr;
     }
     p.scanned = reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 3);
     {
@@ -1484,9 +1584,16 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
                   new_codes.ptr, n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_norm.ptr);
     }
     if (ix->quant == VB200_QUANT_SQ8) {
-        VB_TRY(ix->list_radius.reserve(nlist));
-        VB_LAUNCH(sq8_list_radius_kernel, (nlist * 32 + 127) / 128, 128, 0, new_codes.ptr, stride, dim,
-                  new_off_dev.ptr, nlist, ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->list_radius.ptr);
+        VB_TRY(ix->ball_centre.reserve(static_cast<size_t>(nlist) * SQ8_BALLS * dim));
+        VB_TRY(ix->ball_radius.reserve(static_cast<size_t>(nlist) * SQ8_BALLS));
+        const size_t balls_smem = 2 * static_cast<size_t>(SQ8_BALLS) * dim * sizeof(float);
+        VB_CHECK_ARG(balls_smem <= 200 * 1024, "dim too large for the list-ball kernel");
+        if (balls_smem > 48 * 1024) {
+            VB_CUDA(cudaFuncSetAttribute(sq8_list_balls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(balls_smem)));
+        }
+        VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr,
+                  ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr);
     }
     VB_TRY(sync_stream());
     // 7. commit

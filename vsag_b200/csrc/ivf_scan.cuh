@@ -24,6 +24,8 @@ namespace vb200 {
 constexpr int SCAN_THREADS = 128;
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;
 
+constexpr int SQ8_BALLS = 3;   // covering balls per list for the SQ8 scan's pruning
+
 struct ScanParams {
     const uint8_t* codes;        // [positions x code_stride]
     uint32_t code_stride;        // bytes, multiple of 16
@@ -54,11 +56,12 @@ struct ScanParams {
     float coef_c;
     float inv_sqrt_d;            // RaBitQ
     int metric;
-    // SQ8 list pruning (both null = off): a list whose decoded rows all lie within list_radius[l]
-    // of centroids[l] cannot hold anything closer to q than the triangle inequality allows; when
-    // that is already worse than the query's bound the (query, list) pair is dropped unscanned.
-    const float* centroids;      // [nlist x dim]
-    const float* list_radius;    // [nlist] max |decoded row - centroid|, rounded up
+    // SQ8 list pruning (both null = off): every decoded row of list l lies in one of SQ8_BALLS
+    // balls (centre, radius); a query cannot have anything in the list closer than the triangle
+    // inequality allows for the nearest ball, and when that is already worse than the query's
+    // bound the (query, list) pair is dropped unscanned.
+    const float* ball_centre;    // [nlist][SQ8_BALLS][dim]
+    const float* ball_radius;    // [nlist][SQ8_BALLS], rounded up; -1 = empty ball
     unsigned long long* scanned; // bytes of codes actually scanned (pairs kept x list length x code size)
     // Id filter (filter_pos_inner null = none): a row is skipped when its inner id is tombstoned or
     // when bit (label & 0xFFFFFFFF) of the caller's bitset is set (BlackListFilter::CheckValid,
@@ -371,32 +374,44 @@ ivf_sq8_scan_kernel(const ScanParams p) {
         const uint32_t list = it.list;
         const uint32_t pbeg = it.pbeg;
         int nqt = static_cast<int>(it.nqt);
-        if (p.list_radius != nullptr) {
-            // Eight threads per query measure the query against the list's centroid; the pair
-            // survives unless even the nearest point of the list's ball is beyond the bound.
+        if (p.ball_radius != nullptr) {
+            // Eight threads per query measure the query against the list's balls; the pair
+            // survives unless even the nearest point of every ball is beyond the bound.
             static_assert(SCAN_THREADS == QT * 8, "eight threads per query of the tile");
             const int qi = threadIdx.x >> 3, part = threadIdx.x & 7;
-            float dot = 0.f, qq = 0.f;
+            float dot[SQ8_BALLS];
+            float qq = 0.f;
+#pragma unroll
+            for (int j = 0; j < SQ8_BALLS; ++j) {
+                dot[j] = 0.f;
+            }
             uint32_t q = 0;
             if (qi < nqt) {
                 q = it.pair_q[pbeg + qi];
                 const float* qv = p.queries + static_cast<uint64_t>(q) * p.dim;
-                const float* cv = p.centroids + static_cast<uint64_t>(list) * p.dim;
+                const float* cv = p.ball_centre + static_cast<uint64_t>(list) * SQ8_BALLS * p.dim;
                 for (uint32_t d = part; d < p.dim; d += 8) {
-                    const float x = __ldg(qv + d), c = __ldg(cv + d);
-                    if (p.metric == 0) {
-                        const float t = x - c;
-                        dot = fmaf(t, t, dot);
-                    } else {
-                        dot = fmaf(x, c, dot);
-                        qq = fmaf(x, x, qq);
+                    const float x = __ldg(qv + d);
+                    qq = fmaf(x, x, qq);
+#pragma unroll
+                    for (int j = 0; j < SQ8_BALLS; ++j) {
+                        const float c = __ldg(cv + j * p.dim + d);
+                        if (p.metric == 0) {
+                            const float t = x - c;
+                            dot[j] = fmaf(t, t, dot[j]);
+                        } else {
+                            dot[j] = fmaf(x, c, dot[j]);
+                        }
                     }
                 }
             }
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) {
-                dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 qq += __shfl_xor_sync(0xffffffffu, qq, o);
+#pragma unroll
+                for (int j = 0; j < SQ8_BALLS; ++j) {
+                    dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+                }
             }
             if (part == 0 && qi < QT) {
                 bool keep = qi < nqt;
@@ -404,17 +419,23 @@ ivf_sq8_scan_kernel(const ScanParams p) {
                     const uint32_t u = p.thr_g[q];
                     if (u <= float_to_ordered(INFINITY)) {   // the query has a bound already
                         const float bound = ordered_to_float(u);
-                        const float r = __ldg(p.list_radius + list);
                         // slack: the distances compared here and in the scan differ in rounding only
-                        float lower;
-                        if (p.metric == 0) {
-                            const float gap = sqrtf(dot) - r;
-                            lower = gap > 0.f ? gap * gap : 0.f;
-                            keep = !(lower > bound * 1.001f + 1e-4f * dot);
-                        } else {
-                            lower = 1.0f - dot - sqrtf(qq) * r;
-                            keep = !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
+                        bool any = false;
+#pragma unroll
+                        for (int j = 0; j < SQ8_BALLS; ++j) {
+                            const float r = __ldg(p.ball_radius + static_cast<uint64_t>(list) * SQ8_BALLS + j);
+                            if (r >= 0.f) {
+                                if (p.metric == 0) {
+                                    const float gap = sqrtf(dot[j]) - r;
+                                    const float lower = gap > 0.f ? gap * gap : 0.f;
+                                    any = any || !(lower > bound * 1.001f + 1e-4f * dot[j]);
+                                } else {
+                                    const float lower = 1.0f - dot[j] - sqrtf(qq) * r;
+                                    any = any || !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot[j]) + 1.0f));
+                                }
+                            }
                         }
+                        keep = any;
                     }
                 }
                 ts.cnt[qi] = keep ? 1u : 0u;   // borrowed as the keep flag until the tile is set up
