@@ -452,22 +452,56 @@ route_finalize_kernel(const float* __restrict__ queries, uint32_t dim,
                       int32_t* __restrict__ probes, float* __restrict__ probe_dists) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    float* qs = reinterpret_cast<float*>(keys + n2);   // the query, staged once for all candidates
     const float* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
     const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        qs[d] = q[d];
+    }
+    __syncthreads();
+    const bool vec4 = (dim & 3u) == 0;   // centroid rows are then 16-byte aligned
     for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
         uint64_t key = KEY_INF;
         if (i < ncand && cq[i] != KEY_INF) {
             uint32_t list = static_cast<uint32_t>(cq[i]);
             const float* c = centroids + static_cast<uint64_t>(list) * dim;
             float s = 0.f;
-            if (metric == VB200_METRIC_L2) {
+            // one chain per candidate, dimensions in ascending order, as the reference computes it
+            if (vec4) {
+                const float4* c4 = reinterpret_cast<const float4*>(c);
+                const float4* q4 = reinterpret_cast<const float4*>(qs);
+                if (metric == VB200_METRIC_L2) {
+#pragma unroll 4
+                    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                        const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                        float t = __fsub_rn(qv.x, cv.x);
+                        s = fmaf(t, t, s);
+                        t = __fsub_rn(qv.y, cv.y);
+                        s = fmaf(t, t, s);
+                        t = __fsub_rn(qv.z, cv.z);
+                        s = fmaf(t, t, s);
+                        t = __fsub_rn(qv.w, cv.w);
+                        s = fmaf(t, t, s);
+                    }
+                } else {
+#pragma unroll 4
+                    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                        const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                        s = fmaf(qv.x, cv.x, s);
+                        s = fmaf(qv.y, cv.y, s);
+                        s = fmaf(qv.z, cv.z, s);
+                        s = fmaf(qv.w, cv.w, s);
+                    }
+                    s = __fsub_rn(1.0f, s);
+                }
+            } else if (metric == VB200_METRIC_L2) {
                 for (uint32_t d = 0; d < dim; ++d) {
-                    float t = __fsub_rn(__ldg(q + d), __ldg(c + d));
+                    float t = __fsub_rn(qs[d], __ldg(c + d));
                     s = fmaf(t, t, s);
                 }
             } else {
                 for (uint32_t d = 0; d < dim; ++d) {
-                    s = fmaf(__ldg(q + d), __ldg(c + d), s);
+                    s = fmaf(qs[d], __ldg(c + d), s);
                 }
                 s = __fsub_rn(1.0f, s);
             }
@@ -846,7 +880,7 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
         }
     }
     uint32_t n2 = next_pow2(ncand < 2 ? 2 : ncand);
-    VB_LAUNCH(route_finalize_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev,
+    VB_LAUNCH(route_finalize_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t) + ix->dim * sizeof(float), q_dev,
               ix->dim, ix->centroids.ptr, ws.cand.ptr, ncand, n2, nprobe, ix->metric, probes_dev,
               dists_dev);
     return 0;
