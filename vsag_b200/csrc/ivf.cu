@@ -51,6 +51,7 @@ struct SearchWorkspace {
     DevBuf<uint32_t> pair_ctr;     // pair counts and scatter cursors of both phases: 4 x [nlist]
     DevBuf<uint32_t> pair_off[2];  // [nlist + 1]
     DevBuf<uint32_t> item_off[2];  // [nlist + 1]
+    DevBuf<uint64_t> item_map[2];  // [pairs of the phase]: list | tile << 32 per work item
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
     DevBuf<float> q_unit;         // cosine: the queries divided by their norms
@@ -588,6 +589,7 @@ struct PairTables {
     uint32_t* cursor[2];    // [nlist] scatter cursors
     uint32_t* off[2];       // [nlist + 1] first pair of each list
     uint32_t* item_off[2];  // [nlist + 1] tile prefix by position in the scan order
+    uint64_t* item_map[2];  // [items] list | tile << 32 of every work item
     uint32_t* q[2];         // [pairs] query
     uint32_t* slot[2];      // [pairs] output slot
 };
@@ -618,6 +620,7 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
     const uint32_t* __restrict__ pair_cnt = blockIdx.x == 0 ? tables.cnt[0] : tables.cnt[1];
     uint32_t* __restrict__ pair_off = blockIdx.x == 0 ? tables.off[0] : tables.off[1];
     uint32_t* __restrict__ item_off = blockIdx.x == 0 ? tables.item_off[0] : tables.item_off[1];
+    uint64_t* __restrict__ item_map = blockIdx.x == 0 ? tables.item_map[0] : tables.item_map[1];
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
@@ -653,7 +656,11 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
         }
         if (pos < nlist) {
             pair_off[l] = base_pairs + s_pairs[threadIdx.x] - c;
-            item_off[pos] = base_items + s_items[threadIdx.x] - t;
+            const uint32_t first_item = base_items + s_items[threadIdx.x] - t;
+            item_off[pos] = first_item;
+            for (uint32_t j = 0; j < t; ++j) {   // the scan's work queue reads its items from here
+                item_map[first_item + j] = static_cast<uint64_t>(l) | (static_cast<uint64_t>(j) << 32);
+            }
         }
         __syncthreads();
         if (threadIdx.x == 1023) {
@@ -957,6 +964,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         const uint64_t cap_pairs = ph == 0 ? nq : total;
         VB_TRY(ws.pair_off[ph].reserve(nlist + 1));
         VB_TRY(ws.item_off[ph].reserve(nlist + 1));
+        VB_TRY(ws.item_map[ph].reserve(cap_pairs));
         VB_TRY(ws.pair_q[ph].reserve(cap_pairs));
         VB_TRY(ws.pair_slot[ph].reserve(cap_pairs));
     }
@@ -985,6 +993,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         tables.cursor[ph] = ws.pair_ctr.ptr + static_cast<size_t>(2 + ph) * nlist;
         tables.off[ph] = ws.pair_off[ph].ptr;
         tables.item_off[ph] = ws.item_off[ph].ptr;
+        tables.item_map[ph] = ws.item_map[ph].ptr;
         tables.q[ph] = ws.pair_q[ph].ptr;
         tables.slot[ph] = ws.pair_slot[ph].ptr;
     }
@@ -1064,6 +1073,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             p.pair_q[i] = ws.pair_q[src].ptr;
             p.pair_slot[i] = ws.pair_slot[src].ptr;
             p.item_off[i] = ws.item_off[src].ptr;
+            p.item_map[i] = ws.item_map[src].ptr;
         }
         p.n_phases = count;
         p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + queue_slot);

@@ -41,6 +41,7 @@ struct ScanParams {
     const uint32_t* pair_q[2];     // [pairs] query index
     const uint32_t* pair_slot[2];  // [pairs] output slot (query * nprobe + probe rank)
     const uint32_t* item_off[2];   // [nlist + 1] exclusive prefix of tiles, by position in `order`
+    const uint64_t* item_map[2];   // [items] list | tile << 32 of every work item, in queue order
     uint32_t n_phases;
     uint32_t nlist;
     uint32_t* item_counter;      // work queue head
@@ -223,19 +224,9 @@ scan_next_item(const ScanParams& p, uint32_t* s_item, ScanItem& it) {
     if (second) {
         item -= n0;
     }
-    const uint32_t* item_off = second ? p.item_off[1] : p.item_off[0];
-    // Largest position with item_off[pos] <= item.
-    uint32_t lo = 0, hi = p.nlist;
-    while (hi - lo > 1) {
-        uint32_t mid = (lo + hi) >> 1;
-        if (item_off[mid] <= item) {
-            lo = mid;
-        } else {
-            hi = mid;
-        }
-    }
-    const uint32_t list = p.order[lo];
-    const uint32_t tile = item - item_off[lo];
+    const uint64_t entry = __ldg((second ? p.item_map[1] : p.item_map[0]) + item);
+    const uint32_t list = static_cast<uint32_t>(entry);
+    const uint32_t tile = static_cast<uint32_t>(entry >> 32);
     const uint32_t first = (second ? p.pair_off[1] : p.pair_off[0])[list];
     const uint32_t count = (second ? p.pair_cnt[1] : p.pair_cnt[0])[list];
     it.list = list;
