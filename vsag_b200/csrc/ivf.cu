@@ -569,7 +569,7 @@ tombstone_kernel(const int64_t* __restrict__ labels, uint64_t n_total, const int
 // empty (nprobe when there is none): the list whose scan gives the query its first bound.
 __global__ void
 first_live_kernel(const int32_t* __restrict__ probes, uint64_t nq, uint32_t nprobe, uint32_t nlist,
-                  uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off,
+                  uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off, int nearest_only,
                   uint32_t* __restrict__ first_live) {
     uint64_t q = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (q >= nq) {
@@ -579,7 +579,10 @@ first_live_kernel(const int32_t* __restrict__ probes, uint64_t nq, uint32_t npro
     while (pr < nprobe && !probe_is_live(probes[q * nprobe + pr], nlist, rank, world, list_off)) {
         ++pr;
     }
-    first_live[q] = pr;
+    // nearest_only (shards that exchange their bounds): only the shard that holds a query's
+    // nearest list scans for it before the exchange; the others get its bound, so the first phase
+    // shrinks with the number of shards instead of costing every shard one list per query.
+    first_live[q] = (nearest_only && pr != 0) ? nprobe : pr;
 }
 
 // Grouping tables of the two phases: phase 0 takes every query's first live probe, phase 1 the
@@ -984,7 +987,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
     VB_TRY(ws.first_live.reserve(nq));
     VB_LAUNCH(first_live_kernel, static_cast<uint32_t>((nq + 255) / 256), 256, 0, probes_dev, nq, nprobe, nlist,
-              ix->shard_rank, ix->shard_world, ix->list_off.ptr, ws.first_live.ptr);
+              ix->shard_rank, ix->shard_world, ix->list_off.ptr,
+              (ws.exchange != nullptr && ix->shard_world > 1) ? 1 : 0, ws.first_live.ptr);
     VB_TRY(ws.pair_ctr.reserve(4 * static_cast<size_t>(nlist)));
     VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
     PairTables tables{};
