@@ -48,10 +48,11 @@ TRAIN_ROWS = 64 * NLIST          # the reference's default train_sample_count: m
 KMEANS_ITERS = 25                # hard-coded in IVFNearestPartition::Train
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel's launch, from the ncu capture of
-# the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 284.5 MB + 26.1 MB), scaled
+# the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 111.0 MB + 3.8 MB), scaled
 # by 5 to the 10,000,000-row workload: the traffic is one pass over the codes of the lists that
-# survive pruning plus the partial-result slots, both proportional to the row count.
-SCAN_TRAFFIC_BYTES = 5 * (284.5e6 + 26.1e6)
+# survive pruning plus the partial-result slots; the scaled-down case keeps the rows per mixture
+# component and per list, so both grow with the row count.
+SCAN_TRAFFIC_BYTES = 5 * (111.0e6 + 3.8e6)
 
 
 def env_int(name: str, default: int) -> int:
@@ -141,16 +142,17 @@ def make_data(device, n_base: int, n_query: int):
 
     g = torch.Generator(device=device)
     g.manual_seed(2)
-    centres = torch.rand((N_CENTRES, DIM), generator=g, device=device) * 2.0 - 1.0
+    n_centres = max(16, scaled(N_CENTRES))   # a scaled-down dry run keeps rows per mixture component
+    centres = torch.rand((n_centres, DIM), generator=g, device=device) * 2.0 - 1.0
     base = torch.empty((n_base, DIM), dtype=torch.float32, device=device)
     step = 1_000_000
     for b in range(0, n_base, step):
         e = min(n_base, b + step)
-        which = torch.randint(0, N_CENTRES, (e - b,), generator=g, device=device)
+        which = torch.randint(0, n_centres, (e - b,), generator=g, device=device)
         base[b:e] = centres[which] + SIGMA * torch.randn((e - b, DIM), generator=g, device=device)
     gq = torch.Generator(device=device)
     gq.manual_seed(3)
-    which = torch.randint(0, N_CENTRES, (n_query,), generator=gq, device=device)
+    which = torch.randint(0, n_centres, (n_query,), generator=gq, device=device)
     queries = centres[which] + SIGMA * torch.randn((n_query, DIM), generator=gq, device=device)
     return base, queries.contiguous()
 
