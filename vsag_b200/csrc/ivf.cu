@@ -54,6 +54,7 @@ struct SearchWorkspace {
     DevBuf<uint64_t> item_map[2];  // [pairs of the phase]: list | tile << 32 per work item
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
+    DevBuf<uint8_t> pair_drop;    // [nq x nprobe] second-phase pairs pruned before grouping
     DevBuf<float> q_unit;         // cosine: the queries divided by their norms
     const vb200_filter* filter = nullptr;   // set for the duration of one filtered search
     DevBuf<uint32_t> deny_bits;   // tombstones | the caller's deny_inner_bits
@@ -600,16 +601,112 @@ struct PairTables {
 __global__ void
 pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
                   const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
-                  const uint32_t* __restrict__ list_off, PairTables t) {
+                  const uint32_t* __restrict__ list_off, PairTables t, uint32_t phase_sel,
+                  const uint8_t* __restrict__ drop) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
         return;
     }
     const uint32_t pr = static_cast<uint32_t>(e % nprobe);
     const uint32_t ph = pr == first_live[e / nprobe] ? 0u : 1u;
+    if ((phase_sel < 2 && ph != phase_sel) || (drop != nullptr && drop[e] != 0)) {
+        return;   // phase_sel 0 / 1: group that phase only; dropped pairs were pruned beforehand
+    }
     int32_t l = probes[e];
     if (probe_is_live(l, nlist, rank, world, list_off)) {
         atomicAdd((ph == 0 ? t.cnt[0] : t.cnt[1]) + l, 1u);
+    }
+}
+
+// After the first phase: drop[e] = 1 for every second-phase (query, list) pair that the list's
+// covering balls put beyond the query's bound (the test the scan kernel makes per tile, made here
+// once per pair so that pruned pairs never become work items).  Eight threads per pair.  The code
+// bytes of the dropped pairs still count as algorithmic scan volume (scalars[0]).
+__global__ void __launch_bounds__(256)
+pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
+                 const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
+                 const uint32_t* __restrict__ list_off, const float* __restrict__ queries, uint32_t dim,
+                 const float* __restrict__ ball_centre, const float* __restrict__ ball_radius,
+                 const uint32_t* __restrict__ thr, int metric, uint32_t code_size, uint8_t* __restrict__ drop,
+                 unsigned long long* __restrict__ scalars) {
+    __shared__ unsigned long long s_bytes;
+    if (threadIdx.x == 0) {
+        s_bytes = 0;
+    }
+    __syncthreads();
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * 32 + (threadIdx.x >> 3);
+    const uint32_t part = threadIdx.x & 7;
+    bool candidate = false;
+    uint32_t q = 0;
+    int32_t l = -1;
+    if (e < total) {
+        q = static_cast<uint32_t>(e / nprobe);
+        const uint32_t pr = static_cast<uint32_t>(e % nprobe);
+        l = probes[e];
+        candidate = pr != first_live[q] && probe_is_live(l, nlist, rank, world, list_off) &&
+                    thr[q] <= float_to_ordered(INFINITY);
+    }
+    float dot[SQ8_BALLS];
+    float qq = 0.f;
+#pragma unroll
+    for (int j = 0; j < SQ8_BALLS; ++j) {
+        dot[j] = 0.f;
+    }
+    if (candidate) {
+        const float* qv = queries + static_cast<uint64_t>(q) * dim;
+        const float* cv = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
+        for (uint32_t d = part; d < dim; d += 8) {
+            const float x = __ldg(qv + d);
+            qq = fmaf(x, x, qq);
+#pragma unroll
+            for (int j = 0; j < SQ8_BALLS; ++j) {
+                const float c = __ldg(cv + j * dim + d);
+                if (metric == 0) {
+                    const float t = x - c;
+                    dot[j] = fmaf(t, t, dot[j]);
+                } else {
+                    dot[j] = fmaf(x, c, dot[j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        qq += __shfl_xor_sync(0xffffffffu, qq, o);
+#pragma unroll
+        for (int j = 0; j < SQ8_BALLS; ++j) {
+            dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+        }
+    }
+    if (part == 0 && e < total) {
+        bool dropped = false;
+        if (candidate) {
+            const float bound = ordered_to_float(thr[q]);
+            bool any = false;
+#pragma unroll
+            for (int j = 0; j < SQ8_BALLS; ++j) {
+                const float r = __ldg(ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS + j);
+                if (r >= 0.f) {
+                    if (metric == 0) {
+                        const float gap = sqrtf(dot[j]) - r;
+                        const float lower = gap > 0.f ? gap * gap : 0.f;
+                        any = any || !(lower > bound * 1.001f + 1e-4f * dot[j]);
+                    } else {
+                        const float lower = 1.0f - dot[j] - sqrtf(qq) * r;
+                        any = any || !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot[j]) + 1.0f));
+                    }
+                }
+            }
+            dropped = !any;
+        }
+        drop[e] = dropped ? 1 : 0;
+        if (dropped) {
+            atomicAdd(&s_bytes, static_cast<unsigned long long>(list_off[l + 1] - list_off[l]) * code_size);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && s_bytes != 0) {
+        atomicAdd(scalars, s_bytes);
     }
 }
 
@@ -684,13 +781,17 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
 __global__ void
 pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
                     const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
-                    const uint32_t* __restrict__ list_off, PairTables t) {
+                    const uint32_t* __restrict__ list_off, PairTables t, uint32_t phase_sel,
+                    const uint8_t* __restrict__ drop) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e >= total) {
         return;
     }
     const uint32_t pr = static_cast<uint32_t>(e % nprobe);
     const bool first = pr == first_live[e / nprobe];
+    if ((phase_sel < 2 && (first ? 0u : 1u) != phase_sel) || (drop != nullptr && drop[e] != 0)) {
+        return;
+    }
     int32_t l = probes[e];
     if (probe_is_live(l, nlist, rank, world, list_off)) {
         uint32_t s = (first ? t.off[0] : t.off[1])[l] + atomicAdd((first ? t.cursor[0] : t.cursor[1]) + l, 1u);
@@ -990,7 +1091,6 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
               ix->shard_rank, ix->shard_world, ix->list_off.ptr,
               (ws.exchange != nullptr && ix->shard_world > 1) ? 1 : 0, ws.first_live.ptr);
     VB_TRY(ws.pair_ctr.reserve(4 * static_cast<size_t>(nlist)));
-    VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
     PairTables tables{};
     for (uint32_t ph = 0; ph < 2; ++ph) {
         tables.cnt[ph] = ws.pair_ctr.ptr + static_cast<size_t>(ph) * nlist;
@@ -1001,12 +1101,26 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         tables.q[ph] = ws.pair_q[ph].ptr;
         tables.slot[ph] = ws.pair_slot[ph].ptr;
     }
-    VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
-              ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables);
-    VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->scan_order.ptr, nlist,
-              static_cast<uint32_t>(qt), ix->code_size, ws.scalars.ptr);
-    VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
-              ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables);
+    // Groups the pairs of one phase (0 / 1) or of both (2) by list; `drop` marks pruned pairs.
+    auto group_pairs = [&](uint32_t phase_sel, const uint8_t* drop) -> int {
+        VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
+        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
+                  ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
+        VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->scan_order.ptr, nlist,
+                  static_cast<uint32_t>(qt), ix->code_size, ws.scalars.ptr);
+        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
+                  ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
+        return 0;
+    };
+    // SQ8 with list pruning: the first phase runs alone, then the pairs its bounds rule out are
+    // dropped before the second phase is grouped, so they never become work items.
+    static const bool preprune_enabled = []() {
+        const char* v = std::getenv("VB200_PAIR_PREPRUNE");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    const bool pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
+    const bool split_phases = n_phases == 2 && (ws.exchange != nullptr || (pruning && preprune_enabled));
+    VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr));
 
     ScanParams p{};
     p.codes = ix->codes.ptr;
@@ -1093,21 +1207,33 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         return launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem);
     };
     p.order = ix->scan_order.ptr;
-    if (ws.exchange != nullptr && n_phases == 2) {
-        // Sharded search: after every shard has scanned each query's nearest list it holds, the
-        // shards agree on the tightest bound any of them found, so the remaining lists are
-        // pruned as sharply as on one GPU.  The exchange itself (an all-reduce with MIN over
-        // bounds[nq]) belongs to the caller, who owns the communicator; it must be ordered with
-        // the stream it is handed.
+    if (split_phases) {
         VB_TRY(launch_phases(0, 1, 1));
-        VB_TRY(ws.bounds.reserve(nq));
-        const uint32_t qblocks = static_cast<uint32_t>((nq + 255) / 256);
-        VB_LAUNCH(bounds_to_float_kernel, qblocks, 256, 0, ws.thr.ptr, nq, ws.bounds.ptr);
-        const int rc = ws.exchange(ws.bounds.ptr, nq, static_cast<void*>(st), ws.exchange_arg);
-        if (rc != 0) {
-            VB_FAIL(VB200_INTERNAL_ERROR, "the bound exchange callback failed with status %d", rc);
+        if (ws.exchange != nullptr) {
+            // Sharded search: after the owner of each query's nearest list has scanned it, the
+            // shards agree on the tightest bound any of them found, so the remaining lists are
+            // pruned as sharply as on one GPU.  The exchange itself (an all-reduce with MIN over
+            // bounds[nq]) belongs to the caller, who owns the communicator; it must be ordered
+            // with the stream it is handed.
+            VB_TRY(ws.bounds.reserve(nq));
+            const uint32_t qblocks = static_cast<uint32_t>((nq + 255) / 256);
+            VB_LAUNCH(bounds_to_float_kernel, qblocks, 256, 0, ws.thr.ptr, nq, ws.bounds.ptr);
+            const int rc = ws.exchange(ws.bounds.ptr, nq, static_cast<void*>(st), ws.exchange_arg);
+            if (rc != 0) {
+                VB_FAIL(VB200_INTERNAL_ERROR, "the bound exchange callback failed with status %d", rc);
+            }
+            VB_LAUNCH(bounds_from_float_kernel, qblocks, 256, 0, ws.bounds.ptr, nq, ws.thr.ptr);
         }
-        VB_LAUNCH(bounds_from_float_kernel, qblocks, 256, 0, ws.bounds.ptr, nq, ws.thr.ptr);
+        const uint8_t* drop = nullptr;
+        if (pruning) {
+            VB_TRY(ws.pair_drop.reserve(total));
+            VB_LAUNCH(pair_drop_kernel, static_cast<uint32_t>((total + 31) / 32), 256, 0, probes_dev, total, nprobe,
+                      ws.first_live.ptr, nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, q_dev, ix->dim,
+                      ix->ball_centre.ptr, ix->ball_radius.ptr, ws.thr.ptr, ix->metric, ix->code_size,
+                      ws.pair_drop.ptr, reinterpret_cast<unsigned long long*>(ws.scalars.ptr));
+            drop = ws.pair_drop.ptr;
+        }
+        VB_TRY(group_pairs(1u, drop));
         VB_TRY(launch_phases(1, 1, 2));
     } else {
         VB_TRY(launch_phases(0, n_phases, 1));
