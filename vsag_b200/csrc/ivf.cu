@@ -724,56 +724,55 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
-    __shared__ uint32_t base_pairs, base_items;
     if (threadIdx.x == 0) {
         s_bytes = 0;
-        base_pairs = 0;
-        base_items = 0;
     }
-    __syncthreads();
+    // every thread owns a run of consecutive positions: sums of the run, one block scan, then the
+    // run is walked again from its exclusive prefix
+    const uint32_t per = (nlist + 1023) / 1024;
+    const uint32_t p0 = threadIdx.x * per;
+    const uint32_t p1 = p0 + per < nlist ? p0 + per : nlist;
+    uint32_t sum_p = 0, sum_t = 0;
     unsigned long long my_bytes = 0;
-    for (uint32_t b = 0; b < nlist; b += 1024) {
-        const uint32_t pos = b + threadIdx.x;
-        const uint32_t l = pos < nlist ? order[pos] : 0;
-        uint32_t c = pos < nlist ? pair_cnt[l] : 0;
-        uint32_t t = (c + qt - 1) / qt;
-        if (pos < nlist) {
-            my_bytes += static_cast<unsigned long long>(c) * (list_off[l + 1] - list_off[l]) * code_size;
-        }
-        s_pairs[threadIdx.x] = c;
-        s_items[threadIdx.x] = t;
-        __syncthreads();
-        for (uint32_t off = 1; off < 1024; off <<= 1) {  // Hillis-Steele inclusive scan
-            uint32_t vp = 0, vi = 0;
-            if (threadIdx.x >= off) {
-                vp = s_pairs[threadIdx.x - off];
-                vi = s_items[threadIdx.x - off];
-            }
-            __syncthreads();
-            s_pairs[threadIdx.x] += vp;
-            s_items[threadIdx.x] += vi;
-            __syncthreads();
-        }
-        if (pos < nlist) {
-            pair_off[l] = base_pairs + s_pairs[threadIdx.x] - c;
-            const uint32_t first_item = base_items + s_items[threadIdx.x] - t;
-            item_off[pos] = first_item;
-            for (uint32_t j = 0; j < t; ++j) {   // the scan's work queue reads its items from here
-                item_map[first_item + j] = static_cast<uint64_t>(l) | (static_cast<uint64_t>(j) << 32);
-            }
+    for (uint32_t pos = p0; pos < p1; ++pos) {
+        const uint32_t l = order[pos];
+        const uint32_t c = pair_cnt[l];
+        sum_p += c;
+        sum_t += (c + qt - 1) / qt;
+        my_bytes += static_cast<unsigned long long>(c) * (list_off[l + 1] - list_off[l]) * code_size;
+    }
+    s_pairs[threadIdx.x] = sum_p;
+    s_items[threadIdx.x] = sum_t;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024; off <<= 1) {  // Hillis-Steele inclusive scan
+        uint32_t vp = 0, vi = 0;
+        if (threadIdx.x >= off) {
+            vp = s_pairs[threadIdx.x - off];
+            vi = s_items[threadIdx.x - off];
         }
         __syncthreads();
-        if (threadIdx.x == 1023) {
-            base_pairs += s_pairs[1023];
-            base_items += s_items[1023];
-        }
+        s_pairs[threadIdx.x] += vp;
+        s_items[threadIdx.x] += vi;
         __syncthreads();
+    }
+    uint32_t run_p = s_pairs[threadIdx.x] - sum_p, run_t = s_items[threadIdx.x] - sum_t;
+    for (uint32_t pos = p0; pos < p1; ++pos) {
+        const uint32_t l = order[pos];
+        const uint32_t c = pair_cnt[l];
+        const uint32_t t = (c + qt - 1) / qt;
+        pair_off[l] = run_p;
+        item_off[pos] = run_t;
+        for (uint32_t j = 0; j < t; ++j) {   // the scan's work queue reads its items from here
+            item_map[run_t + j] = static_cast<uint64_t>(l) | (static_cast<uint64_t>(j) << 32);
+        }
+        run_p += c;
+        run_t += t;
     }
     atomicAdd(&s_bytes, my_bytes);
     __syncthreads();
     if (threadIdx.x == 0) {
-        pair_off[nlist] = base_pairs;
-        item_off[nlist] = base_items;
+        pair_off[nlist] = s_pairs[1023];
+        item_off[nlist] = s_items[1023];
         atomicAdd(reinterpret_cast<unsigned long long*>(scalars), s_bytes);  // logical scan volume, both phases
     }
 }
