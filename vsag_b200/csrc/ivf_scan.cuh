@@ -285,10 +285,11 @@ template <int QT, int NR, int NG>
 __device__ __forceinline__ void
 sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_s, uint32_t dpad,
               float (&acc)[SQ8_ROWS][QT]) {
+    constexpr int NQ = NG == 0 ? 1 : NG * 4;   // NG = 0: a tile with a single query (most tiles, once pairs are pruned)
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
 #pragma unroll
-        for (int qi = 0; qi < NG * 4; ++qi) {
+        for (int qi = 0; qi < NQ; ++qi) {
             acc[r][qi] = 0.f;
         }
     }
@@ -321,7 +322,7 @@ sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_
             }
         }
 #pragma unroll
-        for (int qi = 0; qi < NG * 4; ++qi) {
+        for (int qi = 0; qi < NQ; ++qi) {
             float4 wv = wrow[qi];
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
@@ -340,6 +341,7 @@ sq8_tile_dots_ng(int ng, const uint8_t* const (&cp)[SQ8_ROWS], const float* __re
                  uint32_t dpad, float (&acc)[SQ8_ROWS][QT]) {
     static_assert(QT == 16, "query-group dispatch is written for 16-query tiles");
     switch (ng) {
+        case 0: sq8_tile_dots<QT, NR, 0>(cp, w_s, dpad, acc); break;
         case 1: sq8_tile_dots<QT, NR, 1>(cp, w_s, dpad, acc); break;
         case 2: sq8_tile_dots<QT, NR, 2>(cp, w_s, dpad, acc); break;
         case 3: sq8_tile_dots<QT, NR, 3>(cp, w_s, dpad, acc); break;
@@ -483,14 +485,15 @@ ivf_sq8_scan_kernel(const ScanParams p) {
             }
             ts.cnt[qi] = 0;
         }
-        const int ng = (nqt + 3) >> 2;
+        const int ng = nqt == 1 ? 0 : (nqt + 3) >> 2;   // 0: the single-query body
+        const uint32_t slots = nqt == 1 ? 1u : static_cast<uint32_t>(ng) * 4;
         __syncthreads();
         // weights of the tile's queries as [dpad/4][QT] float4 (zeros for the unused slots of the
         // last group of four)
         {
             const uint32_t d4n = dpad >> 2;
             float4* w4s = reinterpret_cast<float4*>(w_s);
-            for (uint32_t i = threadIdx.x; i < static_cast<uint32_t>(ng) * 4 * d4n; i += SCAN_THREADS) {
+            for (uint32_t i = threadIdx.x; i < slots * d4n; i += SCAN_THREADS) {
                 uint32_t qi = i / d4n, d4 = i % d4n;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (static_cast<int>(qi) < nqt) {
