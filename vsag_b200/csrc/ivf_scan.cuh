@@ -335,13 +335,60 @@ sq8_tile_dots(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_
     }
 }
 
+// A tile with one query: the per-trip work is so small that fetching the codes one 32-bit word
+// ahead leaves every trip waiting for its load.  Here the codes come 16 bytes at a time, one chunk
+// ahead, so a row of 96 dimensions costs six dependent loads instead of twenty-four.
+template <int QT, int NR>
+__device__ __forceinline__ void
+sq8_tile_dots_single(const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_s, uint32_t dpad,
+                     float (&acc)[SQ8_ROWS][QT]) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        acc[r][0] = 0.f;
+    }
+    uint4 nxt[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        nxt[r] = __ldg(reinterpret_cast<const uint4*>(cp[r]));
+    }
+    const float4* wrow = reinterpret_cast<const float4*>(w_s);   // [dpad/4][QT]: slot 0 is the query
+#pragma unroll 1
+    for (uint32_t c = 0; c < dpad; c += 16, wrow += 4 * QT) {
+        uint4 cur[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            cur[r] = nxt[r];
+        }
+        if (c + 16 < dpad) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                nxt[r] = __ldg(reinterpret_cast<const uint4*>(cp[r] + c + 16));
+            }
+        }
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float4 wv = wrow[w * QT];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t raw = w == 0 ? cur[r].x : (w == 1 ? cur[r].y : (w == 2 ? cur[r].z : cur[r].w));
+                float a = acc[r][0];
+                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7540)) - 8388736.0f, wv.x, a);
+                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7541)) - 8388736.0f, wv.y, a);
+                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7542)) - 8388736.0f, wv.z, a);
+                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7543)) - 8388736.0f, wv.w, a);
+                acc[r][0] = a;
+            }
+        }
+    }
+}
+
 template <int QT, int NR>
 __device__ __forceinline__ void
 sq8_tile_dots_ng(int ng, const uint8_t* const (&cp)[SQ8_ROWS], const float* __restrict__ w_s,
                  uint32_t dpad, float (&acc)[SQ8_ROWS][QT]) {
     static_assert(QT == 16, "query-group dispatch is written for 16-query tiles");
     switch (ng) {
-        case 0: sq8_tile_dots<QT, NR, 0>(cp, w_s, dpad, acc); break;
+        case 0: sq8_tile_dots_single<QT, NR>(cp, w_s, dpad, acc); break;
         case 1: sq8_tile_dots<QT, NR, 1>(cp, w_s, dpad, acc); break;
         case 2: sq8_tile_dots<QT, NR, 2>(cp, w_s, dpad, acc); break;
         case 3: sq8_tile_dots<QT, NR, 3>(cp, w_s, dpad, acc); break;
