@@ -96,7 +96,7 @@ def test_ivf_remove_and_filters(engine, oracle, quant):
 
 
 @pytest.mark.parametrize("metric,quant,n,nq", [(0, "fp32", 6000, 100), (1, "fp32", 6000, 100),
-                                                (1, "bf16", 120_000, 1000), (0, "fp32", 100_000, 1000)])
+                                                (1, "bf16", 120_000, 4000), (0, "fp32", 100_000, 4000)])
 def test_bruteforce_remove_and_filters(engine, oracle, metric, quant, n, nq):
     """Small cases take the SIMT path, the large ones the tensor-core path; filtered rows get an
     infinite score bias and can never be nominated."""

@@ -434,7 +434,7 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
     }
     // Large problems nominate candidates on the tensor cores; the exact re-scoring below is the
     // same either way.
-    if (tensor_cores_enabled() && kcand <= tc_max_candidates(bf16 ? 1 : 3) && static_cast<double>(nq) * n * dim >= 1e10) {
+    if (tensor_cores_enabled() && kcand <= tc_max_candidates(bf16 ? 1 : 3) && static_cast<double>(nq) * n * dim >= 2e10) {
         const uint32_t chunks = (dim + TC_KC - 1) / TC_KC;
         if (!ix->tiled_valid) {
             const size_t elems = tc_tiled_elems(n, dim);
