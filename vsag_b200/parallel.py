@@ -60,9 +60,15 @@ def make_bounds_exchange(dist, device, group=None, seen=None):
 
     from . import _capi
 
+    views = {}   # (pointer, length) -> tensor over the library's bounds buffer, which is stable between steps
+
     def exchange(ptr, nq, _stream, _arg):
         try:
-            bounds = torch.as_tensor(_DevicePointer(ptr, nq), device=device)
+            bounds = views.get((ptr, nq))
+            if bounds is None:
+                bounds = torch.as_tensor(_DevicePointer(ptr, nq), device=device)
+                views.clear()
+                views[(ptr, nq)] = bounds
             dist.all_reduce(bounds, op=dist.ReduceOp.MIN, group=group)
             if seen is not None:
                 seen.append(int(nq))
