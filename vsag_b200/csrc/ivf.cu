@@ -106,6 +106,7 @@ struct vb200_ivf {
     uint64_t n_removed = 0;
     DevBuf<float> ball_centre;    // SQ8 list pruning: [nlist][SQ8_BALLS][dim] centres of the covering balls
     DevBuf<float> ball_radius;    // [nlist][SQ8_BALLS] their radii (-1: empty)
+    DevBuf<uint32_t> ball_count;  // [nlist] balls in use per list
     bool prune_lists = true;
     int64_t last_scanned_bytes = 0;
     // tensor-core routing: the centroids as tiled bf16 hi/lo terms (rebuilt when they change)
@@ -303,7 +304,8 @@ __global__ void __launch_bounds__(128)
 sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, uint32_t dim,
                       const uint32_t* __restrict__ list_off, const float* __restrict__ lower,
                       const float* __restrict__ diff, const float* __restrict__ centroids,
-                      float* __restrict__ ball_centre, float* __restrict__ ball_radius) {
+                      float* __restrict__ ball_centre, float* __restrict__ ball_radius,
+                      uint32_t* __restrict__ ball_count) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* seeds = reinterpret_cast<float*>(smem_raw);              // [SQ8_BALLS][dim]
     float* sums = seeds + SQ8_BALLS * dim;                          // [SQ8_BALLS][dim]
@@ -314,6 +316,13 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
     const uint32_t beg = list_off[l], len = list_off[l + 1] - beg;
     float* out_c = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
     float* out_r = ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS;
+    // three balls for an ordinary list, one more per 300 rows beyond 900, eight at most: the long
+    // lists are the ones that hold several clusters of the data and that many queries probe
+    int n_balls = static_cast<int>((len + 299) / 300);
+    n_balls = n_balls < 3 ? 3 : (n_balls > SQ8_BALLS ? SQ8_BALLS : n_balls);
+    if (tid == 0) {
+        ball_count[l] = len == 0 ? 0u : static_cast<uint32_t>(n_balls);
+    }
     if (len == 0) {
         for (uint32_t i = tid; i < SQ8_BALLS * dim; i += blockDim.x) {
             out_c[i] = 0.f;
@@ -335,7 +344,7 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
     for (uint32_t d = tid; d < dim; d += blockDim.x) {
         sums[d] = centroids[static_cast<uint64_t>(l) * dim + d];
     }
-    for (int j = 0; j < SQ8_BALLS; ++j) {
+    for (int j = 0; j < n_balls; ++j) {
         if (tid == 0) {
             best = 0ull;
         }
@@ -360,6 +369,10 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
         decode_to(pick < len ? pick : 0, seeds + j * dim);
         __syncthreads();
     }
+    for (uint32_t i = n_balls * dim + tid; i < SQ8_BALLS * dim; i += blockDim.x) {
+        seeds[i] = 0.f;
+    }
+    __syncthreads();
     // two Lloyd steps, then the radii
     for (int it = 0; it < 3; ++it) {
         const bool last = it == 2;
@@ -374,7 +387,7 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
         for (uint32_t r = tid; r < len; r += blockDim.x) {
             int arg = 0;
             float dbest = INFINITY;
-            for (int t = 0; t < SQ8_BALLS; ++t) {
+            for (int t = 0; t < n_balls; ++t) {
                 const float dd = sq8_row_dist(row_ptr(r), dim, lower, diff, seeds + t * dim);
                 if (dd < dbest) {
                     dbest = dd;
@@ -407,7 +420,9 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
         out_c[i] = seeds[i];
     }
     if (tid < SQ8_BALLS) {
-        out_r[tid] = cnt[tid] > 0 ? sqrtf(__uint_as_float(rmax[tid])) * 1.00001f + 1e-12f : -1.0f;
+        out_r[tid] = (static_cast<int>(tid) < n_balls && cnt[tid] > 0)
+                         ? sqrtf(__uint_as_float(rmax[tid])) * 1.00001f + 1e-12f
+                         : -1.0f;
     }
 }
 
@@ -627,7 +642,8 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
                  const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
                  const uint32_t* __restrict__ list_off, const float* __restrict__ queries, uint32_t dim,
                  const float* __restrict__ ball_centre, const float* __restrict__ ball_radius,
-                 const uint32_t* __restrict__ thr, int metric, uint32_t code_size, uint8_t* __restrict__ drop,
+                 const uint32_t* __restrict__ ball_count, const uint32_t* __restrict__ thr, int metric,
+                 uint32_t code_size, uint8_t* __restrict__ drop,
                  unsigned long long* __restrict__ scalars) {
     __shared__ unsigned long long s_bytes;
     if (threadIdx.x == 0) {
@@ -646,59 +662,56 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
         candidate = pr != first_live[q] && probe_is_live(l, nlist, rank, world, list_off) &&
                     thr[q] <= float_to_ordered(INFINITY);
     }
-    float dot[SQ8_BALLS];
-    float qq = 0.f;
-#pragma unroll
-    for (int j = 0; j < SQ8_BALLS; ++j) {
-        dot[j] = 0.f;
-    }
+    // the eight threads of a pair stay together; pairs of one warp leave the loop independently
+    const uint32_t group_mask = 0xFFu << ((threadIdx.x & 31u) & ~7u);
+    bool dropped = false;
     if (candidate) {
         const float* qv = queries + static_cast<uint64_t>(q) * dim;
-        const float* cv = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
-        for (uint32_t d = part; d < dim; d += 8) {
-            const float x = __ldg(qv + d);
-            qq = fmaf(x, x, qq);
+        float qq = 0.f;
+        if (metric != 0) {
+            for (uint32_t d = part; d < dim; d += 8) {
+                const float x = __ldg(qv + d);
+                qq = fmaf(x, x, qq);
+            }
 #pragma unroll
-            for (int j = 0; j < SQ8_BALLS; ++j) {
-                const float c = __ldg(cv + j * dim + d);
+            for (int o = 1; o < 8; o <<= 1) {
+                qq += __shfl_xor_sync(group_mask, qq, o);
+            }
+        }
+        const float bound = ordered_to_float(thr[q]);
+        const uint32_t n_balls = __ldg(ball_count + l);
+        const float* cv = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
+        bool any = false;
+        for (uint32_t j = 0; j < n_balls && !any; ++j, cv += dim) {
+            float dot = 0.f;
+            for (uint32_t d = part; d < dim; d += 8) {
+                const float x = __ldg(qv + d), c = __ldg(cv + d);
                 if (metric == 0) {
                     const float t = x - c;
-                    dot[j] = fmaf(t, t, dot[j]);
+                    dot = fmaf(t, t, dot);
                 } else {
-                    dot[j] = fmaf(x, c, dot[j]);
+                    dot = fmaf(x, c, dot);
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                dot += __shfl_xor_sync(group_mask, dot, o);
+            }
+            const float r = __ldg(ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS + j);
+            if (r >= 0.f) {
+                if (metric == 0) {
+                    const float gap = sqrtf(dot) - r;
+                    const float lower = gap > 0.f ? gap * gap : 0.f;
+                    any = !(lower > bound * 1.001f + 1e-4f * dot);
+                } else {
+                    const float lower = 1.0f - dot - sqrtf(qq) * r;
+                    any = !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
                 }
             }
         }
-    }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-        qq += __shfl_xor_sync(0xffffffffu, qq, o);
-#pragma unroll
-        for (int j = 0; j < SQ8_BALLS; ++j) {
-            dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
-        }
+        dropped = !any;
     }
     if (part == 0 && e < total) {
-        bool dropped = false;
-        if (candidate) {
-            const float bound = ordered_to_float(thr[q]);
-            bool any = false;
-#pragma unroll
-            for (int j = 0; j < SQ8_BALLS; ++j) {
-                const float r = __ldg(ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS + j);
-                if (r >= 0.f) {
-                    if (metric == 0) {
-                        const float gap = sqrtf(dot[j]) - r;
-                        const float lower = gap > 0.f ? gap * gap : 0.f;
-                        any = any || !(lower > bound * 1.001f + 1e-4f * dot[j]);
-                    } else {
-                        const float lower = 1.0f - dot[j] - sqrtf(qq) * r;
-                        any = any || !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot[j]) + 1.0f));
-                    }
-                }
-            }
-            dropped = !any;
-        }
         drop[e] = dropped ? 1 : 0;
         if (dropped) {
             atomicAdd(&s_bytes, static_cast<unsigned long long>(list_off[l + 1] - list_off[l]) * code_size);
@@ -1144,6 +1157,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     if (ws.pruning) {
         p.ball_centre = ix->ball_centre.ptr;
         p.ball_radius = ix->ball_radius.ptr;
+        p.ball_count = ix->ball_count.ptr;
     }
     p.scanned = reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 3);
     {
@@ -1228,7 +1242,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             VB_TRY(ws.pair_drop.reserve(total));
             VB_LAUNCH(pair_drop_kernel, static_cast<uint32_t>((total + 31) / 32), 256, 0, probes_dev, total, nprobe,
                       ws.first_live.ptr, nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, q_dev, ix->dim,
-                      ix->ball_centre.ptr, ix->ball_radius.ptr, ws.thr.ptr, ix->metric, ix->code_size,
+                      ix->ball_centre.ptr, ix->ball_radius.ptr, ix->ball_count.ptr, ws.thr.ptr, ix->metric,
+                      ix->code_size,
                       ws.pair_drop.ptr, reinterpret_cast<unsigned long long*>(ws.scalars.ptr));
             drop = ws.pair_drop.ptr;
         }
@@ -1759,6 +1774,7 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     if (ix->quant == VB200_QUANT_SQ8) {
         VB_TRY(ix->ball_centre.reserve(static_cast<size_t>(nlist) * SQ8_BALLS * dim));
         VB_TRY(ix->ball_radius.reserve(static_cast<size_t>(nlist) * SQ8_BALLS));
+        VB_TRY(ix->ball_count.reserve(nlist));
         const size_t balls_smem = 2 * static_cast<size_t>(SQ8_BALLS) * dim * sizeof(float);
         VB_CHECK_ARG(balls_smem <= 200 * 1024, "dim too large for the list-ball kernel");
         if (balls_smem > 48 * 1024) {
@@ -1766,7 +1782,8 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
                                          static_cast<int>(balls_smem)));
         }
         VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr,
-                  ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr);
+                  ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr,
+                  ix->ball_count.ptr);
     }
     VB_TRY(sync_stream());
     // 7. commit

@@ -24,7 +24,7 @@ namespace vb200 {
 constexpr int SCAN_THREADS = 128;
 constexpr int SCAN_WARPS = SCAN_THREADS / 32;
 
-constexpr int SQ8_BALLS = 3;   // covering balls per list for the SQ8 scan's pruning
+constexpr int SQ8_BALLS = 8;   // most covering balls a list can have for the SQ8 scan's pruning (3 .. 8 by its length)
 
 struct ScanParams {
     const uint8_t* codes;        // [positions x code_stride]
@@ -63,6 +63,7 @@ struct ScanParams {
     // bound the (query, list) pair is dropped unscanned.
     const float* ball_centre;    // [nlist][SQ8_BALLS][dim]
     const float* ball_radius;    // [nlist][SQ8_BALLS], rounded up; -1 = empty ball
+    const uint32_t* ball_count;  // [nlist] balls in use (the first ball_count[l] slots)
     unsigned long long* scanned; // bytes of codes actually scanned (pairs kept x list length x code size)
     // Id filter (filter_pos_inner null = none): a row is skipped when its inner id is tombstoned or
     // when bit (label & 0xFFFFFFFF) of the caller's bitset is set (BlackListFilter::CheckValid,
@@ -419,65 +420,65 @@ ivf_sq8_scan_kernel(const ScanParams p) {
             // survives unless even the nearest point of every ball is beyond the bound.
             static_assert(SCAN_THREADS == QT * 8, "eight threads per query of the tile");
             const int qi = threadIdx.x >> 3, part = threadIdx.x & 7;
-            float dot[SQ8_BALLS];
-            float qq = 0.f;
-#pragma unroll
-            for (int j = 0; j < SQ8_BALLS; ++j) {
-                dot[j] = 0.f;
-            }
             uint32_t q = 0;
+            float qq = 0.f;
+            const float* qv = nullptr;
             if (qi < nqt) {
                 q = it.pair_q[pbeg + qi];
-                const float* qv = p.queries + static_cast<uint64_t>(q) * p.dim;
-                const float* cv = p.ball_centre + static_cast<uint64_t>(list) * SQ8_BALLS * p.dim;
-                for (uint32_t d = part; d < p.dim; d += 8) {
-                    const float x = __ldg(qv + d);
-                    qq = fmaf(x, x, qq);
-#pragma unroll
-                    for (int j = 0; j < SQ8_BALLS; ++j) {
-                        const float c = __ldg(cv + j * p.dim + d);
-                        if (p.metric == 0) {
-                            const float t = x - c;
-                            dot[j] = fmaf(t, t, dot[j]);
-                        } else {
-                            dot[j] = fmaf(x, c, dot[j]);
-                        }
+                qv = p.queries + static_cast<uint64_t>(q) * p.dim;
+                if (p.metric != 0) {
+                    for (uint32_t d = part; d < p.dim; d += 8) {
+                        const float x = __ldg(qv + d);
+                        qq = fmaf(x, x, qq);
                     }
                 }
             }
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) {
                 qq += __shfl_xor_sync(0xffffffffu, qq, o);
+            }
+            float bound = INFINITY;
+            bool bounded = false;
+            if (qi < nqt) {
+                const uint32_t u = p.thr_g[q];
+                bounded = u <= float_to_ordered(INFINITY);   // the query has a bound already
+                bound = bounded ? ordered_to_float(u) : INFINITY;
+            }
+            bool any = !bounded;
+            const uint32_t n_balls = __ldg(p.ball_count + list);
+            const float* cv = p.ball_centre + static_cast<uint64_t>(list) * SQ8_BALLS * p.dim;
+            for (uint32_t j = 0; j < n_balls; ++j, cv += p.dim) {
+                float dot = 0.f;
+                if (qi < nqt && bounded) {
+                    for (uint32_t d = part; d < p.dim; d += 8) {
+                        const float x = __ldg(qv + d), c = __ldg(cv + d);
+                        if (p.metric == 0) {
+                            const float t = x - c;
+                            dot = fmaf(t, t, dot);
+                        } else {
+                            dot = fmaf(x, c, dot);
+                        }
+                    }
+                }
 #pragma unroll
-                for (int j = 0; j < SQ8_BALLS; ++j) {
-                    dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+                for (int o = 1; o < 8; o <<= 1) {
+                    dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                }
+                const float r = __ldg(p.ball_radius + static_cast<uint64_t>(list) * SQ8_BALLS + j);
+                if (r >= 0.f) {
+                    // slack: the distances compared here and in the scan differ in rounding only
+                    if (p.metric == 0) {
+                        const float gap = sqrtf(dot) - r;
+                        const float lower = gap > 0.f ? gap * gap : 0.f;
+                        any = any || !(lower > bound * 1.001f + 1e-4f * dot);
+                    } else {
+                        const float lower = 1.0f - dot - sqrtf(qq) * r;
+                        any = any || !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
+                    }
                 }
             }
             if (part == 0 && qi < QT) {
-                bool keep = qi < nqt;
-                if (keep) {
-                    const uint32_t u = p.thr_g[q];
-                    if (u <= float_to_ordered(INFINITY)) {   // the query has a bound already
-                        const float bound = ordered_to_float(u);
-                        // slack: the distances compared here and in the scan differ in rounding only
-                        bool any = false;
-#pragma unroll
-                        for (int j = 0; j < SQ8_BALLS; ++j) {
-                            const float r = __ldg(p.ball_radius + static_cast<uint64_t>(list) * SQ8_BALLS + j);
-                            if (r >= 0.f) {
-                                if (p.metric == 0) {
-                                    const float gap = sqrtf(dot[j]) - r;
-                                    const float lower = gap > 0.f ? gap * gap : 0.f;
-                                    any = any || !(lower > bound * 1.001f + 1e-4f * dot[j]);
-                                } else {
-                                    const float lower = 1.0f - dot[j] - sqrtf(qq) * r;
-                                    any = any || !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot[j]) + 1.0f));
-                                }
-                            }
-                        }
-                        keep = any;
-                    }
-                }
+                const bool keep = qi < nqt && any;
                 ts.cnt[qi] = keep ? 1u : 0u;   // borrowed as the keep flag until the tile is set up
             }
             __syncthreads();
