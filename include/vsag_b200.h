@@ -229,6 +229,24 @@ VB200_API int64_t vb200_ivf_memory_usage(vb200_ivf_t index);
  * NULL.  code_size = dim (SQ8) or vb200_rabitq_code_size(dim). */
 VB200_API int vb200_ivf_get_lists(vb200_ivf_t index, int64_t* list_sizes, uint8_t* codes, int64_t* inner_ids);
 
+/* The inverse of vb200_ivf_get_lists: fills an empty, trained index (centroids and quantizer model
+ * set, e.g. with the setters above) from lists that are already encoded, in the layout IVF::Serialize
+ * writes for its bucket datacell (src/datacell/bucket_datacell.h:891-904: per list its codes, its
+ * inner ids, its size) plus the label table (ivf.cpp:997).  list_sizes[nlist] is host memory;
+ * codes[total x code_size], inner_ids[total], labels[n_total] (user label of every inner id) and
+ * rows[n_total x dim] (the fp32 vectors by inner id as vb200_ivf_get_rows returns them; required when
+ * reorder is on, else may be NULL) may be host or device memory.  A shard keeps only its own lists
+ * (list % world == rank).  Nothing is re-encoded or normalised again: a search on the loaded index
+ * returns what it returned on the index the lists came from. */
+VB200_API int vb200_ivf_set_lists(vb200_ivf_t index, const int64_t* list_sizes, const uint8_t* codes,
+                        const int64_t* inner_ids, const int64_t* labels, uint64_t n_total,
+                        const float* rows);
+
+/* The fp32 rows an index with reorder keeps for the rerank (the reference's reorder codes,
+ * ivf.cpp:999-1005), [num vectors ever added x dim] by inner id, normalised when the metric is cosine;
+ * rows may be host or device memory. */
+VB200_API int vb200_ivf_get_rows(vb200_ivf_t index, float* rows);
+
 /* IVF::KnnSearch / SearchWithRequest batch branch (ivf.cpp:892-907, :2052-2354, :1693-1828):
  * for each of nq queries, routes to the nprobe = scan_buckets_count nearest lists (exact),
  * scans them, keeps the k best (factor*k when reorder is on, then reranks with the fp32 rows,
@@ -323,6 +341,14 @@ VB200_API int vb200_bf_add(vb200_bf_t index, const float* data, uint64_t count, 
 
 /* Rows that are already bf16 (uint16 bit patterns), for bf16 indexes only. */
 VB200_API int vb200_bf_add_bf16(vb200_bf_t index, const uint16_t* data, uint64_t count, const int64_t* ids);
+
+/* The rows as the index stores them (what BruteForce::Serialize writes as inner_codes_,
+ * src/algorithm/bruteforce/bruteforce.cpp:685-693): fp32 [n x dim], or bf16 bit patterns [n x dim] for a bf16 index,
+ * normalised when the metric is cosine; n counts every vector ever added.  vb200_bf_set_rows puts
+ * such rows back into an empty index without normalising or rounding them again.  Pointers may be
+ * host or device memory. */
+VB200_API int vb200_bf_get_rows(vb200_bf_t index, void* rows);
+VB200_API int vb200_bf_set_rows(vb200_bf_t index, const void* rows, uint64_t count, const int64_t* ids);
 
 VB200_API int64_t vb200_bf_num_elements(vb200_bf_t index);
 

@@ -58,6 +58,8 @@ SIGNATURES = {
     "vb200_ivf_num_elements": (c_i64, [c_void_p]),
     "vb200_ivf_memory_usage": (c_i64, [c_void_p]),
     "vb200_ivf_get_lists": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "vb200_ivf_set_lists": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_u64, c_void_p]),
+    "vb200_ivf_get_rows": (c_int, [c_void_p, c_void_p]),
     "vb200_ivf_search": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p, c_void_p]),
     "vb200_ivf_search_filtered": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p,
                                           c_void_p, c_void_p]),
@@ -74,6 +76,8 @@ SIGNATURES = {
     "vb200_bf_destroy": (c_int, [c_void_p]),
     "vb200_bf_add": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "vb200_bf_add_bf16": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
+    "vb200_bf_get_rows": (c_int, [c_void_p, c_void_p]),
+    "vb200_bf_set_rows": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "vb200_bf_num_elements": (c_i64, [c_void_p]),
     "vb200_bf_search": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p]),
     "vb200_bf_search_filtered": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p, c_void_p]),

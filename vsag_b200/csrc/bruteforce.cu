@@ -337,6 +337,46 @@ vb200_bf_add_bf16(vb200_bf_t ix, const uint16_t* data, uint64_t count, const int
     return bf_append_labels_and_norms(ix, ids, count);
 }
 
+extern "C" int
+vb200_bf_get_rows(vb200_bf_t ix, void* rows) {
+    VB_CHECK_ARG(ix != nullptr && rows != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n == 0) {
+        return 0;
+    }
+    const uint64_t elems = ix->n * ix->dim;
+    if (ix->quant == VB200_QUANT_FP32) {
+        VB_TRY(copy_out(static_cast<float*>(rows), ix->base_f32.ptr, elems));
+    } else {
+        VB_TRY(copy_out(static_cast<uint16_t*>(rows), ix->base_bf16.ptr, elems));
+    }
+    return sync_stream();
+}
+
+extern "C" int
+vb200_bf_set_rows(vb200_bf_t ix, const void* rows, uint64_t count, const int64_t* ids) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n != 0) {
+        VB_FAIL(VB200_WRONG_STATUS, "stored rows can only be loaded into an empty index");
+    }
+    if (count == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(rows != nullptr && ids != nullptr, "null pointer");
+    VB_CHECK_ARG(count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
+    const uint64_t elems = count * ix->dim;
+    if (ix->quant == VB200_QUANT_FP32) {
+        VB_TRY(bf_grow(ix->base_f32, 0, elems));
+        VB_CUDA(cudaMemcpyAsync(ix->base_f32.ptr, rows, elems * sizeof(float), cudaMemcpyDefault, current_stream()));
+    } else {
+        VB_TRY(bf_grow(ix->base_bf16, 0, elems));
+        VB_CUDA(cudaMemcpyAsync(ix->base_bf16.ptr, rows, elems * sizeof(uint16_t), cudaMemcpyDefault,
+                                current_stream()));
+    }
+    return bf_append_labels_and_norms(ix, ids, count);
+}
+
 extern "C" int64_t
 vb200_bf_num_elements(vb200_bf_t ix) {
     return ix == nullptr ? 0 : static_cast<int64_t>(ix->n - ix->n_removed);

@@ -186,6 +186,49 @@ ivf_move_old_kernel(const uint8_t* __restrict__ old_codes, const uint32_t* __res
     }
 }
 
+// Places lists given in the serialised inverted-file layout (per list: its codes packed at code_size
+// bytes each, its inner ids) into this shard's arrays: one thread per (destination position, 16-byte
+// chunk of the padded code).  Inner ids at or beyond n_total are counted in *bad and stored as NONE32.
+__global__ void
+ivf_import_lists_kernel(const uint8_t* __restrict__ src_codes, const int64_t* __restrict__ src_inner,
+                        const uint64_t* __restrict__ src_off, const uint32_t* __restrict__ new_off,
+                        uint32_t nlist, uint64_t n_kept, uint32_t code_size, uint32_t stride16,
+                        uint64_t n_total, uint8_t* __restrict__ new_codes, uint32_t* __restrict__ new_inner,
+                        unsigned long long* __restrict__ bad) {
+    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= n_kept * stride16) {
+        return;
+    }
+    uint32_t np = static_cast<uint32_t>(e / stride16);
+    uint32_t c = static_cast<uint32_t>(e % stride16);
+    uint32_t lo = 0, hi = nlist;  // largest l with new_off[l] <= np
+    while (hi - lo > 1) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (new_off[mid] <= np) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    const uint64_t sp = src_off[lo] + (np - new_off[lo]);
+    const uint8_t* src = src_codes + sp * code_size;
+    uint8_t* dst = new_codes + (static_cast<uint64_t>(np) * stride16 + c) * 16;
+#pragma unroll
+    for (uint32_t b = 0; b < 16; ++b) {
+        uint32_t pos = c * 16 + b;
+        dst[b] = pos < code_size ? src[pos] : uint8_t{0};
+    }
+    if (c == 0) {
+        int64_t inner = src_inner[sp];
+        if (inner < 0 || static_cast<uint64_t>(inner) >= n_total) {
+            atomicAdd(bad, 1ull);
+            new_inner[np] = NONE32;
+        } else {
+            new_inner[np] = static_cast<uint32_t>(inner);
+        }
+    }
+}
+
 // Sorted key s -> destination position of its row: after the rows the list already held, in
 // ascending row order (the append order of IVF::Add with thread_count 1, ivf.cpp:662-676).
 __global__ void
@@ -1626,6 +1669,75 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
     return sync_stream();
 }
 
+// Labels and (for reorder) the fp32 rows of `count` new vectors, by inner id, after the ones the index
+// holds; tombstone words for the new ids.  n_total itself is advanced by ivf_commit_lists.
+static int
+ivf_append_row_data(vb200_ivf* ix, const int64_t* ids, const float* rows_dev, uint64_t count) {
+    cudaStream_t st = current_stream();
+    const uint32_t dim = ix->dim;
+    const uint64_t words = (ix->n_total + count + 31) / 32;
+    if (words > ix->tomb_words) {
+        DevBuf<uint32_t> bigger;
+        const uint64_t cap = words * 2;
+        VB_TRY(bigger.reserve(cap));
+        VB_CUDA(cudaMemsetAsync(bigger.ptr, 0, cap * sizeof(uint32_t), st));
+        if (ix->tomb_words > 0) {
+            VB_CUDA(cudaMemcpyAsync(bigger.ptr, ix->tombstones.ptr, ix->tomb_words * sizeof(uint32_t),
+                                    cudaMemcpyDeviceToDevice, st));
+        }
+        VB_TRY(sync_stream());
+        ix->tombstones = std::move(bigger);
+        ix->tomb_words = cap;
+    }
+    VB_TRY(grow_preserve(ix->labels, ix->n_total, ix->n_total + count));
+    VB_CUDA(cudaMemcpyAsync(ix->labels.ptr + ix->n_total, ids, count * sizeof(int64_t),
+                            cudaMemcpyDefault, st));
+    if (ix->use_reorder) {
+        VB_TRY(grow_preserve(ix->flat, ix->n_total * dim, (ix->n_total + count) * dim));
+        VB_CUDA(cudaMemcpyAsync(ix->flat.ptr + ix->n_total * dim, rows_dev, count * dim * sizeof(float),
+                                cudaMemcpyDeviceToDevice, st));
+    }
+    return 0;
+}
+
+// What every change of the lists recomputes (SQ8: the norm of every decoded code and the covering
+// balls of every list), then the new arrays replace the old ones.
+static int
+ivf_commit_lists(vb200_ivf* ix, DevBuf<uint8_t>& new_codes, DevBuf<uint32_t>& new_inner,
+                 DevBuf<uint32_t>& new_off_dev, const std::vector<uint32_t>& new_off, uint64_t n_new_stored,
+                 uint64_t n_total_new) {
+    const uint32_t nlist = ix->nlist, dim = ix->dim, stride = ix->code_stride;
+    DevBuf<float> new_norm;
+    if (ix->quant == VB200_QUANT_SQ8 && n_new_stored > 0) {
+        VB_TRY(new_norm.reserve(n_new_stored));
+        VB_LAUNCH(sq8_code_norm_kernel, static_cast<uint32_t>((n_new_stored + 127) / 128), 128, 0,
+                  new_codes.ptr, n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_norm.ptr);
+    }
+    if (ix->quant == VB200_QUANT_SQ8) {
+        VB_TRY(ix->ball_centre.reserve(static_cast<size_t>(nlist) * SQ8_BALLS * dim));
+        VB_TRY(ix->ball_radius.reserve(static_cast<size_t>(nlist) * SQ8_BALLS));
+        VB_TRY(ix->ball_count.reserve(nlist));
+        const size_t balls_smem = 2 * static_cast<size_t>(SQ8_BALLS) * dim * sizeof(float);
+        VB_CHECK_ARG(balls_smem <= 200 * 1024, "dim too large for the list-ball kernel");
+        if (balls_smem > 48 * 1024) {
+            VB_CUDA(cudaFuncSetAttribute(sq8_list_balls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(balls_smem)));
+        }
+        VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr,
+                  ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr,
+                  ix->ball_count.ptr);
+    }
+    VB_TRY(sync_stream());
+    ix->code_norm = std::move(new_norm);
+    ix->codes = std::move(new_codes);
+    ix->pos_inner = std::move(new_inner);
+    ix->list_off = std::move(new_off_dev);
+    ix->list_off_host = new_off;
+    ix->n_stored = n_new_stored;
+    ix->n_total = n_total_new;
+    return ivf_refresh_scan_order(ix);
+}
+
 extern "C" int
 vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* ids,
               const int32_t* labels_in) {
@@ -1741,60 +1853,9 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
                                     dst_of_row.ptr, new_codes.ptr, stride));
     }
     // 6. labels and (for reorder) the fp32 rows, by inner id; tombstone words for the new ids
-    {
-        const uint64_t words = (ix->n_total + count + 31) / 32;
-        if (words > ix->tomb_words) {
-            DevBuf<uint32_t> bigger;
-            const uint64_t cap = words * 2;
-            VB_TRY(bigger.reserve(cap));
-            VB_CUDA(cudaMemsetAsync(bigger.ptr, 0, cap * sizeof(uint32_t), st));
-            if (ix->tomb_words > 0) {
-                VB_CUDA(cudaMemcpyAsync(bigger.ptr, ix->tombstones.ptr, ix->tomb_words * sizeof(uint32_t),
-                                        cudaMemcpyDeviceToDevice, st));
-            }
-            VB_TRY(sync_stream());
-            ix->tombstones = std::move(bigger);
-            ix->tomb_words = cap;
-        }
-    }
-    VB_TRY(grow_preserve(ix->labels, ix->n_total, ix->n_total + count));
-    VB_CUDA(cudaMemcpyAsync(ix->labels.ptr + ix->n_total, ids, count * sizeof(int64_t),
-                            cudaMemcpyDefault, st));
-    if (ix->use_reorder) {
-        VB_TRY(grow_preserve(ix->flat, ix->n_total * dim, (ix->n_total + count) * dim));
-        VB_CUDA(cudaMemcpyAsync(ix->flat.ptr + ix->n_total * dim, xr, count * dim * sizeof(float),
-                                cudaMemcpyDeviceToDevice, st));
-    }
-    DevBuf<float> new_norm;
-    if (ix->quant == VB200_QUANT_SQ8 && n_new_stored > 0) {
-        VB_TRY(new_norm.reserve(n_new_stored));
-        VB_LAUNCH(sq8_code_norm_kernel, static_cast<uint32_t>((n_new_stored + 127) / 128), 128, 0,
-                  new_codes.ptr, n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_norm.ptr);
-    }
-    if (ix->quant == VB200_QUANT_SQ8) {
-        VB_TRY(ix->ball_centre.reserve(static_cast<size_t>(nlist) * SQ8_BALLS * dim));
-        VB_TRY(ix->ball_radius.reserve(static_cast<size_t>(nlist) * SQ8_BALLS));
-        VB_TRY(ix->ball_count.reserve(nlist));
-        const size_t balls_smem = 2 * static_cast<size_t>(SQ8_BALLS) * dim * sizeof(float);
-        VB_CHECK_ARG(balls_smem <= 200 * 1024, "dim too large for the list-ball kernel");
-        if (balls_smem > 48 * 1024) {
-            VB_CUDA(cudaFuncSetAttribute(sq8_list_balls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(balls_smem)));
-        }
-        VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr,
-                  ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr,
-                  ix->ball_count.ptr);
-    }
-    VB_TRY(sync_stream());
-    // 7. commit
-    ix->code_norm = std::move(new_norm);
-    ix->codes = std::move(new_codes);
-    ix->pos_inner = std::move(new_inner);
-    ix->list_off = std::move(new_off_dev);
-    ix->list_off_host = new_off;
-    ix->n_stored = n_new_stored;
-    ix->n_total += count;
-    return ivf_refresh_scan_order(ix);
+    VB_TRY(ivf_append_row_data(ix, ids, xr, count));
+    // 7. per-list derived data, then commit
+    return ivf_commit_lists(ix, new_codes, new_inner, new_off_dev, new_off, n_new_stored, ix->n_total + count);
 }
 
 extern "C" int
@@ -1846,6 +1907,85 @@ vb200_ivf_memory_usage(vb200_ivf_t ix) {
     return static_cast<int64_t>(ix->codes.bytes() + ix->pos_inner.bytes() + ix->labels.bytes() +
                                 ix->flat.bytes() + ix->centroids.bytes() + ix->rotation.bytes() +
                                 ix->list_off.bytes());
+}
+
+extern "C" int
+vb200_ivf_set_lists(vb200_ivf_t ix, const int64_t* list_sizes, const uint8_t* codes, const int64_t* inner_ids,
+                    const int64_t* labels, uint64_t n_total, const float* rows) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    VB_CHECK_ARG(list_sizes != nullptr && labels != nullptr, "null pointer");
+    VB_CHECK_ARG(!is_device_pointer(list_sizes), "list_sizes is read on the host");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (!ix->has_centroids || !ix->has_model) {
+        VB_FAIL(VB200_WRONG_STATUS, "index is not trained");
+    }
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_WRONG_STATUS, "lists can only be loaded into an empty index");
+    }
+    VB_CHECK_ARG(n_total > 0 && n_total < 0xFFFFFFFFull, "n_total must be in [1, 2^32-2]");
+    VB_CHECK_ARG(!ix->use_reorder || rows != nullptr, "an index with reorder needs the fp32 rows");
+    const uint32_t nlist = ix->nlist, dim = ix->dim, stride = ix->code_stride;
+    std::vector<uint64_t> src_off(nlist + 1);
+    std::vector<uint32_t> new_off(nlist + 1);
+    uint64_t run_src = 0, run_new = 0;
+    for (uint32_t l = 0; l < nlist; ++l) {
+        VB_CHECK_ARG(list_sizes[l] >= 0, "negative list size");
+        src_off[l] = run_src;
+        new_off[l] = static_cast<uint32_t>(run_new);
+        run_src += static_cast<uint64_t>(list_sizes[l]);
+        if (l % ix->shard_world == ix->shard_rank) {
+            run_new += static_cast<uint64_t>(list_sizes[l]);
+        }
+        VB_CHECK_ARG(run_src < 0xFFFFFFFFull, "lists hold more than 2^32-2 entries");
+    }
+    src_off[nlist] = run_src;
+    new_off[nlist] = static_cast<uint32_t>(run_new);
+    VB_CHECK_ARG(run_src == 0 || (codes != nullptr && inner_ids != nullptr), "null pointer");
+    const uint64_t n_kept = run_new;
+    cudaStream_t st = current_stream();
+
+    DevInput<uint8_t> src_codes;
+    DevInput<int64_t> src_inner;
+    VB_TRY(src_codes.bind(codes, run_src * ix->code_size));
+    VB_TRY(src_inner.bind(inner_ids, run_src));
+    DevBuf<uint64_t> src_off_dev;
+    DevBuf<uint32_t> new_off_dev, new_inner;
+    DevBuf<uint8_t> new_codes;
+    DevBuf<unsigned long long> bad;
+    VB_TRY(src_off_dev.reserve(nlist + 1));
+    VB_TRY(new_off_dev.reserve(nlist + 1));
+    VB_TRY(new_codes.reserve((n_kept > 0 ? n_kept : 1) * stride));
+    VB_TRY(new_inner.reserve(n_kept > 0 ? n_kept : 1));
+    VB_TRY(bad.reserve(1));
+    VB_CUDA(cudaMemcpyAsync(src_off_dev.ptr, src_off.data(), (nlist + 1) * sizeof(uint64_t), cudaMemcpyHostToDevice, st));
+    VB_CUDA(cudaMemcpyAsync(new_off_dev.ptr, new_off.data(), (nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+    VB_CUDA(cudaMemsetAsync(bad.ptr, 0, sizeof(unsigned long long), st));
+    if (n_kept > 0) {
+        const uint64_t work = n_kept * (stride / 16);
+        VB_LAUNCH(ivf_import_lists_kernel, static_cast<uint32_t>((work + 255) / 256), 256, 0, src_codes.ptr,
+                  src_inner.ptr, src_off_dev.ptr, new_off_dev.ptr, nlist, n_kept, ix->code_size, stride / 16, n_total,
+                  new_codes.ptr, new_inner.ptr, bad.ptr);
+    }
+    unsigned long long n_bad = 0;
+    VB_CUDA(cudaMemcpyAsync(&n_bad, bad.ptr, sizeof(n_bad), cudaMemcpyDeviceToHost, st));
+    VB_TRY(sync_stream());
+    VB_CHECK_ARG(n_bad == 0, "%llu inner ids are outside [0, n_total)", n_bad);
+
+    DevInput<float> x;   // the rows as stored: nothing is normalised again
+    if (ix->use_reorder) {
+        VB_TRY(x.bind(rows, n_total * dim));
+    }
+    VB_TRY(ivf_append_row_data(ix, labels, x.ptr, n_total));
+    return ivf_commit_lists(ix, new_codes, new_inner, new_off_dev, new_off, n_kept, n_total);
+}
+
+extern "C" int
+vb200_ivf_get_rows(vb200_ivf_t ix, float* rows) {
+    VB_CHECK_ARG(ix != nullptr && rows != nullptr, "null pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    VB_CHECK_ARG(ix->use_reorder, "the index keeps fp32 rows only when reorder is on");
+    VB_TRY(copy_out(rows, ix->flat.ptr, ix->n_total * ix->dim));
+    return sync_stream();
 }
 
 extern "C" int

@@ -171,6 +171,7 @@ class IvfHandle:
         check(self._lib.vb200_ivf_create(dim, metric, nlist, quant, int(use_reorder), C.byref(h)))
         self._h = h
         self.dim, self.metric, self.nlist, self.quant, self.use_reorder = dim, metric, nlist, quant, use_reorder
+        self.n_added = 0     # vectors ever added (removed ones included): the range of inner ids
 
     def close(self) -> None:
         if getattr(self, "_h", None):
@@ -223,6 +224,7 @@ class IvfHandle:
     def add(self, data, ids, labels=None) -> None:
         check(self._lib.vb200_ivf_add(self._h, ptr(data, np.float32), _rows(data), ptr(ids, np.int64),
                                       ptr(labels, np.int32)))
+        self.n_added += _rows(data)
 
     def num_elements(self) -> int:
         return int(self._lib.vb200_ivf_num_elements(self._h))
@@ -238,6 +240,27 @@ class IvfHandle:
         inner = np.empty(total, np.int64)
         check(self._lib.vb200_ivf_get_lists(self._h, None, ptr(codes), ptr(inner)))
         return sizes, codes, inner
+
+    def set_lists(self, sizes, codes, inner_ids, labels, rows=None) -> None:
+        """Fills an empty, trained index from lists that are already encoded (what `get_lists` returns,
+        or the bucket datacell and label table of a serialised index); `rows` are the fp32 vectors by
+        inner id, needed when reorder is on."""
+        sizes = np.ascontiguousarray(sizes, np.int64)
+        if sizes.shape != (self.nlist,):
+            raise ValueError("sizes must have one entry per list")
+        n_total = _rows(labels) if hasattr(labels, "shape") else len(labels)
+        if not hasattr(labels, "shape"):
+            labels = np.asarray(labels, np.int64)
+        check(self._lib.vb200_ivf_set_lists(self._h, ptr(sizes), ptr(codes, np.uint8), ptr(inner_ids, np.int64),
+                                            ptr(labels, np.int64), n_total,
+                                            ptr(rows, np.float32) if rows is not None else None))
+        self.n_added = n_total
+
+    def get_rows(self) -> np.ndarray:
+        """The fp32 rows kept for the rerank, by inner id (reorder only)."""
+        out = np.empty((self.n_added, self.dim), np.float32)
+        check(self._lib.vb200_ivf_get_rows(self._h, ptr(out)))
+        return out
 
     def route(self, queries, nprobe: int, out=None):
         """(bucket ids, centroid distances) as numpy arrays, or with `out` (an int32 [nq, nprobe]
@@ -321,6 +344,7 @@ class BfHandle:
         check(self._lib.vb200_bf_create(dim, metric, quant, C.byref(h)))
         self._h = h
         self.dim, self.metric, self.quant = dim, metric, quant
+        self.n_added = 0     # vectors ever added (removed ones included)
 
     def close(self) -> None:
         if getattr(self, "_h", None):
@@ -331,9 +355,23 @@ class BfHandle:
 
     def add(self, data, ids) -> None:
         check(self._lib.vb200_bf_add(self._h, ptr(data, np.float32), _rows(data), ptr(ids, np.int64)))
+        self.n_added += _rows(data)
 
     def add_bf16(self, data, ids) -> None:
         check(self._lib.vb200_bf_add_bf16(self._h, ptr(data, np.uint16), _rows(data), ptr(ids, np.int64)))
+        self.n_added += _rows(data)
+
+    def get_rows(self) -> np.ndarray:
+        """The rows as stored: fp32, or bf16 bit patterns (uint16) for a bf16 index."""
+        out = np.empty((self.n_added, self.dim), np.float32 if self.quant == QUANT_FP32 else np.uint16)
+        check(self._lib.vb200_bf_get_rows(self._h, ptr(out)))
+        return out
+
+    def set_rows(self, rows, ids) -> None:
+        """Puts rows from `get_rows` back into an empty index, bit for bit."""
+        check(self._lib.vb200_bf_set_rows(self._h, ptr(rows, np.float32 if self.quant == QUANT_FP32 else np.uint16),
+                                          _rows(rows), ptr(ids, np.int64)))
+        self.n_added = _rows(rows)
 
     def num_elements(self) -> int:
         return int(self._lib.vb200_bf_num_elements(self._h))

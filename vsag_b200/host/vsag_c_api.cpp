@@ -3,9 +3,11 @@
 // knn_search.  They sit on the vsag::Factory / Index mirror, so a program written against the
 // reference's C API links against libvsag_b200.so unchanged for "ivf" and "brute_force".
 // vsag_index_knn_search_batch is an addition: the reference's C API takes one query per call.
+// vsag_serialize_file / vsag_deserialize_file follow include/vsag/vsag_c_api.h:319-330.
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <fstream>
 
 #include "vsag_host.h"
 
@@ -245,4 +247,50 @@ VSAG_C_EXPORT int64_t
 vsag_index_get_num_elements(vsag_index_t index) {
     auto* box = static_cast<IndexBox*>(index);
     return box == nullptr ? 0 : box->index->GetNumElements();
+}
+
+VSAG_C_EXPORT Error_t
+vsag_serialize_file(vsag_index_t index, const char* file_path) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (file_path == nullptr) {
+        return make_error(-static_cast<int>(vsag::ErrorType::INVALID_ARGUMENT), "file_path is NULL");
+    }
+    std::ofstream file(file_path, std::ios::binary);
+    if (!file.is_open()) {
+        return make_error(-1, "failed to open file for writing: " + std::string(file_path));
+    }
+    auto r = box->index->Serialize(file);
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    file.close();
+    if (!file) {
+        return make_error(-static_cast<int>(vsag::ErrorType::INTERNAL_ERROR),
+                          "failed to write file: " + std::string(file_path));
+    }
+    return success();
+}
+
+VSAG_C_EXPORT Error_t
+vsag_deserialize_file(vsag_index_t index, const char* file_path) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (file_path == nullptr) {
+        return make_error(-static_cast<int>(vsag::ErrorType::INVALID_ARGUMENT), "file_path is NULL");
+    }
+    std::ifstream file(file_path, std::ios::binary);
+    if (!file.is_open()) {
+        return make_error(-static_cast<int>(vsag::ErrorType::MISSING_FILE),
+                          "failed to open file for reading: " + std::string(file_path));
+    }
+    auto r = box->index->Deserialize(file);
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    return success();
 }

@@ -4,8 +4,10 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <istream>
 #include <limits>
 #include <mutex>
+#include <ostream>
 #include <random>
 #include <set>
 
@@ -65,6 +67,133 @@ safe_call(Fn&& fn) {
         return Expected<T>(Error{ErrorType::INVALID_ARGUMENT, e.what()});
     } catch (const std::exception& e) {
         return Expected<T>(Error{ErrorType::UNKNOWN_ERROR, e.what()});
+    }
+}
+
+// Runs `fn` for an operation without a result, mapping failures like safe_call.
+template <typename Fn>
+Expected<void>
+safe_void(Fn&& fn) {
+    auto r = safe_call<bool>([&]() {
+        fn();
+        return true;
+    });
+    if (!r.has_value()) {
+        return Expected<void>(r.error());
+    }
+    return Expected<void>();
+}
+
+// Index file: header (magic, version, kind, creation parameters), then the blocks of the kind, then
+// the end mark.  Integers and floats are little-endian, as the reference's StreamWriter writes them.
+constexpr char FILE_MAGIC[8] = {'V', 'B', '2', '0', '0', 'I', 'D', 'X'};
+constexpr uint32_t FILE_VERSION = 1;
+constexpr uint32_t FILE_KIND_IVF = 1, FILE_KIND_BRUTE_FORCE = 2;
+constexpr uint64_t FILE_END_MARK = 0x444e455f30303242ull;
+
+template <typename T>
+void
+write_pod(std::ostream& out, const T& v) {
+    out.write(reinterpret_cast<const char*>(&v), sizeof(T));
+}
+
+template <typename T>
+void
+write_array(std::ostream& out, const std::vector<T>& v) {
+    write_pod<uint64_t>(out, v.size());
+    out.write(reinterpret_cast<const char*>(v.data()), static_cast<std::streamsize>(v.size() * sizeof(T)));
+}
+
+template <typename T>
+T
+read_pod(std::istream& in) {
+    T v{};
+    in.read(reinterpret_cast<char*>(&v), sizeof(T));
+    if (!in) {
+        fail(ErrorType::READ_ERROR, "unexpected end of the index stream");
+    }
+    return v;
+}
+
+// An array whose length must be `want` (sizes follow from the header, so a wrong one means a damaged file).
+template <typename T>
+std::vector<T>
+read_array(std::istream& in, uint64_t want, const char* what) {
+    uint64_t n = read_pod<uint64_t>(in);
+    if (n != want) {
+        fail(ErrorType::INVALID_BINARY, std::string("index stream: block ") + what + " has " + std::to_string(n) +
+                                            " entries, expected " + std::to_string(want));
+    }
+    std::vector<T> v(n);
+    in.read(reinterpret_cast<char*>(v.data()), static_cast<std::streamsize>(n * sizeof(T)));
+    if (!in) {
+        fail(ErrorType::READ_ERROR, std::string("unexpected end of the index stream in block ") + what);
+    }
+    return v;
+}
+
+template <typename T>
+std::vector<T>
+read_array_any(std::istream& in, const char* what) {
+    uint64_t n = read_pod<uint64_t>(in);
+    if (n > (uint64_t{1} << 40) / sizeof(T)) {
+        fail(ErrorType::INVALID_BINARY, std::string("index stream: block ") + what + " is implausibly large");
+    }
+    std::vector<T> v(n);
+    in.read(reinterpret_cast<char*>(v.data()), static_cast<std::streamsize>(n * sizeof(T)));
+    if (!in) {
+        fail(ErrorType::READ_ERROR, std::string("unexpected end of the index stream in block ") + what);
+    }
+    return v;
+}
+
+struct FileHeader {
+    uint32_t kind, dim, nlist, use_reorder;
+    int32_t metric, quant;
+};
+
+void
+write_header(std::ostream& out, const FileHeader& h) {
+    out.write(FILE_MAGIC, sizeof(FILE_MAGIC));
+    write_pod(out, FILE_VERSION);
+    write_pod(out, h);
+}
+
+// Reads the header and checks it against the parameters of the index that is being filled.
+void
+read_header(std::istream& in, const FileHeader& want) {
+    char magic[sizeof(FILE_MAGIC)] = {};
+    in.read(magic, sizeof(magic));
+    if (!in) {
+        fail(ErrorType::READ_ERROR, "unexpected end of the index stream");
+    }
+    if (std::memcmp(magic, FILE_MAGIC, sizeof(magic)) != 0) {
+        fail(ErrorType::INVALID_BINARY, "the stream does not hold an index written by this engine");
+    }
+    uint32_t version = read_pod<uint32_t>(in);
+    if (version != FILE_VERSION) {
+        fail(ErrorType::INVALID_BINARY, "index stream version " + std::to_string(version) + " is not supported");
+    }
+    FileHeader h = read_pod<FileHeader>(in);
+    check_argument(h.kind == want.kind, "the stream holds another kind of index");
+    check_argument(h.dim == want.dim && h.metric == want.metric && h.nlist == want.nlist && h.quant == want.quant &&
+                       h.use_reorder == want.use_reorder,
+                   "the index was written with other creation parameters (dim, metric_type, buckets_count, "
+                   "base_quantization_type or use_reorder differ)");
+}
+
+void
+check_stream_written(std::ostream& out) {
+    write_pod(out, FILE_END_MARK);
+    if (!out) {
+        fail(ErrorType::INTERNAL_ERROR, "writing the index stream failed");
+    }
+}
+
+void
+check_end_mark(std::istream& in) {
+    if (read_pod<uint64_t>(in) != FILE_END_MARK) {
+        fail(ErrorType::INVALID_BINARY, "index stream: end mark not found");
     }
 }
 
@@ -335,8 +464,8 @@ public:
         check_argument(train_sample_count_ >= 512, "train_sample_count must be at least 512");
         check_status(vb200_ivf_create(dim_, metric_, nlist_, quant_, use_reorder_ ? 1 : 0, &handle_));
         if (quant_ == VB200_QUANT_RABITQ) {
-            auto rot = random_rotation(dim_, 47);
-            check_status(vb200_ivf_set_rabitq_rotation(handle_, rot.data()));
+            rotation_ = random_rotation(dim_, 47);
+            check_status(vb200_ivf_set_rabitq_rotation(handle_, rotation_.data()));
         }
     }
 
@@ -423,9 +552,119 @@ public:
     Expected<uint32_t>
     Remove(const std::vector<int64_t>& ids) override {
         return safe_call<uint32_t>([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
             uint64_t removed = 0;
             check_status(remove_labels(ids.data(), ids.size(), &removed));
+            removed_labels_.insert(removed_labels_.end(), ids.begin(), ids.end());
             return static_cast<uint32_t>(removed);
+        });
+    }
+
+    Expected<void>
+    Serialize(std::ostream& out) const override {
+        return safe_void([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            write_header(out, file_header());
+            write_pod<uint32_t>(out, trained_ ? 1 : 0);
+            const uint64_t n_total = labels_host_.size();
+            write_pod<uint64_t>(out, n_total);
+            if (trained_) {
+                std::vector<float> centroids(static_cast<size_t>(nlist_) * dim_);
+                check_status(vb200_ivf_get_centroids(handle_, centroids.data()));
+                write_array(out, centroids);
+                if (quant_ == VB200_QUANT_SQ8) {
+                    std::vector<float> lower(dim_), diff(dim_);
+                    check_status(vb200_ivf_get_sq8_model(handle_, lower.data(), diff.data()));
+                    write_array(out, lower);
+                    write_array(out, diff);
+                } else if (quant_ == VB200_QUANT_RABITQ) {
+                    std::vector<float> centre(dim_);
+                    check_status(vb200_ivf_get_rabitq_centroid(handle_, centre.data()));
+                    write_array(out, rotation_);
+                    write_array(out, centre);
+                }
+            }
+            if (n_total > 0) {
+                std::vector<int64_t> sizes(nlist_);
+                check_status(vb200_ivf_get_lists(handle_, sizes.data(), nullptr, nullptr));
+                uint64_t total = 0;
+                for (int64_t v : sizes) {
+                    total += static_cast<uint64_t>(v);
+                }
+                std::vector<uint8_t> codes(total * static_cast<uint64_t>(code_size()));
+                std::vector<int64_t> inner(total);
+                check_status(vb200_ivf_get_lists(handle_, nullptr, codes.data(), inner.data()));
+                write_array(out, sizes);
+                write_array(out, codes);
+                write_array(out, inner);
+                write_array(out, labels_host_);
+                if (use_reorder_) {
+                    std::vector<float> rows(n_total * dim_);
+                    check_status(vb200_ivf_get_rows(handle_, rows.data()));
+                    write_array(out, rows);
+                }
+            }
+            write_array(out, removed_labels_);
+            check_stream_written(out);
+        });
+    }
+
+    Expected<void>
+    Deserialize(std::istream& in) override {
+        return safe_void([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (trained_ || !labels_host_.empty()) {
+                fail(ErrorType::INDEX_NOT_EMPTY, "failed to Deserialize: index is not empty");
+            }
+            read_header(in, file_header());
+            const bool trained = read_pod<uint32_t>(in) != 0;
+            const uint64_t n_total = read_pod<uint64_t>(in);
+            if (!trained && n_total > 0) {
+                fail(ErrorType::INVALID_BINARY, "index stream: vectors without a trained model");
+            }
+            if (trained) {
+                auto centroids = read_array<float>(in, static_cast<uint64_t>(nlist_) * dim_, "centroids");
+                check_status(vb200_ivf_set_centroids(handle_, centroids.data()));
+                if (quant_ == VB200_QUANT_SQ8) {
+                    auto lower = read_array<float>(in, dim_, "sq8 lower bound");
+                    auto diff = read_array<float>(in, dim_, "sq8 diff");
+                    check_status(vb200_ivf_set_sq8_model(handle_, lower.data(), diff.data()));
+                } else if (quant_ == VB200_QUANT_RABITQ) {
+                    auto rotation = read_array<float>(in, static_cast<uint64_t>(dim_) * dim_, "rabitq rotation");
+                    auto centre = read_array<float>(in, dim_, "rabitq centroid");
+                    check_status(vb200_ivf_set_rabitq_rotation(handle_, rotation.data()));
+                    check_status(vb200_ivf_set_rabitq_centroid(handle_, centre.data()));
+                    rotation_ = std::move(rotation);
+                }
+                trained_ = true;
+            }
+            if (n_total > 0) {
+                auto sizes = read_array<int64_t>(in, nlist_, "list sizes");
+                uint64_t total = 0;
+                for (int64_t v : sizes) {
+                    if (v < 0) {
+                        fail(ErrorType::INVALID_BINARY, "index stream: negative list size");
+                    }
+                    total += static_cast<uint64_t>(v);
+                }
+                auto codes = read_array<uint8_t>(in, total * static_cast<uint64_t>(code_size()), "codes");
+                auto inner = read_array<int64_t>(in, total, "inner ids");
+                auto labels = read_array<int64_t>(in, n_total, "labels");
+                std::vector<float> rows;
+                if (use_reorder_) {
+                    rows = read_array<float>(in, n_total * dim_, "reorder rows");
+                }
+                check_status(vb200_ivf_set_lists(handle_, sizes.data(), codes.data(), inner.data(), labels.data(),
+                                                 n_total, use_reorder_ ? rows.data() : nullptr));
+                labels_host_ = std::move(labels);
+                built_ = true;
+            }
+            auto removed = read_array_any<int64_t>(in, "removed labels");
+            check_end_mark(in);
+            if (!removed.empty()) {
+                check_status(remove_labels(removed.data(), removed.size(), nullptr));
+                removed_labels_ = std::move(removed);
+            }
         });
     }
 
@@ -491,6 +730,9 @@ public:
 private:
     int64_t
     code_size() const {
+        if (quant_ == VB200_QUANT_FP32) {
+            return static_cast<int64_t>(dim_) * 4;
+        }
         return quant_ == VB200_QUANT_SQ8 ? dim_ : static_cast<int64_t>(vb200_rabitq_code_size(dim_));
     }
 
@@ -543,7 +785,14 @@ private:
         return vb200_ivf_remove(handle_, ids, count, removed);
     }
 
-    std::vector<int64_t> labels_host_;   // ids in insertion order, for callback filters
+    FileHeader
+    file_header() const {
+        return FileHeader{FILE_KIND_IVF, dim_, nlist_, use_reorder_ ? 1u : 0u, metric_, quant_};
+    }
+
+    std::vector<int64_t> labels_host_;     // ids in insertion order, for callback filters
+    std::vector<int64_t> removed_labels_;  // every id Remove was asked for, replayed after a reload
+    std::vector<float> rotation_;          // RaBitQ: the rotation in use
 
     uint32_t dim_;
     int metric_;
@@ -650,9 +899,54 @@ public:
     Expected<uint32_t>
     Remove(const std::vector<int64_t>& ids) override {
         return safe_call<uint32_t>([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
             uint64_t removed = 0;
             check_status(remove_labels(ids.data(), ids.size(), &removed));
+            removed_labels_.insert(removed_labels_.end(), ids.begin(), ids.end());
             return static_cast<uint32_t>(removed);
+        });
+    }
+
+    Expected<void>
+    Serialize(std::ostream& out) const override {
+        return safe_void([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            write_header(out, file_header());
+            const uint64_t n_total = labels_host_.size();
+            write_pod<uint64_t>(out, n_total);
+            if (n_total > 0) {
+                // fp32 rows or bf16 bit patterns, as stored
+                std::vector<uint8_t> rows(n_total * dim_ * (quant_ == VB200_QUANT_FP32 ? 4 : 2));
+                check_status(vb200_bf_get_rows(handle_, rows.data()));
+                write_array(out, rows);
+                write_array(out, labels_host_);
+            }
+            write_array(out, removed_labels_);
+            check_stream_written(out);
+        });
+    }
+
+    Expected<void>
+    Deserialize(std::istream& in) override {
+        return safe_void([&]() {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (!labels_host_.empty()) {
+                fail(ErrorType::INDEX_NOT_EMPTY, "failed to Deserialize: index is not empty");
+            }
+            read_header(in, file_header());
+            const uint64_t n_total = read_pod<uint64_t>(in);
+            if (n_total > 0) {
+                auto rows = read_array<uint8_t>(in, n_total * dim_ * (quant_ == VB200_QUANT_FP32 ? 4 : 2), "rows");
+                auto labels = read_array<int64_t>(in, n_total, "labels");
+                check_status(vb200_bf_set_rows(handle_, rows.data(), n_total, labels.data()));
+                labels_host_ = std::move(labels);
+            }
+            auto removed = read_array_any<int64_t>(in, "removed labels");
+            check_end_mark(in);
+            if (!removed.empty()) {
+                check_status(remove_labels(removed.data(), removed.size(), nullptr));
+                removed_labels_ = std::move(removed);
+            }
         });
     }
 
@@ -718,7 +1012,13 @@ private:
         return vb200_bf_remove(handle_, ids, count, removed);
     }
 
-    std::vector<int64_t> labels_host_;   // ids in insertion order, for callback filters
+    FileHeader
+    file_header() const {
+        return FileHeader{FILE_KIND_BRUTE_FORCE, dim_, 0u, 0u, metric_, quant_};
+    }
+
+    std::vector<int64_t> labels_host_;     // ids in insertion order, for callback filters
+    std::vector<int64_t> removed_labels_;  // every id Remove was asked for, replayed after a reload
 
     uint32_t dim_;
     int metric_;

@@ -1,6 +1,6 @@
 // Host-side mirror of the part of VSAG's public API that the accelerated path sits behind:
 // vsag::Factory::CreateIndex("ivf" | "brute_force", json), Index::{Build, Train, Add, KnnSearch,
-// GetNumElements, GetMemoryUsage} and the Dataset builder (reference: include/vsag/factory.h:47-50,
+// Remove, Serialize, Deserialize, GetNumElements, GetMemoryUsage} and the Dataset builder (reference: include/vsag/factory.h:47-50,
 // include/vsag/index.h:126-303, include/vsag/dataset.h:135-511, include/vsag/errors.h:26-48).
 // Same names, argument meaning and error behaviour, written from scratch over the C ABI of
 // include/vsag_b200.h; no exception crosses these calls.
@@ -8,6 +8,7 @@
 
 #include <cstdint>
 #include <functional>
+#include <iosfwd>
 #include <memory>
 #include <string>
 #include <utility>
@@ -54,6 +55,21 @@ public:
 private:
     bool has_;
     T value_{};
+    Error error_{ErrorType::UNKNOWN_ERROR, ""};
+};
+
+// tl::expected<void, Error>: success carries no value.
+template <>
+class Expected<void> {
+public:
+    Expected() = default;
+    Expected(Error error) : has_(false), error_(std::move(error)) {}  // NOLINT(google-explicit-constructor)
+    bool has_value() const { return has_; }
+    explicit operator bool() const { return has_; }
+    const Error& error() const { return error_; }
+
+private:
+    bool has_ = true;
     Error error_{ErrorType::UNKNOWN_ERROR, ""};
 };
 
@@ -144,6 +160,15 @@ public:
     // RemoveMode::MARK_REMOVE (include/vsag/index.h:186-200): the vectors stay stored but are never
     // returned again; the result is the number of ids found and newly marked.
     virtual Expected<uint32_t> Remove(const std::vector<int64_t>& ids) = 0;
+    // Serialize to / Deserialize from an opened stream (include/vsag/index.h:903-940).  Deserialize wants
+    // an empty index created with the parameters of the one that was written (INDEX_NOT_EMPTY,
+    // INVALID_ARGUMENT otherwise); a stream that is not such a file gives INVALID_BINARY, a short one
+    // READ_ERROR.  The bytes are this engine's own container around the pieces IVF::Serialize and
+    // BruteForce::Serialize write (centroids, quantizer model, per-list codes and inner ids, labels,
+    // reorder rows; src/algorithm/ivf/ivf.cpp:990-1056, src/algorithm/bruteforce/bruteforce.cpp:685-705):
+    // codes are stored and reloaded verbatim, so a reloaded index answers bit for bit like the original.
+    virtual Expected<void> Serialize(std::ostream& out) const = 0;
+    virtual Expected<void> Deserialize(std::istream& in) = 0;
     virtual int64_t GetNumElements() const = 0;
     virtual int64_t GetMemoryUsage() const = 0;
     virtual std::string GetIndexType() const = 0;

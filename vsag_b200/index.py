@@ -54,6 +54,9 @@ def _lib():
                                                        C.c_void_p, C.c_uint64, C.c_int64, C.POINTER(_SearchResult)]
         lib.vsag_index_remove.restype = _Error
         lib.vsag_index_remove.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32)]
+        for fn in (lib.vsag_serialize_file, lib.vsag_deserialize_file):
+            fn.restype = _Error
+            fn.argtypes = [C.c_void_p, C.c_char_p]
         lib.vsag_index_get_num_elements.restype = C.c_int64
         lib.vsag_index_get_num_elements.argtypes = [C.c_void_p]
         _bound = True
@@ -132,6 +135,14 @@ class Index:
         removed = C.c_uint32(0)
         _check(_lib().vsag_index_remove(self._h, ids.ctypes.data, ids.size, C.byref(removed)))
         return int(removed.value)
+
+    def serialize_file(self, path: str) -> None:
+        """vsag_serialize_file: the whole index (model, lists, labels, removed ids) to one file."""
+        _check(_lib().vsag_serialize_file(self._h, str(path).encode()))
+
+    def deserialize_file(self, path: str) -> None:
+        """vsag_deserialize_file into an empty index created with the same parameters."""
+        _check(_lib().vsag_deserialize_file(self._h, str(path).encode()))
 
     def knn_search_batch(self, vectors, k: int, parameters: str = "{}"):
         """nq queries -> ids[nq, k], dists[nq, k] padded with -1 / +inf."""
