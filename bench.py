@@ -48,11 +48,11 @@ TRAIN_ROWS = 64 * NLIST          # the reference's default train_sample_count: m
 KMEANS_ITERS = 25                # hard-coded in IVFNearestPartition::Train
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel's two launches per step, from the ncu
-# capture of the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 106.1 MB for the
-# first phase, 11.1 MB for the second), scaled by 5 to the 10,000,000-row workload: the traffic is one
+# capture of the 2,000,000-row case (profiles/ivf_sq8_scan_kernel_2M_set_full.md: 103.7 MB for the
+# first phase, 10.7 MB for the second), scaled by 5 to the 10,000,000-row workload: the traffic is one
 # pass over the codes of the lists that survive pruning plus the partial-result slots; the scaled-down
 # case keeps the rows per mixture component and per list, so both grow with the row count.
-SCAN_TRAFFIC_BYTES = 5 * (106.1e6 + 11.1e6)
+SCAN_TRAFFIC_BYTES = 5 * (103.7e6 + 10.7e6)
 
 
 def env_int(name: str, default: int) -> int:
