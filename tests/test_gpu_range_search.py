@@ -1,0 +1,73 @@
+"""RangeSearch through the factory API (include/vsag/index.h:380-397): the answer is the k-nearest
+answer cut at the radius, as in the reference's range mode (bruteforce.cpp:388-545,
+flat_bucket_searcher.cpp:105-137); checked against the oracle's exact search, like the reference's
+TestRangeSearch (tests/test_index.cpp) checks radius and limit."""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import pytest
+
+from conftest import mixture
+
+pytestmark = pytest.mark.gpu
+
+
+def params(dim, metric="l2", **index_param):
+    return json.dumps({"dtype": "float32", "metric_type": metric, "dim": dim, "index_param": index_param})
+
+
+@pytest.mark.parametrize("name,index_param,search", [
+    ("brute_force", dict(base_quantization_type="fp32"), {}),
+    ("ivf", dict(buckets_count=12, base_quantization_type="fp32"), {"ivf": {"scan_buckets_count": 12}}),
+])
+def test_range_is_knn_cut_at_the_radius(oracle, name, index_param, search):
+    from vsag_b200.index import Index, VsagError
+
+    n, dim = 3000, 32
+    base = mixture(21, n, dim, 12, 0.1)
+    queries = mixture(22, 20, dim, 12, 0.1)
+    ids = np.arange(n, dtype=np.int64) + 50
+    index = Index(name, params(dim, **index_param))
+    index.build(base, ids, n, dim)
+    sp = json.dumps(search)
+    truth_i, truth_d = oracle.bf_search_fp32(base, queries, 600)
+    for qi in range(len(queries)):
+        d = truth_d[qi]
+        for want_count in (0, 1, 7, 100, 300):
+            # a radius strictly between two neighbouring distances
+            radius = float(d[0]) * 0.5 if want_count == 0 else float((d[want_count - 1] + d[want_count]) / 2)
+            got_i, got_d = index.range_search(queries[qi], radius, -1, sp)
+            assert len(got_i) == want_count
+            assert np.array_equal(got_d, d[:want_count])
+            assert set(got_i.tolist()) == set((truth_i[qi][:want_count] + 50).tolist())
+            lim_i, lim_d = index.range_search(queries[qi], radius, 5, sp)       # the nearest five of them
+            assert np.array_equal(lim_d, d[:min(5, want_count)])
+    wide = float(truth_d[0][599])
+    with pytest.raises(VsagError, match="limited_size"):                           # more than 512 in range
+        index.range_search(queries[0], wide, -1, sp)
+    got_i, got_d = index.range_search(queries[0], wide, 40, sp)
+    assert np.array_equal(got_d, truth_d[0][:40])
+    for bad in (dict(radius=-1.0, k=5), dict(radius=float("nan"), k=5), dict(radius=1.0, k=0)):
+        with pytest.raises(VsagError) as e:
+            index.range_search(queries[0], bad["radius"], bad["k"], sp)
+        assert e.value.code == -3
+    assert len(Index(name, params(dim, **index_param)).range_search(queries[0], 1.0, 5, sp)[0]) == 0   # empty index
+
+
+def test_range_search_skips_removed_vectors(oracle):
+    from vsag_b200.index import Index
+
+    n, dim = 1000, 16
+    base = mixture(23, n, dim, 6, 0.1)
+    ids = np.arange(n, dtype=np.int64)
+    index = Index("brute_force", params(dim))
+    index.build(base, ids, n, dim)
+    _, d = oracle.bf_search_fp32(base, base[:1], 20)
+    radius = float(d[0][9] + d[0][10]) / 2
+    before, _ = index.range_search(base[0], radius, -1)
+    assert len(before) == 10 and before[0] == 0
+    index.remove(before[:3])
+    after, _ = index.range_search(base[0], radius, -1)
+    assert after.tolist() == before[3:].tolist()

@@ -294,3 +294,34 @@ vsag_deserialize_file(vsag_index_t index, const char* file_path) {
     }
     return success();
 }
+
+// include/vsag/vsag_c_api.h:174-193: k is the largest number of results (at least 1).  Addition: a
+// negative k asks for every vector within the radius, as Index::RangeSearch does with a negative
+// limited_size; the result arrays then need room for 512 entries (more in-radius vectors are an error).
+VSAG_C_EXPORT Error_t
+vsag_index_range_search(vsag_index_t index, const float* query, uint64_t dim, float radius, int64_t k,
+                        const char* parameters, SearchResult_t* search_result) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (query == nullptr || search_result == nullptr || search_result->ids == nullptr ||
+        search_result->dists == nullptr) {
+        return make_error(-static_cast<int>(vsag::ErrorType::INVALID_ARGUMENT), "query or search_result is NULL");
+    }
+    if (k == 0) {
+        return make_error(-static_cast<int>(vsag::ErrorType::INVALID_ARGUMENT), "k must not be 0");
+    }
+    auto q = borrow(query, nullptr, dim, 1);
+    auto r = box->index->RangeSearch(q, radius, parameters == nullptr ? "" : parameters, k);
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    const int64_t to_write = k > 0 ? std::min<int64_t>(r.value()->GetDim(), k) : r.value()->GetDim();
+    for (int64_t i = 0; i < to_write; ++i) {
+        search_result->ids[i] = r.value()->GetIds()[i];
+        search_result->dists[i] = r.value()->GetDistances()[i];
+    }
+    search_result->count = to_write;
+    return success();
+}

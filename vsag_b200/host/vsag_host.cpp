@@ -316,6 +316,58 @@ pack_result(int64_t* ids, float* dists, int64_t nq, int64_t k, const std::string
     return result;
 }
 
+// RangeSearch on top of the k-nearest search (range mode of BruteForce::SearchWithRequest,
+// src/algorithm/bruteforce/bruteforce.cpp:388-545, and of FlatBucketSearcher,
+// src/algorithm/ivf/flat_bucket_searcher.cpp:105-137): both keep a heap of limited_size entries (all
+// vectors when it is negative) and push what lies within the radius, so the answer is the nearest
+// limited_size of the in-radius vectors, ascending.  That is the k-nearest answer cut at the radius.
+// Without a limit k grows until the answer is complete; past RANGE_K_MAX in-radius vectors the caller
+// has to pass limited_size.  `slack` is what the reference adds to the radius (THRESHOLD_ERROR for
+// IVF, src/impl/searcher/basic_searcher.h:39; nothing for BruteForce).
+constexpr int64_t RANGE_K_MAX = 512;
+
+template <typename Knn>
+DatasetPtr
+range_over_knn(Knn&& knn, const DatasetPtr& query, int64_t n_live, float radius, float slack, int64_t limited_size) {
+    check_argument(query != nullptr, "query is null");
+    check_argument(query->GetNumElements() == 1, "query dataset should contain 1 vector only");
+    check_argument(std::isfinite(radius), "radius must be finite");
+    check_argument(radius >= 0.0f, "radius must be non-negative");
+    check_argument(limited_size != 0, "limited_size must be greater than 0 or less than 0");
+    if (n_live == 0) {
+        return make_empty_result();
+    }
+    int64_t k = limited_size > 0 ? std::min(limited_size, n_live) : std::min<int64_t>(64, n_live);
+    for (;;) {
+        Expected<DatasetPtr> r = knn(k);
+        if (!r.has_value()) {
+            fail(r.error().type, r.error().message);
+        }
+        const DatasetPtr& found = r.value();
+        const int64_t got = found->GetDim();
+        int64_t inside = 0;
+        while (inside < got && found->GetDistances()[inside] <= radius + slack) {
+            ++inside;
+        }
+        const bool complete = limited_size > 0 || inside < got || got < k || k >= n_live;
+        if (!complete && k < RANGE_K_MAX) {
+            k = std::min({k * 8, RANGE_K_MAX, n_live});
+            continue;
+        }
+        if (!complete) {
+            fail(ErrorType::INVALID_ARGUMENT, "more than " + std::to_string(RANGE_K_MAX) +
+                                                  " vectors lie within the radius: pass limited_size");
+        }
+        auto* ids = new int64_t[static_cast<size_t>(std::max<int64_t>(inside, 1))];
+        auto* dists = new float[static_cast<size_t>(std::max<int64_t>(inside, 1))];
+        std::copy(found->GetIds(), found->GetIds() + inside, ids);
+        std::copy(found->GetDistances(), found->GetDistances() + inside, dists);
+        auto result = Dataset::Make()->NumElements(1)->Dim(inside)->Ids(ids)->Distances(dists)->Owner(true);
+        result->Statistics(found->GetStatistics());
+        return result;
+    }
+}
+
 // A random orthogonal matrix with determinant +1, standing in for
 // RandomOrthogonalMatrix::GenerateRandomOrthogonalMatrix (src/impl/transform/
 // random_orthogonal_transformer.cpp:98-149): Gaussian entries from a seeded mt19937, then
@@ -557,6 +609,15 @@ public:
             check_status(remove_labels(ids.data(), ids.size(), &removed));
             removed_labels_.insert(removed_labels_.end(), ids.begin(), ids.end());
             return static_cast<uint32_t>(removed);
+        });
+    }
+
+    Expected<DatasetPtr>
+    RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                int64_t limited_size) const override {
+        return safe_call<DatasetPtr>([&]() {
+            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, nullptr); }, query,
+                                  GetNumElements(), radius, 2e-6f, limited_size);
         });
     }
 
@@ -904,6 +965,15 @@ public:
             check_status(remove_labels(ids.data(), ids.size(), &removed));
             removed_labels_.insert(removed_labels_.end(), ids.begin(), ids.end());
             return static_cast<uint32_t>(removed);
+        });
+    }
+
+    Expected<DatasetPtr>
+    RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                int64_t limited_size) const override {
+        return safe_call<DatasetPtr>([&]() {
+            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, nullptr); }, query,
+                                  GetNumElements(), radius, 0.0f, limited_size);
         });
     }
 

@@ -1,6 +1,6 @@
 // Host-side mirror of the part of VSAG's public API that the accelerated path sits behind:
 // vsag::Factory::CreateIndex("ivf" | "brute_force", json), Index::{Build, Train, Add, KnnSearch,
-// Remove, Serialize, Deserialize, GetNumElements, GetMemoryUsage} and the Dataset builder (reference: include/vsag/factory.h:47-50,
+// RangeSearch, Remove, Serialize, Deserialize, GetNumElements, GetMemoryUsage} and the Dataset builder (reference: include/vsag/factory.h:47-50,
 // include/vsag/index.h:126-303, include/vsag/dataset.h:135-511, include/vsag/errors.h:26-48).
 // Same names, argument meaning and error behaviour, written from scratch over the C ABI of
 // include/vsag_b200.h; no exception crosses these calls.
@@ -157,6 +157,11 @@ public:
                                            BitsetPtr invalid) const = 0;
     virtual Expected<DatasetPtr> KnnSearch(const DatasetPtr& query, int64_t k, const std::string& parameters,
                                            const std::function<bool(int64_t)>& filter) const = 0;
+    // Every vector within `radius` of the one query, nearest first; limited_size >= 1 keeps the nearest
+    // limited_size of them, a negative one keeps all, 0 is an error (include/vsag/index.h:380-397).
+    // NumElements = 1, Dim = results found.
+    virtual Expected<DatasetPtr> RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                                             int64_t limited_size = -1) const = 0;
     // RemoveMode::MARK_REMOVE (include/vsag/index.h:186-200): the vectors stay stored but are never
     // returned again; the result is the number of ids found and newly marked.
     virtual Expected<uint32_t> Remove(const std::vector<int64_t>& ids) = 0;

@@ -54,6 +54,9 @@ def _lib():
                                                        C.c_void_p, C.c_uint64, C.c_int64, C.POINTER(_SearchResult)]
         lib.vsag_index_remove.restype = _Error
         lib.vsag_index_remove.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32)]
+        lib.vsag_index_range_search.restype = _Error
+        lib.vsag_index_range_search.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_float, C.c_int64, C.c_char_p,
+                                                C.POINTER(_SearchResult)]
         for fn in (lib.vsag_serialize_file, lib.vsag_deserialize_file):
             fn.restype = _Error
             fn.argtypes = [C.c_void_p, C.c_char_p]
@@ -135,6 +138,18 @@ class Index:
         removed = C.c_uint32(0)
         _check(_lib().vsag_index_remove(self._h, ids.ctypes.data, ids.size, C.byref(removed)))
         return int(removed.value)
+
+    def range_search(self, vector, radius: float, k: int, parameters: str = "{}"):
+        """vsag_index_range_search: the nearest k of the vectors within `radius`, ascending; k < 0 asks
+        for all of them (at most 512)."""
+        vector = np.ascontiguousarray(vector, np.float32).reshape(-1)
+        room = k if k > 0 else 512
+        ids = np.empty(room, np.int64)
+        dists = np.empty(room, np.float32)
+        res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
+        _check(_lib().vsag_index_range_search(self._h, vector.ctypes.data, vector.size, radius, k, parameters.encode(),
+                                              C.byref(res)))
+        return ids[: res.count].copy(), dists[: res.count].copy()
 
     def serialize_file(self, path: str) -> None:
         """vsag_serialize_file: the whole index (model, lists, labels, removed ids) to one file."""
