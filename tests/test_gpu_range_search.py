@@ -71,3 +71,35 @@ def test_range_search_skips_removed_vectors(oracle):
     index.remove(before[:3])
     after, _ = index.range_search(base[0], radius, -1)
     assert after.tolist() == before[3:].tolist()
+
+
+@pytest.mark.parametrize("name,index_param,search", [
+    ("brute_force", dict(base_quantization_type="fp32"), {}),
+    ("ivf", dict(buckets_count=8, base_quantization_type="fp32"), {"ivf": {"scan_buckets_count": 8}}),
+])
+def test_with_filter_functions_keep_valid_ids_only(oracle, name, index_param, search):
+    """vsag_index_knn_search_with_filter / _range_search_with_filter: the callback says which ids are
+    valid (VsagFilterWrapper::CheckValid, src/vsag_c_api.cpp:337-343)."""
+    from vsag_b200.index import Index
+
+    n, dim, k = 2000, 24, 10
+    base = mixture(24, n, dim, 8, 0.1)
+    queries = mixture(25, 10, dim, 8, 0.1)
+    ids = np.arange(n, dtype=np.int64) * 3
+    index = Index(name, params(dim, **index_param))
+    index.build(base, ids, n, dim)
+    sp = json.dumps(search)
+    valid = lambda i: i % 2 == 0            # noqa: E731
+    keep = np.array([valid(int(i)) for i in ids])
+    truth_i, truth_d = oracle.bf_search_fp32(base[keep], queries, 40)
+    kept_ids = ids[keep]
+    for qi in range(len(queries)):
+        got_i, got_d = index.knn_search_with_filter(queries[qi], k, sp, valid)
+        assert np.array_equal(got_d, truth_d[qi][:k])
+        assert set(got_i.tolist()) == set(kept_ids[truth_i[qi][:k]].tolist())
+        radius = float(truth_d[qi][24] + truth_d[qi][25]) / 2
+        rng_i, rng_d = index.range_search_with_filter(queries[qi], radius, 30, sp, valid)
+        assert np.array_equal(rng_d, truth_d[qi][:25])
+        assert set(rng_i.tolist()) == set(kept_ids[truth_i[qi][:25]].tolist())
+        few_i, few_d = index.range_search_with_filter(queries[qi], radius, 4, sp, valid)
+        assert np.array_equal(few_d, truth_d[qi][:4])

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstring>
 #include <fstream>
+#include <functional>
 
 #include "vsag_host.h"
 
@@ -20,6 +21,8 @@ typedef struct Error {
 } Error_t;
 
 typedef void* vsag_index_t;
+
+typedef bool (*FilterFunc_t)(int64_t id);   // true = the id may be returned (Filter::CheckValid)
 
 typedef struct SearchResult {
     float* dists;
@@ -324,4 +327,66 @@ vsag_index_range_search(vsag_index_t index, const float* query, uint64_t dim, fl
     }
     search_result->count = to_write;
     return success();
+}
+
+namespace {
+
+Error_t
+write_result(const vsag::Expected<vsag::DatasetPtr>& r, int64_t k, SearchResult_t* search_result) {
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    const int64_t to_write = std::min<int64_t>(r.value()->GetDim(), k);
+    for (int64_t i = 0; i < to_write; ++i) {
+        search_result->ids[i] = r.value()->GetIds()[i];
+        search_result->dists[i] = r.value()->GetDistances()[i];
+    }
+    search_result->count = to_write;
+    return success();
+}
+
+}  // namespace
+
+// include/vsag/vsag_c_api.h:152-172 and :195-216: `filter` says which ids are valid.
+VSAG_C_EXPORT Error_t
+vsag_index_knn_search_with_filter(vsag_index_t index, const float* query, uint64_t dim, int64_t k,
+                                  const char* parameters, FilterFunc_t filter, SearchResult_t* search_result) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (search_result == nullptr) {
+        return make_error(-1, "search result is NULL");
+    }
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (k <= 0) {
+        return make_error(-3, "knn_search requires k >= 1");
+    }
+    auto q = borrow(query, nullptr, dim, 1);
+    std::function<bool(int64_t)> out;
+    if (filter != nullptr) {
+        out = [filter](int64_t id) { return !filter(id); };
+    }
+    return write_result(box->index->KnnSearch(q, k, parameters == nullptr ? "{}" : parameters, out), k, search_result);
+}
+
+VSAG_C_EXPORT Error_t
+vsag_index_range_search_with_filter(vsag_index_t index, const float* query, uint64_t dim, float radius, int64_t k,
+                                    const char* parameters, FilterFunc_t filter, SearchResult_t* search_result) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (search_result == nullptr) {
+        return make_error(-1, "search result is NULL");
+    }
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (k <= 0) {
+        return make_error(-3, "range_search requires k >= 1 as result cap");
+    }
+    auto q = borrow(query, nullptr, dim, 1);
+    std::function<bool(int64_t)> out;
+    if (filter != nullptr) {
+        out = [filter](int64_t id) { return !filter(id); };
+    }
+    return write_result(box->index->RangeSearch(q, radius, parameters == nullptr ? "{}" : parameters, out, k), k,
+                        search_result);
 }

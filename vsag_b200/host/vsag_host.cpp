@@ -615,8 +615,40 @@ public:
     Expected<DatasetPtr>
     RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
                 int64_t limited_size) const override {
+        return range_impl(query, radius, parameters, limited_size, nullptr);
+    }
+
+    Expected<DatasetPtr>
+    RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters, BitsetPtr invalid,
+                int64_t limited_size) const override {
+        if (invalid == nullptr || invalid->Words().empty()) {
+            return range_impl(query, radius, parameters, limited_size, nullptr);
+        }
+        vb200_filter f{invalid->Words().data(), invalid->Words().size() * 64, nullptr, 0};
+        return range_impl(query, radius, parameters, limited_size, &f);
+    }
+
+    Expected<DatasetPtr>
+    RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                const std::function<bool(int64_t)>& filter, int64_t limited_size) const override {
+        if (!filter) {
+            return range_impl(query, radius, parameters, limited_size, nullptr);
+        }
+        std::vector<uint32_t> deny((labels_host_.size() + 31) / 32, 0);
+        for (size_t i = 0; i < labels_host_.size(); ++i) {
+            if (filter(labels_host_[i])) {
+                deny[i >> 5] |= 1u << (i & 31);
+            }
+        }
+        vb200_filter f{nullptr, 0, deny.data(), labels_host_.size()};
+        return range_impl(query, radius, parameters, limited_size, &f);
+    }
+
+    Expected<DatasetPtr>
+    range_impl(const DatasetPtr& query, float radius, const std::string& parameters, int64_t limited_size,
+               const vb200_filter* filter) const {
         return safe_call<DatasetPtr>([&]() {
-            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, nullptr); }, query,
+            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, filter); }, query,
                                   GetNumElements(), radius, 2e-6f, limited_size);
         });
     }
@@ -971,8 +1003,40 @@ public:
     Expected<DatasetPtr>
     RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
                 int64_t limited_size) const override {
+        return range_impl(query, radius, parameters, limited_size, nullptr);
+    }
+
+    Expected<DatasetPtr>
+    RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters, BitsetPtr invalid,
+                int64_t limited_size) const override {
+        if (invalid == nullptr || invalid->Words().empty()) {
+            return range_impl(query, radius, parameters, limited_size, nullptr);
+        }
+        vb200_filter f{invalid->Words().data(), invalid->Words().size() * 64, nullptr, 0};
+        return range_impl(query, radius, parameters, limited_size, &f);
+    }
+
+    Expected<DatasetPtr>
+    RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                const std::function<bool(int64_t)>& filter, int64_t limited_size) const override {
+        if (!filter) {
+            return range_impl(query, radius, parameters, limited_size, nullptr);
+        }
+        std::vector<uint32_t> deny((labels_host_.size() + 31) / 32, 0);
+        for (size_t i = 0; i < labels_host_.size(); ++i) {
+            if (filter(labels_host_[i])) {
+                deny[i >> 5] |= 1u << (i & 31);
+            }
+        }
+        vb200_filter f{nullptr, 0, deny.data(), labels_host_.size()};
+        return range_impl(query, radius, parameters, limited_size, &f);
+    }
+
+    Expected<DatasetPtr>
+    range_impl(const DatasetPtr& query, float radius, const std::string& parameters, int64_t limited_size,
+               const vb200_filter* filter) const {
         return safe_call<DatasetPtr>([&]() {
-            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, nullptr); }, query,
+            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, filter); }, query,
                                   GetNumElements(), radius, 0.0f, limited_size);
         });
     }

@@ -162,6 +162,12 @@ public:
     // NumElements = 1, Dim = results found.
     virtual Expected<DatasetPtr> RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
                                              int64_t limited_size = -1) const = 0;
+    // The same with a pre-filter, as for KnnSearch (include/vsag/index.h:399-441).
+    virtual Expected<DatasetPtr> RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                                             BitsetPtr invalid, int64_t limited_size = -1) const = 0;
+    virtual Expected<DatasetPtr> RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
+                                             const std::function<bool(int64_t)>& filter,
+                                             int64_t limited_size = -1) const = 0;
     // RemoveMode::MARK_REMOVE (include/vsag/index.h:186-200): the vectors stay stored but are never
     // returned again; the result is the number of ids found and newly marked.
     virtual Expected<uint32_t> Remove(const std::vector<int64_t>& ids) = 0;

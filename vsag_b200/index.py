@@ -54,6 +54,12 @@ def _lib():
                                                        C.c_void_p, C.c_uint64, C.c_int64, C.POINTER(_SearchResult)]
         lib.vsag_index_remove.restype = _Error
         lib.vsag_index_remove.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32)]
+        lib.vsag_index_knn_search_with_filter.restype = _Error
+        lib.vsag_index_knn_search_with_filter.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int64, C.c_char_p,
+                                                          _FILTER_FUNC, C.POINTER(_SearchResult)]
+        lib.vsag_index_range_search_with_filter.restype = _Error
+        lib.vsag_index_range_search_with_filter.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_float, C.c_int64,
+                                                            C.c_char_p, _FILTER_FUNC, C.POINTER(_SearchResult)]
         lib.vsag_index_range_search.restype = _Error
         lib.vsag_index_range_search.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_float, C.c_int64, C.c_char_p,
                                                 C.POINTER(_SearchResult)]
@@ -64,6 +70,9 @@ def _lib():
         lib.vsag_index_get_num_elements.argtypes = [C.c_void_p]
         _bound = True
     return lib
+
+
+_FILTER_FUNC = C.CFUNCTYPE(C.c_bool, C.c_int64)   # FilterFunc_t: True = the id may be returned
 
 
 def _check(err: _Error) -> None:
@@ -149,6 +158,28 @@ class Index:
         res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
         _check(_lib().vsag_index_range_search(self._h, vector.ctypes.data, vector.size, radius, k, parameters.encode(),
                                               C.byref(res)))
+        return ids[: res.count].copy(), dists[: res.count].copy()
+
+    def knn_search_with_filter(self, vector, k: int, parameters: str, valid):
+        """vsag_index_knn_search_with_filter: `valid(id)` says which ids may be returned."""
+        vector = np.ascontiguousarray(vector, np.float32).reshape(-1)
+        ids = np.empty(max(k, 1), np.int64)
+        dists = np.empty(max(k, 1), np.float32)
+        res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
+        cb = _FILTER_FUNC(lambda i: bool(valid(i)))
+        _check(_lib().vsag_index_knn_search_with_filter(self._h, vector.ctypes.data, vector.size, k,
+                                                        parameters.encode(), cb, C.byref(res)))
+        return ids[: res.count].copy(), dists[: res.count].copy()
+
+    def range_search_with_filter(self, vector, radius: float, k: int, parameters: str, valid):
+        """vsag_index_range_search_with_filter: the nearest k valid vectors within `radius`."""
+        vector = np.ascontiguousarray(vector, np.float32).reshape(-1)
+        ids = np.empty(max(k, 1), np.int64)
+        dists = np.empty(max(k, 1), np.float32)
+        res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
+        cb = _FILTER_FUNC(lambda i: bool(valid(i)))
+        _check(_lib().vsag_index_range_search_with_filter(self._h, vector.ctypes.data, vector.size, radius, k,
+                                                          parameters.encode(), cb, C.byref(res)))
         return ids[: res.count].copy(), dists[: res.count].copy()
 
     def serialize_file(self, path: str) -> None:
