@@ -105,7 +105,10 @@ def test_kmeans_train_follows_oracle(engine, oracle):
     # assignments are bit-exact given equal centroids; centroids carry fp32 summation-order noise
     # from one iteration to the next, so a handful of boundary points may flip.
     assert np.mean(got_l == want_l) > 0.999
-    np.testing.assert_allclose(got_c, want_c, rtol=1e-3, atol=1e-4)
+    # a cluster of about 470 rows that gains or loses one boundary row moves by |row - centroid| / 470,
+    # about 1e-3 per coordinate here; the clusters without a flip agree to summation noise
+    np.testing.assert_allclose(got_c, want_c, rtol=1e-3, atol=5e-3)
+    assert np.median(np.abs(got_c - want_c)) < 1e-5
     assert got_err == pytest.approx(want_err, rel=1e-4)
     # size-independent properties: assigning against the returned centroids is a fixed point of
     # the label step, and every label is in range
