@@ -64,3 +64,28 @@ def test_argument_validation_needs_no_device(engine):
     assert code == -3 and msg
     assert engine.rabitq_code_size(960) == 128
     assert engine.rabitq_code_size(7) == 12
+
+
+def test_reference_named_c_functions_are_exported():
+    """The functions a program written against include/vsag/vsag_c_api.h links to for this path."""
+    from vsag_b200 import _capi
+
+    lib = C.CDLL(str(_capi.lib_path()))
+    names = ["vsag_index_factory", "vsag_index_destroy", "vsag_index_build", "vsag_index_add", "vsag_index_train",
+             "vsag_index_knn_search", "vsag_index_knn_search_with_filter", "vsag_index_range_search",
+             "vsag_index_range_search_with_filter", "vsag_serialize_file", "vsag_deserialize_file"]
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, f"not exported: {missing}"
+
+
+def test_factory_rejects_bad_parameters_without_a_device():
+    """Parameter checks run before any device work: unknown index names and keys fail the same way
+    with or without a GPU (Factory::CreateIndex, src/factory/index_registry.cpp)."""
+    from vsag_b200.index import Index, VsagError
+
+    with pytest.raises(VsagError):
+        Index("hnsw_like_nothing", '{"dtype": "float32", "metric_type": "l2", "dim": 8}')
+    with pytest.raises(VsagError):
+        Index("ivf", '{"dtype": "float32", "metric_type": "l2", "dim": 8, "index_param": {"no_such_key": 1}}')
+    with pytest.raises(VsagError):
+        Index("ivf", "this is not json")
