@@ -102,6 +102,11 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_threads(n: int) -> None:
+    """Worker threads of the oracle's parallel loops (default: what OpenMP takes from the environment)."""
+    lib().orc_set_threads(C.c_int(int(n)))
+
+
 # ---- generators --------------------------------------------------------------------------------
 def gen_uniform(seed: int, count: int, lo: float = 0.0, hi: float = 1.0) -> np.ndarray:
     """count floats from std::mt19937(seed) + std::uniform_real_distribution<float>(lo, hi)."""

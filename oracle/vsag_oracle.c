@@ -1124,6 +1124,20 @@ orc_ivf_rabitq_search(const uint8_t* codes,
     }
 }
 
+/* Number of worker threads of the parallel loops from here on.  The benchmark's CPU arm sets it to the
+ * cores the process may run on, so that an OMP_NUM_THREADS in the environment (torchrun exports 1)
+ * does not decide how many cores the baseline gets. */
+ORC_API void
+orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) {
+        omp_set_num_threads(n);
+    }
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int
 orc_num_threads(void) {
 #ifdef _OPENMP

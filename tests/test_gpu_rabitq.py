@@ -24,13 +24,29 @@ def test_encode_and_query_bit_exact(engine, oracle, dim):
                           oracle.rabitq_process_query(q, rot, centroid))
 
 
-def test_train_centroid_close_to_oracle(engine, oracle):
-    dim = 48
-    x = mixture(3, 20_000, dim, 16, 0.05, lo=0.0, hi=1.0, clip=True)
+@pytest.mark.parametrize("n,dim", [(20_000, 48), (1003, 7), (5, 100), (70_001, 960)])
+def test_train_centroid_bit_equal_to_oracle(engine, oracle, n, dim):
+    x = mixture(3, n, dim, 16, 0.05, lo=0.0, hi=1.0, clip=True)
     rot = oracle.random_rotation(dim, seed=1)
-    # the reference keeps a running fp32 sum over the rows (rabitq_quantizer.cpp:229-243); the
-    # engine sums in double, so the two agree to fp32 rounding of that running sum
-    np.testing.assert_allclose(engine.rabitq_train(x, rot), oracle.rabitq_train(x, rot), rtol=1e-4, atol=1e-5)
+    # the reference keeps a running fp32 sum over the rows in their order (rabitq_quantizer.cpp:229-243);
+    # the engine adds in that order too, so the trained centroid is the reference's bit for bit
+    assert np.array_equal(engine.rabitq_train(x, rot), oracle.rabitq_train(x, rot))
+
+
+def test_engine_trained_index_reproduces_oracle_codes(engine, oracle):
+    """An index trained by the engine itself (not given a centroid) holds the codes the oracle encodes
+    with its own trained centroid: training and encoding are both bit-exact."""
+    dim, n, nlist = 64, 6000, 12
+    x = mixture(9, n, dim, nlist, 0.05, lo=0.0, hi=1.0, clip=True)
+    rot = oracle.random_rotation(dim, seed=9)
+    ix = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_RABITQ)
+    ix.set_rabitq_rotation(rot)
+    ix.train(x, iters=3)
+    centroid = oracle.rabitq_train(x, rot)
+    assert np.array_equal(ix.get_rabitq_centroid(), centroid)
+    ix.add(x, np.arange(n, dtype=np.int64))
+    sizes, codes, inner = ix.get_lists()
+    assert np.array_equal(codes, oracle.rabitq_encode(x, rot, centroid)[inner])
 
 
 def build_rabitq(engine, oracle, n, dim, nlist, use_reorder, seed):

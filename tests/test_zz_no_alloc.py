@@ -23,7 +23,7 @@ def _assign_noalloc(lib, x_dev, c_dev, labels_dev):
                                            c_dev.shape[0], C.c_void_p(labels_dev.data_ptr()))
 
 
-def test_noalloc_assignment_matches_regular_entry_point(engine):
+def test_noalloc_assignment_matches_regular_entry_point(engine, oracle):
     import torch
 
     from vsag_b200 import _capi
@@ -34,14 +34,41 @@ def test_noalloc_assignment_matches_regular_entry_point(engine):
     x_dev = torch.from_numpy(x).cuda()
     labels_dev = torch.empty(x.shape[0], dtype=torch.int32, device="cuda")
     # two calls in a row with different centroid counts: the second must not be disturbed by what
-    # the first left in the shared scratch array (labels are integers: exact equality)
+    # the first left in the shared scratch array (labels are integers: exact equality), and both must
+    # give the labels of the regular entry point and of the CPU oracle
     for k in (300, 17):
         centroids = x[:k].copy()
         want = engine.kmeans_assign(x, centroids)
+        want_oracle, _ = oracle.kmeans_assign(x, centroids)
         c_dev = torch.from_numpy(centroids).cuda()
         labels_dev.fill_(-7)
         assert _assign_noalloc(lib, x_dev, c_dev, labels_dev) == 0, _capi.last_error()
-        assert np.array_equal(labels_dev.cpu().numpy(), want)
+        got = labels_dev.cpu().numpy()
+        assert np.array_equal(got, want)
+        assert np.array_equal(got, want_oracle)
+
+
+def test_noalloc_call_leaves_device_memory_as_it_found_it(engine):
+    """What the entry point exists for: free device memory (cudaMemGetInfo, as torch reports it) is the
+    same before and after a call -- nothing was taken from the allocator, nothing given back."""
+    import torch
+
+    from vsag_b200 import _capi
+
+    lib = _capi.load()
+    x = mixture(12, 4096, 32, 64, 0.1)
+    x_dev = torch.from_numpy(x).cuda()
+    c_dev = x_dev[:64].clone()
+    labels_dev = torch.empty(x.shape[0], dtype=torch.int32, device="cuda")
+    # the first call on a device looks up the scratch array's address (module load happens here at the latest)
+    assert _assign_noalloc(lib, x_dev, c_dev, labels_dev) == 0, _capi.last_error()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert _assign_noalloc(lib, x_dev, c_dev, labels_dev) == 0, _capi.last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
 
 
 def test_noalloc_rejects_what_it_cannot_serve(engine):

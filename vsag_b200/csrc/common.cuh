@@ -168,6 +168,8 @@ struct PinnedBuf {
 
 // True when `p` points into device (or managed) memory; host memory of any kind otherwise.
 bool is_device_pointer(const void* p);
+// True when `p` is device memory of the device current on the calling thread (or managed memory).
+bool is_pointer_on_current_device(const void* p);
 
 // A read-only view of caller data on the device: device pointers are used in place, host
 // pointers are copied into an owned buffer on the current stream.

@@ -33,18 +33,22 @@ current_stream() {
 
 int
 sm_count() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0;
-        cudaDeviceProp prop;
-        if (cudaGetDevice(&dev) == cudaSuccess && cudaGetDeviceProperties(&prop, dev) == cudaSuccess) {
-            cached = prop.multiProcessorCount;
-        } else {
-            cudaGetLastError();
-            cached = 148;
-        }
+    // per device ordinal: grids are sized for the device the calling thread has current
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return 148;
     }
-    return cached;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 148;
+        }
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
 }
 
 bool
@@ -56,6 +60,20 @@ is_device_pointer(const void* p) {
         return false;
     }
     return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+bool
+is_pointer_on_current_device(const void* p) {
+    cudaPointerAttributes attr;
+    int dev = -1;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    if (attr.type == cudaMemoryTypeManaged) {
+        return true;
+    }
+    return attr.type == cudaMemoryTypeDevice && attr.device == dev;
 }
 
 // ---------------------------------------------------------------------------------------------

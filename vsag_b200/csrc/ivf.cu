@@ -14,6 +14,7 @@ namespace vb200 {
 
 constexpr uint32_t NONE32 = 0xFFFFFFFFu;
 constexpr uint32_t ROUTE_SLACK = 8;   // extra routing candidates re-scored exactly
+constexpr uint32_t ROUTE_MAX_PER_ROW = 4096;   // approximate candidates a query may bring to the final pick (32 KiB of keys)
 constexpr int SQ8_QT = 16;
 constexpr uint32_t SQ8_SLACK = 16;    // survivors kept beyond k for exact re-scoring
 constexpr int RABITQ_QT = 8;
@@ -45,6 +46,9 @@ struct SearchWorkspace {
     DevBuf<uint64_t> merged;    // SQ8 survivors before exact re-scoring
     DevBuf<float> scores;       // routing score slab
     DevBuf<uint64_t> cand;      // routing candidates
+    DevBuf<float> route_thr;    // [nq] per-query score threshold of the routing pass
+    DevBuf<uint64_t> route_keys;   // [nq][lists][cap] centroids below the threshold, unsorted
+    DevBuf<uint32_t> route_cnt;    // [nq][lists]
     DevBuf<int32_t> probes;     // [nq x nprobe]
     DevBuf<float> probe_dists;
     // pair grouping, one set per scan phase (nearest list first, then the rest)
@@ -112,6 +116,7 @@ struct vb200_ivf {
     // tensor-core routing: the centroids as tiled bf16 hi/lo terms (rebuilt when they change)
     DevBuf<uint16_t> c_hi, c_lo;
     bool c_tiled = false;
+    DevBuf<float> c_max_norm;     // [1] largest centroid norm
     TcWorkspace tc;
     DevBuf<uint32_t> pos_inner;
     DevBuf<int64_t> labels;
@@ -997,6 +1002,133 @@ launch_merge(const uint64_t* part, uint64_t nq, uint64_t per_query, uint32_t k, 
 // ---------------------------------------------------------------------------------------------
 // routing
 // ---------------------------------------------------------------------------------------------
+// out[0] = sqrt(max_j sq[j]); one CTA.
+__global__ void __launch_bounds__(256)
+max_row_norm_kernel(const float* __restrict__ sq, uint32_t n, float* __restrict__ out) {
+    __shared__ float part[8];
+    float m = 0.f;
+    for (uint32_t j = threadIdx.x; j < n; j += blockDim.x) {
+        m = fmaxf(m, sq[j]);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        part[threadIdx.x >> 5] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) {
+            m = fmaxf(m, part[w]);
+        }
+        out[0] = sqrtf(m);
+    }
+}
+
+// thr[q] = the approximate score of query q's ncand-th best centroid among the sampled ones, plus a
+// margin of 1e-3 |q| max|c| that covers the rounding of the tensor-core scores on both sides: at
+// least ncand centroids score below it exactly, so every one of the query's ncand nearest centroids
+// scores below it approximately.  One warp per query.
+__global__ void __launch_bounds__(128)
+route_threshold_kernel(const uint64_t* __restrict__ sample_keys, uint32_t ncand, const float* __restrict__ queries,
+                       uint32_t dim, uint64_t nq, const float* __restrict__ c_max_norm, float* __restrict__ thr) {
+    const uint64_t q = static_cast<uint64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const uint32_t lane = threadIdx.x & 31;
+    if (q >= nq) {
+        return;
+    }
+    float qq = 0.f;
+    for (uint32_t d = lane; d < dim; d += 32) {
+        const float x = __ldg(queries + q * dim + d);
+        qq = fmaf(x, x, qq);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        qq += __shfl_xor_sync(0xffffffffu, qq, off);
+    }
+    if (lane == 0) {
+        const uint64_t key = sample_keys[q * ncand + ncand - 1];
+        const float worst = key == KEY_INF ? INFINITY : ordered_to_float(static_cast<uint32_t>(key >> 32));
+        thr[q] = worst + 1e-3f * sqrtf(qq) * __ldg(c_max_norm);
+    }
+}
+
+// One CTA per query: gathers the query's centroids below its threshold from their lists, orders them
+// by approximate score, re-scores the ncand best exactly -- L2: FMA chain of (q-c)^2 over d
+// ascending; IP: 1 - chain of q*c (the loop of IVF::route_buckets_only,
+// src/algorithm/ivf/ivf.cpp:1589-1660) -- and writes the nprobe nearest, distance ascending, lower
+// list id first on ties.
+__global__ void __launch_bounds__(256)
+route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids,
+                  const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
+                  uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
+                  float* __restrict__ probe_dists) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ uint32_t s_off[65];
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);                       // [max(lists * cap, 2 * ncand) rounded up]
+    float* qs = reinterpret_cast<float*>(keys + next_pow2(lists * cap > 2 * ncand ? lists * cap : 2 * ncand));
+    const uint64_t q = blockIdx.x;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (uint32_t d = tid; d < dim; d += blockDim.x) {
+        qs[d] = queries[q * dim + d];
+    }
+    if (tid == 0) {
+        uint32_t run = 0;
+        for (uint32_t l = 0; l < lists; ++l) {
+            s_off[l] = run;
+            const uint32_t c = lists_cnt[q * lists + l];
+            run += c < cap ? c : cap;
+        }
+        s_off[lists] = run;
+    }
+    __syncthreads();
+    const uint32_t total = s_off[lists];
+    for (uint32_t l = warp; l < lists; l += blockDim.x >> 5) {
+        const uint32_t beg = s_off[l], c = s_off[l + 1] - beg;
+        const uint64_t* src = lists_keys + (q * lists + l) * cap;
+        for (uint32_t i = lane; i < c; i += 32) {
+            keys[beg + i] = src[i];
+        }
+    }
+    const uint32_t n2 = next_pow2(total < 2 ? 2 : total);
+    for (uint32_t i = total + tid; i < n2; i += blockDim.x) {
+        keys[i] = KEY_INF;
+    }
+    block_bitonic_sort(keys, n2);
+    // exact distances of the ncand best (one chain per candidate, dimensions in ascending order)
+    const uint32_t m2 = next_pow2(ncand < 2 ? 2 : ncand);
+    uint64_t mine = KEY_INF;
+    if (tid < ncand && tid < n2 && keys[tid] != KEY_INF) {
+        const uint32_t list = static_cast<uint32_t>(keys[tid]);
+        const float* c = centroids + static_cast<uint64_t>(list) * dim;
+        float s = 0.f;
+        if (metric == VB200_METRIC_L2) {
+            for (uint32_t d = 0; d < dim; ++d) {
+                const float t = __fsub_rn(qs[d], __ldg(c + d));
+                s = fmaf(t, t, s);
+            }
+        } else {
+            for (uint32_t d = 0; d < dim; ++d) {
+                s = fmaf(qs[d], __ldg(c + d), s);
+            }
+            s = __fsub_rn(1.0f, s);
+        }
+        mine = make_key(s, list);
+    }
+    __syncthreads();
+    if (tid < m2) {
+        keys[tid] = mine;
+    }
+    block_bitonic_sort(keys, m2);
+    for (uint32_t i = tid; i < nprobe; i += blockDim.x) {
+        const uint64_t key = i < m2 ? keys[i] : KEY_INF;
+        const uint64_t o = q * nprobe + i;
+        probes[o] = key == KEY_INF ? -1 : static_cast<int32_t>(static_cast<uint32_t>(key));
+        if (probe_dists != nullptr) {
+            probe_dists[o] = key == KEY_INF ? INFINITY : ordered_to_float(static_cast<uint32_t>(key >> 32));
+        }
+    }
+}
+
 static int
 ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe, int32_t* probes_dev,
                  float* dists_dev) {
@@ -1018,6 +1150,8 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
             VB_TRY(ix->c_hi.reserve(elems));
             VB_TRY(ix->c_lo.reserve(elems));
             VB_TRY(tc_pretile_f32(ix->centroids.ptr, nlist, ix->dim, ix->c_hi.ptr, ix->c_lo.ptr));
+            VB_TRY(ix->c_max_norm.reserve(1));
+            VB_LAUNCH(max_row_norm_kernel, 1, 256, 0, ix->c_sq.ptr, nlist, ix->c_max_norm.ptr);
             ix->c_tiled = true;
         }
         const size_t q_elems = tc_tiled_elems(nq, ix->dim);
@@ -1026,6 +1160,47 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
         VB_TRY(tc_pretile_f32(q_dev, nq, ix->dim, ws.q_hi.ptr, ws.q_lo.ptr));
         TcOperand a{ws.q_hi.ptr, ws.q_lo.ptr, nq, chunks};
         TcOperand b{ix->c_hi.ptr, ix->c_lo.ptr, nlist, chunks};
+        // Large list counts: no score matrix.  The scores against a sample of the centroids (the first
+        // `sample` of them; centroid numbering carries no geometry) give each query a threshold that
+        // at least ncand centroids are known to meet; one pass of the tensor-core kernel over all
+        // centroids then keeps, unsorted, only what scores below it -- about ncand * nlist / sample
+        // per query -- and one small kernel per query orders those and re-scores the best exactly.
+        uint32_t sample = 0;
+        for (uint32_t s = 1024; s <= 4096 && sample == 0; s *= 2) {
+            const uint64_t expected = static_cast<uint64_t>(ncand) * nlist / s;
+            if (4ull * s <= nlist && s >= 4 * ncand && 5 * expected / 2 <= ROUTE_MAX_PER_ROW) {
+                sample = s;
+            }
+        }
+        if (sample != 0 && ncand <= 256) {
+            const float alpha = l2 ? -2.0f : -1.0f;
+            const float* bias = l2 ? ix->c_sq.ptr : nullptr;
+            TcOperand bs{ix->c_hi.ptr, ix->c_lo.ptr, sample, chunks};
+            VB_TRY(ws.scores.reserve(nq * sample));
+            VB_TRY(tc_scores(ix->tc, a, bs, 3, alpha, bias, ws.scores.ptr, sample));
+            VB_TRY(select_rows(ws.scores.ptr, nq, sample, sample, ncand, 0, ws.cand.ptr, ncand));
+            VB_TRY(ws.route_thr.reserve(nq));
+            VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>((nq + 3) / 4), 128, 0, ws.cand.ptr, ncand, q_dev,
+                      ix->dim, nq, ix->c_max_norm.ptr, ws.route_thr.ptr);
+            uint32_t lists = 0, cap = 0;
+            bool overflow = false;
+            const uint32_t expected = static_cast<uint32_t>(static_cast<uint64_t>(ncand) * nlist / sample);
+            VB_TRY(tc_below_threshold(ix->tc, a, b, 3, alpha, bias, ws.route_thr.ptr, expected, ROUTE_MAX_PER_ROW,
+                                      ws.route_keys, ws.route_cnt, &lists, &cap, &overflow));
+            if (!overflow && lists <= 64) {
+                const uint32_t slots = next_pow2(lists * cap > 2 * ncand ? lists * cap : 2 * ncand);
+                const size_t smem = slots * sizeof(uint64_t) + ix->dim * sizeof(float);
+                if (smem > 48 * 1024) {
+                    VB_CUDA(cudaFuncSetAttribute(route_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(smem)));
+                }
+                VB_LAUNCH(route_pick_kernel, static_cast<uint32_t>(nq), 256, smem, q_dev, ix->dim, ix->centroids.ptr,
+                          ws.route_keys.ptr, ws.route_cnt.ptr, lists, cap, ncand, nprobe, ix->metric, probes_dev,
+                          dists_dev);
+                return 0;
+            }
+            // a list overflowed (scores far from what the sample predicted): take the score-matrix path
+        }
         VB_TRY(ws.scores.reserve(nq * ld));
         VB_TRY(tc_scores(ix->tc, a, b, 3, l2 ? -2.0f : -1.0f, l2 ? ix->c_sq.ptr : nullptr, ws.scores.ptr, ld));
         VB_TRY(select_rows(ws.scores.ptr, nq, nlist, ld, ncand, 0, ws.cand.ptr, ncand));
@@ -1169,12 +1344,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     };
     // SQ8 with list pruning: the first phase runs alone, then the pairs its bounds rule out are
     // dropped before the second phase is grouped, so they never become work items.
-    static const bool preprune_enabled = []() {
-        const char* v = std::getenv("VB200_PAIR_PREPRUNE");
-        return !(v != nullptr && v[0] == '0');
-    }();
     const bool pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
-    const bool split_phases = n_phases == 2 && (ws.exchange != nullptr || (pruning && preprune_enabled));
+    const bool split_phases = n_phases == 2 && (ws.exchange != nullptr || pruning);
     VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr));
 
     ScanParams p{};

@@ -685,6 +685,10 @@ vb200_kmeans_assign_noalloc(const float* data_dev, uint64_t count, uint32_t dim,
     VB_CHECK_ARG(is_device_pointer(data_dev) && is_device_pointer(centroids_dev) &&
                      is_device_pointer(labels_dev),
                  "this entry point stages nothing: data, centroids and labels must be device pointers");
+    // the scratch array used below is the current device's copy
+    VB_CHECK_ARG(is_pointer_on_current_device(data_dev) && is_pointer_on_current_device(centroids_dev) &&
+                     is_pointer_on_current_device(labels_dev),
+                 "data, centroids and labels must live on the device that is current on the calling thread");
     float* c_sq = nullptr;
     VB_TRY(noalloc_scratch(&c_sq));
     // Every call rewrites entries [0, k) before reading them, so nothing has to be cleared.

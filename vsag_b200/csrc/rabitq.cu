@@ -8,49 +8,43 @@
 
 namespace vb200 {
 
-// Column sums in double, one thread per column, rows split across blockIdx.y.
-__global__ void
-column_sum_kernel(const float* __restrict__ data, uint64_t count, uint32_t dim, uint64_t rows_per_cta,
-                  double* __restrict__ sums) {
-    uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
+// mean[d] = (((x_0d + x_1d) + x_2d) + ...) / count in fp32: the running sum over the rows in their
+// given order that RaBitQuantizer::TrainImpl keeps (rabitq_quantizer.cpp:229-243), so the centroid -- and
+// with it every sign bit of every code -- is the one a reference build computes from the same rows.  One
+// thread per column; the loads of sixteen rows are issued together, the additions stay in row order.
+__global__ void __launch_bounds__(32)
+column_mean_in_order_kernel(const float* __restrict__ data, uint64_t count, uint32_t dim, float* __restrict__ mean) {
+    const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= dim) {
         return;
     }
-    uint64_t r0 = static_cast<uint64_t>(blockIdx.y) * rows_per_cta;
-    uint64_t r1 = r0 + rows_per_cta < count ? r0 + rows_per_cta : count;
-    double s = 0.0;
-    for (uint64_t r = r0; r < r1; ++r) {
-        s += static_cast<double>(__ldg(data + r * dim + d));
+    const float* p = data + d;
+    float s = 0.f;
+    uint64_t r = 0;
+    for (; r + 16 <= count; r += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            v[j] = __ldg(p + (r + j) * dim);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            s = __fadd_rn(s, v[j]);
+        }
     }
-    atomicAdd(sums + d, s);
-}
-
-__global__ void
-mean_finalize_kernel(const double* __restrict__ sums, uint64_t count, uint32_t dim,
-                     float* __restrict__ mean) {
-    uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d < dim) {
-        mean[d] = static_cast<float>(sums[d] / static_cast<double>(count));
+    for (; r < count; ++r) {
+        s = __fadd_rn(s, __ldg(p + r * dim));
     }
+    mean[d] = __fdiv_rn(s, static_cast<float>(count));
 }
 
 int
 rabitq_train_device(const float* data_dev, uint64_t count, uint32_t dim, const float* rotation_dev,
                     float* centroid_dev) {
     VB_CHECK_ARG(count > 0, "rabitq train: empty input");
-    DevBuf<double> sums;
     DevBuf<float> mean;
-    VB_TRY(sums.reserve(dim));
     VB_TRY(mean.reserve(dim));
-    VB_CUDA(cudaMemsetAsync(sums.ptr, 0, dim * sizeof(double), current_stream()));
-    uint32_t slabs = static_cast<uint32_t>(count < 4096 ? 1 : (count + 4095) / 4096);
-    if (slabs > 4096) {
-        slabs = 4096;
-    }
-    uint64_t rows_per_cta = (count + slabs - 1) / slabs;
-    dim3 grid((dim + 127) / 128, slabs);
-    VB_LAUNCH(column_sum_kernel, grid, 128, 0, data_dev, count, dim, rows_per_cta, sums.ptr);
-    VB_LAUNCH(mean_finalize_kernel, (dim + 127) / 128, 128, 0, sums.ptr, count, dim, mean.ptr);
+    VB_LAUNCH(column_mean_in_order_kernel, (dim + 31) / 32, 32, 0, data_dev, count, dim, mean.ptr);
     VB_TRY(dense_scores_f32(mean.ptr, 1, rotation_dev, dim, dim, 1.0f, nullptr, centroid_dev, dim));
     return sync_stream();
 }

@@ -148,12 +148,16 @@ tc_compact_row(uint64_t* my_buf, uint32_t& my_cnt, float& my_thr, uint32_t owner
 
 // MODE 0: at most four candidates per row, kept sorted in registers by the row's thread (the
 // k-means case); MODE 1: candidates go to per-row buffers compacted as above; MODE 2: no
-// selection, the scores themselves are stored.
+// selection, the scores themselves are stored; MODE 3: every column scoring below the row's fixed
+// threshold (row_bound) is appended, unsorted, to the row's output list of `cap` entries -- no
+// sorting at all, the caller sizes the lists from the threshold's expected pass rate and an
+// overflowing list sets bit 1 of the error flag.
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_candidates_kernel(const TcParams p) {
     constexpr bool SMALL_M = MODE == 0;
     constexpr bool STORE = MODE == 2;
+    constexpr bool THRESH = MODE == 3;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ TcShared sh;
 
@@ -291,7 +295,7 @@ tc_candidates_kernel(const TcParams p) {
             }
             if (!ok) {
                 sh.failed = 1;
-                atomicExch(p.error_flag, 1);
+                atomicOr(p.error_flag, 1);
             }
         }
         __syncwarp();
@@ -371,7 +375,7 @@ tc_candidates_kernel(const TcParams p) {
                 }
             }
             if (!ok) {
-                atomicExch(p.error_flag, 1);
+                atomicOr(p.error_flag, 1);
             }
         }
         __syncwarp();
@@ -397,6 +401,11 @@ tc_candidates_kernel(const TcParams p) {
             const bool valid_row = grow < p.a.rows;
             uint32_t cnt = 0;
             float thr = INFINITY;
+            uint64_t* list = nullptr;   // THRESH: this thread's output list of the item
+            if (THRESH) {
+                thr = valid_row ? __ldg(p.row_bound + grow) : -INFINITY;
+                list = p.out + ((grow * p.n_split + split) * TC_COL_GROUPS + cgroup) * p.cap;
+            }
             // bias of the warp's 32 columns: fetched one tile ahead into a register (lane = column),
             // handed to the other lanes through the warp's own shared-memory slot
             const bool has_bias = p.bias != nullptr;
@@ -575,11 +584,26 @@ tc_candidates_kernel(const TcParams p) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             if (m16[i] < thr) {
-                                if (sc[i] < thr) {
-                                    buf[cnt++] = make_key(sc[i], c0 + i + p.col_base);
-                                }
-                                if (sc[i + 16] < thr) {
-                                    buf[cnt++] = make_key(sc[i + 16], c0 + i + 16 + p.col_base);
+                                if (THRESH) {
+                                    if (sc[i] < thr) {
+                                        if (cnt < p.cap) {
+                                            list[cnt] = make_key(sc[i], c0 + i + p.col_base);
+                                        }
+                                        ++cnt;
+                                    }
+                                    if (sc[i + 16] < thr) {
+                                        if (cnt < p.cap) {
+                                            list[cnt] = make_key(sc[i + 16], c0 + i + 16 + p.col_base);
+                                        }
+                                        ++cnt;
+                                    }
+                                } else {
+                                    if (sc[i] < thr) {
+                                        buf[cnt++] = make_key(sc[i], c0 + i + p.col_base);
+                                    }
+                                    if (sc[i + 16] < thr) {
+                                        buf[cnt++] = make_key(sc[i + 16], c0 + i + 16 + p.col_base);
+                                    }
                                 }
                             }
                         }
@@ -591,6 +615,15 @@ tc_candidates_kernel(const TcParams p) {
                 break;
             }
             if (STORE) {
+                continue;
+            }
+            if (THRESH) {
+                if (valid_row) {
+                    p.out_count[(grow * p.n_split + split) * TC_COL_GROUPS + cgroup] = cnt;
+                    if (cnt > p.cap) {
+                        atomicOr(p.error_flag, 2);
+                    }
+                }
                 continue;
             }
             if (SMALL_M) {
@@ -622,7 +655,7 @@ tc_candidates_kernel(const TcParams p) {
             }
         }
         if (!ok && lane == 0) {
-            atomicExch(p.error_flag, 1);
+            atomicOr(p.error_flag, 1);
         }
     }
 
@@ -767,10 +800,84 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     int flag = 0;
     VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
-    if (flag != 0) {
+    if ((flag & 1) != 0) {
         VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
     }
     *n_split_out = static_cast<uint32_t>(n_split) * TC_COL_GROUPS;
+    return 0;
+}
+
+int
+tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
+                   const float* bias_dev, const float* row_thr_dev, uint32_t expected_per_row, uint32_t max_per_row,
+                   DevBuf<uint64_t>& out, DevBuf<uint32_t>& out_count, uint32_t* lists_out, uint32_t* cap_out,
+                   bool* overflow_out) {
+    VB_CHECK_ARG(a.rows > 0 && b.rows > 0, "tc_below_threshold: empty operand");
+    VB_CHECK_ARG(a.chunks == b.chunks && a.chunks > 0, "tc_below_threshold: operand depths differ");
+    VB_CHECK_ARG(n_terms == 1 || n_terms == 3, "tc_below_threshold: 1 or 3 terms");
+    VB_CHECK_ARG(row_thr_dev != nullptr, "tc_below_threshold: thresholds missing");
+    const uint64_t m_tiles = (a.rows + TC_BM - 1) / TC_BM;
+    const uint64_t n_tiles = (b.rows + TC_BN - 1) / TC_BN;
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    // More column ranges per row tile than the sorted modes take: a list costs nothing but its
+    // slots here, and short items spread evenly over the SMs.
+    uint64_t n_split = (4ull * sms + m_tiles - 1) / m_tiles;
+    if (n_split > 16) {
+        n_split = 16;
+    }
+    if (n_split > n_tiles) {
+        n_split = n_tiles;
+    }
+    if (n_split < 1) {
+        n_split = 1;
+    }
+    const uint64_t tiles_per_split = (n_tiles + n_split - 1) / n_split;
+    n_split = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+    const uint32_t lists = static_cast<uint32_t>(n_split) * TC_COL_GROUPS;
+    // list capacity: 3.5 x the expected share of a list, at least 16, within the caller's limit per row
+    uint32_t cap = next_pow2((7 * expected_per_row / 2 + lists - 1) / lists);
+    if (cap < 16) {
+        cap = 16;
+    }
+    while (cap > 16 && static_cast<uint64_t>(cap) * lists > max_per_row) {
+        cap >>= 1;
+    }
+    VB_CHECK_ARG(static_cast<uint64_t>(cap) * lists <= max_per_row, "tc_below_threshold: %u lists do not fit %u entries",
+                 lists, max_per_row);
+    const uint64_t items = m_tiles * n_split;
+    const uint32_t grid = static_cast<uint32_t>(items < sms ? items : sms);
+    TcParams p{};
+    p.a = a;
+    p.b = b;
+    p.n_terms = n_terms;
+    p.alpha = alpha;
+    p.bias = bias_dev;
+    p.row_bound = row_thr_dev;
+    p.m = 0;
+    p.cap = cap;
+    p.n_split = static_cast<uint32_t>(n_split);
+    p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
+    VB_TRY(out.reserve(static_cast<size_t>(a.rows) * lists * cap));
+    VB_TRY(out_count.reserve(static_cast<size_t>(a.rows) * lists));
+    VB_TRY(ws.error_flag.reserve(1));
+    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
+    p.out = out.ptr;
+    p.out_count = out_count.ptr;
+    p.error_flag = ws.error_flag.ptr;
+    size_t smem = 0;
+    tc_plan(p, 0, &smem);
+    auto kernel = tc_candidates_kernel<3>;
+    VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
+    int flag = 0;
+    VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
+    VB_TRY(sync_stream());
+    if ((flag & 1) != 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
+    }
+    *lists_out = lists;
+    *cap_out = cap;
+    *overflow_out = (flag & 2) != 0;
     return 0;
 }
 
@@ -819,7 +926,7 @@ tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_te
     int flag = 0;
     VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
-    if (flag != 0) {
+    if ((flag & 1) != 0) {
         VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
     }
     return 0;

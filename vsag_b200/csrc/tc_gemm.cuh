@@ -54,6 +54,8 @@ struct TcParams {
     uint32_t tiles_per_split; // B tiles per range
     uint64_t* scratch;        // [grid][128][TC_COL_GROUPS][cap] candidate buffers
     uint64_t* out;            // [a.rows][n_split][TC_COL_GROUPS][m] keys (ordered score << 32 | column), KEY_INF padded
+                              // (threshold mode: [a.rows][n_split][TC_COL_GROUPS][cap], unsorted, with out_count)
+    uint32_t* out_count;      // threshold mode: [a.rows][n_split][TC_COL_GROUPS] entries offered to each list
     uint32_t col_base;        // added to column indices in the keys
     float* store;             // score-matrix mode: [a.rows][store_ld] fp32 scores instead of candidates
     uint64_t store_ld;        // row stride of `store` in floats (multiple of 4, store 16-byte aligned)
@@ -243,6 +245,16 @@ int tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint3
                   const float* bias_dev, uint32_t m, uint32_t col_base, DevBuf<uint64_t>& out,
                   uint32_t* n_split_out, const float* a_sq_dev = nullptr,
                   const float* margin_scale_dev = nullptr, const float* row_bound_dev = nullptr);
+
+// Every column of B whose score alpha * <a, b> + bias lies below the row's threshold row_thr_dev[row],
+// unsorted, in out[a.rows][lists][cap] with the number offered to each list in out_count[a.rows][lists]
+// (a count above cap means the list overflowed and lost entries: *overflow_out is set and the caller
+// must not trust the result).  Lists are sized from expected_per_row, the number of columns the caller
+// expects below a row's threshold; lists * cap never exceeds max_per_row.
+int tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
+                       const float* bias_dev, const float* row_thr_dev, uint32_t expected_per_row,
+                       uint32_t max_per_row, DevBuf<uint64_t>& out, DevBuf<uint32_t>& out_count, uint32_t* lists_out,
+                       uint32_t* cap_out, bool* overflow_out);
 
 // The whole score matrix alpha * <a, b> + bias as fp32 in scores_dev[a.rows][ld] (ld >= b.rows, a
 // multiple of 4, scores_dev 16-byte aligned), from the same tensor-core pipeline.
