@@ -413,6 +413,8 @@ def run_ivf_sq8(args, ctx: Ctx) -> dict:
     nprobe = min(NPROBE, nlist)
     base, queries = make_data(device, n_base, n_query)
     ix = build_index(engine, base, nlist, rank, world, dist)
+    if not env_int("VB200_BENCH_PRUNING", 1):
+        ix.set_list_pruning(False)     # profiling aid: the timed region itself runs unpruned
 
     out_ids = torch.empty((n_query, K), dtype=torch.int64, device=device)
     out_d = torch.empty((n_query, K), dtype=torch.float32, device=device)

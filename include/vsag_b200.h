@@ -87,6 +87,14 @@ VB200_API uint64_t vb200_kernel_launches(void);
  * VB200_DISABLE_TC=1 sets the initial value to 0. */
 VB200_API int vb200_set_tensor_cores(int enable);
 
+/* Test hook with no counterpart in the reference.  Every wait inside the tensor-core kernels (on a
+ * copy, on an accumulator) polls a bounded number of times; when a wait runs out the kernel stops
+ * taking work, frees its tensor memory and returns, and the call fails with VB200_INTERNAL_ERROR
+ * while the CUDA context stays usable.  This sets that number of polls (a negative value restores
+ * the default, 2^24; 0 makes every wait give up at once) so that a test can make a wait run out on
+ * purpose and watch the error path. */
+VB200_API int vb200_debug_set_wait_limit(int32_t polls);
+
 /* Number of CUDA devices visible, or a negative VB200_* code. */
 VB200_API int vb200_device_count(void);
 

@@ -32,6 +32,7 @@ SIGNATURES = {
     "vb200_kernel_launches": (c_u64, []),
     "vb200_device_count": (c_int, []),
     "vb200_set_tensor_cores": (c_int, [c_int]),
+    "vb200_debug_set_wait_limit": (c_int, [c_int]),
     "vb200_sq8_train": (c_int, [c_void_p, c_u64, c_u32, c_int, c_void_p, c_void_p]),
     "vb200_sq8_encode": (c_int, [c_void_p, c_u64, c_u32, c_void_p, c_void_p, c_void_p]),
     "vb200_kmeans_assign": (c_int, [c_void_p, c_u64, c_u32, c_void_p, c_u32, c_void_p, c_void_p]),

@@ -5,6 +5,7 @@
 
 #include "dense.cuh"
 #include "ivf_scan.cuh"
+#include "ivf_scan_tc.cuh"
 #include "kmeans.cuh"
 #include "rabitq.cuh"
 #include "sq8.cuh"
@@ -43,6 +44,8 @@ struct SearchWorkspace {
     DevBuf<float> queries;      // staged queries / processed RaBitQ queries
     DevBuf<float> qproc;
     DevBuf<float> qw, qa;       // SQ8 per-query weights and constants
+    DevBuf<int8_t> qw8;         // SQ8 tensor-core scan: the weights as three signed-byte terms, [nq][3][dpad32]
+    DevBuf<float> qscale;       // [nq] their scale
     DevBuf<uint64_t> merged;    // SQ8 survivors before exact re-scoring
     DevBuf<float> scores;       // routing score slab
     DevBuf<uint64_t> cand;      // routing candidates
@@ -55,7 +58,7 @@ struct SearchWorkspace {
     DevBuf<uint32_t> pair_ctr;     // pair counts and scatter cursors of both phases: 4 x [nlist]
     DevBuf<uint32_t> pair_off[2];  // [nlist + 1]
     DevBuf<uint32_t> item_off[2];  // [nlist + 1]
-    DevBuf<uint64_t> item_map[2];  // [pairs of the phase]: list | tile << 32 per work item
+    DevBuf<ScanItemDesc> item_map[2];  // [pairs of the phase] at most: the work items of the phase
     DevBuf<uint32_t> pair_q[2], pair_slot[2];
     DevBuf<uint32_t> first_live;  // [nq] probe rank of the first list this shard scans for the query
     DevBuf<uint8_t> pair_drop;    // [nq x nprobe] second-phase pairs pruned before grouping
@@ -72,7 +75,7 @@ struct SearchWorkspace {
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
     DevBuf<uint64_t> keys2;     // [nq x k] after rerank
-    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases
+    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases, [3] bytes read, [4] tensor-core scan error flag
     DevBuf<int64_t> out_ids;
     DevBuf<float> out_dists;
 };
@@ -97,6 +100,11 @@ struct vb200_ivf {
     DevBuf<float> lower, diff;           // SQ8, padded to dpad
     DevBuf<float> sq_scale, sq_mid;      // SQ8: diff/255 and lower + 128*diff/255, padded to dpad
     DevBuf<float> code_norm;             // SQ8: |decoded code|^2 per position
+    // SQ8 tensor-core scan: a second copy of the lists as signed bytes (code - 128) in 8-row groups of
+    // 16-byte cores, the shared-memory layout of the MMA's A operand; group_off[l] = first group of list l
+    DevBuf<int8_t> codes_t;
+    DevBuf<uint32_t> group_off;
+    uint32_t kchunks = 0;                // 16-byte chunks per tiled row (dim rounded up to 32, over 16)
     DevBuf<float> rotation, rq_centroid; // RaBitQ
 
     uint64_t n_total = 0;   // rows seen (inner ids 0 .. n_total-1)
@@ -111,6 +119,7 @@ struct vb200_ivf {
     DevBuf<float> ball_centre;    // SQ8 list pruning: [nlist][SQ8_BALLS][dim] centres of the covering balls
     DevBuf<float> ball_radius;    // [nlist][SQ8_BALLS] their radii (-1: empty)
     DevBuf<uint32_t> ball_count;  // [nlist] balls in use per list
+    DevBuf<float> list_radius;    // [nlist] largest distance of a decoded row from the list's centroid, rounded up
     bool prune_lists = true;
     int64_t last_scanned_bytes = 0;
     // tensor-core routing: the centroids as tiled bf16 hi/lo terms (rebuilt when they change)
@@ -292,6 +301,41 @@ fp32_place_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim
     }
 }
 
+// Tiled signed copy of the lists for the tensor-core scan: row r of list l goes to 8-row group
+// group_off[l] + r / 8; its 16-byte chunk c (bytes code - 128, i.e. code ^ 0x80; zero beyond the code)
+// to core c of the group, row r % 8.  One thread per (position, chunk).
+__global__ void
+sq8_tile_codes_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, const uint32_t* __restrict__ list_off,
+                      const uint32_t* __restrict__ group_off, uint32_t nlist, uint64_t n_stored, uint32_t kchunks,
+                      int8_t* __restrict__ tiled) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= n_stored * kchunks) {
+        return;
+    }
+    const uint32_t pos = static_cast<uint32_t>(e / kchunks);
+    const uint32_t c = static_cast<uint32_t>(e % kchunks);
+    uint32_t lo = 0, hi = nlist;  // largest l with list_off[l] <= pos
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (list_off[mid] <= pos) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    const uint32_t r = pos - list_off[lo];
+    const uint64_t g = static_cast<uint64_t>(group_off[lo]) + (r >> 3);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (c * 16 < code_stride) {
+        v = __ldg(reinterpret_cast<const uint4*>(codes + static_cast<uint64_t>(pos) * code_stride + c * 16));
+        v.x ^= 0x80808080u;
+        v.y ^= 0x80808080u;
+        v.z ^= 0x80808080u;
+        v.w ^= 0x80808080u;
+    }
+    *reinterpret_cast<uint4*>(tiled + (g * kchunks + c) * 128 + (r & 7u) * 16) = v;
+}
+
 // code_norm[p] = sum_d x_d^2 with x_d the reference's decode fma(code * (1/255), diff, lower).
 __global__ void
 sq8_code_norm_kernel(const uint8_t* __restrict__ codes, uint64_t n, uint32_t dim, uint32_t code_stride,
@@ -353,7 +397,7 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
                       const uint32_t* __restrict__ list_off, const float* __restrict__ lower,
                       const float* __restrict__ diff, const float* __restrict__ centroids,
                       float* __restrict__ ball_centre, float* __restrict__ ball_radius,
-                      uint32_t* __restrict__ ball_count) {
+                      uint32_t* __restrict__ ball_count, float* __restrict__ list_radius) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* seeds = reinterpret_cast<float*>(smem_raw);              // [SQ8_BALLS][dim]
     float* sums = seeds + SQ8_BALLS * dim;                          // [SQ8_BALLS][dim]
@@ -377,6 +421,9 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
         }
         if (tid < SQ8_BALLS) {
             out_r[tid] = -1.0f;
+        }
+        if (tid == 0) {
+            list_radius[l] = 0.f;
         }
         return;
     }
@@ -413,6 +460,11 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
         }
         atomicMax(&best, mine);
         __syncthreads();
+        if (j == 0 && tid == 0) {
+            // the farthest row from the list's centroid: the radius of the one ball around the centroid,
+            // which costs a pair nothing to test because routing has measured |q - centroid| already
+            list_radius[l] = sqrtf(__uint_as_float(static_cast<uint32_t>(best >> 32))) * 1.00001f + 1e-12f;
+        }
         const uint32_t pick = len - 1 - static_cast<uint32_t>(best & 0xFFFFFFFFull);
         decode_to(pick < len ? pick : 0, seeds + j * dim);
         __syncthreads();
@@ -479,7 +531,8 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
 __global__ void __launch_bounds__(128)
 sq8_query_prep_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t dim, uint32_t dpad,
                       const float* __restrict__ scale, const float* __restrict__ mid, int metric,
-                      float* __restrict__ qw, float* __restrict__ qa) {
+                      float* __restrict__ qw, float* __restrict__ qa, uint32_t dpad32, int8_t* __restrict__ qw8,
+                      float* __restrict__ qscale) {
     uint64_t q = static_cast<uint64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
     uint32_t lane = threadIdx.x & 31;
     if (q >= nq) {
@@ -500,6 +553,33 @@ sq8_query_prep_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t d
     }
     if (lane == 0) {
         qa[q] = metric == VB200_METRIC_L2 ? fmaf(-2.0f, qm, qq) : 1.0f - qm;
+    }
+    if (qw8 == nullptr) {
+        return;
+    }
+    // Tensor-core scan: w = s * (t1 + t2 / 254 + t3 / 254^2) with signed-byte terms, s = max|w| / 127.
+    float wmax = 0.f;
+    for (uint32_t d = lane; d < dim; d += 32) {
+        wmax = fmaxf(wmax, fabsf(__ldg(src + d) * scale[d]));
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, off));
+    }
+    const float s = wmax > 0.f && wmax < INFINITY ? wmax / 127.0f : 1.0f;
+    int8_t* t = qw8 + q * 3 * dpad32;
+    for (uint32_t d = lane; d < dpad32; d += 32) {
+        const float w = d < dim ? __ldg(src + d) * scale[d] : 0.f;
+        const float u = w / s;
+        const float t1 = fminf(fmaxf(rintf(u), -127.f), 127.f);
+        const float v2 = (u - t1) * 254.0f;
+        const float t2 = fminf(fmaxf(rintf(v2), -127.f), 127.f);
+        const float t3 = fminf(fmaxf(rintf((v2 - t2) * 254.0f), -127.f), 127.f);
+        t[d] = static_cast<int8_t>(static_cast<int>(t1));
+        t[dpad32 + d] = static_cast<int8_t>(static_cast<int>(t2));
+        t[2 * dpad32 + d] = static_cast<int8_t>(static_cast<int>(t3));
+    }
+    if (lane == 0) {
+        qscale[q] = s;
     }
 }
 
@@ -656,7 +736,7 @@ struct PairTables {
     uint32_t* cursor[2];    // [nlist] scatter cursors
     uint32_t* off[2];       // [nlist + 1] first pair of each list
     uint32_t* item_off[2];  // [nlist + 1] tile prefix by position in the scan order
-    uint64_t* item_map[2];  // [items] list | tile << 32 of every work item
+    ScanItemDesc* item_map[2];  // [items] every work item
     uint32_t* q[2];         // [pairs] query
     uint32_t* slot[2];      // [pairs] output slot
 };
@@ -682,88 +762,120 @@ pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t n
 }
 
 // After the first phase: drop[e] = 1 for every second-phase (query, list) pair that the list's
-// covering balls put beyond the query's bound (the test the scan kernel makes per tile, made here
-// once per pair so that pruned pairs never become work items).  Eight threads per pair.  The code
-// bytes of the dropped pairs still count as algorithmic scan volume (scalars[0]).
+// covering balls put beyond the query's bound (the test the SIMT scan kernel makes per tile, made here
+// once per pair so that pruned pairs never become work items).  One thread per pair: first the ball
+// around the list's centroid, whose distance from the query routing has computed exactly -- on
+// clustered data that settles most pairs without reading a ball centre -- then the list's covering
+// balls one after the other until one of them cannot exclude the list.  The code bytes of the dropped
+// pairs still count as algorithmic scan volume (scalars[0]).
+__device__ __forceinline__ float
+pair_ball_dot(const float* __restrict__ qv, const float* __restrict__ cv, uint32_t dim, int metric) {
+    float dot = 0.f;
+    if ((dim & 3u) == 0 && ((reinterpret_cast<uintptr_t>(qv) | reinterpret_cast<uintptr_t>(cv)) & 15u) == 0) {
+        const float4* q4 = reinterpret_cast<const float4*>(qv);
+        const float4* c4 = reinterpret_cast<const float4*>(cv);
+#pragma unroll 4
+        for (uint32_t i = 0; i < (dim >> 2); ++i) {
+            const float4 x = __ldg(q4 + i), c = __ldg(c4 + i);
+            if (metric == 0) {
+                float t = x.x - c.x;
+                dot = fmaf(t, t, dot);
+                t = x.y - c.y;
+                dot = fmaf(t, t, dot);
+                t = x.z - c.z;
+                dot = fmaf(t, t, dot);
+                t = x.w - c.w;
+                dot = fmaf(t, t, dot);
+            } else {
+                dot = fmaf(x.x, c.x, dot);
+                dot = fmaf(x.y, c.y, dot);
+                dot = fmaf(x.z, c.z, dot);
+                dot = fmaf(x.w, c.w, dot);
+            }
+        }
+    } else {
+        for (uint32_t d = 0; d < dim; ++d) {
+            const float x = __ldg(qv + d), c = __ldg(cv + d);
+            if (metric == 0) {
+                const float t = x - c;
+                dot = fmaf(t, t, dot);
+            } else {
+                dot = fmaf(x, c, dot);
+            }
+        }
+    }
+    return dot;
+}
+
 __global__ void __launch_bounds__(256)
 pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
                  const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
                  const uint32_t* __restrict__ list_off, const float* __restrict__ queries, uint32_t dim,
                  const float* __restrict__ ball_centre, const float* __restrict__ ball_radius,
                  const uint32_t* __restrict__ ball_count, const uint32_t* __restrict__ thr, int metric,
-                 uint32_t code_size, uint8_t* __restrict__ drop,
-                 unsigned long long* __restrict__ scalars) {
+                 uint32_t code_size, const float* __restrict__ probe_dists, const float* __restrict__ list_radius,
+                 uint8_t* __restrict__ drop, unsigned long long* __restrict__ scalars) {
     __shared__ unsigned long long s_bytes;
     if (threadIdx.x == 0) {
         s_bytes = 0;
     }
     __syncthreads();
-    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * 32 + (threadIdx.x >> 3);
-    const uint32_t part = threadIdx.x & 7;
-    bool candidate = false;
-    uint32_t q = 0;
-    int32_t l = -1;
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    unsigned long long my_bytes = 0;   // code bytes of the pair if it is dropped
     if (e < total) {
-        q = static_cast<uint32_t>(e / nprobe);
+        const uint32_t q = static_cast<uint32_t>(e / nprobe);
         const uint32_t pr = static_cast<uint32_t>(e % nprobe);
-        l = probes[e];
-        candidate = pr != first_live[q] && probe_is_live(l, nlist, rank, world, list_off) &&
-                    thr[q] <= float_to_ordered(INFINITY);
-    }
-    // the eight threads of a pair stay together; pairs of one warp leave the loop independently
-    const uint32_t group_mask = 0xFFu << ((threadIdx.x & 31u) & ~7u);
-    bool dropped = false;
-    if (candidate) {
-        const float* qv = queries + static_cast<uint64_t>(q) * dim;
-        float qq = 0.f;
-        if (metric != 0) {
-            for (uint32_t d = part; d < dim; d += 8) {
-                const float x = __ldg(qv + d);
-                qq = fmaf(x, x, qq);
-            }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                qq += __shfl_xor_sync(group_mask, qq, o);
-            }
-        }
-        const float bound = ordered_to_float(thr[q]);
-        const uint32_t n_balls = __ldg(ball_count + l);
-        const float* cv = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
-        bool any = false;
-        for (uint32_t j = 0; j < n_balls && !any; ++j, cv += dim) {
-            float dot = 0.f;
-            for (uint32_t d = part; d < dim; d += 8) {
-                const float x = __ldg(qv + d), c = __ldg(cv + d);
+        const int32_t l = probes[e];
+        const uint32_t t = thr[q];
+        bool dropped = false;
+        if (pr != first_live[q] && probe_is_live(l, nlist, rank, world, list_off) && t <= float_to_ordered(INFINITY)) {
+            const float bound = ordered_to_float(t);
+            const float* qv = queries + static_cast<uint64_t>(q) * dim;
+            const float qq = metric != 0 ? pair_ball_dot(qv, qv, dim, 1) : 0.f;
+            bool beyond = false;   // the ball around the centroid already excludes the list
+            if (probe_dists != nullptr) {
+                const float dc = __ldg(probe_dists + e), big_r = __ldg(list_radius + l);
                 if (metric == 0) {
-                    const float t = x - c;
-                    dot = fmaf(t, t, dot);
-                } else {
-                    dot = fmaf(x, c, dot);
-                }
-            }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                dot += __shfl_xor_sync(group_mask, dot, o);
-            }
-            const float r = __ldg(ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS + j);
-            if (r >= 0.f) {
-                if (metric == 0) {
-                    const float gap = sqrtf(dot) - r;
+                    const float gap = sqrtf(dc) - big_r;
                     const float lower = gap > 0.f ? gap * gap : 0.f;
-                    any = !(lower > bound * 1.001f + 1e-4f * dot);
+                    beyond = lower > bound * 1.001f + 1e-4f * dc;
                 } else {
-                    const float lower = 1.0f - dot - sqrtf(qq) * r;
-                    any = !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
+                    const float lower = dc - sqrtf(qq) * big_r;   // dc = 1 - <q, centroid>
+                    beyond = lower > bound + 1e-3f * (fabsf(bound) + fabsf(1.0f - dc) + 1.0f);
                 }
             }
+            bool any = false;      // some ball may hold a row within the bound
+            if (!beyond) {
+                const uint32_t n_balls = __ldg(ball_count + l);
+                const float* cv = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
+                for (uint32_t j = 0; j < n_balls && !any; ++j, cv += dim) {
+                    const float r = __ldg(ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS + j);
+                    if (r >= 0.f) {
+                        // slack: the distances compared here and in the scan differ in rounding only
+                        const float dot = pair_ball_dot(qv, cv, dim, metric);
+                        if (metric == 0) {
+                            const float gap = sqrtf(dot) - r;
+                            const float lower = gap > 0.f ? gap * gap : 0.f;
+                            any = !(lower > bound * 1.001f + 1e-4f * dot);
+                        } else {
+                            const float lower = 1.0f - dot - sqrtf(qq) * r;
+                            any = !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
+                        }
+                    }
+                }
+            }
+            dropped = !any;
+            if (dropped) {
+                my_bytes = static_cast<unsigned long long>(list_off[l + 1] - list_off[l]) * code_size;
+            }
         }
-        dropped = !any;
-    }
-    if (part == 0 && e < total) {
         drop[e] = dropped ? 1 : 0;
-        if (dropped) {
-            atomicAdd(&s_bytes, static_cast<unsigned long long>(list_off[l + 1] - list_off[l]) * code_size);
-        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        my_bytes += __shfl_xor_sync(0xffffffffu, my_bytes, o);
+    }
+    if ((threadIdx.x & 31u) == 0 && my_bytes != 0) {
+        atomicAdd(&s_bytes, my_bytes);
     }
     __syncthreads();
     if (threadIdx.x == 0 && s_bytes != 0) {
@@ -775,13 +887,13 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
 // taken in `order` (pair_off is stored by list, item_off by position in the order), plus the
 // logical scan volume sum(pairs[l] * len[l]).
 __global__ void __launch_bounds__(1024)
-pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
+pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
                  const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt, uint32_t code_size,
                  uint64_t* __restrict__ scalars) {
     const uint32_t* __restrict__ pair_cnt = blockIdx.x == 0 ? tables.cnt[0] : tables.cnt[1];
     uint32_t* __restrict__ pair_off = blockIdx.x == 0 ? tables.off[0] : tables.off[1];
     uint32_t* __restrict__ item_off = blockIdx.x == 0 ? tables.item_off[0] : tables.item_off[1];
-    uint64_t* __restrict__ item_map = blockIdx.x == 0 ? tables.item_map[0] : tables.item_map[1];
+    ScanItemDesc* __restrict__ item_map = blockIdx.x == 0 ? tables.item_map[0] : tables.item_map[1];
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
@@ -824,7 +936,16 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off,
         pair_off[l] = run_p;
         item_off[pos] = run_t;
         for (uint32_t j = 0; j < t; ++j) {   // the scan's work queue reads its items from here
-            item_map[run_t + j] = static_cast<uint64_t>(l) | (static_cast<uint64_t>(j) << 32);
+            ScanItemDesc d;
+            d.list = l;
+            d.pbeg = run_p + j * qt;
+            d.nqt = c - j * qt < qt ? c - j * qt : qt;
+            d.lbeg = list_off[l];
+            d.len = list_off[l + 1] - list_off[l];
+            d.goff = group_off != nullptr ? group_off[l] : 0u;
+            d.pad0 = 0;
+            d.pad1 = 0;
+            item_map[run_t + j] = d;
         }
         run_p += c;
         run_t += t;
@@ -1025,83 +1146,335 @@ max_row_norm_kernel(const float* __restrict__ sq, uint32_t n, float* __restrict_
     }
 }
 
-// thr[q] = the approximate score of query q's ncand-th best centroid among the sampled ones, plus a
-// margin of 1e-3 |q| max|c| that covers the rounding of the tensor-core scores on both sides: at
-// least ncand centroids score below it exactly, so every one of the query's ncand nearest centroids
-// scores below it approximately.  One warp per query.
-__global__ void __launch_bounds__(128)
-route_threshold_kernel(const uint64_t* __restrict__ sample_keys, uint32_t ncand, const float* __restrict__ queries,
-                       uint32_t dim, uint64_t nq, const float* __restrict__ c_max_norm, float* __restrict__ thr) {
-    const uint64_t q = static_cast<uint64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-    const uint32_t lane = threadIdx.x & 31;
-    if (q >= nq) {
-        return;
+// Block-wide helpers for the two routing kernels below (256 threads).
+constexpr int ROUTE_THREADS = 256;
+
+__device__ __forceinline__ float
+route_block_min(float v, float* red) {
+    for (int off = 16; off > 0; off >>= 1) {
+        v = fminf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+        red[threadIdx.x >> 5] = v;
+    }
+    __syncthreads();
+    float m = red[0];
+    for (int w = 1; w < ROUTE_THREADS / 32; ++w) {
+        m = fminf(m, red[w]);
+    }
+    return m;
+}
+
+__device__ __forceinline__ float
+route_block_max(float v, float* red) {
+    return -route_block_min(-v, red);
+}
+
+// Given hist[256] and a 1-based rank, finds the bin the rank-th smallest element falls into and the
+// rank it has inside that bin (warp 0 computes, everyone gets the result after the barriers).
+__device__ __forceinline__ void
+route_find_bin(const uint32_t* hist, uint32_t rank, uint32_t* s_bin, uint32_t* s_rank_in_bin) {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const uint32_t lane = threadIdx.x;
+        uint32_t local[8], sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            local[i] = hist[lane * 8 + i];
+            sum += local[i];
+        }
+        uint32_t incl = sum;
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= static_cast<uint32_t>(off)) {
+                incl += v;
+            }
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        const uint32_t want = rank < total ? rank : total;   // fewer elements than the rank: the last one
+        uint32_t run = incl - sum;
+        if (want > run && want <= incl) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (want > run && want <= run + local[i]) {
+                    *s_bin = lane * 8 + i;
+                    *s_rank_in_bin = want - run;
+                }
+                run += local[i];
+            }
+        }
+        if (total == 0 && lane == 0) {
+            *s_bin = 0;
+            *s_rank_in_bin = 0;
+        }
+    }
+    __syncthreads();
+}
+
+// thr[q] = a score that at least ncand of query q's `sample` approximate scores (scores[q][0 .. sample))
+// do not exceed -- one of those scores, at most a few ranks above the ncand-th smallest -- plus a margin
+// of 1e-3 |q| max|c| that covers the rounding of the tensor-core scores on both sides: at least ncand
+// centroids score below it exactly, so every one of the query's ncand nearest centroids scores below
+// it approximately.  One CTA per query: two rounds of a 256-bin histogram over the range of the scores
+// still in question (bins follow the values' own range, so a narrow spread does not pile them into one
+// bin), then the largest score of the bins taken.
+constexpr int ROUTE_THR_PER_THREAD = 16;   // sample <= 4096
+
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_threshold_kernel(const float* __restrict__ scores, uint32_t sample, uint32_t ncand, const float* __restrict__ queries,
+                       uint32_t dim, const float* __restrict__ c_max_norm, float* __restrict__ thr) {
+    __shared__ uint32_t hist[256];
+    __shared__ float red[ROUTE_THREADS / 32];
+    __shared__ uint32_t s_bin, s_rank;
+    const uint64_t q = blockIdx.x;
+    const uint32_t tid = threadIdx.x;
+    float v[ROUTE_THR_PER_THREAD];
+    uint8_t bin1[ROUTE_THR_PER_THREAD];
+    float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ROUTE_THR_PER_THREAD; ++i) {
+        const uint32_t c = tid + i * ROUTE_THREADS;
+        const float x = c < sample ? __ldg(scores + q * sample + c) : NAN;
+        v[i] = x;
+        if (x == x) {   // NaN scores take no part
+            mn = fminf(mn, x);
+            mx = fmaxf(mx, x);
+        }
     }
     float qq = 0.f;
-    for (uint32_t d = lane; d < dim; d += 32) {
+    for (uint32_t d = tid; d < dim; d += ROUTE_THREADS) {
         const float x = __ldg(queries + q * dim + d);
         qq = fmaf(x, x, qq);
     }
+    // sum of the per-thread partial norms
     for (int off = 16; off > 0; off >>= 1) {
         qq += __shfl_xor_sync(0xffffffffu, qq, off);
     }
-    if (lane == 0) {
-        const uint64_t key = sample_keys[q * ncand + ncand - 1];
-        const float worst = key == KEY_INF ? INFINITY : ordered_to_float(static_cast<uint32_t>(key >> 32));
-        thr[q] = worst + 1e-3f * sqrtf(qq) * __ldg(c_max_norm);
+    __shared__ float s_qq[ROUTE_THREADS / 32];
+    if ((tid & 31) == 0) {
+        s_qq[tid >> 5] = qq;
+    }
+    mn = route_block_min(mn, red);
+    mx = route_block_max(mx, red);
+    float bound = mx;   // everything, when the scores do not spread (or there are fewer than ncand of them)
+    if (mx > mn && mx < INFINITY && mn > -INFINITY) {
+        // round 1: bins over [mn, mx]
+        hist[tid] = 0;
+        __syncthreads();
+        const float scale1 = 255.0f / (mx - mn);
+#pragma unroll
+        for (int i = 0; i < ROUTE_THR_PER_THREAD; ++i) {
+            uint32_t b = 255;
+            if (v[i] == v[i]) {
+                const float t = (v[i] - mn) * scale1;
+                b = t >= 255.0f ? 255u : static_cast<uint32_t>(t);
+                atomicAdd(&hist[b], 1u);
+            }
+            bin1[i] = static_cast<uint8_t>(b);
+        }
+        route_find_bin(hist, ncand, &s_bin, &s_rank);
+        const uint32_t b1 = s_bin, rank2 = s_rank;
+        // round 2: the scores of bin b1 alone, over their own range
+        float mn2 = INFINITY, mx2 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < ROUTE_THR_PER_THREAD; ++i) {
+            if (v[i] == v[i] && bin1[i] == b1) {
+                mn2 = fminf(mn2, v[i]);
+                mx2 = fmaxf(mx2, v[i]);
+            }
+        }
+        mn2 = route_block_min(mn2, red);
+        mx2 = route_block_max(mx2, red);
+        float pick = -INFINITY;   // the largest score taken from bin b1
+        if (mx2 > mn2) {
+            hist[tid] = 0;
+            __syncthreads();
+            const float scale2 = 255.0f / (mx2 - mn2);
+            uint8_t bin2[ROUTE_THR_PER_THREAD];
+#pragma unroll
+            for (int i = 0; i < ROUTE_THR_PER_THREAD; ++i) {
+                bin2[i] = 255;
+                if (v[i] == v[i] && bin1[i] == b1) {
+                    const float t = (v[i] - mn2) * scale2;
+                    const uint32_t b = t >= 255.0f ? 255u : static_cast<uint32_t>(t);
+                    bin2[i] = static_cast<uint8_t>(b);
+                    atomicAdd(&hist[b], 1u);
+                }
+            }
+            route_find_bin(hist, rank2, &s_bin, &s_rank);
+            const uint32_t b2 = s_bin;
+#pragma unroll
+            for (int i = 0; i < ROUTE_THR_PER_THREAD; ++i) {
+                if (v[i] == v[i] && bin1[i] == b1 && bin2[i] <= b2) {
+                    pick = fmaxf(pick, v[i]);
+                }
+            }
+        } else {
+            pick = mx2;   // the bin holds one value (possibly many times)
+        }
+        bound = route_block_max(pick, red);
+    }
+    if (tid == 0) {
+        float total = 0.f;
+        for (int w = 0; w < ROUTE_THREADS / 32; ++w) {
+            total += s_qq[w];
+        }
+        thr[q] = bound + 1e-3f * sqrtf(total) * __ldg(c_max_norm);
     }
 }
 
-// One CTA per query: gathers the query's centroids below its threshold from their lists, orders them
-// by approximate score, re-scores the ncand best exactly -- L2: FMA chain of (q-c)^2 over d
+// One CTA per query: gathers the query's centroids below its threshold from their lists, takes the
+// ncand best by approximate score, re-scores them exactly -- L2: FMA chain of (q-c)^2 over d
 // ascending; IP: 1 - chain of q*c (the loop of IVF::route_buckets_only,
 // src/algorithm/ivf/ivf.cpp:1589-1660) -- and writes the nprobe nearest, distance ascending, lower
-// list id first on ties.
-__global__ void __launch_bounds__(256)
+// list id first on ties.  The ncand best come from a histogram over the candidates' score range (the bin
+// that holds the ncand-th and everything below it, a few more than ncand keys), sorted as 64-bit keys so
+// that equal scores keep the lower list id; only if that set does not fit the small sort buffer (a
+// pile of equal scores) are all candidates sorted.
+constexpr uint32_t ROUTE_PICK_SMALL = 512;   // keys the small sort takes
+
+__global__ void __launch_bounds__(ROUTE_THREADS)
 route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids,
                   const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
                   uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
                   float* __restrict__ probe_dists) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ uint32_t s_off[65];
-    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);                       // [max(lists * cap, 2 * ncand) rounded up]
-    float* qs = reinterpret_cast<float*>(keys + next_pow2(lists * cap > 2 * ncand ? lists * cap : 2 * ncand));
+    __shared__ uint32_t hist[256];
+    __shared__ float red[ROUTE_THREADS / 32];
+    __shared__ uint32_t s_bin, s_rank, s_taken;
+    const uint32_t slots = next_pow2(lists * cap > ROUTE_PICK_SMALL ? lists * cap : ROUTE_PICK_SMALL);
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);   // [slots] gathered candidates
+    uint64_t* small = keys + slots;                            // [ROUTE_PICK_SMALL]
+    float* qs = reinterpret_cast<float*>(small + ROUTE_PICK_SMALL);
     const uint64_t q = blockIdx.x;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (uint32_t d = tid; d < dim; d += blockDim.x) {
         qs[d] = queries[q * dim + d];
     }
-    if (tid == 0) {
-        uint32_t run = 0;
-        for (uint32_t l = 0; l < lists; ++l) {
-            s_off[l] = run;
-            const uint32_t c = lists_cnt[q * lists + l];
-            run += c < cap ? c : cap;
+    if (tid < 32) {
+        // exclusive prefix of the (clamped) list counts, two lists per lane
+        const uint32_t l0 = 2 * tid, l1 = 2 * tid + 1;
+        uint32_t c0 = l0 < lists ? lists_cnt[q * lists + l0] : 0u;
+        uint32_t c1 = l1 < lists ? lists_cnt[q * lists + l1] : 0u;
+        c0 = c0 < cap ? c0 : cap;
+        c1 = c1 < cap ? c1 : cap;
+        uint32_t incl = c0 + c1;
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (tid >= static_cast<uint32_t>(off)) {
+                incl += v;
+            }
         }
-        s_off[lists] = run;
+        const uint32_t before = incl - c0 - c1;
+        if (l0 < lists) {
+            s_off[l0] = before;
+        }
+        if (l1 < lists) {
+            s_off[l1] = before + c0;
+        }
+        if (tid == 31) {
+            s_off[lists] = incl;
+        }
+        if (tid == 0) {
+            s_taken = 0;
+        }
     }
     __syncthreads();
     const uint32_t total = s_off[lists];
+    float mn = INFINITY, mx = -INFINITY;
     for (uint32_t l = warp; l < lists; l += blockDim.x >> 5) {
         const uint32_t beg = s_off[l], c = s_off[l + 1] - beg;
         const uint64_t* src = lists_keys + (q * lists + l) * cap;
         for (uint32_t i = lane; i < c; i += 32) {
-            keys[beg + i] = src[i];
+            const uint64_t key = src[i];
+            keys[beg + i] = key;
+            const float sc = ordered_to_float(static_cast<uint32_t>(key >> 32));
+            mn = fminf(mn, sc);
+            mx = fmaxf(mx, sc);
         }
     }
-    const uint32_t n2 = next_pow2(total < 2 ? 2 : total);
-    for (uint32_t i = total + tid; i < n2; i += blockDim.x) {
-        keys[i] = KEY_INF;
+    mn = route_block_min(mn, red);
+    mx = route_block_max(mx, red);
+    uint32_t n_small = 0;
+    bool use_small = false;
+    if (total > ncand && mx > mn) {
+        hist[tid] = 0;
+        __syncthreads();
+        const float scale = 255.0f / (mx - mn);
+        for (uint32_t i = tid; i < total; i += blockDim.x) {
+            const float t = (ordered_to_float(static_cast<uint32_t>(keys[i] >> 32)) - mn) * scale;
+            atomicAdd(&hist[t >= 255.0f ? 255u : static_cast<uint32_t>(t)], 1u);
+        }
+        route_find_bin(hist, ncand, &s_bin, &s_rank);
+        const uint32_t b_last = s_bin;
+        for (uint32_t i = tid; i < total; i += blockDim.x) {
+            const uint64_t key = keys[i];
+            const float t = (ordered_to_float(static_cast<uint32_t>(key >> 32)) - mn) * scale;
+            const uint32_t b = t >= 255.0f ? 255u : static_cast<uint32_t>(t);
+            if (b <= b_last) {
+                const uint32_t at = atomicAdd(&s_taken, 1u);
+                if (at < ROUTE_PICK_SMALL) {
+                    small[at] = key;
+                }
+            }
+        }
+        __syncthreads();
+        n_small = s_taken;
+        use_small = n_small <= ROUTE_PICK_SMALL;
     }
-    block_bitonic_sort(keys, n2);
+    uint64_t* sorted = keys;
+    uint32_t n_sorted;
+    if (use_small) {
+        n_sorted = next_pow2(n_small < 2 ? 2 : n_small);
+        for (uint32_t i = n_small + tid; i < n_sorted; i += blockDim.x) {
+            small[i] = KEY_INF;
+        }
+        block_bitonic_sort(small, n_sorted);
+        sorted = small;
+    } else {
+        n_sorted = next_pow2(total < 2 ? 2 : total);
+        for (uint32_t i = total + tid; i < n_sorted; i += blockDim.x) {
+            keys[i] = KEY_INF;
+        }
+        block_bitonic_sort(keys, n_sorted);
+    }
     // exact distances of the ncand best (one chain per candidate, dimensions in ascending order)
     const uint32_t m2 = next_pow2(ncand < 2 ? 2 : ncand);
     uint64_t mine = KEY_INF;
-    if (tid < ncand && tid < n2 && keys[tid] != KEY_INF) {
-        const uint32_t list = static_cast<uint32_t>(keys[tid]);
+    if (tid < ncand && tid < n_sorted && sorted[tid] != KEY_INF) {
+        const uint32_t list = static_cast<uint32_t>(sorted[tid]);
         const float* c = centroids + static_cast<uint64_t>(list) * dim;
         float s = 0.f;
-        if (metric == VB200_METRIC_L2) {
+        if ((dim & 3u) == 0) {   // centroid rows are then 16-byte aligned: four dimensions per load, several loads in flight
+            const float4* c4 = reinterpret_cast<const float4*>(c);
+            const float4* q4 = reinterpret_cast<const float4*>(qs);
+            if (metric == VB200_METRIC_L2) {
+#pragma unroll 8
+                for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                    const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                    float t = __fsub_rn(qv.x, cv.x);
+                    s = fmaf(t, t, s);
+                    t = __fsub_rn(qv.y, cv.y);
+                    s = fmaf(t, t, s);
+                    t = __fsub_rn(qv.z, cv.z);
+                    s = fmaf(t, t, s);
+                    t = __fsub_rn(qv.w, cv.w);
+                    s = fmaf(t, t, s);
+                }
+            } else {
+#pragma unroll 8
+                for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                    const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                    s = fmaf(qv.x, cv.x, s);
+                    s = fmaf(qv.y, cv.y, s);
+                    s = fmaf(qv.z, cv.z, s);
+                    s = fmaf(qv.w, cv.w, s);
+                }
+                s = __fsub_rn(1.0f, s);
+            }
+        } else if (metric == VB200_METRIC_L2) {
             for (uint32_t d = 0; d < dim; ++d) {
                 const float t = __fsub_rn(qs[d], __ldg(c + d));
                 s = fmaf(t, t, s);
@@ -1116,11 +1489,11 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
     }
     __syncthreads();
     if (tid < m2) {
-        keys[tid] = mine;
+        small[tid] = mine;
     }
-    block_bitonic_sort(keys, m2);
+    block_bitonic_sort(small, m2);
     for (uint32_t i = tid; i < nprobe; i += blockDim.x) {
-        const uint64_t key = i < m2 ? keys[i] : KEY_INF;
+        const uint64_t key = i < m2 ? small[i] : KEY_INF;
         const uint64_t o = q * nprobe + i;
         probes[o] = key == KEY_INF ? -1 : static_cast<int32_t>(static_cast<uint32_t>(key));
         if (probe_dists != nullptr) {
@@ -1178,18 +1551,17 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
             TcOperand bs{ix->c_hi.ptr, ix->c_lo.ptr, sample, chunks};
             VB_TRY(ws.scores.reserve(nq * sample));
             VB_TRY(tc_scores(ix->tc, a, bs, 3, alpha, bias, ws.scores.ptr, sample));
-            VB_TRY(select_rows(ws.scores.ptr, nq, sample, sample, ncand, 0, ws.cand.ptr, ncand));
             VB_TRY(ws.route_thr.reserve(nq));
-            VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>((nq + 3) / 4), 128, 0, ws.cand.ptr, ncand, q_dev,
-                      ix->dim, nq, ix->c_max_norm.ptr, ws.route_thr.ptr);
+            VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>(nq), ROUTE_THREADS, 0, ws.scores.ptr, sample, ncand,
+                      q_dev, ix->dim, ix->c_max_norm.ptr, ws.route_thr.ptr);
             uint32_t lists = 0, cap = 0;
             bool overflow = false;
             const uint32_t expected = static_cast<uint32_t>(static_cast<uint64_t>(ncand) * nlist / sample);
             VB_TRY(tc_below_threshold(ix->tc, a, b, 3, alpha, bias, ws.route_thr.ptr, expected, ROUTE_MAX_PER_ROW,
                                       ws.route_keys, ws.route_cnt, &lists, &cap, &overflow));
             if (!overflow && lists <= 64) {
-                const uint32_t slots = next_pow2(lists * cap > 2 * ncand ? lists * cap : 2 * ncand);
-                const size_t smem = slots * sizeof(uint64_t) + ix->dim * sizeof(float);
+                const uint32_t slots = next_pow2(lists * cap > ROUTE_PICK_SMALL ? lists * cap : ROUTE_PICK_SMALL);
+                const size_t smem = (static_cast<size_t>(slots) + ROUTE_PICK_SMALL) * sizeof(uint64_t) + ix->dim * sizeof(float);
                 if (smem > 48 * 1024) {
                     VB_CUDA(cudaFuncSetAttribute(route_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)));
@@ -1277,7 +1649,7 @@ launch_scan(Kernel kernel, const ScanParams& p, size_t smem) {
 // (payload = inner id) in ws.keys.
 static int
 ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal, uint32_t nprobe,
-                const int32_t* probes_dev) {
+                const int32_t* probes_dev, const float* probe_dists_dev) {
     SearchWorkspace& ws = ix->ws;
     const bool sq8 = ix->quant == VB200_QUANT_SQ8;
     // SQ8 ranks with a re-associated distance and re-scores a few more survivors exactly.
@@ -1305,14 +1677,14 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     VB_TRY(ws.thr.reserve(nq));
     VB_TRY(ws.part.reserve(total * kscan));
     VB_TRY(ws.keys.reserve(nq * kfinal));
-    VB_TRY(ws.scalars.reserve(4));
+    VB_TRY(ws.scalars.reserve(5));
     if (sq8) {
         VB_TRY(ws.qw.reserve(nq * ix->dpad));
         VB_TRY(ws.qa.reserve(nq));
         VB_TRY(ws.merged.reserve(nq * kscan));
     }
     cudaStream_t st = current_stream();
-    VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, 4 * sizeof(uint64_t), st));
+    VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, 5 * sizeof(uint64_t), st));
     VB_CUDA(cudaMemsetAsync(ws.thr.ptr, 0xFF, nq * sizeof(uint32_t), st));
     VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
     const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
@@ -1332,12 +1704,12 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         tables.slot[ph] = ws.pair_slot[ph].ptr;
     }
     // Groups the pairs of one phase (0 / 1) or of both (2) by list; `drop` marks pruned pairs.
-    auto group_pairs = [&](uint32_t phase_sel, const uint8_t* drop) -> int {
+    auto group_pairs = [&](uint32_t phase_sel, const uint8_t* drop, uint32_t queries_per_item) -> int {
         VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
         VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
                   ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
-        VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->scan_order.ptr, nlist,
-                  static_cast<uint32_t>(qt), ix->code_size, ws.scalars.ptr);
+        VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->group_off.ptr, ix->scan_order.ptr, nlist,
+                  queries_per_item, ix->code_size, ws.scalars.ptr);
         VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
                   ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
         return 0;
@@ -1346,7 +1718,17 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     // dropped before the second phase is grouped, so they never become work items.
     const bool pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
     const bool split_phases = n_phases == 2 && (ws.exchange != nullptr || pruning);
-    VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr));
+    // SQ8 work items run on the tensor cores (32 queries per item).  That kernel does not test the lists'
+    // covering balls tile by tile as the SIMT kernel does: with list pruning on, the pairs of the second
+    // phase have just been tested against the bounds of the first (pair_drop_kernel), which are close to
+    // final, and a first phase has no bounds to test against.
+    const uint32_t scan_cap = next_pow2(kscan + SCAN_THREADS);
+    const bool tc_scan = sq8 && tensor_cores_enabled() && ix->codes_t.ptr != nullptr && ix->kchunks > 0 &&
+                         tcs_smem_bytes(ix->kchunks, scan_cap) <= 227 * 1024;
+    const bool tc_first = tc_scan, tc_second = tc_scan;
+    const uint32_t qt_first = tc_first ? TCS_QT : static_cast<uint32_t>(qt);
+    const uint32_t qt_second = tc_second ? TCS_QT : static_cast<uint32_t>(qt);
+    VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr, qt_first));
 
     ScanParams p{};
     p.codes = ix->codes.ptr;
@@ -1356,7 +1738,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.list_off = ix->list_off.ptr;
     p.nlist = nlist;
     p.k = kscan;
-    p.cap = next_pow2(kscan + SCAN_THREADS);
+    p.cap = scan_cap;
     p.thr_g = ws.thr.ptr;
     p.part = ws.part.ptr;
     p.queries = q_dev;
@@ -1406,11 +1788,17 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         }
     }
     if (sq8) {
+        const uint32_t dpad32 = ix->kchunks * 16;
+        if (tc_scan) {
+            VB_TRY(ws.qw8.reserve(nq * 3 * dpad32));
+            VB_TRY(ws.qscale.reserve(nq));
+        }
         VB_LAUNCH(sq8_query_prep_kernel, static_cast<uint32_t>((nq + 3) / 4), 128, 0, q_dev, nq, ix->dim,
-                  ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr);
+                  ix->dpad, ix->sq_scale.ptr, ix->sq_mid.ptr, ix->metric, ws.qw.ptr, ws.qa.ptr, dpad32,
+                  tc_scan ? ws.qw8.ptr : nullptr, tc_scan ? ws.qscale.ptr : nullptr);
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
-    auto launch_phases = [&](uint32_t first, uint32_t count, uint32_t queue_slot) -> int {
+    auto launch_phases = [&](uint32_t first, uint32_t count, uint32_t queue_slot, bool on_tensor_cores) -> int {
         for (uint32_t i = 0; i < 2; ++i) {
             const uint32_t src = i < count ? first + i : first;
             p.pair_off[i] = ws.pair_off[src].ptr;
@@ -1422,6 +1810,32 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         }
         p.n_phases = count;
         p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + queue_slot);
+        if (sq8 && on_tensor_cores) {
+            TcScanParams tp{};
+            tp.s = p;
+            tp.s.ball_centre = nullptr;   // this kernel tests no balls
+            tp.s.ball_radius = nullptr;
+            tp.s.ball_count = nullptr;
+            tp.codes_t = ix->codes_t.ptr;
+            tp.group_off = ix->group_off.ptr;
+            tp.kchunks = ix->kchunks;
+            tp.qw8 = ws.qw8.ptr;
+            tp.qscale = ws.qscale.ptr;
+            tp.count_scanned = ws.pruning ? 1u : 0u;
+            tp.spin_limit = tc_spin_limit();
+            tp.error_flag = reinterpret_cast<int*>(ws.scalars.ptr + 4);
+            const size_t smem = tcs_smem_bytes(ix->kchunks, p.cap);
+            VB_CUDA(cudaFuncSetAttribute(ivf_sq8_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+            VB_CUDA(cudaFuncSetAttribute(ivf_sq8_scan_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+            // Two CTAs per SM when the selection buffers allow it (each holds 256 of the SM's 512 tensor-memory
+            // columns); the CTAs are persistent and pull items from one queue, so a CTA that has to wait for
+            // a free slot simply finds less work left.
+            const uint32_t per_sm = 2 * (smem + 4096) <= 228 * 1024 ? 2u : 1u;   // + static shared memory and the per-CTA reserve
+            VB_LAUNCH(ivf_sq8_scan_tc_kernel, static_cast<uint32_t>(sm_count()) * per_sm, TCS_THREADS, smem, tp);
+            return 0;
+        }
         if (sq8) {
             size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
             return launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem);
@@ -1435,7 +1849,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     };
     p.order = ix->scan_order.ptr;
     if (split_phases) {
-        VB_TRY(launch_phases(0, 1, 1));
+        VB_TRY(launch_phases(0, 1, 1, tc_first));
         if (ws.exchange != nullptr) {
             // Sharded search: after the owner of each query's nearest list has scanned it, the
             // shards agree on the tightest bound any of them found, so the remaining lists are
@@ -1454,17 +1868,17 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         const uint8_t* drop = nullptr;
         if (pruning) {
             VB_TRY(ws.pair_drop.reserve(total));
-            VB_LAUNCH(pair_drop_kernel, static_cast<uint32_t>((total + 31) / 32), 256, 0, probes_dev, total, nprobe,
+            VB_LAUNCH(pair_drop_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, probes_dev, total, nprobe,
                       ws.first_live.ptr, nlist, ix->shard_rank, ix->shard_world, ix->list_off.ptr, q_dev, ix->dim,
                       ix->ball_centre.ptr, ix->ball_radius.ptr, ix->ball_count.ptr, ws.thr.ptr, ix->metric,
-                      ix->code_size,
+                      ix->code_size, probe_dists_dev, ix->list_radius.ptr,
                       ws.pair_drop.ptr, reinterpret_cast<unsigned long long*>(ws.scalars.ptr));
             drop = ws.pair_drop.ptr;
         }
-        VB_TRY(group_pairs(1u, drop));
-        VB_TRY(launch_phases(1, 1, 2));
+        VB_TRY(group_pairs(1u, drop, qt_second));
+        VB_TRY(launch_phases(1, 1, 2, tc_second));
     } else {
-        VB_TRY(launch_phases(0, n_phases, 1));
+        VB_TRY(launch_phases(0, n_phases, 1, tc_first));
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
     ix->scan_timed = true;
@@ -1527,11 +1941,14 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
     }
     // probes
     VB_TRY(ws.probes.reserve(nq * nprobe));
+    const float* probe_dists = nullptr;   // exact centroid distances of the probes, when routing ran here
     if (bucket_ids != nullptr) {
         VB_CUDA(cudaMemcpyAsync(ws.probes.ptr, bucket_ids, nq * nprobe * sizeof(int32_t),
                                 cudaMemcpyDefault, current_stream()));
     } else {
-        VB_TRY(ivf_route_device(ix, q_dev, nq, nprobe, ws.probes.ptr, nullptr));
+        VB_TRY(ws.probe_dists.reserve(nq * nprobe));
+        VB_TRY(ivf_route_device(ix, q_dev, nq, nprobe, ws.probes.ptr, ws.probe_dists.ptr));
+        probe_dists = ws.probe_dists.ptr;
     }
     // codec-specific query transform
     const float* q_scan = q_dev;
@@ -1541,7 +1958,7 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
                                            ws.qproc.ptr));
         q_scan = ws.qproc.ptr;
     }
-    VB_TRY(ivf_scan_device(ix, q_scan, nq, kscan, nprobe, ws.probes.ptr));
+    VB_TRY(ivf_scan_device(ix, q_scan, nq, kscan, nprobe, ws.probes.ptr, probe_dists));
     const uint64_t* keys = ws.keys.ptr;
     if (rerank) {
         VB_TRY(ws.keys2.reserve(nq * k));
@@ -1888,6 +2305,7 @@ ivf_commit_lists(vb200_ivf* ix, DevBuf<uint8_t>& new_codes, DevBuf<uint32_t>& ne
         VB_TRY(ix->ball_centre.reserve(static_cast<size_t>(nlist) * SQ8_BALLS * dim));
         VB_TRY(ix->ball_radius.reserve(static_cast<size_t>(nlist) * SQ8_BALLS));
         VB_TRY(ix->ball_count.reserve(nlist));
+        VB_TRY(ix->list_radius.reserve(nlist));
         const size_t balls_smem = 2 * static_cast<size_t>(SQ8_BALLS) * dim * sizeof(float);
         VB_CHECK_ARG(balls_smem <= 200 * 1024, "dim too large for the list-ball kernel");
         if (balls_smem > 48 * 1024) {
@@ -1896,9 +2314,37 @@ ivf_commit_lists(vb200_ivf* ix, DevBuf<uint8_t>& new_codes, DevBuf<uint32_t>& ne
         }
         VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr,
                   ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr,
-                  ix->ball_count.ptr);
+                  ix->ball_count.ptr, ix->list_radius.ptr);
+    }
+    DevBuf<int8_t> new_tiled;
+    DevBuf<uint32_t> new_group_off;
+    if (ix->quant == VB200_QUANT_SQ8 && n_new_stored > 0 && dim <= 512) {
+        // the tiled signed copy the tensor-core scan reads (a 128-row tile past a list's end runs into the
+        // next list or into 16 groups of padding; those rows are masked by the list length)
+        const uint32_t kchunks = (dim + 31) / 32 * 2;
+        std::vector<uint32_t> goff(nlist + 1);
+        uint64_t run = 0;
+        for (uint32_t l = 0; l < nlist; ++l) {
+            goff[l] = static_cast<uint32_t>(run);
+            run += (new_off[l + 1] - new_off[l] + 7) / 8;
+        }
+        goff[nlist] = static_cast<uint32_t>(run);
+        VB_CHECK_ARG(run + 16 < 0xFFFFFFFFull, "too many rows for the tiled code copy");
+        const size_t bytes = static_cast<size_t>(run + 16) * kchunks * 128;
+        VB_TRY(new_tiled.reserve(bytes));
+        VB_TRY(new_group_off.reserve(nlist + 1));
+        VB_CUDA(cudaMemsetAsync(new_tiled.ptr, 0, bytes, current_stream()));
+        VB_CUDA(cudaMemcpyAsync(new_group_off.ptr, goff.data(), (nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                                current_stream()));
+        const uint64_t work = n_new_stored * kchunks;
+        VB_LAUNCH(sq8_tile_codes_kernel, static_cast<uint32_t>((work + 255) / 256), 256, 0, new_codes.ptr, stride,
+                  new_off_dev.ptr, new_group_off.ptr, nlist, n_new_stored, kchunks, new_tiled.ptr);
+        VB_TRY(sync_stream());   // goff is a local
+        ix->kchunks = kchunks;
     }
     VB_TRY(sync_stream());
+    ix->codes_t = std::move(new_tiled);
+    ix->group_off = std::move(new_group_off);
     ix->code_norm = std::move(new_norm);
     ix->codes = std::move(new_codes);
     ix->pos_inner = std::move(new_inner);
@@ -2075,7 +2521,7 @@ vb200_ivf_memory_usage(vb200_ivf_t ix) {
     if (ix == nullptr) {
         return 0;
     }
-    return static_cast<int64_t>(ix->codes.bytes() + ix->pos_inner.bytes() + ix->labels.bytes() +
+    return static_cast<int64_t>(ix->codes.bytes() + ix->codes_t.bytes() + ix->pos_inner.bytes() + ix->labels.bytes() +
                                 ix->flat.bytes() + ix->centroids.bytes() + ix->rotation.bytes() +
                                 ix->list_off.bytes());
 }
@@ -2256,11 +2702,14 @@ vb200_ivf_search_filtered(vb200_ivf_t ix, const float* queries, uint64_t nq, uin
               ix->labels.ptr, ws.out_ids.ptr, ws.out_dists.ptr);
     VB_TRY(copy_out(ids, ws.out_ids.ptr, total));
     VB_TRY(copy_out(dists, ws.out_dists.ptr, total));
-    uint64_t scalars[4] = {0, 0, 0, 0};
+    uint64_t scalars[5] = {0, 0, 0, 0, 0};
     VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
     ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
     ix->last_scanned_bytes = static_cast<int64_t>(ws.pruning ? scalars[3] : scalars[0]);
+    if (scalars[4] != 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "the tensor-core scan gave up on a bounded wait");
+    }
     return 0;
 }
 
@@ -2306,11 +2755,14 @@ vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint
     VB_TRY(search_status);
     VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
               ix->labels.ptr, keys_dev, labels_dev);
-    uint64_t scalars[4] = {0, 0, 0, 0};
+    uint64_t scalars[5] = {0, 0, 0, 0, 0};
     VB_CUDA(cudaMemcpyAsync(scalars, ix->ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
     ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
     ix->last_scanned_bytes = static_cast<int64_t>(ix->ws.pruning ? scalars[3] : scalars[0]);
+    if (scalars[4] != 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "the tensor-core scan gave up on a bounded wait");
+    }
     return 0;
 }
 

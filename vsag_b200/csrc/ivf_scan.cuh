@@ -26,6 +26,17 @@ constexpr int SCAN_WARPS = SCAN_THREADS / 32;
 
 constexpr int SQ8_BALLS = 8;   // most covering balls a list can have for the SQ8 scan's pruning (3 .. 8 by its length)
 
+// A work item of the scan queue: queries (pairs pbeg .. pbeg + nqt of its phase) against one list.
+struct alignas(32) ScanItemDesc {
+    uint32_t list;
+    uint32_t pbeg;   // first pair of the item
+    uint32_t nqt;    // its number of pairs
+    uint32_t lbeg;   // first position of the list
+    uint32_t len;    // rows of the list
+    uint32_t goff;   // first 8-row group of the list in the tiled code copy (0 when there is none)
+    uint32_t pad0, pad1;
+};
+
 struct ScanParams {
     const uint8_t* codes;        // [positions x code_stride]
     uint32_t code_stride;        // bytes, multiple of 16
@@ -41,7 +52,7 @@ struct ScanParams {
     const uint32_t* pair_q[2];     // [pairs] query index
     const uint32_t* pair_slot[2];  // [pairs] output slot (query * nprobe + probe rank)
     const uint32_t* item_off[2];   // [nlist + 1] exclusive prefix of tiles, by position in `order`
-    const uint64_t* item_map[2];   // [items] list | tile << 32 of every work item, in queue order
+    const ScanItemDesc* item_map[2];   // [items] every work item, in queue order
     uint32_t n_phases;
     uint32_t nlist;
     uint32_t* item_counter;      // work queue head
@@ -175,12 +186,27 @@ struct TileSelect {
         }
     }
 
+    // The same for a kernel in which `nwarps` warps (numbered `warp`) share the selection and a round
+    // offers at most `incoming` candidates per query.
+    __device__ __forceinline__ void
+    make_room_w(int nqt, uint32_t warp, uint32_t lane, uint32_t nwarps, uint32_t incoming) {
+        for (int qi = static_cast<int>(warp); qi < nqt; qi += static_cast<int>(nwarps)) {
+            if (cnt[qi] + incoming > cap) {
+                compact(qi, lane);
+            }
+        }
+    }
+
     // End of the item: write each query's (at most k) best to its slot and publish the bound.
     // Fewer than k survivors are written unsorted: the merge does not need order.
     __device__ __forceinline__ void
     finish(int nqt, uint64_t* part, uint32_t* thr_g) {
-        const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        for (int qi = warp; qi < nqt; qi += SCAN_WARPS) {
+        finish_w(nqt, part, thr_g, threadIdx.x >> 5, threadIdx.x & 31, SCAN_WARPS);
+    }
+
+    __device__ __forceinline__ void
+    finish_w(int nqt, uint64_t* part, uint32_t* thr_g, uint32_t warp, uint32_t lane, uint32_t nwarps) {
+        for (int qi = static_cast<int>(warp); qi < nqt; qi += static_cast<int>(nwarps)) {
             if (cnt[qi] >= k) {
                 compact(qi, lane);
             }
@@ -225,14 +251,10 @@ scan_next_item(const ScanParams& p, uint32_t* s_item, ScanItem& it) {
     if (second) {
         item -= n0;
     }
-    const uint64_t entry = __ldg((second ? p.item_map[1] : p.item_map[0]) + item);
-    const uint32_t list = static_cast<uint32_t>(entry);
-    const uint32_t tile = static_cast<uint32_t>(entry >> 32);
-    const uint32_t first = (second ? p.pair_off[1] : p.pair_off[0])[list];
-    const uint32_t count = (second ? p.pair_cnt[1] : p.pair_cnt[0])[list];
-    it.list = list;
-    it.pbeg = first + tile * QT;
-    it.nqt = min(static_cast<uint32_t>(QT), count - tile * QT);
+    const uint4 head = __ldg(reinterpret_cast<const uint4*>((second ? p.item_map[1] : p.item_map[0]) + item));
+    it.list = head.x;
+    it.pbeg = head.y;
+    it.nqt = head.z;
     it.pair_q = second ? p.pair_q[1] : p.pair_q[0];
     it.pair_slot = second ? p.pair_slot[1] : p.pair_slot[0];
     return true;

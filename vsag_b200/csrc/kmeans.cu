@@ -6,6 +6,8 @@
 
 #include <cstdlib>
 
+#include <cub/device/device_radix_sort.cuh>
+
 #include "dense.cuh"
 
 namespace vb200 {
@@ -165,6 +167,37 @@ kmeans_prev_score_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim, 
     bound[i] = fmaf(-2.0f, ip, __ldg(c_sq + l));
 }
 
+// rows[c] = i for every flagged row i (order irrelevant), *count = how many.
+__global__ void
+kmeans_collect_flagged_kernel(const uint32_t* __restrict__ flags, uint64_t n, uint32_t* __restrict__ rows,
+                              uint32_t* __restrict__ count) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n && flags[i] != 0) {
+        rows[atomicAdd(count, 1u)] = static_cast<uint32_t>(i);
+    }
+}
+
+__global__ void
+kmeans_gather_rows_kernel(const float* __restrict__ x, uint32_t dim, const uint32_t* __restrict__ rows, uint64_t count,
+                          float* __restrict__ out) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e < count * dim) {
+        out[e] = x[static_cast<uint64_t>(rows[e / dim]) * dim + e % dim];
+    }
+}
+
+__global__ void
+kmeans_scatter_labels_kernel(const uint32_t* __restrict__ rows, uint64_t count, const int32_t* __restrict__ lab,
+                             const float* __restrict__ best, int32_t* __restrict__ labels, float* __restrict__ best_out) {
+    const uint64_t c = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c < count) {
+        labels[rows[c]] = lab[c];
+        if (best_out != nullptr) {
+            best_out[rows[c]] = best[c];
+        }
+    }
+}
+
 constexpr uint32_t KMEANS_TC_CANDIDATES = 4;
 constexpr uint64_t KMEANS_TC_SLICE = uint64_t{1} << 22;  // rows tiled at once
 
@@ -209,15 +242,38 @@ kmeans_assign_tc(KMeansWorkspace& ws, const float* x_dev, uint64_t n, uint32_t d
                       rows, dim, centroids_dev, ws.c_sq.ptr, k, prev_labels_dev + r0, ws.row_bound.ptr);
             row_bound = ws.row_bound.ptr;
         }
-        uint32_t n_split = 1;
+        uint32_t n_split = 1, n_flagged = 0;
+        VB_TRY(ws.row_flags.reserve(rows));
+        VB_CUDA(cudaMemsetAsync(ws.row_flags.ptr, 0, rows * sizeof(uint32_t), current_stream()));
         VB_TRY(tc_candidates(ws.tc, a, b, 3, -2.0f, ws.c_sq.ptr, m, 0, ws.cand, &n_split, ws.x_sq.ptr,
-                             ws.margin.ptr, row_bound));
+                             ws.margin.ptr, row_bound, ws.row_flags.ptr, &n_flagged));
         const uint32_t per_row = n_split * m;
         const uint32_t lanes = per_row >= 32 ? 32u : next_pow2(per_row);
         const uint64_t threads = rows * lanes;
         VB_LAUNCH(kmeans_pick_kernel, static_cast<uint32_t>((threads + 127) / 128), 128, 0, x_dev + r0 * dim, rows,
                   dim, centroids_dev, ws.c_sq.ptr, ws.cand.ptr, per_row, lanes, labels_dev + r0,
                   best_dev != nullptr ? best_dev + r0 : nullptr);
+        if (n_flagged > 0) {
+            // A candidate list of these rows ended full of columns within the error margin of its best (many
+            // near-equal centroids, or data far from the origin): the exact winner may not have been
+            // nominated.  They are decided by the fixed-order kernel over all centroids instead.
+            VB_TRY(ws.flagged_rows.reserve(n_flagged));
+            VB_TRY(ws.flagged_count.reserve(1));
+            VB_TRY(ws.flagged_x.reserve(static_cast<size_t>(n_flagged) * dim));
+            VB_TRY(ws.flagged_labels.reserve(n_flagged));
+            VB_TRY(ws.flagged_best.reserve(n_flagged));
+            VB_CUDA(cudaMemsetAsync(ws.flagged_count.ptr, 0, sizeof(uint32_t), current_stream()));
+            VB_LAUNCH(kmeans_collect_flagged_kernel, static_cast<uint32_t>((rows + 255) / 256), 256, 0, ws.row_flags.ptr,
+                      rows, ws.flagged_rows.ptr, ws.flagged_count.ptr);
+            const uint64_t elems = static_cast<uint64_t>(n_flagged) * dim;
+            VB_LAUNCH(kmeans_gather_rows_kernel, static_cast<uint32_t>((elems + 255) / 256), 256, 0, x_dev + r0 * dim, dim,
+                      ws.flagged_rows.ptr, n_flagged, ws.flagged_x.ptr);
+            VB_TRY(dense_argmin_f32(ws.flagged_x.ptr, n_flagged, centroids_dev, k, dim, -2.0f, ws.c_sq.ptr,
+                                    ws.flagged_labels.ptr, ws.flagged_best.ptr));
+            VB_LAUNCH(kmeans_scatter_labels_kernel, static_cast<uint32_t>((n_flagged + 255) / 256), 256, 0,
+                      ws.flagged_rows.ptr, n_flagged, ws.flagged_labels.ptr, ws.flagged_best.ptr, labels_dev + r0,
+                      best_dev != nullptr ? best_dev + r0 : nullptr);
+        }
     }
     return 0;
 }
@@ -249,29 +305,83 @@ kmeans_assign_device(KMeansWorkspace& ws, const float* x_dev, uint64_t n, uint32
     return 0;
 }
 
-// sums[label][d..d+3] += x[i][d..d+3]; one thread per (point, group of up to 4 dimensions).
+// Centroid sums in a fixed order.  The reference adds the rows of a cluster in 1024-point chunks whose
+// partial sums it merges in thread-completion order (kmeans_cluster.cpp:106-172), so its own centroids
+// vary from run to run in the last bits.  Here every cluster is summed in ascending row order, one
+// fp32 addition per row -- the order the CPU oracle uses -- so training is reproducible bit for bit:
+// rows are sorted by (label, row) with a stable radix sort, and one CTA per cluster walks its rows.
+
+// keys[i] = label of row i (k for rows without a valid label), rows[i] = i, counts[label]++.
 __global__ void
-kmeans_accumulate_kernel(const float* __restrict__ x, uint64_t n, uint32_t dim,
-                         const int32_t* __restrict__ labels, uint32_t k, float* __restrict__ sums,
-                         int32_t* __restrict__ counts) {
-    const uint32_t groups = (dim + 3) / 4;
-    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (e >= n * groups) {
+kmeans_sort_keys_kernel(const int32_t* __restrict__ labels, uint64_t n, uint32_t k, uint32_t* __restrict__ keys,
+                        uint32_t* __restrict__ rows, int32_t* __restrict__ counts) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) {
         return;
     }
-    uint64_t i = e / groups;
-    uint32_t g = static_cast<uint32_t>(e % groups);
-    int32_t l = labels[i];
-    if (l < 0 || static_cast<uint32_t>(l) >= k) {
-        return;
-    }
-    if (g == 0) {
+    const int32_t l = labels[i];
+    const bool ok = l >= 0 && static_cast<uint32_t>(l) < k;
+    keys[i] = ok ? static_cast<uint32_t>(l) : k;
+    rows[i] = static_cast<uint32_t>(i);
+    if (ok) {
         atomicAdd(counts + l, 1);
     }
-    const float* p = x + i * dim;
-    float* s = sums + static_cast<uint64_t>(l) * dim;
-    for (uint32_t d = g * 4; d < dim && d < g * 4 + 4; ++d) {
-        atomicAdd(s + d, __ldg(p + d));
+}
+
+// off[j] = number of rows in clusters before j (one CTA; k is small next to the rows).
+__global__ void __launch_bounds__(1024)
+kmeans_cluster_offsets_kernel(const int32_t* __restrict__ counts, uint32_t k, uint32_t* __restrict__ off) {
+    __shared__ uint32_t part[1024];
+    const uint32_t per = (k + 1023) / 1024;
+    const uint32_t j0 = threadIdx.x * per, j1 = j0 + per < k ? j0 + per : k;
+    uint32_t sum = 0;
+    for (uint32_t j = j0; j < j1; ++j) {
+        sum += static_cast<uint32_t>(counts[j]);
+    }
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    for (uint32_t o = 1; o < 1024; o <<= 1) {
+        const uint32_t v = threadIdx.x >= o ? part[threadIdx.x - o] : 0u;
+        __syncthreads();
+        part[threadIdx.x] += v;
+        __syncthreads();
+    }
+    uint32_t run = part[threadIdx.x] - sum;
+    for (uint32_t j = j0; j < j1; ++j) {
+        off[j] = run;
+        run += static_cast<uint32_t>(counts[j]);
+    }
+    if (threadIdx.x == 1023) {
+        off[k] = part[1023];
+    }
+}
+
+// sums[j][d] = ((x[r0][d] + x[r1][d]) + x[r2][d]) + ... over the rows r0 < r1 < ... of cluster j.  One CTA
+// per cluster, one thread per dimension (strided when dim exceeds the CTA); the loads of eight rows are
+// issued together, the additions stay in row order.
+__global__ void __launch_bounds__(128)
+kmeans_sum_in_order_kernel(const float* __restrict__ x, uint32_t dim, const uint32_t* __restrict__ sorted_rows,
+                           const uint32_t* __restrict__ off, float* __restrict__ sums) {
+    const uint32_t j = blockIdx.x;
+    const uint32_t beg = off[j], end = off[j + 1];
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        float s = 0.f;
+        uint32_t r = beg;
+        for (; r + 8 <= end; r += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = __ldg(x + static_cast<uint64_t>(__ldg(sorted_rows + r + i)) * dim + d);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                s = __fadd_rn(s, v[i]);
+            }
+        }
+        for (; r < end; ++r) {
+            s = __fadd_rn(s, __ldg(x + static_cast<uint64_t>(__ldg(sorted_rows + r)) * dim + d));
+        }
+        sums[static_cast<uint64_t>(j) * dim + d] = s;
     }
 }
 
@@ -299,15 +409,38 @@ int
 kmeans_update_device(KMeansWorkspace& ws, const float* x_dev, uint64_t n, uint32_t dim,
                      const int32_t* labels_dev, uint32_t k, uint32_t iter, float* centroids_dev) {
     const size_t kd = static_cast<size_t>(k) * dim;
+    VB_CHECK_ARG(n < 0xFFFFFFFFull, "kmeans update: batch too large");
     VB_TRY(ws.sums.reserve(kd));
     VB_TRY(ws.counts.reserve(k));
-    VB_CUDA(cudaMemsetAsync(ws.sums.ptr, 0, kd * sizeof(float), current_stream()));
-    VB_CUDA(cudaMemsetAsync(ws.counts.ptr, 0, k * sizeof(int32_t), current_stream()));
-    const uint64_t groups = (dim + 3) / 4;
-    uint64_t blocks = (n * groups + 255) / 256;
-    VB_CHECK_ARG(blocks <= 0x7fffffffu, "kmeans update: batch too large");
-    VB_LAUNCH(kmeans_accumulate_kernel, static_cast<uint32_t>(blocks), 256, 0, x_dev, n, dim,
-              labels_dev, k, ws.sums.ptr, ws.counts.ptr);
+    VB_TRY(ws.sort_keys_in.reserve(n));
+    VB_TRY(ws.sort_keys_out.reserve(n));
+    VB_TRY(ws.sort_rows_in.reserve(n));
+    VB_TRY(ws.sort_rows_out.reserve(n));
+    VB_TRY(ws.cluster_off.reserve(static_cast<size_t>(k) + 1));
+    cudaStream_t st = current_stream();
+    VB_CUDA(cudaMemsetAsync(ws.counts.ptr, 0, k * sizeof(int32_t), st));
+    VB_LAUNCH(kmeans_sort_keys_kernel, static_cast<uint32_t>((n + 255) / 256), 256, 0, labels_dev, n, k,
+              ws.sort_keys_in.ptr, ws.sort_rows_in.ptr, ws.counts.ptr);
+    {
+        // stable sort by label: rows of a cluster stay in ascending order
+        int end_bit = 1;
+        while ((uint64_t{1} << end_bit) <= k) {
+            ++end_bit;
+        }
+        size_t tmp_bytes = 0;
+        VB_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, ws.sort_keys_in.ptr, ws.sort_keys_out.ptr,
+                                                ws.sort_rows_in.ptr, ws.sort_rows_out.ptr, static_cast<int64_t>(n), 0,
+                                                end_bit, st));
+        VB_TRY(ws.sort_tmp.reserve(tmp_bytes > 0 ? tmp_bytes : 1));
+        tmp_bytes = ws.sort_tmp.cap;
+        VB_CUDA(cub::DeviceRadixSort::SortPairs(ws.sort_tmp.ptr, tmp_bytes, ws.sort_keys_in.ptr, ws.sort_keys_out.ptr,
+                                                ws.sort_rows_in.ptr, ws.sort_rows_out.ptr, static_cast<int64_t>(n), 0,
+                                                end_bit, st));
+        g_kernel_launches.fetch_add(1);
+    }
+    VB_LAUNCH(kmeans_cluster_offsets_kernel, 1, 1024, 0, ws.counts.ptr, k, ws.cluster_off.ptr);
+    VB_LAUNCH(kmeans_sum_in_order_kernel, k, 128, 0, x_dev, dim, ws.sort_rows_out.ptr, ws.cluster_off.ptr,
+              ws.sums.ptr);
     VB_LAUNCH(kmeans_finalize_kernel, static_cast<uint32_t>((kd + 255) / 256), 256, 0, x_dev, n, dim,
               k, iter, ws.sums.ptr, ws.counts.ptr, centroids_dev);
     return 0;
@@ -695,6 +828,12 @@ vb200_kmeans_assign_noalloc(const float* data_dev, uint64_t count, uint32_t dim,
     VB_TRY(row_sqnorm_f32(centroids_dev, k, dim, c_sq));
     VB_TRY(dense_argmin_f32(data_dev, count, centroids_dev, k, dim, -2.0f, c_sq, labels_dev, nullptr));
     return sync_stream();
+}
+
+extern "C" int
+vb200_debug_set_wait_limit(int32_t polls) {
+    tc_set_spin_limit(polls < 0 ? TC_SPIN_LIMIT : static_cast<uint32_t>(polls));
+    return 0;
 }
 
 extern "C" int

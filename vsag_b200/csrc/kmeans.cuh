@@ -11,6 +11,9 @@ struct KMeansWorkspace {
     DevBuf<float> best;     // best score per point
     DevBuf<float> sums;     // k x dim accumulators
     DevBuf<int32_t> counts; // k
+    // centroid update in a fixed order: rows sorted by (label, row), the first row of each cluster
+    DevBuf<uint32_t> sort_keys_in, sort_keys_out, sort_rows_in, sort_rows_out, cluster_off;
+    DevBuf<uint8_t> sort_tmp;
     DevBuf<double> err;     // 1
     // tensor-core path: tiled bf16 terms of the points (kept while the same rows are assigned
     // again, i.e. across Lloyd iterations) and of the centroids, candidates, kernel scratch
@@ -18,6 +21,11 @@ struct KMeansWorkspace {
     DevBuf<float> x_sq;       // |x_i|^2 of the tiled rows
     DevBuf<float> margin;     // 1e-3 * max_j |c_j|
     DevBuf<float> row_bound;  // score of each row against its previous centroid (warm start)
+    // rows whose tensor-core candidate lists may have lost a column (flagged by the kernel) are decided by
+    // the fixed-order kernel over all centroids
+    DevBuf<uint32_t> row_flags, flagged_rows, flagged_count;
+    DevBuf<float> flagged_x, flagged_best;
+    DevBuf<int32_t> flagged_labels;
     const float* tiled_rows = nullptr;
     uint64_t tiled_n = 0;
     uint32_t tiled_dim = 0;

@@ -9,6 +9,18 @@ namespace vb200 {
 
 constexpr uint32_t TC_MAX_STAGES = 6;   // operand stages in flight; the launch picks how many fit
 
+static std::atomic<uint32_t> g_spin_limit{TC_SPIN_LIMIT};
+
+uint32_t
+tc_spin_limit() {
+    return g_spin_limit.load(std::memory_order_relaxed);
+}
+
+void
+tc_set_spin_limit(uint32_t polls) {
+    g_spin_limit.store(polls, std::memory_order_relaxed);
+}
+
 __device__ __forceinline__ float
 widen_in(float v) {
     return v;
@@ -231,7 +243,7 @@ tc_candidates_kernel(const TcParams p) {
                 uint32_t mtile, ntile0, tiles;
                 open_item(item, mtile, ntile0, tiles);
                 if (a_res && tiles > 0) {
-                    ok = mbar_wait(&sh.a_full, a_phase);
+                    ok = mbar_wait(&sh.a_full, a_phase, p.spin_limit);
                     a_phase ^= 1u;
                     if (!ok) {
                         break;
@@ -241,7 +253,7 @@ tc_candidates_kernel(const TcParams p) {
                     const uint32_t idesc = (tiles - t >= 2 && step == 2) ? idesc_two : idesc_one;
                     if (tiles_started >= 2) {
                         // the epilogue must have drained this accumulator's previous tile
-                        ok = mbar_wait(&sh.acc_free[acc], acc_phase ^ 1u);
+                        ok = mbar_wait(&sh.acc_free[acc], acc_phase ^ 1u, p.spin_limit);
                         if (!ok) {
                             break;
                         }
@@ -249,7 +261,7 @@ tc_candidates_kernel(const TcParams p) {
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * acc_cols;
                     for (uint32_t c = 0; c < chunks && ok; ++c) {
-                        ok = mbar_wait(&sh.full[m_stage], m_phase);
+                        ok = mbar_wait(&sh.full[m_stage], m_phase, p.spin_limit);
                         if (!ok) {
                             break;
                         }
@@ -319,7 +331,7 @@ tc_candidates_kernel(const TcParams p) {
                         continue;
                     }
                     if (n_loaded > 0) {
-                        ok = mbar_wait(&sh.a_free, a_phase);   // previous item's MMAs are done with it
+                        ok = mbar_wait(&sh.a_free, a_phase, p.spin_limit);   // previous item's MMAs are done with it
                         a_phase ^= 1u;
                         if (!ok) {
                             break;
@@ -348,7 +360,7 @@ tc_candidates_kernel(const TcParams p) {
                         for (uint32_t c = 0; c < chunks; ++c) {
                             if (count >= p.stages) {
                                 // the stage's previous use must have been consumed by the tensor core
-                                ok = mbar_wait(&sh.freed[stage], phase ^ 1u);
+                                ok = mbar_wait(&sh.freed[stage], phase ^ 1u, p.spin_limit);
                                 if (!ok) {
                                     break;
                                 }
@@ -427,7 +439,7 @@ tc_candidates_kernel(const TcParams p) {
             uint32_t bc0 = 0xFFFFFFFFu, bc1 = 0xFFFFFFFFu, bc2 = 0xFFFFFFFFu, bc3 = 0xFFFFFFFFu;
             for (uint64_t t = t0; t < t1 && ok; t += step, ++gtile) {
                 const uint32_t acc = static_cast<uint32_t>(gtile & 1);
-                ok = mbar_wait_relaxed(&sh.acc_full[acc], static_cast<uint32_t>((gtile >> 1) & 1));
+                ok = mbar_wait_relaxed(&sh.acc_full[acc], static_cast<uint32_t>((gtile >> 1) & 1), p.spin_limit);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     break;
@@ -627,6 +639,12 @@ tc_candidates_kernel(const TcParams p) {
                 continue;
             }
             if (SMALL_M) {
+                if (valid_row && p.row_flags != nullptr && margin >= 0.f && bc3 != 0xFFFFFFFFu && bs3 <= bs0 + margin) {
+                    // all four slots hold columns within the margin of the best: a fifth may have been turned away
+                    if (atomicExch(p.row_flags + grow, 1u) == 0u) {
+                        atomicAdd(p.error_flag + 1, 1);
+                    }
+                }
                 if (valid_row) {
                     uint64_t* dst = p.out + ((grow * p.n_split + split) * TC_COL_GROUPS + cgroup) * p.m;
                     const float fs[4] = {bs0, bs1, bs2, bs3};
@@ -661,6 +679,14 @@ tc_candidates_kernel(const TcParams p) {
 
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) {
+        sh.failed = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(p.error_flag)) & 1u;
+    }
+    __syncthreads();
+    if (sh.failed != 0) {
+        tc_drain_pause();   // a wait gave up somewhere: let what is still in flight land before the CTA lets go
+        __syncthreads();
+    }
     if (warp == TC_EPI_WARPS) {
         tmem_dealloc(tmem_base, 2 * acc_cols);
     }
@@ -738,7 +764,7 @@ int
 tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
               const float* bias_dev, uint32_t m, uint32_t col_base, DevBuf<uint64_t>& out,
               uint32_t* n_split_out, const float* a_sq_dev, const float* margin_scale_dev,
-              const float* row_bound_dev) {
+              const float* row_bound_dev, uint32_t* row_flags_dev, uint32_t* n_flagged_out) {
     VB_CHECK_ARG(a.rows > 0 && b.rows > 0, "tc_candidates: empty operand");
     VB_CHECK_ARG(a.chunks == b.chunks && a.chunks > 0, "tc_candidates: operand depths differ");
     VB_CHECK_ARG(n_terms == 1 || n_terms == 3, "tc_candidates: 1 or 3 terms");
@@ -783,12 +809,14 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
     p.col_base = col_base;
     VB_TRY(ws.scratch.reserve(static_cast<size_t>(grid) * TC_BM * TC_COL_GROUPS * p.cap));
-    VB_TRY(ws.error_flag.reserve(1));
+    VB_TRY(ws.error_flag.reserve(2));
     VB_TRY(out.reserve(static_cast<size_t>(a.rows) * n_split * TC_COL_GROUPS * m));
-    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
+    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
     p.scratch = ws.scratch.ptr;
     p.out = out.ptr;
     p.error_flag = ws.error_flag.ptr;
+    p.spin_limit = tc_spin_limit();
+    p.row_flags = row_flags_dev;
 
     const bool small_m = m <= 4;
     const size_t sort_bytes = small_m ? 0 : TC_EPI_WARPS * static_cast<size_t>(p.cap) * sizeof(uint64_t);
@@ -797,13 +825,16 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     auto kernel = small_m ? tc_candidates_kernel<0> : tc_candidates_kernel<1>;
     VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
-    int flag = 0;
-    VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
+    int flags[2] = {0, 0};
+    VB_CUDA(cudaMemcpyAsync(flags, ws.error_flag.ptr, 2 * sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
-    if ((flag & 1) != 0) {
+    if ((flags[0] & 1) != 0) {
         VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
     }
     *n_split_out = static_cast<uint32_t>(n_split) * TC_COL_GROUPS;
+    if (n_flagged_out != nullptr) {
+        *n_flagged_out = static_cast<uint32_t>(flags[1]);
+    }
     return 0;
 }
 
@@ -859,11 +890,12 @@ tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint
     p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
     VB_TRY(out.reserve(static_cast<size_t>(a.rows) * lists * cap));
     VB_TRY(out_count.reserve(static_cast<size_t>(a.rows) * lists));
-    VB_TRY(ws.error_flag.reserve(1));
-    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
+    VB_TRY(ws.error_flag.reserve(2));
+    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
     p.out = out.ptr;
     p.out_count = out_count.ptr;
     p.error_flag = ws.error_flag.ptr;
+    p.spin_limit = tc_spin_limit();
     size_t smem = 0;
     tc_plan(p, 0, &smem);
     auto kernel = tc_candidates_kernel<3>;
@@ -915,9 +947,10 @@ tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_te
     p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
     p.store = scores_dev;
     p.store_ld = ld;
-    VB_TRY(ws.error_flag.reserve(1));
-    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, sizeof(int), current_stream()));
+    VB_TRY(ws.error_flag.reserve(2));
+    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
     p.error_flag = ws.error_flag.ptr;
+    p.spin_limit = tc_spin_limit();
     size_t smem = 0;
     tc_plan(p, 0, &smem);
     auto kernel = tc_candidates_kernel<2>;

@@ -59,8 +59,21 @@ struct TcParams {
     uint32_t col_base;        // added to column indices in the keys
     float* store;             // score-matrix mode: [a.rows][store_ld] fp32 scores instead of candidates
     uint64_t store_ld;        // row stride of `store` in floats (multiple of 4, store 16-byte aligned)
-    int* error_flag;          // set non-zero if a bounded wait gave up
+    int* error_flag;          // [0] set non-zero if a bounded wait gave up; [1] counts the rows flagged below
+    uint32_t spin_limit;      // polls a wait may take before it gives up
+    uint32_t* row_flags;      // m <= 4 mode with a margin, optional: [a.rows], set to 1 for a row one of whose
+                              // lists ended full of columns within the margin of its best -- a column the list
+                              // had no room for might be the exact winner, so the caller decides such rows exactly
 };
+
+// A kernel whose wait ran out returns only after this pause, so that the copies and MMAs it still
+// has in flight land in shared and tensor memory it still owns.
+__device__ __forceinline__ void
+tc_drain_pause() {
+    for (int i = 0; i < 64; ++i) {
+        __nanosleep(1000);
+    }
+}
 
 // ---- raw PTX wrappers -----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t
@@ -86,8 +99,8 @@ mbar_arrive(uint64_t* bar) {
 
 // Bounded wait: returns false (and the caller bails out) if the phase never completes.
 __device__ __forceinline__ bool
-mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = TC_SPIN_LIMIT) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\n"
@@ -106,8 +119,8 @@ mbar_wait(uint64_t* bar, uint32_t parity) {
 // The same wait for the many epilogue threads: between polls they sleep, so that their polling
 // does not take issue slots from the three single threads that feed the tensor core.
 __device__ __forceinline__ bool
-mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = TC_SPIN_LIMIT) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\n"
@@ -222,6 +235,11 @@ umma_idesc_bf16(uint32_t m, uint32_t n) {
 
 // ---- host API (tc_gemm.cu) ------------------------------------------------------------------
 
+// Polls a bounded wait of the tensor-core kernels may take before it gives up (default
+// TC_SPIN_LIMIT).  Lowered only by tests that want to see the error path.
+uint32_t tc_spin_limit();
+void tc_set_spin_limit(uint32_t polls);
+
 // Bytes of one pre-tiled term for `rows` x `dim`.
 size_t tc_tiled_elems(uint64_t rows, uint32_t dim);
 // fp32 rows -> hi (and lo when lo_dev != nullptr) bf16 terms in the tiled layout.
@@ -241,10 +259,14 @@ struct TcWorkspace {
 // c such that |approximate score - exact score| << c * |A_i|; columns scoring worse than the row's
 // best by more than that margin are not nominated at all.  row_bound_dev (optional, needs the
 // margin): per row, the exact score of some column; nothing worse than it plus the margin is visited.
+// row_flags_dev / n_flagged_out (optional, with the margin): rows whose candidate lists may have lost a
+// column within the margin (see TcParams::row_flags) are marked and counted; the array must be zeroed by
+// the caller.
 int tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
                   const float* bias_dev, uint32_t m, uint32_t col_base, DevBuf<uint64_t>& out,
                   uint32_t* n_split_out, const float* a_sq_dev = nullptr,
-                  const float* margin_scale_dev = nullptr, const float* row_bound_dev = nullptr);
+                  const float* margin_scale_dev = nullptr, const float* row_bound_dev = nullptr,
+                  uint32_t* row_flags_dev = nullptr, uint32_t* n_flagged_out = nullptr);
 
 // Every column of B whose score alpha * <a, b> + bias lies below the row's threshold row_thr_dev[row],
 // unsorted, in out[a.rows][lists][cap] with the number offered to each list in out_count[a.rows][lists]
