@@ -45,12 +45,17 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hdrs), default=0.0)
 
 
+def _extra_flags() -> list[str]:
+    """VB200_NVCC_FLAGS adds compiler flags (e.g. -DVB200_TCS_PROFILE for the scan kernel's cycle counters)."""
+    return os.environ.get("VB200_NVCC_FLAGS", "").split()
+
+
 def _compile(src: Path, force: bool, verbose: bool) -> Path:
     obj = OBJ_DIR / (src.stem + ".o")
     newest = max(src.stat().st_mtime, _headers_mtime())
     if not force and obj.exists() and obj.stat().st_mtime >= newest:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), "-x", "cu", "-c", str(src), "-o", str(obj)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     log = OBJ_DIR / (src.stem + ".ptxas.log")
     log.write_text(res.stdout + res.stderr)

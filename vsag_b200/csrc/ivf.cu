@@ -1717,14 +1717,15 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     // SQ8 with list pruning: the first phase runs alone, then the pairs its bounds rule out are
     // dropped before the second phase is grouped, so they never become work items.
     const bool pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
+    const uint32_t scan_cap = next_pow2(kscan + SCAN_THREADS);
+    const bool tc_scan = sq8 && tensor_cores_enabled() && ix->codes_t.ptr != nullptr && ix->kchunks > 0 &&
+                         tcs_buffer_cap(kscan) <= 32 * TCS_SELECT_MAX &&
+                         tcs_smem_bytes(ix->kchunks, tcs_buffer_cap(kscan), 2) + 4096 <= 227 * 1024;
     const bool split_phases = n_phases == 2 && (ws.exchange != nullptr || pruning);
     // SQ8 work items run on the tensor cores (32 queries per item).  That kernel does not test the lists'
     // covering balls tile by tile as the SIMT kernel does: with list pruning on, the pairs of the second
     // phase have just been tested against the bounds of the first (pair_drop_kernel), which are close to
     // final, and a first phase has no bounds to test against.
-    const uint32_t scan_cap = next_pow2(kscan + SCAN_THREADS);
-    const bool tc_scan = sq8 && tensor_cores_enabled() && ix->codes_t.ptr != nullptr && ix->kchunks > 0 &&
-                         tcs_smem_bytes(ix->kchunks, scan_cap) <= 227 * 1024;
     const bool tc_first = tc_scan, tc_second = tc_scan;
     const uint32_t qt_first = tc_first ? TCS_QT : static_cast<uint32_t>(qt);
     const uint32_t qt_second = tc_second ? TCS_QT : static_cast<uint32_t>(qt);
@@ -1816,6 +1817,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             tp.s.ball_centre = nullptr;   // this kernel tests no balls
             tp.s.ball_radius = nullptr;
             tp.s.ball_count = nullptr;
+            tp.s.cap = tcs_buffer_cap(p.k);   // this kernel's buffers are small: a full one is compacted and the offer retried
             tp.codes_t = ix->codes_t.ptr;
             tp.group_off = ix->group_off.ptr;
             tp.kchunks = ix->kchunks;
@@ -1824,16 +1826,50 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             tp.count_scanned = ws.pruning ? 1u : 0u;
             tp.spin_limit = tc_spin_limit();
             tp.error_flag = reinterpret_cast<int*>(ws.scalars.ptr + 4);
-            const size_t smem = tcs_smem_bytes(ix->kchunks, p.cap);
+            // Two CTAs per SM when they fit (each holds 256 of the SM's 512 tensor-memory columns), with as many
+            // code tiles in flight as the shared memory left allows; the CTAs are persistent and pull items
+            // from one queue, so a CTA that has to wait for a free slot simply finds less work left.
+            const size_t sm_bytes = 228 * 1024, reserve = 4096;   // static shared memory and the per-CTA reserve
+            uint32_t per_sm = 2, stages = 2;
+            if (2 * (tcs_smem_bytes(ix->kchunks, tp.s.cap, 2) + reserve) > sm_bytes) {
+                per_sm = 1;
+            }
+            while (stages < TCS_MAX_STAGES &&
+                   per_sm * (tcs_smem_bytes(ix->kchunks, tp.s.cap, stages + 1) + reserve) <= sm_bytes - (per_sm == 1 ? 1024 : 0)) {
+                ++stages;
+            }
+            tp.stages = stages;
+            const size_t smem = tcs_smem_bytes(ix->kchunks, tp.s.cap, stages);
+#ifdef VB200_TCS_PROFILE
+            static DevBuf<unsigned long long> prof_buf;
+            VB_TRY(prof_buf.reserve(static_cast<size_t>(sm_count()) * 2 * 24));
+            VB_CUDA(cudaMemsetAsync(prof_buf.ptr, 0, static_cast<size_t>(sm_count()) * 2 * 24 * sizeof(unsigned long long), st));
+            tp.prof = prof_buf.ptr;
+#endif
             VB_CUDA(cudaFuncSetAttribute(ivf_sq8_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)));
             VB_CUDA(cudaFuncSetAttribute(ivf_sq8_scan_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                          cudaSharedmemCarveoutMaxShared));
-            // Two CTAs per SM when the selection buffers allow it (each holds 256 of the SM's 512 tensor-memory
-            // columns); the CTAs are persistent and pull items from one queue, so a CTA that has to wait for
-            // a free slot simply finds less work left.
-            const uint32_t per_sm = 2 * (smem + 4096) <= 228 * 1024 ? 2u : 1u;   // + static shared memory and the per-CTA reserve
             VB_LAUNCH(ivf_sq8_scan_tc_kernel, static_cast<uint32_t>(sm_count()) * per_sm, TCS_THREADS, smem, tp);
+#ifdef VB200_TCS_PROFILE
+            {
+                const size_t n_cta = static_cast<size_t>(sm_count()) * per_sm;
+                std::vector<unsigned long long> h(n_cta * 24);
+                VB_CUDA(cudaMemcpyAsync(h.data(), prof_buf.ptr, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
+                VB_TRY(sync_stream());
+                double sum[24] = {0};
+                for (size_t c = 0; c < n_cta; ++c) {
+                    for (int i = 0; i < 24; ++i) {
+                        sum[i] += static_cast<double>(h[c * 24 + i]);
+                    }
+                }
+                std::fprintf(stderr, "tcs-prof ctas=%zu stages=%u cap=%u :", n_cta, stages, tp.s.cap);
+                for (int i = 0; i < 24; ++i) {
+                    std::fprintf(stderr, " %.0f", sum[i] / static_cast<double>(n_cta));
+                }
+                std::fprintf(stderr, "\n");
+            }
+#endif
             return 0;
         }
         if (sq8) {

@@ -154,6 +154,9 @@ struct TileSelect {
     __device__ __forceinline__ void
     compact(int qi, uint32_t lane) {
         uint32_t c = cnt[qi];
+        if (c > cap) {
+            c = cap;   // offers beyond the buffer were counted but not stored (the tensor-core scan retries them)
+        }
         uint64_t* kq = keys + static_cast<uint32_t>(qi) * cap;
         uint32_t n2 = next_pow2(c < 2 ? 2 : c);
         for (uint32_t i = c + lane; i < n2; i += 32) {

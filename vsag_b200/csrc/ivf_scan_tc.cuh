@@ -39,7 +39,8 @@ constexpr int TCS_ROWS = 128;                      // code rows per tile
 constexpr int TCS_EPI_WARPS = 8;                   // two per 32-lane quarter of tensor memory: 16 queries each
 constexpr int TCS_EPI_THREADS = 32 * TCS_EPI_WARPS;
 constexpr int TCS_THREADS = TCS_EPI_THREADS + 64;  // + one warp to issue the MMAs, one for the copies and the work queue
-constexpr int TCS_STAGES = 2;                          // code tiles in flight per CTA (two CTAs share an SM)
+constexpr int TCS_MAX_STAGES = 6;                  // code tiles in flight per CTA, at most (the launch picks how many fit)
+constexpr int TCS_MAX_ROUNDS = 40;                 // offer rounds a tile may take (it needs at most 128 / (cap - k) + 1)
 constexpr uint32_t TCS_ACC_COLS = 128;             // tensor-memory columns reserved per accumulator
 
 struct TcScanParams {
@@ -51,6 +52,10 @@ struct TcScanParams {
     const float* qscale;        // [nq] s of each query
     uint32_t count_scanned;     // add the items' code bytes to s.scanned
     uint32_t spin_limit;        // polls a wait may take before it gives up (TC_SPIN_LIMIT; tests pass less)
+    uint32_t stages;            // code tiles in flight per CTA, 2 .. TCS_MAX_STAGES
+#ifdef VB200_TCS_PROFILE
+    unsigned long long* prof;   // [grid][16] cycle counters of one thread per role (diagnostic builds only)
+#endif
     int* error_flag;
 };
 
@@ -100,8 +105,8 @@ struct TcsStaged {
 };
 
 struct TcsShared {
-    uint64_t full[TCS_STAGES];    // a tile's codes have landed
-    uint64_t freed[TCS_STAGES];   // the MMAs that read the stage have retired
+    uint64_t full[TCS_MAX_STAGES];    // a tile's codes have landed
+    uint64_t freed[TCS_MAX_STAGES];   // the MMAs that read the stage have retired
     uint64_t acc_full[2];         // accumulator holds a finished tile
     uint64_t acc_free[2];         // accumulator drained by the epilogue threads
     uint32_t tmem_base;
@@ -111,26 +116,36 @@ struct TcsShared {
     alignas(16) float cq[TCS_QT]; // coef_c * s of the running item's queries
 };
 
-// Bounded wait that also gives up as soon as another role of the CTA has failed.
+#ifdef VB200_TCS_PROFILE
+#define TCS_T0() const long long _t0 = clock64()
+#define TCS_ACC(slot) prof_acc[slot] += static_cast<unsigned long long>(clock64() - _t0)
+#define TCS_CNT(slot) prof_acc[slot] += 1
+#else
+#define TCS_T0()
+#define TCS_ACC(slot)
+#define TCS_CNT(slot)
+#endif
+
+// Bounded wait that also gives up as soon as another role of the CTA has failed.  Each poll may
+// suspend the thread in hardware for up to a microsecond and ends as soon as the phase completes, so
+// waiting threads neither spin on issue slots (the two single-thread roles share their schedulers with
+// epilogue warps) nor oversleep (the epilogue warps meet at a barrier after every tile).
 __device__ __forceinline__ bool
-tcs_wait(uint64_t* bar, uint32_t parity, const volatile uint32_t* failed, uint32_t limit, bool relaxed) {
+tcs_wait(uint64_t* bar, uint32_t parity, const volatile uint32_t* failed, uint32_t limit) {
     for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
             "selp.u32 %0, 1, 0, p;\n}"
             : "=r"(done)
-            : "r"(smem_u32(bar)), "r"(parity)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
             : "memory");
         if (done) {
             return true;
         }
-        if ((spin & 63u) == 63u && *failed != 0) {
+        if ((spin & 15u) == 15u && *failed != 0) {
             return false;
-        }
-        if (relaxed) {
-            __nanosleep(32);
         }
     }
     return false;
@@ -155,6 +170,89 @@ tcs_epilogue_barrier_any(bool flag) {
         : "memory");
     return out != 0;
 }
+
+// Sorts a query's candidate buffer in registers and cuts it to its k smallest keys (one warp).  Element
+// e of the buffer sits in register e / 32 of lane e % 32; the bitonic network exchanges registers of a
+// lane when the partner is 32 or more elements away and shuffles between lanes otherwise, so a sort of
+// 128 keys is 25 shuffle stages instead of 28 trips through shared memory with a warp barrier each.
+// Returns the k-th smallest key (KEY_INF when the buffer holds fewer than k: nothing is cut then).
+// Kept out of line: it runs once in many tiles and must not claim registers in the epilogue's loop.
+template <int R>
+__device__ __noinline__ uint64_t
+tcs_sort_cut(uint64_t* kq, uint32_t count, uint32_t k, uint32_t lane) {
+    uint64_t key[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const uint32_t i = r * 32 + lane;
+        key[r] = i < count ? kq[i] : KEY_INF;
+    }
+#pragma unroll
+    for (uint32_t size = 2; size <= 32u * R; size <<= 1) {
+#pragma unroll
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            if (stride >= 32) {
+                // partner in the same lane: registers r and r ^ (stride / 32)
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int pr = r ^ static_cast<int>(stride >> 5);
+                    if (pr > r) {
+                        const bool up = (((static_cast<uint32_t>(r) << 5) | lane) & size) == 0;
+                        const uint64_t a = key[r], b = key[pr];
+                        if ((a > b) == up) {
+                            key[r] = b;
+                            key[pr] = a;
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint32_t e = (static_cast<uint32_t>(r) << 5) | lane;
+                    const uint64_t mine = key[r];
+                    const uint64_t other = __shfl_xor_sync(0xffffffffu, mine, stride);
+                    const bool up = (e & size) == 0;
+                    const bool lower = (lane & stride) == 0;        // this lane holds the lower index of the pair
+                    const bool take_min = lower == up;
+                    key[r] = take_min ? (mine < other ? mine : other) : (mine > other ? mine : other);
+                }
+            }
+        }
+    }
+    if (count < k) {
+        return KEY_INF;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const uint32_t e = (static_cast<uint32_t>(r) << 5) | lane;
+        if (e < k) {
+            kq[e] = key[r];
+        }
+    }
+    uint64_t kth = 0;
+    const uint32_t last = k - 1;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const uint64_t v = __shfl_sync(0xffffffffu, key[r], last & 31u);
+        if (static_cast<uint32_t>(r) == (last >> 5)) {
+            kth = v;
+        }
+    }
+    __syncwarp();
+    return kth;
+}
+
+__device__ __forceinline__ uint64_t
+tcs_sort_cut_any(uint64_t* kq, uint32_t count, uint32_t k, uint32_t cap, uint32_t lane) {
+    if (cap <= 64) {
+        return tcs_sort_cut<2>(kq, count, k, lane);
+    }
+    if (cap <= 128) {
+        return tcs_sort_cut<4>(kq, count, k, lane);
+    }
+    return tcs_sort_cut<8>(kq, count, k, lane);
+}
+
+constexpr int TCS_SELECT_MAX = 8;   // keys per lane at most: buffers of up to 256 keys
 
 // Next work item from the queue (one thread).
 __device__ __forceinline__ void
@@ -196,8 +294,9 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     const uint32_t group_bytes = kchunks * 128;              // one 8-row group
     const uint32_t tile_bytes = TCS_ROWS * row_bytes;
     const uint32_t b_bytes = TCS_N * row_bytes;
-    unsigned char* a_smem = smem;                            // [TCS_STAGES][tile_bytes]
-    unsigned char* b_smem = smem + TCS_STAGES * tile_bytes;  // [2][TCS_N rows][row_bytes] in core layout
+    const uint32_t stages = tp.stages;
+    unsigned char* a_smem = smem;                            // [stages][tile_bytes]
+    unsigned char* b_smem = smem + stages * tile_bytes;      // [2][TCS_N rows][row_bytes] in core layout
     TileSelect<TCS_QT> ts;
     float* unused;
     tile_carve<TCS_QT>(b_smem + 2 * b_bytes, p.cap, 0, unused, ts);
@@ -206,9 +305,16 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     const uint32_t n0 = p.item_off[0][p.nlist];
     const uint32_t n1 = p.n_phases > 1 ? p.item_off[1][p.nlist] : 0u;
     const uint32_t spin_limit = tp.spin_limit;
+#ifdef VB200_TCS_PROFILE
+    // 0 E:wait acc  1 E:load+math  2 E:offer rounds+barrier  3 E:set-up+barrier 2  4 E:loop-top barrier  5 E:finish
+    // 6 M:wait acc_free  7 M:wait full  8 M:issue  9 P:wait freed  10 P:prepare  11 P:loop-top barrier
+    // 12 tiles  13 items  14 extra rounds  15 total cycles  16 E:offer loop  17 E:barrier_any  18 E:compaction+barrier  19 offers
+    unsigned long long prof_acc[24] = {0};
+    const long long prof_begin = clock64();
+#endif
 
     if (tid == 0) {
-        for (int s = 0; s < TCS_STAGES; ++s) {
+        for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(&sh.full[s], 1);
             mbar_init(&sh.freed[s], 1);
         }
@@ -243,15 +349,17 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
 
     // One code tile into the next stage (lane 0 of the copy warp).
     auto copy_tile = [&](const unsigned char* src) -> bool {
-        if (c_count >= TCS_STAGES) {
-            if (!tcs_wait(&sh.freed[c_stage], c_phase ^ 1u, failed, spin_limit, false)) {
+        if (c_count >= stages) {
+            TCS_T0();
+            if (!tcs_wait(&sh.freed[c_stage], c_phase ^ 1u, failed, spin_limit)) {
                 return false;
             }
+            TCS_ACC(9);
         }
         mbar_expect_tx(&sh.full[c_stage], tile_bytes);
         bulk_copy_g2s(a_smem + c_stage * tile_bytes, src, tile_bytes, &sh.full[c_stage]);
         ++c_count;
-        if (++c_stage == TCS_STAGES) {
+        if (++c_stage == stages) {
             c_stage = 0;
             c_phase ^= 1u;
         }
@@ -311,7 +419,7 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
             const uint32_t ntiles = (it.len + TCS_ROWS - 1) / TCS_ROWS;
             const unsigned char* a_src = reinterpret_cast<const unsigned char*>(tp.codes_t) +
                                          static_cast<uint64_t>(it.goff) * group_bytes;
-            const uint32_t ahead = ntiles < TCS_STAGES ? ntiles : TCS_STAGES;
+            const uint32_t ahead = ntiles < stages ? ntiles : stages;
             for (uint32_t t = 0; t < ahead && c_ok; ++t) {
                 c_ok = copy_tile(a_src + static_cast<uint64_t>(t) * tile_bytes);
                 if (c_ok) {
@@ -331,7 +439,11 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     }
 
     for (uint32_t n_item = 0;; ++n_item) {
-        __syncthreads();   // the previous item is finished by every role; this one has been prepared
+        {
+            TCS_T0();
+            __syncthreads();   // the previous item is finished by every role; this one has been prepared
+            TCS_ACC(warp == TCS_EPI_WARPS + 1 ? 11 : 4);
+        }
         const uint32_t buf = n_item & 1u;
         const TcsItem it = sh.item[buf];
         if (it.valid == 0 || sh.failed != 0) {
@@ -340,6 +452,17 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
         const int nqt = static_cast<int>(it.nqt);
         const uint32_t lbeg = it.lbeg, len = it.len;
         const uint32_t ntiles = (len + TCS_ROWS - 1) / TCS_ROWS;
+        {
+            // The candidate buffers of an item share one pool: an item with few queries gives each of them a
+            // larger buffer (up to about 4k keys), which spares a query without a bound yet -- every row is a
+            // candidate then -- most of its compactions.
+            uint32_t c = p.cap;
+            const uint32_t want = next_pow2(4 * p.k);
+            while (c < want && 2 * c <= 32 * TCS_SELECT_MAX && 2 * c * it.nqt <= p.cap * TCS_QT) {
+                c <<= 1;
+            }
+            ts.cap = c;
+        }
 
         if (warp == TCS_EPI_WARPS + 1) {
             // ---------------- the rest of this item's code tiles, then the next item ----------------
@@ -355,9 +478,15 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                 }
             }
             __syncwarp();
-            prepare_item(n_item + 1);
+            {
+                TCS_T0();
+                prepare_item(n_item + 1);
+                TCS_ACC(10);
+            }
             continue;   // the copy warp takes no part in the barriers below
         }
+        TCS_T0();
+        TCS_CNT(13);
         if (tid < TCS_QT) {
             // selection state of the item's queries from what the copy warp staged
             const TcsStaged& st = sh.staged[buf];
@@ -375,6 +504,7 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
             ts.cnt[qi] = 0;
         }
         asm volatile("bar.sync 2, %0;" ::"n"(TCS_EPI_THREADS + 32) : "memory");   // epilogue warps + the MMA warp
+        TCS_ACC(3);
 
         if (warp == TCS_EPI_WARPS) {
             // ---------------- MMA issue (one thread) ----------------
@@ -383,15 +513,22 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                 bool ok = true;
                 for (uint32_t t = 0; t < ntiles && ok; ++t) {
                     if (m_tiles >= 2) {
-                        ok = tcs_wait(&sh.acc_free[m_acc], m_acc_phase ^ 1u, failed, spin_limit, false);
+                        TCS_T0();
+                        ok = tcs_wait(&sh.acc_free[m_acc], m_acc_phase ^ 1u, failed, spin_limit);
+                        TCS_ACC(6);
                         if (!ok) {
                             break;
                         }
                     }
-                    ok = tcs_wait(&sh.full[m_stage], m_phase, failed, spin_limit, false);
+                    {
+                        TCS_T0();
+                        ok = tcs_wait(&sh.full[m_stage], m_phase, failed, spin_limit);
+                        TCS_ACC(7);
+                    }
                     if (!ok) {
                         break;
                     }
+                    TCS_T0();
                     tc_fence_after_sync();
                     const uint64_t a_desc = umma_desc(smem_u32(a_smem + m_stage * tile_bytes), 128, group_bytes);
                     const uint32_t d_tmem = tmem_base + m_acc * TCS_ACC_COLS;
@@ -401,7 +538,8 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                     }
                     umma_commit(&sh.freed[m_stage]);
                     umma_commit(&sh.acc_full[m_acc]);
-                    if (++m_stage == TCS_STAGES) {
+                    TCS_ACC(8);
+                    if (++m_stage == stages) {
                         m_stage = 0;
                         m_phase ^= 1u;
                     }
@@ -420,21 +558,48 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
         } else {
             // ---------------- epilogue: one thread per (row of the tile, half of the queries) ----------------
             const bool any_query = static_cast<int>(q_first) < nqt;   // this warp's half holds live queries
+            // one warp: query qi keeps its k best candidates, its bound becomes the k-th
+            auto compact_query = [&](int qi) {
+                const uint32_t have = ts.cnt[qi] < ts.cap ? ts.cnt[qi] : ts.cap;   // offers beyond the buffer were not stored
+                const uint64_t kth = tcs_sort_cut_any(ts.keys + static_cast<uint32_t>(qi) * ts.cap, have, ts.k, ts.cap, lane);
+                if (lane == 0) {
+                    ts.cnt[qi] = have < ts.k ? have : ts.k;
+                    if (kth != KEY_INF && static_cast<uint32_t>(kth >> 32) < ts.thr[qi]) {
+                        ts.set_bound(qi, static_cast<uint32_t>(kth >> 32));
+                    }
+                }
+                __syncwarp();
+            };
             for (uint32_t t = 0; t < ntiles; ++t, ++e_tile) {
                 const uint32_t acc = e_tile & 1u;
                 const uint32_t r = t * TCS_ROWS + row;
                 const bool valid = r < len;
                 const uint32_t pos = lbeg + (valid ? r : 0u);
                 const float xb = p.coef_b * __ldg(p.code_norm + pos);
-                bool need_room = false;
-                bool ok = tcs_wait(&sh.acc_full[acc], (e_tile >> 1) & 1u, failed, spin_limit, true);
-                ok = __all_sync(0xffffffffu, ok);
+                uint32_t pend = 0;   // bit j: this row is a candidate of query slot q_first + j that is not stored yet
+                uint32_t a1[16], a2[16], a3[16];
+                // sum_d w_d (code_d - 128) / s = A1 + (254 A2 + A3) / 254^2; A1 < 2^22 converts exactly through
+                // the float whose integer image is 1.5 * 2^23 + A1
+                auto partial_of = [&](int j, float cqj) -> float {
+                    const int32_t low = static_cast<int32_t>(a2[j]) * 254 + static_cast<int32_t>(a3[j]);
+                    const float hi = __int_as_float(static_cast<int32_t>(a1[j]) + 0x4B400000) - 12582912.0f;
+                    const float f = fmaf(static_cast<float>(low), 1.0f / 64516.0f, hi);
+                    return fmaf(cqj, f, xb);
+                };
+                TCS_CNT(12);
+                bool ok;
+                {
+                    TCS_T0();
+                    ok = tcs_wait(&sh.acc_full[acc], (e_tile >> 1) & 1u, failed, spin_limit);
+                    ok = __all_sync(0xffffffffu, ok);
+                    TCS_ACC(0);
+                }
+                TCS_T0();
                 if (!ok) {
                     sh.failed = 1;
                 } else {
                     tc_fence_after_sync();
                     const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * TCS_ACC_COLS + q_first;
-                    uint32_t a1[16], a2[16], a3[16];
                     if (any_query) {
                         tmem_load_16(taddr, a1);
                         tmem_load_16(taddr + TCS_QT, a2);
@@ -445,14 +610,6 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                     tc_fence_before_sync();
                     mbar_arrive(&sh.acc_free[acc]);
                     if (any_query && valid) {
-                        // sum_d w_d (code_d - 128) / s = A1 + (254 A2 + A3) / 254^2; A1 < 2^22 converts exactly
-                        // through the float whose integer image is 1.5 * 2^23 + A1
-                        auto partial_of = [&](int j, float cqj) -> float {
-                            const int32_t low = static_cast<int32_t>(a2[j]) * 254 + static_cast<int32_t>(a3[j]);
-                            const float hi = __int_as_float(static_cast<int32_t>(a1[j]) + 0x4B400000) - 12582912.0f;
-                            const float f = fmaf(static_cast<float>(low), 1.0f / 64516.0f, hi);
-                            return fmaf(cqj, f, xb);
-                        };
                         float worst = INFINITY;   // min over the queries of (distance - bound): <= 0 means a candidate
 #pragma unroll
                         for (int j4 = 0; j4 < 16; j4 += 4) {
@@ -463,46 +620,133 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                             worst = fminf(worst, partial_of(j4 + 2, cq4.z) - th4.z);
                             worst = fminf(worst, partial_of(j4 + 3, cq4.w) - th4.w);
                         }
-                        if (worst <= 0.f) {
-                            // Rare once the bounds have settled.  The threads of the warp that are here offer their
-                            // candidates query by query; those with a candidate for the same query take their slots
-                            // with one addition to the query's counter.
-                            const bool filtered = p.filter_pos_inner != nullptr && scan_row_filtered(p, pos);
+                        // rare once the bounds have settled
+                        if (worst <= 0.f && !(p.filter_pos_inner != nullptr && scan_row_filtered(p, pos))) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
-                                const int qi = static_cast<int>(q_first) + j;
-                                const float part = partial_of(j, sh.cq[qi]);
-                                const bool pass = !filtered && part <= ts.thrq[qi];   // unused slots: bound -inf
-                                const unsigned here = __activemask();
-                                const unsigned passing = __ballot_sync(here, pass);
-                                if (passing != 0) {
-                                    const int leader = __ffs(passing) - 1;
-                                    uint32_t base = 0;
-                                    if (static_cast<int>(lane) == leader) {
-                                        base = atomicAdd(&ts.cnt[qi], static_cast<uint32_t>(__popc(passing)));
-                                    }
-                                    base = __shfl_sync(here, base, leader);
-                                    if (pass) {
-                                        const uint32_t s = base + __popc(passing & ((1u << lane) - 1u));
-                                        ts.keys[static_cast<uint32_t>(qi) * ts.cap + s] = make_key(part + ts.qa[qi], pos);
-                                        need_room = need_room || s + 1 + TCS_ROWS > ts.cap;
-                                    }
+                                if (partial_of(j, sh.cq[q_first + j]) <= ts.thrq[q_first + j]) {   // unused slots: bound -inf
+                                    pend |= 1u << j;
                                 }
                             }
                         }
                     }
                 }
-                // one barrier per tile; a second one only when a query's buffer has to be compacted
-                if (tcs_epilogue_barrier_any(need_room)) {
-                    ts.make_room_w(nqt, warp, lane, TCS_EPI_WARPS, TCS_ROWS);
+                TCS_ACC(1);
+                const long long _t1 = clock64();
+                (void)_t1;
+                // Offer rounds.  The threads of a warp that hold a candidate for the same query take their slots
+                // in its buffer with one addition to its counter.  The buffers are small (k + 32 keys, rounded
+                // up): when one is full its query is compacted -- sorted, cut to k, bound tightened -- and the
+                // candidates that did not get in try again against the new bound.  One barrier per tile when
+                // nothing overflows.
+                for (int round = 0; round < TCS_MAX_ROUNDS; ++round) {
+                    bool overflow = false;
+#ifdef VB200_TCS_PROFILE
+                    const long long _o0 = clock64();
+#endif
+                    if (pend != 0) {
+                        TCS_CNT(19);
+                        // query slots for which some thread of the warp that is here holds a candidate
+                        const unsigned slots = __reduce_or_sync(__activemask(), pend);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (((slots >> j) & 1u) == 0) {
+                                continue;
+                            }
+                            const int qi = static_cast<int>(q_first) + j;
+                            bool want = ((pend >> j) & 1u) != 0;
+                            float part = 0.f;
+                            if (want) {
+                                part = partial_of(j, sh.cq[qi]);
+                                if (!(part <= ts.thrq[qi])) {   // the bound moved past it in a compaction
+                                    want = false;
+                                    pend &= ~(1u << j);
+                                }
+                            }
+                            const unsigned here = __activemask();
+                            const unsigned offering = __ballot_sync(here, want);
+                            if (offering != 0) {
+                                const int leader = __ffs(offering) - 1;
+                                uint32_t base = 0;
+                                if (static_cast<int>(lane) == leader) {
+                                    base = atomicAdd(&ts.cnt[qi], static_cast<uint32_t>(__popc(offering)));
+                                }
+                                base = __shfl_sync(here, base, leader);
+                                if (want) {
+                                    const uint32_t s = base + __popc(offering & ((1u << lane) - 1u));
+                                    if (s < ts.cap) {
+                                        ts.keys[static_cast<uint32_t>(qi) * ts.cap + s] = make_key(part + ts.qa[qi], pos);
+                                        pend &= ~(1u << j);
+                                    } else {
+                                        overflow = true;
+                                    }
+                                }
+                            }
+                        }
+                    }
+#ifdef VB200_TCS_PROFILE
+                    const long long _o1 = clock64();
+                    prof_acc[16] += static_cast<unsigned long long>(_o1 - _o0);
+                    const bool _any = tcs_epilogue_barrier_any(overflow);
+                    const long long _o2 = clock64();
+                    prof_acc[17] += static_cast<unsigned long long>(_o2 - _o1);
+                    if (!_any) {
+                        break;
+                    }
+#else
+                    if (!tcs_epilogue_barrier_any(overflow)) {
+                        break;
+                    }
+#endif
+                    TCS_CNT(14);
+                    for (int qi = static_cast<int>(warp); qi < nqt; qi += TCS_EPI_WARPS) {
+                        if (ts.cnt[qi] >= ts.cap) {
+                            compact_query(qi);
+                        }
+                    }
                     tcs_epilogue_barrier();
+#ifdef VB200_TCS_PROFILE
+                    prof_acc[18] += static_cast<unsigned long long>(clock64() - _o2);
+#endif
                 }
+                if (pend != 0) {
+                    sh.failed = 1;   // cannot happen: every round stores at least cap - k candidates of a full query
+                }
+#ifdef VB200_TCS_PROFILE
+                prof_acc[2] += static_cast<unsigned long long>(clock64() - _t1);
+#endif
             }
             tcs_epilogue_barrier();   // a failed wait of any warp is visible to all of them
-            if (sh.failed == 0) {
-                ts.finish_w(nqt, p.part, p.thr_g, warp, lane, TCS_EPI_WARPS);
-            } else if (tid == 0) {
-                atomicOr(tp.error_flag, 1);
+            {
+                TCS_T0();
+                if (sh.failed == 0) {
+                    // every query's (at most k) best to its slot, unordered; its bound to the global table
+                    for (int qi = static_cast<int>(warp); qi < nqt; qi += TCS_EPI_WARPS) {
+                        if (ts.cnt[qi] > ts.k) {
+                            compact_query(qi);
+                        }
+                        const uint32_t c = ts.cnt[qi];
+                        const uint64_t* kq = ts.keys + static_cast<uint32_t>(qi) * ts.cap;
+                        uint64_t* dst = p.part + static_cast<uint64_t>(ts.slot[qi]) * ts.k;
+                        uint32_t worst = 0;
+                        for (uint32_t i = lane; i < ts.k; i += 32) {
+                            const uint64_t key = i < c ? kq[i] : KEY_INF;
+                            dst[i] = key;
+                            if (i < c) {
+                                worst = max(worst, static_cast<uint32_t>(key >> 32));
+                            }
+                        }
+                        if (c >= ts.k) {
+                            worst = __reduce_max_sync(0xffffffffu, worst);
+                            if (lane == 0) {
+                                atomicMin(p.thr_g + ts.qidx[qi], worst);
+                            }
+                        }
+                    }
+                } else if (tid == 0) {
+                    atomicOr(tp.error_flag, 1);
+                }
+                TCS_ACC(5);
             }
         }
     }
@@ -510,6 +754,25 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     if (warp == TCS_EPI_WARPS + 1 && lane == 0 && tp.count_scanned != 0 && p.scanned != nullptr && scanned_local != 0) {
         atomicAdd(p.scanned, scanned_local);
     }
+#ifdef VB200_TCS_PROFILE
+    if (tp.prof != nullptr && lane == 0 && (warp == 0 || warp >= TCS_EPI_WARPS)) {
+        prof_acc[15] = static_cast<unsigned long long>(clock64() - prof_begin);
+        unsigned long long* dst = tp.prof + static_cast<size_t>(blockIdx.x) * 24;
+        const int lo = warp == 0 ? 0 : (warp == TCS_EPI_WARPS ? 6 : 9), hi = warp == 0 ? 6 : (warp == TCS_EPI_WARPS ? 9 : 12);
+        for (int i = lo; i < hi; ++i) {
+            dst[i] = prof_acc[i];
+        }
+        if (warp == 0) {
+            dst[12] = prof_acc[12];
+            dst[13] = prof_acc[13];
+            dst[14] = prof_acc[14];
+            dst[15] = prof_acc[15];
+            for (int i = 16; i < 24; ++i) {
+                dst[i] = prof_acc[i];
+            }
+        }
+    }
+#endif
     tc_fence_before_sync();
     __syncthreads();
     if (sh.failed != 0) {
@@ -523,9 +786,16 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
 
 // Shared memory of a launch: code stages, the B operand, the selection state.
 inline size_t
-tcs_smem_bytes(uint32_t kchunks, uint32_t cap) {
+tcs_smem_bytes(uint32_t kchunks, uint32_t cap, uint32_t stages) {
     const size_t row_bytes = static_cast<size_t>(kchunks) * 16;
-    return TCS_STAGES * TCS_ROWS * row_bytes + 2 * TCS_N * row_bytes + tile_smem_bytes<TCS_QT>(cap, 0);
+    return stages * TCS_ROWS * row_bytes + 2 * TCS_N * row_bytes + tile_smem_bytes<TCS_QT>(cap, 0);
+}
+
+// Candidate buffer of a query in this kernel: k survivors plus room for a warp's worth of offers.
+inline uint32_t
+tcs_buffer_cap(uint32_t k) {
+    const uint32_t cap = next_pow2(k + 32);
+    return cap < 64 ? 64 : cap;
 }
 
 }  // namespace vb200

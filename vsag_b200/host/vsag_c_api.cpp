@@ -183,6 +183,54 @@ vsag_index_knn_search_batch(vsag_index_t index, const float* queries, uint64_t d
     return success();
 }
 
+// Index::SearchWithRequest (include/vsag/index.h:333) for nq queries with explicit bucket lists, an addition
+// to the reference's C interface: bucket_ids holds the lists of all queries back to back, bucket_counts[q]
+// says how many belong to query q (bucket_counts NULL = default routing).  KNN only; ids[nq x k], dists[nq x k],
+// padded with -1 / +inf.  The lists are validated as IVF::SearchWithRequest validates
+// SearchRequest::bucket_ids_ (src/algorithm/ivf/ivf.cpp:2075-2112).
+VSAG_C_EXPORT Error_t
+vsag_index_search_with_request(vsag_index_t index, const float* queries, uint64_t dim, uint64_t nq, int64_t k,
+                               const char* parameters, const int64_t* bucket_ids, const uint64_t* bucket_counts,
+                               int64_t* ids, float* dists) {
+    auto* box = static_cast<IndexBox*>(index);
+    if (box == nullptr) {
+        return make_error(-1, "index is NULL");
+    }
+    if (ids == nullptr || dists == nullptr) {
+        return make_error(-3, "output buffers are NULL");
+    }
+    vsag::SearchRequest request;
+    request.query_ = borrow(queries, nullptr, dim, nq);
+    request.topk_ = k;
+    request.params_str_ = parameters == nullptr ? "{}" : parameters;
+    if (bucket_counts != nullptr) {
+        uint64_t at = 0;
+        request.bucket_ids_.resize(nq);
+        for (uint64_t q = 0; q < nq; ++q) {
+            if (bucket_counts[q] > 0) {
+                if (bucket_ids == nullptr) {
+                    return make_error(-3, "bucket_ids is NULL although bucket_counts names buckets");
+                }
+                request.bucket_ids_[q].assign(bucket_ids + at, bucket_ids + at + bucket_counts[q]);
+            }
+            at += bucket_counts[q];
+        }
+    }
+    auto r = box->index->SearchWithRequest(request);
+    if (!r.has_value()) {
+        return make_error(r.error());
+    }
+    const auto& res = r.value();
+    for (uint64_t q = 0; q < nq; ++q) {
+        for (int64_t i = 0; i < k; ++i) {
+            bool have = static_cast<int64_t>(q) < res->GetNumElements() && i < res->GetDim() && res->GetIds() != nullptr;
+            ids[q * k + i] = have ? res->GetIds()[q * res->GetDim() + i] : -1;
+            dists[q * k + i] = have ? res->GetDistances()[q * res->GetDim() + i] : __builtin_inff();
+        }
+    }
+    return success();
+}
+
 // Two additions to the reference's C interface (include/vsag/vsag_c_api.h has no filter or remove
 // entry point; the C++ interface does, include/vsag/index.h:186-200, 276-303).
 // invalid_bits: n_words 64-bit words, bit (id & 0xFFFFFFFF) set = filtered out; may be NULL.

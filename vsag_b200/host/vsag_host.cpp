@@ -644,11 +644,43 @@ public:
         return range_impl(query, radius, parameters, limited_size, &f);
     }
 
+    // IVF::SearchWithRequest (src/algorithm/ivf/ivf.cpp:2052-2354): the request's filters become the
+    // engine's id filter (a bitset marks ids that are filtered out, filter_ says which ids are valid),
+    // bucket_ids_ replaces routing after the reference's checks, range mode takes one query.
+    Expected<DatasetPtr>
+    SearchWithRequest(const SearchRequest& request) const override {
+        std::vector<uint32_t> deny;
+        vb200_filter f{nullptr, 0, nullptr, 0};
+        bool filtered = false;
+        if (request.enable_bitset_filter_ && request.bitset_filter_ != nullptr && !request.bitset_filter_->Words().empty()) {
+            f.invalid_label_bits = request.bitset_filter_->Words().data();
+            f.n_label_bits = request.bitset_filter_->Words().size() * 64;
+            filtered = true;
+        }
+        if (request.enable_filter_ && request.filter_) {
+            deny.assign((labels_host_.size() + 31) / 32, 0);
+            for (size_t i = 0; i < labels_host_.size(); ++i) {
+                if (!request.filter_(labels_host_[i])) {
+                    deny[i >> 5] |= 1u << (i & 31);
+                }
+            }
+            f.deny_inner_bits = deny.data();
+            f.n_inner_bits = labels_host_.size();
+            filtered = true;
+        }
+        const vb200_filter* fp = filtered ? &f : nullptr;
+        const auto* buckets = request.bucket_ids_.empty() ? nullptr : &request.bucket_ids_;
+        if (request.mode_ == SearchMode::RANGE_SEARCH) {
+            return range_impl(request.query_, request.radius_, request.params_str_, request.limited_size_, fp, buckets);
+        }
+        return knn_impl(request.query_, request.topk_, request.params_str_, fp, buckets);
+    }
+
     Expected<DatasetPtr>
     range_impl(const DatasetPtr& query, float radius, const std::string& parameters, int64_t limited_size,
-               const vb200_filter* filter) const {
+               const vb200_filter* filter, const std::vector<std::vector<int64_t>>* bucket_ids = nullptr) const {
         return safe_call<DatasetPtr>([&]() {
-            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, filter); }, query,
+            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, filter, bucket_ids); }, query,
                                   GetNumElements(), radius, 2e-6f, limited_size);
         });
     }
@@ -762,7 +794,8 @@ public:
     }
 
     Expected<DatasetPtr>
-    knn_impl(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter) const {
+    knn_impl(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter,
+             const std::vector<std::vector<int64_t>>* bucket_ids = nullptr) const {
         return safe_call<DatasetPtr>([&]() {
             check_argument(query != nullptr, "query is null");
             check_argument(k > 0, "k must be greater than 0");
@@ -781,6 +814,38 @@ public:
             }
             check_base(query, dim_, false);
             const int64_t nq = query->GetNumElements();
+            // SearchRequest::bucket_ids_: the checks of IVF::SearchWithRequest (src/algorithm/ivf/ivf.cpp:2075-2112),
+            // then one row of bucket ids per query, padded with -1 to the longest list
+            std::vector<int32_t> buckets_flat;
+            if (bucket_ids != nullptr && !bucket_ids->empty()) {
+                check_argument(static_cast<int64_t>(bucket_ids->size()) == nq,
+                               "bucket_ids_ size must match the number of query vectors; got " +
+                                   std::to_string(bucket_ids->size()) + " bucket lists for " + std::to_string(nq) +
+                                   " queries");
+                check_argument(!disable_scan, "bucket_ids_ is incompatible with disable_bucket_scan mode");
+                size_t longest = 0;
+                for (size_t qi = 0; qi < bucket_ids->size(); ++qi) {
+                    const auto& ids = (*bucket_ids)[qi];
+                    check_argument(!ids.empty(), "bucket_ids_[" + std::to_string(qi) +
+                                                     "] must not be empty; use empty outer vector for default routing");
+                    std::vector<int64_t> seen(ids);
+                    std::sort(seen.begin(), seen.end());
+                    for (size_t i = 0; i < seen.size(); ++i) {
+                        check_argument(seen[i] >= 0 && seen[i] < static_cast<int64_t>(nlist_),
+                                       "bucket_id " + std::to_string(seen[i]) + " out of range [0, " +
+                                           std::to_string(nlist_) + ")");
+                        check_argument(i == 0 || seen[i] != seen[i - 1], "duplicate bucket_id " + std::to_string(seen[i]));
+                    }
+                    longest = std::max(longest, ids.size());
+                }
+                buckets_flat.assign(static_cast<size_t>(nq) * longest, -1);
+                for (size_t qi = 0; qi < bucket_ids->size(); ++qi) {
+                    for (size_t i = 0; i < (*bucket_ids)[qi].size(); ++i) {
+                        buckets_flat[qi * longest + i] = static_cast<int32_t>((*bucket_ids)[qi][i]);
+                    }
+                }
+                nprobe = static_cast<int64_t>(longest);
+            }
             if (disable_scan) {
                 // routing only: bucket ids with their centroid distances (IVF::route_buckets_only,
                 // src/algorithm/ivf/ivf.cpp:1589-1660)
@@ -804,7 +869,8 @@ public:
             auto* dists = new float[static_cast<size_t>(nq * k)];
             int status = vb200_ivf_search_filtered(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
                                                    static_cast<uint32_t>(std::min<int64_t>(nprobe, 0x7fffffff)),
-                                                   static_cast<float>(factor), nullptr, filter, ids, dists);
+                                                   static_cast<float>(factor),
+                                                   buckets_flat.empty() ? nullptr : buckets_flat.data(), filter, ids, dists);
             if (status != 0) {
                 delete[] ids;
                 delete[] dists;
@@ -1030,6 +1096,39 @@ public:
         }
         vb200_filter f{nullptr, 0, deny.data(), labels_host_.size()};
         return range_impl(query, radius, parameters, limited_size, &f);
+    }
+
+    // BruteForce::SearchWithRequest (src/algorithm/bruteforce/bruteforce.cpp:370-635): KNN or range search
+    // with the request's filters; bucket lists have no meaning here and are rejected.
+    Expected<DatasetPtr>
+    SearchWithRequest(const SearchRequest& request) const override {
+        if (!request.bucket_ids_.empty()) {
+            return Error{ErrorType::INVALID_ARGUMENT, "bucket_ids_ is only supported by the ivf index"};
+        }
+        std::vector<uint32_t> deny;
+        vb200_filter f{nullptr, 0, nullptr, 0};
+        bool filtered = false;
+        if (request.enable_bitset_filter_ && request.bitset_filter_ != nullptr && !request.bitset_filter_->Words().empty()) {
+            f.invalid_label_bits = request.bitset_filter_->Words().data();
+            f.n_label_bits = request.bitset_filter_->Words().size() * 64;
+            filtered = true;
+        }
+        if (request.enable_filter_ && request.filter_) {
+            deny.assign((labels_host_.size() + 31) / 32, 0);
+            for (size_t i = 0; i < labels_host_.size(); ++i) {
+                if (!request.filter_(labels_host_[i])) {
+                    deny[i >> 5] |= 1u << (i & 31);
+                }
+            }
+            f.deny_inner_bits = deny.data();
+            f.n_inner_bits = labels_host_.size();
+            filtered = true;
+        }
+        const vb200_filter* fp = filtered ? &f : nullptr;
+        if (request.mode_ == SearchMode::RANGE_SEARCH) {
+            return range_impl(request.query_, request.radius_, request.params_str_, request.limited_size_, fp);
+        }
+        return knn_impl(request.query_, request.topk_, request.params_str_, fp);
     }
 
     Expected<DatasetPtr>

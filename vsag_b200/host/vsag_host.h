@@ -139,6 +139,32 @@ private:
 };
 using BitsetPtr = std::shared_ptr<Bitset>;
 
+enum class SearchMode {
+    KNN_SEARCH = 1,
+    RANGE_SEARCH = 2,
+};
+
+// The request form of a search (include/vsag/search_request.h:48-227), with the fields this path
+// honours; names and defaults are the reference's.  `filter_` stands for the reference's FilterPtr:
+// it returns true for an id that may be returned (Filter::CheckValid).
+class SearchRequest {
+public:
+    DatasetPtr query_{nullptr};
+    SearchMode mode_{SearchMode::KNN_SEARCH};
+    int64_t topk_{10};
+    float radius_{0.5F};
+    int64_t limited_size_{-1};
+    std::string params_str_{};
+    bool enable_filter_{false};
+    std::function<bool(int64_t)> filter_{nullptr};
+    bool enable_bitset_filter_{false};
+    BitsetPtr bitset_filter_{nullptr};
+    // IVF only: per query, the buckets to scan instead of routing (one list per query; empty outer
+    // vector = default routing).  Validated as IVF::SearchWithRequest does
+    // (src/algorithm/ivf/ivf.cpp:2075-2112).
+    std::vector<std::vector<int64_t>> bucket_ids_{};
+};
+
 class Index {
 public:
     virtual ~Index() = default;
@@ -168,6 +194,10 @@ public:
     virtual Expected<DatasetPtr> RangeSearch(const DatasetPtr& query, float radius, const std::string& parameters,
                                              const std::function<bool(int64_t)>& filter,
                                              int64_t limited_size = -1) const = 0;
+    // Search described by a request object (include/vsag/index.h:333): KNN for one query or a batch, range
+    // search for one query, optional id filter, and for IVF the explicit bucket lists of
+    // SearchRequest::bucket_ids_.
+    virtual Expected<DatasetPtr> SearchWithRequest(const SearchRequest& request) const = 0;
     // RemoveMode::MARK_REMOVE (include/vsag/index.h:186-200): the vectors stay stored but are never
     // returned again; the result is the number of ids found and newly marked.
     virtual Expected<uint32_t> Remove(const std::vector<int64_t>& ids) = 0;

@@ -49,6 +49,9 @@ def _lib():
         lib.vsag_index_knn_search_batch.restype = _Error
         lib.vsag_index_knn_search_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int64,
                                                     C.c_char_p, C.c_void_p, C.c_void_p]
+        lib.vsag_index_search_with_request.restype = _Error
+        lib.vsag_index_search_with_request.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int64,
+                                                       C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.vsag_index_knn_search_filtered.restype = _Error
         lib.vsag_index_knn_search_filtered.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int64, C.c_char_p,
                                                        C.c_void_p, C.c_uint64, C.c_int64, C.POINTER(_SearchResult)]
@@ -198,6 +201,27 @@ class Index:
         dists = np.empty((nq, k), np.float32)
         _check(_lib().vsag_index_knn_search_batch(self._h, vectors.ctypes.data, dim, nq, k, parameters.encode(),
                                                   ids.ctypes.data, dists.ctypes.data))
+        return ids, dists
+
+    def search_with_request(self, vectors, k: int, parameters: str = "{}", bucket_ids=None):
+        """Index::SearchWithRequest for nq queries: `bucket_ids` is a list with, per query, the list of
+        buckets to scan instead of routing (SearchRequest::bucket_ids_); None or [] = default routing."""
+        vectors = np.ascontiguousarray(vectors, np.float32)
+        nq, dim = vectors.shape
+        ids = np.empty((nq, k), np.int64)
+        dists = np.empty((nq, k), np.float32)
+        flat = counts = None
+        if bucket_ids:
+            counts = np.array([len(b) for b in bucket_ids], np.uint64)
+            flat = np.array([x for b in bucket_ids for x in b], np.int64)
+            if counts.size != nq:
+                # the library checks this too; it needs one count per query to read the lists at all
+                raise VsagError(-3, f"bucket_ids_ size must match the number of query vectors; got {counts.size} "
+                                    f"bucket lists for {nq} queries")
+        _check(_lib().vsag_index_search_with_request(
+            self._h, vectors.ctypes.data, dim, nq, k, parameters.encode(),
+            flat.ctypes.data if flat is not None and flat.size else None,
+            counts.ctypes.data if counts is not None else None, ids.ctypes.data, dists.ctypes.data))
         return ids, dists
 
     def get_num_elements(self) -> int:
