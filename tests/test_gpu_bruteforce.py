@@ -94,6 +94,9 @@ def test_row_sharded_search_equals_unsharded(engine, oracle):
     (1, "fp32", 120_077, 100, 2000, 40),
     (1, "bf16", 150_001, 96, 2000, 100),
     (0, "bf16", 100_000, 128, 1800, 10),
+    # bases beyond 64 MB of tiled operand with several query tiles: the interleaved tile schedule
+    (0, "fp32", 300_000, 128, 2000, 10),
+    (1, "bf16", 700_001, 64, 1000, 20),
 ])
 def test_tensor_core_candidates_equal_simt_path(engine, oracle, metric, quant, n, dim, nq, k):
     """Large searches nominate candidates with the tcgen05 kernel; after the exact re-scoring the

@@ -46,7 +46,9 @@ def _headers_mtime() -> float:
 
 
 def _extra_flags() -> list[str]:
-    """VB200_NVCC_FLAGS adds compiler flags (e.g. -DVB200_TCS_PROFILE for the scan kernel's cycle counters)."""
+    """VB200_NVCC_FLAGS adds compiler flags: -DVB200_TCS_PROFILE for the scan kernel's cycle counters,
+    -DVB200_TC_DIAG for the candidate kernel's timing switches (VB200_TC_DIAG=1/2/4/8 at run time skips the
+    selection, the MMAs, the list appends, the final sorts: wrong results, for finding the slowest stage)."""
     return os.environ.get("VB200_NVCC_FLAGS", "").split()
 
 

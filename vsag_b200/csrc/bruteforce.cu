@@ -34,8 +34,15 @@ bf_rescore_kernel(const T* __restrict__ queries, uint32_t dim, const T* __restri
                   int metric, uint64_t* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
+    float* qf = reinterpret_cast<float*>(keys + n2);   // the query, widened once
     const T* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
     const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        qf[d] = widen(q[d]);
+    }
+    __syncthreads();
+    constexpr uint32_t VEC = 16 / sizeof(T);           // elements per 16-byte load
+    const bool wide_loads = dim % VEC == 0 && (reinterpret_cast<uintptr_t>(base) & 15u) == 0;
     for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
         uint64_t key = KEY_INF;
         // candidates with an infinite nominating score are filtered-out rows that only filled up a
@@ -44,15 +51,46 @@ bf_rescore_kernel(const T* __restrict__ queries, uint32_t dim, const T* __restri
             uint32_t row = static_cast<uint32_t>(cq[i]);
             const T* x = base + static_cast<uint64_t>(row) * dim;
             float s = 0.f;
-            if (metric == VB200_METRIC_L2) {
+            const bool l2 = metric == VB200_METRIC_L2;
+            if (wide_loads) {
+                // same chain, rows fetched sixteen bytes at a time with a few loads in flight
+                const uint4* xv = reinterpret_cast<const uint4*>(x);
+                const uint32_t nv = dim / VEC;
+                for (uint32_t v0 = 0; v0 < nv; v0 += 4) {
+                    uint4 w[4];
+#pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u) {
+                        w[u] = v0 + u < nv ? __ldg(xv + v0 + u) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u) {
+                        if (v0 + u < nv) {
+                            T e[VEC];
+                            *reinterpret_cast<uint4*>(e) = w[u];
+                            const float* qq = qf + (v0 + u) * VEC;
+#pragma unroll
+                            for (uint32_t j = 0; j < VEC; ++j) {
+                                if (l2) {
+                                    float t = __fsub_rn(widen(e[j]), qq[j]);
+                                    s = fmaf(t, t, s);
+                                } else {
+                                    s = fmaf(widen(e[j]), qq[j], s);
+                                }
+                            }
+                        }
+                    }
+                }
+            } else if (l2) {
                 for (uint32_t d = 0; d < dim; ++d) {
-                    float t = __fsub_rn(widen(x[d]), widen(q[d]));
+                    float t = __fsub_rn(widen(x[d]), qf[d]);
                     s = fmaf(t, t, s);
                 }
             } else {
                 for (uint32_t d = 0; d < dim; ++d) {
-                    s = fmaf(widen(x[d]), widen(q[d]), s);
+                    s = fmaf(widen(x[d]), qf[d], s);
                 }
+            }
+            if (!l2) {
                 s = __fsub_rn(1.0f, s);
             }
             key = make_key(s, row);
@@ -66,21 +104,40 @@ bf_rescore_kernel(const T* __restrict__ queries, uint32_t dim, const T* __restri
     }
 }
 
+template <typename T>
+static int
+bf_rescore(const T* queries, uint64_t nq, uint32_t dim, const T* base, const uint64_t* cand, uint32_t ncand, uint32_t n2,
+           uint32_t k, int metric, uint64_t* out) {
+    const size_t smem = n2 * sizeof(uint64_t) + dim * sizeof(float);
+    VB_CHECK_ARG(smem <= 200 * 1024, "dim = %u is too large for the exact re-scoring step", dim);
+    auto kernel = bf_rescore_kernel<T>;
+    if (smem > 48 * 1024) {
+        VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    VB_LAUNCH(kernel, static_cast<uint32_t>(nq), 128, smem, queries, dim, base, cand, ncand, n2, k, metric, out);
+    return 0;
+}
+
+// One block per query: the k best keys of its `per_query` partial keys and, when `prev` is given, of the k
+// keys an earlier call left there (prev may be `out`).  bound_out[q], when asked for, is the score of the
+// k-th key found, or +inf while fewer than k exist: no key scoring at or above it can enter the k best later.
 __global__ void __launch_bounds__(256)
-bf_merge_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_t k, uint32_t cap,
-                uint64_t* __restrict__ out) {
+bf_merge_kernel(const uint64_t* __restrict__ part, uint64_t per_query, const uint64_t* prev, uint32_t k, uint32_t cap,
+                uint64_t* out, float* __restrict__ bound_out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
     uint32_t* state = reinterpret_cast<uint32_t*>(keys + cap);
     BlockSelect sel;
     sel.init(keys, state, k, cap);
     const uint64_t* src = part + static_cast<uint64_t>(blockIdx.x) * per_query;
-    for (uint64_t base = 0; base < per_query; base += blockDim.x) {
+    const uint64_t n_prev = prev != nullptr ? k : 0;
+    const uint64_t* old = prev != nullptr ? prev + static_cast<uint64_t>(blockIdx.x) * k : nullptr;
+    for (uint64_t base = 0; base < per_query + n_prev; base += blockDim.x) {
         sel.make_room(blockDim.x);
         uint64_t thr = sel.threshold();
         uint64_t i = base + threadIdx.x;
-        if (i < per_query) {
-            uint64_t key = __ldg(src + i);
+        if (i < per_query + n_prev) {
+            uint64_t key = i < n_prev ? old[i] : __ldg(src + (i - n_prev));
             if (key != KEY_INF) {
                 sel.offer(key, thr);
             }
@@ -90,6 +147,9 @@ bf_merge_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_t 
     uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
     for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
         dst[i] = i < cnt ? keys[i] : KEY_INF;
+    }
+    if (bound_out != nullptr && threadIdx.x == 0) {
+        bound_out[blockIdx.x] = cnt >= k ? ordered_to_float(static_cast<uint32_t>(keys[k - 1] >> 32)) : INFINITY;
     }
 }
 
@@ -192,6 +252,7 @@ struct vb200_bf {
     DevBuf<uint16_t> base_hi, base_lo, q_hi, q_lo;
     bool tiled_valid = false;
     DevBuf<uint64_t> tc_out;
+    DevBuf<float> row_bound;   // per query: the kcand-th candidate score after the column ranges searched so far
     TcWorkspace tc;
     DevBuf<int64_t> out_ids;
     DevBuf<float> out_dists;
@@ -496,25 +557,46 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
             VB_TRY(tc_pretile_f32(q_dev, nq, dim, ix->q_hi.ptr, ix->q_lo.ptr));
         }
         TcOperand a{ix->q_hi.ptr, bf16 ? nullptr : ix->q_lo.ptr, nq, chunks};
-        TcOperand b{ix->base_hi.ptr, bf16 ? nullptr : ix->base_lo.ptr, n, chunks};
-        uint32_t lists = 1;
-        VB_TRY(tc_candidates(ix->tc, a, b, bf16 ? 1 : 3, l2 ? -2.0f : -1.0f, bias_all, kcand, 0,
-                             ix->tc_out, &lists));
         VB_TRY(ix->cand.reserve(nq * kcand));
-        {
-            uint32_t cap = next_pow2(kcand + 256);
-            size_t smem = cap * sizeof(uint64_t) + 16;
-            VB_LAUNCH(bf_merge_kernel, static_cast<uint32_t>(nq), 256, smem, ix->tc_out.ptr,
-                      static_cast<uint64_t>(lists) * kcand, kcand, cap, ix->cand.ptr);
+        VB_TRY(ix->row_bound.reserve(nq));
+        // The base goes through the tensor cores in a few column ranges of growing size (a first one of about
+        // a thousand rows, then sixteen times as many each time).  After each range the per-query candidate
+        // lists are merged and the kcand-th score so far becomes the query's bound for the next range: no
+        // column at or above it can be among the kcand best, so with rows in no particular order only about
+        // 16 * kcand columns per query pass the bound in a range, and the kernel's per-row buffers hardly ever
+        // need compacting.  Whatever the order of the rows, the result is the same set of candidates.
+        const uint64_t n_tiles = (n + TC_BN - 1) / TC_BN;
+        uint64_t len = n_tiles;
+        if (n_tiles >= 1024) {
+            len = 2 * kcand / TC_BN + 1 < 8 ? 8 : 2 * kcand / TC_BN + 1;
+        }
+        const uint32_t merge_cap = next_pow2(kcand + 256);
+        const size_t merge_smem = merge_cap * sizeof(uint64_t) + 16;
+        for (uint64_t tile0 = 0; tile0 < n_tiles; len *= 16) {
+            uint64_t tile1 = tile0 + len;
+            if (tile1 >= n_tiles || n_tiles - tile1 < len) {
+                tile1 = n_tiles;   // no short last range
+            }
+            const uint64_t row0 = tile0 * TC_BN;
+            const uint64_t rows = (tile1 * TC_BN < n ? tile1 * TC_BN : n) - row0;
+            const size_t off = static_cast<size_t>(tile0) * chunks * TC_CHUNK_ELEMS;
+            TcOperand b{ix->base_hi.ptr + off, bf16 ? nullptr : ix->base_lo.ptr + off, rows, chunks};
+            const bool first = tile0 == 0;
+            uint32_t lists = 1;
+            VB_TRY(tc_candidates(ix->tc, a, b, bf16 ? 1 : 3, l2 ? -2.0f : -1.0f, bias_all != nullptr ? bias_all + row0 : nullptr,
+                                 kcand, static_cast<uint32_t>(row0), ix->tc_out, &lists, nullptr, nullptr,
+                                 first ? nullptr : ix->row_bound.ptr));
+            VB_LAUNCH(bf_merge_kernel, static_cast<uint32_t>(nq), 256, merge_smem, ix->tc_out.ptr,
+                      static_cast<uint64_t>(lists) * kcand, first ? static_cast<const uint64_t*>(nullptr) : ix->cand.ptr,
+                      kcand, merge_cap, ix->cand.ptr, tile1 < n_tiles ? ix->row_bound.ptr : static_cast<float*>(nullptr));
+            tile0 = tile1;
         }
         VB_TRY(ix->keys.reserve(nq * k));
         uint32_t n2 = next_pow2(kcand < 2 ? 2 : kcand);
         if (bf16) {
-            VB_LAUNCH(bf_rescore_kernel<uint16_t>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t),
-                      ix->q_bf16.ptr, dim, ix->base_bf16.ptr, ix->cand.ptr, kcand, n2, k, ix->metric, ix->keys.ptr);
+            VB_TRY(bf_rescore(ix->q_bf16.ptr, nq, dim, ix->base_bf16.ptr, ix->cand.ptr, kcand, n2, k, ix->metric, ix->keys.ptr));
         } else {
-            VB_LAUNCH(bf_rescore_kernel<float>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev, dim,
-                      ix->base_f32.ptr, ix->cand.ptr, kcand, n2, k, ix->metric, ix->keys.ptr);
+            VB_TRY(bf_rescore(q_dev, nq, dim, ix->base_f32.ptr, ix->cand.ptr, kcand, n2, k, ix->metric, ix->keys.ptr));
         }
         return 0;
     }
@@ -560,17 +642,16 @@ bf_search_keys(vb200_bf* ix, const float* queries, uint64_t nq, uint32_t k) {
         uint32_t cap = next_pow2(kcand + 256);
         size_t smem = cap * sizeof(uint64_t) + 16;
         VB_LAUNCH(bf_merge_kernel, static_cast<uint32_t>(nq), 256, smem, ix->part.ptr,
-                  static_cast<uint64_t>(keys_ld), kcand, cap, ix->cand.ptr);
+                  static_cast<uint64_t>(keys_ld), static_cast<const uint64_t*>(nullptr), kcand, cap, ix->cand.ptr,
+                  static_cast<float*>(nullptr));
         cand = ix->cand.ptr;
     }
     VB_TRY(ix->keys.reserve(nq * k));
     uint32_t n2 = next_pow2(kcand < 2 ? 2 : kcand);
     if (bf16) {
-        VB_LAUNCH(bf_rescore_kernel<uint16_t>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t),
-                  ix->q_bf16.ptr, dim, ix->base_bf16.ptr, cand, kcand, n2, k, ix->metric, ix->keys.ptr);
+        VB_TRY(bf_rescore(ix->q_bf16.ptr, nq, dim, ix->base_bf16.ptr, cand, kcand, n2, k, ix->metric, ix->keys.ptr));
     } else {
-        VB_LAUNCH(bf_rescore_kernel<float>, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev,
-                  dim, ix->base_f32.ptr, cand, kcand, n2, k, ix->metric, ix->keys.ptr);
+        VB_TRY(bf_rescore(q_dev, nq, dim, ix->base_f32.ptr, cand, kcand, n2, k, ix->metric, ix->keys.ptr));
     }
     return 0;
 }

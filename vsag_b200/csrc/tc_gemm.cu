@@ -213,15 +213,42 @@ tc_candidates_kernel(const TcParams p) {
 
     const uint32_t n_items32 = static_cast<uint32_t>(n_items);
     const uint32_t n_tiles32 = static_cast<uint32_t>(n_tiles);
-    auto open_item = [&](uint32_t item, uint32_t& mtile, uint32_t& ntile0, uint32_t& tiles) {
-        mtile = item / p.n_split;
-        uint32_t split = item - mtile * p.n_split;
-        ntile0 = split * p.tiles_per_split;
-        uint32_t t1 = ntile0 + p.tiles_per_split;
-        if (t1 > n_tiles32) {
-            t1 = n_tiles32;
+    // A work item is a row tile of A against one of n_split shares of B's tiles.  Contiguous shares: share s
+    // holds tiles s * tiles_per_split ..., and the items of a row tile are neighbours in the queue.
+    // Interleaved shares (p.interleaved): share s holds tiles s, s + n_split, s + 2 n_split, ..., and the
+    // queue walks the row tiles of one share before the next share, so the CTAs running at any moment
+    // sweep B front to back together and a B tile fetched from DRAM by one of them is an L2 hit for the
+    // others -- what a base far larger than L2 needs when there are many row tiles.
+    const uint32_t m_tiles32 = static_cast<uint32_t>(m_tiles);
+    auto open_item = [&](uint32_t item, uint32_t& mtile, uint32_t& split, uint32_t& tiles) {
+        if (p.interleaved) {
+            split = item / m_tiles32;
+            mtile = item - split * m_tiles32;
+            tiles = n_tiles32 > split ? (n_tiles32 - split + p.n_split - 1) / p.n_split : 0u;
+        } else {
+            mtile = item / p.n_split;
+            split = item - mtile * p.n_split;
+            const uint32_t t0 = split * p.tiles_per_split;
+            uint32_t t1 = t0 + p.tiles_per_split;
+            if (t1 > n_tiles32) {
+                t1 = n_tiles32;
+            }
+            tiles = t1 > t0 ? t1 - t0 : 0;
         }
-        tiles = t1 > ntile0 ? t1 - ntile0 : 0;
+    };
+    // B tile number u of share `split`.  With p.window > 0 (a power of two) the share is walked in windows
+    // of that many tiles and every row tile starts each window at its own offset, wrapping round: the CTAs
+    // that sweep a share together then ask L2 for different tiles at any moment instead of all for the same
+    // lines, while a window still passes through L2 once.
+    auto tile_at = [&](uint32_t split, uint32_t mtile, uint32_t tiles, uint32_t u) -> uint32_t {
+        if (p.window != 0) {
+            const uint32_t w0 = u & ~(p.window - 1u);
+            const uint32_t len = tiles - w0 < p.window ? tiles - w0 : p.window;
+            uint32_t r = (u - w0) + ((mtile * 29u) & (p.window - 1u));
+            r = len == p.window ? (r & (p.window - 1u)) : r % len;
+            u = w0 + r;
+        }
+        return p.interleaved ? split + u * p.n_split : split * p.tiles_per_split + u;
     };
     if (warp == TC_EPI_WARPS) {
         // ---------------- MMA issue (one thread) ----------------
@@ -240,8 +267,8 @@ tc_candidates_kernel(const TcParams p) {
             bool ok = true;
             uint32_t m_stage = 0, m_phase = 0, acc = 0, acc_phase = 0, tiles_started = 0, a_phase = 0;
             for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
-                uint32_t mtile, ntile0, tiles;
-                open_item(item, mtile, ntile0, tiles);
+                uint32_t mtile, split, tiles;
+                open_item(item, mtile, split, tiles);
                 if (a_res && tiles > 0) {
                     ok = mbar_wait(&sh.a_full, a_phase, p.spin_limit);
                     a_phase ^= 1u;
@@ -268,6 +295,11 @@ tc_candidates_kernel(const TcParams p) {
                         tc_fence_after_sync();
 #pragma unroll
                         for (uint32_t kk = 0; kk < TC_KC / 16; ++kk) {
+#ifdef VB200_TC_DIAG
+                            if ((p.diag & 2u) != 0) {
+                                continue;
+                            }
+#endif
                             // a k-step of 16 elements = two 8-element cores: 256 B = 16 descriptor units
                             const uint64_t koff = kk * 16;
                             const uint32_t accumulate = (c == 0 && kk == 0) ? 0u : 1u;
@@ -325,8 +357,8 @@ tc_candidates_kernel(const TcParams p) {
                 // the whole A tile of an item at once, into the resident region
                 uint32_t a_phase = 0, n_loaded = 0;
                 for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
-                    uint32_t mtile, ntile0, tiles;
-                    open_item(item, mtile, ntile0, tiles);
+                    uint32_t mtile, split, tiles;
+                    open_item(item, mtile, split, tiles);
                     if (tiles == 0) {
                         continue;
                     }
@@ -353,8 +385,8 @@ tc_candidates_kernel(const TcParams p) {
                 const uint32_t op_off = (is_a || a_res) ? 0u : terms * TC_CHUNK_BYTES;   // A terms first, then B terms
                 uint32_t stage = 0, phase = 0, count = 0;
                 for (uint32_t item = blockIdx.x; item < n_items32 && ok; item += gridDim.x) {
-                    uint32_t mtile, ntile0, tiles;
-                    open_item(item, mtile, ntile0, tiles);
+                    uint32_t mtile, split, tiles;
+                    open_item(item, mtile, split, tiles);
                     for (uint32_t t = 0; t < tiles && ok; t += step) {
                         const uint32_t here = is_a ? 1u : (tiles - t >= step ? step : 1u);   // B tiles of this step
                         for (uint32_t c = 0; c < chunks; ++c) {
@@ -368,7 +400,7 @@ tc_candidates_kernel(const TcParams p) {
                             unsigned char* dst = smem + a_region_bytes + stage * stage_bytes + op_off;
                             mbar_expect_tx(&sh.full[stage], terms * here * TC_CHUNK_BYTES);
                             for (uint32_t slot = 0; slot < here; ++slot) {
-                                const size_t row_tile = is_a ? mtile : ntile0 + t + slot;
+                                const size_t row_tile = is_a ? mtile : tile_at(split, mtile, tiles, t + slot);
                                 const size_t off = (row_tile * chunks + c) * TC_CHUNK_ELEMS;
                                 const uint32_t slots = is_a ? 1u : step;   // slots per term in the stage
                                 bulk_copy_g2s(dst + slot * TC_CHUNK_BYTES, op.hi + off, TC_CHUNK_BYTES, &sh.full[stage]);
@@ -402,18 +434,18 @@ tc_candidates_kernel(const TcParams p) {
         uint64_t gtile = 0;
         bool ok = true;
         for (uint64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-            const uint64_t m_tile = item / p.n_split;
-            const uint64_t split = item % p.n_split;
-            const uint64_t t0 = split * p.tiles_per_split;
-            uint64_t t1 = t0 + p.tiles_per_split;
-            if (t1 > n_tiles) {
-                t1 = n_tiles;
-            }
+            uint32_t m_tile32, split32, tiles32;
+            open_item(static_cast<uint32_t>(item), m_tile32, split32, tiles32);
+            const uint64_t m_tile = m_tile32, split = split32;
+            const uint64_t t0 = 0, t1 = tiles32;   // the item's B tiles by their number within its share
             const uint64_t grow = m_tile * TC_BM + row;
             const bool valid_row = grow < p.a.rows;
             uint32_t cnt = 0;
             float thr = INFINITY;
             uint64_t* list = nullptr;   // THRESH: this thread's output list of the item
+            if (MODE == 1 && p.row_bound != nullptr && valid_row) {
+                thr = __ldg(p.row_bound + grow);   // the caller's bound: columns scoring at or above it are of no use
+            }
             if (THRESH) {
                 thr = valid_row ? __ldg(p.row_bound + grow) : -INFINITY;
                 list = p.out + ((grow * p.n_split + split) * TC_COL_GROUPS + cgroup) * p.cap;
@@ -423,7 +455,9 @@ tc_candidates_kernel(const TcParams p) {
             const bool has_bias = p.bias != nullptr;
             // first global column of this warp's block `half` in the tile step that starts at B tile t
             auto block_col = [&](uint64_t t, uint32_t half) -> uint64_t {
-                return p.wide ? (t + (cgroup >> 1)) * TC_BN + (cgroup & 1u) * 64 + half * 32 : t * TC_BN + cgroup * 32;
+                return p.wide ? static_cast<uint64_t>(tile_at(split32, m_tile32, tiles32, static_cast<uint32_t>(t) + (cgroup >> 1))) * TC_BN +
+                                    (cgroup & 1u) * 64 + half * 32
+                              : static_cast<uint64_t>(tile_at(split32, m_tile32, tiles32, static_cast<uint32_t>(t))) * TC_BN + cgroup * 32;
             };
             float next_bias = 0.f;
             if (has_bias) {
@@ -477,6 +511,11 @@ tc_candidates_kernel(const TcParams p) {
                             full &= full - 1;
                         }
                     }
+#ifdef VB200_TC_DIAG
+                    if ((p.diag & 1u) != 0) {
+                        continue;
+                    }
+#endif
                     const uint32_t c0 = static_cast<uint32_t>(n0);
                     // Scores of the block and their minimum first (two instructions per element);
                     // the selection code below runs only when the minimum beats the row's bound.
@@ -591,7 +630,11 @@ tc_candidates_kernel(const TcParams p) {
                             // without: anything better than the fourth best is kept
                             bound = fminf(bound, margin >= 0.f ? fminf(bs3, bs0 + margin) : bs3);
                         }
-                    } else if (mn < thr) {
+                    } else if (mn < thr
+#ifdef VB200_TC_DIAG
+                               && (p.diag & 4u) == 0
+#endif
+                    ) {
                         // few elements pass: test them in pairs through the first level of the tree
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
@@ -658,6 +701,11 @@ tc_candidates_kernel(const TcParams p) {
                 }
             } else {
                 // final order of every row of this warp, then the m best go out
+#ifdef VB200_TC_DIAG
+                if ((p.diag & 8u) != 0) {
+                    continue;
+                }
+#endif
                 for (uint32_t owner = 0; owner < 32; ++owner) {
                     tc_compact_row(buf, cnt, thr, owner, lane, p.m, sort_area);
                     const uint64_t orow = m_tile * TC_BM + quarter * 32 + owner;
@@ -781,6 +829,34 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     }
     uint64_t tiles_per_split = (n_tiles + n_split - 1) / n_split;
     n_split = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+    // A B operand far larger than L2 under many row tiles (BruteForce over millions of rows): interleaved
+    // shares, so that the CTAs running together sweep B front to back together and DRAM delivers every B
+    // tile about once instead of once per row tile.  The number of shares makes the item count close to a
+    // whole number of waves of the grid.
+    const uint64_t b_bytes = n_tiles * b.chunks * static_cast<uint64_t>(TC_CHUNK_BYTES) * (n_terms == 3 ? 2 : 1);
+    bool interleaved = false;
+    if (b_bytes > (uint64_t{64} << 20) && m_tiles >= 4 && n_tiles >= 64) {
+        // the queue deals items round-robin and items take about equally long: pick the share count that
+        // leaves the fewest CTAs idle in the last round (79 row tiles on 148 SMs: 13 shares = 6.94 rounds)
+        double best_eff = 0.0;
+        for (uint64_t ns = 4; ns <= 32 && ns * 8 <= n_tiles; ++ns) {
+            const uint64_t count = m_tiles * ns;
+            const uint64_t rounds = (count + sms - 1) / sms;
+            const double eff = static_cast<double>(count) / static_cast<double>(rounds * sms);
+            if (rounds >= 2 && eff > best_eff + 0.01) {
+                best_eff = eff;
+                n_split = ns;
+                interleaved = true;
+            }
+        }
+        if (!interleaved && m_tiles >= sms) {
+            n_split = 1;
+            interleaved = true;
+        }
+        if (interleaved) {
+            tiles_per_split = (n_tiles + n_split - 1) / n_split;
+        }
+    }
     const uint64_t items = m_tiles * n_split;
     const uint32_t grid = static_cast<uint32_t>(items < sms ? items : sms);
 
@@ -790,6 +866,24 @@ tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t 
     p.n_terms = n_terms;
     p.alpha = alpha;
     p.bias = bias_dev;
+    p.interleaved = interleaved ? 1u : 0u;
+#ifdef VB200_TC_DIAG
+    {
+        const char* env = std::getenv("VB200_TC_DIAG");
+        p.diag = env != nullptr ? static_cast<uint32_t>(std::atoi(env)) : 0u;
+    }
+#endif
+    p.window = 0;
+    if (interleaved) {
+        p.window = 64;
+        const char* env = std::getenv("VB200_TC_WINDOW");   // tuning aid: 0 or a power of two
+        if (env != nullptr && env[0] != 0) {
+            const uint32_t w = static_cast<uint32_t>(std::atoi(env));
+            if ((w & (w - 1u)) == 0) {
+                p.window = w;
+            }
+        }
+    }
     p.a_sq = a_sq_dev;
     p.margin_scale = margin_scale_dev;
     p.row_bound = row_bound_dev;

@@ -50,8 +50,13 @@ struct TcParams {
     uint32_t stages;          // operand stages in shared memory (2 .. 6)
     uint32_t a_resident;      // 1: the A tile of a work item stays in shared memory for all its B tiles
     uint32_t wide;            // 1: two B tiles per MMA (128 x 256 x 16), 512 TMEM columns
-    uint32_t n_split;         // column ranges per row tile
-    uint32_t tiles_per_split; // B tiles per range
+    uint32_t n_split;         // shares of B's tiles per row tile
+    uint32_t tiles_per_split; // B tiles per share when the shares are contiguous
+#ifdef VB200_TC_DIAG
+    uint32_t diag;            // timing experiments only: bit 0 skips the selection, bit 1 the MMAs
+#endif
+    uint32_t window;          // 0, or a power of two: tiles per window of the staggered walk over a share
+    uint32_t interleaved;     // 1: share s holds tiles s, s + n_split, ...; the queue walks row tiles within a share
     uint64_t* scratch;        // [grid][128][TC_COL_GROUPS][cap] candidate buffers
     uint64_t* out;            // [a.rows][n_split][TC_COL_GROUPS][m] keys (ordered score << 32 | column), KEY_INF padded
                               // (threshold mode: [a.rows][n_split][TC_COL_GROUPS][cap], unsorted, with out_count)
@@ -257,8 +262,10 @@ struct TcWorkspace {
 // chosen here and returned in n_split_out.
 // a_sq_dev / margin_scale_dev (both optional, m <= 4 only): squared row norms of A and a device scalar
 // c such that |approximate score - exact score| << c * |A_i|; columns scoring worse than the row's
-// best by more than that margin are not nominated at all.  row_bound_dev (optional, needs the
-// margin): per row, the exact score of some column; nothing worse than it plus the margin is visited.
+// best by more than that margin are not nominated at all.  row_bound_dev (optional): with the margin
+// (m <= 4), per row the exact score of some column: nothing worse than it plus the margin is visited;
+// with m > 4, per row a score that columns must stay below to be of use (e.g. the m-th best score found
+// in another column range): columns at or above it are not nominated.
 // row_flags_dev / n_flagged_out (optional, with the margin): rows whose candidate lists may have lost a
 // column within the margin (see TcParams::row_flags) are marked and counted; the array must be zeroed by
 // the caller.
