@@ -182,6 +182,16 @@ class Ctx:
             self.dist = dist_mod
             self.dist.init_process_group("nccl", device_id=self.device)
         self.peaks = measured_peaks()
+        self._comm = None
+
+    @property
+    def comm(self):
+        """The library's own communicator (vb200_comm_init); torch.distributed only carries its id."""
+        if self._comm is None and self.world > 1:
+            from vsag_b200 import parallel
+
+            self._comm = parallel.Comm(self.dist, self.rank, self.world, self.device)
+        return self._comm
 
     def timed(self, fn, steps: int) -> float:
         torch = self.torch
@@ -202,6 +212,8 @@ class Ctx:
         return float(ms.item())
 
     def close(self) -> None:
+        if self._comm is not None:
+            self._comm.close()
         if self.world > 1:
             self.dist.destroy_process_group()
 
@@ -422,15 +434,15 @@ def run_ivf_sq8(args, ctx: Ctx) -> dict:
     if world > 1:
         from vsag_b200 import parallel
 
-        sharded = parallel.ShardedIvfSearch(ix, n_query, K, world, device, dist, rank)
+        sharded = parallel.ShardedIvfSearch(ix, n_query, K, world, device, dist, rank, comm=ctx.comm)
 
     def step_device(np_=nprobe):
         if world == 1:
             ix.search(queries, K, np_, out=(out_ids, out_d))
         else:
-            # every rank routes its slice of the batch, the probe lists are all-gathered, every
-            # rank scans the probed lists it owns, and the per-shard top-k are all-gathered over
-            # NVLink and merged locally
+            # one C-ABI call per rank: every rank routes its slice of the batch, the probe lists are
+            # all-gathered, every rank scans the probed lists it owns, and the per-shard top-k are
+            # all-gathered over NVLink and merged locally
             sharded.search(queries, np_, 2.0, out_ids, out_d)
 
     for _ in range(args.warmup):
@@ -460,10 +472,7 @@ def run_ivf_sq8(args, ctx: Ctx) -> dict:
         if world == 1:
             ix.search(q_host, K, nprobe, out=(ids_host, d_host))
         else:
-            queries.copy_(q_host, non_blocking=True)
-            step_device()
-            ids_host.copy_(out_ids, non_blocking=True)
-            d_host.copy_(out_d, non_blocking=True)
+            sharded.search(q_host, nprobe, 2.0, ids_host, d_host)   # host buffers through the same C-ABI call
 
     for _ in range(2):
         step_e2e()
@@ -713,19 +722,14 @@ def run_bruteforce(args, ctx: Ctx, steps: int, warmup: int) -> dict:
     q = (q / q.norm(dim=1, keepdim=True)).contiguous()
     out_ids = torch.empty((nq, k), dtype=torch.int64, device=device)
     out_d = torch.empty((nq, k), dtype=torch.float32, device=device)
-    if world > 1:
-        keys_local = torch.empty((nq, k), dtype=torch.int64, device=device)
-        labels_local = torch.empty((nq, k), dtype=torch.int64, device=device)
-        keys_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
-        labels_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
+    comm = ctx.comm
 
     def step(queries=q, ids=out_ids, dists=out_d):
         if world == 1:
             ix.search(queries, k, out=(ids, dists))
         else:
-            ix.search_partial(queries, k, keys_local, labels_local)
-            parallel.exchange_partials(keys_local, labels_local, keys_all, labels_all, dist)
-            engine.merge_partials(keys_all, labels_all, world, nq, k, out=(ids, dists))
+            # one C-ABI call: this rank's rows, an all-gather of the packed per-rank top-k, the merge
+            ix.search_sharded(comm, queries, k, out=(ids, dists))
 
     for _ in range(warmup):
         step()
@@ -744,13 +748,7 @@ def run_bruteforce(args, ctx: Ctx, steps: int, warmup: int) -> dict:
     d_host = torch.empty((nq, k), dtype=torch.float32, pin_memory=True)
 
     def step_e2e():
-        if world == 1:
-            step(q_host, ids_host, d_host)
-        else:
-            q.copy_(q_host, non_blocking=True)
-            step()
-            ids_host.copy_(out_ids, non_blocking=True)
-            d_host.copy_(out_d, non_blocking=True)
+        step(q_host, ids_host, d_host)   # host buffers straight through the C-ABI call, at every N
 
     step_e2e()
     e2e_ms = ctx.timed(step_e2e, steps) / steps
@@ -962,6 +960,23 @@ def main() -> None:
         run_reference_arm(args)
         return
 
+    # Libraries write to stdout as they please (NCCL prints its version line when a communicator is
+    # created, through C stdio); this program's stdout carries the JSON line only, so everything before
+    # it goes to stderr.
+    import ctypes
+
+    libc = ctypes.CDLL(None)
+    sys.stdout.flush()
+    libc.fflush(None)
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def restore_stdout():
+        sys.stdout.flush()
+        libc.fflush(None)
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
+
     ctx = Ctx()
     if args.workload == "kmeans":
         line = run_kmeans(args, ctx, args.steps, args.warmup)
@@ -986,9 +1001,10 @@ def main() -> None:
             if ctx.rank == 0:
                 extras["bruteforce_bf16"] = brief(bf_line)
                 line["extra_workloads"] = extras
+    ctx.close()
+    restore_stdout()
     if ctx.rank == 0:
         print(json.dumps(line), flush=True)
-    ctx.close()
 
 
 if __name__ == "__main__":

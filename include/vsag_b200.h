@@ -65,6 +65,7 @@ extern "C" {
 
 typedef struct vb200_ivf* vb200_ivf_t;
 typedef struct vb200_bf* vb200_bf_t;
+typedef struct vb200_comm* vb200_comm_t;
 
 /* ---------------------------------------------------------------------------------------------
  * Library state
@@ -375,6 +376,39 @@ VB200_API int vb200_bf_remove(vb200_bf_t index, const int64_t* labels, uint64_t 
 /* Partial result for a row-sharded index, see vb200_ivf_search_partial. */
 VB200_API int vb200_bf_search_partial(vb200_bf_t index, const float* queries, uint64_t nq, uint32_t k,
                             uint64_t* keys_dev, int64_t* labels_dev);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sharded search over the GPUs of one node: one process per GPU, lists (IVF) or rows (BruteForce)
+ * dealt to the ranks, one exchange step.  The reference's analogue is a set of shard indexes built
+ * from one model whose results the caller merges (IVF::Merge and the model-equality checks,
+ * src/algorithm/ivf/ivf.cpp:1989-2050); here the exchange runs over NVLink through NCCL, which the
+ * library opens itself (libnccl.so.2) when the first communicator is created.
+ * ------------------------------------------------------------------------------------------- */
+#define VB200_COMM_ID_BYTES 128
+
+/* Rank 0 draws the communicator's id and hands it to the other ranks by whatever means the host has (a
+ * file, a socket, an existing process group); then every rank calls vb200_comm_init with its rank, after
+ * selecting its GPU with cudaSetDevice.  vb200_comm_init blocks until all `world` ranks have called it. */
+VB200_API int vb200_comm_unique_id(uint8_t* id_out /* VB200_COMM_ID_BYTES */);
+VB200_API int vb200_comm_init(vb200_comm_t* comm_out, const uint8_t* id, int rank, int world);
+VB200_API int vb200_comm_destroy(vb200_comm_t comm);
+VB200_API int vb200_comm_rank(vb200_comm_t comm);
+VB200_API int vb200_comm_world(vb200_comm_t comm);
+
+/* The whole search step of a list-sharded IVF index (vb200_ivf_set_shard(rank, world) on every rank, all
+ * ranks holding the same centroids and quantizer model), called by all ranks with the same query batch:
+ * each rank routes its slice of the batch, the probe lists and their centroid distances are all-gathered,
+ * every rank scans the probed lists it owns -- first each query's nearest list, then, after an all-reduce
+ * (MIN) of the per-query bounds, the rest -- and the per-rank top-k, packed as (key, label) arrays, are
+ * all-gathered and merged on every rank.  Every rank receives the full result, equal to the unsharded
+ * index's.  One host synchronisation at the end (plus the status checks of the tensor-core kernels). */
+VB200_API int vb200_ivf_search_sharded(vb200_ivf_t index, vb200_comm_t comm, const float* queries, uint64_t nq,
+                                       uint32_t k, uint32_t nprobe, float factor, int64_t* ids, float* dists);
+
+/* The same for a row-sharded BruteForce index: every rank searches its rows for the whole batch, the
+ * per-rank top-k are all-gathered and merged on every rank. */
+VB200_API int vb200_bf_search_sharded(vb200_bf_t index, vb200_comm_t comm, const float* queries, uint64_t nq,
+                                      uint32_t k, int64_t* ids, float* dists);
 
 #ifdef __cplusplus
 }

@@ -5,6 +5,7 @@
 
 #include "dense.cuh"
 #include "kmeans.cuh"
+#include "comm.cuh"
 #include "tc_gemm.cuh"
 
 namespace vb200 {
@@ -252,6 +253,7 @@ struct vb200_bf {
     DevBuf<uint16_t> base_hi, base_lo, q_hi, q_lo;
     bool tiled_valid = false;
     DevBuf<uint64_t> tc_out;
+    DevBuf<uint64_t> sh_local, sh_all;   // sharded search: this rank's packed [keys | labels] and the gathered ones
     DevBuf<float> row_bound;   // per query: the kcand-th candidate score after the column ranges searched so far
     TcWorkspace tc;
     DevBuf<int64_t> out_ids;
@@ -720,5 +722,36 @@ vb200_bf_search_partial(vb200_bf_t ix, const float* queries, uint64_t nq, uint32
     VB_TRY(bf_search_keys(ix, queries, nq, k));
     VB_LAUNCH(bf_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, ix->keys.ptr, total,
               ix->labels.ptr, labels_dev, nullptr, keys_dev);
+    return sync_stream();
+}
+
+extern "C" int
+vb200_bf_search_sharded(vb200_bf_t ix, vb200_comm_t comm, const float* queries, uint64_t nq, uint32_t k,
+                        int64_t* ids, float* dists) {
+    VB_CHECK_ARG(comm != nullptr, "null communicator");
+    if (comm->world == 1) {
+        return vb200_bf_search(ix, queries, nq, k, ids, dists);
+    }
+    VB_TRY(bf_check_search(ix, queries, nq, k));
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(ids != nullptr && dists != nullptr, "null output pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    cudaStream_t st = current_stream();
+    const uint64_t total = nq * k;
+    const uint32_t world = static_cast<uint32_t>(comm->world);
+    VB_TRY(ix->sh_local.reserve(2 * total));
+    VB_TRY(ix->sh_all.reserve(static_cast<size_t>(world) * 2 * total));
+    if (ix->n == 0) {
+        VB_CUDA(cudaMemsetAsync(ix->sh_local.ptr, 0xFF, 2 * total * sizeof(uint64_t), st));
+    } else {
+        VB_TRY(bf_search_keys(ix, queries, nq, k));
+        VB_LAUNCH(bf_results_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, ix->keys.ptr, total,
+                  ix->labels.ptr, reinterpret_cast<int64_t*>(ix->sh_local.ptr + total), nullptr, ix->sh_local.ptr);
+    }
+    VB_TRY(comm_all_gather(comm, ix->sh_local.ptr, ix->sh_all.ptr, 2 * total * sizeof(uint64_t), st));
+    VB_TRY(merge_partials_device(ix->sh_all.ptr, reinterpret_cast<const int64_t*>(ix->sh_all.ptr + total), world,
+                                 2 * total, nq, k, ids, dists));
     return sync_stream();
 }

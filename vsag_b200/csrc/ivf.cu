@@ -5,6 +5,7 @@
 
 #include "dense.cuh"
 #include "ivf_scan.cuh"
+#include "comm.cuh"
 #include "ivf_scan_tc.cuh"
 #include "kmeans.cuh"
 #include "rabitq.cuh"
@@ -71,6 +72,13 @@ struct SearchWorkspace {
     DevBuf<uint16_t> q_hi, q_lo;  // tensor-core routing: tiled bf16 terms of the queries
     vb200_exchange_fn exchange = nullptr;   // set for the duration of one partial search
     void* exchange_arg = nullptr;
+    const float* ext_probe_dists = nullptr;   // centroid distances of caller-given probe lists (same duration)
+    // sharded search: this rank's routed slice [probes | distances], the gathered probe lists and distances,
+    // this rank's packed partial result [keys | labels] and the gathered ones
+    DevBuf<uint32_t> sh_route_local;
+    DevBuf<int32_t> sh_probes_all;
+    DevBuf<float> sh_dists_all;
+    DevBuf<uint64_t> sh_local, sh_all;
     DevBuf<uint32_t> thr;       // [nq]
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
@@ -1092,20 +1100,21 @@ keys_to_results_kernel(const uint64_t* __restrict__ keys, uint64_t total,
 // Cross-shard merge input: labels gathered beside the keys; payload = index into the gathered
 // arrays so the label can be fetched after selection.
 __global__ void
-tag_partials_kernel(const uint64_t* __restrict__ keys, uint32_t parts, uint64_t nq, uint32_t k,
+tag_partials_kernel(const uint64_t* __restrict__ keys, uint32_t parts, uint64_t part_stride, uint64_t nq, uint32_t k,
                     uint64_t* __restrict__ tagged) {
     uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     uint64_t total = static_cast<uint64_t>(parts) * nq * k;
     if (e >= total) {
         return;
     }
-    // input [part][q][i] -> output [q][part][i]
+    // input [part][q][i] (parts part_stride keys apart) -> output [q][part][i]
     uint64_t part = e / (nq * k);
     uint64_t rem = e % (nq * k);
     uint64_t q = rem / k, i = rem % k;
-    uint64_t key = keys[e];
+    uint64_t src = part * part_stride + rem;
+    uint64_t key = keys[src];
     uint64_t o = (q * parts + part) * k + i;
-    tagged[o] = key == KEY_INF ? KEY_INF : ((key & 0xFFFFFFFF00000000ull) | static_cast<uint32_t>(e));
+    tagged[o] = key == KEY_INF ? KEY_INF : ((key & 0xFFFFFFFF00000000ull) | static_cast<uint32_t>(src));
 }
 
 static int
@@ -1981,6 +1990,7 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
     if (bucket_ids != nullptr) {
         VB_CUDA(cudaMemcpyAsync(ws.probes.ptr, bucket_ids, nq * nprobe * sizeof(int32_t),
                                 cudaMemcpyDefault, current_stream()));
+        probe_dists = ws.ext_probe_dists;   // the caller routed elsewhere and brought the distances along
     } else {
         VB_TRY(ws.probe_dists.reserve(nq * nprobe));
         VB_TRY(ivf_route_device(ix, q_dev, nq, nprobe, ws.probes.ptr, ws.probe_dists.ptr));
@@ -2851,17 +2861,15 @@ tagged_to_results_kernel(const uint64_t* __restrict__ keys, uint64_t total,
     }
 }
 
-extern "C" int
-vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32_t parts, uint64_t nq,
-                     uint32_t k, int64_t* ids, float* dists) {
-    VB_CHECK_ARG(keys_dev != nullptr && labels_dev != nullptr && ids != nullptr && dists != nullptr,
-                 "null pointer");
-    VB_CHECK_ARG(parts >= 1 && k >= 1 && k <= 1024, "bad merge shape");
-    if (nq == 0) {
-        return 0;
-    }
+namespace vb200 {
+
+// Merge of `parts` partial results [nq][k], part p's keys at keys_all + p * part_stride and its labels at
+// labels_all + p * part_stride, into ids / dists (host or device).  No host synchronisation.
+int
+merge_partials_device(const uint64_t* keys_all, const int64_t* labels_all, uint32_t parts, uint64_t part_stride,
+                      uint64_t nq, uint32_t k, int64_t* ids, float* dists) {
     const uint64_t in_total = static_cast<uint64_t>(parts) * nq * k;
-    VB_CHECK_ARG(in_total < 0xFFFFFFFFull, "merge input too large");
+    VB_CHECK_ARG(static_cast<uint64_t>(parts) * part_stride < 0xFFFFFFFFull, "merge input too large");
     // Workspace kept between calls (a serving loop merges the same shape every step); one merge
     // at a time per process.
     static std::mutex merge_mu;
@@ -2871,14 +2879,188 @@ vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32
     std::lock_guard<std::mutex> lock(merge_mu);
     VB_TRY(tagged.reserve(in_total));
     VB_TRY(merged.reserve(nq * k));
-    VB_TRY(out_ids.reserve(nq * k));
-    VB_TRY(out_dists.reserve(nq * k));
-    VB_LAUNCH(tag_partials_kernel, static_cast<uint32_t>((in_total + 255) / 256), 256, 0, keys_dev, parts,
-              nq, k, tagged.ptr);
+    VB_LAUNCH(tag_partials_kernel, static_cast<uint32_t>((in_total + 255) / 256), 256, 0, keys_all, parts,
+              part_stride, nq, k, tagged.ptr);
     VB_TRY(launch_merge(tagged.ptr, nq, static_cast<uint64_t>(parts) * k, k, merged.ptr));
+    const bool direct = is_device_pointer(ids) && is_device_pointer(dists);
+    int64_t* ids_dev = ids;
+    float* dists_dev = dists;
+    if (!direct) {
+        VB_TRY(out_ids.reserve(nq * k));
+        VB_TRY(out_dists.reserve(nq * k));
+        ids_dev = out_ids.ptr;
+        dists_dev = out_dists.ptr;
+    }
     VB_LAUNCH(tagged_to_results_kernel, static_cast<uint32_t>((nq * k + 255) / 256), 256, 0, merged.ptr,
-              nq * k, labels_dev, out_ids.ptr, out_dists.ptr);
-    VB_TRY(copy_out(ids, out_ids.ptr, nq * k));
-    VB_TRY(copy_out(dists, out_dists.ptr, nq * k));
+              nq * k, labels_all, ids_dev, dists_dev);
+    if (!direct) {
+        VB_TRY(copy_out(ids, out_ids.ptr, nq * k));
+        VB_TRY(copy_out(dists, out_dists.ptr, nq * k));
+    }
+    return 0;
+}
+
+}  // namespace vb200
+
+extern "C" int
+vb200_merge_partials(const uint64_t* keys_dev, const int64_t* labels_dev, uint32_t parts, uint64_t nq,
+                     uint32_t k, int64_t* ids, float* dists) {
+    VB_CHECK_ARG(keys_dev != nullptr && labels_dev != nullptr && ids != nullptr && dists != nullptr,
+                 "null pointer");
+    VB_CHECK_ARG(parts >= 1 && k >= 1 && k <= 1024, "bad merge shape");
+    if (nq == 0) {
+        return 0;
+    }
+    VB_TRY(merge_partials_device(keys_dev, labels_dev, parts, nq * k, nq, k, ids, dists));
     return sync_stream();
+}
+
+__global__ void
+fill_f32_kernel(float* __restrict__ out, uint64_t n, float value) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        out[i] = value;
+    }
+}
+
+// Bound exchange of the sharded search: an all-reduce (MIN) over the ranks of the communicator in `arg`.
+static int
+exchange_bounds_over_comm(float* bounds_dev, uint64_t nq, void* cuda_stream, void* arg) {
+    return comm_all_reduce_min_f32(static_cast<vb200_comm*>(arg), bounds_dev, nq, static_cast<cudaStream_t>(cuda_stream));
+}
+
+extern "C" int
+vb200_ivf_search_sharded(vb200_ivf_t ix, vb200_comm_t comm, const float* queries, uint64_t nq, uint32_t k,
+                         uint32_t nprobe, float factor, int64_t* ids, float* dists) {
+    VB_CHECK_ARG(comm != nullptr, "null communicator");
+    VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
+    if (comm->world == 1) {
+        return vb200_ivf_search(ix, queries, nq, k, nprobe, factor, nullptr, ids, dists);
+    }
+    VB_CHECK_ARG(ix->shard_world == static_cast<uint32_t>(comm->world) && ix->shard_rank == static_cast<uint32_t>(comm->rank),
+                 "the index is shard %u of %u but the communicator is rank %d of %d", ix->shard_rank, ix->shard_world,
+                 comm->rank, comm->world);
+    if (nq == 0) {
+        return 0;
+    }
+    VB_CHECK_ARG(ids != nullptr && dists != nullptr, "null output pointer");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    SearchWorkspace& ws = ix->ws;
+    cudaStream_t st = current_stream();
+    if (nprobe > ix->nlist) {
+        nprobe = ix->nlist;
+    }
+    const uint32_t world = static_cast<uint32_t>(comm->world), rank = static_cast<uint32_t>(comm->rank);
+    const uint64_t total = nq * k;
+    // VB200_SHARD_PROFILE=1: device time of the step's sections from CUDA events, averaged and printed to
+    // stderr every 20 calls (rank 0 and the last rank)
+    static const bool profile = std::getenv("VB200_SHARD_PROFILE") != nullptr && std::getenv("VB200_SHARD_PROFILE")[0] == '1';
+    static cudaEvent_t ev[6];
+    static double acc_ms[5] = {0, 0, 0, 0, 0};
+    static int n_prof = 0;
+    if (profile && n_prof == 0 && ev[0] == nullptr) {
+        for (auto& e : ev) {
+            VB_CUDA(cudaEventCreate(&e));
+        }
+    }
+    auto mark = [&](int i) {
+        if (profile) {
+            cudaEventRecord(ev[i], st);
+        }
+    };
+    mark(0);
+    // the batch on the device, once for routing and scan
+    const float* q_dev = queries;
+    if (!is_device_pointer(queries)) {
+        VB_TRY(ws.queries.reserve(nq * ix->dim));
+        VB_CUDA(cudaMemcpyAsync(ws.queries.ptr, queries, nq * ix->dim * sizeof(float), cudaMemcpyHostToDevice, st));
+        q_dev = ws.queries.ptr;
+    }
+    // 1. this rank routes rows [lo, hi) of the batch; probe lists and their centroid distances are gathered
+    const uint64_t per = (nq + world - 1) / world;
+    const uint64_t lo = std::min<uint64_t>(nq, rank * per), hi = std::min<uint64_t>(nq, lo + per);
+    const uint64_t slice_entries = per * nprobe;
+    VB_TRY(ws.sh_route_local.reserve(2 * slice_entries));
+    VB_TRY(ws.sh_probes_all.reserve(static_cast<size_t>(world) * slice_entries));
+    VB_TRY(ws.sh_dists_all.reserve(static_cast<size_t>(world) * slice_entries));
+    int32_t* probes_local = reinterpret_cast<int32_t*>(ws.sh_route_local.ptr);
+    float* dists_local = reinterpret_cast<float*>(ws.sh_route_local.ptr + slice_entries);
+    if (hi - lo < per) {
+        VB_CUDA(cudaMemsetAsync(ws.sh_route_local.ptr, 0, 2 * slice_entries * sizeof(uint32_t), st));
+    }
+    if (hi > lo) {
+        const float* q_slice = q_dev + lo * ix->dim;
+        if (ix->cosine) {
+            VB_TRY(ws.q_unit.reserve(nq * ix->dim));
+            VB_TRY(normalize_rows_f32(q_slice, hi - lo, ix->dim, ws.q_unit.ptr));
+            q_slice = ws.q_unit.ptr;
+        }
+        VB_TRY(ivf_route_device(ix, q_slice, hi - lo, nprobe, probes_local, dists_local));
+    }
+    mark(1);
+    VB_TRY(comm_group_start());
+    VB_TRY(comm_all_gather(comm, probes_local, ws.sh_probes_all.ptr, slice_entries * sizeof(int32_t), st));
+    VB_TRY(comm_all_gather(comm, dists_local, ws.sh_dists_all.ptr, slice_entries * sizeof(float), st));
+    VB_TRY(comm_group_end());
+    mark(2);
+    // 2. scan of the probed lists this rank owns, bounds shared between the two phases
+    VB_TRY(ws.sh_local.reserve(2 * total));
+    VB_TRY(ws.sh_all.reserve(static_cast<size_t>(world) * 2 * total));
+    uint64_t* keys_local = ws.sh_local.ptr;
+    int64_t* labels_local = reinterpret_cast<int64_t*>(ws.sh_local.ptr + total);
+    if (ix->n_total == 0 || ix->n_stored == 0) {
+        VB_CUDA(cudaMemsetAsync(ws.sh_local.ptr, 0xFF, 2 * total * sizeof(uint64_t), st));
+        ix->last_scan_bytes = 0;
+        if (nprobe > 1) {
+            // the ranks that hold rows exchange their bounds between the two scan phases (a search with more
+            // than one probe list has two): take part with "no bound"
+            VB_TRY(ws.bounds.reserve(nq));
+            VB_LAUNCH(fill_f32_kernel, static_cast<uint32_t>((nq + 255) / 256), 256, 0, ws.bounds.ptr, nq, INFINITY);
+            VB_TRY(comm_all_reduce_min_f32(comm, ws.bounds.ptr, nq, st));
+        }
+    } else {
+        const uint64_t* keys = nullptr;
+        ws.exchange = exchange_bounds_over_comm;
+        ws.exchange_arg = comm;
+        ws.ext_probe_dists = ws.sh_dists_all.ptr;
+        const int search_status = ivf_search_keys(ix, q_dev, nq, k, nprobe, factor, ws.sh_probes_all.ptr, &keys);
+        ws.exchange = nullptr;
+        ws.exchange_arg = nullptr;
+        ws.ext_probe_dists = nullptr;
+        VB_TRY(search_status);
+        VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
+                  ix->labels.ptr, keys_local, labels_local);
+    }
+    // 3. one gather of the packed (keys, labels) and the merge, on every rank
+    mark(3);
+    VB_TRY(comm_all_gather(comm, ws.sh_local.ptr, ws.sh_all.ptr, 2 * total * sizeof(uint64_t), st));
+    mark(4);
+    VB_TRY(merge_partials_device(ws.sh_all.ptr, reinterpret_cast<const int64_t*>(ws.sh_all.ptr + total), world, 2 * total,
+                                 nq, k, ids, dists));
+    mark(5);
+    uint64_t scalars[5] = {0, 0, 0, 0, 0};
+    VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, st));
+    VB_TRY(sync_stream());
+    if (profile) {
+        for (int i = 0; i < 5; ++i) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+            acc_ms[i] += ms;
+        }
+        if (++n_prof % 20 == 0 && (rank == 0 || rank + 1 == world)) {
+            std::fprintf(stderr, "shard-prof rank %u: route %.3f gather %.3f scan+exchange %.3f gather %.3f merge %.3f ms\n", rank,
+                         acc_ms[0] / 20, acc_ms[1] / 20, acc_ms[2] / 20, acc_ms[3] / 20, acc_ms[4] / 20);
+            for (auto& a : acc_ms) {
+                a = 0;
+            }
+        }
+    }
+    if (ix->n_total != 0 && ix->n_stored != 0) {
+        ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
+        ix->last_scanned_bytes = static_cast<int64_t>(ws.pruning ? scalars[3] : scalars[0]);
+        if (scalars[4] != 0) {
+            VB_FAIL(VB200_INTERNAL_ERROR, "the tensor-core scan gave up on a bounded wait");
+        }
+    }
+    return 0;
 }

@@ -319,6 +319,19 @@ class IvfHandle:
                                                  nprobe, factor, ptr(bucket_ids, np.int32), cb, None,
                                                  ptr(keys_dev), ptr(labels_dev)))
 
+    def search_sharded(self, comm, queries, k: int, nprobe: int, factor: float = 2.0, out=None):
+        """The whole step of a list-sharded search (vb200_ivf_search_sharded); `comm` is a parallel.Comm.
+        Every rank calls it with the same batch and gets the full result."""
+        nq = _rows(queries)
+        if out is None:
+            ids = _empty_like_side(queries, (nq, k), np.int64)
+            dists = _empty_like_side(queries, (nq, k), np.float32)
+        else:
+            ids, dists = out
+        check(self._lib.vb200_ivf_search_sharded(self._h, comm.handle, ptr(queries, np.float32), nq, k, nprobe, factor,
+                                                 ptr(ids), ptr(dists)))
+        return ids, dists
+
     def last_scanned_bytes(self) -> int:
         """Bytes of codes the last search read after list pruning (<= last_scan_bytes)."""
         return int(self._lib.vb200_ivf_last_scanned_bytes(self._h))
@@ -410,6 +423,18 @@ class BfHandle:
     def search_partial(self, queries, k: int, keys_dev, labels_dev) -> None:
         check(self._lib.vb200_bf_search_partial(self._h, ptr(queries, np.float32), _rows(queries), k,
                                                 ptr(keys_dev), ptr(labels_dev)))
+
+    def search_sharded(self, comm, queries, k: int, out=None):
+        """The whole step of a row-sharded search (vb200_bf_search_sharded); `comm` is a parallel.Comm."""
+        nq = _rows(queries)
+        if out is None:
+            ids = _empty_like_side(queries, (nq, k), np.int64)
+            dists = _empty_like_side(queries, (nq, k), np.float32)
+        else:
+            ids, dists = out
+        check(self._lib.vb200_bf_search_sharded(self._h, comm.handle, ptr(queries, np.float32), nq, k, ptr(ids),
+                                                ptr(dists)))
+        return ids, dists
 
 
 __all__ = [name for name in globals() if not name.startswith("_")]

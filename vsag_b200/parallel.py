@@ -82,6 +82,38 @@ def make_bounds_exchange(dist, device, group=None, seen=None):
     return _capi.EXCHANGE_FN(exchange)
 
 
+class Comm:
+    """A communicator of the library's own (vb200_comm_init: NCCL opened by the shared library), one rank
+    per GPU.  The id rank 0 draws travels to the others through an existing torch.distributed group, which
+    is used for nothing else; the CUDA device must be selected before."""
+
+    def __init__(self, dist, rank: int, world: int, device):
+        import ctypes as C
+
+        import torch
+
+        from . import _capi
+
+        lib = _capi.load()
+        ident = np.zeros(128, np.uint8)
+        if rank == 0:
+            _capi.check(lib.vb200_comm_unique_id(_capi.ptr(ident)))
+        on_gpu = getattr(device, "type", str(device)) == "cuda"
+        carrier = torch.from_numpy(ident).to(device) if on_gpu else torch.from_numpy(ident)
+        dist.broadcast(carrier, src=0)
+        ident = carrier.cpu().numpy().copy()
+        handle = C.c_void_p()
+        _capi.check(lib.vb200_comm_init(C.byref(handle), _capi.ptr(ident), rank, world))
+        self.handle, self.rank, self.world, self._lib = handle, rank, world, lib
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self._lib.vb200_comm_destroy(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+
 class ShardedIvfSearch:
     """Search step of a list-sharded IVF index on this rank's GPU.
 
@@ -90,10 +122,11 @@ class ShardedIvfSearch:
     batch -- first each query's nearest list on the rank, then, after an all-reduce (MIN) of the
     per-query bounds, the others -- and the partial top-k are all-gathered and merged."""
 
-    def __init__(self, index, nq: int, k: int, world: int, device, dist, rank: int = 0):
+    def __init__(self, index, nq: int, k: int, world: int, device, dist, rank: int = 0, comm=None):
         import torch
 
         self.index, self.nq, self.k, self.world, self.dist, self.rank = index, nq, k, world, dist, rank
+        self.comm = comm   # a Comm: the whole step then runs inside the library (vb200_ivf_search_sharded)
         self.keys_local = torch.empty((nq, k), dtype=torch.int64, device=device)
         self.labels_local = torch.empty((nq, k), dtype=torch.int64, device=device)
         self.keys_all = torch.empty((world, nq, k), dtype=torch.int64, device=device)
@@ -118,6 +151,9 @@ class ShardedIvfSearch:
 
     def search(self, queries, nprobe: int, factor: float, out_ids, out_dists):
         from . import _capi
+
+        if self.comm is not None:
+            return self.index.search_sharded(self.comm, queries, self.k, nprobe, factor, out=(out_ids, out_dists))
 
         probes = self._route(queries, nprobe) if self.world > 1 else None
         self.index.search_partial(queries, self.k, nprobe, factor, self.keys_local, self.labels_local,
