@@ -113,38 +113,52 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
         self.thread = None
+        self.t_begin = None
 
     def start(self) -> None:
+        """Starts nvidia-smi in its sampling loop and waits for its first line (its start-up takes driver
+        locks for tens of milliseconds, which must not fall into a timed region)."""
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
+        deadline = time.time() + 3.0
+        while not self.lines and time.time() < deadline:
+            time.sleep(0.01)
+        self.t_begin = time.time()
 
     def _pump(self) -> None:
         assert self.proc is not None and self.proc.stdout is not None
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self) -> dict:
+        """Ends the sampling; the samples taken since start() returned (the timed region) are summarised,
+        or, if the region was shorter than one sampling period, the ones on either side of it."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        t_end = time.time()
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        inside = [text for t, text in self.lines if self.t_begin is not None and self.t_begin <= t <= t_end]
+        around = [text for t, text in self.lines
+                  if self.t_begin is not None and self.t_begin - 0.05 <= t <= t_end + 0.05]
+        lines = inside or around or [text for _, text in self.lines]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -158,7 +172,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "samples_inside_timed_region": len(inside)}
 
 
 class Ctx:

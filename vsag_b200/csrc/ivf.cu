@@ -893,7 +893,7 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
 
 // One CTA per phase: exclusive prefixes of (pairs) and of (tiles of qt queries) over the lists
 // taken in `order` (pair_off is stored by list, item_off by position in the order), plus the
-// logical scan volume sum(pairs[l] * len[l]).
+// logical scan volume sum(pairs[l] * len[l]).  pair_items_kernel turns the prefixes into work items.
 __global__ void __launch_bounds__(1024)
 pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
                  const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt, uint32_t code_size,
@@ -901,7 +901,6 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const
     const uint32_t* __restrict__ pair_cnt = blockIdx.x == 0 ? tables.cnt[0] : tables.cnt[1];
     uint32_t* __restrict__ pair_off = blockIdx.x == 0 ? tables.off[0] : tables.off[1];
     uint32_t* __restrict__ item_off = blockIdx.x == 0 ? tables.item_off[0] : tables.item_off[1];
-    ScanItemDesc* __restrict__ item_map = blockIdx.x == 0 ? tables.item_map[0] : tables.item_map[1];
     __shared__ uint32_t s_pairs[1024];
     __shared__ uint32_t s_items[1024];
     __shared__ unsigned long long s_bytes;
@@ -943,18 +942,6 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const
         const uint32_t t = (c + qt - 1) / qt;
         pair_off[l] = run_p;
         item_off[pos] = run_t;
-        for (uint32_t j = 0; j < t; ++j) {   // the scan's work queue reads its items from here
-            ScanItemDesc d;
-            d.list = l;
-            d.pbeg = run_p + j * qt;
-            d.nqt = c - j * qt < qt ? c - j * qt : qt;
-            d.lbeg = list_off[l];
-            d.len = list_off[l + 1] - list_off[l];
-            d.goff = group_off != nullptr ? group_off[l] : 0u;
-            d.pad0 = 0;
-            d.pad1 = 0;
-            item_map[run_t + j] = d;
-        }
         run_p += c;
         run_t += t;
     }
@@ -964,6 +951,38 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const
         pair_off[nlist] = s_pairs[1023];
         item_off[nlist] = s_items[1023];
         atomicAdd(reinterpret_cast<unsigned long long*>(scalars), s_bytes);  // logical scan volume, both phases
+    }
+}
+
+// The work items of the scan's queue, written from the prefixes above: one thread per list position and
+// phase (blockIdx.y), each writing the descriptors of its list's tiles of qt queries.
+__global__ void __launch_bounds__(256)
+pair_items_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
+                  const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt) {
+    const uint32_t pos = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pos >= nlist) {
+        return;
+    }
+    const uint32_t ph = blockIdx.y;
+    const uint32_t l = order[pos];
+    const uint32_t c = tables.cnt[ph][l];
+    if (c == 0) {
+        return;
+    }
+    const uint32_t t = (c + qt - 1) / qt;
+    const uint32_t first_pair = tables.off[ph][l], first_item = tables.item_off[ph][pos];
+    ScanItemDesc d;
+    d.list = l;
+    d.lbeg = list_off[l];
+    d.len = list_off[l + 1] - d.lbeg;
+    d.goff = group_off != nullptr ? group_off[l] : 0u;
+    d.pad0 = 0;
+    d.pad1 = 0;
+    ScanItemDesc* __restrict__ item_map = tables.item_map[ph];
+    for (uint32_t j = 0; j < t; ++j) {
+        d.pbeg = first_pair + j * qt;
+        d.nqt = c - j * qt < qt ? c - j * qt : qt;
+        item_map[first_item + j] = d;
     }
 }
 
@@ -1719,6 +1738,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                   ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
         VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->group_off.ptr, ix->scan_order.ptr, nlist,
                   queries_per_item, ix->code_size, ws.scalars.ptr);
+        VB_LAUNCH(pair_items_kernel, dim3((nlist + 255) / 256, 2), 256, 0, tables, ix->list_off.ptr, ix->group_off.ptr,
+                  ix->scan_order.ptr, nlist, queries_per_item);
         VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
                   ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
         return 0;

@@ -725,68 +725,82 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
 
         const uint32_t lbeg = p.list_off[list];
         const uint32_t len = p.list_off[list + 1] - lbeg;
-        for (uint32_t r0 = 0; r0 < len; r0 += SCAN_THREADS) {
-            const uint32_t row = r0 + threadIdx.x;
-            const bool valid = row < len;
-            const uint8_t* code = p.codes + static_cast<uint64_t>(lbeg + (valid ? row : 0)) * p.code_stride;
-            float acc[QT];
+        // Two rows per thread: every shared-memory read of a query's four values feeds eight additions,
+        // and a thread carries 2 * QT independent chains.
+        for (uint32_t r0 = 0; r0 < len; r0 += 2 * SCAN_THREADS) {
+            uint32_t rows[2] = {r0 + threadIdx.x, r0 + SCAN_THREADS + threadIdx.x};
+            const bool valid[2] = {rows[0] < len, rows[1] < len};
+            const uint8_t* code[2] = {p.codes + static_cast<uint64_t>(lbeg + (valid[0] ? rows[0] : 0)) * p.code_stride,
+                                      p.codes + static_cast<uint64_t>(lbeg + (valid[1] ? rows[1] : 0)) * p.code_stride};
+            float acc[2][QT];
 #pragma unroll
             for (int qi = 0; qi < QT; ++qi) {
-                acc[qi] = 0.f;
+                acc[0][qi] = 0.f;
+                acc[1][qi] = 0.f;
             }
             for (uint32_t c = 0; c < bits_bytes; c += 4) {
                 // Sign bits of 32 dimensions; bytes past the sign field are never read because
                 // bits_bytes is a multiple of 4 and the loop stops there.
-                uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(code + c));
+                const uint32_t w0 = __ldg(reinterpret_cast<const uint32_t*>(code[0] + c));
+                const uint32_t w1 = __ldg(reinterpret_cast<const uint32_t*>(code[1] + c));
                 const uint32_t d0 = c * 8;
 #pragma unroll
-                for (int g = 0; g < QT; g += 4) {
-                    if (g < nqt) {
+                for (int b4 = 0; b4 < 8; ++b4) {
+                    // bit set -> +sv, clear -> -sv.  fma(sv, +-1, acc) rounds exactly like
+                    // acc + (+-sv), and the multipliers are shared by the tile's queries.
+                    const uint32_t n0 = ~w0 >> (4 * b4), n1 = ~w1 >> (4 * b4);
+                    const float a0 = __uint_as_float(0x3F800000u | ((n0 & 1u) << 31));
+                    const float a1 = __uint_as_float(0x3F800000u | ((n0 & 2u) << 30));
+                    const float a2 = __uint_as_float(0x3F800000u | ((n0 & 4u) << 29));
+                    const float a3 = __uint_as_float(0x3F800000u | ((n0 & 8u) << 28));
+                    const float b0 = __uint_as_float(0x3F800000u | ((n1 & 1u) << 31));
+                    const float b1 = __uint_as_float(0x3F800000u | ((n1 & 2u) << 30));
+                    const float b2 = __uint_as_float(0x3F800000u | ((n1 & 4u) << 29));
+                    const float b3 = __uint_as_float(0x3F800000u | ((n1 & 8u) << 28));
 #pragma unroll
-                        for (int b4 = 0; b4 < 8; ++b4) {
-                            // bit set -> +sv, clear -> -sv.  fma(sv, +-1, acc) rounds exactly like
-                            // acc + (+-sv), and the four multipliers are shared by the tile's queries.
-                            const uint32_t nb = ~w >> (4 * b4);
-                            const float m0 = __uint_as_float(0x3F800000u | ((nb & 1u) << 31));
-                            const float m1 = __uint_as_float(0x3F800000u | ((nb & 2u) << 30));
-                            const float m2 = __uint_as_float(0x3F800000u | ((nb & 4u) << 29));
-                            const float m3 = __uint_as_float(0x3F800000u | ((nb & 8u) << 28));
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                float4 s = *reinterpret_cast<const float4*>(sv + (g + u) * dpad + d0 + 4 * b4);
-                                float a = acc[g + u];
-                                a = fmaf(s.x, m0, a);
-                                a = fmaf(s.y, m1, a);
-                                a = fmaf(s.z, m2, a);
-                                a = fmaf(s.w, m3, a);
-                                acc[g + u] = a;
-                            }
+                    for (int qi = 0; qi < QT; ++qi) {
+                        if (qi < nqt) {
+                            const float4 sq = *reinterpret_cast<const float4*>(sv + qi * dpad + d0 + 4 * b4);
+                            float x = acc[0][qi], y = acc[1][qi];
+                            x = fmaf(sq.x, a0, x);
+                            y = fmaf(sq.x, b0, y);
+                            x = fmaf(sq.y, a1, x);
+                            y = fmaf(sq.y, b1, y);
+                            x = fmaf(sq.z, a2, x);
+                            y = fmaf(sq.z, b2, y);
+                            x = fmaf(sq.w, a3, x);
+                            y = fmaf(sq.w, b3, y);
+                            acc[0][qi] = x;
+                            acc[1][qi] = y;
                         }
                     }
                 }
             }
-            if (valid) {
-                float bn = __ldg(reinterpret_cast<const float*>(code + bits_bytes));
-                float err = __ldg(reinterpret_cast<const float*>(code + bits_bytes + 4));
-                if (static_cast<double>(fabsf(err)) < 1e-5) {  // float compared with a double literal, as in the reference
-                    err = err >= 0.f ? 1.0f : -1.0f;
-                }
 #pragma unroll
-                for (int qi = 0; qi < QT; ++qi) {
-                    if (qi < nqt) {
-                        float qn = s_qnorm[qi];
-                        float est = __fdiv_rn(acc[qi], err);
-                        float p1 = __fmul_rn(bn, bn);
-                        float p2 = __fmul_rn(qn, qn);
-                        float p3 = __fmul_rn(__fmul_rn(__fmul_rn(-2.0f, bn), qn), est);
-                        float dist = __fadd_rn(__fadd_rn(p1, p2), p3);
-                        ts.push(p, qi, dist, lbeg + row);
+            for (int h = 0; h < 2; ++h) {
+                if (valid[h]) {
+                    float bn = __ldg(reinterpret_cast<const float*>(code[h] + bits_bytes));
+                    float err = __ldg(reinterpret_cast<const float*>(code[h] + bits_bytes + 4));
+                    if (static_cast<double>(fabsf(err)) < 1e-5) {  // float compared with a double literal, as in the reference
+                        err = err >= 0.f ? 1.0f : -1.0f;
+                    }
+#pragma unroll
+                    for (int qi = 0; qi < QT; ++qi) {
+                        if (qi < nqt) {
+                            float qn = s_qnorm[qi];
+                            float est = __fdiv_rn(acc[h][qi], err);
+                            float p1 = __fmul_rn(bn, bn);
+                            float p2 = __fmul_rn(qn, qn);
+                            float p3 = __fmul_rn(__fmul_rn(__fmul_rn(-2.0f, bn), qn), est);
+                            float dist = __fadd_rn(__fadd_rn(p1, p2), p3);
+                            ts.push(p, qi, dist, lbeg + rows[h]);
+                        }
                     }
                 }
+                __syncthreads();
+                ts.make_room(nqt);
+                __syncthreads();
             }
-            __syncthreads();
-            ts.make_room(nqt);
-            __syncthreads();
         }
         ts.finish(nqt, p.part, p.thr_g);
     }
