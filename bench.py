@@ -59,7 +59,7 @@ FP32_FMA_PEAK_T = 148 * 128 * 1.965e9 / 1e12   # fp32 FMA/s of one B200 in units
 # 2,000,000-row case) per byte of codes the kernel reported as read in that capture: lists that several
 # tiles scan are L2 hits after the first, so the ratio is below one.  `traffic` is this ratio times the
 # code bytes the timed run itself reports, per rank.
-SCAN_DRAM_PER_CODE_BYTE = 0.79
+SCAN_DRAM_PER_CODE_BYTE = 0.83   # profiles/ivf_sq8_scan_tc_kernel_2M_set_full.md: 123.1 MB of DRAM traffic for 148.3 MB of codes
 WORKLOAD_NAME = "IVF-SQ8 search, 10M x 96, nlist 16384, nprobe 64, 10000 queries, k 10"
 METRIC_NAME = "QPS at nprobe=64, IVF-SQ8 10Mx96, k=10"
 
@@ -398,21 +398,23 @@ def scan_probe(ix, step_fn, repeats: int):
     return float(np.mean(ms)), float(np.mean(logical)), float(np.mean(read))
 
 
-def scan_roofline(peaks: dict, kernel_ms: float, logical: float, read: float, unique_bytes: float | None) -> dict:
+def scan_roofline(peaks: dict, kernel_ms: float, logical: float, read: float, unique_bytes: float | None,
+                  pruned: bool = True) -> dict:
     """Roofline of the scan kernel on the bytes it fetched, with the logical figure beside it.
 
     read     pairs scanned x list length x code size: what the kernel's loads requested (a list scanned
              by several query tiles counts once per tile; most of those re-reads are L2 hits)
     logical  the reference's scan volume: every (query, probed list) pair, pruned or not
-    One FMA is issued per (query, code byte) scanned, so `read` is also the FMA count."""
+    On the tensor-core kernel a (query, code byte) is three int8 multiply-adds; `read` is that count / 3."""
     peak = peaks["hbm_gbs"]
     sec = kernel_ms / 1e3
     achieved = read / sec / 1e9
-    out = {"bound": "hbm", "kernel": "ivf_sq8_scan_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    out = {"bound": "hbm", "kernel": "ivf_sq8_scan_tc_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
            "frac": achieved / peak, "peak_source": peaks["hbm_kind"], "kernel_ms": kernel_ms,
-           "traffic": SCAN_DRAM_PER_CODE_BYTE * read,
+           # the captured ratio belongs to the pruned step; no capture exists of the unpruned one
+           "traffic": SCAN_DRAM_PER_CODE_BYTE * read if pruned else None,
            "traffic_source": f"{SCAN_DRAM_PER_CODE_BYTE} DRAM bytes per code byte read (ncu capture of the 2M-row "
-                             "case) x code_bytes_read of this run and rank",
+                             "case, both scan launches of a step) x code_bytes_read of this run and rank",
            "code_bytes_read": read, "algorithmic_bytes": logical, "algorithmic_gbs": logical / sec / 1e9,
            "algorithmic_frac": logical / sec / 1e9 / peak,
            "note": "achieved = code bytes the kernel read / its device time; algorithmic_* counts every probed "
@@ -422,11 +424,17 @@ def scan_roofline(peaks: dict, kernel_ms: float, logical: float, read: float, un
     return out
 
 
+INT8_TENSOR_PEAK_TOPS = 4500.0   # nominal dense int8 rate of one B200 (no measured figure exists for kind::i8)
+
+
 def fma_roofline(kernel_ms: float, macs: float) -> dict:
-    t = macs / (kernel_ms / 1e3) / 1e12
-    return {"bound": "fp32 fma pipe", "achieved": t, "peak": FP32_FMA_PEAK_T, "unit": "TFMA/s",
-            "frac": t / FP32_FMA_PEAK_T, "peak_source": "nominal: 148 SMs x 128 lanes x 1.965 GHz",
-            "note": "multiply-adds of the ranking form: one per (query, code byte) scanned"}
+    """The scan's arithmetic against the tensor pipe: every (query, code byte) scanned is three int8
+    multiply-adds (the three terms of the query weight) on `tcgen05.mma.kind::i8`."""
+    t = 6.0 * macs / (kernel_ms / 1e3) / 1e12
+    return {"bound": "tensor (int8)", "achieved": t, "peak": INT8_TENSOR_PEAK_TOPS, "unit": "TOP/s",
+            "frac": t / INT8_TENSOR_PEAK_TOPS, "peak_source": "nominal dense int8",
+            "note": "2 x 3 int8 terms per (query, code byte) scanned; work items are padded to 32 queries, so the "
+                    "pipe executes more than this"}
 
 
 def run_ivf_sq8(args, ctx: Ctx) -> dict:
@@ -522,7 +530,7 @@ def run_ivf_sq8(args, ctx: Ctx) -> dict:
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roof,
-        "roofline_fma": fma_roofline(kernel_ms, read),
+        "roofline_tensor": fma_roofline(kernel_ms, read),
     }
     if world > 1 or env_int("VB200_BENCH_SKIP_EXTRAS", 0):
         return line
@@ -558,12 +566,12 @@ def run_ivf_sq8(args, ctx: Ctx) -> dict:
     off_ids = out_ids.cpu().numpy()
     ix.set_list_pruning(True)
     uniq = unique_bytes(host["probes"])
-    off_roof = scan_roofline(ctx.peaks, k_ms, lg, rd, uniq)
+    off_roof = scan_roofline(ctx.peaks, k_ms, lg, rd, uniq, pruned=False)
     line["pruning_off"] = {
         "ms_per_step": off_ms, "value": n_query / (off_ms / 1e3), "kernel_ms": k_ms,
         "frac": uniq / (k_ms / 1e3) / 1e9 / ctx.peaks["hbm_gbs"],
         "frac_note": "probed lists' codes counted once each (the bytes that must cross HBM) / kernel time / HBM peak",
-        "frac_pairs": off_roof["frac"], "frac_fma": fma_roofline(k_ms, rd)["frac"],
+        "frac_pairs": off_roof["frac"], "frac_tensor_int8": fma_roofline(k_ms, rd)["frac"],
         "code_bytes_read": rd, "unique_list_bytes": uniq,
         "ids_agree_with_cpu": float(np.mean(cpu_ids == off_ids[:sample])),
         "ids_agree_with_pruned": float(np.mean(off_ids == ids_host.numpy())),
@@ -629,7 +637,7 @@ def second_base_run(args, ctx: Ctx, engine, n_base: int, n_query: int, nlist: in
            "ids_agree_with_cpu": float(np.mean(want_ids == got[:ssample])), "ids_sample": ssample,
            "cpu_qps": ssample / dt, "cpu_cores": cores, "cpu_kind": kind,
            "roofline": scan_roofline(ctx.peaks, k_ms, lg, rd, uniq),
-           "frac_fma": fma_roofline(k_ms, rd)["frac"],
+           "frac_tensor_int8": fma_roofline(k_ms, rd)["frac"],
            "pruned_share_of_pairs": 1.0 - rd / lg if lg > 0 else None}
     ix.close()
     return out
