@@ -59,7 +59,7 @@ FP32_FMA_PEAK_T = 148 * 128 * 1.965e9 / 1e12   # fp32 FMA/s of one B200 in units
 # 2,000,000-row case) per byte of codes the kernel reported as read in that capture: lists that several
 # tiles scan are L2 hits after the first, so the ratio is below one.  `traffic` is this ratio times the
 # code bytes the timed run itself reports, per rank.
-SCAN_DRAM_PER_CODE_BYTE = 0.83   # profiles/ivf_sq8_scan_tc_kernel_2M_set_full.md: 123.1 MB of DRAM traffic for 148.3 MB of codes
+SCAN_DRAM_PER_CODE_BYTE = 0.83   # 123.1 MB of DRAM traffic for 148.3 MB of codes fetched
 WORKLOAD_NAME = "IVF-SQ8 search, 10M x 96, nlist 16384, nprobe 64, 10000 queries, k 10"
 METRIC_NAME = "QPS at nprobe=64, IVF-SQ8 10Mx96, k=10"
 

@@ -297,6 +297,23 @@ VB200_API int vb200_ivf_remove(vb200_ivf_t index, const int64_t* labels, uint64_
 VB200_API int vb200_ivf_route(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t nprobe,
                     int32_t* bucket_ids, float* bucket_dists);
 
+/* Per-call search options of IndexSearchParameter (src/algorithm/index_search_parameter.h:27-57).
+ * enable_reorder = 0: an index built with use_reorder answers with the quantized distances of its k best
+ * (no factor * k candidates, no exact re-ranking: IVF::SearchWithRequest, src/algorithm/ivf/ivf.cpp:2312-2321).
+ * has_timeout != 0: once timeout_ms have passed since the call's device work began the scan hands out no
+ * further list, the call returns what it found and *timed_out is 1 -- the reference checks its timer between
+ * buckets and reports is_timeout in the statistics (ivf.cpp:1747-1751). */
+typedef struct vb200_search_options {
+    int enable_reorder;
+    int has_timeout;
+    double timeout_ms;
+} vb200_search_options;
+
+/* vb200_ivf_search_filtered with options (NULL = defaults: reorder on, no timeout); timed_out may be NULL. */
+VB200_API int vb200_ivf_search_ex(vb200_ivf_t index, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe,
+                        float factor, const int32_t* bucket_ids, const vb200_filter* filter,
+                        const vb200_search_options* options, int64_t* ids, float* dists, int* timed_out);
+
 /* Called by vb200_ivf_search_partial between its two scan phases: bounds_dev[nq] holds, per query,
  * the distance bound this shard has found so far (+inf = none).  The callee replaces every entry
  * by the minimum over all shards (an all-reduce with MIN on the communicator it owns), enqueued

@@ -44,9 +44,15 @@ def test_range_is_knn_cut_at_the_radius(oracle, name, index_param, search):
             assert set(got_i.tolist()) == set((truth_i[qi][:want_count] + 50).tolist())
             lim_i, lim_d = index.range_search(queries[qi], radius, 5, sp)       # the nearest five of them
             assert np.array_equal(lim_d, d[:min(5, want_count)])
+    # more in-radius vectors than one search can return (512): fetched in pages, still every one of them
+    far_i, far_d = oracle.bf_search_fp32(base, queries[:2], 1400)
+    for qi, count in ((0, 599), (1, 1300)):
+        wide = float((far_d[qi][count - 1] + far_d[qi][count]) / 2)
+        got_i, got_d = index.range_search(queries[qi], wide, -1, sp)
+        assert len(got_i) == count and len(set(got_i.tolist())) == count
+        assert np.array_equal(got_d, far_d[qi][:count])
+        assert set(got_i.tolist()) == set((far_i[qi][:count] + 50).tolist())
     wide = float(truth_d[0][599])
-    with pytest.raises(VsagError, match="limited_size"):                           # more than 512 in range
-        index.range_search(queries[0], wide, -1, sp)
     got_i, got_d = index.range_search(queries[0], wide, 40, sp)
     assert np.array_equal(got_d, truth_d[0][:40])
     for bad in (dict(radius=-1.0, k=5), dict(radius=float("nan"), k=5), dict(radius=1.0, k=0)):

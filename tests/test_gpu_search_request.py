@@ -111,3 +111,54 @@ def test_brute_force_rejects_bucket_lists(oracle):
     assert np.array_equal(got[0], want[0])
     with pytest.raises(VsagError, match="only supported by the ivf index"):
         index.search_with_request(base[:1], K, "{}", [[0]])
+
+
+def test_enable_reorder_false_answers_like_an_index_without_reorder(oracle):
+    """`enable_reorder` (src/algorithm/index_search_parameter.h:46-48): with it off, an index built with
+    use_reorder scans for k candidates and returns their quantized distances, which is what the same index
+    built without reorder returns (IVF::SearchWithRequest, src/algorithm/ivf/ivf.cpp:2312-2321)."""
+    from vsag_b200.index import Index
+
+    base = oracle.gen_uniform(47, N * DIM, 0.1, 0.9).reshape(N, DIM)
+    queries = oracle.gen_uniform(48, 8 * DIM, 0.1, 0.9).reshape(8, DIM)
+    made = {}
+    for reorder in (False, True):
+        made[reorder] = Index("ivf", json.dumps({
+            "dtype": "float32", "metric_type": "l2", "dim": DIM,
+            "index_param": {"buckets_count": NLIST, "base_quantization_type": "sq8", "use_reorder": reorder}}))
+        made[reorder].build(base, np.arange(N, dtype=np.int64), N, DIM)
+    plain = made[False].knn_search_batch(queries, K, SEARCH)
+    off = made[True].knn_search_batch(queries, K, json.dumps({"ivf": {"scan_buckets_count": NLIST, "enable_reorder": False}}))
+    on = made[True].knn_search_batch(queries, K, json.dumps({"ivf": {"scan_buckets_count": NLIST, "factor": 3.0}}))
+    assert np.array_equal(off[0], plain[0]) and np.array_equal(off[1], plain[1])
+    # with reorder the distances are exact fp32 ones and differ from the quantized ones
+    exact = ((base[on[0]] - queries[:, None, :]) ** 2).sum(-1)      # of the ids it returned
+    np.testing.assert_allclose(on[1], exact, rtol=1e-5)
+    assert not np.array_equal(on[1], plain[1])
+    # keys the reference's parser does not know are ignored, as IVFSearchParameters::FromJson does
+    odd = made[False].knn_search_batch(queries, K, json.dumps({"ivf": {"scan_buckets_count": NLIST, "no_such_key": 1,
+                                                                       "parallelism": 4}}))
+    assert np.array_equal(odd[0], plain[0])
+
+
+def test_timeout_stops_the_scan_and_is_reported(engine, oracle):
+    """`timeout_ms` (src/algorithm/index_search_parameter.h:35-38): the reference checks its timer between
+    buckets, stops scanning and reports is_timeout (src/algorithm/ivf/ivf.cpp:1747-1751).  A budget that has
+    passed before the scan starts returns nothing and says so; a generous one changes nothing."""
+    n, dim, nlist = 20_000, 32, 64
+    from conftest import mixture
+
+    x = mixture(5, n, dim, nlist, 0.15)
+    q = mixture(6, 50, dim, nlist, 0.15)
+    ix = engine.IvfHandle(dim, engine.METRIC_L2, nlist, engine.QUANT_SQ8)
+    ix.train(x, iters=3, init=x[:nlist].copy())
+    ix.add(x, np.arange(n, dtype=np.int64))
+    want_i, want_d = ix.search(q, 10, 8)
+    got_i, got_d, late = ix.search_ex(q, 10, 8, timeout_ms=60_000)
+    assert not late and np.array_equal(got_i, want_i) and np.array_equal(got_d, want_d)
+    got_i, got_d, late = ix.search_ex(q, 10, 8, timeout_ms=0)
+    assert late
+    assert np.all(got_i == -1) and np.all(np.isinf(got_d))
+    # and the next search is whole again
+    got_i, got_d, late = ix.search_ex(q, 10, 8)
+    assert not late and np.array_equal(got_i, want_i)

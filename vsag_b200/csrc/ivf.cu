@@ -83,7 +83,10 @@ struct SearchWorkspace {
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
     DevBuf<uint64_t> keys2;     // [nq x k] after rerank
-    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases, [3] bytes read, [4] tensor-core scan error flag
+    DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases, [3] bytes read, [4] tensor-core scan error flag,
+                                // [5] the deadline passed, [6] the deadline (%globaltimer value; written by deadline_stamp_kernel)
+    bool opt_no_reorder = false;   // search options of the running call (vb200_search_options)
+    bool opt_deadline = false;
     DevBuf<int64_t> out_ids;
     DevBuf<float> out_dists;
 };
@@ -1705,14 +1708,14 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     VB_TRY(ws.thr.reserve(nq));
     VB_TRY(ws.part.reserve(total * kscan));
     VB_TRY(ws.keys.reserve(nq * kfinal));
-    VB_TRY(ws.scalars.reserve(5));
+    VB_TRY(ws.scalars.reserve(8));
     if (sq8) {
         VB_TRY(ws.qw.reserve(nq * ix->dpad));
         VB_TRY(ws.qa.reserve(nq));
         VB_TRY(ws.merged.reserve(nq * kscan));
     }
     cudaStream_t st = current_stream();
-    VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, 5 * sizeof(uint64_t), st));
+    VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, 6 * sizeof(uint64_t), st));   // not [6]: the deadline is stamped before routing
     VB_CUDA(cudaMemsetAsync(ws.thr.ptr, 0xFF, nq * sizeof(uint32_t), st));
     VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
     const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
@@ -1841,6 +1844,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         }
         p.n_phases = count;
         p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + queue_slot);
+        p.deadline = ws.opt_deadline ? reinterpret_cast<const unsigned long long*>(ws.scalars.ptr + 6) : nullptr;
+        p.timed_out = reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 5);
         if (sq8 && on_tensor_cores) {
             TcScanParams tp{};
             tp.s = p;
@@ -1984,7 +1989,7 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
         nprobe = ix->nlist;  // clamp like IVF::create_search_param (ivf.cpp:1573-1575)
     }
     uint32_t kscan = k;
-    const bool rerank = ix->use_reorder;
+    const bool rerank = ix->use_reorder && !ws.opt_no_reorder;
     if (rerank) {
         VB_CHECK_ARG(factor > 0.0f, "factor must be positive when use_reorder is true, got %f", factor);
         kscan = static_cast<uint32_t>(static_cast<int64_t>(factor * static_cast<float>(k)));
@@ -2737,10 +2742,29 @@ vb200_ivf_search(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, 
     return vb200_ivf_search_filtered(ix, queries, nq, k, nprobe, factor, bucket_ids, nullptr, ids, dists);
 }
 
+// *deadline = now + budget on the GPU's own clock; launched first in a search with a timeout, so the budget
+// runs from the start of the call's device work.
+__global__ void
+deadline_stamp_kernel(unsigned long long* deadline, unsigned long long budget_ns) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    *deadline = now + budget_ns;
+}
+
 extern "C" int
 vb200_ivf_search_filtered(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe,
                           float factor, const int32_t* bucket_ids, const vb200_filter* filter, int64_t* ids,
                           float* dists) {
+    return vb200_ivf_search_ex(ix, queries, nq, k, nprobe, factor, bucket_ids, filter, nullptr, ids, dists, nullptr);
+}
+
+extern "C" int
+vb200_ivf_search_ex(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t k, uint32_t nprobe, float factor,
+                    const int32_t* bucket_ids, const vb200_filter* filter, const vb200_search_options* options,
+                    int64_t* ids, float* dists, int* timed_out) {
+    if (timed_out != nullptr) {
+        *timed_out = 0;
+    }
     VB_TRY(check_search_ready(ix, queries, nq, k, nprobe));
     if (nq == 0) {
         return 0;
@@ -2748,6 +2772,26 @@ vb200_ivf_search_filtered(vb200_ivf_t ix, const float* queries, uint64_t nq, uin
     VB_CHECK_ARG(ids != nullptr && dists != nullptr, "null output pointer");
     std::lock_guard<std::mutex> lock(ix->mu);
     SearchWorkspace& ws = ix->ws;
+    struct OptionScope {   // the options hold for this call only, whatever way it ends
+        SearchWorkspace& w;
+        ~OptionScope() {
+            w.opt_no_reorder = false;
+            w.opt_deadline = false;
+        }
+    } option_scope{ws};
+    if (options != nullptr) {
+        ws.opt_no_reorder = options->enable_reorder == 0;
+        // IndexSearchParameter's default is "no limit" (src/algorithm/index_search_parameter.h:53); a limit of
+        // zero or less has passed as soon as the scan asks
+        const double ms = options->timeout_ms;
+        if (options->has_timeout != 0 && ms < 1e12) {
+            VB_TRY(ws.scalars.reserve(8));
+            const double ns = ms > 0.0 ? ms * 1e6 : 0.0;
+            VB_LAUNCH(deadline_stamp_kernel, 1, 1, 0, reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 6),
+                      static_cast<unsigned long long>(ns));
+            ws.opt_deadline = true;
+        }
+    }
     const uint64_t total = nq * k;
     VB_TRY(ws.out_ids.reserve(total));
     VB_TRY(ws.out_dists.reserve(total));
@@ -2769,13 +2813,16 @@ vb200_ivf_search_filtered(vb200_ivf_t ix, const float* queries, uint64_t nq, uin
               ix->labels.ptr, ws.out_ids.ptr, ws.out_dists.ptr);
     VB_TRY(copy_out(ids, ws.out_ids.ptr, total));
     VB_TRY(copy_out(dists, ws.out_dists.ptr, total));
-    uint64_t scalars[5] = {0, 0, 0, 0, 0};
+    uint64_t scalars[6] = {0, 0, 0, 0, 0, 0};
     VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
     ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
     ix->last_scanned_bytes = static_cast<int64_t>(ws.pruning ? scalars[3] : scalars[0]);
     if (scalars[4] != 0) {
         VB_FAIL(VB200_INTERNAL_ERROR, "the tensor-core scan gave up on a bounded wait");
+    }
+    if (timed_out != nullptr) {
+        *timed_out = scalars[5] != 0 ? 1 : 0;
     }
     return 0;
 }

@@ -56,6 +56,11 @@ struct ScanParams {
     uint32_t n_phases;
     uint32_t nlist;
     uint32_t* item_counter;      // work queue head
+    // Optional deadline of the search (timeout_ms): *deadline is a %globaltimer value; once it has passed no
+    // further work item is handed out and *timed_out is set -- the granularity at which the reference checks
+    // its timer (between buckets, src/algorithm/ivf/ivf.cpp:1747-1751).  nullptr: no deadline.
+    const unsigned long long* deadline;
+    unsigned long long* timed_out;
     uint32_t k;
     uint32_t cap;                // per-query candidate buffer, power of two >= k + SCAN_THREADS
     uint32_t* thr_g;             // [nq] global bound, ordered distance
@@ -236,6 +241,18 @@ struct ScanItem {
 };
 
 // Fetches the next work item; returns false when the queue is empty.  All threads call it.
+// True once the search's deadline has passed (one thread asks, per work item); records the fact.
+__device__ __forceinline__ bool
+scan_deadline_passed(const ScanParams& p) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    if (now <= *reinterpret_cast<const volatile unsigned long long*>(p.deadline)) {
+        return false;
+    }
+    *reinterpret_cast<volatile unsigned long long*>(p.timed_out) = 1ull;
+    return true;
+}
+
 template <int QT>
 __device__ __forceinline__ bool
 scan_next_item(const ScanParams& p, uint32_t* s_item, ScanItem& it) {
@@ -243,7 +260,11 @@ scan_next_item(const ScanParams& p, uint32_t* s_item, ScanItem& it) {
     const uint32_t n0 = p.item_off[0][p.nlist];
     const uint32_t n1 = p.n_phases > 1 ? p.item_off[1][p.nlist] : 0u;
     if (threadIdx.x == 0) {
-        s_item[0] = atomicAdd(p.item_counter, 1u);
+        uint32_t next = atomicAdd(p.item_counter, 1u);
+        if (p.deadline != nullptr && scan_deadline_passed(p)) {
+            next = 0xFFFFFFFFu;
+        }
+        s_item[0] = next;
     }
     __syncthreads();
     uint32_t item = s_item[0];

@@ -258,7 +258,7 @@ constexpr int TCS_SELECT_MAX = 8;   // keys per lane at most: buffers of up to 2
 __device__ __forceinline__ void
 tcs_fetch_item(const ScanParams& p, uint32_t n0, uint32_t n1, TcsItem* out) {
     uint32_t item = atomicAdd(p.item_counter, 1u);
-    if (item >= n0 + n1) {
+    if (item >= n0 + n1 || (p.deadline != nullptr && scan_deadline_passed(p))) {
         out->valid = 0;
         return;
     }

@@ -310,6 +310,24 @@ class IvfHandle:
                                                   ptr(bucket_ids, np.int32), C.byref(f), ptr(ids), ptr(dists)))
         return ids, dists
 
+    def search_ex(self, queries, k: int, nprobe: int, factor: float = 2.0, bucket_ids=None, enable_reorder: bool = True,
+                  timeout_ms=None):
+        """vb200_ivf_search_ex: the search with IndexSearchParameter's per-call options; returns
+        (ids, dists, timed_out)."""
+        nq = _rows(queries)
+        ids = _empty_like_side(queries, (nq, k), np.int64)
+        dists = _empty_like_side(queries, (nq, k), np.float32)
+
+        class Options(C.Structure):
+            _fields_ = [("enable_reorder", C.c_int), ("has_timeout", C.c_int), ("timeout_ms", C.c_double)]
+
+        opt = Options(int(bool(enable_reorder)), int(timeout_ms is not None), float(timeout_ms or 0.0))
+        timed_out = C.c_int(0)
+        check(self._lib.vb200_ivf_search_ex(self._h, ptr(queries, np.float32), nq, k, nprobe, factor,
+                                            ptr(bucket_ids, np.int32), None, C.cast(C.byref(opt), C.c_void_p), ptr(ids),
+                                            ptr(dists), C.byref(timed_out)))
+        return ids, dists, bool(timed_out.value)
+
     def search_partial(self, queries, k: int, nprobe: int, factor: float, keys_dev, labels_dev,
                        bucket_ids=None, exchange=None) -> None:
         """exchange: an _capi.EXCHANGE_FN instance (kept alive by the caller) that reduces the

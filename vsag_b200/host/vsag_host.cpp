@@ -321,14 +321,18 @@ pack_result(int64_t* ids, float* dists, int64_t nq, int64_t k, const std::string
 // src/algorithm/ivf/flat_bucket_searcher.cpp:105-137): both keep a heap of limited_size entries (all
 // vectors when it is negative) and push what lies within the radius, so the answer is the nearest
 // limited_size of the in-radius vectors, ascending.  That is the k-nearest answer cut at the radius.
-// Without a limit k grows until the answer is complete; past RANGE_K_MAX in-radius vectors the caller
-// has to pass limited_size.  `slack` is what the reference adds to the radius (THRESHOLD_ERROR for
+// Without a limit k grows until the answer is complete; past RANGE_K_MAX in-radius vectors (the scan's
+// per-query candidate buffers bound k) the answer is fetched in pages: the vectors found so far are added
+// to the search's inner-id deny bitmap and the next RANGE_K_MAX nearest are asked for, until a page reaches
+// past the radius.  Pages are disjoint and each holds the nearest of what is left, so their concatenation
+// is the ascending in-radius list.  `slack` is what the reference adds to the radius (THRESHOLD_ERROR for
 // IVF, src/impl/searcher/basic_searcher.h:39; nothing for BruteForce).
 constexpr int64_t RANGE_K_MAX = 512;
 
 template <typename Knn>
 DatasetPtr
-range_over_knn(Knn&& knn, const DatasetPtr& query, int64_t n_live, float radius, float slack, int64_t limited_size) {
+range_over_knn(Knn&& knn, const DatasetPtr& query, int64_t n_live, float radius, float slack, int64_t limited_size,
+               const vb200_filter* filter, const std::vector<int64_t>& label_of_inner) {
     check_argument(query != nullptr, "query is null");
     check_argument(query->GetNumElements() == 1, "query dataset should contain 1 vector only");
     check_argument(std::isfinite(radius), "radius must be finite");
@@ -337,34 +341,77 @@ range_over_knn(Knn&& knn, const DatasetPtr& query, int64_t n_live, float radius,
     if (n_live == 0) {
         return make_empty_result();
     }
+    auto inside_of = [&](const DatasetPtr& found) {
+        int64_t inside = 0;
+        while (inside < found->GetDim() && found->GetDistances()[inside] <= radius + slack) {
+            ++inside;
+        }
+        return inside;
+    };
+    auto pack = [&](const int64_t* src_ids, const float* src_dists, int64_t count, const std::string& stats) {
+        auto* ids = new int64_t[static_cast<size_t>(std::max<int64_t>(count, 1))];
+        auto* dists = new float[static_cast<size_t>(std::max<int64_t>(count, 1))];
+        std::copy(src_ids, src_ids + count, ids);
+        std::copy(src_dists, src_dists + count, dists);
+        auto result = Dataset::Make()->NumElements(1)->Dim(count)->Ids(ids)->Distances(dists)->Owner(true);
+        result->Statistics(stats);
+        return result;
+    };
     int64_t k = limited_size > 0 ? std::min(limited_size, n_live) : std::min<int64_t>(64, n_live);
     for (;;) {
-        Expected<DatasetPtr> r = knn(k);
+        Expected<DatasetPtr> r = knn(k, filter);
         if (!r.has_value()) {
             fail(r.error().type, r.error().message);
         }
         const DatasetPtr& found = r.value();
         const int64_t got = found->GetDim();
-        int64_t inside = 0;
-        while (inside < got && found->GetDistances()[inside] <= radius + slack) {
-            ++inside;
-        }
+        const int64_t inside = inside_of(found);
         const bool complete = limited_size > 0 || inside < got || got < k || k >= n_live;
         if (!complete && k < RANGE_K_MAX) {
             k = std::min({k * 8, RANGE_K_MAX, n_live});
             continue;
         }
-        if (!complete) {
-            fail(ErrorType::INVALID_ARGUMENT, "more than " + std::to_string(RANGE_K_MAX) +
-                                                  " vectors lie within the radius: pass limited_size");
+        if (complete) {
+            return pack(found->GetIds(), found->GetDistances(), inside, found->GetStatistics());
         }
-        auto* ids = new int64_t[static_cast<size_t>(std::max<int64_t>(inside, 1))];
-        auto* dists = new float[static_cast<size_t>(std::max<int64_t>(inside, 1))];
-        std::copy(found->GetIds(), found->GetIds() + inside, ids);
-        std::copy(found->GetDistances(), found->GetDistances() + inside, dists);
-        auto result = Dataset::Make()->NumElements(1)->Dim(inside)->Ids(ids)->Distances(dists)->Owner(true);
-        result->Statistics(found->GetStatistics());
-        return result;
+        // every one of the RANGE_K_MAX nearest lies within the radius: go on in pages
+        std::vector<int64_t> all_ids(found->GetIds(), found->GetIds() + inside);
+        std::vector<float> all_dists(found->GetDistances(), found->GetDistances() + inside);
+        std::unordered_map<int64_t, uint32_t> inner_of_label;
+        inner_of_label.reserve(label_of_inner.size());
+        for (size_t i = 0; i < label_of_inner.size(); ++i) {
+            inner_of_label.emplace(label_of_inner[i], static_cast<uint32_t>(i));
+        }
+        std::vector<uint32_t> deny((label_of_inner.size() + 31) / 32, 0);
+        if (filter != nullptr && filter->deny_inner_bits != nullptr) {
+            const size_t words = std::min<size_t>(deny.size(), (filter->n_inner_bits + 31) / 32);
+            std::copy(filter->deny_inner_bits, filter->deny_inner_bits + words, deny.begin());
+        }
+        vb200_filter paged = filter != nullptr ? *filter : vb200_filter{};
+        paged.deny_inner_bits = deny.data();
+        paged.n_inner_bits = label_of_inner.size();
+        size_t marked = 0;
+        std::string stats = found->GetStatistics();
+        for (;;) {
+            for (; marked < all_ids.size(); ++marked) {
+                auto it = inner_of_label.find(all_ids[marked]);
+                if (it != inner_of_label.end()) {
+                    deny[it->second >> 5] |= 1u << (it->second & 31);
+                }
+            }
+            Expected<DatasetPtr> page = knn(RANGE_K_MAX, &paged);
+            if (!page.has_value()) {
+                fail(page.error().type, page.error().message);
+            }
+            const DatasetPtr& next = page.value();
+            const int64_t page_inside = inside_of(next);
+            all_ids.insert(all_ids.end(), next->GetIds(), next->GetIds() + page_inside);
+            all_dists.insert(all_dists.end(), next->GetDistances(), next->GetDistances() + page_inside);
+            if (page_inside < next->GetDim() || next->GetDim() < RANGE_K_MAX) {
+                break;
+            }
+        }
+        return pack(all_ids.data(), all_dists.data(), static_cast<int64_t>(all_ids.size()), stats);
     }
 }
 
@@ -680,8 +727,9 @@ public:
     range_impl(const DatasetPtr& query, float radius, const std::string& parameters, int64_t limited_size,
                const vb200_filter* filter, const std::vector<std::vector<int64_t>>* bucket_ids = nullptr) const {
         return safe_call<DatasetPtr>([&]() {
-            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, filter, bucket_ids); }, query,
-                                  GetNumElements(), radius, 2e-6f, limited_size);
+            return range_over_knn(
+                [&](int64_t k, const vb200_filter* f) { return knn_impl(query, k, parameters, f, bucket_ids); }, query,
+                GetNumElements(), radius, 2e-6f, limited_size, filter, labels_host_);
         });
     }
 
@@ -809,6 +857,13 @@ public:
             check_argument(nprobe >= 1, "scan_buckets_count must be positive");
             double factor = get_number(ivf, "factor", 2.0);
             bool disable_scan = get_bool(ivf, "disable_bucket_scan", false);
+            // IndexSearchParameter::FromJson (src/algorithm/index_search_parameter.h:27-48): enable_reorder
+            // (default true), timeout_ms (an integer; present = the search is timed), parallelism (host threads
+            // of the reference's scan: nothing to do here).  Keys it does not know are ignored, as there.
+            vb200_search_options options{};
+            options.enable_reorder = get_bool(ivf, "enable_reorder", true) ? 1 : 0;
+            options.has_timeout = ivf.Contains("timeout_ms") ? 1 : 0;
+            options.timeout_ms = options.has_timeout != 0 ? static_cast<double>(get_int(ivf, "timeout_ms", 0)) : 0.0;
             if (query->GetNumElements() == 0 || vb200_ivf_num_elements(handle_) == 0) {
                 return make_empty_result();
             }
@@ -867,17 +922,21 @@ public:
             }
             auto* ids = new int64_t[static_cast<size_t>(nq * k)];
             auto* dists = new float[static_cast<size_t>(nq * k)];
-            int status = vb200_ivf_search_filtered(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
-                                                   static_cast<uint32_t>(std::min<int64_t>(nprobe, 0x7fffffff)),
-                                                   static_cast<float>(factor),
-                                                   buckets_flat.empty() ? nullptr : buckets_flat.data(), filter, ids, dists);
+            int timed_out = 0;
+            int status = vb200_ivf_search_ex(handle_, query->GetFloat32Vectors(), nq, static_cast<uint32_t>(k),
+                                             static_cast<uint32_t>(std::min<int64_t>(nprobe, 0x7fffffff)),
+                                             static_cast<float>(factor),
+                                             buckets_flat.empty() ? nullptr : buckets_flat.data(), filter, &options, ids,
+                                             dists, &timed_out);
             if (status != 0) {
                 delete[] ids;
                 delete[] dists;
                 check_status(status);
             }
             int64_t scanned = vb200_ivf_last_scan_bytes(handle_);
-            std::string stats = "{\"dist_cmp\":" + std::to_string(code_size() > 0 ? scanned / code_size() : 0) + "}";
+            // the fields of QueryStats a caller reads back (dist_cmp, is_timeout)
+            std::string stats = "{\"dist_cmp\":" + std::to_string(code_size() > 0 ? scanned / code_size() : 0) +
+                                ",\"is_timeout\":" + (timed_out != 0 ? "true" : "false") + "}";
             return pack_result(ids, dists, nq, k, stats);
         });
     }
@@ -1135,8 +1194,8 @@ public:
     range_impl(const DatasetPtr& query, float radius, const std::string& parameters, int64_t limited_size,
                const vb200_filter* filter) const {
         return safe_call<DatasetPtr>([&]() {
-            return range_over_knn([&](int64_t k) { return knn_impl(query, k, parameters, filter); }, query,
-                                  GetNumElements(), radius, 0.0f, limited_size);
+            return range_over_knn([&](int64_t k, const vb200_filter* f) { return knn_impl(query, k, parameters, f); },
+                                  query, GetNumElements(), radius, 0.0f, limited_size, filter, labels_host_);
         });
     }
 

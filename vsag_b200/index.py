@@ -153,9 +153,9 @@ class Index:
 
     def range_search(self, vector, radius: float, k: int, parameters: str = "{}"):
         """vsag_index_range_search: the nearest k of the vectors within `radius`, ascending; k < 0 asks
-        for all of them (at most 512)."""
+        for all of them."""
         vector = np.ascontiguousarray(vector, np.float32).reshape(-1)
-        room = k if k > 0 else 512
+        room = k if k > 0 else max(1, self.get_num_elements())
         ids = np.empty(room, np.int64)
         dists = np.empty(room, np.float32)
         res = _SearchResult(dists.ctypes.data_as(C.POINTER(C.c_float)), ids.ctypes.data_as(C.POINTER(C.c_int64)), 0, None)
