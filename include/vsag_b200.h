@@ -58,6 +58,7 @@ extern "C" {
 #define VB200_QUANT_SQ8 1
 #define VB200_QUANT_RABITQ 2
 #define VB200_QUANT_BF16 3
+#define VB200_QUANT_FP16 4   /* IVF buckets only */
 
 /* SQTrainMode (src/quantization/scalar_quantization/scalar_quantization_trainer.h:25-29). */
 #define VB200_SQ_TRAIN_CLASSIC 1
@@ -192,7 +193,9 @@ VB200_API int vb200_rabitq_process_query(const float* queries, uint64_t count, u
  * ------------------------------------------------------------------------------------------- */
 
 /* Replaces IVF::IVF (src/algorithm/ivf/ivf.cpp:412-474): nlist = buckets_count, quant =
- * base_quantization_type (VB200_QUANT_FP32, the reference's default, VB200_QUANT_SQ8 or VB200_QUANT_RABITQ),
+ * base_quantization_type (VB200_QUANT_FP32, the reference's default, VB200_QUANT_SQ8, VB200_QUANT_RABITQ, or the
+ * half-precision codecs VB200_QUANT_BF16 / VB200_QUANT_FP16 of
+ * src/quantization/scalar_quantization/half_precision_quantizer.cpp:54-123),
  * use_reorder keeps the fp32 rows for exact rerank (precise_quantization_type fp32). */
 VB200_API int vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_reorder,
                      vb200_ivf_t* out);

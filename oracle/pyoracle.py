@@ -299,6 +299,38 @@ def ivf_fp32_search(rows, list_off, inner_ids, q, probes, k: int, metric: int = 
     return ids, dists
 
 
+def float_to_half(x, fmt: str) -> np.ndarray:
+    """HalfPrecisionQuantizer::EncodeOneImpl element by element: "bf16" rounds half up, "fp16" clamps the
+    exponent and truncates (generic::FloatToBF16 / FloatToFP16)."""
+    x, px = _a(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    lib().orc_float_to_half_batch(px, _u64(x.size), _i32(0 if fmt == "bf16" else 1), _p(out.ctypes.data))
+    return out
+
+
+def half_to_float(x, fmt: str) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.uint16)
+    fn = lib().orc_bf16_to_float if fmt == "bf16" else lib().orc_fp16_to_float
+    fn.restype = C.c_float
+    return np.array([fn(C.c_uint16(int(v))) for v in x.reshape(-1)], np.float32).reshape(x.shape)
+
+
+def ivf_half_search(codes, list_off, inner_ids, q, probes, k: int, metric: int = 0, fmt: str = "bf16"):
+    """IVF scan over bf16 / fp16 buckets: codes[n, dim] uint16 in list order; metric 0 l2, 1 ip, 2 cosine
+    (the query is normalised first)."""
+    codes, pc = _a(codes, np.uint16)
+    list_off, po = _a(list_off, np.int64)
+    inner_ids, pi = _a(inner_ids, np.int64)
+    q, pq = _a(q, np.float32)
+    probes, pp = _a(probes, np.int32)
+    nq, d = q.shape
+    ids = np.empty((nq, k), np.int64)
+    dists = np.empty((nq, k), np.float32)
+    lib().orc_ivf_half_search(pc, po, pi, _u64(d), pq, _u64(nq), pp, _u64(probes.shape[1]), _i64(k), _i32(metric),
+                              _i32(0 if fmt == "bf16" else 1), _p(ids.ctypes.data), _p(dists.ctypes.data))
+    return ids, dists
+
+
 def ivf_sq8_search(codes, list_off, inner_ids, lower, diff, q, probes, k: int, metric: int = 0,
                    fn=None, nthreads: int = 0):
     codes, pc = _a(codes, np.uint8)

@@ -5,6 +5,7 @@
 #include <cstdint>
 
 #include "simd/bf16_simd.h"
+#include "simd/fp16_simd.h"
 #include "simd/fp32_simd.h"
 #include "simd/normalize.h"
 #include "simd/rabitq_simd.h"
@@ -60,6 +61,21 @@ float ref_generic_RaBitQFloatBinaryIP(const float* v, const uint8_t* bits, uint6
 }
 float ref_generic_NormalizeWithCentroid(const float* from, const float* centroid, float* to, uint64_t d) {
     return vsag::generic::NormalizeWithCentroid(from, centroid, to, d);
+}
+uint16_t ref_FloatToFP16(float v) {
+    return vsag::generic::FloatToFP16(v);
+}
+float ref_FP16ToFloat(uint16_t v) {
+    return vsag::generic::FP16ToFloat(v);
+}
+float ref_FP16ComputeIP(const uint8_t* a, const uint8_t* b, uint64_t d) {
+    return vsag::FP16ComputeIP(a, b, d);
+}
+float ref_FP16ComputeL2Sqr(const uint8_t* a, const uint8_t* b, uint64_t d) {
+    return vsag::FP16ComputeL2Sqr(a, b, d);
+}
+float ref_generic_FP16ComputeL2Sqr(const uint8_t* a, const uint8_t* b, uint64_t d) {
+    return vsag::generic::FP16ComputeL2Sqr(a, b, d);
 }
 uint16_t ref_FloatToBF16(float v) {
     return vsag::generic::FloatToBF16(v);

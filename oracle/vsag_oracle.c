@@ -916,6 +916,122 @@ orc_bf_search_bf16(const uint16_t* base,
     }
 }
 
+/* generic::FloatToFP16 (src/simd/generic.cpp:214-228): the exponent is clamped to [-14, 15] and the
+ * mantissa truncated to 10 bits -- no rounding, no zero, denormal, infinity or NaN encodings (0.0f
+ * becomes 2^-14).  Every code it writes is a normal number of IEEE half precision. */
+ORC_API uint16_t
+orc_float_to_fp16(float v) {
+    uint32_t bits;
+    memcpy(&bits, &v, 4);
+    uint32_t sign = (bits >> 31) & 1u;
+    int32_t exp = (int32_t)((bits >> 23) & 0xFFu) - 127;
+    uint32_t mantissa = bits & 0x007FFFFFu;
+    if (exp > 15) {
+        exp = 15;
+    } else if (exp < -14) {
+        exp = -14;
+    }
+    return (uint16_t)((sign << 15) | ((uint32_t)(exp + 15) << 10) | (mantissa >> 13));
+}
+
+/* generic::FP16ToFloat (src/simd/generic.cpp:204-212): rebias the exponent, widen the mantissa. */
+ORC_API float
+orc_fp16_to_float(uint16_t v) {
+    uint32_t sign = (v >> 15) & 1u;
+    int32_t exp = (int32_t)((v >> 10) & 0x1Fu) - 15;
+    uint32_t mantissa = ((uint32_t)v & 0x3FFu) << 13;
+    uint32_t bits = (sign << 31) | ((uint32_t)(exp + 127) << 23) | mantissa;
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* fmt 0: bf16, 1: fp16 */
+ORC_API void
+orc_float_to_half_batch(const float* in, uint64_t n, int fmt, uint16_t* out) {
+    for (uint64_t i = 0; i < n; ++i) {
+        out[i] = fmt == 0 ? orc_float_to_bf16(in[i]) : orc_float_to_fp16(in[i]);
+    }
+}
+
+static float
+half_to_float(uint16_t v, int fmt) {
+    return fmt == 0 ? orc_bf16_to_float(v) : orc_fp16_to_float(v);
+}
+
+/* HalfComputeIPImpl / HalfComputeL2SqrImpl in scalar width (src/simd/kernels/half_compute.h:31-94). */
+ORC_API float
+orc_half_ip(const uint16_t* a, const uint16_t* b, uint64_t dim, int fmt) {
+    float sum = 0.0f;
+    for (uint64_t i = 0; i < dim; ++i) {
+        sum = fmaf(half_to_float(a[i], fmt), half_to_float(b[i], fmt), sum);
+    }
+    return sum;
+}
+
+ORC_API float
+orc_half_l2sqr(const uint16_t* a, const uint16_t* b, uint64_t dim, int fmt) {
+    float sum = 0.0f;
+    for (uint64_t i = 0; i < dim; ++i) {
+        float d = half_to_float(a[i], fmt) - half_to_float(b[i], fmt);
+        sum = fmaf(d, d, sum);
+    }
+    return sum;
+}
+
+/* The probe loop over half-precision buckets (HalfPrecisionQuantizer,
+ * src/quantization/scalar_quantization/half_precision_quantizer.cpp:54-123): the query is encoded like a
+ * row (ProcessQueryImpl), the distance is ComputeL2Sqr or 1 - ComputeIP between the two codes.  Rows of a
+ * cosine index were normalised before they were encoded; so is the query here (metric 2). */
+ORC_API void
+orc_ivf_half_search(const uint16_t* codes,
+                    const int64_t* list_off,
+                    const int64_t* inner_ids,
+                    uint64_t dim,
+                    const float* q,
+                    uint64_t nq,
+                    const int32_t* probes,
+                    uint64_t nprobe,
+                    int64_t k,
+                    int metric,
+                    int fmt,
+                    int64_t* out_ids,
+                    float* out_dists) {
+#pragma omp parallel
+    {
+        orc_heap h;
+        h.a = (orc_rec*)malloc((size_t)(k + 2) * sizeof(orc_rec));
+        h.cap = k + 2;
+        uint16_t* qh = (uint16_t*)malloc(dim * sizeof(uint16_t));
+        float* qn = (float*)malloc(dim * sizeof(float));
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t i = 0; i < (int64_t)nq; ++i) {
+            const float* qi = q + (uint64_t)i * dim;
+            if (metric == 2) {
+                orc_normalize_rows(qi, 1, dim, qn);
+                qi = qn;
+            }
+            orc_float_to_half_batch(qi, dim, fmt, qh);
+            h.size = 0;
+            for (uint64_t p = 0; p < nprobe; ++p) {
+                int32_t l = probes[(uint64_t)i * nprobe + p];
+                if (l < 0) {
+                    continue;
+                }
+                for (int64_t r = list_off[l]; r < list_off[l + 1]; ++r) {
+                    const uint16_t* x = codes + (uint64_t)r * dim;
+                    float d = metric == 0 ? orc_half_l2sqr(qh, x, dim, fmt) : 1.0f - orc_half_ip(qh, x, dim, fmt);
+                    heap_offer_strict(&h, k, d, inner_ids[r]);
+                }
+            }
+            heap_drain(&h, k, out_ids + (uint64_t)i * k, out_dists + (uint64_t)i * k);
+        }
+        free(h.a);
+        free(qh);
+        free(qn);
+    }
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* RaBitQ, 1 bit per dimension, fp32 query, "standard" layout                                   */
 /* ------------------------------------------------------------------------------------------ */

@@ -71,3 +71,35 @@ def test_fp32_and_bf16_match_reference(oracle, ref):
     vals = rng.normal(size=1000).astype(np.float32)
     want = np.array([ref.ref_FloatToBF16(float(v)) for v in vals], np.uint16)
     assert np.array_equal(oracle.float_to_bf16(vals), want)
+
+
+def test_fp16_matches_reference(oracle, ref):
+    """generic::FloatToFP16 / FP16ToFloat bit for bit, FP16ComputeIP / L2Sqr (dispatched and generic) on encoded
+    vectors: every code the encoder writes is a normal half, so the vector paths' IEEE widening agrees with the
+    generic bit formula and only the summation order differs."""
+    rng = np.random.default_rng(3)
+    vals = np.concatenate([rng.normal(0, 1, 2000), rng.normal(0, 1e-3, 500),
+                           [0.0, -0.0, 1.0, 65504.0, 1e5, -1e5, 1e-8, 6e-5]]).astype(np.float32)
+    ref.ref_FloatToFP16.restype = C.c_uint16
+    ref.ref_FloatToFP16.argtypes = [C.c_float]
+    ref.ref_FP16ToFloat.restype = C.c_float
+    ref.ref_FP16ToFloat.argtypes = [C.c_uint16]
+    want = np.array([ref.ref_FloatToFP16(float(v)) for v in vals], np.uint16)
+    got = oracle.float_to_half(vals, "fp16")
+    assert np.array_equal(got, want)
+    back = np.array([ref.ref_FP16ToFloat(int(v)) for v in got], np.float32)
+    assert np.array_equal(oracle.half_to_float(got, "fp16"), back)
+    lib = oracle.lib()
+    lib.orc_half_ip.restype = C.c_float
+    lib.orc_half_l2sqr.restype = C.c_float
+    for fn in (ref.ref_FP16ComputeIP, ref.ref_FP16ComputeL2Sqr, ref.ref_generic_FP16ComputeL2Sqr):
+        fn.restype = C.c_float
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+    for dim in (1, 7, 16, 96, 100, 768):
+        a = oracle.float_to_half(rng.normal(0, 1, dim).astype(np.float32), "fp16")
+        b = oracle.float_to_half(rng.normal(0, 1, dim).astype(np.float32), "fp16")
+        ip = lib.orc_half_ip(_p(a), _p(b), C.c_uint64(dim), C.c_int(1))
+        l2 = lib.orc_half_l2sqr(_p(a), _p(b), C.c_uint64(dim), C.c_int(1))
+        assert l2 == ref.ref_generic_FP16ComputeL2Sqr(a.ctypes.data, b.ctypes.data, dim)      # same order: same bits
+        assert ip == pytest.approx(ref.ref_FP16ComputeIP(a.ctypes.data, b.ctypes.data, dim), rel=1e-5, abs=1e-5)
+        assert l2 == pytest.approx(ref.ref_FP16ComputeL2Sqr(a.ctypes.data, b.ctypes.data, dim), rel=1e-5)

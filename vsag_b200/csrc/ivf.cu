@@ -312,6 +312,23 @@ fp32_place_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim
     }
 }
 
+// The same for half-precision buckets: every element encoded to 16 bits on its way in.
+template <int FMT>
+__global__ void
+half_place_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim, const uint32_t* __restrict__ dst_pos,
+                       uint8_t* __restrict__ codes, uint32_t code_stride) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= count * dim) {
+        return;
+    }
+    const uint64_t row = e / dim;
+    const uint32_t d = static_cast<uint32_t>(e % dim);
+    const uint32_t pos = dst_pos[row];
+    if (pos != 0xFFFFFFFFu) {
+        reinterpret_cast<uint16_t*>(codes + static_cast<uint64_t>(pos) * code_stride)[d] = half_encode<FMT>(x[e]);
+    }
+}
+
 // Tiled signed copy of the lists for the tensor-core scan: row r of list l goes to 8-row group
 // group_off[l] + r / 8; its 16-byte chunk c (bytes code - 128, i.e. code ^ 0x80; zero beyond the code)
 // to core c of the group, row r % 8.  One thread per (position, chunk).
@@ -1691,7 +1708,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                  static_cast<unsigned long long>(total));
     VB_CHECK_ARG(kfinal >= 1 && kscan <= 1024 - SCAN_THREADS, "k = %u out of range [1, %u]", kfinal,
                  1024 - SCAN_THREADS - (sq8 ? SQ8_SLACK : 0));
-    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : (ix->quant == VB200_QUANT_FP32 ? FP32_QT : RABITQ_QT);
+    const bool flat_rows = ix->quant == VB200_QUANT_FP32 || ix->quant == VB200_QUANT_BF16 || ix->quant == VB200_QUANT_FP16;
+    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : (flat_rows ? FP32_QT : RABITQ_QT);
 
     // Phase 0 scans every query's nearest list (of those this shard holds), phase 1 the other
     // probes: after phase 0 the per-query bound is already close to final, so almost nothing
@@ -1911,8 +1929,14 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
             return launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem);
         }
-        if (ix->quant == VB200_QUANT_FP32) {
+        if (flat_rows) {
             size_t smem = tile_smem_bytes<FP32_QT>(p.cap, FP32_QT * ix->dpad);
+            if (ix->quant == VB200_QUANT_BF16) {
+                return launch_scan(ivf_fp32_scan_kernel<FP32_QT, SCAN_FMT_BF16>, p, smem);
+            }
+            if (ix->quant == VB200_QUANT_FP16) {
+                return launch_scan(ivf_fp32_scan_kernel<FP32_QT, SCAN_FMT_FP16>, p, smem);
+            }
             return launch_scan(ivf_fp32_scan_kernel<FP32_QT>, p, smem);
         }
         size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
@@ -2076,7 +2100,8 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
     VB_CHECK_ARG(out != nullptr, "null output handle");
     VB_CHECK_ARG(dim > 0, "dim must be positive");
     VB_CHECK_ARG(nlist >= 1, "buckets_count must be at least 1");
-    VB_CHECK_ARG(quant == VB200_QUANT_SQ8 || quant == VB200_QUANT_RABITQ || quant == VB200_QUANT_FP32,
+    VB_CHECK_ARG(quant == VB200_QUANT_SQ8 || quant == VB200_QUANT_RABITQ || quant == VB200_QUANT_FP32 ||
+                     quant == VB200_QUANT_BF16 || quant == VB200_QUANT_FP16,
                  "base_quantization_type must be fp32, sq8 or rabitq for this engine (got %d)", quant);
     VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP || metric == VB200_METRIC_COSINE,
                  "metric_type must be l2, ip or cosine (got %d)", metric);
@@ -2109,6 +2134,11 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
         ix->dpad = (dim + 3) / 4 * 4;
         ix->code_stride = ix->dpad * 4;
         ix->has_model = true;   // nothing to train beyond the centroids
+    } else if (quant == VB200_QUANT_BF16 || quant == VB200_QUANT_FP16) {
+        ix->code_size = dim * 2;
+        ix->dpad = (dim + 7) / 8 * 8;       // rows start on 16-byte boundaries
+        ix->code_stride = ix->dpad * 2;
+        ix->has_model = true;   // HalfPrecisionQuantizer::TrainImpl has nothing to learn
     } else {
         ix->code_size = rabitq_code_size(dim);
         ix->dpad = rabitq_bits_bytes(dim) * 8;
@@ -2537,6 +2567,12 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     } else if (ix->quant == VB200_QUANT_FP32) {
         VB_LAUNCH(fp32_place_rows_kernel, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count, dim,
                   dst_of_row.ptr, new_codes.ptr, stride);
+    } else if (ix->quant == VB200_QUANT_BF16) {
+        VB_LAUNCH(half_place_rows_kernel<SCAN_FMT_BF16>, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count,
+                  dim, dst_of_row.ptr, new_codes.ptr, stride);
+    } else if (ix->quant == VB200_QUANT_FP16) {
+        VB_LAUNCH(half_place_rows_kernel<SCAN_FMT_FP16>, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count,
+                  dim, dst_of_row.ptr, new_codes.ptr, stride);
     } else {
         VB_TRY(rabitq_encode_device(xr, count, dim, ix->rotation.ptr, ix->rq_centroid.ptr,
                                     dst_of_row.ptr, new_codes.ptr, stride));

@@ -836,7 +836,39 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
 // ---------------------------------------------------------------------------------------------
 constexpr int FP32_QT = 8;
 
-template <int QT>
+// Half-precision buckets (base_quantization_type "bf16" / "fp16"; HalfPrecisionQuantizer,
+// src/quantization/scalar_quantization/half_precision_quantizer.cpp:54-123): rows and query are both encoded
+// to 16 bits, the distance is the fp32 chain over the widened values (src/simd/kernels/half_compute.h:31-94).
+// bf16: FloatToBF16 adds 0x8000 and truncates; fp16: FloatToFP16 clamps the exponent to [-14, 15] and
+// truncates the mantissa -- no zero, denormal or infinity encodings -- and FP16ToFloat rebiases
+// (src/simd/generic.cpp:191-228).
+constexpr int SCAN_FMT_FP32 = 0, SCAN_FMT_BF16 = 1, SCAN_FMT_FP16 = 2;
+
+template <int FMT>
+__device__ __forceinline__ uint16_t
+half_encode(float v) {
+    const uint32_t bits = __float_as_uint(v);
+    if (FMT == SCAN_FMT_BF16) {
+        return static_cast<uint16_t>((bits + 0x8000u) >> 16);
+    }
+    const uint32_t sign = bits >> 31;
+    int32_t exp = static_cast<int32_t>((bits >> 23) & 0xFFu) - 127;
+    exp = exp > 15 ? 15 : (exp < -14 ? -14 : exp);
+    return static_cast<uint16_t>((sign << 15) | (static_cast<uint32_t>(exp + 15) << 10) | ((bits & 0x007FFFFFu) >> 13));
+}
+
+template <int FMT>
+__device__ __forceinline__ float
+half_decode(uint32_t h) {
+    if (FMT == SCAN_FMT_BF16) {
+        return __uint_as_float(h << 16);
+    }
+    const uint32_t sign = (h >> 15) & 1u;
+    const uint32_t exp = ((h >> 10) & 0x1Fu) + 112u;   // - 15 + 127
+    return __uint_as_float((sign << 31) | (exp << 23) | ((h & 0x3FFu) << 13));
+}
+
+template <int QT, int FMT = SCAN_FMT_FP32>
 __global__ void __launch_bounds__(SCAN_THREADS)
 ivf_fp32_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -875,6 +907,9 @@ ivf_fp32_scan_kernel(const ScanParams p) {
             float v = 0.f;
             if (static_cast<int>(qi) < nqt && d < p.dim) {
                 v = __ldg(p.queries + static_cast<uint64_t>(ts.qidx[qi]) * p.dim + d);
+                if (FMT != SCAN_FMT_FP32) {
+                    v = half_decode<FMT>(half_encode<FMT>(v));   // the query is encoded like a row
+                }
             }
             sv[i] = v;
         }
@@ -885,15 +920,28 @@ ivf_fp32_scan_kernel(const ScanParams p) {
         for (uint32_t r0 = 0; r0 < len; r0 += SCAN_THREADS) {
             const uint32_t row = r0 + threadIdx.x;
             const bool valid = row < len;
-            const float4* x4 = reinterpret_cast<const float4*>(
-                p.codes + static_cast<uint64_t>(lbeg + (valid ? row : 0)) * p.code_stride);
+            const unsigned char* row_ptr = p.codes + static_cast<uint64_t>(lbeg + (valid ? row : 0)) * p.code_stride;
+            const float4* x4 = reinterpret_cast<const float4*>(row_ptr);
+            const uint2* h4 = reinterpret_cast<const uint2*>(row_ptr);
             float acc[QT];
 #pragma unroll
             for (int qi = 0; qi < QT; ++qi) {
                 acc[qi] = 0.f;
             }
             for (uint32_t d4 = 0; d4 < (dpad >> 2); ++d4) {
-                const float4 x = __ldg(x4 + d4);   // padding columns hold zeros on both sides
+                float4 x;
+                if (FMT == SCAN_FMT_FP32) {
+                    x = __ldg(x4 + d4);   // padding columns hold zeros on both sides
+                } else {
+                    // four 16-bit codes; columns past dim count as zero on both sides (the fp16 decoding of
+                    // padding bits is not zero)
+                    const uint2 h = __ldg(h4 + d4);
+                    const uint32_t d0 = 4 * d4;
+                    x.x = d0 < p.dim ? half_decode<FMT>(h.x & 0xFFFFu) : 0.f;
+                    x.y = d0 + 1 < p.dim ? half_decode<FMT>(h.x >> 16) : 0.f;
+                    x.z = d0 + 2 < p.dim ? half_decode<FMT>(h.y & 0xFFFFu) : 0.f;
+                    x.w = d0 + 3 < p.dim ? half_decode<FMT>(h.y >> 16) : 0.f;
+                }
 #pragma unroll
                 for (int qi = 0; qi < QT; ++qi) {
                     if (qi < nqt) {

@@ -13,7 +13,7 @@ from . import _capi
 from ._capi import VsagB200Error, check, ptr
 
 METRIC_L2, METRIC_IP, METRIC_COSINE = 0, 1, 2
-QUANT_FP32, QUANT_SQ8, QUANT_RABITQ, QUANT_BF16 = 0, 1, 2, 3
+QUANT_FP32, QUANT_SQ8, QUANT_RABITQ, QUANT_BF16, QUANT_FP16 = 0, 1, 2, 3, 4
 SQ_TRAIN_CLASSIC, SQ_TRAIN_TRUNC_BOUND = 1, 3
 
 METRICS = {"l2": METRIC_L2, "ip": METRIC_IP, "cosine": METRIC_COSINE}
@@ -184,6 +184,8 @@ class IvfHandle:
     def code_size(self) -> int:
         if self.quant == QUANT_SQ8:
             return self.dim
+        if self.quant in (QUANT_BF16, QUANT_FP16):
+            return self.dim * 2
         return self.dim * 4 if self.quant == QUANT_FP32 else rabitq_code_size(self.dim)
 
     def set_shard(self, rank: int, world: int) -> None:

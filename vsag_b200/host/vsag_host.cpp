@@ -533,9 +533,13 @@ public:
             quant_ = VB200_QUANT_RABITQ;
         } else if (quant == "fp32") {
             quant_ = VB200_QUANT_FP32;
+        } else if (quant == "bf16") {
+            quant_ = VB200_QUANT_BF16;
+        } else if (quant == "fp16") {
+            quant_ = VB200_QUANT_FP16;
         } else {
             fail(ErrorType::INVALID_ARGUMENT, "base_quantization_type \"" + quant +
-                                                  "\" is not served by the GPU engine (fp32, sq8 and rabitq are)");
+                                                  "\" is not served by the GPU engine (fp32, bf16, fp16, sq8 and rabitq are)");
         }
         use_reorder_ = get_bool(p, "use_reorder", false);
         std::string precise = get_string(p, "precise_quantization_type", "fp32");
@@ -950,6 +954,9 @@ private:
     code_size() const {
         if (quant_ == VB200_QUANT_FP32) {
             return static_cast<int64_t>(dim_) * 4;
+        }
+        if (quant_ == VB200_QUANT_BF16 || quant_ == VB200_QUANT_FP16) {
+            return static_cast<int64_t>(dim_) * 2;
         }
         return quant_ == VB200_QUANT_SQ8 ? dim_ : static_cast<int64_t>(vb200_rabitq_code_size(dim_));
     }
