@@ -57,7 +57,7 @@ def test_argument_validation_needs_no_device(engine):
     h = C.c_void_p()
     assert lib.vb200_ivf_create(0, 0, 4, 1, 0, C.byref(h)) == -3      # dim must be positive
     assert lib.vb200_ivf_create(8, 7, 4, 1, 0, C.byref(h)) == -3      # unknown metric
-    assert lib.vb200_ivf_create(8, 0, 4, 3, 0, C.byref(h)) == -3      # bf16 is not a bucket codec here
+    assert lib.vb200_ivf_create(8, 0, 4, 9, 0, C.byref(h)) == -3      # no such bucket codec
     assert lib.vb200_bf_create(8, 0, 1, C.byref(h)) == -3             # sq8 is not a brute-force codec here
     assert lib.vb200_kmeans_train(None, 10, 4, 2, 1, None, None, None) == -3
     code, msg = _capi.last_error()
