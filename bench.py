@@ -120,10 +120,12 @@ class ClockSampler:
     def start(self) -> None:
         """Starts nvidia-smi in its sampling loop and waits for its first line (its start-up takes driver
         locks for tens of milliseconds, which must not fall into a timed region)."""
+        if env_int("VB200_BENCH_NO_CLOCKS", 0):   # to measure what the sampling itself costs
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "20"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -146,7 +148,7 @@ class ClockSampler:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         t_end = time.time()
-        time.sleep(0.05)
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -154,7 +156,7 @@ class ClockSampler:
             self.proc.kill()
         inside = [text for t, text in self.lines if self.t_begin is not None and self.t_begin <= t <= t_end]
         around = [text for t, text in self.lines
-                  if self.t_begin is not None and self.t_begin - 0.05 <= t <= t_end + 0.05]
+                  if self.t_begin is not None and self.t_begin - 0.15 <= t <= t_end + 0.15]
         lines = inside or around or [text for _, text in self.lines]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -968,6 +970,13 @@ def brief(line: dict) -> dict:
     return {k: line[k] for k in keep if k in line}
 
 
+def engine_release() -> None:
+    """The training entry point keeps its workspace between calls; the other workloads want the memory."""
+    from vsag_b200 import engine
+
+    engine.release_workspaces()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1015,6 +1024,7 @@ def main() -> None:
             extras = {}
             if ctx.world == 1:
                 extras["kmeans"] = brief(run_kmeans(args, ctx, 10, 3))
+                engine_release()
                 torch.cuda.empty_cache()
                 extras["rabitq"] = brief(run_rabitq(args, ctx, 5, 3))
                 torch.cuda.empty_cache()

@@ -75,6 +75,10 @@ typedef struct vb200_comm* vb200_comm_t;
 /* Copies the calling thread's last error text into buf (NUL terminated) and returns its code. */
 VB200_API int vb200_last_error(char* buf, size_t buf_len);
 
+/* vb200_kmeans_train keeps its device workspace between calls (allocating it costs more than the iterations it
+ * serves); this frees it.  Indexes own their workspaces and free them with the handle. */
+VB200_API int vb200_release_workspaces(void);
+
 /* CUDA stream (a cudaStream_t) the calling thread's subsequent calls launch on; NULL = the
  * default stream. */
 VB200_API int vb200_set_stream(void* cuda_stream);

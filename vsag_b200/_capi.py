@@ -28,6 +28,7 @@ EXCHANGE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_
 # name -> (restype, argtypes); the single source for the "every declared symbol is exported" test.
 SIGNATURES = {
     "vb200_last_error": (c_int, [C.c_char_p, C.c_size_t]),
+    "vb200_release_workspaces": (c_int, []),
     "vb200_set_stream": (c_int, [c_void_p]),
     "vb200_kernel_launches": (c_u64, []),
     "vb200_device_count": (c_int, []),

@@ -19,7 +19,7 @@ constexpr uint32_t ROUTE_SLACK = 8;   // extra routing candidates re-scored exac
 constexpr uint32_t ROUTE_MAX_PER_ROW = 4096;   // approximate candidates a query may bring to the final pick (32 KiB of keys)
 constexpr int SQ8_QT = 16;
 constexpr uint32_t SQ8_SLACK = 16;    // survivors kept beyond k for exact re-scoring
-constexpr int RABITQ_QT = 8;
+constexpr int RABITQ_QT = 4;
 
 template <typename T>
 static int
@@ -72,6 +72,7 @@ struct SearchWorkspace {
     DevBuf<uint16_t> q_hi, q_lo;  // tensor-core routing: tiled bf16 terms of the queries
     vb200_exchange_fn exchange = nullptr;   // set for the duration of one partial search
     void* exchange_arg = nullptr;
+    DevBuf<float> qrot;   // RaBitQ: rotated query rows of one slice
     const float* ext_probe_dists = nullptr;   // centroid distances of caller-given probe lists (same duration)
     // sharded search: this rank's routed slice [probes | distances], the gathered probe lists and distances,
     // this rank's packed partial result [keys | labels] and the gathered ones
@@ -123,6 +124,7 @@ struct vb200_ivf {
     DevBuf<uint8_t> codes;
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
+    uint32_t max_list_len = 0;   // the longest list this index (shard) holds
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
     DevBuf<uint32_t> tombstones;  // bitmap over inner ids: vectors removed with MARK_REMOVE
     uint64_t tomb_words = 0;
@@ -1678,7 +1680,7 @@ bounds_from_float_kernel(const float* __restrict__ bounds, uint64_t nq, uint32_t
 template <typename Kernel>
 static int
 launch_scan(Kernel kernel, const ScanParams& p, size_t smem) {
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {   // the kernels' static shared memory counts against the 48 KiB default too
         VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
     }
@@ -1939,8 +1941,22 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             }
             return launch_scan(ivf_fp32_scan_kernel<FP32_QT>, p, smem);
         }
+        // Lists no longer than the scan depth need no selection (every probed row is a candidate): their items
+        // go to the kernel variant without selection buffers, the longer lists' items to the one with them.
+        // Each launch walks the whole queue with a counter of its own.
+        const size_t direct_smem = static_cast<size_t>(RABITQ_QT) * ix->dpad * sizeof(float);
+        if (ix->max_list_len <= p.k) {
+            return launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT, true>, p, direct_smem);
+        }
+        p.len_class = 2;
         size_t smem = tile_smem_bytes<RABITQ_QT>(p.cap, RABITQ_QT * ix->dpad);
-        return launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem);
+        VB_TRY(launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT>, p, smem));
+        VB_CUDA(cudaMemsetAsync(ws.scalars.ptr + 7, 0, sizeof(uint64_t), st));
+        p.len_class = 1;
+        p.item_counter = reinterpret_cast<uint32_t*>(ws.scalars.ptr + 7);
+        const int rc = launch_scan(ivf_rabitq_scan_kernel<RABITQ_QT, true>, p, direct_smem);
+        p.len_class = 0;
+        return rc;
     };
     p.order = ix->scan_order.ptr;
     if (split_phases) {
@@ -2051,7 +2067,7 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
     if (ix->quant == VB200_QUANT_RABITQ) {
         VB_TRY(ws.qproc.reserve(nq * (ix->dim + 1)));
         VB_TRY(rabitq_process_query_device(q_dev, nq, ix->dim, ix->rotation.ptr, ix->rq_centroid.ptr,
-                                           ws.qproc.ptr));
+                                           ws.qproc.ptr, &ws.qrot));
         q_scan = ws.qproc.ptr;
     }
     VB_TRY(ivf_scan_device(ix, q_scan, nq, kscan, nprobe, ws.probes.ptr, probe_dists));
@@ -2452,6 +2468,10 @@ ivf_commit_lists(vb200_ivf* ix, DevBuf<uint8_t>& new_codes, DevBuf<uint32_t>& ne
     ix->pos_inner = std::move(new_inner);
     ix->list_off = std::move(new_off_dev);
     ix->list_off_host = new_off;
+    ix->max_list_len = 0;
+    for (size_t l = 0; l + 1 < new_off.size(); ++l) {
+        ix->max_list_len = std::max(ix->max_list_len, new_off[l + 1] - new_off[l]);
+    }
     ix->n_stored = n_new_stored;
     ix->n_total = n_total_new;
     return ivf_refresh_scan_order(ix);

@@ -61,6 +61,9 @@ struct ScanParams {
     // its timer (between buckets, src/algorithm/ivf/ivf.cpp:1747-1751).  nullptr: no deadline.
     const unsigned long long* deadline;
     unsigned long long* timed_out;
+    // 0: every work item; 1: only items of lists no longer than k; 2: only items of longer lists.  A launch
+    // with a class walks the whole queue with its own counter and passes over the other class's items.
+    uint32_t len_class;
     uint32_t k;
     uint32_t cap;                // per-query candidate buffer, power of two >= k + SCAN_THREADS
     uint32_t* thr_g;             // [nq] global bound, ordered distance
@@ -261,6 +264,14 @@ scan_next_item(const ScanParams& p, uint32_t* s_item, ScanItem& it) {
     const uint32_t n1 = p.n_phases > 1 ? p.item_off[1][p.nlist] : 0u;
     if (threadIdx.x == 0) {
         uint32_t next = atomicAdd(p.item_counter, 1u);
+        while (p.len_class != 0 && next < n0 + n1) {
+            const ScanItemDesc* d = next < n0 ? p.item_map[0] + next : p.item_map[1] + (next - n0);
+            const bool is_short = __ldg(&d->len) <= p.k;
+            if (is_short == (p.len_class == 1u)) {
+                break;
+            }
+            next = atomicAdd(p.item_counter, 1u);
+        }
         if (p.deadline != nullptr && scan_deadline_passed(p)) {
             next = 0xFFFFFFFFu;
         }
@@ -694,15 +705,27 @@ sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_
 // Shared memory holds, per query, sv[d] = (1/sqrt(D)) * q_d already rounded, so the inner loop is
 // one add of +-sv[d] per dimension.
 // ---------------------------------------------------------------------------------------------
-template <int QT>
+// DIRECT: no list is longer than k (the scan depth, factor * k with reorder), so nothing can be selected
+// away inside a list -- every row of a probed list is a candidate of its (query, list) slot and is written
+// there as it is computed (the slots were cleared to "none" before the launch; the merge takes them in any
+// order).  Without the per-query selection buffers a CTA needs only the query values in shared memory, and
+// three to four times as many warps fit on an SM, which is what this latency-bound kernel lacks.
+template <int QT, bool DIRECT = false>
 __global__ void __launch_bounds__(SCAN_THREADS)
 ivf_rabitq_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ uint32_t s_item[1];
     __shared__ float s_qnorm[QT];
+    __shared__ uint32_t s_direct_q[QT], s_direct_slot[QT];
     TileSelect<QT> ts;
     float* fbuf;
-    tile_carve<QT>(smem, p.cap, 0, fbuf, ts);
+    if (DIRECT) {
+        fbuf = reinterpret_cast<float*>(smem);
+        ts.qidx = s_direct_q;
+        ts.slot = s_direct_slot;
+    } else {
+        tile_carve<QT>(smem, p.cap, 0, fbuf, ts);
+    }
     ts.k = p.k;
     ts.cap = p.cap;
     const uint32_t dpad = p.dpad;  // multiple of 128
@@ -720,17 +743,23 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
                 uint32_t q = it.pair_q[pbeg + qi];
                 ts.qidx[qi] = q;
                 ts.slot[qi] = it.pair_slot[pbeg + qi];
-                ts.qa[qi] = 0.f;
-                ts.set_bound(qi, p.thr_g[q]);
+                if (!DIRECT) {
+                    ts.qa[qi] = 0.f;
+                    ts.set_bound(qi, p.thr_g[q]);
+                }
                 s_qnorm[qi] = __ldg(p.queries + static_cast<uint64_t>(q) * (p.dim + 1) + p.dim);
             } else {
                 ts.qidx[qi] = 0;
                 ts.slot[qi] = 0;
-                ts.qa[qi] = 0.f;
-                ts.set_bound(qi, 0u);
+                if (!DIRECT) {
+                    ts.qa[qi] = 0.f;
+                    ts.set_bound(qi, 0u);
+                }
                 s_qnorm[qi] = 0.f;
             }
-            ts.cnt[qi] = 0;
+            if (!DIRECT) {
+                ts.cnt[qi] = 0;
+            }
         }
         __syncthreads();
         for (uint32_t i = threadIdx.x; i < static_cast<uint32_t>(QT) * dpad; i += SCAN_THREADS) {
@@ -814,16 +843,27 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
                             float p2 = __fmul_rn(qn, qn);
                             float p3 = __fmul_rn(__fmul_rn(__fmul_rn(-2.0f, bn), qn), est);
                             float dist = __fadd_rn(__fadd_rn(p1, p2), p3);
-                            ts.push(p, qi, dist, lbeg + rows[h]);
+                            if (DIRECT) {
+                                const uint32_t pos = lbeg + rows[h];
+                                if (p.filter_pos_inner == nullptr || !scan_row_filtered(p, pos)) {
+                                    p.part[static_cast<uint64_t>(ts.slot[qi]) * p.k + rows[h]] = make_key(dist, pos);
+                                }
+                            } else {
+                                ts.push(p, qi, dist, lbeg + rows[h]);
+                            }
                         }
                     }
                 }
-                __syncthreads();
-                ts.make_room(nqt);
-                __syncthreads();
+                if (!DIRECT) {
+                    __syncthreads();
+                    ts.make_room(nqt);
+                    __syncthreads();
+                }
             }
         }
-        ts.finish(nqt, p.part, p.thr_g);
+        if (!DIRECT) {
+            ts.finish(nqt, p.part, p.thr_g);
+        }
     }
 }
 

@@ -469,6 +469,51 @@ kmeans_update_device(KMeansWorkspace& ws, const float* x_dev, uint64_t n, uint32
 
 using namespace vb200;
 
+// The training entry points keep one workspace per process between calls (tiled rows, candidate lists, sort
+// buffers: 1.3 GB for 1 M x 128 rows against 4096 centroids), because allocating and freeing it costs more than
+// two Lloyd iterations; a second caller at the same time gets a workspace of its own.
+// vb200_release_workspaces() frees the kept one.
+namespace {
+
+std::mutex g_kmeans_ws_mu;
+KMeansWorkspace* g_kmeans_ws = nullptr;   // never destroyed at exit: the CUDA context may be gone by then
+
+class WorkspaceLease {
+public:
+    WorkspaceLease() : kept_(g_kmeans_ws_mu.try_lock()) {
+        if (kept_ && g_kmeans_ws == nullptr) {
+            g_kmeans_ws = new (std::nothrow) KMeansWorkspace;
+            if (g_kmeans_ws == nullptr) {
+                g_kmeans_ws_mu.unlock();
+                kept_ = false;
+            }
+        }
+        if (kept_) {
+            g_kmeans_ws->forget_points();   // another call's rows may have lived at the same address
+        }
+    }
+    ~WorkspaceLease() {
+        if (kept_) {
+            g_kmeans_ws_mu.unlock();
+        }
+    }
+    KMeansWorkspace& get() { return kept_ ? *g_kmeans_ws : own_; }
+
+private:
+    bool kept_;
+    KMeansWorkspace own_;
+};
+
+}  // namespace
+
+extern "C" int
+vb200_release_workspaces(void) {
+    std::lock_guard<std::mutex> lock(g_kmeans_ws_mu);
+    delete g_kmeans_ws;
+    g_kmeans_ws = nullptr;
+    return 0;
+}
+
 static int
 check_kmeans_args(const float* data, uint64_t count, uint32_t dim, const float* centroids, uint32_t k) {
     // Argument checks of KMeansCluster::Run (kmeans_cluster.cpp:54-65).
@@ -530,7 +575,8 @@ vb200_kmeans_train(const float* data, uint64_t count, uint32_t dim, uint32_t k, 
     VB_CUDA(cudaMemcpyAsync(c.ptr, centroids, kd * sizeof(float), cudaMemcpyDefault, current_stream()));
     DevBuf<int32_t> lab;
     VB_TRY(lab.reserve(count));
-    KMeansWorkspace ws;
+    WorkspaceLease lease;
+    KMeansWorkspace& ws = lease.get();
     for (int it = 0; it < iters; ++it) {
         double* err = (it == iters - 1) ? mean_err : nullptr;
         VB_TRY(kmeans_assign_device(ws, x.ptr, count, dim, c.ptr, k, lab.ptr, err, it > 0 ? lab.ptr : nullptr));

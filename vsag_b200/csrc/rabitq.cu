@@ -143,7 +143,8 @@ rabitq_encode_device(const float* data_dev, uint64_t count, uint32_t dim, const 
 
 int
 rabitq_process_query_device(const float* q_dev, uint64_t count, uint32_t dim,
-                            const float* rotation_dev, const float* centroid_dev, float* out_dev) {
+                            const float* rotation_dev, const float* centroid_dev, float* out_dev,
+                            DevBuf<float>* scratch) {
     if (count == 0) {
         return 0;
     }
@@ -154,7 +155,10 @@ rabitq_process_query_device(const float* q_dev, uint64_t count, uint32_t dim,
     if (slice > count) {
         slice = count;
     }
-    DevBuf<float> t;
+    // rotated rows of one slice: the caller's buffer when it has one to keep between calls (a search must not
+    // allocate and free, nor wait for the device, in the middle of its step)
+    DevBuf<float> own;
+    DevBuf<float>& t = scratch != nullptr ? *scratch : own;
     VB_TRY(t.reserve(slice * dim));
     for (uint64_t b = 0; b < count; b += slice) {
         uint64_t n = count - b < slice ? count - b : slice;
@@ -162,7 +166,7 @@ rabitq_process_query_device(const float* q_dev, uint64_t count, uint32_t dim,
         VB_LAUNCH(rabitq_pack_kernel<true>, static_cast<uint32_t>((n + 63) / 64), 64, 0, t.ptr, n, dim,
                   centroid_dev, 0.f, nullptr, nullptr, 0, out_dev + b * (dim + 1));
     }
-    return sync_stream();
+    return scratch != nullptr ? 0 : sync_stream();   // `own` is freed on return: its work must be done
 }
 
 }  // namespace vb200
@@ -225,7 +229,7 @@ vb200_rabitq_process_query(const float* queries, uint64_t count, uint32_t dim, c
     VB_TRY(cen.bind(centroid, dim));
     DevBuf<float> o;
     VB_TRY(o.reserve(count * (dim + 1)));
-    VB_TRY(rabitq_process_query_device(q.ptr, count, dim, rot.ptr, cen.ptr, o.ptr));
+    VB_TRY(rabitq_process_query_device(q.ptr, count, dim, rot.ptr, cen.ptr, o.ptr, nullptr));
     VB_TRY(copy_out(out, o.ptr, count * (dim + 1)));
     return sync_stream();
 }

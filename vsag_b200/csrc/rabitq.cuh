@@ -24,9 +24,10 @@ int rabitq_encode_device(const float* data_dev, uint64_t count, uint32_t dim,
                          const float* rotation_dev, const float* centroid_dev,
                          const uint32_t* dst_pos_dev, uint8_t* codes_dev, uint32_t code_stride);
 
-// out_dev[count x (dim + 1)]: rotated, centred, normalised rows followed by the norm.
+// out_dev[count x (dim + 1)]: rotated, centred, normalised rows followed by the norm.  With `scratch` (a
+// buffer the caller keeps between calls) nothing is allocated and the call does not wait for the device.
 int rabitq_process_query_device(const float* q_dev, uint64_t count, uint32_t dim,
                                 const float* rotation_dev, const float* centroid_dev,
-                                float* out_dev);
+                                float* out_dev, DevBuf<float>* scratch);
 
 }  // namespace vb200

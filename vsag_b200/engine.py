@@ -457,4 +457,9 @@ class BfHandle:
         return ids, dists
 
 
+def release_workspaces() -> None:
+    """Frees the device workspace vb200_kmeans_train keeps between calls."""
+    check(_capi.load().vb200_release_workspaces())
+
+
 __all__ = [name for name in globals() if not name.startswith("_")]
