@@ -59,6 +59,7 @@ extern "C" {
 #define VB200_QUANT_RABITQ 2
 #define VB200_QUANT_BF16 3
 #define VB200_QUANT_FP16 4   /* IVF buckets only */
+#define VB200_QUANT_SQ8_UNIFORM 5   /* IVF buckets only */
 
 /* SQTrainMode (src/quantization/scalar_quantization/scalar_quantization_trainer.h:25-29). */
 #define VB200_SQ_TRAIN_CLASSIC 1
@@ -215,6 +216,13 @@ VB200_API int vb200_ivf_set_shard(vb200_ivf_t index, uint32_t rank, uint32_t wor
  * bucket quantizer on the same rows.  For RABITQ, `rotation` must have been set first. */
 VB200_API int vb200_ivf_train(vb200_ivf_t index, const float* data, uint64_t count, int kmeans_iters,
                     const float* init);
+
+/* SQ8 uniform (base_quantization_type "sq8_uniform", SQ8UniformQuantizer,
+ * src/quantization/scalar_quantization/sq8_uniform_quantizer.cpp:76-186): one lower bound and one range for all
+ * dimensions; codes carry their uint64 squared norm (L2) or fp32 value sum (IP / cosine), queries are encoded
+ * like rows and distances come from the exact integer inner product of the byte codes. */
+VB200_API int vb200_ivf_set_sq8_uniform_model(vb200_ivf_t index, float lower, float diff);
+VB200_API int vb200_ivf_get_sq8_uniform_model(vb200_ivf_t index, float* lower, float* diff);
 
 /* Model import/export, the pieces IVF::ExportModel / Serialize carry (ivf.cpp:990-1056,
  * :1677-1691): centroids[nlist x dim]; SQ8 lower[dim], diff[dim]

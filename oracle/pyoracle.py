@@ -299,6 +299,43 @@ def ivf_fp32_search(rows, list_off, inner_ids, q, probes, k: int, metric: int = 
     return ids, dists
 
 
+def sq8u_code_size(dim: int, metric: int = 0) -> int:
+    lib().orc_sq8u_code_size.restype = C.c_uint64
+    return int(lib().orc_sq8u_code_size(_u64(dim), _i32(metric)))
+
+
+def sq8u_train(data, metric: int = 0) -> np.ndarray:
+    """SQ8UniformQuantizer::TrainImpl: model = [lower, diff] over all dimensions (metric 2 normalises first)."""
+    data, pd = _a(data, np.float32)
+    model = np.empty(2, np.float32)
+    assert lib().orc_sq8u_train(pd, _u64(data.shape[0]), _u64(data.shape[1]), _i32(metric), _p(model.ctypes.data)) == 0
+    return model
+
+
+def sq8u_encode(data, model, metric: int = 0) -> np.ndarray:
+    """Code records [n, code_size]: codes, padding, then the uint64 norm (l2) or the fp32 sum (ip / cosine)."""
+    data, pd = _a(data, np.float32)
+    model, pm = _a(model, np.float32)
+    out = np.empty((data.shape[0], sq8u_code_size(data.shape[1], metric)), np.uint8)
+    lib().orc_sq8u_encode(pd, _u64(data.shape[0]), _u64(data.shape[1]), _i32(metric), pm, _p(out.ctypes.data))
+    return out
+
+
+def ivf_sq8u_search(codes, list_off, inner_ids, dim: int, model, q, probes, k: int, metric: int = 0):
+    codes, pc = _a(codes, np.uint8)
+    list_off, po = _a(list_off, np.int64)
+    inner_ids, pi = _a(inner_ids, np.int64)
+    model, pm = _a(model, np.float32)
+    q, pq = _a(q, np.float32)
+    probes, pp = _a(probes, np.int32)
+    nq = q.shape[0]
+    ids = np.empty((nq, k), np.int64)
+    dists = np.empty((nq, k), np.float32)
+    lib().orc_ivf_sq8u_search(pc, po, pi, _u64(dim), pm, pq, _u64(nq), pp, _u64(probes.shape[1]), _i64(k), _i32(metric),
+                              _p(ids.ctypes.data), _p(dists.ctypes.data))
+    return ids, dists
+
+
 def float_to_half(x, fmt: str) -> np.ndarray:
     """HalfPrecisionQuantizer::EncodeOneImpl element by element: "bf16" rounds half up, "fp16" clamps the
     exponent and truncates (generic::FloatToBF16 / FloatToFP16)."""

@@ -11,6 +11,7 @@
 #include "simd/rabitq_simd.h"
 #include "simd/simd_status.h"
 #include "simd/sq8_simd.h"
+#include "simd/sq8_uniform_simd.h"
 
 extern "C" {
 
@@ -61,6 +62,9 @@ float ref_generic_RaBitQFloatBinaryIP(const float* v, const uint8_t* bits, uint6
 }
 float ref_generic_NormalizeWithCentroid(const float* from, const float* centroid, float* to, uint64_t d) {
     return vsag::generic::NormalizeWithCentroid(from, centroid, to, d);
+}
+float ref_SQ8UniformComputeCodesIP(const uint8_t* a, const uint8_t* b, uint64_t d) {
+    return vsag::SQ8UniformComputeCodesIP(a, b, d);
 }
 uint16_t ref_FloatToFP16(float v) {
     return vsag::generic::FloatToFP16(v);

@@ -916,6 +916,170 @@ orc_bf_search_bf16(const uint16_t* base,
     }
 }
 
+/* ------------------------------------------------------------------------------------------ */
+/* SQ8 uniform: one lower bound and one range for all dimensions, integer inner products         */
+/* ------------------------------------------------------------------------------------------ */
+
+/* SQ8UniformQuantizer::TrainImpl (src/quantization/scalar_quantization/sq8_uniform_quantizer.cpp:76-100):
+ * CLASSIC bounds of the sample (scalar_quantization_trainer.cpp:47-60: the largest per-dimension maximum and
+ * the smallest per-dimension minimum, i.e. the extremes of the whole sample), diff = upper - lower.  Rows of
+ * a cosine index are normalised before (metric 2).  model = {lower, diff}. */
+ORC_API int
+orc_sq8u_train(const float* data, uint64_t count, uint64_t dim, int metric, float* model) {
+    if (data == NULL || count == 0) {
+        return -1;
+    }
+    const uint64_t max_sample = 100000;
+    uint64_t step = 2147483647ULL % count;
+    uint64_t cnt = max_sample;
+    if (count <= max_sample) {
+        step = 1;
+        cnt = count;
+    }
+    float up = -FLT_MAX, lo = FLT_MAX;
+    float* row = (float*)malloc(dim * sizeof(float));
+    for (uint64_t j = 0; j < cnt; ++j) {
+        const float* x = data + ((j * step) % count) * dim;
+        if (metric == 2) {
+            orc_normalize_rows(x, 1, dim, row);
+            x = row;
+        }
+        for (uint64_t d = 0; d < dim; ++d) {
+            up = x[d] > up ? x[d] : up;
+            lo = x[d] < lo ? x[d] : lo;
+        }
+    }
+    free(row);
+    model[0] = lo;
+    model[1] = up - lo;
+    return 0;
+}
+
+/* Code record (sq8_uniform_quantizer.cpp:32-60): the codes padded to the alignment of the trailing field,
+ * then for L2 the uint64 sum of squared codes, for IP / cosine the fp32 sum of the (normalised) values. */
+ORC_API uint64_t
+orc_sq8u_code_size(uint64_t dim, int metric) {
+    uint64_t align = metric == 0 ? 8 : 4;
+    return (dim + align - 1) / align * align + align;
+}
+
+/* scalar_rate_ = (diff / 255.0) * (diff / 255.0), evaluated in double and stored as float (:96). */
+ORC_API float
+orc_sq8u_scalar_rate(float diff) {
+    return (float)(((double)diff / 255.0) * ((double)diff / 255.0));
+}
+
+/* SQ8UniformQuantizer::EncodeOneImpl (:102-142), also used for the query (ProcessQueryImpl, :188-199). */
+ORC_API void
+orc_sq8u_encode(const float* data, uint64_t count, uint64_t dim, int metric, const float* model, uint8_t* codes) {
+    const uint64_t cs = orc_sq8u_code_size(dim, metric);
+    const float lower = model[0], diff = model[1];
+    const float inv_diff = diff == 0.0f ? 0.0f : 1.0f / diff;
+    float* row = (float*)malloc(dim * sizeof(float));
+    for (uint64_t i = 0; i < count; ++i) {
+        const float* x = data + i * dim;
+        if (metric == 2) {
+            orc_normalize_rows(x, 1, dim, row);
+            x = row;
+        }
+        uint8_t* c = codes + i * cs;
+        memset(c, 0, cs);
+        uint64_t norm = 0;
+        float sum = 0.0f;
+        for (uint64_t d = 0; d < dim; ++d) {
+            float delta = (x[d] - lower) * inv_diff;
+            if (!(delta >= 0.0f)) {
+                delta = 0.0f;
+            } else if (delta > 0.999f) {
+                delta = 1.0f;
+            }
+            uint8_t scaled = (uint8_t)(255.0f * delta);
+            c[d] = scaled;
+            norm += (uint64_t)scaled * (uint64_t)scaled;
+            sum += x[d];
+        }
+        if (metric == 0) {
+            memcpy(c + cs - 8, &norm, 8);
+        } else {
+            memcpy(c + cs - 4, &sum, 4);
+        }
+    }
+    free(row);
+}
+
+/* generic::SQ8UniformComputeCodesIP (src/simd/generic.cpp:424-433): int32 sum of byte products. */
+ORC_API float
+orc_sq8u_codes_ip(const uint8_t* a, const uint8_t* b, uint64_t dim) {
+    int32_t r = 0;
+    for (uint64_t d = 0; d < dim; ++d) {
+        r += (int32_t)a[d] * (int32_t)b[d];
+    }
+    return (float)r;
+}
+
+/* SQ8UniformQuantizer::ComputeImpl (:153-186). */
+ORC_API float
+orc_sq8u_dist(const uint8_t* q, const uint8_t* c, uint64_t dim, int metric, const float* model) {
+    const uint64_t cs = orc_sq8u_code_size(dim, metric);
+    const float rate = orc_sq8u_scalar_rate(model[1]);
+    float result = orc_sq8u_codes_ip(q, c, dim);
+    if (metric == 0) {
+        uint64_t n1, n2;
+        memcpy(&n1, q + cs - 8, 8);
+        memcpy(&n2, c + cs - 8, 8);
+        return ((float)n1 + (float)n2 - 2 * result) * rate;
+    }
+    float s1, s2;
+    memcpy(&s1, q + cs - 4, 4);
+    memcpy(&s2, c + cs - 4, 4);
+    const float lower = model[0];
+    result = lower * (s1 + s2) + rate * result + lower * lower;
+    return 1 - result;
+}
+
+/* The probe loop over sq8_uniform buckets: the query is encoded like a row, distances are ComputeImpl's. */
+ORC_API void
+orc_ivf_sq8u_search(const uint8_t* codes,
+                    const int64_t* list_off,
+                    const int64_t* inner_ids,
+                    uint64_t dim,
+                    const float* model,
+                    const float* q,
+                    uint64_t nq,
+                    const int32_t* probes,
+                    uint64_t nprobe,
+                    int64_t k,
+                    int metric,
+                    int64_t* out_ids,
+                    float* out_dists) {
+    const uint64_t cs = orc_sq8u_code_size(dim, metric);
+#pragma omp parallel
+    {
+        orc_heap h;
+        h.a = (orc_rec*)malloc((size_t)(k + 2) * sizeof(orc_rec));
+        h.cap = k + 2;
+        uint8_t* qc = (uint8_t*)malloc(cs);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t i = 0; i < (int64_t)nq; ++i) {
+            orc_sq8u_encode(q + (uint64_t)i * dim, 1, dim, metric, model, qc);
+            h.size = 0;
+            for (uint64_t p = 0; p < nprobe; ++p) {
+                int32_t l = probes[(uint64_t)i * nprobe + p];
+                if (l < 0) {
+                    continue;
+                }
+                for (int64_t r = list_off[l]; r < list_off[l + 1]; ++r) {
+                    float d = orc_sq8u_dist(qc, codes + (uint64_t)r * cs, dim, metric, model);
+                    heap_offer_strict(&h, k, d, inner_ids[r]);
+                }
+            }
+            heap_drain(&h, k, out_ids + (uint64_t)i * k, out_dists + (uint64_t)i * k);
+        }
+        free(h.a);
+        free(qc);
+    }
+}
+
 /* generic::FloatToFP16 (src/simd/generic.cpp:214-228): the exponent is clamped to [-14, 15] and the
  * mantissa truncated to 10 bits -- no rounding, no zero, denormal, infinity or NaN encodings (0.0f
  * becomes 2^-14).  Every code it writes is a normal number of IEEE half precision. */

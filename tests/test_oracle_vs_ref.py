@@ -103,3 +103,17 @@ def test_fp16_matches_reference(oracle, ref):
         assert l2 == ref.ref_generic_FP16ComputeL2Sqr(a.ctypes.data, b.ctypes.data, dim)      # same order: same bits
         assert ip == pytest.approx(ref.ref_FP16ComputeIP(a.ctypes.data, b.ctypes.data, dim), rel=1e-5, abs=1e-5)
         assert l2 == pytest.approx(ref.ref_FP16ComputeL2Sqr(a.ctypes.data, b.ctypes.data, dim), rel=1e-5)
+
+
+def test_sq8_uniform_codes_ip_matches_reference(oracle, ref):
+    """SQ8UniformComputeCodesIP as the reference dispatches it (AVX-512 here): an exact integer, whatever the order."""
+    rng = np.random.default_rng(4)
+    ref.ref_SQ8UniformComputeCodesIP.restype = C.c_float
+    ref.ref_SQ8UniformComputeCodesIP.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+    lib = oracle.lib()
+    lib.orc_sq8u_codes_ip.restype = C.c_float
+    for dim in (1, 7, 64, 96, 100, 960):
+        a = rng.integers(0, 256, dim, dtype=np.uint8)
+        b = rng.integers(0, 256, dim, dtype=np.uint8)
+        want = ref.ref_SQ8UniformComputeCodesIP(a.ctypes.data, b.ctypes.data, dim)
+        assert lib.orc_sq8u_codes_ip(_p(a), _p(b), C.c_uint64(dim)) == want == float(a.astype(np.int64) @ b.astype(np.int64))

@@ -19,7 +19,7 @@ constexpr uint32_t ROUTE_SLACK = 8;   // extra routing candidates re-scored exac
 constexpr uint32_t ROUTE_MAX_PER_ROW = 4096;   // approximate candidates a query may bring to the final pick (32 KiB of keys)
 constexpr int SQ8_QT = 16;
 constexpr uint32_t SQ8_SLACK = 16;    // survivors kept beyond k for exact re-scoring
-constexpr int RABITQ_QT = 4;
+constexpr int RABITQ_QT = 4;   // 4-query tiles: twice the resident warps of 8-query tiles, which this latency-bound scan needs more than reuse
 
 template <typename T>
 static int
@@ -73,6 +73,7 @@ struct SearchWorkspace {
     vb200_exchange_fn exchange = nullptr;   // set for the duration of one partial search
     void* exchange_arg = nullptr;
     DevBuf<float> qrot;   // RaBitQ: rotated query rows of one slice
+    DevBuf<uint8_t> qcodes;   // SQ8 uniform: the queries' code records
     const float* ext_probe_dists = nullptr;   // centroid distances of caller-given probe lists (same duration)
     // sharded search: this rank's routed slice [probes | distances], the gathered probe lists and distances,
     // this rank's packed partial result [keys | labels] and the gathered ones
@@ -125,6 +126,7 @@ struct vb200_ivf {
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
     uint32_t max_list_len = 0;   // the longest list this index (shard) holds
+    float su_lower = 0.f, su_diff = 0.f;   // SQ8 uniform model (one bound and one range for all dimensions)
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
     DevBuf<uint32_t> tombstones;  // bitmap over inner ids: vectors removed with MARK_REMOVE
     uint64_t tomb_words = 0;
@@ -1711,7 +1713,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     VB_CHECK_ARG(kfinal >= 1 && kscan <= 1024 - SCAN_THREADS, "k = %u out of range [1, %u]", kfinal,
                  1024 - SCAN_THREADS - (sq8 ? SQ8_SLACK : 0));
     const bool flat_rows = ix->quant == VB200_QUANT_FP32 || ix->quant == VB200_QUANT_BF16 || ix->quant == VB200_QUANT_FP16;
-    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT : (flat_rows ? FP32_QT : RABITQ_QT);
+    const int qt = ix->quant == VB200_QUANT_SQ8 ? SQ8_QT
+                   : (flat_rows ? FP32_QT : (ix->quant == VB200_QUANT_SQ8_UNIFORM ? SQ8U_QT : RABITQ_QT));
 
     // Phase 0 scans every query's nearest list (of those this shard holds), phase 1 the other
     // probes: after phase 0 the per-query bound is already close to final, so almost nothing
@@ -1802,6 +1805,10 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.coef_b = ix->metric == VB200_METRIC_L2 ? 1.0f : 0.0f;
     p.coef_c = ix->metric == VB200_METRIC_L2 ? -2.0f : -1.0f;
     p.inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(ix->dim));
+    p.qcodes = ws.qcodes.ptr;
+    p.qcode_stride = ix->code_stride;
+    p.su_lower = ix->su_lower;
+    p.su_rate = static_cast<float>((static_cast<double>(ix->su_diff) / 255.0) * (static_cast<double>(ix->su_diff) / 255.0));
     p.metric = ix->metric;
     ws.pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
     if (ws.pruning) {
@@ -1941,6 +1948,10 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             }
             return launch_scan(ivf_fp32_scan_kernel<FP32_QT>, p, smem);
         }
+        if (ix->quant == VB200_QUANT_SQ8_UNIFORM) {
+            size_t smem = tile_smem_bytes<SQ8U_QT>(p.cap, SQ8U_QT * (ix->dpad / 4));
+            return launch_scan(ivf_sq8u_scan_kernel<SQ8U_QT>, p, smem);
+        }
         // Lists no longer than the scan depth need no selection (every probed row is a candidate): their items
         // go to the kernel variant without selection buffers, the longer lists' items to the one with them.
         // Each launch walks the whole queue with a counter of its own.
@@ -2070,6 +2081,12 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
                                            ws.qproc.ptr, &ws.qrot));
         q_scan = ws.qproc.ptr;
     }
+    if (ix->quant == VB200_QUANT_SQ8_UNIFORM) {
+        // ProcessQueryImpl: the query becomes a code record of its own
+        VB_TRY(ws.qcodes.reserve(nq * ix->code_stride));
+        VB_TRY(sq8u_encode_device(q_dev, nq, ix->dim, ix->metric == VB200_METRIC_L2 ? 1 : 0, ix->su_lower, ix->su_diff,
+                                  nullptr, ws.qcodes.ptr, ix->code_stride));
+    }
     VB_TRY(ivf_scan_device(ix, q_scan, nq, kscan, nprobe, ws.probes.ptr, probe_dists));
     const uint64_t* keys = ws.keys.ptr;
     if (rerank) {
@@ -2117,7 +2134,7 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
     VB_CHECK_ARG(dim > 0, "dim must be positive");
     VB_CHECK_ARG(nlist >= 1, "buckets_count must be at least 1");
     VB_CHECK_ARG(quant == VB200_QUANT_SQ8 || quant == VB200_QUANT_RABITQ || quant == VB200_QUANT_FP32 ||
-                     quant == VB200_QUANT_BF16 || quant == VB200_QUANT_FP16,
+                     quant == VB200_QUANT_BF16 || quant == VB200_QUANT_FP16 || quant == VB200_QUANT_SQ8_UNIFORM,
                  "base_quantization_type must be fp32, sq8 or rabitq for this engine (got %d)", quant);
     VB_CHECK_ARG(metric == VB200_METRIC_L2 || metric == VB200_METRIC_IP || metric == VB200_METRIC_COSINE,
                  "metric_type must be l2, ip or cosine (got %d)", metric);
@@ -2155,6 +2172,11 @@ vb200_ivf_create(uint32_t dim, int metric, uint32_t nlist, int quant, int use_re
         ix->dpad = (dim + 7) / 8 * 8;       // rows start on 16-byte boundaries
         ix->code_stride = ix->dpad * 2;
         ix->has_model = true;   // HalfPrecisionQuantizer::TrainImpl has nothing to learn
+    } else if (quant == VB200_QUANT_SQ8_UNIFORM) {
+        const int is_l2 = ix->metric == VB200_METRIC_L2 ? 1 : 0;   // cosine was mapped to IP above
+        ix->code_size = sq8u_code_size(dim, is_l2);
+        ix->dpad = ix->code_size - (is_l2 ? 8u : 4u);   // bytes of a record before its trailing field
+        ix->code_stride = (ix->code_size + 15) / 16 * 16;
     } else {
         ix->code_size = rabitq_code_size(dim);
         ix->dpad = rabitq_bits_bytes(dim) * 8;
@@ -2275,6 +2297,31 @@ vb200_ivf_get_sq8_model(vb200_ivf_t ix, float* lower, float* diff) {
 }
 
 extern "C" int
+vb200_ivf_set_sq8_uniform_model(vb200_ivf_t ix, float lower, float diff) {
+    VB_CHECK_ARG(ix != nullptr, "null pointer");
+    VB_CHECK_ARG(ix->quant == VB200_QUANT_SQ8_UNIFORM, "index is not sq8_uniform");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "quantizer model cannot change after vectors were added");
+    }
+    ix->su_lower = lower;
+    ix->su_diff = diff;
+    ix->has_model = true;
+    return 0;
+}
+
+extern "C" int
+vb200_ivf_get_sq8_uniform_model(vb200_ivf_t ix, float* lower, float* diff) {
+    VB_CHECK_ARG(ix != nullptr && lower != nullptr && diff != nullptr, "null pointer");
+    if (ix->quant != VB200_QUANT_SQ8_UNIFORM || !ix->has_model) {
+        VB_FAIL(VB200_WRONG_STATUS, "index has no sq8_uniform model");
+    }
+    *lower = ix->su_lower;
+    *diff = ix->su_diff;
+    return 0;
+}
+
+extern "C" int
 vb200_ivf_set_rabitq_rotation(vb200_ivf_t ix, const float* rotation) {
     VB_CHECK_ARG(ix != nullptr && rotation != nullptr, "null pointer");
     VB_CHECK_ARG(ix->quant == VB200_QUANT_RABITQ, "index is not rabitq");
@@ -2354,7 +2401,7 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
         // (ivf_nearest_partition.cpp:81-85); the quantizer sees normalised rows
         // (scalar_quantization_trainer.cpp:139-141).
         VB_TRY(normalize_rows_f32(ix->centroids.ptr, ix->nlist, ix->dim, ix->centroids.ptr));
-        if (ix->quant == VB200_QUANT_SQ8) {
+        if (ix->quant == VB200_QUANT_SQ8 || ix->quant == VB200_QUANT_SQ8_UNIFORM) {
             VB_TRY(unit_rows.reserve(count * ix->dim));
             VB_TRY(normalize_rows_f32(x.ptr, count, ix->dim, unit_rows.ptr));
             x_model = unit_rows.ptr;
@@ -2370,6 +2417,15 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
     } else if (ix->quant == VB200_QUANT_RABITQ) {
         VB_TRY(ix->rq_centroid.reserve(ix->dim));
         VB_TRY(rabitq_train_device(x.ptr, count, ix->dim, ix->rotation.ptr, ix->rq_centroid.ptr));
+        ix->has_model = true;
+    } else if (ix->quant == VB200_QUANT_SQ8_UNIFORM) {
+        DevBuf<float> model;
+        VB_TRY(model.reserve(2));
+        VB_TRY(sq8u_train_device(x_model, count, ix->dim, model.ptr));
+        float host_model[2] = {0.f, 0.f};
+        VB_CUDA(cudaMemcpy(host_model, model.ptr, sizeof(host_model), cudaMemcpyDeviceToHost));
+        ix->su_lower = host_model[0];
+        ix->su_diff = host_model[1];
         ix->has_model = true;
     }
     return sync_stream();
@@ -2587,6 +2643,9 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     } else if (ix->quant == VB200_QUANT_FP32) {
         VB_LAUNCH(fp32_place_rows_kernel, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count, dim,
                   dst_of_row.ptr, new_codes.ptr, stride);
+    } else if (ix->quant == VB200_QUANT_SQ8_UNIFORM) {
+        VB_TRY(sq8u_encode_device(xr, count, dim, ix->metric == VB200_METRIC_L2 ? 1 : 0, ix->su_lower, ix->su_diff,
+                                  dst_of_row.ptr, new_codes.ptr, stride));
     } else if (ix->quant == VB200_QUANT_BF16) {
         VB_LAUNCH(half_place_rows_kernel<SCAN_FMT_BF16>, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count,
                   dim, dst_of_row.ptr, new_codes.ptr, stride);

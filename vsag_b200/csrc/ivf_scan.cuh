@@ -75,6 +75,10 @@ struct ScanParams {
     float coef_b;                // SQ8: distance = qa + coef_b * |x|^2 + coef_c * dot
     float coef_c;
     float inv_sqrt_d;            // RaBitQ
+    const uint8_t* qcodes;       // SQ8 uniform: [nq x qcode_stride] the queries' own code records
+    uint32_t qcode_stride;
+    float su_lower;              // SQ8 uniform: lower bound and (diff / 255)^2
+    float su_rate;
     int metric;
     // SQ8 list pruning (both null = off): every decoded row of list l lies in one of SQ8_BALLS
     // balls (centre, radius); a query cannot have anything in the list closer than the triangle
@@ -864,6 +868,117 @@ ivf_rabitq_scan_kernel(const ScanParams p) {
         if (!DIRECT) {
             ts.finish(nqt, p.part, p.thr_g);
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SQ8 uniform (SQ8UniformQuantizer::ComputeImpl, src/quantization/scalar_quantization/
+// sq8_uniform_quantizer.cpp:153-186): the query is encoded like a row, the inner product of the two byte codes
+// is an exact integer (generic::SQ8UniformComputeCodesIP, src/simd/generic.cpp:424-433; any summation order
+// gives it: four products per dp4a), and the distance is
+//   L2:  (float(norm_q) + float(norm_x) - 2 * ip) * rate          with the uint64 norms stored in the records,
+//   IP:  1 - (lower * (sum_q + sum_x) + rate * ip + lower * lower) with the fp32 sums stored in the records,
+// each operation rounded on its own as written there.  p.dpad = bytes of a record before its trailing field.
+// ---------------------------------------------------------------------------------------------
+constexpr int SQ8U_QT = 8;
+
+template <int QT>
+__global__ void __launch_bounds__(SCAN_THREADS)
+ivf_sq8u_scan_kernel(const ScanParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ uint32_t s_item[1];
+    __shared__ float s_qfield[QT];   // float(norm) or sum of each query of the tile
+    TileSelect<QT> ts;
+    float* fbuf;
+    tile_carve<QT>(smem, p.cap, 0, fbuf, ts);
+    ts.k = p.k;
+    ts.cap = p.cap;
+    const uint32_t words = p.dpad / 4;
+    uint32_t* sq = reinterpret_cast<uint32_t*>(fbuf);   // [QT][words] the queries' code bytes
+    const bool l2 = p.metric == 0;
+
+    ScanItem it;
+    while (scan_next_item<QT>(p, s_item, it)) {
+        const uint32_t list = it.list;
+        const uint32_t pbeg = it.pbeg;
+        const int nqt = static_cast<int>(it.nqt);
+        if (threadIdx.x < QT) {
+            int qi = threadIdx.x;
+            ts.qa[qi] = 0.f;
+            float field = 0.f;
+            if (qi < nqt) {
+                uint32_t q = it.pair_q[pbeg + qi];
+                ts.qidx[qi] = q;
+                ts.slot[qi] = it.pair_slot[pbeg + qi];
+                ts.set_bound(qi, p.thr_g[q]);
+                const uint8_t* rec = p.qcodes + static_cast<uint64_t>(q) * p.qcode_stride + p.dpad;
+                field = l2 ? static_cast<float>(*reinterpret_cast<const unsigned long long*>(rec))
+                           : *reinterpret_cast<const float*>(rec);
+            } else {
+                ts.qidx[qi] = 0;
+                ts.slot[qi] = 0;
+                ts.set_bound(qi, 0u);
+            }
+            s_qfield[qi] = field;
+            ts.cnt[qi] = 0;
+        }
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < static_cast<uint32_t>(QT) * words; i += SCAN_THREADS) {
+            const uint32_t qi = i / words, w = i % words;
+            uint32_t v = 0;
+            if (static_cast<int>(qi) < nqt) {
+                v = __ldg(reinterpret_cast<const uint32_t*>(p.qcodes + static_cast<uint64_t>(ts.qidx[qi]) * p.qcode_stride) + w);
+            }
+            sq[i] = v;
+        }
+        __syncthreads();
+
+        const uint32_t lbeg = p.list_off[list];
+        const uint32_t len = p.list_off[list + 1] - lbeg;
+        for (uint32_t r0 = 0; r0 < len; r0 += SCAN_THREADS) {
+            const uint32_t row = r0 + threadIdx.x;
+            const bool valid = row < len;
+            const unsigned char* rec = p.codes + static_cast<uint64_t>(lbeg + (valid ? row : 0)) * p.code_stride;
+            const uint32_t* xw = reinterpret_cast<const uint32_t*>(rec);
+            uint32_t acc[QT];
+#pragma unroll
+            for (int qi = 0; qi < QT; ++qi) {
+                acc[qi] = 0u;
+            }
+            for (uint32_t w = 0; w < words; ++w) {
+                const uint32_t x = __ldg(xw + w);
+#pragma unroll
+                for (int qi = 0; qi < QT; ++qi) {
+                    if (qi < nqt) {
+                        acc[qi] = __dp4a(x, sq[qi * words + w], acc[qi]);
+                    }
+                }
+            }
+            if (valid) {
+                const float field = l2 ? static_cast<float>(*reinterpret_cast<const unsigned long long*>(rec + p.dpad))
+                                       : *reinterpret_cast<const float*>(rec + p.dpad);
+#pragma unroll
+                for (int qi = 0; qi < QT; ++qi) {
+                    if (qi < nqt) {
+                        const float ip = static_cast<float>(static_cast<int32_t>(acc[qi]));
+                        float dist;
+                        if (l2) {
+                            dist = __fmul_rn(__fsub_rn(__fadd_rn(s_qfield[qi], field), __fmul_rn(2.0f, ip)), p.su_rate);
+                        } else {
+                            const float r = __fadd_rn(__fadd_rn(__fmul_rn(p.su_lower, __fadd_rn(s_qfield[qi], field)),
+                                                                __fmul_rn(p.su_rate, ip)),
+                                                      __fmul_rn(p.su_lower, p.su_lower));
+                            dist = __fsub_rn(1.0f, r);
+                        }
+                        ts.push(p, qi, dist, lbeg + row);
+                    }
+                }
+            }
+            __syncthreads();
+            ts.make_room(nqt);
+            __syncthreads();
+        }
+        ts.finish(nqt, p.part, p.thr_g);
     }
 }
 

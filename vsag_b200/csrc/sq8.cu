@@ -111,6 +111,139 @@ sq8_train_device(const float* data_dev, uint64_t count, uint32_t dim, int mode, 
 }
 
 // ---------------------------------------------------------------------------------------------
+// SQ8 uniform
+// ---------------------------------------------------------------------------------------------
+
+// extremes[0] = min, extremes[1] = max (as ordered keys) over the sampled rows' values.
+__global__ void __launch_bounds__(256)
+sq8u_extremes_kernel(const float* __restrict__ data, uint64_t count, uint32_t dim, uint64_t step, uint32_t cnt,
+                     uint32_t* __restrict__ extremes) {
+    __shared__ uint32_t s_lo[8], s_hi[8];
+    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+    const uint64_t total = static_cast<uint64_t>(cnt) * dim;
+    for (uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+         e += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint64_t j = e / dim;
+        const uint32_t d = static_cast<uint32_t>(e % dim);
+        const uint64_t row = (j * step) % count;
+        const uint32_t key = float_to_ordered(__ldg(data + row * dim + d));
+        lo = key < lo ? key : lo;
+        hi = key > hi ? key : hi;
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        s_lo[threadIdx.x >> 5] = lo;
+        s_hi[threadIdx.x >> 5] = hi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) {
+            lo = min(lo, s_lo[w]);
+            hi = max(hi, s_hi[w]);
+        }
+        atomicMin(extremes, lo);
+        atomicMax(extremes + 1, hi);
+    }
+}
+
+__global__ void
+sq8u_model_kernel(const uint32_t* __restrict__ extremes, float* __restrict__ model) {
+    const float lo = ordered_to_float(extremes[0]), up = ordered_to_float(extremes[1]);
+    model[0] = lo;
+    model[1] = __fsub_rn(up, lo);   // diff_ -= lower_bound_ (:95)
+}
+
+int
+sq8u_train_device(const float* data_dev, uint64_t count, uint32_t dim, float* model_dev) {
+    VB_CHECK_ARG(count > 0 && dim > 0, "sq8_uniform train: empty input");
+    const uint64_t max_sample = 100000;
+    uint64_t step = 2147483647ull % count;
+    uint32_t cnt = static_cast<uint32_t>(max_sample);
+    if (count <= max_sample) {
+        step = 1;
+        cnt = static_cast<uint32_t>(count);
+    }
+    DevBuf<uint32_t> extremes;
+    VB_TRY(extremes.reserve(2));
+    const uint32_t init[2] = {0xFFFFFFFFu, 0u};
+    VB_CUDA(cudaMemcpyAsync(extremes.ptr, init, sizeof(init), cudaMemcpyHostToDevice, current_stream()));
+    const uint64_t total = static_cast<uint64_t>(cnt) * dim;
+    const uint32_t blocks = static_cast<uint32_t>(std::min<uint64_t>((total + 255) / 256, 4096));
+    VB_LAUNCH(sq8u_extremes_kernel, blocks, 256, 0, data_dev, count, dim, step, cnt, extremes.ptr);
+    VB_LAUNCH(sq8u_model_kernel, 1, 1, 0, extremes.ptr, model_dev);
+    return sync_stream();
+}
+
+// One warp per row.  EncodeOneImpl (:102-142) operation by operation: inv_diff = 1 / diff (0 when diff is 0),
+// delta = (x - lower) * inv_diff, clamp, truncate 255 * delta; norm = integer sum of squared codes; sum = the
+// values added one after the other in fp32 (lane 0 walks the row for it: the order is part of the result).
+__global__ void __launch_bounds__(128)
+sq8u_encode_kernel(const float* __restrict__ data, uint64_t count, uint32_t dim, int metric_is_l2, float lower,
+                   float inv_diff, const uint32_t* __restrict__ dst_pos, uint8_t* __restrict__ codes,
+                   uint32_t code_stride, uint32_t code_size) {
+    const uint64_t i = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    if (i >= count) {
+        return;
+    }
+    uint64_t p = i;
+    if (dst_pos != nullptr) {
+        const uint32_t t = dst_pos[i];
+        if (t == 0xFFFFFFFFu) {
+            return;
+        }
+        p = t;
+    }
+    const float* x = data + i * dim;
+    uint8_t* c = codes + p * code_stride;
+    unsigned long long norm = 0;
+    for (uint32_t d = lane; d < code_size - (metric_is_l2 ? 8u : 4u); d += 32) {
+        uint8_t scaled = 0;
+        if (d < dim) {
+            float delta = __fmul_rn(__fsub_rn(__ldg(x + d), lower), inv_diff);
+            if (!(delta >= 0.0f)) {
+                delta = 0.0f;
+            } else if (delta > 0.999f) {
+                delta = 1.0f;
+            }
+            scaled = static_cast<uint8_t>(__fmul_rn(255.0f, delta));
+        }
+        c[d] = scaled;
+        norm += static_cast<unsigned long long>(scaled) * scaled;
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        norm += __shfl_xor_sync(0xffffffffu, norm, off);
+    }
+    if (lane == 0) {
+        if (metric_is_l2) {
+            *reinterpret_cast<unsigned long long*>(c + code_size - 8) = norm;
+        } else {
+            float sum = 0.f;
+            for (uint32_t d = 0; d < dim; ++d) {
+                sum = __fadd_rn(sum, __ldg(x + d));
+            }
+            *reinterpret_cast<float*>(c + code_size - 4) = sum;
+        }
+    }
+}
+
+int
+sq8u_encode_device(const float* data_dev, uint64_t count, uint32_t dim, int metric_is_l2, float lower, float diff,
+                   const uint32_t* dst_pos_dev, uint8_t* codes_dev, uint32_t code_stride) {
+    if (count == 0) {
+        return 0;
+    }
+    const float inv_diff = diff == 0.0f ? 0.0f : 1.0f / diff;
+    const uint64_t threads = count * 32;
+    VB_LAUNCH(sq8u_encode_kernel, static_cast<uint32_t>((threads + 127) / 128), 128, 0, data_dev, count, dim,
+              metric_is_l2, lower, inv_diff, dst_pos_dev, codes_dev, code_stride, sq8u_code_size(dim, metric_is_l2));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // encoding
 // ---------------------------------------------------------------------------------------------
 

@@ -13,7 +13,7 @@ from . import _capi
 from ._capi import VsagB200Error, check, ptr
 
 METRIC_L2, METRIC_IP, METRIC_COSINE = 0, 1, 2
-QUANT_FP32, QUANT_SQ8, QUANT_RABITQ, QUANT_BF16, QUANT_FP16 = 0, 1, 2, 3, 4
+QUANT_FP32, QUANT_SQ8, QUANT_RABITQ, QUANT_BF16, QUANT_FP16, QUANT_SQ8_UNIFORM = 0, 1, 2, 3, 4, 5
 SQ_TRAIN_CLASSIC, SQ_TRAIN_TRUNC_BOUND = 1, 3
 
 METRICS = {"l2": METRIC_L2, "ip": METRIC_IP, "cosine": METRIC_COSINE}
@@ -186,7 +186,18 @@ class IvfHandle:
             return self.dim
         if self.quant in (QUANT_BF16, QUANT_FP16):
             return self.dim * 2
+        if self.quant == QUANT_SQ8_UNIFORM:
+            align = 8 if self.metric == METRIC_L2 else 4
+            return (self.dim + align - 1) // align * align + align
         return self.dim * 4 if self.quant == QUANT_FP32 else rabitq_code_size(self.dim)
+
+    def set_sq8_uniform_model(self, lower: float, diff: float) -> None:
+        check(self._lib.vb200_ivf_set_sq8_uniform_model(self._h, float(lower), float(diff)))
+
+    def get_sq8_uniform_model(self):
+        lower, diff = C.c_float(0), C.c_float(0)
+        check(self._lib.vb200_ivf_get_sq8_uniform_model(self._h, C.byref(lower), C.byref(diff)))
+        return np.array([lower.value, diff.value], np.float32)
 
     def set_shard(self, rank: int, world: int) -> None:
         check(self._lib.vb200_ivf_set_shard(self._h, rank, world))

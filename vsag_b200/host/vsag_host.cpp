@@ -537,9 +537,12 @@ public:
             quant_ = VB200_QUANT_BF16;
         } else if (quant == "fp16") {
             quant_ = VB200_QUANT_FP16;
+        } else if (quant == "sq8_uniform") {
+            quant_ = VB200_QUANT_SQ8_UNIFORM;
         } else {
-            fail(ErrorType::INVALID_ARGUMENT, "base_quantization_type \"" + quant +
-                                                  "\" is not served by the GPU engine (fp32, bf16, fp16, sq8 and rabitq are)");
+            fail(ErrorType::INVALID_ARGUMENT,
+                 "base_quantization_type \"" + quant +
+                     "\" is not served by the GPU engine (fp32, bf16, fp16, sq8, sq8_uniform and rabitq are)");
         }
         use_reorder_ = get_bool(p, "use_reorder", false);
         std::string precise = get_string(p, "precise_quantization_type", "fp32");
@@ -754,6 +757,10 @@ public:
                     check_status(vb200_ivf_get_sq8_model(handle_, lower.data(), diff.data()));
                     write_array(out, lower);
                     write_array(out, diff);
+                } else if (quant_ == VB200_QUANT_SQ8_UNIFORM) {
+                    std::vector<float> model(2);
+                    check_status(vb200_ivf_get_sq8_uniform_model(handle_, &model[0], &model[1]));
+                    write_array(out, model);
                 } else if (quant_ == VB200_QUANT_RABITQ) {
                     std::vector<float> centre(dim_);
                     check_status(vb200_ivf_get_rabitq_centroid(handle_, centre.data()));
@@ -806,6 +813,9 @@ public:
                     auto lower = read_array<float>(in, dim_, "sq8 lower bound");
                     auto diff = read_array<float>(in, dim_, "sq8 diff");
                     check_status(vb200_ivf_set_sq8_model(handle_, lower.data(), diff.data()));
+                } else if (quant_ == VB200_QUANT_SQ8_UNIFORM) {
+                    auto model = read_array<float>(in, 2, "sq8_uniform model");
+                    check_status(vb200_ivf_set_sq8_uniform_model(handle_, model[0], model[1]));
                 } else if (quant_ == VB200_QUANT_RABITQ) {
                     auto rotation = read_array<float>(in, static_cast<uint64_t>(dim_) * dim_, "rabitq rotation");
                     auto centre = read_array<float>(in, dim_, "rabitq centroid");
@@ -957,6 +967,10 @@ private:
         }
         if (quant_ == VB200_QUANT_BF16 || quant_ == VB200_QUANT_FP16) {
             return static_cast<int64_t>(dim_) * 2;
+        }
+        if (quant_ == VB200_QUANT_SQ8_UNIFORM) {
+            const int64_t align = metric_ == VB200_METRIC_L2 ? 8 : 4;   // sq8_uniform_quantizer.cpp:32-60
+            return (static_cast<int64_t>(dim_) + align - 1) / align * align + align;
         }
         return quant_ == VB200_QUANT_SQ8 ? dim_ : static_cast<int64_t>(vb200_rabitq_code_size(dim_));
     }
