@@ -217,6 +217,13 @@ VB200_API int vb200_ivf_set_shard(vb200_ivf_t index, uint32_t rank, uint32_t wor
 VB200_API int vb200_ivf_train(vb200_ivf_t index, const float* data, uint64_t count, int kmeans_iters,
                     const float* init);
 
+/* buckets_per_data (IVF creation parameter, src/algorithm/ivf/ivf.cpp:607, :659-676): every vector is stored
+ * in that many of its nearest lists; a search looks for buckets_per_data times as many postings and folds the
+ * duplicates of a vector into its smallest distance (:1722-1727, :1799-1825).  Set before the first add; 1 is
+ * the default; not available on a sharded index.  With it, vb200_ivf_add's labels_in (when given) holds
+ * count x buckets_per_data list ids, vector by vector. */
+VB200_API int vb200_ivf_set_buckets_per_data(vb200_ivf_t index, uint32_t buckets_per_data);
+
 /* SQ8 uniform (base_quantization_type "sq8_uniform", SQ8UniformQuantizer,
  * src/quantization/scalar_quantization/sq8_uniform_quantizer.cpp:76-186): one lower bound and one range for all
  * dimensions; codes carry their uint64 squared norm (L2) or fp32 value sum (IP / cosine), queries are encoded

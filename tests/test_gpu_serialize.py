@@ -22,6 +22,8 @@ CASES = [
     ("ivf", "ip", dict(buckets_count=24, base_quantization_type="sq8"), {"ivf": {"scan_buckets_count": 6}}),
     ("ivf", "cosine", dict(buckets_count=24, base_quantization_type="fp32"), {"ivf": {"scan_buckets_count": 6}}),
     ("ivf", "l2", dict(buckets_count=24, base_quantization_type="bf16"), {"ivf": {"scan_buckets_count": 6}}),
+    ("ivf", "l2", dict(buckets_count=24, base_quantization_type="sq8_uniform", buckets_per_data=2),
+     {"ivf": {"scan_buckets_count": 6}}),
     ("ivf", "cosine", dict(buckets_count=24, base_quantization_type="fp16", use_reorder=True),
      {"ivf": {"scan_buckets_count": 6, "factor": 3.0}}),
     ("ivf", "l2", dict(buckets_count=16, base_quantization_type="rabitq", use_reorder=True),

@@ -74,6 +74,7 @@ struct SearchWorkspace {
     void* exchange_arg = nullptr;
     DevBuf<float> qrot;   // RaBitQ: rotated query rows of one slice
     DevBuf<uint8_t> qcodes;   // SQ8 uniform: the queries' code records
+    DevBuf<uint64_t> keys_unique;   // buckets_per_data > 1: a query's postings folded to one per vector
     const float* ext_probe_dists = nullptr;   // centroid distances of caller-given probe lists (same duration)
     // sharded search: this rank's routed slice [probes | distances], the gathered probe lists and distances,
     // this rank's packed partial result [keys | labels] and the gathered ones
@@ -126,6 +127,7 @@ struct vb200_ivf {
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
     uint32_t max_list_len = 0;   // the longest list this index (shard) holds
+    uint32_t buckets_per_data = 1;   // every vector is stored in this many of its nearest lists (IVF buckets_per_data)
     float su_lower = 0.f, su_diff = 0.f;   // SQ8 uniform model (one bound and one range for all dimensions)
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
     DevBuf<uint32_t> tombstones;  // bitmap over inner ids: vectors removed with MARK_REMOVE
@@ -263,7 +265,7 @@ ivf_import_lists_kernel(const uint8_t* __restrict__ src_codes, const int64_t* __
 __global__ void
 ivf_place_new_kernel(const uint64_t* __restrict__ sorted_keys, uint64_t n, uint32_t nlist,
                      const uint32_t* __restrict__ new_off, const uint32_t* __restrict__ old_off,
-                     const uint32_t* __restrict__ add_off, uint32_t inner_base,
+                     const uint32_t* __restrict__ add_off, uint32_t inner_base, uint32_t per_vector,
                      uint32_t* __restrict__ dst_of_row, uint32_t* __restrict__ new_inner) {
     uint64_t s = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (s >= n) {
@@ -279,7 +281,7 @@ ivf_place_new_kernel(const uint64_t* __restrict__ sorted_keys, uint64_t n, uint3
     uint32_t old_size = old_off[list + 1] - old_off[list];
     uint32_t np = new_off[list] + old_size + static_cast<uint32_t>(s - add_off[list]);
     dst_of_row[row] = np;
-    new_inner[np] = inner_base + row;
+    new_inner[np] = inner_base + row / per_vector;   // per_vector consecutive rows are postings of one vector
 }
 
 // scale_d = diff_d / 255, mid_d = lower_d + 128 * scale_d (zero beyond dim).
@@ -313,6 +315,56 @@ fp32_place_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim
     const uint32_t pos = dst_pos[row];
     if (pos != 0xFFFFFFFFu) {
         reinterpret_cast<float*>(codes + static_cast<uint64_t>(pos) * code_stride)[d] = x[e];
+    }
+}
+
+// out[p] = x[p / per_vector]: the rows of the postings of an add with buckets_per_data > 1.
+__global__ void
+repeat_rows_kernel(const float* __restrict__ x, uint64_t postings, uint32_t dim, uint32_t per_vector,
+                   float* __restrict__ out) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e < postings * dim) {
+        out[e] = x[(e / dim) / per_vector * dim + e % dim];
+    }
+}
+
+// buckets_per_data > 1: the same vector can be found in several probed lists.  keys[q][n] hold a query's n
+// best postings ascending with the vector's inner id as payload; the first posting of every vector (its
+// smallest distance) stays, and the k best of those go out (the de-duplication of IVF::search,
+// src/algorithm/ivf/ivf.cpp:1799-1825).  One CTA per query.
+__global__ void __launch_bounds__(128)
+dedup_keys_kernel(const uint64_t* __restrict__ keys, uint32_t n, uint32_t k, uint64_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char dedup_smem[];
+    uint64_t* kq = reinterpret_cast<uint64_t*>(dedup_smem);
+    uint32_t* keep = reinterpret_cast<uint32_t*>(kq + n);
+    const uint64_t* src = keys + static_cast<uint64_t>(blockIdx.x) * n;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        kq[i] = src[i];
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint64_t key = kq[i];
+        uint32_t first = key != KEY_INF ? 1u : 0u;
+        const uint32_t id = static_cast<uint32_t>(key);
+        for (uint32_t j = 0; j < i && first != 0; ++j) {
+            if (static_cast<uint32_t>(kq[j]) == id && kq[j] != KEY_INF) {
+                first = 0;
+            }
+        }
+        keep[i] = first;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {   // n is a few hundred at most: an in-order walk keeps the ascending order
+        uint32_t w = 0;
+        uint64_t* dst = out + static_cast<uint64_t>(blockIdx.x) * k;
+        for (uint32_t i = 0; i < n && w < k; ++i) {
+            if (keep[i] != 0) {
+                dst[w++] = kq[i];
+            }
+        }
+        for (; w < k; ++w) {
+            dst[w] = KEY_INF;
+        }
     }
 }
 
@@ -2048,6 +2100,15 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
             kscan = 1;
         }
     }
+    // buckets_per_data > 1: the scan looks for that many times as many postings, duplicates of a vector are
+    // folded afterwards (IVF::search scales topk before and de-duplicates after, ivf.cpp:1722-1727, :1799-1825)
+    const uint32_t kunique = kscan;
+    if (ix->buckets_per_data > 1) {
+        VB_CHECK_ARG(static_cast<uint64_t>(kscan) * ix->buckets_per_data <= 1024,
+                     "k = %u with buckets_per_data = %u is too large (limit 1024 postings per query)", k,
+                     ix->buckets_per_data);
+        kscan *= ix->buckets_per_data;
+    }
     // queries on the device
     const float* q_dev = queries;
     if (!is_device_pointer(queries)) {
@@ -2088,6 +2149,14 @@ ivf_search_keys(vb200_ivf* ix, const float* queries, uint64_t nq, uint32_t k, ui
                                   nullptr, ws.qcodes.ptr, ix->code_stride));
     }
     VB_TRY(ivf_scan_device(ix, q_scan, nq, kscan, nprobe, ws.probes.ptr, probe_dists));
+    if (ix->buckets_per_data > 1) {
+        VB_TRY(ws.keys_unique.reserve(nq * kunique));
+        VB_LAUNCH(dedup_keys_kernel, static_cast<uint32_t>(nq), 128, kscan * (sizeof(uint64_t) + sizeof(uint32_t)),
+                  ws.keys.ptr, kscan, kunique, ws.keys_unique.ptr);
+        VB_CUDA(cudaMemcpyAsync(ws.keys.ptr, ws.keys_unique.ptr, nq * kunique * sizeof(uint64_t), cudaMemcpyDeviceToDevice,
+                                current_stream()));
+        kscan = kunique;
+    }
     const uint64_t* keys = ws.keys.ptr;
     if (rerank) {
         VB_TRY(ws.keys2.reserve(nq * k));
@@ -2217,6 +2286,7 @@ vb200_ivf_set_shard(vb200_ivf_t ix, uint32_t rank, uint32_t world) {
     if (ix->n_total != 0) {
         VB_FAIL(VB200_INDEX_NOT_EMPTY, "set_shard must precede the first add");
     }
+    VB_CHECK_ARG(world == 1 || ix->buckets_per_data == 1, "an index with buckets_per_data > 1 cannot be sharded");
     ix->shard_rank = rank;
     ix->shard_world = world;
     return 0;
@@ -2294,6 +2364,21 @@ vb200_ivf_get_sq8_model(vb200_ivf_t ix, float* lower, float* diff) {
     VB_TRY(copy_out(lower, ix->lower.ptr, ix->dim));
     VB_TRY(copy_out(diff, ix->diff.ptr, ix->dim));
     return sync_stream();
+}
+
+extern "C" int
+vb200_ivf_set_buckets_per_data(vb200_ivf_t ix, uint32_t buckets_per_data) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    VB_CHECK_ARG(buckets_per_data >= 1 && buckets_per_data <= ix->nlist && buckets_per_data <= 16,
+                 "buckets_per_data must lie in [1, min(buckets_count, 16)], got %u", buckets_per_data);
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "buckets_per_data cannot change after vectors were added");
+    }
+    VB_CHECK_ARG(buckets_per_data == 1 || ix->shard_world == 1,
+                 "buckets_per_data > 1 is not served on a sharded index (a vector's lists may live on different shards)");
+    ix->buckets_per_data = buckets_per_data;
+    return 0;
 }
 
 extern "C" int
@@ -2545,7 +2630,7 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     if (!ix->has_centroids || !ix->has_model) {
         VB_FAIL(VB200_WRONG_STATUS, "index is not trained");
     }
-    VB_CHECK_ARG(ix->n_total + count < 0xFFFFFFFFull, "index would exceed 2^32-1 vectors");
+    VB_CHECK_ARG((ix->n_total + count) * ix->buckets_per_data < 0xFFFFFFFFull, "index would exceed 2^32-1 postings");
     const uint32_t nlist = ix->nlist, dim = ix->dim;
     cudaStream_t st = current_stream();
 
@@ -2558,11 +2643,21 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
         VB_TRY(normalize_rows_f32(x.ptr, count, dim, unit_rows.ptr));
         xr = unit_rows.ptr;
     }
-    // 1. list of every row
+    // 1. list of every posting.  With buckets_per_data = b > 1 a vector is stored in its b nearest lists
+    // (IVF::Add, src/algorithm/ivf/ivf.cpp:607, :659-676): posting p = b * row + j is row's j-th nearest list,
+    // and from here on the postings are the "rows" that are sorted, placed and encoded.
+    const uint32_t per_vector = ix->buckets_per_data;
+    const uint64_t n_rows = count;            // vectors of this call
+    count *= per_vector;                      // postings of this call
+    VB_CHECK_ARG(count < 0xFFFFFFFFull, "too many postings in one add");
     DevBuf<int32_t> lab;
+    DevBuf<float> posting_rows, route_dists;
     VB_TRY(lab.reserve(count));
     if (labels_in != nullptr) {
         VB_CUDA(cudaMemcpyAsync(lab.ptr, labels_in, count * sizeof(int32_t), cudaMemcpyDefault, st));
+    } else if (per_vector > 1) {
+        VB_TRY(route_dists.reserve(count));
+        VB_TRY(ivf_route_device(ix, xr, n_rows, per_vector, lab.ptr, route_dists.ptr));
     } else {
         if (ix->metric == VB200_METRIC_L2) {
             // the k-means assignment (tensor-core candidates + exact pick when large enough)
@@ -2572,6 +2667,13 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
         } else {
             VB_TRY(dense_argmin_f32(xr, count, ix->centroids.ptr, nlist, dim, -1.0f, nullptr, lab.ptr, nullptr));
         }
+    }
+    const float* x_rows = xr;                 // one row per vector: labels, reorder rows
+    if (per_vector > 1) {
+        VB_TRY(posting_rows.reserve(count * dim));
+        VB_LAUNCH(repeat_rows_kernel, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count, dim, per_vector,
+                  posting_rows.ptr);
+        xr = posting_rows.ptr;
     }
     // 2. sort rows by (list, row)
     DevBuf<uint64_t> keys, sorted;
@@ -2635,7 +2737,7 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     }
     VB_LAUNCH(ivf_place_new_kernel, static_cast<uint32_t>((count + 255) / 256), 256, 0, sorted.ptr, count,
               nlist, new_off_dev.ptr, ix->list_off.ptr, add_off_dev.ptr,
-              static_cast<uint32_t>(ix->n_total), dst_of_row.ptr, new_inner.ptr);
+              static_cast<uint32_t>(ix->n_total), per_vector, dst_of_row.ptr, new_inner.ptr);
     // 5. encode the new rows in place
     if (ix->quant == VB200_QUANT_SQ8) {
         VB_TRY(sq8_encode_device(xr, count, dim, ix->lower.ptr, ix->diff.ptr, dst_of_row.ptr,
@@ -2657,9 +2759,9 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
                                     dst_of_row.ptr, new_codes.ptr, stride));
     }
     // 6. labels and (for reorder) the fp32 rows, by inner id; tombstone words for the new ids
-    VB_TRY(ivf_append_row_data(ix, ids, xr, count));
+    VB_TRY(ivf_append_row_data(ix, ids, x_rows, n_rows));
     // 7. per-list derived data, then commit
-    return ivf_commit_lists(ix, new_codes, new_inner, new_off_dev, new_off, n_new_stored, ix->n_total + count);
+    return ivf_commit_lists(ix, new_codes, new_inner, new_off_dev, new_off, n_new_stored, ix->n_total + n_rows);
 }
 
 extern "C" int

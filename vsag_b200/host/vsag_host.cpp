@@ -553,7 +553,9 @@ public:
         kmeans_iters_ = train_type == "kmeans" ? 25 : 0;  // IVFNearestPartition::Train hard-codes 25
         check_argument(get_string(p, "partition_strategy_type", "ivf") == "ivf",
                        "partition_strategy_type must be ivf for the GPU engine (gno_imi is out of scope)");
-        check_argument(get_int(p, "buckets_per_data", 1) == 1, "buckets_per_data must be 1 for the GPU engine");
+        buckets_per_data_ = get_int(p, "buckets_per_data", 1);
+        check_argument(buckets_per_data_ >= 1 && buckets_per_data_ <= std::min<int64_t>(nlist_, 16),
+                       "buckets_per_data must lie in [1, min(buckets_count, 16)]");
         check_argument(get_int(p, "thread_count", 1) >= 1, "thread_count must be positive");
         check_argument(!get_bool(p, "use_residual", false), "use_residual is not served by the GPU engine");
         check_argument(!get_bool(p, "use_attribute_filter", false),
@@ -569,6 +571,9 @@ public:
         train_sample_count_ = get_int(p, "train_sample_count", def_sample);
         check_argument(train_sample_count_ >= 512, "train_sample_count must be at least 512");
         check_status(vb200_ivf_create(dim_, metric_, nlist_, quant_, use_reorder_ ? 1 : 0, &handle_));
+        if (buckets_per_data_ > 1) {
+            check_status(vb200_ivf_set_buckets_per_data(handle_, static_cast<uint32_t>(buckets_per_data_)));
+        }
         if (quant_ == VB200_QUANT_RABITQ) {
             rotation_ = random_rotation(dim_, 47);
             check_status(vb200_ivf_set_rabitq_rotation(handle_, rotation_.data()));
@@ -1026,7 +1031,9 @@ private:
 
     FileHeader
     file_header() const {
-        return FileHeader{FILE_KIND_IVF, dim_, nlist_, use_reorder_ ? 1u : 0u, metric_, quant_};
+        // the flag word also carries buckets_per_data, so that a file is only loaded into an index created alike
+        return FileHeader{FILE_KIND_IVF, dim_, nlist_, (use_reorder_ ? 1u : 0u) | (static_cast<uint32_t>(buckets_per_data_ - 1) << 8),
+                          metric_, quant_};
     }
 
     std::vector<int64_t> labels_host_;     // ids in insertion order, for callback filters
@@ -1035,6 +1042,7 @@ private:
 
     uint32_t dim_;
     int metric_;
+    int64_t buckets_per_data_ = 1;
     static constexpr uint32_t KMEANS_SEED = 47;
     uint32_t nlist_ = 10;
     int quant_ = VB200_QUANT_SQ8;
