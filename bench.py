@@ -137,6 +137,10 @@ class ClockSampler:
             time.sleep(0.01)
         self.t_begin = time.time()
 
+    def begin(self) -> None:
+        """Marks the start of the timed region (start() ran before the warm-up)."""
+        self.t_begin = time.time()
+
     def _pump(self) -> None:
         assert self.proc is not None and self.proc.stdout is not None
         for line in self.proc.stdout:
@@ -469,13 +473,13 @@ def run_ivf_sq8(args, ctx: Ctx) -> dict:
             # all-gathered over NVLink and merged locally
             sharded.search(queries, np_, 2.0, out_ids, out_d)
 
+    sampler = ClockSampler(ctx.local_rank)
+    if rank == 0:
+        sampler.start()              # before the warm-up: its start-up must not fall into the timed region
     for _ in range(args.warmup):
         step_device()
     torch.cuda.synchronize()
-
-    sampler = ClockSampler(ctx.local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler.begin()
     launches0 = engine.kernel_launches()
     torch.cuda.nvtx.range_push("timed_steps")   # lets a profiler pick out the timed region
     total_ms = ctx.timed(step_device, args.steps)
@@ -663,11 +667,12 @@ def run_kmeans(args, ctx: Ctx, steps: int, warmup: int) -> dict:
     x = centres[torch.randint(0, k, (n,), generator=g, device=device)]
     x = (x + 0.1 * torch.randn((n, dim), generator=g, device=device)).contiguous()
     seeds = x[:k].clone()
-    engine.kmeans_train(x, seeds, warmup)                      # warm-up iterations
-    launches0 = engine.kernel_launches()
     sampler = ClockSampler(ctx.local_rank)
     if rank == 0:
         sampler.start()
+    engine.kmeans_train(x, seeds, warmup)                      # warm-up iterations
+    launches0 = engine.kernel_launches()
+    sampler.begin()
     torch.cuda.nvtx.range_push("timed_steps")
     ms = ctx.timed(lambda: engine.kmeans_train(x, seeds, steps), 1) / steps
     torch.cuda.nvtx.range_pop()
@@ -755,12 +760,13 @@ def run_bruteforce(args, ctx: Ctx, steps: int, warmup: int) -> dict:
             # one C-ABI call: this rank's rows, an all-gather of the packed per-rank top-k, the merge
             ix.search_sharded(comm, queries, k, out=(ids, dists))
 
-    for _ in range(warmup):
-        step()
-    launches0 = engine.kernel_launches()
     sampler = ClockSampler(ctx.local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(warmup):
+        step()
+    launches0 = engine.kernel_launches()
+    sampler.begin()
     torch.cuda.nvtx.range_push("timed_steps")
     ms = ctx.timed(step, steps) / steps
     torch.cuda.nvtx.range_pop()
@@ -886,11 +892,12 @@ def run_rabitq(args, ctx: Ctx, steps: int, warmup: int) -> dict:
     def step(queries=q, ids=out_ids, dists=out_d):
         ix.search(queries, k, nprobe, factor=factor, out=(ids, dists))
 
+    sampler = ClockSampler(ctx.local_rank)
+    sampler.start()
     for _ in range(warmup):
         step()
     launches0 = engine.kernel_launches()
-    sampler = ClockSampler(ctx.local_rank)
-    sampler.start()
+    sampler.begin()
     torch.cuda.nvtx.range_push("timed_steps")
     ms = ctx.timed(step, steps) / steps
     torch.cuda.nvtx.range_pop()
