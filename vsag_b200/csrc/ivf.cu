@@ -1834,7 +1834,11 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     // covering balls tile by tile as the SIMT kernel does: with list pruning on, the pairs of the second
     // phase have just been tested against the bounds of the first (pair_drop_kernel), which are close to
     // final, and a first phase has no bounds to test against.
-    const bool tc_first = tc_scan, tc_second = tc_scan;
+    // A first phase that runs alone (pruning on) is a few thousand items of one or two queries: 32-query tiles
+    // are nearly empty there and the SIMT kernel's single-query body is the faster one; VB200_TC_FIRST=1 keeps it
+    // on the tensor cores (for comparisons).
+    static const bool tc_first_forced = std::getenv("VB200_TC_FIRST") != nullptr && std::getenv("VB200_TC_FIRST")[0] == '1';
+    const bool tc_first = tc_scan && (!(split_phases && pruning) || tc_first_forced), tc_second = tc_scan;
     const uint32_t qt_first = tc_first ? TCS_QT : static_cast<uint32_t>(qt);
     const uint32_t qt_second = tc_second ? TCS_QT : static_cast<uint32_t>(qt);
     VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr, qt_first));
