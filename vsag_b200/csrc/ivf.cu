@@ -977,55 +977,88 @@ pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const
     const uint32_t* __restrict__ pair_cnt = blockIdx.x == 0 ? tables.cnt[0] : tables.cnt[1];
     uint32_t* __restrict__ pair_off = blockIdx.x == 0 ? tables.off[0] : tables.off[1];
     uint32_t* __restrict__ item_off = blockIdx.x == 0 ? tables.item_off[0] : tables.item_off[1];
-    __shared__ uint32_t s_pairs[1024];
-    __shared__ uint32_t s_items[1024];
+    __shared__ uint32_t s_pairs[33], s_items[33];   // exclusive prefixes of the warps' chunks, totals in [32]
     __shared__ unsigned long long s_bytes;
     if (threadIdx.x == 0) {
         s_bytes = 0;
     }
-    // every thread owns a run of consecutive positions: sums of the run, one block scan, then the
-    // run is walked again from its exclusive prefix
-    const uint32_t per = (nlist + 1023) / 1024;
-    const uint32_t p0 = threadIdx.x * per;
-    const uint32_t p1 = p0 + per < nlist ? p0 + per : nlist;
+    __syncthreads();
+    // A warp owns a contiguous chunk of positions and walks it 32 at a time, so the loads of `order` are
+    // coalesced and the gathers behind them independent: sums of the chunks, one scan over the 32 warps,
+    // then the chunk is walked again with a warp scan per round.
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t per_warp = ((nlist + 31) / 32 + 31) / 32 * 32;
+    const uint32_t w0 = warp * per_warp < nlist ? warp * per_warp : nlist;
+    const uint32_t w1 = w0 + per_warp < nlist ? w0 + per_warp : nlist;
     uint32_t sum_p = 0, sum_t = 0;
     unsigned long long my_bytes = 0;
-    for (uint32_t pos = p0; pos < p1; ++pos) {
-        const uint32_t l = order[pos];
-        const uint32_t c = pair_cnt[l];
-        sum_p += c;
-        sum_t += (c + qt - 1) / qt;
-        my_bytes += static_cast<unsigned long long>(c) * (list_off[l + 1] - list_off[l]) * code_size;
-    }
-    s_pairs[threadIdx.x] = sum_p;
-    s_items[threadIdx.x] = sum_t;
-    __syncthreads();
-    for (uint32_t off = 1; off < 1024; off <<= 1) {  // Hillis-Steele inclusive scan
-        uint32_t vp = 0, vi = 0;
-        if (threadIdx.x >= off) {
-            vp = s_pairs[threadIdx.x - off];
-            vi = s_items[threadIdx.x - off];
+#pragma unroll 4
+    for (uint32_t base = w0; base < w1; base += 32) {
+        const uint32_t pos = base + lane;
+        if (pos < w1) {
+            const uint32_t l = __ldg(order + pos);
+            const uint32_t c = pair_cnt[l];
+            sum_p += c;
+            sum_t += (c + qt - 1) / qt;
+            my_bytes += static_cast<unsigned long long>(c) * (__ldg(list_off + l + 1) - __ldg(list_off + l)) * code_size;
         }
-        __syncthreads();
-        s_pairs[threadIdx.x] += vp;
-        s_items[threadIdx.x] += vi;
-        __syncthreads();
     }
-    uint32_t run_p = s_pairs[threadIdx.x] - sum_p, run_t = s_items[threadIdx.x] - sum_t;
-    for (uint32_t pos = p0; pos < p1; ++pos) {
-        const uint32_t l = order[pos];
-        const uint32_t c = pair_cnt[l];
-        const uint32_t t = (c + qt - 1) / qt;
-        pair_off[l] = run_p;
-        item_off[pos] = run_t;
-        run_p += c;
-        run_t += t;
+    for (int off = 16; off > 0; off >>= 1) {
+        sum_p += __shfl_xor_sync(0xffffffffu, sum_p, off);
+        sum_t += __shfl_xor_sync(0xffffffffu, sum_t, off);
+        my_bytes += __shfl_xor_sync(0xffffffffu, my_bytes, off);
     }
-    atomicAdd(&s_bytes, my_bytes);
+    if (lane == 0) {
+        s_pairs[warp] = sum_p;
+        s_items[warp] = sum_t;
+        atomicAdd(&s_bytes, my_bytes);
+    }
     __syncthreads();
+    if (warp == 0) {
+        uint32_t vp = s_pairs[lane], vt = s_items[lane];
+        uint32_t ip = vp, it = vt;
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, ip, off), ut = __shfl_up_sync(0xffffffffu, it, off);
+            if (lane >= static_cast<uint32_t>(off)) {
+                ip += up;
+                it += ut;
+            }
+        }
+        s_pairs[lane] = ip - vp;
+        s_items[lane] = it - vt;
+        if (lane == 31) {
+            s_pairs[32] = ip;
+            s_items[32] = it;
+        }
+    }
+    __syncthreads();
+    uint32_t run_p = s_pairs[warp], run_t = s_items[warp];
+    for (uint32_t base = w0; base < w1; base += 32) {
+        const uint32_t pos = base + lane;
+        uint32_t l = 0, c = 0;
+        if (pos < w1) {
+            l = __ldg(order + pos);
+            c = pair_cnt[l];
+        }
+        const uint32_t t = (c + qt - 1) / qt;
+        uint32_t ip = c, it = t;
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, ip, off), ut = __shfl_up_sync(0xffffffffu, it, off);
+            if (lane >= static_cast<uint32_t>(off)) {
+                ip += up;
+                it += ut;
+            }
+        }
+        if (pos < w1) {
+            pair_off[l] = run_p + ip - c;
+            item_off[pos] = run_t + it - t;
+        }
+        run_p += __shfl_sync(0xffffffffu, ip, 31);
+        run_t += __shfl_sync(0xffffffffu, it, 31);
+    }
     if (threadIdx.x == 0) {
-        pair_off[nlist] = s_pairs[1023];
-        item_off[nlist] = s_items[1023];
+        pair_off[nlist] = s_pairs[32];
+        item_off[nlist] = s_items[32];
         atomicAdd(reinterpret_cast<unsigned long long*>(scalars), s_bytes);  // logical scan volume, both phases
     }
 }
