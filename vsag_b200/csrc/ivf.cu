@@ -3275,7 +3275,7 @@ vb200_ivf_search_sharded(vb200_ivf_t ix, vb200_comm_t comm, const float* queries
     const uint32_t world = static_cast<uint32_t>(comm->world), rank = static_cast<uint32_t>(comm->rank);
     const uint64_t total = nq * k;
     // VB200_SHARD_PROFILE=1: device time of the step's sections from CUDA events, averaged and printed to
-    // stderr every 20 calls (rank 0 and the last rank)
+    // stderr every 20 calls after the first three (rank 0 and the last rank)
     static const bool profile = std::getenv("VB200_SHARD_PROFILE") != nullptr && std::getenv("VB200_SHARD_PROFILE")[0] == '1';
     static cudaEvent_t ev[6];
     static double acc_ms[5] = {0, 0, 0, 0, 0};
@@ -3363,7 +3363,8 @@ vb200_ivf_search_sharded(vb200_ivf_t ix, vb200_comm_t comm, const float* queries
     uint64_t scalars[5] = {0, 0, 0, 0, 0};
     VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, st));
     VB_TRY(sync_stream());
-    if (profile) {
+    static int n_calls = 0;
+    if (profile && ++n_calls > 3) {   // the first three calls are a caller's warm-up
         for (int i = 0; i < 5; ++i) {
             float ms = 0.f;
             cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
