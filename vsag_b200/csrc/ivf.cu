@@ -1396,7 +1396,7 @@ route_threshold_kernel(const float* __restrict__ scores, uint32_t sample, uint32
     mx = route_block_max(mx, red);
     float bound = mx;   // everything, when the scores do not spread (or there are fewer than ncand of them)
     if (mx > mn && mx < INFINITY && mn > -INFINITY) {
-        // round 1: bins over [mn, mx]
+        // first pass: bins over [mn, mx]
         hist[tid] = 0;
         __syncthreads();
         const float scale1 = 255.0f / (mx - mn);
@@ -1412,7 +1412,7 @@ route_threshold_kernel(const float* __restrict__ scores, uint32_t sample, uint32
         }
         route_find_bin(hist, ncand, &s_bin, &s_rank);
         const uint32_t b1 = s_bin, rank2 = s_rank;
-        // round 2: the scores of bin b1 alone, over their own range
+        // second pass: the scores of bin b1 alone, over their own range
         float mn2 = INFINITY, mx2 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < ROUTE_THR_PER_THREAD; ++i) {
