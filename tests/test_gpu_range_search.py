@@ -109,3 +109,30 @@ def test_with_filter_functions_keep_valid_ids_only(oracle, name, index_param, se
         assert set(rng_i.tolist()) == set(kept_ids[truth_i[qi][:25]].tolist())
         few_i, few_d = index.range_search_with_filter(queries[qi], radius, 4, sp, valid)
         assert np.array_equal(few_d, truth_d[qi][:4])
+
+
+@pytest.mark.parametrize("name,index_param,search", [
+    ("brute_force", dict(base_quantization_type="fp32"), {}),
+    ("ivf", dict(buckets_count=12, base_quantization_type="fp32"), {"ivf": {"scan_buckets_count": 12}}),
+])
+def test_k_beyond_one_search_is_fetched_in_pages(oracle, name, index_param, search):
+    """The engine returns at most a few hundred neighbours per search; a larger k is served in pages of 512
+    (the found vectors join the deny bitmap of the next page), as the reference serves any k."""
+    from vsag_b200.index import Index
+
+    n, dim, k = 3000, 32, 1300
+    base = mixture(21, n, dim, 12, 0.1)
+    queries = mixture(22, 3, dim, 12, 0.1)
+    ids = np.arange(n, dtype=np.int64) + 50
+    index = Index(name, params(dim, **index_param))
+    index.build(base, ids, n, dim)
+    sp = json.dumps(search)
+    want_i, want_d = oracle.bf_search_fp32(base, queries, k)
+    got_i, got_d = index.knn_search_batch(queries, k, sp)
+    assert np.array_equal(got_d, want_d)
+    for q in range(len(queries)):
+        assert len(set(got_i[q].tolist())) == k
+        assert set(got_i[q].tolist()) == set((want_i[q] + 50).tolist())
+    one_i, one_d = index.knn_search(queries[0], n + 10, sp)          # more than the index holds: all of it, once
+    assert len(one_i) == n and len(set(one_i.tolist())) == n
+    assert np.array_equal(one_d, oracle.bf_search_fp32(base, queries[:1], n)[1][0])

@@ -127,6 +127,7 @@ struct vb200_ivf {
     DevBuf<uint32_t> list_off;
     std::vector<uint32_t> list_off_host;
     uint32_t max_list_len = 0;   // the longest list this index (shard) holds
+    bool balls_valid = false;    // the covering balls describe the lists as they are stored
     uint32_t buckets_per_data = 1;   // every vector is stored in this many of its nearest lists (IVF buckets_per_data)
     float su_lower = 0.f, su_diff = 0.f;   // SQ8 uniform model (one bound and one range for all dimensions)
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
@@ -478,7 +479,8 @@ sq8_row_dist(const uint8_t* __restrict__ row, uint32_t dim, const float* __restr
 
 __global__ void __launch_bounds__(128)
 sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, uint32_t dim,
-                      const uint32_t* __restrict__ list_off, const float* __restrict__ lower,
+                      const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ old_off,
+                      const float* __restrict__ lower,
                       const float* __restrict__ diff, const float* __restrict__ centroids,
                       float* __restrict__ ball_centre, float* __restrict__ ball_radius,
                       uint32_t* __restrict__ ball_count, float* __restrict__ list_radius) {
@@ -490,6 +492,9 @@ sq8_list_balls_kernel(const uint8_t* __restrict__ codes, uint32_t code_stride, u
     __shared__ uint32_t rmax[SQ8_BALLS];
     const uint32_t l = blockIdx.x, tid = threadIdx.x;
     const uint32_t beg = list_off[l], len = list_off[l + 1] - beg;
+    if (old_off != nullptr && len == old_off[l + 1] - old_off[l]) {
+        return;   // rows are only ever appended: a list of unchanged length keeps the balls it has
+    }
     float* out_c = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
     float* out_r = ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS;
     // three balls for an ordinary list, one more per 300 rows beyond 900, eight at most: the long
@@ -2608,9 +2613,12 @@ ivf_commit_lists(vb200_ivf* ix, DevBuf<uint8_t>& new_codes, DevBuf<uint32_t>& ne
             VB_CUDA(cudaFuncSetAttribute(sq8_list_balls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(balls_smem)));
         }
-        VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr,
+        // only the lists that grew get new balls (an add of a few rows must not cost a pass over the index)
+        const uint32_t* old_off = ix->balls_valid ? ix->list_off.ptr : nullptr;
+        VB_LAUNCH(sq8_list_balls_kernel, nlist, 128, balls_smem, new_codes.ptr, stride, dim, new_off_dev.ptr, old_off,
                   ix->lower.ptr, ix->diff.ptr, ix->centroids.ptr, ix->ball_centre.ptr, ix->ball_radius.ptr,
                   ix->ball_count.ptr, ix->list_radius.ptr);
+        ix->balls_valid = true;
     }
     DevBuf<int8_t> new_tiled;
     DevBuf<uint32_t> new_group_off;

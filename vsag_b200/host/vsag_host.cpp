@@ -415,6 +415,72 @@ range_over_knn(Knn&& knn, const DatasetPtr& query, int64_t n_live, float radius,
     }
 }
 
+// k beyond what one search of the engine returns (its per-query candidate buffers live in shared memory): the
+// answer is fetched in pages like an unlimited range search -- what was found joins the deny bitmap, the next
+// KNN_PAGE nearest are asked for -- one query at a time, since the bitmap belongs to a query.  `knn(one, k, f, i)`
+// searches query i alone.
+constexpr int64_t KNN_PAGE = 512;
+
+template <typename Knn>
+DatasetPtr
+knn_in_pages(Knn&& knn, const DatasetPtr& query, int64_t dim, int64_t k, const vb200_filter* filter,
+             const std::vector<int64_t>& label_of_inner) {
+    check_argument(query != nullptr, "query is null");
+    const int64_t nq = query->GetNumElements();
+    check_argument(query->GetFloat32Vectors() != nullptr, "query vectors are null");
+    std::unordered_map<int64_t, uint32_t> inner_of_label;
+    inner_of_label.reserve(label_of_inner.size());
+    for (size_t i = 0; i < label_of_inner.size(); ++i) {
+        inner_of_label.emplace(label_of_inner[i], static_cast<uint32_t>(i));
+    }
+    auto* ids = new int64_t[static_cast<size_t>(std::max<int64_t>(nq * k, 1))];
+    auto* dists = new float[static_cast<size_t>(std::max<int64_t>(nq * k, 1))];
+    std::fill(ids, ids + nq * k, int64_t{-1});
+    std::fill(dists, dists + nq * k, std::numeric_limits<float>::infinity());
+    std::string stats;
+    try {
+        for (int64_t qi = 0; qi < nq; ++qi) {
+            auto one = Dataset::Make()->NumElements(1)->Dim(dim)->Float32Vectors(query->GetFloat32Vectors() + qi * dim)->Owner(false);
+            std::vector<uint32_t> deny((label_of_inner.size() + 31) / 32, 0);
+            if (filter != nullptr && filter->deny_inner_bits != nullptr) {
+                const size_t words = std::min<size_t>(deny.size(), (filter->n_inner_bits + 31) / 32);
+                std::copy(filter->deny_inner_bits, filter->deny_inner_bits + words, deny.begin());
+            }
+            vb200_filter paged = filter != nullptr ? *filter : vb200_filter{};
+            paged.deny_inner_bits = deny.data();
+            paged.n_inner_bits = label_of_inner.size();
+            int64_t have = 0;
+            while (have < k) {
+                const int64_t want = std::min<int64_t>(KNN_PAGE, k - have);
+                Expected<DatasetPtr> page = knn(one, want, &paged, qi);
+                if (!page.has_value()) {
+                    fail(page.error().type, page.error().message);
+                }
+                const DatasetPtr& found = page.value();
+                stats = found->GetStatistics();
+                const int64_t got = found->GetDim();
+                for (int64_t j = 0; j < got; ++j) {
+                    ids[qi * k + have + j] = found->GetIds()[j];
+                    dists[qi * k + have + j] = found->GetDistances()[j];
+                    auto it = inner_of_label.find(found->GetIds()[j]);
+                    if (it != inner_of_label.end()) {
+                        deny[it->second >> 5] |= 1u << (it->second & 31);
+                    }
+                }
+                have += got;
+                if (got < want) {
+                    break;
+                }
+            }
+        }
+    } catch (...) {
+        delete[] ids;
+        delete[] dists;
+        throw;
+    }
+    return pack_result(ids, dists, nq, k, stats);
+}
+
 // A random orthogonal matrix with determinant +1, standing in for
 // RandomOrthogonalMatrix::GenerateRandomOrthogonalMatrix (src/impl/transform/
 // random_orthogonal_transformer.cpp:98-149): Gaussian entries from a seeded mt19937, then
@@ -863,6 +929,29 @@ public:
     Expected<DatasetPtr>
     knn_impl(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter,
              const std::vector<std::vector<int64_t>>* bucket_ids = nullptr) const {
+        if (k <= KNN_PAGE || query == nullptr || query->GetNumElements() == 0 || vb200_ivf_num_elements(handle_) == 0) {
+            return knn_page(query, k, parameters, filter, bucket_ids);
+        }
+        return safe_call<DatasetPtr>([&]() {
+            check_base(query, dim_, false);
+            const bool listed = bucket_ids != nullptr && !bucket_ids->empty();
+            check_argument(!listed || static_cast<int64_t>(bucket_ids->size()) == query->GetNumElements(),
+                           "bucket_ids_ size must match the number of query vectors");
+            return knn_in_pages(
+                [&](const DatasetPtr& one, int64_t kk, const vb200_filter* f, int64_t qi) {
+                    if (!listed) {
+                        return knn_page(one, kk, parameters, f, nullptr);
+                    }
+                    std::vector<std::vector<int64_t>> mine{(*bucket_ids)[static_cast<size_t>(qi)]};
+                    return knn_page(one, kk, parameters, f, &mine);
+                },
+                query, dim_, k, filter, labels_host_);
+        });
+    }
+
+    Expected<DatasetPtr>
+    knn_page(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter,
+             const std::vector<std::vector<int64_t>>* bucket_ids = nullptr) const {
         return safe_call<DatasetPtr>([&]() {
             check_argument(query != nullptr, "query is null");
             check_argument(k > 0, "k must be greater than 0");
@@ -1273,6 +1362,19 @@ public:
 
     Expected<DatasetPtr>
     knn_impl(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter) const {
+        if (k <= KNN_PAGE || query == nullptr || query->GetNumElements() == 0 || vb200_bf_num_elements(handle_) == 0) {
+            return knn_page(query, k, parameters, filter);
+        }
+        return safe_call<DatasetPtr>([&]() {
+            check_base(query, dim_, false);
+            return knn_in_pages([&](const DatasetPtr& one, int64_t kk, const vb200_filter* f, int64_t) {
+                return knn_page(one, kk, parameters, f);
+            }, query, dim_, k, filter, labels_host_);
+        });
+    }
+
+    Expected<DatasetPtr>
+    knn_page(const DatasetPtr& query, int64_t k, const std::string& parameters, const vb200_filter* filter) const {
         return safe_call<DatasetPtr>([&]() {
             check_argument(query != nullptr, "query is null");
             check_argument(k > 0, "k must be greater than 0");
