@@ -217,6 +217,13 @@ VB200_API int vb200_ivf_set_shard(vb200_ivf_t index, uint32_t rank, uint32_t wor
 VB200_API int vb200_ivf_train(vb200_ivf_t index, const float* data, uint64_t count, int kmeans_iters,
                     const float* init);
 
+/* use_residual (IVF creation parameter; sq8 buckets): lists hold the codes of x - centroid; the quantizer is
+ * trained on the residuals of the training rows (BucketDataCell::Train, src/datacell/bucket_datacell.h:593-614),
+ * a row's L2 bias -2 * IP(c, decoded) - IP(c, c) is kept beside its code (:621-651) and a distance is the
+ * quantizer's distance between the raw query and the residual code, minus the bias (L2), minus 2 * IP(q, c)
+ * (L2) or IP(q, c) (IP / cosine) (:552-566).  Choose before training.  Such an index scans without list pruning. */
+VB200_API int vb200_ivf_set_use_residual(vb200_ivf_t index, int use_residual);
+
 /* buckets_per_data (IVF creation parameter, src/algorithm/ivf/ivf.cpp:607, :659-676): every vector is stored
  * in that many of its nearest lists; a search looks for buckets_per_data times as many postings and folds the
  * duplicates of a vector into its smallest distance (:1722-1727, :1799-1825).  Set before the first add; 1 is

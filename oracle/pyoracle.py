@@ -299,6 +299,48 @@ def ivf_fp32_search(rows, list_off, inner_ids, q, probes, k: int, metric: int = 
     return ids, dists
 
 
+def residual_rows(rows, lists, centroids) -> np.ndarray:
+    """rows - centroid of each row's list (BucketDataCell::Train with use_residual)."""
+    rows, pr = _a(rows, np.float32)
+    lists, pl = _a(lists, np.int32)
+    centroids, pc = _a(centroids, np.float32)
+    out = np.empty_like(rows)
+    lib().orc_residual_rows(pr, _u64(rows.shape[0]), _u64(rows.shape[1]), pl, pc, _p(out.ctypes.data))
+    return out
+
+
+def sq8_residual_encode(rows, lists, centroids, lower, diff, metric: int = 0):
+    """use_residual encoding: (codes of rows - centroid, per-row bias for L2)."""
+    rows, pr = _a(rows, np.float32)
+    lists, pl = _a(lists, np.int32)
+    centroids, pc = _a(centroids, np.float32)
+    lower, plo = _a(lower, np.float32)
+    diff, pdf = _a(diff, np.float32)
+    codes = np.empty(rows.shape, np.uint8)
+    bias = np.empty(rows.shape[0], np.float32)
+    lib().orc_sq8_residual_encode(pr, _u64(rows.shape[0]), _u64(rows.shape[1]), pl, pc, plo, pdf, _i32(metric),
+                                  _p(codes.ctypes.data), _p(bias.ctypes.data))
+    return codes, bias
+
+
+def ivf_sq8_residual_search(codes, bias, list_off, inner_ids, lower, diff, centroids, q, probes, k: int, metric: int = 0):
+    codes, pc = _a(codes, np.uint8)
+    bias, pb = _a(bias, np.float32)
+    list_off, po = _a(list_off, np.int64)
+    inner_ids, pi = _a(inner_ids, np.int64)
+    lower, plo = _a(lower, np.float32)
+    diff, pdf = _a(diff, np.float32)
+    centroids, pce = _a(centroids, np.float32)
+    q, pq = _a(q, np.float32)
+    probes, pp = _a(probes, np.int32)
+    nq, d = q.shape
+    ids = np.empty((nq, k), np.int64)
+    dists = np.empty((nq, k), np.float32)
+    lib().orc_ivf_sq8_residual_search(pc, pb, po, pi, _u64(d), plo, pdf, pce, pq, _u64(nq), pp, _u64(probes.shape[1]),
+                                      _i64(k), _i32(metric), _p(ids.ctypes.data), _p(dists.ctypes.data))
+    return ids, dists
+
+
 def sq8u_code_size(dim: int, metric: int = 0) -> int:
     lib().orc_sq8u_code_size.restype = C.c_uint64
     return int(lib().orc_sq8u_code_size(_u64(dim), _i32(metric)))

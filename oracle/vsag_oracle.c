@@ -755,6 +755,95 @@ orc_ivf_sq8_search(const uint8_t* codes,
     }
 }
 
+/* use_residual (src/datacell/bucket_datacell.h): a bucket stores the codes of x - centroid.
+ * Encoding (encode_vector, :621-651): residual = FP32Sub(x, c); codes = EncodeOne(residual); for L2 the row's
+ * bias = -2 * IP(c, DecodeOne(codes)) - IP(c, c).  rows are the vectors as stored (normalised for cosine). */
+ORC_API void
+orc_sq8_residual_encode(const float* rows, uint64_t count, uint64_t dim, const int32_t* lists, const float* centroids,
+                        const float* lower, const float* diff, int metric, uint8_t* codes, float* bias) {
+    float* r = (float*)malloc(dim * sizeof(float));
+    float* dec = (float*)malloc(dim * sizeof(float));
+    for (uint64_t i = 0; i < count; ++i) {
+        const float* c = centroids + (uint64_t)lists[i] * dim;
+        for (uint64_t d = 0; d < dim; ++d) {
+            r[d] = rows[i * dim + d] - c[d];
+        }
+        orc_sq8_encode(r, 1, dim, lower, diff, codes + i * dim);
+        bias[i] = 0.0f;
+        if (metric == 0) {
+            orc_sq8_decode(codes + i * dim, 1, dim, lower, diff, dec);
+            bias[i] = -2 * orc_fp32_ip(c, dec, dim) - orc_fp32_ip(c, c, dim);
+        }
+    }
+    free(r);
+    free(dec);
+}
+
+/* Residual rows of a training set (BucketDataCell::Train, :593-614): x - centroid of its nearest bucket. */
+ORC_API void
+orc_residual_rows(const float* rows, uint64_t count, uint64_t dim, const int32_t* lists, const float* centroids,
+                  float* out) {
+    for (uint64_t i = 0; i < count; ++i) {
+        const float* c = centroids + (uint64_t)lists[i] * dim;
+        for (uint64_t d = 0; d < dim; ++d) {
+            out[i * dim + d] = rows[i * dim + d] - c[d];
+        }
+    }
+}
+
+/* ScanBucketById with use_residual (:526-572): the quantizer's distance between the raw query and the residual
+ * code, minus the row's bias (L2), minus 2 * IP(q, c) (L2) or IP(q, c) (IP / cosine). */
+ORC_API void
+orc_ivf_sq8_residual_search(const uint8_t* codes,
+                            const float* bias,
+                            const int64_t* list_off,
+                            const int64_t* inner_ids,
+                            uint64_t dim,
+                            const float* lower,
+                            const float* diff,
+                            const float* centroids,
+                            const float* q,
+                            uint64_t nq,
+                            const int32_t* probes,
+                            uint64_t nprobe,
+                            int64_t k,
+                            int metric,
+                            int64_t* out_ids,
+                            float* out_dists) {
+#pragma omp parallel
+    {
+        orc_heap h;
+        h.a = (orc_rec*)malloc((size_t)(k + 2) * sizeof(orc_rec));
+        h.cap = k + 2;
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t i = 0; i < (int64_t)nq; ++i) {
+            const float* qi = q + (uint64_t)i * dim;
+            h.size = 0;
+            for (uint64_t p = 0; p < nprobe; ++p) {
+                int32_t l = probes[(uint64_t)i * nprobe + p];
+                if (l < 0) {
+                    continue;
+                }
+                float ipd = orc_fp32_ip(qi, centroids + (uint64_t)l * dim, dim);
+                if (metric == 0) {
+                    ipd *= 2;
+                }
+                for (int64_t r = list_off[l]; r < list_off[l + 1]; ++r) {
+                    const uint8_t* c = codes + (uint64_t)r * dim;
+                    float d = metric == 0 ? orc_sq8_l2sqr(qi, c, lower, diff, dim) : 1.0f - orc_sq8_ip(qi, c, lower, diff, dim);
+                    if (metric == 0) {
+                        d = d - bias[r];
+                    }
+                    d -= ipd;
+                    heap_offer_strict(&h, k, d, inner_ids[r]);
+                }
+            }
+            heap_drain(&h, k, out_ids + (uint64_t)i * k, out_dists + (uint64_t)i * k);
+        }
+        free(h.a);
+    }
+}
+
 /* The same probe loop over fp32 buckets (FP32Quantizer::ComputeDistImpl,
  * src/quantization/fp32_quantizer.cpp:163-190): rows[list_off[l] .. list_off[l+1]) are the rows of
  * list l as they were added. */

@@ -87,6 +87,7 @@ SIGNATURES = {
     "vb200_bf_search_partial": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_void_p]),
     "vb200_ivf_search_ex": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_u32, c_float, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, C.POINTER(c_int)]),
+    "vb200_ivf_set_use_residual": (c_int, [c_void_p, c_int]),
     "vb200_ivf_set_buckets_per_data": (c_int, [c_void_p, c_u32]),
     "vb200_ivf_set_sq8_uniform_model": (c_int, [c_void_p, c_float, c_float]),
     "vb200_ivf_get_sq8_uniform_model": (c_int, [c_void_p, C.POINTER(c_float), C.POINTER(c_float)]),

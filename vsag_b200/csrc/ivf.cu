@@ -74,6 +74,7 @@ struct SearchWorkspace {
     void* exchange_arg = nullptr;
     DevBuf<float> qrot;   // RaBitQ: rotated query rows of one slice
     DevBuf<uint8_t> qcodes;   // SQ8 uniform: the queries' code records
+    DevBuf<float> pair_const;       // residual codes: per (query, probe) the centroid term of the distance
     DevBuf<uint64_t> keys_unique;   // buckets_per_data > 1: a query's postings folded to one per vector
     const float* ext_probe_dists = nullptr;   // centroid distances of caller-given probe lists (same duration)
     // sharded search: this rank's routed slice [probes | distances], the gathered probe lists and distances,
@@ -128,6 +129,8 @@ struct vb200_ivf {
     std::vector<uint32_t> list_off_host;
     uint32_t max_list_len = 0;   // the longest list this index (shard) holds
     bool balls_valid = false;    // the covering balls describe the lists as they are stored
+    bool use_residual = false;       // SQ8: lists hold the codes of x - centroid (IVF use_residual)
+    DevBuf<float> res_bias;          // [n_stored] L2 residual bias of every stored code (bucket_datacell.h:642-649)
     uint32_t buckets_per_data = 1;   // every vector is stored in this many of its nearest lists (IVF buckets_per_data)
     float su_lower = 0.f, su_diff = 0.f;   // SQ8 uniform model (one bound and one range for all dimensions)
     DevBuf<uint32_t> scan_order;  // list ids, longest list first: the order the scan queue walks
@@ -317,6 +320,83 @@ fp32_place_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim
     if (pos != 0xFFFFFFFFu) {
         reinterpret_cast<float*>(codes + static_cast<uint64_t>(pos) * code_stride)[d] = x[e];
     }
+}
+
+// use_residual: out[i] = x[i] - centroid of the row's list (FP32Sub, src/datacell/bucket_datacell.h:607-612, :634);
+// rows without a list (another shard's) are copied as they are and never stored.
+__global__ void
+residual_rows_kernel(const float* __restrict__ x, uint64_t count, uint32_t dim, const int32_t* __restrict__ lists,
+                     uint32_t nlist, const float* __restrict__ centroids, float* __restrict__ out) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= count * dim) {
+        return;
+    }
+    const int32_t l = lists[e / dim];
+    const float c = (l >= 0 && static_cast<uint32_t>(l) < nlist) ? centroids[static_cast<uint64_t>(l) * dim + e % dim] : 0.f;
+    out[e] = __fsub_rn(x[e], c);
+}
+
+// Residual codes, per stored position p of list l: bias[p] = -2 * IP(c_l, DecodeOne(code)) - IP(c_l, c_l) for L2
+// (encode_vector, bucket_datacell.h:642-649; DecodeOne = code / 255 * diff + lower, scalar_quantizer.cpp:112-124;
+// IP = one ascending FMA chain), and the ranking form's per-row term becomes |decoded|^2 - bias.
+__global__ void
+sq8_residual_bias_kernel(const uint8_t* __restrict__ codes, uint64_t n, uint32_t dim, uint32_t code_stride,
+                         const float* __restrict__ lower, const float* __restrict__ diff,
+                         const uint32_t* __restrict__ list_off, uint32_t nlist, const float* __restrict__ centroids,
+                         int metric, float* __restrict__ bias, float* __restrict__ code_norm) {
+    const uint64_t p = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (p >= n) {
+        return;
+    }
+    if (metric != VB200_METRIC_L2) {
+        bias[p] = 0.f;
+        return;
+    }
+    uint32_t lo = 0, hi = nlist;
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (list_off[mid] <= p) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    const float* cen = centroids + static_cast<uint64_t>(lo) * dim;
+    const uint8_t* c = codes + p * code_stride;
+    float ip_cd = 0.f, ip_cc = 0.f;
+    for (uint32_t d = 0; d < dim; ++d) {
+        const float dec = __fadd_rn(__fmul_rn(__fdiv_rn(static_cast<float>(c[d]), 255.0f), __ldg(diff + d)), __ldg(lower + d));
+        const float cv = __ldg(cen + d);
+        ip_cd = fmaf(cv, dec, ip_cd);
+        ip_cc = fmaf(cv, cv, ip_cc);
+    }
+    const float b = __fsub_rn(__fmul_rn(-2.0f, ip_cd), ip_cc);
+    bias[p] = b;
+    code_norm[p] = code_norm[p] - b;
+}
+
+// pair_const[e] for pair e = (query, probe): -2 <q, c_l> (L2) or -<q, c_l> (IP), the centroid term of a distance
+// over residual codes; used for ranking only (the exact re-scoring recomputes it in the reference's order).
+__global__ void
+pair_const_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, uint32_t nlist,
+                  const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids, int metric,
+                  float* __restrict__ pair_const) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= total) {
+        return;
+    }
+    const int32_t l = probes[e];
+    float v = 0.f;
+    if (l >= 0 && static_cast<uint32_t>(l) < nlist) {
+        const float* q = queries + (e / nprobe) * dim;
+        const float* c = centroids + static_cast<uint64_t>(l) * dim;
+        float ip = 0.f;
+        for (uint32_t d = 0; d < dim; ++d) {
+            ip = fmaf(__ldg(q + d), __ldg(c + d), ip);
+        }
+        v = metric == VB200_METRIC_L2 ? -2.0f * ip : -ip;
+    }
+    pair_const[e] = v;
 }
 
 // out[p] = x[p / per_vector]: the rows of the postings of an add with buckets_per_data > 1.
@@ -1862,9 +1942,9 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     };
     // SQ8 with list pruning: the first phase runs alone, then the pairs its bounds rule out are
     // dropped before the second phase is grouped, so they never become work items.
-    const bool pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
+    const bool pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr && !ix->use_residual;
     const uint32_t scan_cap = next_pow2(kscan + SCAN_THREADS);
-    const bool tc_scan = sq8 && tensor_cores_enabled() && ix->codes_t.ptr != nullptr && ix->kchunks > 0 &&
+    const bool tc_scan = sq8 && !ix->use_residual && tensor_cores_enabled() && ix->codes_t.ptr != nullptr && ix->kchunks > 0 &&
                          tcs_buffer_cap(kscan) <= 32 * TCS_SELECT_MAX &&
                          tcs_smem_bytes(ix->kchunks, tcs_buffer_cap(kscan), 2) + 4096 <= 227 * 1024;
     const bool split_phases = n_phases == 2 && (ws.exchange != nullptr || pruning);
@@ -1904,7 +1984,14 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.su_lower = ix->su_lower;
     p.su_rate = static_cast<float>((static_cast<double>(ix->su_diff) / 255.0) * (static_cast<double>(ix->su_diff) / 255.0));
     p.metric = ix->metric;
-    ws.pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr;
+    ws.pruning = sq8 && ix->prune_lists && ix->ball_radius.ptr != nullptr && !ix->use_residual;
+    if (sq8 && ix->use_residual) {
+        // the covering balls describe decoded residuals, not vectors: no list pruning, SIMT scan only
+        VB_TRY(ws.pair_const.reserve(total));
+        VB_LAUNCH(pair_const_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, probes_dev, total, nprobe, nlist, q_dev,
+                  ix->dim, ix->centroids.ptr, ix->metric, ws.pair_const.ptr);
+        p.pair_const = ws.pair_const.ptr;
+    }
     if (ws.pruning) {
         p.ball_centre = ix->ball_centre.ptr;
         p.ball_radius = ix->ball_radius.ptr;
@@ -2103,7 +2190,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         uint32_t n2 = next_pow2(kscan < 2 ? 2 : kscan);
         VB_LAUNCH(sq8_rescore_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev, ix->dim,
                   ix->codes.ptr, ix->code_stride, ix->lower.ptr, ix->diff.ptr, ws.merged.ptr, kscan, n2,
-                  kfinal, ix->metric, ws.keys.ptr);
+                  kfinal, ix->metric, ws.keys.ptr, ix->use_residual ? ix->res_bias.ptr : static_cast<const float*>(nullptr),
+                  ix->centroids.ptr, ix->list_off.ptr, nlist);
     } else {
         VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.keys.ptr));
     }
@@ -2409,6 +2497,19 @@ vb200_ivf_get_sq8_model(vb200_ivf_t ix, float* lower, float* diff) {
 }
 
 extern "C" int
+vb200_ivf_set_use_residual(vb200_ivf_t ix, int use_residual) {
+    VB_CHECK_ARG(ix != nullptr, "null index");
+    VB_CHECK_ARG(use_residual == 0 || ix->quant == VB200_QUANT_SQ8,
+                 "use_residual is served for sq8 buckets only");
+    std::lock_guard<std::mutex> lock(ix->mu);
+    if (ix->n_total != 0 || (ix->quant == VB200_QUANT_SQ8 && ix->has_model && (use_residual != 0) != ix->use_residual)) {
+        VB_FAIL(VB200_INDEX_NOT_EMPTY, "use_residual must be chosen before the quantizer is trained");
+    }
+    ix->use_residual = use_residual != 0;
+    return 0;
+}
+
+extern "C" int
 vb200_ivf_set_buckets_per_data(vb200_ivf_t ix, uint32_t buckets_per_data) {
     VB_CHECK_ARG(ix != nullptr, "null index");
     VB_CHECK_ARG(buckets_per_data >= 1 && buckets_per_data <= ix->nlist && buckets_per_data <= 16,
@@ -2535,6 +2636,23 @@ vb200_ivf_train(vb200_ivf_t ix, const float* data, uint64_t count, int kmeans_it
         }
     }
     VB_TRY(ivf_refresh_centroid_norms(ix));
+    DevBuf<float> residuals;
+    if (ix->quant == VB200_QUANT_SQ8 && ix->use_residual) {
+        // BucketDataCell::Train (src/datacell/bucket_datacell.h:593-614): the quantizer learns from the rows minus
+        // the centroid of their nearest bucket
+        VB_TRY(lab.reserve(count));
+        if (ix->metric == VB200_METRIC_L2) {
+            ix->kws.forget_points();
+            VB_TRY(kmeans_assign_device(ix->kws, x_model, count, ix->dim, ix->centroids.ptr, ix->nlist, lab.ptr, nullptr));
+            ix->kws.forget_points();
+        } else {
+            VB_TRY(dense_argmin_f32(x_model, count, ix->centroids.ptr, ix->nlist, ix->dim, -1.0f, nullptr, lab.ptr, nullptr));
+        }
+        VB_TRY(residuals.reserve(count * ix->dim));
+        VB_LAUNCH(residual_rows_kernel, static_cast<uint32_t>((count * ix->dim + 255) / 256), 256, 0, x_model, count, ix->dim,
+                  lab.ptr, ix->nlist, ix->centroids.ptr, residuals.ptr);
+        x_model = residuals.ptr;
+    }
     if (ix->quant == VB200_QUANT_SQ8) {
         DevBuf<float> model;
         VB_TRY(model.reserve(2 * static_cast<size_t>(ix->dim)));
@@ -2601,6 +2719,12 @@ ivf_commit_lists(vb200_ivf* ix, DevBuf<uint8_t>& new_codes, DevBuf<uint32_t>& ne
         VB_TRY(new_norm.reserve(n_new_stored));
         VB_LAUNCH(sq8_code_norm_kernel, static_cast<uint32_t>((n_new_stored + 127) / 128), 128, 0,
                   new_codes.ptr, n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_norm.ptr);
+        if (ix->use_residual) {
+            VB_TRY(ix->res_bias.reserve(n_new_stored));
+            VB_LAUNCH(sq8_residual_bias_kernel, static_cast<uint32_t>((n_new_stored + 127) / 128), 128, 0, new_codes.ptr,
+                      n_new_stored, dim, stride, ix->lower.ptr, ix->diff.ptr, new_off_dev.ptr, nlist, ix->centroids.ptr,
+                      ix->metric, ix->res_bias.ptr, new_norm.ptr);
+        }
     }
     if (ix->quant == VB200_QUANT_SQ8) {
         VB_TRY(ix->ball_centre.reserve(static_cast<size_t>(nlist) * SQ8_BALLS * dim));
@@ -2785,8 +2909,17 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
               static_cast<uint32_t>(ix->n_total), per_vector, dst_of_row.ptr, new_inner.ptr);
     // 5. encode the new rows in place
     if (ix->quant == VB200_QUANT_SQ8) {
-        VB_TRY(sq8_encode_device(xr, count, dim, ix->lower.ptr, ix->diff.ptr, dst_of_row.ptr,
+        DevBuf<float> residuals;
+        const float* to_encode = xr;
+        if (ix->use_residual) {
+            VB_TRY(residuals.reserve(count * dim));
+            VB_LAUNCH(residual_rows_kernel, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count, dim, lab.ptr,
+                      nlist, ix->centroids.ptr, residuals.ptr);
+            to_encode = residuals.ptr;
+        }
+        VB_TRY(sq8_encode_device(to_encode, count, dim, ix->lower.ptr, ix->diff.ptr, dst_of_row.ptr,
                                  new_codes.ptr, stride));
+        VB_TRY(sync_stream());   // `residuals` ends with this scope
     } else if (ix->quant == VB200_QUANT_FP32) {
         VB_LAUNCH(fp32_place_rows_kernel, static_cast<uint32_t>((count * dim + 255) / 256), 256, 0, xr, count, dim,
                   dst_of_row.ptr, new_codes.ptr, stride);

@@ -75,6 +75,7 @@ struct ScanParams {
     float coef_b;                // SQ8: distance = qa + coef_b * |x|^2 + coef_c * dot
     float coef_c;
     float inv_sqrt_d;            // RaBitQ
+    const float* pair_const;     // SQ8 with residual codes: [nq x nprobe] per-(query, list) term of the distance, by slot
     const uint8_t* qcodes;       // SQ8 uniform: [nq x qcode_stride] the queries' own code records
     uint32_t qcode_stride;
     float su_lower;              // SQ8 uniform: lower bound and (diff / 255)^2
@@ -584,7 +585,7 @@ ivf_sq8_scan_kernel(const ScanParams p) {
                 uint32_t q = it.pair_q[pbeg + qi];
                 ts.qidx[qi] = q;
                 ts.slot[qi] = it.pair_slot[pbeg + qi];
-                ts.qa[qi] = __ldg(p.qa + q);
+                ts.qa[qi] = __ldg(p.qa + q) + (p.pair_const != nullptr ? __ldg(p.pair_const + ts.slot[qi]) : 0.f);
                 ts.set_bound(qi, p.thr_g[q]);
             } else {
                 ts.qidx[qi] = 0;
@@ -666,7 +667,8 @@ __global__ void __launch_bounds__(128)
 sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_t* __restrict__ codes,
                    uint32_t code_stride, const float* __restrict__ lower, const float* __restrict__ diff,
                    const uint64_t* __restrict__ cand, uint32_t ncand, uint32_t n2, uint32_t k, int metric,
-                   uint64_t* __restrict__ out) {
+                   uint64_t* __restrict__ out, const float* __restrict__ res_bias, const float* __restrict__ centroids,
+                   const uint32_t* __restrict__ list_off, uint32_t nlist) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
     const float* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
@@ -689,6 +691,29 @@ sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_
             }
             if (metric != VB200_METRIC_L2) {
                 s = __fsub_rn(1.0f, s);
+            }
+            if (res_bias != nullptr) {
+                // residual codes (BucketDataCell::ScanBucketById, src/datacell/bucket_datacell.h:552-566): the
+                // row's bias leaves first (L2), then 2 * IP(q, centroid) (L2) or IP(q, centroid) (IP)
+                uint32_t lo = 0, hi = nlist;   // the list that holds pos
+                while (hi - lo > 1) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if (__ldg(list_off + mid) <= pos) {
+                        lo = mid;
+                    } else {
+                        hi = mid;
+                    }
+                }
+                const float* cen = centroids + static_cast<uint64_t>(lo) * dim;
+                float ipd = 0.f;
+                for (uint32_t d = 0; d < dim; ++d) {
+                    ipd = fmaf(__ldg(q + d), __ldg(cen + d), ipd);
+                }
+                if (metric == VB200_METRIC_L2) {
+                    ipd = __fmul_rn(ipd, 2.0f);
+                    s = __fsub_rn(s, __ldg(res_bias + pos));
+                }
+                s = __fsub_rn(s, ipd);
             }
             key = make_key(s, pos);
         }

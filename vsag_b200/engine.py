@@ -191,6 +191,9 @@ class IvfHandle:
             return (self.dim + align - 1) // align * align + align
         return self.dim * 4 if self.quant == QUANT_FP32 else rabitq_code_size(self.dim)
 
+    def set_use_residual(self, on: bool = True) -> None:
+        check(self._lib.vb200_ivf_set_use_residual(self._h, int(bool(on))))
+
     def set_buckets_per_data(self, b: int) -> None:
         check(self._lib.vb200_ivf_set_buckets_per_data(self._h, int(b)))
 

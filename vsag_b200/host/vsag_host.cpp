@@ -623,7 +623,9 @@ public:
         check_argument(buckets_per_data_ >= 1 && buckets_per_data_ <= std::min<int64_t>(nlist_, 16),
                        "buckets_per_data must lie in [1, min(buckets_count, 16)]");
         check_argument(get_int(p, "thread_count", 1) >= 1, "thread_count must be positive");
-        check_argument(!get_bool(p, "use_residual", false), "use_residual is not served by the GPU engine");
+        use_residual_ = get_bool(p, "use_residual", false);
+        check_argument(!use_residual_ || quant_ == VB200_QUANT_SQ8,
+                       "use_residual is served by the GPU engine for sq8 buckets only");
         check_argument(!get_bool(p, "use_attribute_filter", false),
                        "use_attribute_filter is not served by the GPU engine");
         check_argument(get_int(p, "rabitq_bits_per_dim_query", 32) == 32 &&
@@ -639,6 +641,9 @@ public:
         check_status(vb200_ivf_create(dim_, metric_, nlist_, quant_, use_reorder_ ? 1 : 0, &handle_));
         if (buckets_per_data_ > 1) {
             check_status(vb200_ivf_set_buckets_per_data(handle_, static_cast<uint32_t>(buckets_per_data_)));
+        }
+        if (use_residual_) {
+            check_status(vb200_ivf_set_use_residual(handle_, 1));
         }
         if (quant_ == VB200_QUANT_RABITQ) {
             rotation_ = random_rotation(dim_, 47);
@@ -1120,8 +1125,8 @@ private:
 
     FileHeader
     file_header() const {
-        // the flag word also carries buckets_per_data, so that a file is only loaded into an index created alike
-        return FileHeader{FILE_KIND_IVF, dim_, nlist_, (use_reorder_ ? 1u : 0u) | (static_cast<uint32_t>(buckets_per_data_ - 1) << 8),
+        // the flag word also carries use_residual and buckets_per_data, so that a file is only loaded into an index created alike
+        return FileHeader{FILE_KIND_IVF, dim_, nlist_, (use_reorder_ ? 1u : 0u) | (use_residual_ ? 2u : 0u) | (static_cast<uint32_t>(buckets_per_data_ - 1) << 8),
                           metric_, quant_};
     }
 
@@ -1132,6 +1137,7 @@ private:
     uint32_t dim_;
     int metric_;
     int64_t buckets_per_data_ = 1;
+    bool use_residual_ = false;
     static constexpr uint32_t KMEANS_SEED = 47;
     uint32_t nlist_ = 10;
     int quant_ = VB200_QUANT_SQ8;
