@@ -51,7 +51,9 @@ def test_bad_values():
     expect_invalid("integer", index_param={"buckets_count": "many", "base_quantization_type": "sq8"})
     expect_invalid("buckets_count", index_param={"buckets_count": 0, "base_quantization_type": "sq8"})
     expect_invalid("not served", index_param={"base_quantization_type": "pq"})
-    expect_invalid("buckets_per_data", index_param={"base_quantization_type": "sq8", "buckets_per_data": 2})
+    expect_invalid("buckets_per_data", index_param={"base_quantization_type": "sq8", "buckets_per_data": 0})
+    expect_invalid("buckets_per_data", index_param={"base_quantization_type": "sq8", "buckets_per_data": 17})
+    expect_invalid("use_residual", index_param={"base_quantization_type": "fp32", "use_residual": True})
     expect_invalid("train_sample_count", index_param={"base_quantization_type": "sq8", "train_sample_count": 10})
 
 
