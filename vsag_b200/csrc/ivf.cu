@@ -74,6 +74,7 @@ struct SearchWorkspace {
     void* exchange_arg = nullptr;
     DevBuf<float> qrot;   // RaBitQ: rotated query rows of one slice
     DevBuf<uint8_t> qcodes;   // SQ8 uniform: the queries' code records
+    DevBuf<uint8_t> route_handled;  // routing: queries the warp-per-query pick answered
     DevBuf<float> pair_const;       // residual codes: per (query, probe) the centroid term of the distance
     DevBuf<uint64_t> keys_unique;   // buckets_per_data > 1: a query's postings folded to one per vector
     const float* ext_probe_dists = nullptr;   // centroid distances of caller-given probe lists (same duration)
@@ -1554,13 +1555,207 @@ route_threshold_kernel(const float* __restrict__ scores, uint32_t sample, uint32
 // that holds the ncand-th and everything below it, a few more than ncand keys), sorted as 64-bit keys so
 // that equal scores keep the lower list id; only if that set does not fit the small sort buffer (a
 // pile of equal scores) are all candidates sorted.
+// Bitonic sort of 32 * R keys held R per lane (element e = 32 * r + lane lives in key[r] of lane e % 32):
+// compare-exchanges inside a lane when the partner is 32 or more elements away, shuffles otherwise; ascending.
+template <int R>
+__device__ __forceinline__ void
+warp_sort_registers(uint64_t (&key)[R], uint32_t lane) {
+#pragma unroll
+    for (uint32_t size = 2; size <= 32u * R; size <<= 1) {
+#pragma unroll
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            if (stride >= 32) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int pr = r ^ static_cast<int>(stride >> 5);
+                    if (pr > r) {
+                        const bool up = (((static_cast<uint32_t>(r) << 5) | lane) & size) == 0;
+                        const uint64_t a = key[r], b = key[pr];
+                        if ((a > b) == up) {
+                            key[r] = b;
+                            key[pr] = a;
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint32_t e = (static_cast<uint32_t>(r) << 5) | lane;
+                    const uint64_t mine = key[r];
+                    const uint64_t other = __shfl_xor_sync(0xffffffffu, mine, stride);
+                    const bool up = (e & size) == 0;
+                    const bool lower = (lane & stride) == 0;
+                    const bool take_min = lower == up;
+                    key[r] = take_min ? (mine < other ? mine : other) : (mine > other ? mine : other);
+                }
+            }
+        }
+    }
+}
+
+// buf[0 .. 32 R) sorted ascending through registers (one warp).
+template <int R>
+__device__ __noinline__ void
+warp_sort_buffer(uint64_t* buf, uint32_t lane) {
+    uint64_t key[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        key[r] = buf[r * 32 + lane];
+    }
+    warp_sort_registers<R>(key, lane);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        buf[r * 32 + lane] = key[r];
+    }
+    __syncwarp();
+}
+
+// route_pick_kernel for the common case, one warp per query and no block-wide barrier: a query whose lists hold at
+// most 512 candidates (288 expected for nprobe 64 at a quarter sample) has them sorted through registers, the
+// ncand <= 128 best re-scored exactly, one chain per lane, and sorted again.  handled[q] = 1 tells route_pick_kernel
+// (launched afterwards over all queries) to leave the query alone.
+constexpr uint32_t ROUTE_WARP_KEYS = 512;
+
+__global__ void __launch_bounds__(256)
+route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t dim, const float* __restrict__ centroids,
+                       const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
+                       uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
+                       float* __restrict__ probe_dists, uint8_t* __restrict__ handled) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint64_t q = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + warp;
+    if (q >= nq) {
+        return;
+    }
+    uint64_t* buf = reinterpret_cast<uint64_t*>(smem_raw) + static_cast<size_t>(warp) * ROUTE_WARP_KEYS;
+    float* qs = reinterpret_cast<float*>(reinterpret_cast<uint64_t*>(smem_raw) + static_cast<size_t>(blockDim.x >> 5) * ROUTE_WARP_KEYS) +
+                static_cast<size_t>(warp) * dim;
+    // exclusive prefix of the (clamped) list counts, two lists per lane
+    const uint32_t l0 = 2 * lane, l1 = 2 * lane + 1;
+    uint32_t c0 = l0 < lists ? lists_cnt[q * lists + l0] : 0u;
+    uint32_t c1 = l1 < lists ? lists_cnt[q * lists + l1] : 0u;
+    c0 = c0 < cap ? c0 : cap;
+    c1 = c1 < cap ? c1 : cap;
+    uint32_t incl = c0 + c1;
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= static_cast<uint32_t>(off)) {
+            incl += v;
+        }
+    }
+    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+    if (total > ROUTE_WARP_KEYS) {
+        if (lane == 0) {
+            handled[q] = 0;
+        }
+        return;
+    }
+    const uint32_t before = incl - c0 - c1;
+    for (uint32_t d = lane; d < dim; d += 32) {
+        qs[d] = queries[q * dim + d];
+    }
+    for (uint32_t i = total + lane; i < ROUTE_WARP_KEYS; i += 32) {
+        buf[i] = KEY_INF;
+    }
+    // every lane copies its two lists (short: a few entries each)
+    {
+        const uint64_t* src0 = lists_keys + (q * lists + l0) * cap;
+        for (uint32_t i = 0; i < c0; ++i) {
+            buf[before + i] = src0[i];
+        }
+        const uint64_t* src1 = lists_keys + (q * lists + l1) * cap;
+        for (uint32_t i = 0; i < c1; ++i) {
+            buf[before + c0 + i] = src1[i];
+        }
+    }
+    __syncwarp();
+    if (total <= 128) {
+        warp_sort_buffer<4>(buf, lane);
+    } else if (total <= 256) {
+        warp_sort_buffer<8>(buf, lane);
+    } else {
+        warp_sort_buffer<16>(buf, lane);
+    }
+    // exact distances of the ncand best by approximate score, one chain per lane, dimensions ascending
+    uint64_t exact[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t e = r * 32 + lane;
+        uint64_t mine = KEY_INF;
+        if (e < ncand && e < total) {
+            const uint32_t list = static_cast<uint32_t>(buf[e]);
+            const float* c = centroids + static_cast<uint64_t>(list) * dim;
+            float s = 0.f;
+            if ((dim & 3u) == 0) {
+                const float4* c4 = reinterpret_cast<const float4*>(c);
+                const float4* q4 = reinterpret_cast<const float4*>(qs);
+                if (metric == VB200_METRIC_L2) {
+#pragma unroll 8
+                    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                        const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                        float t = __fsub_rn(qv.x, cv.x);
+                        s = fmaf(t, t, s);
+                        t = __fsub_rn(qv.y, cv.y);
+                        s = fmaf(t, t, s);
+                        t = __fsub_rn(qv.z, cv.z);
+                        s = fmaf(t, t, s);
+                        t = __fsub_rn(qv.w, cv.w);
+                        s = fmaf(t, t, s);
+                    }
+                } else {
+#pragma unroll 8
+                    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                        const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                        s = fmaf(qv.x, cv.x, s);
+                        s = fmaf(qv.y, cv.y, s);
+                        s = fmaf(qv.z, cv.z, s);
+                        s = fmaf(qv.w, cv.w, s);
+                    }
+                    s = __fsub_rn(1.0f, s);
+                }
+            } else if (metric == VB200_METRIC_L2) {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    const float t = __fsub_rn(qs[d], __ldg(c + d));
+                    s = fmaf(t, t, s);
+                }
+            } else {
+                for (uint32_t d = 0; d < dim; ++d) {
+                    s = fmaf(qs[d], __ldg(c + d), s);
+                }
+                s = __fsub_rn(1.0f, s);
+            }
+            mine = make_key(s, list);
+        }
+        exact[r] = mine;
+    }
+    warp_sort_registers<4>(exact, lane);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t i = r * 32 + lane;
+        if (i < nprobe) {
+            const uint64_t key = exact[r];
+            const uint64_t o = q * nprobe + i;
+            probes[o] = key == KEY_INF ? -1 : static_cast<int32_t>(static_cast<uint32_t>(key));
+            if (probe_dists != nullptr) {
+                probe_dists[o] = key == KEY_INF ? INFINITY : ordered_to_float(static_cast<uint32_t>(key >> 32));
+            }
+        }
+    }
+    if (lane == 0) {
+        handled[q] = 1;
+    }
+}
+
 constexpr uint32_t ROUTE_PICK_SMALL = 512;   // keys the small sort takes
 
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids,
                   const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
                   uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
-                  float* __restrict__ probe_dists) {
+                  float* __restrict__ probe_dists, const uint8_t* __restrict__ handled) {
+    if (handled != nullptr && handled[blockIdx.x] != 0) {
+        return;   // route_pick_warp_kernel answered this query
+    }
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ uint32_t s_off[65];
     __shared__ uint32_t hist[256];
@@ -1760,8 +1955,10 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
         // at least ncand centroids are known to meet; one pass of the tensor-core kernel over all
         // centroids then keeps, unsorted, only what scores below it -- about ncand * nlist / sample
         // per query -- and one small kernel per query orders those and re-scores the best exactly.
+        // (the largest sample that qualifies: the pass over it costs a quarter of the full pass at most, and every
+        // doubling halves what the per-query kernels have to order)
         uint32_t sample = 0;
-        for (uint32_t s = 1024; s <= 4096 && sample == 0; s *= 2) {
+        for (uint32_t s = 4096; s >= 1024 && sample == 0; s /= 2) {
             const uint64_t expected = static_cast<uint64_t>(ncand) * nlist / s;
             if (4ull * s <= nlist && s >= 4 * ncand && 5 * expected / 2 <= ROUTE_MAX_PER_ROW) {
                 sample = s;
@@ -1788,9 +1985,24 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
                     VB_CUDA(cudaFuncSetAttribute(route_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)));
                 }
+                // queries with few candidates (nearly all) are answered by a warp each; the block-per-query kernel
+                // takes what is left
+                const uint8_t* handled = nullptr;
+                const size_t warp_smem = 8 * (ROUTE_WARP_KEYS * sizeof(uint64_t) + ix->dim * sizeof(float));
+                if (ncand <= 128 && nprobe <= 128 && warp_smem <= 200 * 1024) {
+                    VB_TRY(ws.route_handled.reserve(nq));
+                    if (warp_smem > 48 * 1024) {
+                        VB_CUDA(cudaFuncSetAttribute(route_pick_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(warp_smem)));
+                    }
+                    VB_LAUNCH(route_pick_warp_kernel, static_cast<uint32_t>((nq + 7) / 8), 256, warp_smem, q_dev, nq, ix->dim,
+                              ix->centroids.ptr, ws.route_keys.ptr, ws.route_cnt.ptr, lists, cap, ncand, nprobe, ix->metric,
+                              probes_dev, dists_dev, ws.route_handled.ptr);
+                    handled = ws.route_handled.ptr;
+                }
                 VB_LAUNCH(route_pick_kernel, static_cast<uint32_t>(nq), 256, smem, q_dev, ix->dim, ix->centroids.ptr,
                           ws.route_keys.ptr, ws.route_cnt.ptr, lists, cap, ncand, nprobe, ix->metric, probes_dev,
-                          dists_dev);
+                          dists_dev, handled);
                 return 0;
             }
             // a list overflowed (scores far from what the sample predicted): take the score-matrix path
