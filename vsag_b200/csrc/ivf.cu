@@ -2169,7 +2169,11 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     // on the tensor cores (for comparisons).
     static const bool tc_first_forced = std::getenv("VB200_TC_FIRST") != nullptr && std::getenv("VB200_TC_FIRST")[0] == '1';
     const bool tc_first = tc_scan && (!(split_phases && pruning) || tc_first_forced), tc_second = tc_scan;
-    const uint32_t qt_first = tc_first ? TCS_QT : static_cast<uint32_t>(qt);
+    // ... and when every item is a single query anyway, a warp per item beats a CTA per item (VB200_WARP_FIRST=0: off)
+    static const bool warp_first_off = std::getenv("VB200_WARP_FIRST") != nullptr && std::getenv("VB200_WARP_FIRST")[0] == '0';
+    const bool warp_first = sq8 && split_phases && pruning && !tc_first && !warp_first_off && kscan <= 192 &&
+                            sq8_first_smem_bytes(kscan, ix->dpad) <= 96 * 1024;
+    const uint32_t qt_first = warp_first ? 1u : (tc_first ? TCS_QT : static_cast<uint32_t>(qt));
     const uint32_t qt_second = tc_second ? TCS_QT : static_cast<uint32_t>(qt);
     VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr, qt_first));
 
@@ -2252,7 +2256,8 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                   tc_scan ? ws.qw8.ptr : nullptr, tc_scan ? ws.qscale.ptr : nullptr);
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
-    auto launch_phases = [&](uint32_t first, uint32_t count, uint32_t queue_slot, bool on_tensor_cores) -> int {
+    auto launch_phases = [&](uint32_t first, uint32_t count, uint32_t queue_slot, bool on_tensor_cores,
+                             bool warp_items = false) -> int {
         for (uint32_t i = 0; i < 2; ++i) {
             const uint32_t src = i < count ? first + i : first;
             p.pair_off[i] = ws.pair_off[src].ptr;
@@ -2327,6 +2332,21 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
 #endif
             return 0;
         }
+        if (sq8 && warp_items) {
+            const size_t smem = sq8_first_smem_bytes(p.k, ix->dpad);
+            if (smem > 40 * 1024) {
+                VB_CUDA(cudaFuncSetAttribute(ivf_sq8_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem)));
+            }
+            int per_sm = 0;
+            VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ivf_sq8_first_kernel, SQ8_FIRST_WARPS * 32, smem));
+            if (per_sm < 1) {
+                VB_FAIL(VB200_INTERNAL_ERROR, "the first-phase scan does not fit an SM with %zu bytes of shared memory", smem);
+            }
+            VB_LAUNCH(ivf_sq8_first_kernel, static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(per_sm),
+                      SQ8_FIRST_WARPS * 32, smem, p);
+            return 0;
+        }
         if (sq8) {
             size_t smem = tile_smem_bytes<SQ8_QT>(p.cap, SQ8_QT * ix->dpad);
             return launch_scan(ivf_sq8_scan_kernel<SQ8_QT>, p, smem);
@@ -2364,7 +2384,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     };
     p.order = ix->scan_order.ptr;
     if (split_phases) {
-        VB_TRY(launch_phases(0, 1, 1, tc_first));
+        VB_TRY(launch_phases(0, 1, 1, tc_first, warp_first));
         if (ws.exchange != nullptr) {
             // Sharded search: after the owner of each query's nearest list has scanned it, the
             // shards agree on the tightest bound any of them found, so the remaining lists are

@@ -660,6 +660,162 @@ ivf_sq8_scan_kernel(const ScanParams p) {
     }
 }
 
+// The first phase when it runs alone: every work item is one query against its nearest list, a few hundred
+// rows.  A CTA per item spends most of its time in barriers and set-up, so here a warp takes an item by itself:
+// its lanes own two rows each per round, the query's weights sit in the warp's slice of shared memory (every
+// lane reads the same word: a broadcast), candidates that beat the bound are appended through a ballot, and
+// the warp sorts its own small buffer when it fills.  The arithmetic per row is that of sq8_tile_dots_single,
+// so the survivors are the ones the CTA kernel would keep.
+constexpr int SQ8_FIRST_WARPS = 8;
+
+__host__ __device__ inline uint32_t
+sq8_first_cap(uint32_t k) {
+    uint32_t v = k + 64, c = 64;
+    while (c < v) {
+        c <<= 1;
+    }
+    return c;
+}
+
+__host__ __device__ inline size_t
+sq8_first_smem_bytes(uint32_t k, uint32_t dpad) {
+    return static_cast<size_t>(SQ8_FIRST_WARPS) * (static_cast<size_t>(sq8_first_cap(k)) * 8 + static_cast<size_t>(dpad) * 4);
+}
+
+__global__ void __launch_bounds__(SQ8_FIRST_WARPS * 32)
+ivf_sq8_first_kernel(const ScanParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cap = sq8_first_cap(p.k), k = p.k, dpad = p.dpad;
+    uint64_t* kb = reinterpret_cast<uint64_t*>(smem) + static_cast<size_t>(warp) * cap;
+    float* w_s = reinterpret_cast<float*>(smem + static_cast<size_t>(SQ8_FIRST_WARPS) * cap * 8) + static_cast<size_t>(warp) * dpad;
+    const uint32_t n_items = p.item_off[0][p.nlist];
+    const uint32_t lt_mask = (1u << lane) - 1u;
+
+    for (;;) {
+        uint32_t item = 0;
+        if (lane == 0) {
+            item = atomicAdd(p.item_counter, 1u);
+            if (p.deadline != nullptr && scan_deadline_passed(p)) {
+                item = 0xFFFFFFFFu;
+            }
+        }
+        item = __shfl_sync(0xffffffffu, item, 0);
+        if (item >= n_items) {
+            return;
+        }
+        const ScanItemDesc* desc = p.item_map[0] + item;
+        const uint4 head = __ldg(reinterpret_cast<const uint4*>(desc));
+        const uint32_t list = head.x, pbeg = head.y, nqt = head.z;
+        const uint32_t lbeg = __ldg(p.list_off + list);
+        const uint32_t len = __ldg(p.list_off + list + 1) - lbeg;
+        for (uint32_t pi = 0; pi < nqt; ++pi) {
+            const uint32_t q = __ldg(p.pair_q[0] + pbeg + pi);
+            const uint32_t slot = __ldg(p.pair_slot[0] + pbeg + pi);
+            const float qa = __ldg(p.qa + q) + (p.pair_const != nullptr ? __ldg(p.pair_const + slot) : 0.f);
+            uint32_t thr = p.thr_g[q];
+            float thrq = (thr >= 0xFF800000u ? INFINITY : ordered_to_float(thr)) - qa;
+            uint32_t cnt = 0;
+            __syncwarp();
+            {
+                const float4* src = reinterpret_cast<const float4*>(p.qw + static_cast<uint64_t>(q) * dpad);
+                float4* dst = reinterpret_cast<float4*>(w_s);
+                for (uint32_t i = lane; i < (dpad >> 2); i += 32) {
+                    dst[i] = __ldg(src + i);
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && p.scanned != nullptr) {
+                atomicAdd(p.scanned, static_cast<unsigned long long>(len) * p.dim);
+            }
+            // sorts the buffer, keeps the k best and tightens the bound (all lanes)
+            auto compact = [&]() {
+                const uint32_t n2 = next_pow2(cnt < 2 ? 2 : cnt);
+                for (uint32_t i = cnt + lane; i < n2; i += 32) {
+                    kb[i] = KEY_INF;
+                }
+                warp_bitonic_sort(kb, n2, lane);
+                if (cnt >= k) {
+                    const uint32_t t = static_cast<uint32_t>(kb[k - 1] >> 32);
+                    if (t < thr) {
+                        thr = t;
+                        thrq = (t >= 0xFF800000u ? INFINITY : ordered_to_float(t)) - qa;
+                    }
+                    cnt = k;
+                }
+            };
+            for (uint32_t r0 = 0; r0 < len; r0 += 64) {
+                const uint32_t row0 = r0 + lane, row1 = r0 + 32 + lane;
+                const bool v0 = row0 < len, v1 = row1 < len;
+                const uint8_t* c0 = p.codes + static_cast<uint64_t>(lbeg + (v0 ? row0 : 0)) * p.code_stride;
+                const uint8_t* c1 = p.codes + static_cast<uint64_t>(lbeg + (v1 ? row1 : 0)) * p.code_stride;
+                float a0 = 0.f, a1 = 0.f;
+                uint4 n0 = __ldg(reinterpret_cast<const uint4*>(c0));
+                uint4 n1 = __ldg(reinterpret_cast<const uint4*>(c1));
+                const float4* wrow = reinterpret_cast<const float4*>(w_s);
+#pragma unroll 1
+                for (uint32_t c = 0; c < dpad; c += 16, wrow += 4) {
+                    const uint4 u0 = n0, u1 = n1;
+                    if (c + 16 < dpad) {
+                        n0 = __ldg(reinterpret_cast<const uint4*>(c0 + c + 16));
+                        n1 = __ldg(reinterpret_cast<const uint4*>(c1 + c + 16));
+                    }
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const float4 wv = wrow[w];
+                        const uint32_t r0w = w == 0 ? u0.x : (w == 1 ? u0.y : (w == 2 ? u0.z : u0.w));
+                        const uint32_t r1w = w == 0 ? u1.x : (w == 1 ? u1.y : (w == 2 ? u1.z : u1.w));
+                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7540)) - 8388736.0f, wv.x, a0);
+                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7540)) - 8388736.0f, wv.x, a1);
+                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7541)) - 8388736.0f, wv.y, a0);
+                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7541)) - 8388736.0f, wv.y, a1);
+                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7542)) - 8388736.0f, wv.z, a0);
+                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7542)) - 8388736.0f, wv.z, a1);
+                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7543)) - 8388736.0f, wv.w, a0);
+                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7543)) - 8388736.0f, wv.w, a1);
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const bool valid = h == 0 ? v0 : v1;
+                    const uint32_t pos = lbeg + (h == 0 ? row0 : row1);
+                    float partial = 0.f;
+                    bool pass = false;
+                    if (valid) {
+                        partial = fmaf(p.coef_c, h == 0 ? a0 : a1, p.coef_b * __ldg(p.code_norm + pos));
+                        pass = partial <= thrq;
+                        if (pass && p.filter_pos_inner != nullptr && scan_row_filtered(p, pos)) {
+                            pass = false;
+                        }
+                    }
+                    const uint32_t mask = __ballot_sync(0xffffffffu, pass);
+                    if (mask != 0) {
+                        if (cnt + 32 > cap) {
+                            compact();
+                        }
+                        if (pass) {
+                            kb[cnt + __popc(mask & lt_mask)] = make_key(partial + qa, pos);
+                        }
+                        cnt += __popc(mask);
+                        __syncwarp();
+                    }
+                }
+            }
+            if (cnt >= k) {
+                compact();
+            }
+            __syncwarp();
+            uint64_t* dst = p.part + static_cast<uint64_t>(slot) * k;
+            for (uint32_t i = lane; i < k; i += 32) {
+                dst[i] = i < cnt ? kb[i] : KEY_INF;
+            }
+            if (lane == 0 && cnt >= k) {
+                atomicMin(p.thr_g + q, static_cast<uint32_t>(kb[k - 1] >> 32));
+            }
+        }
+    }
+}
+
 // Exact SQ8 distances of the survivors, in the reference's operation order (one thread per
 // candidate walks the dimensions upward: SQ8ComputeL2Sqr / SQ8ComputeIP with Width 1), then a
 // sort by (distance, position).  cand/out payloads are code positions.
