@@ -371,8 +371,8 @@ def test_threshold_routing_equals_oracle(engine, oracle, metric, nlist, nprobe, 
     """From 4096 lists on, routing keeps no score matrix: a threshold per query from a sample of the
     centroids, one tensor-core pass that keeps what scores below it, exact re-scoring of the best.  The
     probe lists and distances are the oracle's bit for bit -- also when many centroids coincide, which
-    piles candidates at one score (and, past what the candidate lists hold, falls back to the
-    score-matrix path)."""
+    piles candidates at one score (a query whose candidate lists overflow is answered inside the pick
+    kernel from exact distances to every centroid)."""
     dim, nq = 96, 600
     cents = mixture(71 + nlist, nlist, dim, 200, 0.3)
     if dup:

@@ -16,6 +16,7 @@ namespace vb200 {
 
 constexpr uint32_t NONE32 = 0xFFFFFFFFu;
 constexpr uint32_t ROUTE_SLACK = 8;   // extra routing candidates re-scored exactly
+constexpr size_t SCALARS = 10;                // entries of the search workspace's scalar block
 constexpr uint32_t ROUTE_MAX_PER_ROW = 4096;   // approximate candidates a query may bring to the final pick (32 KiB of keys)
 constexpr int SQ8_QT = 16;
 constexpr uint32_t SQ8_SLACK = 16;    // survivors kept beyond k for exact re-scoring
@@ -1547,6 +1548,53 @@ route_threshold_kernel(const float* __restrict__ scores, uint32_t sample, uint32
     }
 }
 
+// Exact routing distance of a query (in shared memory) to one centroid: L2 as an FMA chain of (q-c)^2 over the
+// dimensions ascending, IP as 1 - the chain of q*c (the loop of IVF::route_buckets_only,
+// src/algorithm/ivf/ivf.cpp:1589-1660).
+__device__ __forceinline__ float
+route_exact_score(const float* __restrict__ qs, const float* __restrict__ c, uint32_t dim, int metric) {
+    float s = 0.f;
+    if ((dim & 3u) == 0) {   // centroid rows are then 16-byte aligned: four dimensions per load, several loads in flight
+        const float4* c4 = reinterpret_cast<const float4*>(c);
+        const float4* q4 = reinterpret_cast<const float4*>(qs);
+        if (metric == VB200_METRIC_L2) {
+#pragma unroll 8
+            for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                float t = __fsub_rn(qv.x, cv.x);
+                s = fmaf(t, t, s);
+                t = __fsub_rn(qv.y, cv.y);
+                s = fmaf(t, t, s);
+                t = __fsub_rn(qv.z, cv.z);
+                s = fmaf(t, t, s);
+                t = __fsub_rn(qv.w, cv.w);
+                s = fmaf(t, t, s);
+            }
+        } else {
+#pragma unroll 8
+            for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+                const float4 cv = __ldg(c4 + d4), qv = q4[d4];
+                s = fmaf(qv.x, cv.x, s);
+                s = fmaf(qv.y, cv.y, s);
+                s = fmaf(qv.z, cv.z, s);
+                s = fmaf(qv.w, cv.w, s);
+            }
+            s = __fsub_rn(1.0f, s);
+        }
+    } else if (metric == VB200_METRIC_L2) {
+        for (uint32_t d = 0; d < dim; ++d) {
+            const float t = __fsub_rn(qs[d], __ldg(c + d));
+            s = fmaf(t, t, s);
+        }
+    } else {
+        for (uint32_t d = 0; d < dim; ++d) {
+            s = fmaf(qs[d], __ldg(c + d), s);
+        }
+        s = __fsub_rn(1.0f, s);
+    }
+    return s;
+}
+
 // One CTA per query: gathers the query's centroids below its threshold from their lists, takes the
 // ncand best by approximate score, re-scores them exactly -- L2: FMA chain of (q-c)^2 over d
 // ascending; IP: 1 - chain of q*c (the loop of IVF::route_buckets_only,
@@ -1634,6 +1682,7 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
     const uint32_t l0 = 2 * lane, l1 = 2 * lane + 1;
     uint32_t c0 = l0 < lists ? lists_cnt[q * lists + l0] : 0u;
     uint32_t c1 = l1 < lists ? lists_cnt[q * lists + l1] : 0u;
+    const bool lost = __any_sync(0xffffffffu, c0 > cap || c1 > cap);   // a list overflowed: route_pick_kernel's business
     c0 = c0 < cap ? c0 : cap;
     c1 = c1 < cap ? c1 : cap;
     uint32_t incl = c0 + c1;
@@ -1644,7 +1693,7 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
         }
     }
     const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-    if (total > ROUTE_WARP_KEYS) {
+    if (lost || total > ROUTE_WARP_KEYS) {
         if (lane == 0) {
             handled[q] = 0;
         }
@@ -1684,46 +1733,7 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
         uint64_t mine = KEY_INF;
         if (e < ncand && e < total) {
             const uint32_t list = static_cast<uint32_t>(buf[e]);
-            const float* c = centroids + static_cast<uint64_t>(list) * dim;
-            float s = 0.f;
-            if ((dim & 3u) == 0) {
-                const float4* c4 = reinterpret_cast<const float4*>(c);
-                const float4* q4 = reinterpret_cast<const float4*>(qs);
-                if (metric == VB200_METRIC_L2) {
-#pragma unroll 8
-                    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
-                        const float4 cv = __ldg(c4 + d4), qv = q4[d4];
-                        float t = __fsub_rn(qv.x, cv.x);
-                        s = fmaf(t, t, s);
-                        t = __fsub_rn(qv.y, cv.y);
-                        s = fmaf(t, t, s);
-                        t = __fsub_rn(qv.z, cv.z);
-                        s = fmaf(t, t, s);
-                        t = __fsub_rn(qv.w, cv.w);
-                        s = fmaf(t, t, s);
-                    }
-                } else {
-#pragma unroll 8
-                    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
-                        const float4 cv = __ldg(c4 + d4), qv = q4[d4];
-                        s = fmaf(qv.x, cv.x, s);
-                        s = fmaf(qv.y, cv.y, s);
-                        s = fmaf(qv.z, cv.z, s);
-                        s = fmaf(qv.w, cv.w, s);
-                    }
-                    s = __fsub_rn(1.0f, s);
-                }
-            } else if (metric == VB200_METRIC_L2) {
-                for (uint32_t d = 0; d < dim; ++d) {
-                    const float t = __fsub_rn(qs[d], __ldg(c + d));
-                    s = fmaf(t, t, s);
-                }
-            } else {
-                for (uint32_t d = 0; d < dim; ++d) {
-                    s = fmaf(qs[d], __ldg(c + d), s);
-                }
-                s = __fsub_rn(1.0f, s);
-            }
+            const float s = route_exact_score(qs, centroids + static_cast<uint64_t>(list) * dim, dim, metric);
             mine = make_key(s, list);
         }
         exact[r] = mine;
@@ -1752,12 +1762,13 @@ __global__ void __launch_bounds__(ROUTE_THREADS)
 route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids,
                   const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
                   uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
-                  float* __restrict__ probe_dists, const uint8_t* __restrict__ handled) {
+                  float* __restrict__ probe_dists, const uint8_t* __restrict__ handled, uint32_t nlist) {
     if (handled != nullptr && handled[blockIdx.x] != 0) {
         return;   // route_pick_warp_kernel answered this query
     }
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ uint32_t s_off[65];
+    __shared__ uint32_t s_lost, s_state[3];
     __shared__ uint32_t hist[256];
     __shared__ float red[ROUTE_THREADS / 32];
     __shared__ uint32_t s_bin, s_rank, s_taken;
@@ -1775,6 +1786,10 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
         const uint32_t l0 = 2 * tid, l1 = 2 * tid + 1;
         uint32_t c0 = l0 < lists ? lists_cnt[q * lists + l0] : 0u;
         uint32_t c1 = l1 < lists ? lists_cnt[q * lists + l1] : 0u;
+        const bool lost = __any_sync(0xffffffffu, c0 > cap || c1 > cap);
+        if (tid == 0) {
+            s_lost = lost ? 1u : 0u;
+        }
         c0 = c0 < cap ? c0 : cap;
         c1 = c1 < cap ? c1 : cap;
         uint32_t incl = c0 + c1;
@@ -1799,6 +1814,32 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
         }
     }
     __syncthreads();
+    if (s_lost != 0) {
+        // One of the query's lists overflowed (its scores lie far from what the centroid sample predicted), so
+        // candidates were lost.  The query is answered from scratch instead: exact distances to every centroid,
+        // the nprobe nearest kept by a streaming selection.  Rare, and decided here, so the host never has to
+        // wait for the candidate pass to know.
+        BlockSelect sel;
+        sel.init(keys, s_state, nprobe, next_pow2(nprobe + blockDim.x));
+        for (uint32_t base = 0; base < nlist; base += blockDim.x) {
+            sel.make_room(blockDim.x);
+            const uint64_t bound = sel.threshold();
+            const uint32_t c = base + tid;
+            if (c < nlist) {
+                sel.offer(make_key(route_exact_score(qs, centroids + static_cast<uint64_t>(c) * dim, dim, metric), c), bound);
+            }
+        }
+        const uint32_t found = sel.finish();
+        for (uint32_t i = tid; i < nprobe; i += blockDim.x) {
+            const uint64_t key = i < found ? keys[i] : KEY_INF;
+            const uint64_t o = q * nprobe + i;
+            probes[o] = key == KEY_INF ? -1 : static_cast<int32_t>(static_cast<uint32_t>(key));
+            if (probe_dists != nullptr) {
+                probe_dists[o] = key == KEY_INF ? INFINITY : ordered_to_float(static_cast<uint32_t>(key >> 32));
+            }
+        }
+        return;
+    }
     const uint32_t total = s_off[lists];
     float mn = INFINITY, mx = -INFINITY;
     for (uint32_t l = warp; l < lists; l += blockDim.x >> 5) {
@@ -1862,46 +1903,7 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
     uint64_t mine = KEY_INF;
     if (tid < ncand && tid < n_sorted && sorted[tid] != KEY_INF) {
         const uint32_t list = static_cast<uint32_t>(sorted[tid]);
-        const float* c = centroids + static_cast<uint64_t>(list) * dim;
-        float s = 0.f;
-        if ((dim & 3u) == 0) {   // centroid rows are then 16-byte aligned: four dimensions per load, several loads in flight
-            const float4* c4 = reinterpret_cast<const float4*>(c);
-            const float4* q4 = reinterpret_cast<const float4*>(qs);
-            if (metric == VB200_METRIC_L2) {
-#pragma unroll 8
-                for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
-                    const float4 cv = __ldg(c4 + d4), qv = q4[d4];
-                    float t = __fsub_rn(qv.x, cv.x);
-                    s = fmaf(t, t, s);
-                    t = __fsub_rn(qv.y, cv.y);
-                    s = fmaf(t, t, s);
-                    t = __fsub_rn(qv.z, cv.z);
-                    s = fmaf(t, t, s);
-                    t = __fsub_rn(qv.w, cv.w);
-                    s = fmaf(t, t, s);
-                }
-            } else {
-#pragma unroll 8
-                for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
-                    const float4 cv = __ldg(c4 + d4), qv = q4[d4];
-                    s = fmaf(qv.x, cv.x, s);
-                    s = fmaf(qv.y, cv.y, s);
-                    s = fmaf(qv.z, cv.z, s);
-                    s = fmaf(qv.w, cv.w, s);
-                }
-                s = __fsub_rn(1.0f, s);
-            }
-        } else if (metric == VB200_METRIC_L2) {
-            for (uint32_t d = 0; d < dim; ++d) {
-                const float t = __fsub_rn(qs[d], __ldg(c + d));
-                s = fmaf(t, t, s);
-            }
-        } else {
-            for (uint32_t d = 0; d < dim; ++d) {
-                s = fmaf(qs[d], __ldg(c + d), s);
-            }
-            s = __fsub_rn(1.0f, s);
-        }
+        const float s = route_exact_score(qs, centroids + static_cast<uint64_t>(list) * dim, dim, metric);
         mine = make_key(s, list);
     }
     __syncthreads();
@@ -1919,10 +1921,43 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
     }
 }
 
+// The workspace's scalar block, zeroed when it is first allocated (entry 8, the routing passes' flag, is read at
+// the end of every search whether or not that search routed).
+static int
+reserve_scalars(SearchWorkspace& ws) {
+    if (ws.scalars.cap >= SCALARS) {
+        return 0;
+    }
+    VB_TRY(ws.scalars.reserve(SCALARS));
+    VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, SCALARS * sizeof(uint64_t), current_stream()));
+    return 0;
+}
+
+// After a synchronisation: fails if a tensor-core routing pass of the call reported a wait that gave up.
+static int
+route_flag_check(uint64_t flag_word) {
+    if ((flag_word & 1u) != 0) {
+        VB_FAIL(VB200_INTERNAL_ERROR, "tensor-core kernel gave up on a bounded wait");
+    }
+    return 0;
+}
+
+// For callers that only route: waits for the stream and reads the flag.
+static int
+route_sync_and_check(SearchWorkspace& ws) {
+    uint64_t word = 0;
+    VB_CUDA(cudaMemcpyAsync(&word, ws.scalars.ptr + 8, sizeof(word), cudaMemcpyDeviceToHost, current_stream()));
+    VB_TRY(sync_stream());
+    return route_flag_check(word);
+}
+
 static int
 ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe, int32_t* probes_dev,
                  float* dists_dev) {
     SearchWorkspace& ws = ix->ws;
+    VB_TRY(reserve_scalars(ws));
+    int* route_flag = reinterpret_cast<int*>(ws.scalars.ptr + 8);
+    VB_CUDA(cudaMemsetAsync(route_flag, 0, sizeof(uint64_t), current_stream()));
     const uint32_t nlist = ix->nlist;
     uint32_t ncand = nprobe + ROUTE_SLACK < nlist ? nprobe + ROUTE_SLACK : nlist;
     VB_CHECK_ARG(ncand <= 1024, "scan_buckets_count %u is too large (limit %u)", nprobe,
@@ -1969,16 +2004,20 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
             const float* bias = l2 ? ix->c_sq.ptr : nullptr;
             TcOperand bs{ix->c_hi.ptr, ix->c_lo.ptr, sample, chunks};
             VB_TRY(ws.scores.reserve(nq * sample));
-            VB_TRY(tc_scores(ix->tc, a, bs, 3, alpha, bias, ws.scores.ptr, sample));
+            // No wait for either tensor-core pass: what they report (a bounded wait that gave up) is OR-ed into
+            // ws.scalars[8], which every caller reads when it synchronises at the end of its call; a query whose
+            // candidate lists overflowed is answered exactly by route_pick_kernel itself.
+            VB_TRY(tc_scores(ix->tc, a, bs, 3, alpha, bias, ws.scores.ptr, sample, route_flag));
             VB_TRY(ws.route_thr.reserve(nq));
             VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>(nq), ROUTE_THREADS, 0, ws.scores.ptr, sample, ncand,
                       q_dev, ix->dim, ix->c_max_norm.ptr, ws.route_thr.ptr);
             uint32_t lists = 0, cap = 0;
             bool overflow = false;
             const uint32_t expected = static_cast<uint32_t>(static_cast<uint64_t>(ncand) * nlist / sample);
+            const uint32_t n_keep = next_pow2(nprobe + ROUTE_THREADS);   // the exact fallback's selection buffer
             VB_TRY(tc_below_threshold(ix->tc, a, b, 3, alpha, bias, ws.route_thr.ptr, expected, ROUTE_MAX_PER_ROW,
-                                      ws.route_keys, ws.route_cnt, &lists, &cap, &overflow));
-            if (!overflow && lists <= 64) {
+                                      ws.route_keys, ws.route_cnt, &lists, &cap, &overflow, route_flag));
+            if (lists <= 64 && n_keep <= ROUTE_PICK_SMALL) {
                 const uint32_t slots = next_pow2(lists * cap > ROUTE_PICK_SMALL ? lists * cap : ROUTE_PICK_SMALL);
                 const size_t smem = (static_cast<size_t>(slots) + ROUTE_PICK_SMALL) * sizeof(uint64_t) + ix->dim * sizeof(float);
                 if (smem > 48 * 1024) {
@@ -2002,10 +2041,10 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
                 }
                 VB_LAUNCH(route_pick_kernel, static_cast<uint32_t>(nq), 256, smem, q_dev, ix->dim, ix->centroids.ptr,
                           ws.route_keys.ptr, ws.route_cnt.ptr, lists, cap, ncand, nprobe, ix->metric, probes_dev,
-                          dists_dev, handled);
+                          dists_dev, handled, nlist);
                 return 0;
             }
-            // a list overflowed (scores far from what the sample predicted): take the score-matrix path
+            VB_TRY(sync_stream());   // (more lists than the pick kernels take: the score-matrix path below)
         }
         VB_TRY(ws.scores.reserve(nq * ld));
         VB_TRY(tc_scores(ix->tc, a, b, 3, l2 ? -2.0f : -1.0f, l2 ? ix->c_sq.ptr : nullptr, ws.scores.ptr, ld));
@@ -2113,7 +2152,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     VB_TRY(ws.thr.reserve(nq));
     VB_TRY(ws.part.reserve(total * kscan));
     VB_TRY(ws.keys.reserve(nq * kfinal));
-    VB_TRY(ws.scalars.reserve(8));
+    VB_TRY(reserve_scalars(ws));
     if (sq8) {
         VB_TRY(ws.qw.reserve(nq * ix->dpad));
         VB_TRY(ws.qa.reserve(nq));
@@ -3059,6 +3098,7 @@ vb200_ivf_add(vb200_ivf_t ix, const float* data, uint64_t count, const int64_t* 
     } else if (per_vector > 1) {
         VB_TRY(route_dists.reserve(count));
         VB_TRY(ivf_route_device(ix, xr, n_rows, per_vector, lab.ptr, route_dists.ptr));
+        VB_TRY(route_sync_and_check(ix->ws));
     } else {
         if (ix->metric == VB200_METRIC_L2) {
             // the k-means assignment (tensor-core candidates + exact pick when large enough)
@@ -3360,7 +3400,7 @@ vb200_ivf_route(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t npro
     if (bucket_dists != nullptr) {
         VB_TRY(copy_out(bucket_dists, ix->ws.probe_dists.ptr, nq * nprobe));
     }
-    return sync_stream();
+    return route_sync_and_check(ix->ws);
 }
 
 extern "C" int
@@ -3412,7 +3452,7 @@ vb200_ivf_search_ex(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t 
         // zero or less has passed as soon as the scan asks
         const double ms = options->timeout_ms;
         if (options->has_timeout != 0 && ms < 1e12) {
-            VB_TRY(ws.scalars.reserve(8));
+            VB_TRY(reserve_scalars(ws));
             const double ns = ms > 0.0 ? ms * 1e6 : 0.0;
             VB_LAUNCH(deadline_stamp_kernel, 1, 1, 0, reinterpret_cast<unsigned long long*>(ws.scalars.ptr + 6),
                       static_cast<unsigned long long>(ns));
@@ -3440,9 +3480,10 @@ vb200_ivf_search_ex(vb200_ivf_t ix, const float* queries, uint64_t nq, uint32_t 
               ix->labels.ptr, ws.out_ids.ptr, ws.out_dists.ptr);
     VB_TRY(copy_out(ids, ws.out_ids.ptr, total));
     VB_TRY(copy_out(dists, ws.out_dists.ptr, total));
-    uint64_t scalars[6] = {0, 0, 0, 0, 0, 0};
+    uint64_t scalars[SCALARS] = {};
     VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
+    VB_TRY(route_flag_check(scalars[8]));
     ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
     ix->last_scanned_bytes = static_cast<int64_t>(ws.pruning ? scalars[3] : scalars[0]);
     if (scalars[4] != 0) {
@@ -3496,9 +3537,10 @@ vb200_ivf_search_partial(vb200_ivf_t ix, const float* queries, uint64_t nq, uint
     VB_TRY(search_status);
     VB_LAUNCH(keys_labels_kernel, static_cast<uint32_t>((total + 255) / 256), 256, 0, keys, total,
               ix->labels.ptr, keys_dev, labels_dev);
-    uint64_t scalars[5] = {0, 0, 0, 0, 0};
+    uint64_t scalars[SCALARS] = {};
     VB_CUDA(cudaMemcpyAsync(scalars, ix->ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
+    VB_TRY(route_flag_check(scalars[8]));
     ix->last_scan_bytes = static_cast<int64_t>(scalars[0]);
     ix->last_scanned_bytes = static_cast<int64_t>(ix->ws.pruning ? scalars[3] : scalars[0]);
     if (scalars[4] != 0) {
@@ -3733,9 +3775,10 @@ vb200_ivf_search_sharded(vb200_ivf_t ix, vb200_comm_t comm, const float* queries
     VB_TRY(merge_partials_device(ws.sh_all.ptr, reinterpret_cast<const int64_t*>(ws.sh_all.ptr + total), world, 2 * total,
                                  nq, k, ids, dists));
     mark(5);
-    uint64_t scalars[5] = {0, 0, 0, 0, 0};
+    uint64_t scalars[SCALARS] = {};
     VB_CUDA(cudaMemcpyAsync(scalars, ws.scalars.ptr, sizeof(scalars), cudaMemcpyDeviceToHost, st));
     VB_TRY(sync_stream());
+    VB_TRY(route_flag_check(scalars[8]));
     static int n_calls = 0;
     if (profile && ++n_calls > 3) {   // the first three calls are a caller's warm-up
         for (int i = 0; i < 5; ++i) {

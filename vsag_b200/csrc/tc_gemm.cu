@@ -936,7 +936,7 @@ int
 tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
                    const float* bias_dev, const float* row_thr_dev, uint32_t expected_per_row, uint32_t max_per_row,
                    DevBuf<uint64_t>& out, DevBuf<uint32_t>& out_count, uint32_t* lists_out, uint32_t* cap_out,
-                   bool* overflow_out) {
+                   bool* overflow_out, int* deferred_flag_dev) {
     VB_CHECK_ARG(a.rows > 0 && b.rows > 0, "tc_below_threshold: empty operand");
     VB_CHECK_ARG(a.chunks == b.chunks && a.chunks > 0, "tc_below_threshold: operand depths differ");
     VB_CHECK_ARG(n_terms == 1 || n_terms == 3, "tc_below_threshold: 1 or 3 terms");
@@ -984,17 +984,25 @@ tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint
     p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
     VB_TRY(out.reserve(static_cast<size_t>(a.rows) * lists * cap));
     VB_TRY(out_count.reserve(static_cast<size_t>(a.rows) * lists));
-    VB_TRY(ws.error_flag.reserve(2));
-    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
+    if (deferred_flag_dev == nullptr) {
+        VB_TRY(ws.error_flag.reserve(2));
+        VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
+    }
     p.out = out.ptr;
     p.out_count = out_count.ptr;
-    p.error_flag = ws.error_flag.ptr;
+    p.error_flag = deferred_flag_dev != nullptr ? deferred_flag_dev : ws.error_flag.ptr;
     p.spin_limit = tc_spin_limit();
     size_t smem = 0;
     tc_plan(p, 0, &smem);
     auto kernel = tc_candidates_kernel<3>;
     VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
+    *lists_out = lists;
+    *cap_out = cap;
+    *overflow_out = false;
+    if (deferred_flag_dev != nullptr) {
+        return 0;
+    }
     int flag = 0;
     VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());
@@ -1009,7 +1017,7 @@ tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint
 
 int
 tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
-          const float* bias_dev, float* scores_dev, uint64_t ld) {
+          const float* bias_dev, float* scores_dev, uint64_t ld, int* deferred_flag_dev) {
     VB_CHECK_ARG(a.rows > 0 && b.rows > 0, "tc_scores: empty operand");
     VB_CHECK_ARG(a.chunks == b.chunks && a.chunks > 0, "tc_scores: operand depths differ");
     VB_CHECK_ARG(n_terms == 1 || n_terms == 3, "tc_scores: 1 or 3 terms");
@@ -1041,15 +1049,20 @@ tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_te
     p.tiles_per_split = static_cast<uint32_t>(tiles_per_split);
     p.store = scores_dev;
     p.store_ld = ld;
-    VB_TRY(ws.error_flag.reserve(2));
-    VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
-    p.error_flag = ws.error_flag.ptr;
+    if (deferred_flag_dev == nullptr) {
+        VB_TRY(ws.error_flag.reserve(2));
+        VB_CUDA(cudaMemsetAsync(ws.error_flag.ptr, 0, 2 * sizeof(int), current_stream()));
+    }
+    p.error_flag = deferred_flag_dev != nullptr ? deferred_flag_dev : ws.error_flag.ptr;
     p.spin_limit = tc_spin_limit();
     size_t smem = 0;
     tc_plan(p, 0, &smem);
     auto kernel = tc_candidates_kernel<2>;
     VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     VB_LAUNCH(kernel, grid, TC_THREADS, smem, p);
+    if (deferred_flag_dev != nullptr) {
+        return 0;
+    }
     int flag = 0;
     VB_CUDA(cudaMemcpyAsync(&flag, ws.error_flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, current_stream()));
     VB_TRY(sync_stream());

@@ -280,15 +280,19 @@ int tc_candidates(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint3
 // (a count above cap means the list overflowed and lost entries: *overflow_out is set and the caller
 // must not trust the result).  Lists are sized from expected_per_row, the number of columns the caller
 // expects below a row's threshold; lists * cap never exceeds max_per_row.
+// With deferred_flag_dev (two ints the caller zeroed on the stream) the call does not wait for the kernel:
+// bit 0 (a bounded wait gave up) and bit 1 (some list overflowed) are OR-ed into deferred_flag_dev[0] for the
+// caller to read when it next synchronises, and *overflow_out is left false.
 int tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
                        const float* bias_dev, const float* row_thr_dev, uint32_t expected_per_row,
                        uint32_t max_per_row, DevBuf<uint64_t>& out, DevBuf<uint32_t>& out_count, uint32_t* lists_out,
-                       uint32_t* cap_out, bool* overflow_out);
+                       uint32_t* cap_out, bool* overflow_out, int* deferred_flag_dev = nullptr);
 
 // The whole score matrix alpha * <a, b> + bias as fp32 in scores_dev[a.rows][ld] (ld >= b.rows, a
 // multiple of 4, scores_dev 16-byte aligned), from the same tensor-core pipeline.
+// deferred_flag_dev: as for tc_below_threshold.
 int tc_scores(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint32_t n_terms, float alpha,
-              const float* bias_dev, float* scores_dev, uint64_t ld);
+              const float* bias_dev, float* scores_dev, uint64_t ld, int* deferred_flag_dev = nullptr);
 
 // Largest m tc_candidates accepts for the given number of terms.
 uint32_t tc_max_candidates(uint32_t n_terms);
