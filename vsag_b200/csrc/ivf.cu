@@ -1659,7 +1659,7 @@ warp_sort_buffer(uint64_t* buf, uint32_t lane) {
 }
 
 // route_pick_kernel for the common case, one warp per query and no block-wide barrier: a query whose lists hold at
-// most 512 candidates (288 expected for nprobe 64 at a quarter sample) has them sorted through registers, the
+// most 512 candidates (288 expected for nprobe 64) has them sorted through registers, the
 // ncand <= 128 best re-scored exactly, one chain per lane, and sorted again.  handled[q] = 1 tells route_pick_kernel
 // (launched afterwards over all queries) to leave the query alone.
 constexpr uint32_t ROUTE_WARP_KEYS = 512;
@@ -1693,7 +1693,7 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
         }
     }
     const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-    if (lost || total > ROUTE_WARP_KEYS) {
+    if (lost || total > ROUTE_WARP_KEYS || total < ncand) {   // (fewer than ncand: the threshold came out too low)
         if (lane == 0) {
             handled[q] = 0;
         }
@@ -1814,9 +1814,9 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
         }
     }
     __syncthreads();
-    if (s_lost != 0) {
+    if (s_lost != 0 || s_off[lists] < ncand) {
         // One of the query's lists overflowed (its scores lie far from what the centroid sample predicted), so
-        // candidates were lost.  The query is answered from scratch instead: exact distances to every centroid,
+        // candidates were lost -- or the threshold came out so low that fewer than ncand centroids passed.  The query is answered from scratch instead: exact distances to every centroid,
         // the nprobe nearest kept by a streaming selection.  Rare, and decided here, so the host never has to
         // wait for the candidate pass to know.
         BlockSelect sel;
@@ -1986,17 +1986,23 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
         TcOperand a{ws.q_hi.ptr, ws.q_lo.ptr, nq, chunks};
         TcOperand b{ix->c_hi.ptr, ix->c_lo.ptr, nlist, chunks};
         // Large list counts: no score matrix.  The scores against a sample of the centroids (the first
-        // `sample` of them; centroid numbering carries no geometry) give each query a threshold that
-        // at least ncand centroids are known to meet; one pass of the tensor-core kernel over all
-        // centroids then keeps, unsorted, only what scores below it -- about ncand * nlist / sample
-        // per query -- and one small kernel per query orders those and re-scores the best exactly.
-        // (the largest sample that qualifies: the pass over it costs a quarter of the full pass at most, and every
-        // doubling halves what the per-query kernels have to order)
-        uint32_t sample = 0;
-        for (uint32_t s = 4096; s >= 1024 && sample == 0; s /= 2) {
-            const uint64_t expected = static_cast<uint64_t>(ncand) * nlist / s;
+        // `sample` of them; centroid numbering carries no geometry) give each query a threshold; one pass
+        // of the tensor-core kernel over all centroids then keeps, unsorted, only what scores below it --
+        // about rank * nlist / sample per query -- and one small kernel per query orders those and
+        // re-scores the best exactly.
+        // The threshold is the score of rank `rank` in the sample, chosen so that about four times ncand
+        // centroids are expected below it.  With rank = ncand that many are certain; with a smaller sample
+        // and a lower rank they are only very likely, and a query that ends up with fewer than ncand is
+        // answered exactly by route_pick_kernel like one whose lists overflowed.
+        uint32_t sample = 0, rank = 0;
+        for (uint32_t s = 1024; s <= 4096 && sample == 0; s *= 2) {
+            uint64_t r = (4ull * ncand * s + nlist - 1) / nlist;
+            r = r < 16 ? 16 : r;
+            r = r > ncand ? ncand : r;
+            const uint64_t expected = r * nlist / s;
             if (4ull * s <= nlist && s >= 4 * ncand && 5 * expected / 2 <= ROUTE_MAX_PER_ROW) {
                 sample = s;
+                rank = static_cast<uint32_t>(r);
             }
         }
         if (sample != 0 && ncand <= 256) {
@@ -2009,11 +2015,11 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
             // candidate lists overflowed is answered exactly by route_pick_kernel itself.
             VB_TRY(tc_scores(ix->tc, a, bs, 3, alpha, bias, ws.scores.ptr, sample, route_flag));
             VB_TRY(ws.route_thr.reserve(nq));
-            VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>(nq), ROUTE_THREADS, 0, ws.scores.ptr, sample, ncand,
+            VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>(nq), ROUTE_THREADS, 0, ws.scores.ptr, sample, rank,
                       q_dev, ix->dim, ix->c_max_norm.ptr, ws.route_thr.ptr);
             uint32_t lists = 0, cap = 0;
             bool overflow = false;
-            const uint32_t expected = static_cast<uint32_t>(static_cast<uint64_t>(ncand) * nlist / sample);
+            const uint32_t expected = static_cast<uint32_t>(static_cast<uint64_t>(rank) * nlist / sample);
             const uint32_t n_keep = next_pow2(nprobe + ROUTE_THREADS);   // the exact fallback's selection buffer
             VB_TRY(tc_below_threshold(ix->tc, a, b, 3, alpha, bias, ws.route_thr.ptr, expected, ROUTE_MAX_PER_ROW,
                                       ws.route_keys, ws.route_cnt, &lists, &cap, &overflow, route_flag));
