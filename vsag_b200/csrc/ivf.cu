@@ -1664,7 +1664,7 @@ warp_sort_buffer(uint64_t* buf, uint32_t lane) {
 // (launched afterwards over all queries) to leave the query alone.
 constexpr uint32_t ROUTE_WARP_KEYS = 512;
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 5)   // 40 warps per SM: the sort's registers just fit
 route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t dim, const float* __restrict__ centroids,
                        const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
                        uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
@@ -2216,8 +2216,12 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     const bool tc_first = tc_scan && (!(split_phases && pruning) || tc_first_forced), tc_second = tc_scan;
     // ... and when every item is a single query anyway, a warp per item beats a CTA per item (VB200_WARP_FIRST=0: off)
     static const bool warp_first_off = std::getenv("VB200_WARP_FIRST") != nullptr && std::getenv("VB200_WARP_FIRST")[0] == '0';
+    // (the warps rank with the tensor-core scan's integer weight terms when those are prepared anyway, so both
+    // phases nominate with one arithmetic; VB200_FIRST_INT8=0: the SIMT scan's fp32 weights instead)
+    static const bool first_int8 = !(std::getenv("VB200_FIRST_INT8") != nullptr && std::getenv("VB200_FIRST_INT8")[0] == '0');
+    const uint32_t first_dpad32 = (tc_scan && first_int8) ? ix->kchunks * 16 : 0u;
     const bool warp_first = sq8 && split_phases && pruning && !tc_first && !warp_first_off && kscan <= 192 &&
-                            sq8_first_smem_bytes(kscan, ix->dpad) <= 96 * 1024;
+                            sq8_first_smem_bytes(kscan, ix->dpad, first_dpad32) <= 96 * 1024;
     const uint32_t qt_first = warp_first ? 1u : (tc_first ? TCS_QT : static_cast<uint32_t>(qt));
     const uint32_t qt_second = tc_second ? TCS_QT : static_cast<uint32_t>(qt);
     VB_TRY(group_pairs(split_phases ? 0u : 2u, nullptr, qt_first));
@@ -2378,18 +2382,20 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             return 0;
         }
         if (sq8 && warp_items) {
-            const size_t smem = sq8_first_smem_bytes(p.k, ix->dpad);
+            const bool int8 = first_dpad32 != 0;
+            const size_t smem = sq8_first_smem_bytes(p.k, ix->dpad, first_dpad32);
+            auto kernel = int8 ? ivf_sq8_first_kernel<true> : ivf_sq8_first_kernel<false>;
             if (smem > 40 * 1024) {
-                VB_CUDA(cudaFuncSetAttribute(ivf_sq8_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem)));
+                VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             }
             int per_sm = 0;
-            VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ivf_sq8_first_kernel, SQ8_FIRST_WARPS * 32, smem));
+            VB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SQ8_FIRST_WARPS * 32, smem));
             if (per_sm < 1) {
                 VB_FAIL(VB200_INTERNAL_ERROR, "the first-phase scan does not fit an SM with %zu bytes of shared memory", smem);
             }
-            VB_LAUNCH(ivf_sq8_first_kernel, static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(per_sm),
-                      SQ8_FIRST_WARPS * 32, smem, p);
+            VB_LAUNCH(kernel, static_cast<uint32_t>(sm_count()) * static_cast<uint32_t>(per_sm), SQ8_FIRST_WARPS * 32, smem, p,
+                      int8 ? ws.qw8.ptr : static_cast<const int8_t*>(nullptr),
+                      int8 ? ws.qscale.ptr : static_cast<const float*>(nullptr), first_dpad32);
             return 0;
         }
         if (sq8) {

@@ -664,8 +664,10 @@ ivf_sq8_scan_kernel(const ScanParams p) {
 // rows.  A CTA per item spends most of its time in barriers and set-up, so here a warp takes an item by itself:
 // its lanes own two rows each per round, the query's weights sit in the warp's slice of shared memory (every
 // lane reads the same word: a broadcast), candidates that beat the bound are appended through a ballot, and
-// the warp sorts its own small buffer when it fills.  The arithmetic per row is that of sq8_tile_dots_single,
-// so the survivors are the ones the CTA kernel would keep.
+// the warp sorts its own small buffer when it fills.  The arithmetic per row is that of sq8_tile_dots_single
+// (INT8 false), so the survivors are the ones the CTA kernel would keep -- or, with INT8, that of the tensor-core
+// scan: the weights' three signed-byte terms against the codes as signed bytes (code ^ 0x80 = code - 128), three
+// exact integer dot products per four dimensions (dp4a), combined as that kernel's epilogue combines them.
 constexpr int SQ8_FIRST_WARPS = 8;
 
 __host__ __device__ inline uint32_t
@@ -677,18 +679,28 @@ sq8_first_cap(uint32_t k) {
     return c;
 }
 
-__host__ __device__ inline size_t
-sq8_first_smem_bytes(uint32_t k, uint32_t dpad) {
-    return static_cast<size_t>(SQ8_FIRST_WARPS) * (static_cast<size_t>(sq8_first_cap(k)) * 8 + static_cast<size_t>(dpad) * 4);
+// bytes of a warp's weight slot: the fp32 weights, or the three signed-byte terms of the tensor-core scan's split
+__host__ __device__ inline uint32_t
+sq8_first_weight_bytes(uint32_t dpad, uint32_t dpad32) {
+    const uint32_t f = dpad * 4, b = dpad32 * 3;
+    return ((f > b ? f : b) + 15u) & ~15u;
 }
 
+__host__ __device__ inline size_t
+sq8_first_smem_bytes(uint32_t k, uint32_t dpad, uint32_t dpad32) {
+    return static_cast<size_t>(SQ8_FIRST_WARPS) * (static_cast<size_t>(sq8_first_cap(k)) * 8 + sq8_first_weight_bytes(dpad, dpad32));
+}
+
+template <bool INT8>
 __global__ void __launch_bounds__(SQ8_FIRST_WARPS * 32)
-ivf_sq8_first_kernel(const ScanParams p) {
+ivf_sq8_first_kernel(const ScanParams p, const int8_t* __restrict__ qw8, const float* __restrict__ qscale, uint32_t dpad32) {
     extern __shared__ __align__(16) unsigned char smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cap = sq8_first_cap(p.k), k = p.k, dpad = p.dpad;
     uint64_t* kb = reinterpret_cast<uint64_t*>(smem) + static_cast<size_t>(warp) * cap;
-    float* w_s = reinterpret_cast<float*>(smem + static_cast<size_t>(SQ8_FIRST_WARPS) * cap * 8) + static_cast<size_t>(warp) * dpad;
+    unsigned char* w_raw = smem + static_cast<size_t>(SQ8_FIRST_WARPS) * cap * 8 +
+                           static_cast<size_t>(warp) * sq8_first_weight_bytes(dpad, dpad32);
+    float* w_s = reinterpret_cast<float*>(w_raw);
     const uint32_t n_items = p.item_off[0][p.nlist];
     const uint32_t lt_mask = (1u << lane) - 1u;
 
@@ -716,8 +728,16 @@ ivf_sq8_first_kernel(const ScanParams p) {
             uint32_t thr = p.thr_g[q];
             float thrq = (thr >= 0xFF800000u ? INFINITY : ordered_to_float(thr)) - qa;
             uint32_t cnt = 0;
+            float cq = 0.f;   // INT8: coef_c * the query's weight scale
             __syncwarp();
-            {
+            if (INT8) {
+                const uint4* src = reinterpret_cast<const uint4*>(qw8 + static_cast<uint64_t>(q) * 3 * dpad32);
+                uint4* dst = reinterpret_cast<uint4*>(w_raw);
+                for (uint32_t i = lane; i < (3 * dpad32) >> 4; i += 32) {
+                    dst[i] = __ldg(src + i);
+                }
+                cq = p.coef_c * __ldg(qscale + q);
+            } else {
                 const float4* src = reinterpret_cast<const float4*>(p.qw + static_cast<uint64_t>(q) * dpad);
                 float4* dst = reinterpret_cast<float4*>(w_s);
                 for (uint32_t i = lane; i < (dpad >> 2); i += 32) {
@@ -752,9 +772,38 @@ ivf_sq8_first_kernel(const ScanParams p) {
                 float a0 = 0.f, a1 = 0.f;
                 uint4 n0 = __ldg(reinterpret_cast<const uint4*>(c0));
                 uint4 n1 = __ldg(reinterpret_cast<const uint4*>(c1));
+                if (INT8) {
+                    int32_t s0[3] = {0, 0, 0}, s1[3] = {0, 0, 0};
+#pragma unroll 1
+                    for (uint32_t c = 0; c < dpad; c += 16) {
+                        const uint4 u0 = n0, u1 = n1;
+                        if (c + 16 < dpad) {
+                            n0 = __ldg(reinterpret_cast<const uint4*>(c0 + c + 16));
+                            n1 = __ldg(reinterpret_cast<const uint4*>(c1 + c + 16));
+                        }
+                        const int32_t x0[4] = {static_cast<int32_t>(u0.x ^ 0x80808080u), static_cast<int32_t>(u0.y ^ 0x80808080u),
+                                               static_cast<int32_t>(u0.z ^ 0x80808080u), static_cast<int32_t>(u0.w ^ 0x80808080u)};
+                        const int32_t x1[4] = {static_cast<int32_t>(u1.x ^ 0x80808080u), static_cast<int32_t>(u1.y ^ 0x80808080u),
+                                               static_cast<int32_t>(u1.z ^ 0x80808080u), static_cast<int32_t>(u1.w ^ 0x80808080u)};
+#pragma unroll
+                        for (int t = 0; t < 3; ++t) {
+                            const uint4 wv = *reinterpret_cast<const uint4*>(w_raw + t * dpad32 + c);
+                            const int32_t wt[4] = {static_cast<int32_t>(wv.x), static_cast<int32_t>(wv.y), static_cast<int32_t>(wv.z),
+                                                   static_cast<int32_t>(wv.w)};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                s0[t] = __dp4a(x0[j], wt[j], s0[t]);
+                                s1[t] = __dp4a(x1[j], wt[j], s1[t]);
+                            }
+                        }
+                    }
+                    // sum_d w_d (code_d - 128) / s = A1 + (254 A2 + A3) / 254^2, as the tensor-core scan's epilogue
+                    a0 = fmaf(static_cast<float>(s0[1] * 254 + s0[2]), 1.0f / 64516.0f, static_cast<float>(s0[0]));
+                    a1 = fmaf(static_cast<float>(s1[1] * 254 + s1[2]), 1.0f / 64516.0f, static_cast<float>(s1[0]));
+                }
                 const float4* wrow = reinterpret_cast<const float4*>(w_s);
 #pragma unroll 1
-                for (uint32_t c = 0; c < dpad; c += 16, wrow += 4) {
+                for (uint32_t c = 0; !INT8 && c < dpad; c += 16, wrow += 4) {
                     const uint4 u0 = n0, u1 = n1;
                     if (c + 16 < dpad) {
                         n0 = __ldg(reinterpret_cast<const uint4*>(c0 + c + 16));
@@ -782,7 +831,7 @@ ivf_sq8_first_kernel(const ScanParams p) {
                     float partial = 0.f;
                     bool pass = false;
                     if (valid) {
-                        partial = fmaf(p.coef_c, h == 0 ? a0 : a1, p.coef_b * __ldg(p.code_norm + pos));
+                        partial = fmaf(INT8 ? cq : p.coef_c, h == 0 ? a0 : a1, p.coef_b * __ldg(p.code_norm + pos));
                         pass = partial <= thrq;
                         if (pass && p.filter_pos_inner != nullptr && scan_row_filtered(p, pos)) {
                             pass = false;

@@ -291,6 +291,7 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t kchunks = tp.kchunks;
     const uint32_t row_bytes = kchunks * 16;                 // bytes of one code row in the tiled copy
+    const bool wide_sums = row_bytes > 256;                  // an integer sum may pass 2^22
     const uint32_t group_bytes = kchunks * 128;              // one 8-row group
     const uint32_t tile_bytes = TCS_ROWS * row_bytes;
     const uint32_t b_bytes = TCS_N * row_bytes;
@@ -578,11 +579,13 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                 const float xb = p.coef_b * __ldg(p.code_norm + pos);
                 uint32_t pend = 0;   // bit j: this row is a candidate of query slot q_first + j that is not stored yet
                 uint32_t a1[16], a2[16], a3[16];
-                // sum_d w_d (code_d - 128) / s = A1 + (254 A2 + A3) / 254^2; A1 < 2^22 converts exactly through
-                // the float whose integer image is 1.5 * 2^23 + A1
+                // sum_d w_d (code_d - 128) / s = A1 + (254 A2 + A3) / 254^2; |A1| < 2^22 (certain up to 256 dimensions:
+                // 127 * 128 * 256 < 2^22) converts exactly through the float whose integer image is 1.5 * 2^23 + A1,
+                // longer rows take the conversion instruction
                 auto partial_of = [&](int j, float cqj) -> float {
                     const int32_t low = static_cast<int32_t>(a2[j]) * 254 + static_cast<int32_t>(a3[j]);
-                    const float hi = __int_as_float(static_cast<int32_t>(a1[j]) + 0x4B400000) - 12582912.0f;
+                    const float hi = wide_sums ? static_cast<float>(static_cast<int32_t>(a1[j]))
+                                               : __int_as_float(static_cast<int32_t>(a1[j]) + 0x4B400000) - 12582912.0f;
                     const float f = fmaf(static_cast<float>(low), 1.0f / 64516.0f, hi);
                     return fmaf(cqj, f, xb);
                 };
