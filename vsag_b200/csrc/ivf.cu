@@ -934,19 +934,22 @@ pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t n
 
 // After the first phase: drop[e] = 1 for every second-phase (query, list) pair that the list's
 // covering balls put beyond the query's bound (the test the SIMT scan kernel makes per tile, made here
-// once per pair so that pruned pairs never become work items).  One thread per pair: first the ball
-// around the list's centroid, whose distance from the query routing has computed exactly -- on
-// clustered data that settles most pairs without reading a ball centre -- then the list's covering
-// balls one after the other until one of them cannot exclude the list.  The code bytes of the dropped
-// pairs still count as algorithmic scan volume (scalars[0]).
+// once per pair so that pruned pairs never become work items).  Two steps per warp.  Every lane applies
+// the cheap test to its own pair: the ball around the list's centroid, whose distance from the query
+// routing has computed exactly -- on clustered data that settles most pairs without reading a ball
+// centre.  The pairs that pass it are then measured against the list's covering balls, one ball after the
+// other until one of them cannot exclude the list, four pairs at a time with eight lanes per pair, so the
+// loads of a step cover 128 contiguous bytes of each centre instead of 32 separate lines; sums are reduced
+// within the eight lanes.  The code bytes of the dropped pairs still count as algorithmic scan volume
+// (scalars[0]).
 __device__ __forceinline__ float
-pair_ball_dot(const float* __restrict__ qv, const float* __restrict__ cv, uint32_t dim, int metric) {
+pair_ball_dot8(const float* __restrict__ qv, const float* __restrict__ cv, uint32_t dim, int metric, uint32_t part,
+               uint32_t gmask) {
     float dot = 0.f;
     if ((dim & 3u) == 0 && ((reinterpret_cast<uintptr_t>(qv) | reinterpret_cast<uintptr_t>(cv)) & 15u) == 0) {
         const float4* q4 = reinterpret_cast<const float4*>(qv);
         const float4* c4 = reinterpret_cast<const float4*>(cv);
-#pragma unroll 4
-        for (uint32_t i = 0; i < (dim >> 2); ++i) {
+        for (uint32_t i = part; i < (dim >> 2); i += 8) {
             const float4 x = __ldg(q4 + i), c = __ldg(c4 + i);
             if (metric == 0) {
                 float t = x.x - c.x;
@@ -965,7 +968,7 @@ pair_ball_dot(const float* __restrict__ qv, const float* __restrict__ cv, uint32
             }
         }
     } else {
-        for (uint32_t d = 0; d < dim; ++d) {
+        for (uint32_t d = part; d < dim; d += 8) {
             const float x = __ldg(qv + d), c = __ldg(cv + d);
             if (metric == 0) {
                 const float t = x - c;
@@ -975,77 +978,121 @@ pair_ball_dot(const float* __restrict__ qv, const float* __restrict__ cv, uint32
             }
         }
     }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        dot += __shfl_xor_sync(gmask, dot, o);
+    }
     return dot;
 }
 
 __global__ void __launch_bounds__(256)
 pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
-                 const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
-                 const uint32_t* __restrict__ list_off, const float* __restrict__ queries, uint32_t dim,
-                 const float* __restrict__ ball_centre, const float* __restrict__ ball_radius,
-                 const uint32_t* __restrict__ ball_count, const uint32_t* __restrict__ thr, int metric,
-                 uint32_t code_size, const float* __restrict__ probe_dists, const float* __restrict__ list_radius,
-                 uint8_t* __restrict__ drop, unsigned long long* __restrict__ scalars) {
+                         const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
+                         const uint32_t* __restrict__ list_off, const float* __restrict__ queries, uint32_t dim,
+                         const float* __restrict__ ball_centre, const float* __restrict__ ball_radius,
+                         const uint32_t* __restrict__ ball_count, const uint32_t* __restrict__ thr, int metric,
+                         uint32_t code_size, const float* __restrict__ probe_dists, const float* __restrict__ list_radius,
+                         uint8_t* __restrict__ drop, unsigned long long* __restrict__ scalars) {
     __shared__ unsigned long long s_bytes;
     if (threadIdx.x == 0) {
         s_bytes = 0;
     }
     __syncthreads();
     const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    unsigned long long my_bytes = 0;   // code bytes of the pair if it is dropped
+    const uint32_t lane = threadIdx.x & 31u;
+    unsigned long long my_bytes = 0;   // code bytes of the pairs this lane reports dropped
+    // step 1: the lane's own pair
+    bool need_balls = false;
+    uint32_t q = 0;
+    int32_t l = 0;
+    float bound = 0.f;
     if (e < total) {
-        const uint32_t q = static_cast<uint32_t>(e / nprobe);
+        q = static_cast<uint32_t>(e / nprobe);
         const uint32_t pr = static_cast<uint32_t>(e % nprobe);
-        const int32_t l = probes[e];
+        l = probes[e];
         const uint32_t t = thr[q];
         bool dropped = false;
         if (pr != first_live[q] && probe_is_live(l, nlist, rank, world, list_off) && t <= float_to_ordered(INFINITY)) {
-            const float bound = ordered_to_float(t);
-            const float* qv = queries + static_cast<uint64_t>(q) * dim;
-            const float qq = metric != 0 ? pair_ball_dot(qv, qv, dim, 1) : 0.f;
+            bound = ordered_to_float(t);
             bool beyond = false;   // the ball around the centroid already excludes the list
-            if (probe_dists != nullptr) {
+            if (probe_dists != nullptr && metric == 0) {
                 const float dc = __ldg(probe_dists + e), big_r = __ldg(list_radius + l);
-                if (metric == 0) {
-                    const float gap = sqrtf(dc) - big_r;
-                    const float lower = gap > 0.f ? gap * gap : 0.f;
-                    beyond = lower > bound * 1.001f + 1e-4f * dc;
-                } else {
-                    const float lower = dc - sqrtf(qq) * big_r;   // dc = 1 - <q, centroid>
-                    beyond = lower > bound + 1e-3f * (fabsf(bound) + fabsf(1.0f - dc) + 1.0f);
-                }
+                const float gap = sqrtf(dc) - big_r;
+                const float lower = gap > 0.f ? gap * gap : 0.f;
+                beyond = lower > bound * 1.001f + 1e-4f * dc;
             }
-            bool any = false;      // some ball may hold a row within the bound
-            if (!beyond) {
-                const uint32_t n_balls = __ldg(ball_count + l);
-                const float* cv = ball_centre + static_cast<uint64_t>(l) * SQ8_BALLS * dim;
-                for (uint32_t j = 0; j < n_balls && !any; ++j, cv += dim) {
-                    const float r = __ldg(ball_radius + static_cast<uint64_t>(l) * SQ8_BALLS + j);
-                    if (r >= 0.f) {
-                        // slack: the distances compared here and in the scan differ in rounding only
-                        const float dot = pair_ball_dot(qv, cv, dim, metric);
-                        if (metric == 0) {
-                            const float gap = sqrtf(dot) - r;
-                            const float lower = gap > 0.f ? gap * gap : 0.f;
-                            any = !(lower > bound * 1.001f + 1e-4f * dot);
-                        } else {
-                            const float lower = 1.0f - dot - sqrtf(qq) * r;
-                            any = !(lower > bound + 1e-3f * (fabsf(bound) + fabsf(dot) + 1.0f));
-                        }
-                    }
-                }
-            }
-            dropped = !any;
+            dropped = beyond;
+            need_balls = !beyond;
+        }
+        if (!need_balls) {
+            drop[e] = dropped ? 1 : 0;
             if (dropped) {
                 my_bytes = static_cast<unsigned long long>(list_off[l + 1] - list_off[l]) * code_size;
             }
         }
-        drop[e] = dropped ? 1 : 0;
+    }
+    // step 2: the warp's remaining pairs, four at a time
+    uint32_t todo = __ballot_sync(0xffffffffu, need_balls);
+    const uint32_t group = lane >> 3, part = lane & 7u;
+    const uint32_t gmask = 0xFFu << (lane & 24u);
+    while (todo != 0) {
+        // the group's pair: the group-th lowest set bit of todo
+        uint32_t rest = todo;
+        for (uint32_t g = 0; g < group && rest != 0; ++g) {
+            rest &= rest - 1;
+        }
+        const bool have = rest != 0;
+        const uint32_t src = have ? static_cast<uint32_t>(__ffs(rest)) - 1u : 0u;
+        const uint32_t pq = __shfl_sync(0xffffffffu, q, src);
+        const int32_t pl = __shfl_sync(0xffffffffu, l, src);
+        const float pbound = __shfl_sync(0xffffffffu, bound, src);
+        if (have) {
+            const float* qv = queries + static_cast<uint64_t>(pq) * dim;
+            const float qq = metric != 0 ? pair_ball_dot8(qv, qv, dim, 1, part, gmask) : 0.f;
+            bool beyond = false;
+            if (probe_dists != nullptr && metric != 0) {
+                const uint64_t pe = e - lane + src;
+                const float dc = __ldg(probe_dists + pe), big_r = __ldg(list_radius + pl);
+                const float lower = dc - sqrtf(qq) * big_r;   // dc = 1 - <q, centroid>
+                beyond = lower > pbound + 1e-3f * (fabsf(pbound) + fabsf(1.0f - dc) + 1.0f);
+            }
+            bool any = false;      // some ball may hold a row within the bound
+            if (!beyond) {
+                const uint32_t n_balls = __ldg(ball_count + pl);
+                const float* cv = ball_centre + static_cast<uint64_t>(pl) * SQ8_BALLS * dim;
+                for (uint32_t j = 0; j < n_balls && !any; ++j, cv += dim) {
+                    const float r = __ldg(ball_radius + static_cast<uint64_t>(pl) * SQ8_BALLS + j);
+                    if (r >= 0.f) {
+                        // slack: the distances compared here and in the scan differ in rounding only
+                        const float dot = pair_ball_dot8(qv, cv, dim, metric, part, gmask);
+                        if (metric == 0) {
+                            const float gap = sqrtf(dot) - r;
+                            const float lower = gap > 0.f ? gap * gap : 0.f;
+                            any = !(lower > pbound * 1.001f + 1e-4f * dot);
+                        } else {
+                            const float lower = 1.0f - dot - sqrtf(qq) * r;
+                            any = !(lower > pbound + 1e-3f * (fabsf(pbound) + fabsf(dot) + 1.0f));
+                        }
+                    }
+                }
+            }
+            if (part == 0) {
+                const uint64_t pe = e - lane + src;
+                drop[pe] = any ? 0 : 1;
+                if (!any) {
+                    my_bytes += static_cast<unsigned long long>(list_off[pl + 1] - list_off[pl]) * code_size;
+                }
+            }
+        }
+        // the four lowest set bits are done
+        for (int g = 0; g < 4 && todo != 0; ++g) {
+            todo &= todo - 1;
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         my_bytes += __shfl_xor_sync(0xffffffffu, my_bytes, o);
     }
-    if ((threadIdx.x & 31u) == 0 && my_bytes != 0) {
+    if (lane == 0 && my_bytes != 0) {
         atomicAdd(&s_bytes, my_bytes);
     }
     __syncthreads();
@@ -2355,11 +2402,11 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             VB_CUDA(cudaMemsetAsync(prof_buf.ptr, 0, static_cast<size_t>(sm_count()) * 2 * 24 * sizeof(unsigned long long), st));
             tp.prof = prof_buf.ptr;
 #endif
-            VB_CUDA(cudaFuncSetAttribute(ivf_sq8_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem)));
-            VB_CUDA(cudaFuncSetAttribute(ivf_sq8_scan_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+            auto tc_kernel = ix->kchunks * 16 > 256 ? ivf_sq8_scan_tc_kernel<true> : ivf_sq8_scan_tc_kernel<false>;
+            VB_CUDA(cudaFuncSetAttribute(tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            VB_CUDA(cudaFuncSetAttribute(tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                          cudaSharedmemCarveoutMaxShared));
-            VB_LAUNCH(ivf_sq8_scan_tc_kernel, static_cast<uint32_t>(sm_count()) * per_sm, TCS_THREADS, smem, tp);
+            VB_LAUNCH(tc_kernel, static_cast<uint32_t>(sm_count()) * per_sm, TCS_THREADS, smem, tp);
 #ifdef VB200_TCS_PROFILE
             {
                 const size_t n_cta = static_cast<size_t>(sm_count()) * per_sm;

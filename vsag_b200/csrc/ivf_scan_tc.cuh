@@ -282,6 +282,8 @@ tcs_fetch_item(const ScanParams& p, uint32_t n0, uint32_t n1, TcsItem* out) {
 // everything else: it takes work items from the queue one ahead, stages the next item's query
 // constants and its B operand (two B buffers) and copies code tiles as stages come free, also across
 // the boundary between two items, so an item starts with its operands already in shared memory.
+// WIDE: code rows longer than 256 bytes in the tiled copy (see the conversion of the first integer sum below).
+template <bool WIDE>
 __global__ void __launch_bounds__(TCS_THREADS, 2)
 ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     extern __shared__ __align__(1024) unsigned char tcs_smem[];
@@ -291,7 +293,7 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t kchunks = tp.kchunks;
     const uint32_t row_bytes = kchunks * 16;                 // bytes of one code row in the tiled copy
-    const bool wide_sums = row_bytes > 256;                  // an integer sum may pass 2^22
+    constexpr bool wide_sums = WIDE;                         // rows past 256 bytes: an integer sum may pass 2^22
     const uint32_t group_bytes = kchunks * 128;              // one 8-row group
     const uint32_t tile_bytes = TCS_ROWS * row_bytes;
     const uint32_t b_bytes = TCS_N * row_bytes;
