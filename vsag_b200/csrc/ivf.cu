@@ -89,6 +89,7 @@ struct SearchWorkspace {
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
     DevBuf<uint64_t> keys2;     // [nq x k] after rerank
+    DevBuf<uint8_t> slot_written;   // [nq x nprobe] SQ8: which slots of `part` a scan kernel wrote
     DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases, [3] bytes read, [4] tensor-core scan error flag,
                                 // [5] the deadline passed, [6] the deadline (%globaltimer value; written by deadline_stamp_kernel)
     bool opt_no_reorder = false;   // search options of the running call (vb200_search_options)
@@ -1254,7 +1255,7 @@ pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t
 // Per query: the k smallest of its `per_query` partial keys, ascending.
 __global__ void __launch_bounds__(256)
 merge_keys_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_t k, uint32_t cap,
-                  uint64_t* __restrict__ out) {
+                  uint64_t* __restrict__ out, const uint8_t* __restrict__ slot_written, uint32_t slot_keys) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
     uint32_t* state = reinterpret_cast<uint32_t*>(keys + cap);
@@ -1265,7 +1266,9 @@ merge_keys_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_
         sel.make_room(blockDim.x);
         uint64_t thr = sel.threshold();
         uint64_t i = base + threadIdx.x;
-        if (i < per_query) {
+        // (with slot flags only the slots a scan kernel wrote hold keys; the others were never initialised)
+        if (i < per_query &&
+            (slot_written == nullptr || slot_written[(static_cast<uint64_t>(blockIdx.x) * per_query + i) / slot_keys] != 0)) {
             uint64_t key = __ldg(src + i);
             if (key != KEY_INF) {
                 sel.offer(key, thr);
@@ -1380,14 +1383,15 @@ tag_partials_kernel(const uint64_t* __restrict__ keys, uint32_t parts, uint64_t 
 }
 
 static int
-launch_merge(const uint64_t* part, uint64_t nq, uint64_t per_query, uint32_t k, uint64_t* out) {
+launch_merge(const uint64_t* part, uint64_t nq, uint64_t per_query, uint32_t k, uint64_t* out,
+             const uint8_t* slot_written = nullptr, uint32_t slot_keys = 1) {
     uint32_t cap = next_pow2(k + 256);
     size_t smem = cap * sizeof(uint64_t) + 16;
     if (smem > 48 * 1024) {
         VB_CUDA(cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
     }
-    VB_LAUNCH(merge_keys_kernel, static_cast<uint32_t>(nq), 256, smem, part, per_query, k, cap, out);
+    VB_LAUNCH(merge_keys_kernel, static_cast<uint32_t>(nq), 256, smem, part, per_query, k, cap, out, slot_written, slot_keys);
     return 0;
 }
 
@@ -2171,6 +2175,54 @@ launch_scan(Kernel kernel, const ScanParams& p, size_t smem) {
     return 0;
 }
 
+// VB200_SCAN_PROFILE=1: device time of the scan's sections from CUDA events, averaged over 20 calls after the
+// first three and printed to stderr (a diagnostic; the events are recorded on the search's stream and read at
+// the next call, after that call's own work has been queued behind them).
+struct ScanProfile {
+    static constexpr int N = 8;
+    cudaEvent_t ev[N + 1] = {};
+    double acc[N] = {};
+    int calls = 0, pending = 0;
+    bool on = false, init = false;
+    void begin(cudaStream_t st) {
+        if (!init) {
+            const char* e = std::getenv("VB200_SCAN_PROFILE");
+            on = e != nullptr && e[0] == '1';
+            init = true;
+            if (on) {
+                for (auto& x : ev) {
+                    cudaEventCreate(&x);
+                }
+            }
+        }
+        if (!on) {
+            return;
+        }
+        if (pending > 0 && cudaEventSynchronize(ev[pending]) == cudaSuccess && ++calls > 3) {
+            for (int i = 0; i < pending; ++i) {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+                acc[i] += ms;
+            }
+            if ((calls - 3) % 20 == 0) {
+                std::fprintf(stderr, "scan-prof: prep %.3f first %.3f exchange %.3f drop %.3f group %.3f second %.3f merge %.3f tail %.3f ms\n",
+                             acc[0] / 20, acc[1] / 20, acc[2] / 20, acc[3] / 20, acc[4] / 20, acc[5] / 20, acc[6] / 20, acc[7] / 20);
+                for (auto& a : acc) {
+                    a = 0;
+                }
+            }
+        }
+        pending = 0;
+        cudaEventRecord(ev[0], st);
+    }
+    void mark(cudaStream_t st) {
+        if (on && pending < N) {
+            cudaEventRecord(ev[++pending], st);
+        }
+    }
+};
+static ScanProfile g_scan_profile;
+
 // Scans the probed lists of every query and leaves, per query, the kscan best as keys
 // (payload = inner id) in ws.keys.
 static int
@@ -2212,9 +2264,16 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         VB_TRY(ws.merged.reserve(nq * kscan));
     }
     cudaStream_t st = current_stream();
+    g_scan_profile.begin(st);
     VB_CUDA(cudaMemsetAsync(ws.scalars.ptr, 0, 6 * sizeof(uint64_t), st));   // not [6]: the deadline is stamped before routing
     VB_CUDA(cudaMemsetAsync(ws.thr.ptr, 0xFF, nq * sizeof(uint32_t), st));
-    VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
+    if (sq8) {
+        // the SQ8 kernels flag the slots they write: one byte per (query, probe) to clear instead of the slots themselves
+        VB_TRY(ws.slot_written.reserve(total));
+        VB_CUDA(cudaMemsetAsync(ws.slot_written.ptr, 0, total, st));
+    } else {
+        VB_CUDA(cudaMemsetAsync(ws.part.ptr, 0xFF, total * kscan * sizeof(uint64_t), st));
+    }
     const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
     VB_TRY(ws.first_live.reserve(nq));
     VB_LAUNCH(first_live_kernel, static_cast<uint32_t>((nq + 255) / 256), 256, 0, probes_dev, nq, nprobe, nlist,
@@ -2284,6 +2343,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.cap = scan_cap;
     p.thr_g = ws.thr.ptr;
     p.part = ws.part.ptr;
+    p.slot_written = sq8 ? ws.slot_written.ptr : nullptr;
     p.queries = q_dev;
     p.qw = ws.qw.ptr;
     p.qa = ws.qa.ptr;
@@ -2352,6 +2412,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                   tc_scan ? ws.qw8.ptr : nullptr, tc_scan ? ws.qscale.ptr : nullptr);
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_begin, st));
+    g_scan_profile.mark(st);   // prep
     auto launch_phases = [&](uint32_t first, uint32_t count, uint32_t queue_slot, bool on_tensor_cores,
                              bool warp_items = false) -> int {
         for (uint32_t i = 0; i < 2; ++i) {
@@ -2431,7 +2492,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         if (sq8 && warp_items) {
             const bool int8 = first_dpad32 != 0;
             const size_t smem = sq8_first_smem_bytes(p.k, ix->dpad, first_dpad32);
-            auto kernel = int8 ? ivf_sq8_first_kernel<true> : ivf_sq8_first_kernel<false>;
+            auto kernel = int8 ? ivf_sq8_first_kernel<true, 3> : ivf_sq8_first_kernel<false, 2>;   // rows per lane: measured best
             if (smem > 40 * 1024) {
                 VB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             }
@@ -2483,6 +2544,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     p.order = ix->scan_order.ptr;
     if (split_phases) {
         VB_TRY(launch_phases(0, 1, 1, tc_first, warp_first));
+        g_scan_profile.mark(st);   // first
         if (ws.exchange != nullptr) {
             // Sharded search: after the owner of each query's nearest list has scanned it, the
             // shards agree on the tightest bound any of them found, so the remaining lists are
@@ -2498,6 +2560,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
             }
             VB_LAUNCH(bounds_from_float_kernel, qblocks, 256, 0, ws.bounds.ptr, nq, ws.thr.ptr);
         }
+        g_scan_profile.mark(st);   // exchange
         const uint8_t* drop = nullptr;
         if (pruning) {
             VB_TRY(ws.pair_drop.reserve(total));
@@ -2508,15 +2571,18 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
                       ws.pair_drop.ptr, reinterpret_cast<unsigned long long*>(ws.scalars.ptr));
             drop = ws.pair_drop.ptr;
         }
+        g_scan_profile.mark(st);   // drop
         VB_TRY(group_pairs(1u, drop, qt_second));
+        g_scan_profile.mark(st);   // group
         VB_TRY(launch_phases(1, 1, 2, tc_second));
+        g_scan_profile.mark(st);   // second
     } else {
         VB_TRY(launch_phases(0, n_phases, 1, tc_first));
     }
     VB_CUDA(cudaEventRecord(ix->ev_scan_end, st));
     ix->scan_timed = true;
     if (sq8) {
-        VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.merged.ptr));
+        VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.merged.ptr, ws.slot_written.ptr, kscan));
         uint32_t n2 = next_pow2(kscan < 2 ? 2 : kscan);
         VB_LAUNCH(sq8_rescore_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev, ix->dim,
                   ix->codes.ptr, ix->code_stride, ix->lower.ptr, ix->diff.ptr, ws.merged.ptr, kscan, n2,
@@ -2528,6 +2594,7 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     const uint64_t nkeys = nq * kfinal;
     VB_LAUNCH(keys_pos_to_inner_kernel, static_cast<uint32_t>((nkeys + 255) / 256), 256, 0, ws.keys.ptr,
               nkeys, ix->pos_inner.ptr);
+    g_scan_profile.mark(st);   // merge
     return 0;
 }
 

@@ -68,6 +68,8 @@ struct ScanParams {
     uint32_t cap;                // per-query candidate buffer, power of two >= k + SCAN_THREADS
     uint32_t* thr_g;             // [nq] global bound, ordered distance
     uint64_t* part;              // [slots x k] partial results
+    uint8_t* slot_written;       // [slots] set to 1 by whoever writes a slot of `part`, or null: then the caller has
+                                 // filled `part` with KEY_INF beforehand and reads all of it
     const float* queries;        // RaBitQ: [nq x (dim + 1)] processed queries
     const float* qw;             // SQ8: [nq x dpad] weights q_d * diff_d / 255, zero padded
     const float* qa;             // SQ8: [nq] per-query constant of the distance
@@ -216,12 +218,13 @@ struct TileSelect {
     // End of the item: write each query's (at most k) best to its slot and publish the bound.
     // Fewer than k survivors are written unsorted: the merge does not need order.
     __device__ __forceinline__ void
-    finish(int nqt, uint64_t* part, uint32_t* thr_g) {
-        finish_w(nqt, part, thr_g, threadIdx.x >> 5, threadIdx.x & 31, SCAN_WARPS);
+    finish(int nqt, uint64_t* part, uint32_t* thr_g, uint8_t* written = nullptr) {
+        finish_w(nqt, part, thr_g, threadIdx.x >> 5, threadIdx.x & 31, SCAN_WARPS, written);
     }
 
     __device__ __forceinline__ void
-    finish_w(int nqt, uint64_t* part, uint32_t* thr_g, uint32_t warp, uint32_t lane, uint32_t nwarps) {
+    finish_w(int nqt, uint64_t* part, uint32_t* thr_g, uint32_t warp, uint32_t lane, uint32_t nwarps,
+             uint8_t* written = nullptr) {
         for (int qi = static_cast<int>(warp); qi < nqt; qi += static_cast<int>(nwarps)) {
             if (cnt[qi] >= k) {
                 compact(qi, lane);
@@ -234,6 +237,9 @@ struct TileSelect {
             }
             if (lane == 0 && c >= k) {
                 atomicMin(thr_g + qidx[qi], static_cast<uint32_t>(kq[k - 1] >> 32));
+            }
+            if (lane == 0 && written != nullptr) {
+                written[slot[qi]] = 1;
             }
         }
     }
@@ -656,13 +662,13 @@ ivf_sq8_scan_kernel(const ScanParams p) {
                 }
             }
         }
-        ts.finish(nqt, p.part, p.thr_g);
+        ts.finish(nqt, p.part, p.thr_g, p.slot_written);
     }
 }
 
 // The first phase when it runs alone: every work item is one query against its nearest list, a few hundred
 // rows.  A CTA per item spends most of its time in barriers and set-up, so here a warp takes an item by itself:
-// its lanes own two rows each per round, the query's weights sit in the warp's slice of shared memory (every
+// its lanes own NR rows each per round, the query's weights sit in the warp's slice of shared memory (every
 // lane reads the same word: a broadcast), candidates that beat the bound are appended through a ballot, and
 // the warp sorts its own small buffer when it fills.  The arithmetic per row is that of sq8_tile_dots_single
 // (INT8 false), so the survivors are the ones the CTA kernel would keep -- or, with INT8, that of the tensor-core
@@ -691,7 +697,7 @@ sq8_first_smem_bytes(uint32_t k, uint32_t dpad, uint32_t dpad32) {
     return static_cast<size_t>(SQ8_FIRST_WARPS) * (static_cast<size_t>(sq8_first_cap(k)) * 8 + sq8_first_weight_bytes(dpad, dpad32));
 }
 
-template <bool INT8>
+template <bool INT8, int NR = 2>
 __global__ void __launch_bounds__(SQ8_FIRST_WARPS * 32)
 ivf_sq8_first_kernel(const ScanParams p, const int8_t* __restrict__ qw8, const float* __restrict__ qscale, uint32_t dpad32) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -764,27 +770,55 @@ ivf_sq8_first_kernel(const ScanParams p, const int8_t* __restrict__ qw8, const f
                     cnt = k;
                 }
             };
-            for (uint32_t r0 = 0; r0 < len; r0 += 64) {
-                const uint32_t row0 = r0 + lane, row1 = r0 + 32 + lane;
-                const bool v0 = row0 < len, v1 = row1 < len;
-                const uint8_t* c0 = p.codes + static_cast<uint64_t>(lbeg + (v0 ? row0 : 0)) * p.code_stride;
-                const uint8_t* c1 = p.codes + static_cast<uint64_t>(lbeg + (v1 ? row1 : 0)) * p.code_stride;
-                float a0 = 0.f, a1 = 0.f;
-                uint4 n0 = __ldg(reinterpret_cast<const uint4*>(c0));
-                uint4 n1 = __ldg(reinterpret_cast<const uint4*>(c1));
+            // NR rows per lane and round.  The first 16 bytes of the next round's rows and this round's |x|^2 are
+            // requested before the round's arithmetic, so a round does not start with a trip to memory.
+            constexpr uint32_t ROUND = 32u * NR;
+            uint4 nxt[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t row = r * 32u + lane;
+                nxt[r] = __ldg(reinterpret_cast<const uint4*>(p.codes + static_cast<uint64_t>(lbeg + (row < len ? row : 0)) * p.code_stride));
+            }
+            for (uint32_t r0 = 0; r0 < len; r0 += ROUND) {
+                const uint8_t* cp[NR];
+                bool valid[NR];
+                float norm[NR], acc[NR];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t row = r0 + r * 32u + lane;
+                    valid[r] = row < len;
+                    cp[r] = p.codes + static_cast<uint64_t>(lbeg + (valid[r] ? row : 0)) * p.code_stride;
+                    norm[r] = valid[r] ? __ldg(p.code_norm + lbeg + row) : 0.f;
+                    acc[r] = 0.f;
+                }
                 if (INT8) {
-                    int32_t s0[3] = {0, 0, 0}, s1[3] = {0, 0, 0};
+                    int32_t sum[NR][3];
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) {
+                        sum[r][0] = sum[r][1] = sum[r][2] = 0;
+                    }
 #pragma unroll 1
                     for (uint32_t c = 0; c < dpad; c += 16) {
-                        const uint4 u0 = n0, u1 = n1;
-                        if (c + 16 < dpad) {
-                            n0 = __ldg(reinterpret_cast<const uint4*>(c0 + c + 16));
-                            n1 = __ldg(reinterpret_cast<const uint4*>(c1 + c + 16));
+                        int32_t x[NR][4];
+#pragma unroll
+                        for (int r = 0; r < NR; ++r) {
+                            x[r][0] = static_cast<int32_t>(nxt[r].x ^ 0x80808080u);
+                            x[r][1] = static_cast<int32_t>(nxt[r].y ^ 0x80808080u);
+                            x[r][2] = static_cast<int32_t>(nxt[r].z ^ 0x80808080u);
+                            x[r][3] = static_cast<int32_t>(nxt[r].w ^ 0x80808080u);
                         }
-                        const int32_t x0[4] = {static_cast<int32_t>(u0.x ^ 0x80808080u), static_cast<int32_t>(u0.y ^ 0x80808080u),
-                                               static_cast<int32_t>(u0.z ^ 0x80808080u), static_cast<int32_t>(u0.w ^ 0x80808080u)};
-                        const int32_t x1[4] = {static_cast<int32_t>(u1.x ^ 0x80808080u), static_cast<int32_t>(u1.y ^ 0x80808080u),
-                                               static_cast<int32_t>(u1.z ^ 0x80808080u), static_cast<int32_t>(u1.w ^ 0x80808080u)};
+                        if (c + 16 < dpad) {
+#pragma unroll
+                            for (int r = 0; r < NR; ++r) {
+                                nxt[r] = __ldg(reinterpret_cast<const uint4*>(cp[r] + c + 16));
+                            }
+                        } else if (r0 + ROUND < len) {
+#pragma unroll
+                            for (int r = 0; r < NR; ++r) {
+                                const uint32_t row = r0 + ROUND + r * 32u + lane;
+                                nxt[r] = __ldg(reinterpret_cast<const uint4*>(p.codes + static_cast<uint64_t>(lbeg + (row < len ? row : 0)) * p.code_stride));
+                            }
+                        }
 #pragma unroll
                         for (int t = 0; t < 3; ++t) {
                             const uint4 wv = *reinterpret_cast<const uint4*>(w_raw + t * dpad32 + c);
@@ -792,46 +826,62 @@ ivf_sq8_first_kernel(const ScanParams p, const int8_t* __restrict__ qw8, const f
                                                    static_cast<int32_t>(wv.w)};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                s0[t] = __dp4a(x0[j], wt[j], s0[t]);
-                                s1[t] = __dp4a(x1[j], wt[j], s1[t]);
+#pragma unroll
+                                for (int r = 0; r < NR; ++r) {
+                                    sum[r][t] = __dp4a(x[r][j], wt[j], sum[r][t]);
+                                }
                             }
                         }
                     }
                     // sum_d w_d (code_d - 128) / s = A1 + (254 A2 + A3) / 254^2, as the tensor-core scan's epilogue
-                    a0 = fmaf(static_cast<float>(s0[1] * 254 + s0[2]), 1.0f / 64516.0f, static_cast<float>(s0[0]));
-                    a1 = fmaf(static_cast<float>(s1[1] * 254 + s1[2]), 1.0f / 64516.0f, static_cast<float>(s1[0]));
-                }
-                const float4* wrow = reinterpret_cast<const float4*>(w_s);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) {
+                        acc[r] = fmaf(static_cast<float>(sum[r][1] * 254 + sum[r][2]), 1.0f / 64516.0f, static_cast<float>(sum[r][0]));
+                    }
+                } else {
+                    const float4* wrow = reinterpret_cast<const float4*>(w_s);
 #pragma unroll 1
-                for (uint32_t c = 0; !INT8 && c < dpad; c += 16, wrow += 4) {
-                    const uint4 u0 = n0, u1 = n1;
-                    if (c + 16 < dpad) {
-                        n0 = __ldg(reinterpret_cast<const uint4*>(c0 + c + 16));
-                        n1 = __ldg(reinterpret_cast<const uint4*>(c1 + c + 16));
-                    }
+                    for (uint32_t c = 0; c < dpad; c += 16, wrow += 4) {
+                        uint4 cur[NR];
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const float4 wv = wrow[w];
-                        const uint32_t r0w = w == 0 ? u0.x : (w == 1 ? u0.y : (w == 2 ? u0.z : u0.w));
-                        const uint32_t r1w = w == 0 ? u1.x : (w == 1 ? u1.y : (w == 2 ? u1.z : u1.w));
-                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7540)) - 8388736.0f, wv.x, a0);
-                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7540)) - 8388736.0f, wv.x, a1);
-                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7541)) - 8388736.0f, wv.y, a0);
-                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7541)) - 8388736.0f, wv.y, a1);
-                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7542)) - 8388736.0f, wv.z, a0);
-                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7542)) - 8388736.0f, wv.z, a1);
-                        a0 = fmaf(__uint_as_float(__byte_perm(r0w, 0x4B000000u, 0x7543)) - 8388736.0f, wv.w, a0);
-                        a1 = fmaf(__uint_as_float(__byte_perm(r1w, 0x4B000000u, 0x7543)) - 8388736.0f, wv.w, a1);
+                        for (int r = 0; r < NR; ++r) {
+                            cur[r] = nxt[r];
+                        }
+                        if (c + 16 < dpad) {
+#pragma unroll
+                            for (int r = 0; r < NR; ++r) {
+                                nxt[r] = __ldg(reinterpret_cast<const uint4*>(cp[r] + c + 16));
+                            }
+                        } else if (r0 + ROUND < len) {
+#pragma unroll
+                            for (int r = 0; r < NR; ++r) {
+                                const uint32_t row = r0 + ROUND + r * 32u + lane;
+                                nxt[r] = __ldg(reinterpret_cast<const uint4*>(p.codes + static_cast<uint64_t>(lbeg + (row < len ? row : 0)) * p.code_stride));
+                            }
+                        }
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            const float4 wv = wrow[w];
+#pragma unroll
+                            for (int r = 0; r < NR; ++r) {
+                                const uint32_t raw = w == 0 ? cur[r].x : (w == 1 ? cur[r].y : (w == 2 ? cur[r].z : cur[r].w));
+                                float a = acc[r];
+                                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7540)) - 8388736.0f, wv.x, a);
+                                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7541)) - 8388736.0f, wv.y, a);
+                                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7542)) - 8388736.0f, wv.z, a);
+                                a = fmaf(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7543)) - 8388736.0f, wv.w, a);
+                                acc[r] = a;
+                            }
+                        }
                     }
                 }
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const bool valid = h == 0 ? v0 : v1;
-                    const uint32_t pos = lbeg + (h == 0 ? row0 : row1);
+                for (int h = 0; h < NR; ++h) {
+                    const uint32_t pos = lbeg + r0 + h * 32u + lane;
                     float partial = 0.f;
                     bool pass = false;
-                    if (valid) {
-                        partial = fmaf(INT8 ? cq : p.coef_c, h == 0 ? a0 : a1, p.coef_b * __ldg(p.code_norm + pos));
+                    if (valid[h]) {
+                        partial = fmaf(INT8 ? cq : p.coef_c, acc[h], p.coef_b * norm[h]);
                         pass = partial <= thrq;
                         if (pass && p.filter_pos_inner != nullptr && scan_row_filtered(p, pos)) {
                             pass = false;
@@ -860,6 +910,9 @@ ivf_sq8_first_kernel(const ScanParams p, const int8_t* __restrict__ qw8, const f
             }
             if (lane == 0 && cnt >= k) {
                 atomicMin(p.thr_g + q, static_cast<uint32_t>(kb[k - 1] >> 32));
+            }
+            if (lane == 0 && p.slot_written != nullptr) {
+                p.slot_written[slot] = 1;
             }
         }
     }

@@ -747,6 +747,9 @@ ivf_sq8_scan_tc_kernel(const TcScanParams tp) {
                                 atomicMin(p.thr_g + ts.qidx[qi], worst);
                             }
                         }
+                        if (lane == 0 && p.slot_written != nullptr) {
+                            p.slot_written[ts.slot[qi]] = 1;
+                        }
                     }
                 } else if (tid == 0) {
                     atomicOr(tp.error_flag, 1);
