@@ -2584,7 +2584,12 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     if (sq8) {
         VB_TRY(launch_merge(ws.part.ptr, nq, static_cast<uint64_t>(nprobe) * kscan, kscan, ws.merged.ptr, ws.slot_written.ptr, kscan));
         uint32_t n2 = next_pow2(kscan < 2 ? 2 : kscan);
-        VB_LAUNCH(sq8_rescore_kernel, static_cast<uint32_t>(nq), 128, n2 * sizeof(uint64_t), q_dev, ix->dim,
+        const size_t rescore_smem = n2 * sizeof(uint64_t) + 3 * ix->dim * sizeof(float);
+        if (rescore_smem > 48 * 1024) {
+            VB_CUDA(cudaFuncSetAttribute(sq8_rescore_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(rescore_smem)));
+        }
+        VB_LAUNCH(sq8_rescore_kernel, static_cast<uint32_t>(nq), 128, rescore_smem, q_dev, ix->dim,
                   ix->codes.ptr, ix->code_stride, ix->lower.ptr, ix->diff.ptr, ws.merged.ptr, kscan, n2,
                   kfinal, ix->metric, ws.keys.ptr, ix->use_residual ? ix->res_bias.ptr : static_cast<const float*>(nullptr),
                   ix->centroids.ptr, ix->list_off.ptr, nlist);

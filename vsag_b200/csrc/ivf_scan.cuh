@@ -929,7 +929,17 @@ sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_
                    const uint32_t* __restrict__ list_off, uint32_t nlist) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
-    const float* q = queries + static_cast<uint64_t>(blockIdx.x) * dim;
+    // the query and the quantizer's two vectors, staged once: the candidates' chains read them from shared memory
+    float* qs = reinterpret_cast<float*>(keys + n2);   // [3][dim]: query, lower, diff
+    float* los = qs + dim;
+    float* dis = los + dim;
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        qs[d] = __ldg(queries + static_cast<uint64_t>(blockIdx.x) * dim + d);
+        los[d] = __ldg(lower + d);
+        dis[d] = __ldg(diff + d);
+    }
+    __syncthreads();
+    const float* q = qs;
     const uint64_t* cq = cand + static_cast<uint64_t>(blockIdx.x) * ncand;
     const float inv255 = 1.0f / 255.0f;
     for (uint32_t i = threadIdx.x; i < n2; i += blockDim.x) {
@@ -938,13 +948,24 @@ sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_
             uint32_t pos = static_cast<uint32_t>(cq[i]);
             const uint8_t* c = codes + static_cast<uint64_t>(pos) * code_stride;
             float s = 0.f;
-            for (uint32_t d = 0; d < dim; ++d) {
-                float x = fmaf(__fmul_rn(static_cast<float>(c[d]), inv255), __ldg(diff + d), __ldg(lower + d));
-                if (metric == VB200_METRIC_L2) {
-                    float t = __fsub_rn(__ldg(q + d), x);
-                    s = fmaf(t, t, s);
-                } else {
-                    s = fmaf(__ldg(q + d), x, s);
+            // the same chain over d ascending; the code bytes arrive sixteen at a time (rows are 16-byte aligned)
+            for (uint32_t d0 = 0; d0 < dim; d0 += 16) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(c + d0));
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+                const uint32_t left = dim - d0 < 16 ? dim - d0 : 16;
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j) {
+                    if (j < left) {
+                        const uint32_t d = d0 + j;
+                        const float byte = static_cast<float>((words[j >> 2] >> ((j & 3u) * 8)) & 0xFFu);
+                        const float x = fmaf(__fmul_rn(byte, inv255), dis[d], los[d]);
+                        if (metric == VB200_METRIC_L2) {
+                            const float t = __fsub_rn(q[d], x);
+                            s = fmaf(t, t, s);
+                        } else {
+                            s = fmaf(q[d], x, s);
+                        }
+                    }
                 }
             }
             if (metric != VB200_METRIC_L2) {
@@ -965,7 +986,7 @@ sq8_rescore_kernel(const float* __restrict__ queries, uint32_t dim, const uint8_
                 const float* cen = centroids + static_cast<uint64_t>(lo) * dim;
                 float ipd = 0.f;
                 for (uint32_t d = 0; d < dim; ++d) {
-                    ipd = fmaf(__ldg(q + d), __ldg(cen + d), ipd);
+                    ipd = fmaf(q[d], __ldg(cen + d), ipd);
                 }
                 if (metric == VB200_METRIC_L2) {
                     ipd = __fmul_rn(ipd, 2.0f);
