@@ -1252,26 +1252,56 @@ pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t
     }
 }
 
-// Per query: the k smallest of its `per_query` partial keys, ascending.
+// Per query: the k smallest of its `per_query` partial keys, ascending.  With slot flags (slot_written, slots of
+// slot_keys keys) only the slots a scan kernel wrote hold keys -- the others were never initialised -- and the
+// query's written slots are listed first, so the rounds run over those alone.
+constexpr uint32_t MERGE_MAX_SLOTS = 1024;
+
 __global__ void __launch_bounds__(256)
 merge_keys_kernel(const uint64_t* __restrict__ part, uint64_t per_query, uint32_t k, uint32_t cap,
                   uint64_t* __restrict__ out, const uint8_t* __restrict__ slot_written, uint32_t slot_keys) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ uint16_t s_slots[MERGE_MAX_SLOTS];
+    __shared__ uint32_t s_nslots;
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);
     uint32_t* state = reinterpret_cast<uint32_t*>(keys + cap);
     BlockSelect sel;
-    sel.init(keys, state, k, cap);
     const uint64_t* src = part + static_cast<uint64_t>(blockIdx.x) * per_query;
-    for (uint64_t base = 0; base < per_query; base += blockDim.x) {
+    uint64_t n_keys = per_query;
+    const uint32_t n_slots = slot_written != nullptr ? static_cast<uint32_t>(per_query / slot_keys) : 0u;
+    const bool listed = slot_written != nullptr && n_slots <= MERGE_MAX_SLOTS;
+    if (listed) {
+        if (threadIdx.x == 0) {
+            s_nslots = 0;
+        }
+        __syncthreads();
+        const uint8_t* flags = slot_written + static_cast<uint64_t>(blockIdx.x) * n_slots;
+        for (uint32_t sl = threadIdx.x; sl < n_slots; sl += blockDim.x) {
+            if (flags[sl] != 0) {
+                s_slots[atomicAdd(&s_nslots, 1u)] = static_cast<uint16_t>(sl);   // any order: the selection sorts
+            }
+        }
+        __syncthreads();
+        n_keys = static_cast<uint64_t>(s_nslots) * slot_keys;
+    }
+    sel.init(keys, state, k, cap);
+    for (uint64_t base = 0; base < n_keys; base += blockDim.x) {
         sel.make_room(blockDim.x);
         uint64_t thr = sel.threshold();
         uint64_t i = base + threadIdx.x;
-        // (with slot flags only the slots a scan kernel wrote hold keys; the others were never initialised)
-        if (i < per_query &&
-            (slot_written == nullptr || slot_written[(static_cast<uint64_t>(blockIdx.x) * per_query + i) / slot_keys] != 0)) {
-            uint64_t key = __ldg(src + i);
-            if (key != KEY_INF) {
-                sel.offer(key, thr);
+        if (i < n_keys) {
+            bool present = true;
+            uint64_t at = i;
+            if (listed) {
+                at = static_cast<uint64_t>(s_slots[i / slot_keys]) * slot_keys + i % slot_keys;
+            } else if (slot_written != nullptr) {
+                present = slot_written[(static_cast<uint64_t>(blockIdx.x) * per_query + i) / slot_keys] != 0;
+            }
+            if (present) {
+                uint64_t key = __ldg(src + at);
+                if (key != KEY_INF) {
+                    sel.offer(key, thr);
+                }
             }
         }
     }
@@ -1494,8 +1524,8 @@ route_find_bin(const uint32_t* hist, uint32_t rank, uint32_t* s_bin, uint32_t* s
 // it approximately.  One CTA per query: two rounds of a 256-bin histogram over the range of the scores
 // still in question (bins follow the values' own range, so a narrow spread does not pile them into one
 // bin), then the largest score of the bins taken.
-constexpr int ROUTE_THR_PER_THREAD = 16;   // sample <= 4096
-
+// ROUTE_THR_PER_THREAD: scores a thread holds, sample / ROUTE_THREADS rounded up (sample <= 4096).
+template <int ROUTE_THR_PER_THREAD>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_threshold_kernel(const float* __restrict__ scores, uint32_t sample, uint32_t ncand, const float* __restrict__ queries,
                        uint32_t dim, const float* __restrict__ c_max_norm, float* __restrict__ thr) {
@@ -2047,7 +2077,7 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
         // answered exactly by route_pick_kernel like one whose lists overflowed.
         uint32_t sample = 0, rank = 0;
         for (uint32_t s = 1024; s <= 4096 && sample == 0; s *= 2) {
-            uint64_t r = (4ull * ncand * s + nlist - 1) / nlist;
+            uint64_t r = (4ull * ncand * s + nlist - 1) / nlist;   // (3x and 5x measured slower: exact fallbacks, longer sorts)
             r = r < 16 ? 16 : r;
             r = r > ncand ? ncand : r;
             const uint64_t expected = r * nlist / s;
@@ -2066,7 +2096,9 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
             // candidate lists overflowed is answered exactly by route_pick_kernel itself.
             VB_TRY(tc_scores(ix->tc, a, bs, 3, alpha, bias, ws.scores.ptr, sample, route_flag));
             VB_TRY(ws.route_thr.reserve(nq));
-            VB_LAUNCH(route_threshold_kernel, static_cast<uint32_t>(nq), ROUTE_THREADS, 0, ws.scores.ptr, sample, rank,
+            auto thr_kernel = sample <= 4 * ROUTE_THREADS ? route_threshold_kernel<4>
+                                                          : (sample <= 8 * ROUTE_THREADS ? route_threshold_kernel<8> : route_threshold_kernel<16>);
+            VB_LAUNCH(thr_kernel, static_cast<uint32_t>(nq), ROUTE_THREADS, 0, ws.scores.ptr, sample, rank,
                       q_dev, ix->dim, ix->c_max_norm.ptr, ws.route_thr.ptr);
             uint32_t lists = 0, cap = 0;
             bool overflow = false;
