@@ -1,6 +1,7 @@
 // IVF index: device-resident inverted lists, exact routing, the batched list-major scan
 // scheduler, the partial-result merge and the fp32 rerank.
 #include <algorithm>
+#include <cooperative_groups.h>
 #include <cub/device/device_radix_sort.cuh>
 
 #include "dense.cuh"
@@ -913,17 +914,13 @@ struct PairTables {
     uint32_t* slot[2];      // [pairs] output slot
 };
 
-__global__ void
-pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
-                  const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
-                  const uint32_t* __restrict__ list_off, PairTables t, uint32_t phase_sel,
-                  const uint8_t* __restrict__ drop) {
-    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (e >= total) {
-        return;
-    }
-    const uint32_t pr = static_cast<uint32_t>(e % nprobe);
-    const uint32_t ph = pr == first_live[e / nprobe] ? 0u : 1u;
+__device__ __forceinline__ void
+pair_count_one(uint64_t e, const int32_t* __restrict__ probes, uint32_t nprobe, const uint32_t* __restrict__ first_live,
+               uint32_t nlist, uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off, const PairTables& t,
+               uint32_t phase_sel, const uint8_t* __restrict__ drop) {
+    const uint32_t e32 = static_cast<uint32_t>(e);   // (the batch holds fewer than 2^32 pairs: 32-bit division)
+    const uint32_t qi = e32 / nprobe, pr = e32 - qi * nprobe;
+    const uint32_t ph = pr == first_live[qi] ? 0u : 1u;
     if ((phase_sel < 2 && ph != phase_sel) || (drop != nullptr && drop[e] != 0)) {
         return;   // phase_sel 0 / 1: group that phase only; dropped pairs were pruned beforehand
     }
@@ -1008,8 +1005,8 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
     int32_t l = 0;
     float bound = 0.f;
     if (e < total) {
-        q = static_cast<uint32_t>(e / nprobe);
-        const uint32_t pr = static_cast<uint32_t>(e % nprobe);
+        q = static_cast<uint32_t>(e) / nprobe;   // (fewer than 2^32 pairs in a batch: 32-bit division)
+        const uint32_t pr = static_cast<uint32_t>(e) - q * nprobe;
         l = probes[e];
         const uint32_t t = thr[q];
         bool dropped = false;
@@ -1105,109 +1102,113 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
 // One CTA per phase: exclusive prefixes of (pairs) and of (tiles of qt queries) over the lists
 // taken in `order` (pair_off is stored by list, item_off by position in the order), plus the
 // logical scan volume sum(pairs[l] * len[l]).  pair_items_kernel turns the prefixes into work items.
-__global__ void __launch_bounds__(1024)
-pair_scan_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
-                 const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt, uint32_t code_size,
-                 uint64_t* __restrict__ scalars) {
-    const uint32_t* __restrict__ pair_cnt = blockIdx.x == 0 ? tables.cnt[0] : tables.cnt[1];
-    uint32_t* __restrict__ pair_off = blockIdx.x == 0 ? tables.off[0] : tables.off[1];
-    uint32_t* __restrict__ item_off = blockIdx.x == 0 ? tables.item_off[0] : tables.item_off[1];
-    __shared__ uint32_t s_pairs[33], s_items[33];   // exclusive prefixes of the warps' chunks, totals in [32]
+// A thread owns PAIR_SCAN_PER consecutive positions of a 1024 * PAIR_SCAN_PER-position slab: all its loads of
+// `order` go out together, then all the gathers behind them, so a slab costs two trips to memory and one block
+// scan rather than a chain of dependent gathers per 32 positions.
+constexpr int PAIR_SCAN_PER = 16;
+
+__device__ __forceinline__ void
+pair_scan_block(uint32_t ph, const PairTables& tables, const uint32_t* __restrict__ list_off,
+                const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt, uint32_t code_size,
+                uint64_t* __restrict__ scalars) {
+    const uint32_t* __restrict__ pair_cnt = ph == 0 ? tables.cnt[0] : tables.cnt[1];
+    uint32_t* __restrict__ pair_off = ph == 0 ? tables.off[0] : tables.off[1];
+    uint32_t* __restrict__ item_off = ph == 0 ? tables.item_off[0] : tables.item_off[1];
+    __shared__ uint32_t s_pairs[33], s_items[33];   // exclusive prefixes of the warps' sums, totals in [32]
     __shared__ unsigned long long s_bytes;
+    __syncthreads();   // (a CTA may run this for one phase after the other)
     if (threadIdx.x == 0) {
         s_bytes = 0;
     }
-    __syncthreads();
-    // A warp owns a contiguous chunk of positions and walks it 32 at a time, so the loads of `order` are
-    // coalesced and the gathers behind them independent: sums of the chunks, one scan over the 32 warps,
-    // then the chunk is walked again with a warp scan per round.
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t per_warp = ((nlist + 31) / 32 + 31) / 32 * 32;
-    const uint32_t w0 = warp * per_warp < nlist ? warp * per_warp : nlist;
-    const uint32_t w1 = w0 + per_warp < nlist ? w0 + per_warp : nlist;
-    uint32_t sum_p = 0, sum_t = 0;
+    uint32_t carry_p = 0, carry_t = 0;
     unsigned long long my_bytes = 0;
-#pragma unroll 4
-    for (uint32_t base = w0; base < w1; base += 32) {
-        const uint32_t pos = base + lane;
-        if (pos < w1) {
-            const uint32_t l = __ldg(order + pos);
-            const uint32_t c = pair_cnt[l];
-            sum_p += c;
-            sum_t += (c + qt - 1) / qt;
-            my_bytes += static_cast<unsigned long long>(c) * (__ldg(list_off + l + 1) - __ldg(list_off + l)) * code_size;
+    for (uint32_t slab = 0; slab < nlist; slab += 1024u * PAIR_SCAN_PER) {
+        const uint32_t p0 = slab + threadIdx.x * PAIR_SCAN_PER;
+        uint32_t l[PAIR_SCAN_PER], c[PAIR_SCAN_PER];
+#pragma unroll
+        for (int i = 0; i < PAIR_SCAN_PER; ++i) {
+            l[i] = p0 + i < nlist ? __ldg(order + p0 + i) : 0xFFFFFFFFu;
         }
+        uint32_t sum_p = 0, sum_t = 0;
+        uint32_t len[PAIR_SCAN_PER];
+#pragma unroll
+        for (int i = 0; i < PAIR_SCAN_PER; ++i) {
+            const bool real = l[i] != 0xFFFFFFFFu;
+            c[i] = real ? pair_cnt[l[i]] : 0u;
+            len[i] = real ? __ldg(list_off + l[i] + 1) - __ldg(list_off + l[i]) : 0u;   // asked for unconditionally: no load waits for another
+        }
+#pragma unroll
+        for (int i = 0; i < PAIR_SCAN_PER; ++i) {
+            sum_p += c[i];
+            sum_t += (c[i] + qt - 1) / qt;
+            my_bytes += static_cast<unsigned long long>(c[i]) * len[i] * code_size;
+        }
+        // block-wide exclusive prefix of the threads' sums
+        uint32_t ip = sum_p, it = sum_t;
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, ip, off), ut = __shfl_up_sync(0xffffffffu, it, off);
+            if (lane >= static_cast<uint32_t>(off)) {
+                ip += up;
+                it += ut;
+            }
+        }
+        __syncthreads();   // the previous slab's reads of s_pairs / s_items are done
+        if (lane == 31) {
+            s_pairs[warp] = ip;
+            s_items[warp] = it;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t vp = s_pairs[lane], vt = s_items[lane];
+            uint32_t wp = vp, wt = vt;
+            for (int off = 1; off < 32; off <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, wp, off), ut = __shfl_up_sync(0xffffffffu, wt, off);
+                if (lane >= static_cast<uint32_t>(off)) {
+                    wp += up;
+                    wt += ut;
+                }
+            }
+            s_pairs[lane] = wp - vp;
+            s_items[lane] = wt - vt;
+            if (lane == 31) {
+                s_pairs[32] = wp;
+                s_items[32] = wt;
+            }
+        }
+        __syncthreads();
+        uint32_t run_p = carry_p + s_pairs[warp] + ip - sum_p, run_t = carry_t + s_items[warp] + it - sum_t;
+#pragma unroll
+        for (int i = 0; i < PAIR_SCAN_PER; ++i) {
+            if (l[i] != 0xFFFFFFFFu) {
+                pair_off[l[i]] = run_p;
+                item_off[p0 + i] = run_t;
+                run_p += c[i];
+                run_t += (c[i] + qt - 1) / qt;
+            }
+        }
+        carry_p += s_pairs[32];
+        carry_t += s_items[32];
     }
     for (int off = 16; off > 0; off >>= 1) {
-        sum_p += __shfl_xor_sync(0xffffffffu, sum_p, off);
-        sum_t += __shfl_xor_sync(0xffffffffu, sum_t, off);
         my_bytes += __shfl_xor_sync(0xffffffffu, my_bytes, off);
     }
-    if (lane == 0) {
-        s_pairs[warp] = sum_p;
-        s_items[warp] = sum_t;
+    if (lane == 0 && my_bytes != 0) {
         atomicAdd(&s_bytes, my_bytes);
     }
     __syncthreads();
-    if (warp == 0) {
-        uint32_t vp = s_pairs[lane], vt = s_items[lane];
-        uint32_t ip = vp, it = vt;
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t up = __shfl_up_sync(0xffffffffu, ip, off), ut = __shfl_up_sync(0xffffffffu, it, off);
-            if (lane >= static_cast<uint32_t>(off)) {
-                ip += up;
-                it += ut;
-            }
-        }
-        s_pairs[lane] = ip - vp;
-        s_items[lane] = it - vt;
-        if (lane == 31) {
-            s_pairs[32] = ip;
-            s_items[32] = it;
-        }
-    }
-    __syncthreads();
-    uint32_t run_p = s_pairs[warp], run_t = s_items[warp];
-    for (uint32_t base = w0; base < w1; base += 32) {
-        const uint32_t pos = base + lane;
-        uint32_t l = 0, c = 0;
-        if (pos < w1) {
-            l = __ldg(order + pos);
-            c = pair_cnt[l];
-        }
-        const uint32_t t = (c + qt - 1) / qt;
-        uint32_t ip = c, it = t;
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t up = __shfl_up_sync(0xffffffffu, ip, off), ut = __shfl_up_sync(0xffffffffu, it, off);
-            if (lane >= static_cast<uint32_t>(off)) {
-                ip += up;
-                it += ut;
-            }
-        }
-        if (pos < w1) {
-            pair_off[l] = run_p + ip - c;
-            item_off[pos] = run_t + it - t;
-        }
-        run_p += __shfl_sync(0xffffffffu, ip, 31);
-        run_t += __shfl_sync(0xffffffffu, it, 31);
-    }
     if (threadIdx.x == 0) {
-        pair_off[nlist] = s_pairs[32];
-        item_off[nlist] = s_items[32];
+        pair_off[nlist] = carry_p;
+        item_off[nlist] = carry_t;
         atomicAdd(reinterpret_cast<unsigned long long*>(scalars), s_bytes);  // logical scan volume, both phases
     }
 }
 
 // The work items of the scan's queue, written from the prefixes above: one thread per list position and
 // phase (blockIdx.y), each writing the descriptors of its list's tiles of qt queries.
-__global__ void __launch_bounds__(256)
-pair_items_kernel(PairTables tables, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
-                  const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt) {
-    const uint32_t pos = blockIdx.x * blockDim.x + threadIdx.x;
-    if (pos >= nlist) {
-        return;
-    }
-    const uint32_t ph = blockIdx.y;
+__device__ __forceinline__ void
+pair_items_one(uint32_t pos, uint32_t ph, const PairTables& tables, const uint32_t* __restrict__ list_off,
+               const uint32_t* __restrict__ group_off, const uint32_t* __restrict__ order, uint32_t qt) {
     const uint32_t l = order[pos];
     const uint32_t c = tables.cnt[ph][l];
     if (c == 0) {
@@ -1230,25 +1231,57 @@ pair_items_kernel(PairTables tables, const uint32_t* __restrict__ list_off, cons
     }
 }
 
-__global__ void
-pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
-                    const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
-                    const uint32_t* __restrict__ list_off, PairTables t, uint32_t phase_sel,
-                    const uint8_t* __restrict__ drop) {
-    uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (e >= total) {
-        return;
-    }
-    const uint32_t pr = static_cast<uint32_t>(e % nprobe);
-    const bool first = pr == first_live[e / nprobe];
+__device__ __forceinline__ void
+pair_scatter_one(uint64_t e, const int32_t* __restrict__ probes, uint32_t nprobe, const uint32_t* __restrict__ first_live,
+                 uint32_t nlist, uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off, const PairTables& t,
+                 uint32_t phase_sel, const uint8_t* __restrict__ drop) {
+    const uint32_t e32 = static_cast<uint32_t>(e);
+    const uint32_t qi = e32 / nprobe, pr = e32 - qi * nprobe;
+    const bool first = pr == first_live[qi];
     if ((phase_sel < 2 && (first ? 0u : 1u) != phase_sel) || (drop != nullptr && drop[e] != 0)) {
         return;
     }
     int32_t l = probes[e];
     if (probe_is_live(l, nlist, rank, world, list_off)) {
         uint32_t s = (first ? t.off[0] : t.off[1])[l] + atomicAdd((first ? t.cursor[0] : t.cursor[1]) + l, 1u);
-        (first ? t.q[0] : t.q[1])[s] = static_cast<uint32_t>(e / nprobe);
+        (first ? t.q[0] : t.q[1])[s] = qi;
         (first ? t.slot[0] : t.slot[1])[s] = static_cast<uint32_t>(e);
+    }
+}
+
+// Groups the (query, probed list) pairs by list and writes the scan's work queue, in one cooperative launch:
+// clear the counters | count the pairs of every list | prefix sums (one CTA per phase) | work items and the
+// pairs' places, with a grid-wide barrier between the stages.  As four launches the stages cost more in launch
+// and drain latency than in work.
+__global__ void __launch_bounds__(1024, 1)
+pair_group_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
+                  const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
+                  const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
+                  const uint32_t* __restrict__ order, PairTables t, uint32_t* __restrict__ counters, uint32_t phase_sel,
+                  const uint8_t* __restrict__ drop, uint32_t qt, uint32_t code_size, uint64_t* __restrict__ scalars) {
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t nthreads = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = tid; i < 4ull * nlist; i += nthreads) {
+        counters[i] = 0;
+    }
+    grid.sync();
+    for (uint64_t e = tid; e < total; e += nthreads) {
+        pair_count_one(e, probes, nprobe, first_live, nlist, rank, world, list_off, t, phase_sel, drop);
+    }
+    grid.sync();
+    if (gridDim.x == 1) {
+        pair_scan_block(0, t, list_off, order, nlist, qt, code_size, scalars);
+        pair_scan_block(1, t, list_off, order, nlist, qt, code_size, scalars);
+    } else if (blockIdx.x < 2) {
+        pair_scan_block(blockIdx.x, t, list_off, order, nlist, qt, code_size, scalars);
+    }
+    grid.sync();
+    for (uint64_t i = tid; i < 2ull * nlist; i += nthreads) {
+        pair_items_one(static_cast<uint32_t>(i % nlist), static_cast<uint32_t>(i / nlist), t, list_off, group_off, order, qt);
+    }
+    for (uint64_t e = tid; e < total; e += nthreads) {
+        pair_scatter_one(e, probes, nprobe, first_live, nlist, rank, world, list_off, t, phase_sel, drop);
     }
 }
 
@@ -2324,15 +2357,24 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
     }
     // Groups the pairs of one phase (0 / 1) or of both (2) by list; `drop` marks pruned pairs.
     auto group_pairs = [&](uint32_t phase_sel, const uint8_t* drop, uint32_t queries_per_item) -> int {
-        VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
-        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
-                  ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
-        VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->group_off.ptr, ix->scan_order.ptr, nlist,
-                  queries_per_item, ix->code_size, ws.scalars.ptr);
-        VB_LAUNCH(pair_items_kernel, dim3((nlist + 255) / 256, 2), 256, 0, tables, ix->list_off.ptr, ix->group_off.ptr,
-                  ix->scan_order.ptr, nlist, queries_per_item);
-        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist,
-                  ix->shard_rank, ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
+        const int32_t* a_probes = probes_dev;
+        uint64_t a_total = total;
+        uint32_t a_nprobe = nprobe, a_nlist = nlist, a_rank = ix->shard_rank, a_world = ix->shard_world, a_sel = phase_sel,
+                 a_qt = queries_per_item, a_code = ix->code_size;
+        const uint32_t* a_first = ws.first_live.ptr;
+        const uint32_t* a_off = ix->list_off.ptr;
+        const uint32_t* a_goff = ix->group_off.ptr;
+        const uint32_t* a_order = ix->scan_order.ptr;
+        PairTables a_tables = tables;
+        uint32_t* a_ctr = ws.pair_ctr.ptr;
+        const uint8_t* a_drop = drop;
+        uint64_t* a_scalars = ws.scalars.ptr;
+        void* args[] = {&a_probes, &a_total, &a_nprobe, &a_first, &a_nlist, &a_rank, &a_world, &a_off, &a_goff, &a_order,
+                        &a_tables, &a_ctr, &a_sel, &a_drop, &a_qt, &a_code, &a_scalars};
+        // every CTA of a cooperative launch must be resident: one per SM
+        VB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(pair_group_kernel), dim3(static_cast<uint32_t>(sm_count())),
+                                            dim3(1024), args, 0, st));
+        g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
         return 0;
     };
     // SQ8 with list pruning: the first phase runs alone, then the pairs its bounds rule out are
