@@ -1,6 +1,7 @@
 // tcgen05 / TMEM candidate-generation GEMM: operand pre-tiling, the kernel and its launcher.
 #include "tc_gemm.cuh"
 
+#include <cmath>
 #include <cstdlib>
 
 #include <cuda_bf16.h>
@@ -959,8 +960,15 @@ tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint
     const uint64_t tiles_per_split = (n_tiles + n_split - 1) / n_split;
     n_split = (n_tiles + tiles_per_split - 1) / tiles_per_split;
     const uint32_t lists = static_cast<uint32_t>(n_split) * TC_COL_GROUPS;
-    // list capacity: 3.5 x the expected share of a list, at least 16, within the caller's limit per row
-    uint32_t cap = next_pow2((7 * expected_per_row / 2 + lists - 1) / lists);
+    // list capacity: a list's expected share plus eight standard deviations of a Poisson count and a few more
+    // (3.5 x the share at least), within the caller's limit per row.  An overflowing list costs its row a slow
+    // exact answer, and with many short lists per row a multiple of the mean alone is passed every few thousand lists.
+    const double share = static_cast<double>(expected_per_row) / lists;
+    uint32_t want = static_cast<uint32_t>(share + 8.0 * std::sqrt(share) + 8.0);
+    if (want < (7 * expected_per_row / 2 + lists - 1) / lists) {
+        want = (7 * expected_per_row / 2 + lists - 1) / lists;
+    }
+    uint32_t cap = next_pow2(want);
     if (cap < 16) {
         cap = 16;
     }
