@@ -59,7 +59,7 @@ FP32_FMA_PEAK_T = 148 * 128 * 1.965e9 / 1e12   # fp32 FMA/s of one B200 in units
 # 2,000,000-row case) per byte of codes the kernel reported as read in that capture: lists that several
 # tiles scan are L2 hits after the first, so the ratio is below one.  `traffic` is this ratio times the
 # code bytes the timed run itself reports, per rank.
-SCAN_DRAM_PER_CODE_BYTE = 0.78   # 115.2 MB of DRAM traffic for 148.3 MB of codes fetched
+SCAN_DRAM_PER_CODE_BYTE = 0.79   # 116.5 MB of DRAM traffic for 148.3 MB of codes fetched
 WORKLOAD_NAME = "IVF-SQ8 search, 10M x 96, nlist 16384, nprobe 64, 10000 queries, k 10"
 METRIC_NAME = "QPS at nprobe=64, IVF-SQ8 10Mx96, k=10"
 
@@ -416,7 +416,7 @@ def scan_roofline(peaks: dict, kernel_ms: float, logical: float, read: float, un
     sec = kernel_ms / 1e3
     achieved = read / sec / 1e9
     out = {"bound": "hbm",
-           "kernel": ("ivf_sq8_scan_kernel (first phase) + ivf_sq8_scan_tc_kernel (second phase)" if pruned
+           "kernel": ("ivf_sq8_first_kernel (first phase) + ivf_sq8_scan_tc_kernel (second phase)" if pruned
                       else "ivf_sq8_scan_tc_kernel"),
            "achieved": achieved, "peak": peak, "unit": "GB/s",
            "frac": achieved / peak, "peak_source": peaks["hbm_kind"], "kernel_ms": kernel_ms,
