@@ -1832,9 +1832,45 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
         }
     }
     __syncwarp();
-    if (total <= 128) {
+    // Only the ncand best are wanted, so most of the keys need no sorting: a pivot from a 32-key sample -- the key
+    // at 1.6 times the rank that would cut off ncand, plus two -- is counted against all keys, and when between
+    // ncand and 256 keys lie at or below it those alone are compacted to the front and sorted.  The set of the
+    // ncand smallest is the same either way (keys are distinct: the list id is their low word).
+    uint32_t n_keys = total;
+    if (total > 128) {
+        uint64_t sample[1] = {buf[(lane * total) >> 5]};
+        warp_sort_registers<1>(sample, lane);
+        uint32_t r = (ncand * 32u * 8u / 5u) / total + 2u;
+        r = r > 31u ? 31u : r;
+        const uint64_t pivot = __shfl_sync(0xffffffffu, sample[0], r);
+        uint32_t below = 0;
+        for (uint32_t i = lane; i < ROUTE_WARP_KEYS; i += 32) {
+            below += __popc(__ballot_sync(0xffffffffu, i < total && buf[i] <= pivot));
+        }
+        if (below >= ncand && below <= 256) {
+            uint32_t cnt = 0;
+            for (uint32_t i = lane; i < ROUTE_WARP_KEYS; i += 32) {   // all lanes take the same number of trips
+                const uint64_t key = i < total ? buf[i] : KEY_INF;
+                const bool keep = key <= pivot && i < total;
+                const uint32_t mask = __ballot_sync(0xffffffffu, keep);
+                __syncwarp();
+                if (keep) {
+                    buf[cnt + __popc(mask & ((1u << lane) - 1u))] = key;   // at or before its own place
+                }
+                cnt += __popc(mask);
+                __syncwarp();
+            }
+            const uint32_t pad = cnt <= 128 ? 128u : 256u;
+            for (uint32_t i = cnt + lane; i < pad; i += 32) {
+                buf[i] = KEY_INF;
+            }
+            __syncwarp();
+            n_keys = cnt;
+        }
+    }
+    if (n_keys <= 128) {
         warp_sort_buffer<4>(buf, lane);
-    } else if (total <= 256) {
+    } else if (n_keys <= 256) {
         warp_sort_buffer<8>(buf, lane);
     } else {
         warp_sort_buffer<16>(buf, lane);
@@ -1845,7 +1881,7 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
     for (int r = 0; r < 4; ++r) {
         const uint32_t e = r * 32 + lane;
         uint64_t mine = KEY_INF;
-        if (e < ncand && e < total) {
+        if (e < ncand && e < n_keys) {
             const uint32_t list = static_cast<uint32_t>(buf[e]);
             const float s = route_exact_score(qs, centroids + static_cast<uint64_t>(list) * dim, dim, metric);
             mine = make_key(s, list);
