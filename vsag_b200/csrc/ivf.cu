@@ -1709,6 +1709,63 @@ route_exact_score(const float* __restrict__ qs, const float* __restrict__ c, uin
     return s;
 }
 
+// Four such distances at once (each chain in the same order as route_exact_score): the four chains' loads and
+// FMAs interleave, which a thread working through them one after the other cannot do.  c[j] null: +inf.
+__device__ __forceinline__ void
+route_exact_score4(const float* __restrict__ qs, const float* const (&c)[4], uint32_t dim, int metric, float (&out)[4]) {
+    if ((dim & 3u) != 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            out[j] = c[j] != nullptr ? route_exact_score(qs, c[j], dim, metric) : INFINITY;
+        }
+        return;
+    }
+    const float4* q4 = reinterpret_cast<const float4*>(qs);
+    const float* safe = c[0] != nullptr ? c[0] : (c[1] != nullptr ? c[1] : (c[2] != nullptr ? c[2] : c[3]));
+    const float4* c4[4];
+    float s[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        c4[j] = reinterpret_cast<const float4*>(c[j] != nullptr ? c[j] : safe);
+        s[j] = 0.f;
+    }
+    if (safe == nullptr) {
+        out[0] = out[1] = out[2] = out[3] = INFINITY;
+        return;
+    }
+#pragma unroll 4
+    for (uint32_t d4 = 0; d4 < (dim >> 2); ++d4) {
+        const float4 qv = q4[d4];
+        float4 cv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            cv[j] = __ldg(c4[j] + d4);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (metric == VB200_METRIC_L2) {
+                float t = __fsub_rn(qv.x, cv[j].x);
+                s[j] = fmaf(t, t, s[j]);
+                t = __fsub_rn(qv.y, cv[j].y);
+                s[j] = fmaf(t, t, s[j]);
+                t = __fsub_rn(qv.z, cv[j].z);
+                s[j] = fmaf(t, t, s[j]);
+                t = __fsub_rn(qv.w, cv[j].w);
+                s[j] = fmaf(t, t, s[j]);
+            } else {
+                s[j] = fmaf(qv.x, cv[j].x, s[j]);
+                s[j] = fmaf(qv.y, cv[j].y, s[j]);
+                s[j] = fmaf(qv.z, cv[j].z, s[j]);
+                s[j] = fmaf(qv.w, cv[j].w, s[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        out[j] = c[j] == nullptr ? INFINITY : (metric == VB200_METRIC_L2 ? s[j] : __fsub_rn(1.0f, s[j]));
+    }
+}
+
 // One CTA per query: gathers the query's centroids below its threshold from their lists, takes the
 // ncand best by approximate score, re-scores them exactly -- L2: FMA chain of (q-c)^2 over d
 // ascending; IP: 1 - chain of q*c (the loop of IVF::route_buckets_only,
@@ -1971,12 +2028,24 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
         // wait for the candidate pass to know.
         BlockSelect sel;
         sel.init(keys, s_state, nprobe, next_pow2(nprobe + blockDim.x));
-        for (uint32_t base = 0; base < nlist; base += blockDim.x) {
-            sel.make_room(blockDim.x);
-            const uint64_t bound = sel.threshold();
-            const uint32_t c = base + tid;
-            if (c < nlist) {
-                sel.offer(make_key(route_exact_score(qs, centroids + static_cast<uint64_t>(c) * dim, dim, metric), c), bound);
+        // four centroids per thread and trip, so four chains of loads and FMAs are in flight at once
+        for (uint32_t base = 0; base < nlist; base += 4 * blockDim.x) {
+            float sc[4];
+            const float* rows[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t c = base + j * blockDim.x + tid;
+                rows[j] = c < nlist ? centroids + static_cast<uint64_t>(c) * dim : nullptr;
+            }
+            route_exact_score4(qs, rows, dim, metric, sc);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t c = base + j * blockDim.x + tid;
+                sel.make_room(blockDim.x);
+                const uint64_t bound = sel.threshold();
+                if (c < nlist) {
+                    sel.offer(make_key(sc[j], c), bound);
+                }
             }
         }
         const uint32_t found = sel.finish();

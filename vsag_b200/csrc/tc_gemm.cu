@@ -947,15 +947,18 @@ tc_below_threshold(TcWorkspace& ws, const TcOperand& a, const TcOperand& b, uint
     const uint32_t sms = static_cast<uint32_t>(sm_count());
     // More column ranges per row tile than the sorted modes take: a list costs nothing but its
     // slots here, and short items spread evenly over the SMs.
-    uint64_t n_split = (4ull * sms + m_tiles - 1) / m_tiles;
-    if (n_split > 16) {
-        n_split = 16;
-    }
-    if (n_split > n_tiles) {
-        n_split = n_tiles;
-    }
-    if (n_split < 1) {
-        n_split = 1;
+    // The number of column ranges (at most 16: the pick kernels take 64 lists per row) that needs the fewest
+    // tile steps: rounds of the persistent CTAs times the tiles of an item.
+    uint64_t n_split = 1, best_cost = ~0ull;
+    for (uint64_t ns = 1; ns <= 16 && ns <= n_tiles; ++ns) {
+        const uint64_t tps = (n_tiles + ns - 1) / ns;
+        const uint64_t ns_eff = (n_tiles + tps - 1) / tps;
+        const uint64_t rounds = (m_tiles * ns_eff + sms - 1) / sms;
+        const uint64_t cost = rounds * tps;
+        if (cost < best_cost) {
+            best_cost = cost;
+            n_split = ns_eff;
+        }
     }
     const uint64_t tiles_per_split = (n_tiles + n_split - 1) / n_split;
     n_split = (n_tiles + tiles_per_split - 1) / tiles_per_split;
