@@ -983,6 +983,66 @@ pair_ball_dot8(const float* __restrict__ qv, const float* __restrict__ cv, uint3
     return dot;
 }
 
+// The same for four consecutive ball centres of a list at once (cv, cv + dim, ...): one trip to memory instead
+// of four for a pair that has to look at several balls.
+__device__ __forceinline__ void
+pair_ball_dot8x4(const float* __restrict__ qv, const float* __restrict__ cv, uint32_t dim, int metric, uint32_t part,
+                 uint32_t gmask, float (&dot)[4]) {
+    dot[0] = dot[1] = dot[2] = dot[3] = 0.f;
+    if ((dim & 3u) == 0 && ((reinterpret_cast<uintptr_t>(qv) | reinterpret_cast<uintptr_t>(cv)) & 15u) == 0) {
+        const float4* q4 = reinterpret_cast<const float4*>(qv);
+        const float4* c4 = reinterpret_cast<const float4*>(cv);
+        const uint32_t row4 = dim >> 2;
+        for (uint32_t i = part; i < row4; i += 8) {
+            const float4 x = __ldg(q4 + i);
+            float4 c[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                c[b] = __ldg(c4 + b * row4 + i);
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (metric == 0) {
+                    float t = x.x - c[b].x;
+                    dot[b] = fmaf(t, t, dot[b]);
+                    t = x.y - c[b].y;
+                    dot[b] = fmaf(t, t, dot[b]);
+                    t = x.z - c[b].z;
+                    dot[b] = fmaf(t, t, dot[b]);
+                    t = x.w - c[b].w;
+                    dot[b] = fmaf(t, t, dot[b]);
+                } else {
+                    dot[b] = fmaf(x.x, c[b].x, dot[b]);
+                    dot[b] = fmaf(x.y, c[b].y, dot[b]);
+                    dot[b] = fmaf(x.z, c[b].z, dot[b]);
+                    dot[b] = fmaf(x.w, c[b].w, dot[b]);
+                }
+            }
+        }
+    } else {
+        for (uint32_t d = part; d < dim; d += 8) {
+            const float x = __ldg(qv + d);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float c = __ldg(cv + b * dim + d);
+                if (metric == 0) {
+                    const float t = x - c;
+                    dot[b] = fmaf(t, t, dot[b]);
+                } else {
+                    dot[b] = fmaf(x, c, dot[b]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            dot[b] += __shfl_xor_sync(gmask, dot[b], o);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256)
 pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe,
                          const uint32_t* __restrict__ first_live, uint32_t nlist, uint32_t rank, uint32_t world,
@@ -1056,20 +1116,29 @@ pair_drop_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t np
             }
             bool any = false;      // some ball may hold a row within the bound
             if (!beyond) {
+                static_assert(SQ8_BALLS % 4 == 0, "a list's ball slots are read four at a time");
                 const uint32_t n_balls = __ldg(ball_count + pl);
                 const float* cv = ball_centre + static_cast<uint64_t>(pl) * SQ8_BALLS * dim;
-                for (uint32_t j = 0; j < n_balls && !any; ++j, cv += dim) {
-                    const float r = __ldg(ball_radius + static_cast<uint64_t>(pl) * SQ8_BALLS + j);
-                    if (r >= 0.f) {
-                        // slack: the distances compared here and in the scan differ in rounding only
-                        const float dot = pair_ball_dot8(qv, cv, dim, metric, part, gmask);
-                        if (metric == 0) {
-                            const float gap = sqrtf(dot) - r;
-                            const float lower = gap > 0.f ? gap * gap : 0.f;
-                            any = !(lower > pbound * 1.001f + 1e-4f * dot);
-                        } else {
-                            const float lower = 1.0f - dot - sqrtf(qq) * r;
-                            any = !(lower > pbound + 1e-3f * (fabsf(pbound) + fabsf(dot) + 1.0f));
+                // four balls per trip (every list owns SQ8_BALLS slots, so slots past n_balls may be read; they are
+                // not judged)
+                for (uint32_t j0 = 0; j0 < n_balls && !any; j0 += 4, cv += 4 * static_cast<size_t>(dim)) {
+                    float dots[4];
+                    pair_ball_dot8x4(qv, cv, dim, metric, part, gmask, dots);
+#pragma unroll
+                    for (uint32_t b = 0; b < 4; ++b) {
+                        const uint32_t j = j0 + b;
+                        const float r = j < n_balls ? __ldg(ball_radius + static_cast<uint64_t>(pl) * SQ8_BALLS + j) : -1.f;
+                        if (r >= 0.f && !any) {
+                            // slack: the distances compared here and in the scan differ in rounding only
+                            const float dot = dots[b];
+                            if (metric == 0) {
+                                const float gap = sqrtf(dot) - r;
+                                const float lower = gap > 0.f ? gap * gap : 0.f;
+                                any = !(lower > pbound * 1.001f + 1e-4f * dot);
+                            } else {
+                                const float lower = 1.0f - dot - sqrtf(qq) * r;
+                                any = !(lower > pbound + 1e-3f * (fabsf(pbound) + fabsf(dot) + 1.0f));
+                            }
                         }
                     }
                 }
