@@ -90,6 +90,7 @@ struct SearchWorkspace {
     DevBuf<uint64_t> part;      // [nq x nprobe x k]
     DevBuf<uint64_t> keys;      // [nq x kscan]
     DevBuf<uint64_t> keys2;     // [nq x k] after rerank
+    bool group_by_stages = false;   // the cooperative grouping launch was refused once: use the four-kernel form
     DevBuf<uint8_t> slot_written;   // [nq x nprobe] SQ8: which slots of `part` a scan kernel wrote
     DevBuf<uint64_t> scalars;   // [0] scan bytes, [1], [2] work-queue heads of the two phases, [3] bytes read, [4] tensor-core scan error flag,
                                 // [5] the deadline passed, [6] the deadline (%globaltimer value; written by deadline_stamp_kernel)
@@ -1315,6 +1316,43 @@ pair_scatter_one(uint64_t e, const int32_t* __restrict__ probes, uint32_t nprobe
         uint32_t s = (first ? t.off[0] : t.off[1])[l] + atomicAdd((first ? t.cursor[0] : t.cursor[1]) + l, 1u);
         (first ? t.q[0] : t.q[1])[s] = qi;
         (first ? t.slot[0] : t.slot[1])[s] = static_cast<uint32_t>(e);
+    }
+}
+
+// The four stages as kernels of their own: the path for a context that cannot hold one CTA per SM resident (the
+// cooperative launch below refuses then), and for comparisons (VB200_GROUP_COOPERATIVE=0).
+__global__ void
+pair_count_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, const uint32_t* __restrict__ first_live,
+                  uint32_t nlist, uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off, PairTables t,
+                  uint32_t phase_sel, const uint8_t* __restrict__ drop) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e < total) {
+        pair_count_one(e, probes, nprobe, first_live, nlist, rank, world, list_off, t, phase_sel, drop);
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+pair_scan_kernel(PairTables t, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ order, uint32_t nlist,
+                 uint32_t qt, uint32_t code_size, uint64_t* __restrict__ scalars) {
+    pair_scan_block(blockIdx.x, t, list_off, order, nlist, qt, code_size, scalars);
+}
+
+__global__ void
+pair_items_kernel(PairTables t, const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ group_off,
+                  const uint32_t* __restrict__ order, uint32_t nlist, uint32_t qt) {
+    const uint32_t pos = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pos < nlist) {
+        pair_items_one(pos, blockIdx.y, t, list_off, group_off, order, qt);
+    }
+}
+
+__global__ void
+pair_scatter_kernel(const int32_t* __restrict__ probes, uint64_t total, uint32_t nprobe, const uint32_t* __restrict__ first_live,
+                    uint32_t nlist, uint32_t rank, uint32_t world, const uint32_t* __restrict__ list_off, PairTables t,
+                    uint32_t phase_sel, const uint8_t* __restrict__ drop) {
+    const uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e < total) {
+        pair_scatter_one(e, probes, nprobe, first_live, nlist, rank, world, list_off, t, phase_sel, drop);
     }
 }
 
@@ -2546,9 +2584,30 @@ ivf_scan_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t kfinal,
         void* args[] = {&a_probes, &a_total, &a_nprobe, &a_first, &a_nlist, &a_rank, &a_world, &a_off, &a_goff, &a_order,
                         &a_tables, &a_ctr, &a_sel, &a_drop, &a_qt, &a_code, &a_scalars};
         // every CTA of a cooperative launch must be resident: one per SM
-        VB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(pair_group_kernel), dim3(static_cast<uint32_t>(sm_count())),
-                                            dim3(1024), args, 0, st));
-        g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+        static const bool cooperative_off =
+            std::getenv("VB200_GROUP_COOPERATIVE") != nullptr && std::getenv("VB200_GROUP_COOPERATIVE")[0] == '0';
+        if (!cooperative_off && !ws.group_by_stages) {
+            const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(pair_group_kernel),
+                                                              dim3(static_cast<uint32_t>(sm_count())), dim3(1024), args, 0, st);
+            if (e == cudaSuccess) {
+                g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+                return 0;
+            }
+            if (e != cudaErrorCooperativeLaunchTooLarge && e != cudaErrorNotSupported) {
+                VB_CUDA(e);
+            }
+            (void)cudaGetLastError();        // the refusal is not an error of this call
+            ws.group_by_stages = true;       // this context cannot hold the grid: stage by stage from now on
+        }
+        VB_CUDA(cudaMemsetAsync(ws.pair_ctr.ptr, 0, 4 * static_cast<size_t>(nlist) * sizeof(uint32_t), st));
+        VB_LAUNCH(pair_count_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist, ix->shard_rank,
+                  ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
+        VB_LAUNCH(pair_scan_kernel, 2, 1024, 0, tables, ix->list_off.ptr, ix->scan_order.ptr, nlist, queries_per_item,
+                  ix->code_size, ws.scalars.ptr);
+        VB_LAUNCH(pair_items_kernel, dim3((nlist + 255) / 256, 2), 256, 0, tables, ix->list_off.ptr, ix->group_off.ptr,
+                  ix->scan_order.ptr, nlist, queries_per_item);
+        VB_LAUNCH(pair_scatter_kernel, blocks, 256, 0, probes_dev, total, nprobe, ws.first_live.ptr, nlist, ix->shard_rank,
+                  ix->shard_world, ix->list_off.ptr, tables, phase_sel, drop);
         return 0;
     };
     // SQ8 with list pruning: the first phase runs alone, then the pairs its bounds rule out are
