@@ -2072,14 +2072,12 @@ route_pick_warp_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t 
 
 constexpr uint32_t ROUTE_PICK_SMALL = 512;   // keys the small sort takes
 
-__global__ void __launch_bounds__(ROUTE_THREADS)
-route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids,
-                  const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
-                  uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
-                  float* __restrict__ probe_dists, const uint8_t* __restrict__ handled, uint32_t nlist) {
-    if (handled != nullptr && handled[blockIdx.x] != 0) {
-        return;   // route_pick_warp_kernel answered this query
-    }
+// One query (q) by the whole CTA.
+__device__ __forceinline__ void
+route_pick_one(const uint64_t q, const float* __restrict__ queries, uint32_t dim, const float* __restrict__ centroids,
+               const uint64_t* __restrict__ lists_keys, const uint32_t* __restrict__ lists_cnt, uint32_t lists,
+               uint32_t cap, uint32_t ncand, uint32_t nprobe, int metric, int32_t* __restrict__ probes,
+               float* __restrict__ probe_dists, uint32_t nlist) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ uint32_t s_off[65];
     __shared__ uint32_t s_lost, s_state[3];
@@ -2090,7 +2088,6 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);   // [slots] gathered candidates
     uint64_t* small = keys + slots;                            // [ROUTE_PICK_SMALL]
     float* qs = reinterpret_cast<float*>(small + ROUTE_PICK_SMALL);
-    const uint64_t q = blockIdx.x;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (uint32_t d = tid; d < dim; d += blockDim.x) {
         qs[d] = queries[q * dim + d];
@@ -2247,6 +2244,28 @@ route_pick_kernel(const float* __restrict__ queries, uint32_t dim, const float* 
     }
 }
 
+// A CTA takes `per_block` consecutive queries one after the other and passes over those route_pick_warp_kernel
+// answered (handled[q] != 0): nearly all of them, which is why the queries are not given a CTA each.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_pick_kernel(const float* __restrict__ queries, uint64_t nq, uint32_t per_block, uint32_t dim,
+                  const float* __restrict__ centroids, const uint64_t* __restrict__ lists_keys,
+                  const uint32_t* __restrict__ lists_cnt, uint32_t lists, uint32_t cap, uint32_t ncand, uint32_t nprobe,
+                  int metric, int32_t* __restrict__ probes, float* __restrict__ probe_dists,
+                  const uint8_t* __restrict__ handled, uint32_t nlist) {
+    for (uint32_t i = 0; i < per_block; ++i) {
+        const uint64_t q = static_cast<uint64_t>(blockIdx.x) * per_block + i;
+        if (q >= nq) {
+            return;
+        }
+        if (handled != nullptr && handled[q] != 0) {
+            continue;
+        }
+        __syncthreads();   // the previous query's shared memory is no longer read
+        route_pick_one(q, queries, dim, centroids, lists_keys, lists_cnt, lists, cap, ncand, nprobe, metric, probes, probe_dists,
+                       nlist);
+    }
+}
+
 // The workspace's scalar block, zeroed when it is first allocated (entry 8, the routing passes' flag, is read at
 // the end of every search whether or not that search routed).
 static int
@@ -2373,9 +2392,10 @@ ivf_route_device(vb200_ivf* ix, const float* q_dev, uint64_t nq, uint32_t nprobe
                               probes_dev, dists_dev, ws.route_handled.ptr);
                     handled = ws.route_handled.ptr;
                 }
-                VB_LAUNCH(route_pick_kernel, static_cast<uint32_t>(nq), 256, smem, q_dev, ix->dim, ix->centroids.ptr,
-                          ws.route_keys.ptr, ws.route_cnt.ptr, lists, cap, ncand, nprobe, ix->metric, probes_dev,
-                          dists_dev, handled, nlist);
+                const uint32_t per_block = handled != nullptr ? 8u : 1u;   // with the warp kernel in front, few queries are left
+                VB_LAUNCH(route_pick_kernel, static_cast<uint32_t>((nq + per_block - 1) / per_block), 256, smem, q_dev, nq, per_block,
+                          ix->dim, ix->centroids.ptr, ws.route_keys.ptr, ws.route_cnt.ptr, lists, cap, ncand, nprobe, ix->metric,
+                          probes_dev, dists_dev, handled, nlist);
                 return 0;
             }
             VB_TRY(sync_stream());   // (more lists than the pick kernels take: the score-matrix path below)
